@@ -1,0 +1,449 @@
+// MoE token dispatch / combine as an active-message all-to-all over peer
+// memory. The reference has only point-to-point active messages
+// (ucx_context/ucx_connection.cpp:353-374: one ucp_am_send_nbx per message);
+// here every routed (token, k) row is one active message whose 16-byte header
+// {src_token, k_slot | local_expert, gate weight, src_rank} and payload row are
+// stored by the sending GPU straight into the destination GPU's receive arena.
+//
+// Receive arena of a rank: `world` regions (one per source rank) of `capacity`
+// rows. Inside a region rows are grouped by local expert, so an expert GEMM can
+// consume them as contiguous groups; per-(src, expert) counts travel with the
+// arrival flag.
+//
+// flags block of a rank (uint64 words):
+//   [0,W)        arrival sequence written by source rank s
+//   [W,2W)       number of rows source rank s sent here
+//   [2W,3W)      "expert output ready" sequence written by expert rank e
+//   [3W,3W+W*EPR) rows per (source rank, local expert)
+//
+// Combine is a pull: the source rank reads its rows back from the expert ranks'
+// arenas with peer loads and accumulates sum_k w_k * y_k in fp32 registers, so
+// the weighted combine is fused into the receive and no intermediate buffer
+// exists.
+#include "eux_device.cuh"
+
+namespace eux {
+
+constexpr int kMoeThreads = 512;
+constexpr int kMaxWorld = 16;
+
+__host__ __device__ __forceinline__ size_t moe_row_bytes(int hidden, int fp8) {
+  return fp8 ? (size_t)hidden + (size_t)(hidden / 128) * 4 : (size_t)hidden * 2;
+}
+
+// ---- routing: slot assignment, grouped by expert (single CTA) --------------
+// counters layout: [0,W) rows per dst rank | [W,W+E) rows per expert | [W+E] done-CTA word
+__global__ void __launch_bounds__(1024) moe_route_kernel(eux_moe_desc d) {
+  extern __shared__ int sm[];
+  int* cnt = sm;                    // [E]
+  int* off = sm + d.n_experts;      // [E]
+  int* cur = sm + 2 * d.n_experts;  // [E]
+  const int E = d.n_experts, W = d.world, EPR = E / W;
+  const int n = d.n_tokens * d.topk;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0, cur[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int e = d.topk_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int base = (e / EPR) * EPR, s = 0;
+    for (int j = base; j < e; ++j) s += cnt[j];
+    off[e] = s;
+    d.counters[W + e] = cnt[e];
+  }
+  for (int r = threadIdx.x; r < W; r += blockDim.x) {
+    int s = 0;
+    for (int j = r * EPR; j < (r + 1) * EPR; ++j) s += cnt[j];
+    if (s > d.capacity) set_status(d.status, EUX_ST_OVERFLOW, 10);
+    d.counters[r] = s < d.capacity ? s : d.capacity;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int e = d.topk_idx[i];
+    int slot = -1;
+    if (e >= 0 && e < E) {
+      slot = off[e] + atomicAdd(&cur[e], 1);
+      if (slot >= d.capacity) slot = -1;
+    }
+    d.slot_of[i] = slot;
+  }
+}
+
+__device__ __forceinline__ void moe_publish(const eux_moe_desc& d) {
+  // last CTA: send counts + arrival flags to every destination rank
+  __syncthreads();
+  __shared__ int s_last;
+  const int W = d.world, E = d.n_experts, EPR = E / W;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t old = atomicAdd(reinterpret_cast<uint32_t*>(d.counters + W + E), 1u);
+    s_last = (old == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < W * EPR; i += blockDim.x) {
+    int dst = i / EPR, le = i - dst * EPR;
+    d.flag_peer[dst][3 * W + d.rank * EPR + le] = (uint64_t)d.counters[W + dst * EPR + le];
+  }
+  for (int dst = threadIdx.x; dst < W; dst += blockDim.x) d.flag_peer[dst][W + d.rank] = (uint64_t)d.counters[dst];
+  __threadfence_system();
+  __syncthreads();
+  for (int dst = threadIdx.x; dst < W; dst += blockDim.x) st_release_sys(&d.flag_peer[dst][d.rank], d.seq);
+  if (threadIdx.x == 0) d.counters[W + E] = 0;
+}
+
+// ---- dispatch, bf16 rows ----------------------------------------------------
+// Work unit = (token, 128 consecutive 16-byte chunks): a warp loads 4 chunks per
+// lane once and stores them to each of the token's top-k destinations.
+__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_bf16_kernel(eux_moe_desc d) {
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int chunks = d.hidden / 8;  // uint4 per row
+  const int upr = (chunks + 127) / 128;
+  const size_t row_bytes = (size_t)d.hidden * 2;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int64_t units = (int64_t)d.n_tokens * upr;
+  for (int64_t u = warp; u < units; u += nwarps) {
+    const int t = (int)(u / upr), part = (int)(u - (int64_t)t * upr);
+    const uint4* src = reinterpret_cast<const uint4*>(d.x) + (size_t)t * chunks;
+    const int c0 = part * 128 + lane;
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int c = c0 + 32 * j;
+      if (c < chunks) v[j] = ld_stream_u4(src + c);
+    }
+    // lane k (< topk) owns the routing entry of slot k
+    int my_e = -1, my_slot = -1;
+    float my_w = 0.f;
+    if (lane < K) {
+      my_e = d.topk_idx[t * K + lane];
+      my_slot = d.slot_of[t * K + lane];
+      my_w = d.topk_w[t * K + lane];
+    }
+    for (int k = 0; k < K; ++k) {
+      const int e = __shfl_sync(0xffffffffu, my_e, k);
+      const int slot = __shfl_sync(0xffffffffu, my_slot, k);
+      if (slot < 0) continue;
+      const int dst = e / EPR;
+      const size_t row = (size_t)d.rank * d.capacity + slot;
+      uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(d.arena_peer[dst]) + row * row_bytes);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int c = c0 + 32 * j;
+        if (c < chunks) st_u4(out + c, v[j]);
+      }
+      if (part == 0 && lane == k) {
+        uint4 h;
+        h.x = (uint32_t)t;
+        h.y = (uint32_t)k | ((uint32_t)(e - dst * EPR) << 16);
+        h.z = __float_as_uint(my_w);
+        h.w = (uint32_t)d.rank;
+        st_u4(reinterpret_cast<uint4*>(d.meta_peer[dst]) + row, h);
+      }
+    }
+  }
+  moe_publish(d);
+}
+
+// ---- dispatch, e4m3 rows with one fp32 scale per 128 elements ---------------
+// Work unit = (token, 512 elements): lane holds 16 elements; 8 lanes share a scale.
+__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_fp8_kernel(eux_moe_desc d) {
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int upr = (d.hidden + 511) / 512;
+  const size_t row_bytes = moe_row_bytes(d.hidden, 1);
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int64_t units = (int64_t)d.n_tokens * upr;
+  for (int64_t u = warp; u < units; u += nwarps) {
+    const int t = (int)(u / upr), part = (int)(u - (int64_t)t * upr);
+    const int e0 = part * 512 + lane * 16;  // first element of this lane
+    const bool in = e0 < d.hidden;
+    float f[16];
+    if (in) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(d.x) + (size_t)t * d.hidden + e0);
+      uint4 a = ld_stream_u4(src), b = ld_stream_u4(src + 1);
+      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 x = __bfloat1622float2(pa[j]), y = __bfloat1622float2(pb[j]);
+        f[2 * j] = x.x, f[2 * j + 1] = x.y, f[8 + 2 * j] = y.x, f[8 + 2 * j + 1] = y.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) f[j] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+    const float inv = 1.0f / scale;
+    uint4 q;
+    {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j] * inv, f[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j + 2] * inv, f[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        w[j] = lo | (hi << 16);
+      }
+      q = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    int my_e = -1, my_slot = -1;
+    float my_w = 0.f;
+    if (lane < K) {
+      my_e = d.topk_idx[t * K + lane];
+      my_slot = d.slot_of[t * K + lane];
+      my_w = d.topk_w[t * K + lane];
+    }
+    for (int k = 0; k < K; ++k) {
+      const int e = __shfl_sync(0xffffffffu, my_e, k);
+      const int slot = __shfl_sync(0xffffffffu, my_slot, k);
+      if (slot < 0) continue;
+      const int dst = e / EPR;
+      const size_t row = (size_t)d.rank * d.capacity + slot;
+      unsigned char* out = reinterpret_cast<unsigned char*>(d.arena_peer[dst]) + row * row_bytes;
+      if (in) {
+        st_u4(out + e0, q);
+        if ((lane & 7) == 0) reinterpret_cast<float*>(out + d.hidden)[e0 >> 7] = scale;
+      }
+      if (part == 0 && lane == k) {
+        uint4 h;
+        h.x = (uint32_t)t;
+        h.y = (uint32_t)k | ((uint32_t)(e - dst * EPR) << 16);
+        h.z = __float_as_uint(my_w);
+        h.w = (uint32_t)d.rank;
+        st_u4(reinterpret_cast<uint4*>(d.meta_peer[dst]) + row, h);
+      }
+    }
+  }
+  moe_publish(d);
+}
+
+// ---- expert side: wait for every source, (identity expert), tell the sources -
+__global__ void moe_expert_ready_kernel(eux_moe_desc d) {
+  const int W = d.world;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < W) {
+    if (!wait_flag_ge(&d.flag_peer[d.rank][threadIdx.x], d.seq, d.wait_timeout_ns)) {
+      set_status(d.status, EUX_ST_TIMEOUT, 11);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  // identity expert: the rows already are the expert output
+  if ((int)threadIdx.x < W && s_ok) {
+    __threadfence_system();
+    st_release_sys(&d.flag_peer[threadIdx.x][2 * W + d.rank], d.seq);
+  }
+}
+
+__device__ __forceinline__ bool moe_wait_experts(const eux_moe_desc& d) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < d.world) {
+    if (!wait_flag_ge(&d.flag_peer[d.rank][2 * d.world + threadIdx.x], d.seq, d.wait_timeout_ns)) {
+      set_status(d.status, EUX_ST_TIMEOUT, 12);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+// ---- combine, bf16: unit = (token, 64 chunks); 16 peer loads in flight per lane
+__global__ void __launch_bounds__(kMoeThreads) moe_combine_bf16_kernel(eux_moe_desc d) {
+  if (!moe_wait_experts(d)) return;
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int chunks = d.hidden / 8;
+  const int upr = (chunks + 63) / 64;
+  const size_t row_bytes = (size_t)d.hidden * 2;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int64_t units = (int64_t)d.n_tokens * upr;
+  for (int64_t u = warp; u < units; u += nwarps) {
+    const int t = (int)(u / upr), part = (int)(u - (int64_t)t * upr);
+    const int c0 = part * 64 + lane, c1 = c0 + 32;
+    const unsigned char* my_row = nullptr;
+    float my_w = 0.f;
+    if (lane < K) {
+      int e = d.topk_idx[t * K + lane];
+      int slot = d.slot_of[t * K + lane];
+      if (slot >= 0) {
+        int dst = e / EPR;
+        my_row = reinterpret_cast<const unsigned char*>(d.arena_peer[dst]) + ((size_t)d.rank * d.capacity + slot) * row_bytes;
+        my_w = d.topk_w[t * K + lane];
+      }
+    }
+    float acc0[8], acc1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc0[j] = 0.f, acc1[j] = 0.f;
+    for (int kb = 0; kb < K; kb += 8) {
+      uint4 v0[8], v1[8];
+      float w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const unsigned char* row = (const unsigned char*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, (kb + k) & 31);
+        w[k] = __shfl_sync(0xffffffffu, my_w, (kb + k) & 31);
+        if (kb + k >= K) row = nullptr;
+        v0[k] = make_uint4(0, 0, 0, 0);
+        v1[k] = make_uint4(0, 0, 0, 0);
+        if (row) {
+          if (c0 < chunks) v0[k] = ld_cg_u4(reinterpret_cast<const uint4*>(row) + c0);
+          if (c1 < chunks) v1[k] = ld_cg_u4(reinterpret_cast<const uint4*>(row) + c1);
+        } else {
+          w[k] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&v0[k]);
+        const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&v1[k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 a = __bfloat1622float2(p0[j]), b = __bfloat1622float2(p1[j]);
+          acc0[2 * j] = fmaf(w[k], a.x, acc0[2 * j]);
+          acc0[2 * j + 1] = fmaf(w[k], a.y, acc0[2 * j + 1]);
+          acc1[2 * j] = fmaf(w[k], b.x, acc1[2 * j]);
+          acc1[2 * j + 1] = fmaf(w[k], b.y, acc1[2 * j + 1]);
+        }
+      }
+    }
+    uint4* out = reinterpret_cast<uint4*>(d.out) + (size_t)t * chunks;
+    uint4 o0, o1;
+    __nv_bfloat162* q0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+    __nv_bfloat162* q1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      q0[j] = __floats2bfloat162_rn(acc0[2 * j], acc0[2 * j + 1]);
+      q1[j] = __floats2bfloat162_rn(acc1[2 * j], acc1[2 * j + 1]);
+    }
+    if (c0 < chunks) st_stream_u4(out + c0, o0);
+    if (c1 < chunks) st_stream_u4(out + c1, o1);
+  }
+}
+
+// ---- combine, fp8 rows: lane owns 16 elements; dequantise while accumulating --
+__global__ void __launch_bounds__(kMoeThreads) moe_combine_fp8_kernel(eux_moe_desc d) {
+  if (!moe_wait_experts(d)) return;
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int upr = (d.hidden + 511) / 512;
+  const size_t row_bytes = moe_row_bytes(d.hidden, 1);
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int64_t units = (int64_t)d.n_tokens * upr;
+  for (int64_t u = warp; u < units; u += nwarps) {
+    const int t = (int)(u / upr), part = (int)(u - (int64_t)t * upr);
+    const int e0 = part * 512 + lane * 16;
+    const bool in = e0 < d.hidden;
+    const unsigned char* my_row = nullptr;
+    float my_w = 0.f;
+    if (lane < K) {
+      int e = d.topk_idx[t * K + lane];
+      int slot = d.slot_of[t * K + lane];
+      if (slot >= 0) {
+        int dst = e / EPR;
+        my_row = reinterpret_cast<const unsigned char*>(d.arena_peer[dst]) + ((size_t)d.rank * d.capacity + slot) * row_bytes;
+        my_w = d.topk_w[t * K + lane];
+      }
+    }
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+    for (int kb = 0; kb < K; kb += 8) {
+      uint4 v[8];
+      float w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const unsigned char* row = (const unsigned char*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, (kb + k) & 31);
+        float wk = __shfl_sync(0xffffffffu, my_w, (kb + k) & 31);
+        if (kb + k >= K) row = nullptr;
+        v[k] = make_uint4(0, 0, 0, 0);
+        w[k] = 0.f;
+        if (row && in) {
+          v[k] = ld_cg_u4(row + e0);
+          w[k] = wk * __ldcg(reinterpret_cast<const float*>(row + d.hidden) + (e0 >> 7));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v[k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(p[j] & 0xffffu), __NV_E4M3);
+          __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(p[j] >> 16), __NV_E4M3);
+          float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+          float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+          acc[4 * j] = fmaf(w[k], a.x, acc[4 * j]);
+          acc[4 * j + 1] = fmaf(w[k], a.y, acc[4 * j + 1]);
+          acc[4 * j + 2] = fmaf(w[k], b.x, acc[4 * j + 2]);
+          acc[4 * j + 3] = fmaf(w[k], b.y, acc[4 * j + 3]);
+        }
+      }
+    }
+    if (in) {
+      uint4 o0, o1;
+      __nv_bfloat162* q0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+      __nv_bfloat162* q1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        q0[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        q1[j] = __floats2bfloat162_rn(acc[8 + 2 * j], acc[8 + 2 * j + 1]);
+      }
+      uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(d.out) + (size_t)t * d.hidden + e0);
+      st_stream_u4(out, o0);
+      st_stream_u4(out + 1, o1);
+    }
+  }
+}
+
+static int moe_check(const eux_moe_desc* d) {
+  if (!d || d->world < 1 || d->world > kMaxWorld || d->rank < 0 || d->rank >= d->world) return EUX_ERR_BAD_ARG;
+  if (d->n_experts % d->world || d->hidden % 128 || d->hidden <= 0 || d->topk < 1 || d->topk > 32) return EUX_ERR_BAD_ARG;
+  if (d->n_experts > 4096 || d->capacity < 1 || d->n_tokens < 0) return EUX_ERR_BAD_ARG;
+  return 0;
+}
+
+}  // namespace eux
+
+using namespace eux;
+
+extern "C" size_t eux_moe_row_bytes(int hidden, int fp8) { return moe_row_bytes(hidden, fp8); }
+
+extern "C" int eux_moe_dispatch_launch(const eux_moe_desc* d, int ctas, void* stream) {
+  if (int rc = moe_check(d)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ctas <= 0) ctas = 296;
+  moe_route_kernel<<<1, 1024, 3 * d->n_experts * sizeof(int), st>>>(*d);
+  if (d->fp8) moe_dispatch_fp8_kernel<<<ctas, kMoeThreads, 0, st>>>(*d);
+  else moe_dispatch_bf16_kernel<<<ctas, kMoeThreads, 0, st>>>(*d);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int eux_moe_expert_ready_launch(const eux_moe_desc* d, void* stream) {
+  if (int rc = moe_check(d)) return rc;
+  moe_expert_ready_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*d);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int eux_moe_combine_launch(const eux_moe_desc* d, int ctas, void* stream) {
+  if (int rc = moe_check(d)) return rc;
+  if (ctas <= 0) ctas = 296;
+  if (d->fp8) moe_combine_fp8_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
+  else moe_combine_bf16_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,455 @@
+// Tensor send/recv data plane (the role UCX's cuda_ipc/cuda_copy transports
+// play under ucp_am_send_nbx in the reference, ucx_context/ucx_connection.cpp:353-398,
+// and the role of the divide-by-two "handler" kernel in
+// ucx_context/ucx_am_context/ucx_am_context_test_cuda_helper.cu:27-78).
+//
+// One kernel does: (optional bounded acquire-wait on an arrival flag) ->
+// strided gather / dense read of the source tensor -> elementwise handler ->
+// dtype cast -> dense store into the destination (normally a slot of the
+// peer's receive arena, mapped into this process) -> system-scope release of
+// a sequence flag. Nothing is staged through the host.
+#include "eux_device.cuh"
+
+namespace eux {
+
+constexpr int kXferThreads = 512;
+
+struct XferArgs {
+  eux_xfer_desc d;
+  uint32_t* counter;
+};
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ float to(float v) { return v; }
+  static __device__ __forceinline__ float from(float f) { return f; }
+};
+template <>
+struct Elem<__half> {
+  static __device__ __forceinline__ float to(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from(float f) { return __float2half_rn(f); }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from(float f) { return __float2bfloat16_rn(f); }
+};
+template <>
+struct Elem<__nv_fp8_e4m3> {
+  static __device__ __forceinline__ float to(__nv_fp8_e4m3 v) { return float(v); }
+  static __device__ __forceinline__ __nv_fp8_e4m3 from(float f) { return __nv_fp8_e4m3(f); }
+};
+
+template <int BYTES>
+struct PackT;
+template <>
+struct PackT<8> {
+  using type = uint2;
+};
+template <>
+struct PackT<16> {
+  using type = uint4;
+};
+
+// Wait (bounded) for the arrival flag; every thread of the CTA learns the outcome.
+__device__ __forceinline__ bool cta_wait_arrival(const eux_xfer_desc& d) {
+  if (d.wait_flag == nullptr) return true;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    bool ok = wait_flag_ge(d.wait_flag, d.wait_value, d.wait_timeout_ns);
+    if (!ok) set_status(d.status, EUX_ST_TIMEOUT, 1);
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+// All stores of this CTA are done; the last CTA of the grid publishes the flag.
+__device__ __forceinline__ void cta_publish(const eux_xfer_desc& d, uint32_t* counter, bool ok) {
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  __threadfence_system();
+  bool last = true;
+  if (gridDim.x > 1) {
+    uint32_t old = atomicAdd(counter, 1u);
+    last = (old == gridDim.x - 1);
+    if (last) {
+      *counter = 0;  // leave the scratch word clean for the next launch
+      __threadfence();
+    }
+  }
+  if (last && ok && d.flag) st_release_sys(d.flag, d.flag_value);
+}
+
+// Dense byte copy, 16 B per access, 4 accesses in flight per thread.
+__device__ __forceinline__ void copy_bytes_grid(const unsigned char* src, unsigned char* dst, uint64_t nbytes,
+                                                uint64_t tid, uint64_t nthreads) {
+  const uint64_t nvec = nbytes >> 4;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  uint64_t i = tid;
+  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
+    uint4 a = ld_cg_u4(s4 + i);
+    uint4 b = ld_cg_u4(s4 + i + nthreads);
+    uint4 c = ld_cg_u4(s4 + i + 2 * nthreads);
+    uint4 e = ld_cg_u4(s4 + i + 3 * nthreads);
+    st_u4(d4 + i, a);
+    st_u4(d4 + i + nthreads, b);
+    st_u4(d4 + i + 2 * nthreads, c);
+    st_u4(d4 + i + 3 * nthreads, e);
+  }
+  for (; i < nvec; i += nthreads) st_u4(d4 + i, ld_cg_u4(s4 + i));
+  for (uint64_t b = (nvec << 4) + tid; b < nbytes; b += nthreads) dst[b] = src[b];
+}
+
+__global__ void __launch_bounds__(kXferThreads) xfer_bytes_kernel(XferArgs a) {
+  const eux_xfer_desc& d = a.d;
+  bool ok = cta_wait_arrival(d);
+  if (ok) {
+    const uint64_t nbytes = d.n_elems * (uint64_t)dtype_size(d.src_dtype);
+    copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.src), reinterpret_cast<unsigned char*>(d.dst), nbytes,
+                    (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
+  }
+  cta_publish(d, a.counter, ok);
+}
+
+// Dense typed path: 8 elements per step, cast + handler fused.
+template <typename S, typename D>
+__global__ void __launch_bounds__(kXferThreads) xfer_typed_kernel(XferArgs a) {
+  const eux_xfer_desc& d = a.d;
+  bool ok = cta_wait_arrival(d);
+  if (ok) {
+    const S* src = reinterpret_cast<const S*>(d.src);
+    D* dst = reinterpret_cast<D*>(d.dst);
+    const uint64_t n8 = d.n_elems >> 3;
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
+    const int op = d.op;
+    const float arg = d.op_arg;
+    using PS = typename PackT<(8 * sizeof(S) >= 32 ? 16 : 8 * sizeof(S))>::type;
+    using PD = typename PackT<(8 * sizeof(D) >= 32 ? 16 : 8 * sizeof(D))>::type;
+    constexpr int NS = 8 * sizeof(S) / sizeof(PS);
+    constexpr int ND = 8 * sizeof(D) / sizeof(PD);
+    for (uint64_t i = tid; i < n8; i += nthreads) {
+      alignas(16) S sv[8];
+      alignas(16) D dv[8];
+#pragma unroll
+      for (int k = 0; k < NS; ++k)
+        reinterpret_cast<PS*>(sv)[k] = __ldcg(reinterpret_cast<const PS*>(src + i * 8) + k);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) dv[k] = Elem<D>::from(apply_op(Elem<S>::to(sv[k]), op, arg));
+#pragma unroll
+      for (int k = 0; k < ND; ++k) reinterpret_cast<PD*>(dst + i * 8)[k] = reinterpret_cast<PD*>(dv)[k];
+    }
+    for (uint64_t e = (n8 << 3) + tid; e < d.n_elems; e += nthreads)
+      dst[e] = Elem<D>::from(apply_op(Elem<S>::to(src[e]), op, arg));
+  }
+  cta_publish(d, a.counter, ok);
+}
+
+// Strided gather (and the catch-all for unaligned bases): one element per step.
+__global__ void __launch_bounds__(kXferThreads) xfer_strided_kernel(XferArgs a) {
+  const eux_xfer_desc& d = a.d;
+  bool ok = cta_wait_arrival(d);
+  if (ok) {
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
+    const bool raw = (d.src_dtype == d.dst_dtype && d.op == EUX_OP_NONE) || d.src_dtype == EUX_DT_BYTES;
+    const int esz = dtype_size(d.src_dtype);
+    for (uint64_t e = tid; e < d.n_elems; e += nthreads) {
+      uint64_t rem = e;
+      int64_t off = 0;
+      if (d.ndim == 0) {
+        off = (int64_t)e;
+      } else {
+        for (int k = d.ndim - 1; k >= 0; --k) {
+          uint64_t q = rem / (uint64_t)d.shape[k];
+          off += (int64_t)(rem - q * (uint64_t)d.shape[k]) * d.stride[k];
+          rem = q;
+        }
+      }
+      if (raw) {
+        const unsigned char* s = reinterpret_cast<const unsigned char*>(d.src) + off * esz;
+        unsigned char* t = reinterpret_cast<unsigned char*>(d.dst) + e * esz;
+        if (esz == 4) *reinterpret_cast<uint32_t*>(t) = *reinterpret_cast<const uint32_t*>(s);
+        else if (esz == 2) *reinterpret_cast<uint16_t*>(t) = *reinterpret_cast<const uint16_t*>(s);
+        else *t = *s;
+      } else {
+        store_from_float(d.dst, e, d.dst_dtype, apply_op(load_as_float(d.src, (uint64_t)off, d.src_dtype), d.op, d.op_arg));
+      }
+    }
+  }
+  cta_publish(d, a.counter, ok);
+}
+
+// One CTA per descriptor; meant for many small messages per launch.
+__global__ void __launch_bounds__(256) xfer_batch_kernel(const eux_xfer_desc* descs, int n) {
+  if ((int)blockIdx.x >= n) return;
+  __shared__ eux_xfer_desc d;
+  {
+    const uint32_t* s = reinterpret_cast<const uint32_t*>(descs + blockIdx.x);
+    uint32_t* t = reinterpret_cast<uint32_t*>(&d);
+    for (int i = threadIdx.x; i < (int)(sizeof(eux_xfer_desc) / 4); i += blockDim.x) t[i] = s[i];
+  }
+  __syncthreads();
+  bool ok = true;
+  if (d.wait_flag) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+      bool w = wait_flag_ge(d.wait_flag, d.wait_value, d.wait_timeout_ns);
+      if (!w) set_status(d.status, EUX_ST_TIMEOUT, 2);
+      s_ok = w;
+    }
+    __syncthreads();
+    ok = s_ok != 0;
+  }
+  if (ok) {
+    const uint64_t esz = (uint64_t)dtype_size(d.src_dtype);
+    const bool dense = d.ndim == 0;
+    const bool raw = d.src_dtype == d.dst_dtype && d.op == EUX_OP_NONE;
+    const bool al16 = ((((uintptr_t)d.src) | ((uintptr_t)d.dst)) & 15u) == 0;
+    if (dense && raw && al16) {
+      copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.src), reinterpret_cast<unsigned char*>(d.dst),
+                      d.n_elems * esz, threadIdx.x, blockDim.x);
+    } else if (dense && al16 && d.src_dtype == EUX_DT_F32 && d.dst_dtype == EUX_DT_F32) {
+      const float4* s = reinterpret_cast<const float4*>(d.src);
+      float4* t = reinterpret_cast<float4*>(d.dst);
+      const uint64_t n4 = d.n_elems >> 2;
+      for (uint64_t i = threadIdx.x; i < n4; i += blockDim.x) {
+        float4 v = __ldcg(s + i);
+        v.x = apply_op(v.x, d.op, d.op_arg);
+        v.y = apply_op(v.y, d.op, d.op_arg);
+        v.z = apply_op(v.z, d.op, d.op_arg);
+        v.w = apply_op(v.w, d.op, d.op_arg);
+        t[i] = v;
+      }
+      for (uint64_t e = (n4 << 2) + threadIdx.x; e < d.n_elems; e += blockDim.x)
+        reinterpret_cast<float*>(d.dst)[e] = apply_op(reinterpret_cast<const float*>(d.src)[e], d.op, d.op_arg);
+    } else {
+      for (uint64_t e = threadIdx.x; e < d.n_elems; e += blockDim.x) {
+        uint64_t rem = e;
+        int64_t off = dense ? (int64_t)e : 0;
+        if (!dense)
+          for (int k = d.ndim - 1; k >= 0; --k) {
+            uint64_t q = rem / (uint64_t)d.shape[k];
+            off += (int64_t)(rem - q * (uint64_t)d.shape[k]) * d.stride[k];
+            rem = q;
+          }
+        if (raw) {
+          const unsigned char* s = reinterpret_cast<const unsigned char*>(d.src) + off * esz;
+          unsigned char* t = reinterpret_cast<unsigned char*>(d.dst) + e * esz;
+          for (uint64_t b = 0; b < esz; ++b) t[b] = s[b];
+        } else {
+          store_from_float(d.dst, e, d.dst_dtype,
+                           apply_op(load_as_float(d.src, (uint64_t)off, d.src_dtype), d.op, d.op_arg));
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && ok && d.flag) {
+    __threadfence_system();
+    st_release_sys(d.flag, d.flag_value);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Device-driven ping-pong: both GPUs run this kernel at the same time (one
+// launch per GPU, never two on the same GPU). The initiator pushes its buffer
+// into the peer's buffer and publishes seq; the echo side waits for seq,
+// pushes the received bytes back and publishes seq on the initiator.
+// initiator == 2 is a single-GPU loopback (no flags, peer_buf is local).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool grid_barrier(uint32_t* bar, uint32_t& gen, uint64_t timeout_ns) {
+  __syncthreads();
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    gen += 1;
+    atomicAdd(bar, 1u);
+    s_ok = wait_u32_ge_gpu(bar, gen * gridDim.x, timeout_ns);
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__global__ void __launch_bounds__(kXferThreads) pingpong_kernel(eux_pingpong_desc d) {
+  uint32_t gen = 0;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
+  __shared__ int s_ok;
+  bool alive = true;
+  for (int it = 0; it < d.iters && alive; ++it) {
+    const uint64_t seq = d.base_seq + 1 + (uint64_t)it;
+    if (d.ts_out && tid == 0) d.ts_out[it] = globaltimer_ns();
+    if (d.initiator == 0) {
+      if (threadIdx.x == 0) s_ok = wait_flag_ge(d.local_flag, seq, d.wait_timeout_ns);
+      __syncthreads();
+      if (!s_ok) { alive = false; break; }
+    }
+    copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.local_buf), reinterpret_cast<unsigned char*>(d.peer_buf),
+                    d.nbytes, tid, nthreads);
+    if (!grid_barrier(d.grid_bar, gen, d.wait_timeout_ns)) { alive = false; break; }
+    if (d.initiator == 2) {
+      copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.peer_buf), reinterpret_cast<unsigned char*>(d.local_buf),
+                      d.nbytes, tid, nthreads);
+      if (!grid_barrier(d.grid_bar, gen, d.wait_timeout_ns)) { alive = false; break; }
+      continue;
+    }
+    if (tid == 0) st_release_sys(d.peer_flag, seq);
+    if (d.initiator == 1) {
+      if (threadIdx.x == 0) s_ok = wait_flag_ge(d.local_flag, seq, d.wait_timeout_ns);
+      __syncthreads();
+      if (!s_ok) { alive = false; break; }
+    }
+  }
+  if (!alive && threadIdx.x == 0) set_status(d.status, EUX_ST_TIMEOUT, 3);
+  if (d.ts_out && tid == 0) d.ts_out[d.iters] = globaltimer_ns();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t old = atomicAdd(d.grid_bar + 1, 1u);
+    if (old == gridDim.x - 1) {
+      d.grid_bar[0] = 0;
+      d.grid_bar[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
+static int num_sms() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+template <typename S>
+static int launch_typed(const XferArgs& a, int grid, cudaStream_t st) {
+  switch (a.d.dst_dtype) {
+    case EUX_DT_F32: xfer_typed_kernel<S, float><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_F16: xfer_typed_kernel<S, __half><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_BF16: xfer_typed_kernel<S, __nv_bfloat16><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_F8E4M3: xfer_typed_kernel<S, __nv_fp8_e4m3><<<grid, kXferThreads, 0, st>>>(a); break;
+    default: return EUX_ERR_BAD_ARG;
+  }
+  return 0;
+}
+
+}  // namespace eux
+
+using namespace eux;
+
+extern "C" int eux_xfer_launch(const eux_xfer_desc* d, uint32_t* scratch_counter, int max_ctas, void* stream) {
+  if (!d || !d->src || !d->dst || d->ndim < 0 || d->ndim > EUX_MAX_DIMS) return EUX_ERR_BAD_ARG;
+  if (d->src_dtype == EUX_DT_BYTES && (d->dst_dtype != EUX_DT_BYTES || d->op != EUX_OP_NONE)) return EUX_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  XferArgs a{*d, scratch_counter};
+  const int sms = num_sms();
+  if (max_ctas <= 0) max_ctas = 2 * sms;
+  const uint64_t src_bytes = d->n_elems * (uint64_t)dtype_size(d->src_dtype);
+  const bool raw = d->src_dtype == d->dst_dtype && d->op == EUX_OP_NONE;
+  const uintptr_t al = ((uintptr_t)d->src) | ((uintptr_t)d->dst);
+  int grid;
+  if (d->ndim == 0 && raw && (al & 15u) == 0) {
+    // 64 B per thread per step; small messages stay on one CTA (no counter traffic)
+    uint64_t want = (src_bytes + (uint64_t)kXferThreads * 64 - 1) / ((uint64_t)kXferThreads * 64);
+    grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
+    if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
+    xfer_bytes_kernel<<<grid, kXferThreads, 0, st>>>(a);
+  } else if (d->ndim == 0 && d->src_dtype != EUX_DT_BYTES && (al & 15u) == 0) {
+    uint64_t want = (d->n_elems / 8 + kXferThreads - 1) / kXferThreads;
+    grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
+    if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
+    int rc = 0;
+    switch (d->src_dtype) {
+      case EUX_DT_F32: rc = launch_typed<float>(a, grid, st); break;
+      case EUX_DT_F16: rc = launch_typed<__half>(a, grid, st); break;
+      case EUX_DT_BF16: rc = launch_typed<__nv_bfloat16>(a, grid, st); break;
+      case EUX_DT_F8E4M3: rc = launch_typed<__nv_fp8_e4m3>(a, grid, st); break;
+      default: rc = EUX_ERR_BAD_ARG;
+    }
+    if (rc) return rc;
+  } else {
+    uint64_t want = (d->n_elems + kXferThreads * 4 - 1) / (kXferThreads * 4);
+    grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
+    if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
+    xfer_strided_kernel<<<grid, kXferThreads, 0, st>>>(a);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int eux_xfer_batch_launch(const eux_xfer_desc* descs_dev, int n, void* stream) {
+  if (n <= 0) return 0;
+  if (!descs_dev) return EUX_ERR_BAD_ARG;
+  xfer_batch_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(descs_dev, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int eux_pingpong_launch(const eux_pingpong_desc* d, int ctas, void* stream) {
+  if (!d || !d->local_buf || !d->peer_buf || !d->grid_bar || (d->nbytes & 15u)) return EUX_ERR_BAD_ARG;
+  if (d->initiator != 2 && (!d->local_flag || !d->peer_flag)) return EUX_ERR_BAD_ARG;
+  const int sms = num_sms();
+  if (ctas <= 0 || ctas > sms) ctas = sms;  // every CTA must be resident: they wait on one another
+  uint64_t want = (d->nbytes + (uint64_t)kXferThreads * 64 - 1) / ((uint64_t)kXferThreads * 64);
+  if ((uint64_t)ctas > want) ctas = (int)(want < 1 ? 1 : want);
+  eux_pingpong_desc dd = *d;
+  void* args[] = {&dd};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)pingpong_kernel, dim3(ctas), dim3(kXferThreads), args, 0,
+                                              (cudaStream_t)stream);
+  return (int)e;
+}
+
+extern "C" int eux_ipc_export(void* dev_ptr, unsigned char handle_out[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, dev_ptr);
+  if (e == cudaSuccess) memcpy(handle_out, &h, 64);
+  return (int)e;
+}
+extern "C" int eux_ipc_open(const unsigned char handle[64], void** dev_ptr_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  return (int)cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+extern "C" int eux_ipc_close(void* dev_ptr) { return (int)cudaIpcCloseMemHandle(dev_ptr); }
+extern "C" int eux_enable_peer_access(int this_dev, int peer_dev) {
+  int can = 0;
+  cudaError_t e = cudaDeviceCanAccessPeer(&can, this_dev, peer_dev);
+  if (e != cudaSuccess) return (int)e;
+  if (!can) return EUX_ERR_UNSUPPORTED;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(this_dev);
+  e = cudaDeviceEnablePeerAccess(peer_dev, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    e = cudaSuccess;
+  }
+  cudaSetDevice(cur);
+  return (int)e;
+}
+extern "C" int eux_device_malloc(void** p, size_t bytes) { return (int)cudaMalloc(p, bytes); }
+extern "C" int eux_device_free(void* p) { return (int)cudaFree(p); }
+extern "C" int eux_host_alloc_mapped(void** host_ptr, void** dev_ptr, size_t bytes) {
+  cudaError_t e = cudaHostAlloc(host_ptr, bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e != cudaSuccess) return (int)e;
+  memset(*host_ptr, 0, bytes);
+  return (int)cudaHostGetDevicePointer(dev_ptr, *host_ptr, 0);
+}
+extern "C" int eux_host_free(void* host_ptr) { return (int)cudaFreeHost(host_ptr); }
+extern "C" const char* eux_error_string(int err) {
+  switch (err) {
+    case EUX_ERR_BAD_ARG: return "eux: bad argument";
+    case EUX_ERR_TOO_LARGE: return "eux: size beyond the supported maximum";
+    case EUX_ERR_UNSUPPORTED: return "eux: unsupported on this device";
+    default: return cudaGetErrorString((cudaError_t)err);
+  }
+}

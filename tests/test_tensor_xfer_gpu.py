@@ -1,0 +1,121 @@
+"""K1 tensor transfer kernels against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _flag(dev):
+    return torch.zeros(4, dtype=torch.int64, device=dev)
+
+
+@pytest.mark.parametrize("nbytes", [16, 4096, 4096 + 48, 1 << 20, (1 << 26) + 16])
+def test_dense_copy_and_flag(cuda_device, nbytes):
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    src = torch.randn(nbytes // 2, device=cuda_device).to(torch.bfloat16)
+    dst = torch.zeros_like(src)
+    flag = _flag(cuda_device)
+    tx.push(src, dst, flag_ptr=flag.data_ptr(), flag_value=7)
+    torch.cuda.synchronize()
+    assert torch.equal(src.view(torch.int16), dst.view(torch.int16))
+    assert int(flag[0]) == 7
+
+
+@pytest.mark.parametrize("sd,dd", [(torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16),
+                                   (torch.float32, torch.float8_e4m3fn), (torch.float16, torch.bfloat16),
+                                   (torch.float8_e4m3fn, torch.float32)])
+@pytest.mark.parametrize("n", [8, 1000, 1 << 20])
+def test_cast(cuda_device, sd, dd, n):
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    src = (torch.randn(n, device=cuda_device) * 3).to(sd)
+    dst = torch.zeros(n, dtype=dd, device=cuda_device)
+    tx.push(src, dst)
+    torch.cuda.synchronize()
+    ref = src.float().to(dd)
+    assert torch.equal(dst.float(), ref.float())
+
+
+@pytest.mark.parametrize("op,arg", [(1, 1.0), (2, 0.5)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_handler_epilogue(cuda_device, op, arg, dt):
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    src = torch.rand(4099, device=cuda_device).mul(2).sub(1).to(dt)
+    dst = torch.zeros_like(src)
+    tx.push(src, dst, op=op, op_arg=arg)
+    torch.cuda.synchronize()
+    ref = (src.float() + arg if op == 1 else src.float() * arg).to(dt)
+    assert torch.equal(dst.float(), ref.float())
+
+
+def test_strided_gather(cuda_device):
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    base = torch.randn(37, 64, 5, device=cuda_device)
+    for view in (base.transpose(0, 2), base[:, ::3, 1:4], base.permute(1, 2, 0)[3:40:2]):
+        assert not view.is_contiguous()
+        dst = torch.zeros(view.numel(), dtype=torch.bfloat16, device=cuda_device)
+        tx.push(view, dst)
+        torch.cuda.synchronize()
+        assert torch.equal(dst.float(), view.contiguous().view(-1).to(torch.bfloat16).float())
+        raw = torch.zeros(view.numel(), dtype=torch.float32, device=cuda_device)
+        tx.push(view, raw)
+        torch.cuda.synchronize()
+        assert torch.equal(raw, view.contiguous().view(-1))
+
+
+def test_batch(cuda_device):
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    g = torch.Generator(device="cpu").manual_seed(3)
+    srcs, dsts, descs = [], [], []
+    flags = torch.zeros(64, dtype=torch.int64, device=cuda_device)
+    for i in range(40):
+        n = int(torch.randint(64, 16384, (1,), generator=g))
+        s = torch.rand(n, device=cuda_device) * 2 - 1
+        d = torch.zeros_like(s)
+        srcs.append(s), dsts.append(d)
+        descs.append(tx.make_desc(s, d.data_ptr(), torch.float32, op=tx.OP_ADD, op_arg=1.0,
+                                  flag_ptr=flags.data_ptr() + 8 * i, flag_value=i + 1))
+    tx.push_batch(descs)
+    torch.cuda.synchronize()
+    for i, (s, d) in enumerate(zip(srcs, dsts)):
+        assert torch.equal(d, s + 1.0)
+        assert int(flags[i]) == i + 1
+
+
+def test_bounded_wait_reports_timeout(cuda_device):
+    """A wait that nothing satisfies ends by itself with a status, not a hang."""
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    src = torch.ones(1024, device=cuda_device)
+    dst = torch.zeros_like(src)
+    never = _flag(cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    out_flag = _flag(cuda_device)
+    tx.push(src, dst, wait_flag_ptr=never.data_ptr(), wait_value=1, wait_timeout_ns=20_000_000,
+            status_ptr=status.data_ptr(), flag_ptr=out_flag.data_ptr(), flag_value=5)
+    torch.cuda.synchronize()
+    assert int(status[0]) & 0xff == 1
+    assert int(out_flag[0]) == 0 and float(dst.sum()) == 0.0
+    # the context is still usable and a satisfied wait goes through
+    never[0] = 1
+    status.zero_()
+    tx.push(src, dst, wait_flag_ptr=never.data_ptr(), wait_value=1, wait_timeout_ns=20_000_000,
+            status_ptr=status.data_ptr(), flag_ptr=out_flag.data_ptr(), flag_value=5)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and int(out_flag[0]) == 5 and torch.equal(src, dst)
+
+
+def test_pingpong_loopback(cuda_device):
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    n = 1 << 22
+    a = torch.randint(0, 255, (n,), dtype=torch.uint8, device=cuda_device)
+    keep = a.clone()
+    b = torch.zeros_like(a)
+    bar = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    ts = torch.zeros(6, dtype=torch.int64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    tx.pingpong(a, b.data_ptr(), n, 0, 0, bar, iters=5, initiator=2, ts_out=ts, status=status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert torch.equal(a, keep) and torch.equal(b, keep)
+    assert int(bar.sum()) == 0
+    d = (ts[1:] - ts[:-1]).tolist()
+    assert all(x > 0 for x in d)
