@@ -1,0 +1,441 @@
+// Remote-GEMM RPC kernel: Y[M,N] = X[M,K] * W[K,N] with the activation X living
+// in the caller's (peer) memory and the result written straight back into the
+// caller's memory. The reference has no GEMM; this is the callee side of an RPC
+// whose handler is a matrix product, fused with the transfer of its argument.
+//
+// One persistent launch, one CTA per SM, three kinds of CTA / warp:
+//   * copy CTAs (blockIdx < copy_ctas): stream 128-row panels of X from the
+//     caller's memory into a local staging buffer with plain 16-byte loads and
+//     stores and publish a per-panel arrival count;
+//   * GEMM CTAs: warp 0 = TMA producer (waits for the panel, then loads A and B
+//     tiles with non-multicast cp.async.bulk.tensor, 128B swizzle), warp 1 =
+//     tcgen05.mma issuer (accumulators in TMEM, two 256-column buffers),
+//     warps 4..7 = epilogue (tcgen05.ld -> bf16 -> 16-byte stores into Y,
+//     which may be peer memory).
+// W is resident in K-major form Wt[N,K] so both operands are K-major.
+//
+// Every wait is bounded: when one runs out the CTA raises an abort flag, stops
+// issuing work, lets its copies land, frees its TMEM and returns with
+// EUX_ST_TIMEOUT in the status word.
+#include <cuda.h>
+
+#include "eux_device.cuh"
+
+namespace eux {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BKB = 128;  // bytes of K per stage row = one 128B swizzle atom
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BKB;   // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BKB;   // 32 KiB
+constexpr int GEMM_THREADS = 256;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
+
+struct GemmParams {
+  const unsigned char* x_src;
+  unsigned char* x_stage;
+  unsigned char* y;
+  int M, N, K;
+  int elem_bytes;
+  uint32_t* panel_flags;
+  uint32_t* sched;
+  uint64_t* done_flag;
+  uint64_t done_value;
+  uint64_t timeout_ns;
+  uint32_t* status;
+  int copy_ctas;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; returns false (and raises *abort) when the limit passes or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, uint64_t timeout_ns) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t limit = timeout_ns ? timeout_ns : 2000000000ull;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort) return false;
+      if (globaltimer_ns() - t0 > limit) {
+        *abort = 1;
+        return false;
+      }
+    }
+  }
+  *abort = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major, 128B-swizzled operand tile: rows are 128 B apart, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)(1024u >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;             // descriptor version
+  d |= (uint64_t)2 << 61;             // SWIZZLE_128B
+  return d;
+}
+
+template <bool FP8>
+__device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
+  const int per_group = GROUP_M * n_blocks;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int rows = min(GROUP_M, m_blocks - g * GROUP_M);
+  mb = g * GROUP_M + r % rows;
+  nb = r / rows;
+}
+
+// instruction descriptor: D=f32, A/B = bf16 (or e4m3), both K-major, M=128, N=BN_
+template <bool FP8, int BN_>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  return (1u << 4) | ((FP8 ? 0u : 1u) << 7) | ((FP8 ? 0u : 1u) << 10) | ((uint32_t)(BN_ >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+// Copy CTAs: all of them work on one panel at a time, in order, so the first
+// panel is complete after 1/copy_ctas of its transfer time.
+__device__ void copy_role(const GemmParams& p) {
+  const size_t row_bytes = (size_t)p.K * p.elem_bytes;
+  const size_t panel_vec = (size_t)BM * row_bytes / 16;
+  const int panels = p.M / BM;
+  const size_t per_cta = (panel_vec + p.copy_ctas - 1) / p.copy_ctas;
+  for (int pn = 0; pn < panels; ++pn) {
+    const uint4* s = reinterpret_cast<const uint4*>(p.x_src + (size_t)pn * BM * row_bytes);
+    uint4* d = reinterpret_cast<uint4*>(p.x_stage + (size_t)pn * BM * row_bytes);
+    const size_t lo = (size_t)blockIdx.x * per_cta;
+    const size_t hi = min(panel_vec, lo + per_cta);
+    size_t i = lo + threadIdx.x;
+    for (; i + 7 * GEMM_THREADS < hi; i += 8 * GEMM_THREADS) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = ld_cg_u4(s + i + j * GEMM_THREADS);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) st_u4(d + i + j * GEMM_THREADS, v[j]);
+    }
+    for (; i < hi; i += GEMM_THREADS) st_u4(d + i, ld_cg_u4(s + i));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");
+      red_release_gpu_add(p.panel_flags + pn, 1u);
+    }
+  }
+}
+
+__device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  __threadfence_system();
+  const uint32_t old = atomicAdd(p.sched, 1u);
+  if (old == gridDim.x - 1) {
+    const bool all_ok = ok && p.sched[1] == 0;
+    for (int i = 0; i < p.M / BM; ++i) p.panel_flags[i] = 0;
+    p.sched[0] = 0;
+    p.sched[1] = 0;
+    __threadfence_system();
+    if (all_ok && p.done_flag) st_release_sys(p.done_flag, p.done_value);
+  }
+}
+
+template <bool FP8>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  if ((int)blockIdx.x < p.copy_ctas) {
+    copy_role(p);
+    finish_cta(p, true);
+    return;
+  }
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  // bars: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int m_blocks = p.M / BM, n_blocks = p.N / BN;
+  const int total = m_blocks * n_blocks;
+  const int k_iters = p.K * p.elem_bytes / BKB;
+  const int kelems = BKB / p.elem_bytes;  // elements of K per stage
+  const int first = (int)blockIdx.x - p.copy_ctas;
+  const int step = (int)gridDim.x - p.copy_ctas;
+  volatile int* abort = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int tile = first; tile < total && !*abort; tile += step) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        if (p.copy_ctas > 0) {
+          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)p.copy_ctas, p.timeout_ns)) {
+            *abort = 1;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort, p.timeout_ns)) break;
+          mbar_expect_tx(full_bar(s), A_STAGE_BYTES + B_STAGE_BYTES);
+          tma_load_2d(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_a, full_bar(s), k * kelems, mb * BM);
+          tma_load_2d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_b, full_bar(s), k * kelems, nb * BN);
+          if (++s == STAGES) s = 0, ph ^= 1u;
+        }
+      }
+      if (*abort) {  // let copies that are still in flight land before the CTA retires
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<FP8, BN>();
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      for (int tile = first; tile < total && !*abort; tile += step, ++it) {
+        const int buf = it & 1;
+        const uint32_t tph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abort, p.timeout_ns)) break;
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + (uint32_t)buf * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(full_bar(s), ph, abort, p.timeout_ns)) break;
+          tc_fence_after();
+          const uint32_t a0 = smem_u32(sA + (size_t)s * A_STAGE_BYTES);
+          const uint32_t b0 = smem_u32(sB + (size_t)s * B_STAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BKB / 32; ++kk) {
+            umma<FP8>(tacc, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), idesc, (uint32_t)((k | kk) != 0));
+          }
+          umma_commit(empty_bar(s));
+          if (++s == STAGES) s = 0, ph ^= 1u;
+        }
+        umma_commit(tfull_bar(buf));
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- epilogue ----------------
+    const int lg = warp - 4;  // TMEM lane group of this warp
+    int it = 0;
+    for (int tile = first; tile < total && !*abort; tile += step, ++it) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      const int buf = it & 1;
+      const uint32_t tph = (uint32_t)(it >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns)) break;
+      tc_fence_after();
+      const int row = mb * BM + lg * 32 + lane;
+      __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)row * p.N + (size_t)nb * BN;
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tbase + c * 32, r);
+        tmem_ld_wait();
+        uint4 o[4];
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) q[j] = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) st_u4(dst + j, o[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+  const bool ok = s_abort == 0;
+  if (!ok && threadIdx.x == 0) {
+    set_status(p.status, EUX_ST_TIMEOUT, 20);
+    atomicExch(p.sched + 1, 1u);
+  }
+  finish_cta(p, ok);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// rows x cols (cols contiguous), box = box_rows x (128 bytes of columns), 128B swizzle
+static int make_map(CUtensorMap* m, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return EUX_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(BKB / elem_bytes), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : EUX_ERR_BAD_ARG;
+}
+
+}  // namespace eux
+
+using namespace eux;
+
+extern "C" int eux_gemm_num_sms(void) {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  return n;
+}
+
+extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
+  if (!d || !d->x_stage || !d->w_t || !d->y_dst || !d->sched || !d->panel_flags) return EUX_ERR_BAD_ARG;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->M % BM || d->N % BN) return EUX_ERR_BAD_ARG;
+  if (d->fp8) return EUX_ERR_UNSUPPORTED;  // the block-scaled variant has its own entry point
+  const int eb = 2;
+  if ((d->K * eb) % BKB) return EUX_ERR_BAD_ARG;
+  const bool pull = d->x_src && d->x_src != d->x_stage;
+  int copy_ctas = pull ? (d->copy_ctas > 0 ? d->copy_ctas : 12) : 0;
+  const int sms = eux_gemm_num_sms();
+  if (copy_ctas >= sms) return EUX_ERR_BAD_ARG;
+  CUtensorMap ma, mb;
+  if (int rc = make_map(&ma, d->x_stage, eb, (uint64_t)d->M, (uint64_t)d->K, BM)) return rc;
+  if (int rc = make_map(&mb, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, BN)) return rc;
+  GemmParams p;
+  p.x_src = (const unsigned char*)d->x_src;
+  p.x_stage = (unsigned char*)d->x_stage;
+  p.y = (unsigned char*)d->y_dst;
+  p.M = d->M, p.N = d->N, p.K = d->K, p.elem_bytes = eb;
+  p.panel_flags = d->panel_flags, p.sched = d->sched;
+  p.done_flag = d->done_flag, p.done_value = d->done_value;
+  p.timeout_ns = d->wait_timeout_ns, p.status = d->status, p.copy_ctas = copy_ctas;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return EUX_ERR_BAD_ARG;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(remote_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
+  }
+  const int tiles = (d->M / BM) * (d->N / BN);
+  int grid = copy_ctas + (tiles < sms - copy_ctas ? tiles : sms - copy_ctas);
+  remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}

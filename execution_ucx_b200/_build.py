@@ -102,7 +102,7 @@ def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
 
     objs, changed = _compile_objects(srcs, cc, "cu", deps, verbose or ptxas_info)
     if changed or not out.exists():
-        _run([NVCC, "-shared", "-o", out, *objs, "-lcuda", "-Xlinker", "-rpath=" + str(CUDA_HOME / "lib64")], verbose)
+        _run([NVCC, "-shared", "-o", out, *objs, "-Xlinker", "-rpath=" + str(CUDA_HOME / "lib64")], verbose)
     return out
 
 

@@ -1,0 +1,69 @@
+"""Remote-GEMM RPC kernel (tcgen05 / TMEM / TMA) as a Python op.
+
+``RemoteGemm`` is the callee side: it holds the resident weight in K-major
+form and, per call, consumes the caller's activation (local, or pulled from
+peer memory by the kernel's copy CTAs while the tensor cores already work on
+the panels that have arrived) and writes Y into the caller's memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _native
+
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+class RemoteGemm:
+    def __init__(self, w: torch.Tensor, max_m: int):
+        """``w`` is W[K,N] (bf16); it is stored once as Wt[N,K] for the kernel."""
+        assert w.dtype == torch.bfloat16 and w.dim() == 2
+        self.K, self.N = w.shape
+        self.w_t = w.t().contiguous()
+        dev = w.device
+        self.max_m = max_m
+        self.x_stage = torch.empty(max_m, self.K, dtype=torch.bfloat16, device=dev)
+        self.panel_flags = torch.zeros(max(1, max_m // 128), dtype=torch.int32, device=dev)
+        self.sched = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def __call__(self, x_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
+                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000) -> None:
+        """Y[m,N] (at ``y_ptr``) = X[m,K] (at ``x_ptr``) @ W. Both addresses may be peer memory."""
+        global _launches
+        if m > self.max_m:
+            raise ValueError("m exceeds the staging buffer")
+        d = _native.GemmDesc()
+        d.x_src = x_ptr
+        d.x_stage = x_ptr if x_is_local else self.x_stage.data_ptr()
+        d.w_t, d.y_dst = self.w_t.data_ptr(), y_ptr
+        d.M, d.N, d.K, d.fp8 = m, self.N, self.K, 0
+        d.panel_flags, d.sched = self.panel_flags.data_ptr(), self.sched.data_ptr()
+        d.done_flag, d.done_value = done_flag_ptr or None, done_value
+        d.wait_timeout_ns, d.status, d.copy_ctas = timeout_ns, self.status.data_ptr(), copy_ctas
+        _native.check(_native.load().eux_gemm_launch(C.byref(d), C.c_void_p(_native.current_stream_ptr())),
+                      "eux_gemm_launch")
+        _launches += 1
+
+    def check_status(self) -> None:
+        s = int(self.status.item())
+        if s:
+            raise RuntimeError(f"remote gemm status code={s & 0xff} where={s >> 8}")
+
+
+def smoke(device) -> None:
+    x = torch.randn(256, 256, device=device).to(torch.bfloat16)
+    w = (torch.randn(256, 512, device=device) * 0.05).to(torch.bfloat16)
+    g = RemoteGemm(w, 256)
+    y = torch.empty(256, 512, dtype=torch.bfloat16, device=device)
+    g(x.data_ptr(), 256, y.data_ptr(), x_is_local=True)
+    torch.cuda.synchronize()
+    g.check_status()
+    torch.testing.assert_close(y.float(), x.float() @ w.float(), rtol=2e-2, atol=2e-2)
