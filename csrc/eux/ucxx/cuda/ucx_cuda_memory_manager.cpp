@@ -1,0 +1,289 @@
+#include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
+
+#include <cuda_runtime_api.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <new>
+#include <stdexcept>
+
+#include "eux/ucxx/cuda/ucx_cuda_macro.h"
+
+namespace eux::ucxx {
+
+namespace {
+constexpr size_t kGranule = 256;
+size_t round_up(size_t n, size_t a) { return (n + a - 1) / a * a; }
+
+// cuMemGetAddressRange through the runtime's driver entry point (no link-time libcuda dependency)
+bool address_range(const void* ptr, void** base, size_t* size) {
+  using Fn = int (*)(unsigned long long*, size_t*, unsigned long long);
+  static Fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<Fn>(p);
+  }();
+  if (!fn) return false;
+  unsigned long long b = 0;
+  size_t s = 0;
+  if (fn(&b, &s, reinterpret_cast<unsigned long long>(ptr)) != 0) return false;
+  *base = reinterpret_cast<void*>(b);
+  *size = s;
+  return true;
+}
+
+class PinnedHostResource final : public std::pmr::memory_resource {
+  void* do_allocate(size_t bytes, size_t) override {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocPortable) != cudaSuccess) throw std::bad_alloc();
+    return p;
+  }
+  void do_deallocate(void* p, size_t, size_t) override { cudaFreeHost(p); }
+  bool do_is_equal(const std::pmr::memory_resource& o) const noexcept override { return this == &o; }
+};
+PinnedHostResource& pinned_resource() {
+  static PinnedHostResource r;
+  return r;
+}
+}  // namespace
+
+UcxCudaMemoryResourceManager::UcxCudaMemoryResourceManager() : UcxCudaMemoryResourceManager(Options{}) {}
+
+UcxCudaMemoryResourceManager::UcxCudaMemoryResourceManager(const Options& opt) : opt_(opt) {
+  if (opt_.pinned_host) register_memory_resource(ucx_memory_type::HOST, pinned_resource());
+  else register_memory_resource(ucx_memory_type::HOST, *std::pmr::new_delete_resource());
+  auto copy = [](cudaMemcpyKind kind) {
+    return [kind](void* d, const void* s, size_t n) -> void* {
+      if (n) EUX_CUDA_CHECK(cudaMemcpy(d, s, n, kind));
+      return d;
+    };
+  };
+  const ucx_memory_type_t dev_kinds[] = {ucx_memory_type::CUDA, ucx_memory_type::CUDA_MANAGED};
+  register_memcpy_fn(ucx_memory_type::HOST, ucx_memory_type::HOST,
+                     [](void* d, const void* s, size_t n) { return std::memcpy(d, s, n); });
+  for (auto k : dev_kinds) {
+    register_memcpy_fn(k, ucx_memory_type::HOST, copy(cudaMemcpyHostToDevice));
+    register_memcpy_fn(ucx_memory_type::HOST, k, copy(cudaMemcpyDeviceToHost));
+    for (auto k2 : dev_kinds) register_memcpy_fn(k, k2, copy(cudaMemcpyDeviceToDevice));
+  }
+}
+
+UcxCudaMemoryResourceManager::~UcxCudaMemoryResourceManager() {
+  release_imports();
+  std::lock_guard lk(mu_);
+  for (auto& a : arenas_) cudaFree(a.base);
+  for (auto& [p, n] : dedicated_) cudaFree(p);
+}
+
+void* UcxCudaMemoryResourceManager::pool_alloc(size_t bytes) {
+  bytes = round_up(bytes ? bytes : 1, kGranule);
+  std::lock_guard lk(mu_);
+  if (bytes > opt_.arena_bytes / 2) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) throw std::bad_alloc();
+    dedicated_[p] = bytes;
+    return p;
+  }
+  for (int pass = 0; pass < 2; ++pass) {
+    for (auto& a : arenas_) {
+      for (auto it = a.free_by_off.begin(); it != a.free_by_off.end(); ++it) {
+        if (it->second < bytes) continue;
+        size_t off = it->first, len = it->second;
+        a.free_by_off.erase(it);
+        if (len > bytes) a.free_by_off[off + bytes] = len - bytes;
+        a.in_use += bytes;
+        return a.base + off;
+      }
+    }
+    Arena a;
+    void* p = nullptr;
+    if (cudaMalloc(&p, opt_.arena_bytes) != cudaSuccess) throw std::bad_alloc();
+    a.base = static_cast<char*>(p);
+    a.size = opt_.arena_bytes;
+    a.free_by_off[0] = a.size;
+    arenas_.push_back(std::move(a));
+  }
+  throw std::bad_alloc();
+}
+
+bool UcxCudaMemoryResourceManager::pool_free(void* p, size_t bytes) {
+  std::lock_guard lk(mu_);
+  if (auto it = dedicated_.find(p); it != dedicated_.end()) {
+    regs_.erase(reinterpret_cast<uintptr_t>(p));
+    cudaFree(p);
+    dedicated_.erase(it);
+    return true;
+  }
+  bytes = round_up(bytes ? bytes : 1, kGranule);
+  for (auto& a : arenas_) {
+    char* c = static_cast<char*>(p);
+    if (c < a.base || c >= a.base + a.size) continue;
+    size_t off = static_cast<size_t>(c - a.base);
+    auto [it, ok] = a.free_by_off.emplace(off, bytes);
+    if (!ok) return false;  // double free
+    a.in_use -= bytes;
+    auto next = std::next(it);
+    if (next != a.free_by_off.end() && it->first + it->second == next->first) {
+      it->second += next->second;
+      a.free_by_off.erase(next);
+    }
+    if (it != a.free_by_off.begin()) {
+      auto prev = std::prev(it);
+      if (prev->first + prev->second == it->first) {
+        prev->second += it->second;
+        a.free_by_off.erase(it);
+      }
+    }
+    return true;
+  }
+  return false;
+}
+
+void* UcxCudaMemoryResourceManager::allocate(ucx_memory_type_t type, size_t bytes, size_t alignment) {
+  switch (type) {
+    case ucx_memory_type::CUDA: return pool_alloc(bytes);
+    case ucx_memory_type::CUDA_MANAGED: {
+      void* p = nullptr;
+      if (cudaMallocManaged(&p, bytes ? bytes : 1) != cudaSuccess) throw std::bad_alloc();
+      return p;
+    }
+    default: {
+      auto* r = get_memory_resource(type);
+      if (!r) throw std::bad_alloc();
+      return r->allocate(bytes, alignment);
+    }
+  }
+}
+
+void UcxCudaMemoryResourceManager::deallocate(ucx_memory_type_t type, void* p, size_t bytes, size_t alignment) {
+  if (!p) return;
+  switch (type) {
+    case ucx_memory_type::CUDA:
+      if (!pool_free(p, bytes)) throw std::invalid_argument("pointer does not belong to the CUDA pool");
+      return;
+    case ucx_memory_type::CUDA_MANAGED: cudaFree(p); return;
+    default: {
+      auto* r = get_memory_resource(type);
+      if (!r) throw std::invalid_argument("no memory resource registered for this memory type");
+      r->deallocate(p, bytes, alignment);
+    }
+  }
+}
+
+void* UcxCudaMemoryResourceManager::memcpy(ucx_memory_type_t dest_type, void* dest, ucx_memory_type_t src_type,
+                                           const void* src, size_t count) {
+  auto fn = get_memcpy_fn(dest_type, src_type);
+  if (!fn) throw std::invalid_argument("no memcpy function registered for this pair of memory types");
+  return fn(dest, src, count);
+}
+
+const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::find_registration(const void* ptr) const {
+  std::lock_guard lk(mu_);
+  auto key = reinterpret_cast<uintptr_t>(ptr);
+  auto it = regs_.upper_bound(key);
+  if (it == regs_.begin()) return nullptr;
+  --it;
+  if (key >= it->first && key < it->first + it->second.size) return &it->second;
+  return nullptr;
+}
+
+const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::register_memory(const void* ptr, size_t) {
+  if (auto* r = find_registration(ptr)) return r;
+  void* base = nullptr;
+  size_t size = 0;
+  if (!address_range(ptr, &base, &size)) return nullptr;
+  Registration reg;
+  reg.base = base;
+  reg.size = size;
+  cudaPointerAttributes attr{};
+  reg.device = cudaPointerGetAttributes(&attr, ptr) == cudaSuccess ? attr.device : opt_.device;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, base) == cudaSuccess) {
+    static_assert(sizeof(h) == 64);
+    std::memcpy(reg.handle, &h, 64);
+    reg.exportable = true;
+  } else {
+    cudaGetLastError();  // clear; the region can still be used inside this process
+  }
+  std::lock_guard lk(mu_);
+  auto [it, ok] = regs_.emplace(reinterpret_cast<uintptr_t>(base), reg);
+  return &it->second;
+}
+
+bool UcxCudaMemoryResourceManager::unregister_memory(const void* ptr) {
+  std::lock_guard lk(mu_);
+  auto key = reinterpret_cast<uintptr_t>(ptr);
+  auto it = regs_.upper_bound(key);
+  if (it == regs_.begin()) return false;
+  --it;
+  if (key < it->first || key >= it->first + it->second.size) return false;
+  regs_.erase(it);
+  return true;
+}
+
+bool UcxCudaMemoryResourceManager::export_region(const void* ptr, size_t len, PeerRegionDesc* out) {
+  const Registration* r = register_memory(ptr, len);
+  if (!r) return false;
+  auto p = reinterpret_cast<uintptr_t>(ptr), b = reinterpret_cast<uintptr_t>(r->base);
+  if (p + len > b + r->size) return false;
+  out->pid = static_cast<uint32_t>(getpid());
+  out->device = r->device;
+  out->base = b;
+  out->offset = p - b;
+  out->length = len;
+  out->exportable = r->exportable;
+  std::memcpy(out->handle, r->handle, 64);
+  return true;
+}
+
+void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d) {
+  if (d.pid == static_cast<uint32_t>(getpid())) {
+    if (d.device != opt_.device) {
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, opt_.device, d.device) != cudaSuccess || !can) return nullptr;
+      cudaError_t e = cudaDeviceEnablePeerAccess(d.device, 0);
+      if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return nullptr;
+      cudaGetLastError();
+    }
+    return reinterpret_cast<void*>(d.base + d.offset);
+  }
+  if (!d.exportable) return nullptr;
+  std::lock_guard lk(mu_);
+  ImportKey key{d.pid, d.base};
+  auto it = imports_.find(key);
+  if (it == imports_.end()) {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, d.handle, 64);
+    void* mapped = nullptr;
+    if (cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    it = imports_.emplace(key, mapped).first;
+  }
+  return static_cast<char*>(it->second) + d.offset;
+}
+
+void UcxCudaMemoryResourceManager::release_imports() {
+  std::lock_guard lk(mu_);
+  for (auto& [k, p] : imports_) cudaIpcCloseMemHandle(p);
+  imports_.clear();
+}
+
+size_t UcxCudaMemoryResourceManager::pooled_bytes() const {
+  std::lock_guard lk(mu_);
+  size_t n = 0;
+  for (auto& a : arenas_) n += a.size;
+  return n;
+}
+size_t UcxCudaMemoryResourceManager::pooled_bytes_in_use() const {
+  std::lock_guard lk(mu_);
+  size_t n = 0;
+  for (auto& a : arenas_) n += a.in_use;
+  return n;
+}
+
+}  // namespace eux::ucxx

@@ -1,0 +1,100 @@
+// CUDA memory resource manager with pooled, registered and peer-exportable
+// device memory.
+//
+// The reference ships a test-grade manager (cudaMalloc per allocation, blocking
+// cudaMemcpy; ucx_context/cuda/ucx_cuda_memory_manager.hpp:43-154) and registers
+// user memory with ucp_mem_map (ucx_am_context.cpp:1128-1147). Here:
+//   * CUDA allocations are carved out of large cudaMalloc arenas (first fit,
+//     256-byte granules, coalescing free list), so a receive never pays for
+//     cudaMalloc and every pooled byte is already registered;
+//   * register_memory() records an allocation (found from any interior pointer)
+//     and export_region() produces a PeerRegionDesc carrying its CUDA IPC
+//     handle, which a peer process opens once with import_region() and caches;
+//   * the same descriptor works inside one process (the address is used as is).
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "eux/ucxx/ucx_memory_resource.hpp"
+
+namespace eux::ucxx {
+
+// Wire-format description of a byte range in some process's device memory.
+struct PeerRegionDesc {
+  uint32_t pid = 0;
+  int32_t device = -1;
+  uint64_t base = 0;    // base address of the allocation in the owner's address space
+  uint64_t offset = 0;  // start of the range inside the allocation
+  uint64_t length = 0;
+  uint8_t exportable = 0;
+  uint8_t reserved[7] = {0};
+  unsigned char handle[64] = {0};  // cudaIpcMemHandle_t of the allocation
+};
+static_assert(sizeof(PeerRegionDesc) == 104, "PeerRegionDesc travels on the wire");
+
+class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
+ public:
+  struct Options {
+    int device = 0;
+    size_t arena_bytes = size_t(64) << 20;
+    bool pinned_host = false;  // HOST allocations from cudaHostAlloc (staging buffers)
+  };
+  struct Registration {
+    void* base = nullptr;
+    size_t size = 0;
+    int device = -1;
+    bool exportable = false;
+    unsigned char handle[64] = {0};
+  };
+
+  UcxCudaMemoryResourceManager();
+  explicit UcxCudaMemoryResourceManager(const Options& opt);
+  ~UcxCudaMemoryResourceManager() override;
+
+  void* allocate(ucx_memory_type_t type, size_t bytes, size_t alignment = 8) override;
+  void deallocate(ucx_memory_type_t type, void* p, size_t bytes, size_t alignment = 8) override;
+  void* memcpy(ucx_memory_type_t dest_type, void* dest, ucx_memory_type_t src_type, const void* src,
+               size_t count) override;
+
+  // Record the allocation that contains ptr (its extent is asked from the driver).
+  const Registration* register_memory(const void* ptr, size_t size);
+  bool unregister_memory(const void* ptr);
+  const Registration* find_registration(const void* ptr) const;
+  // Describe [ptr, ptr+len) for a peer; registers the allocation on first use.
+  bool export_region(const void* ptr, size_t len, PeerRegionDesc* out);
+  // Map a peer's region into this process (cached per owner pid + allocation); nullptr on failure.
+  void* import_region(const PeerRegionDesc& d);
+  void release_imports();
+
+  int device() const { return opt_.device; }
+  size_t pooled_bytes() const;
+  size_t pooled_bytes_in_use() const;
+
+ private:
+  struct Arena {
+    char* base = nullptr;
+    size_t size = 0;
+    std::map<size_t, size_t> free_by_off;  // offset -> length
+    size_t in_use = 0;
+  };
+  void* pool_alloc(size_t bytes);
+  bool pool_free(void* p, size_t bytes);
+  Options opt_;
+  mutable std::mutex mu_;
+  std::vector<Arena> arenas_;
+  std::unordered_map<void*, size_t> dedicated_;  // oversize allocations
+  std::map<uintptr_t, Registration> regs_;       // by base address
+  struct ImportKey {
+    uint32_t pid;
+    uint64_t base;
+    bool operator<(const ImportKey& o) const { return pid != o.pid ? pid < o.pid : base < o.base; }
+  };
+  std::map<ImportKey, void*> imports_;
+};
+
+}  // namespace eux::ucxx

@@ -1,0 +1,302 @@
+// The transport under the active-message context: what libucp is to the
+// reference (ucp_worker_progress, ucp_am_send_nbx, ucp_am_recv_data_nbx,
+// listeners and endpoints; ucx_context/ucx_connection.cpp:184-242, 353-450).
+//
+// Control plane: non-blocking TCP sockets polled by the single worker thread.
+// Every active message is a frame {fixed 40-byte frame header, AM header bytes,
+// segment sizes, payload}. Small host payloads travel inline (eager). Larger
+// ones, scatter-gather ones and every device payload use a rendezvous:
+//
+//   host memory:    RTS -> (receiver posts its buffer) -> CTS -> DATA, read by
+//                   the receiver straight into the posted buffer;
+//   device memory:  RTS carries one PeerRegionDesc (CUDA IPC export) per
+//                   segment; the receiver maps the regions and launches the
+//                   transfer kernel that reads the sender's memory over NVLink
+//                   into the posted device buffer, then answers FIN. The kernel
+//                   signals completion by writing a flag in mapped pinned host
+//                   memory that progress() polls. When the regions cannot be
+//                   mapped (or the receiver wants host memory) the payload is
+//                   staged through host memory with the host protocol.
+//
+// The Worker is single-threaded: every method is called from the thread that
+// runs progress().
+#pragma once
+
+#include <netinet/in.h>
+#include <sys/socket.h>
+
+#include <chrono>
+#include <cstdint>
+#include <deque>
+#include <functional>
+#include <list>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
+#include "eux/ucxx/ucx_context_def.h"
+#include "eux/ucxx/ucx_memory_resource.hpp"
+#include "eux/ucxx/ucx_status.hpp"
+
+namespace eux::ucxx::transport {
+
+class Worker;
+class Endpoint;
+
+using Completion = std::function<void(int status)>;
+
+constexpr uint32_t kFrameMagic = 0x46585545u;  // "EUXF"
+enum FrameType : uint8_t {
+  kHello = 1,
+  kHelloAck = 2,
+  kAmEager = 3,
+  kAmRts = 4,
+  kRndvCts = 5,
+  kRndvData = 6,
+  kRndvFin = 7,
+  kClose = 8,
+};
+enum FrameFlags : uint8_t {
+  kFlagDeviceRegions = 1,  // RTS carries PeerRegionDesc per segment
+  kFlagStage = 2,          // CTS: send the payload through host memory
+};
+
+#pragma pack(push, 1)
+struct FrameHeader {
+  uint32_t magic = kFrameMagic;
+  uint8_t type = 0;
+  uint8_t flags = 0;
+  uint16_t am_id = 0;
+  uint32_t header_len = 0;  // AM header bytes that follow
+  uint32_t seg_count = 0;   // number of payload segments described after the AM header
+  uint64_t payload_len = 0; // total payload bytes (inline for eager / DATA)
+  uint64_t msg_id = 0;
+  uint32_t mem_type = 0;    // ucx_memory_type of the sender's payload
+  int32_t status = 0;       // FIN
+};
+#pragma pack(pop)
+static_assert(sizeof(FrameHeader) == 40);
+
+// Address of a worker, exchanged out of band (what get_ucp_address() returns).
+struct WorkerAddress {
+  uint32_t magic = 0x41585545u;  // "EUXA"
+  uint32_t ipv4 = 0;             // network byte order
+  uint16_t port = 0;             // host byte order
+  uint16_t reserved = 0;
+  uint32_t pid = 0;
+  int32_t device = -1;
+  uint64_t uid = 0;
+  char name[32] = {0};
+  std::vector<std::byte> serialize() const;
+  static bool parse(const std::byte* p, size_t n, WorkerAddress* out);
+};
+
+// An incoming active message as seen by the context (UcxAmDesc in the reference).
+struct AmArrival {
+  Endpoint* ep = nullptr;
+  void* header = nullptr;   // HOST memory from the worker's memory resource; ownership passes to the callee
+  size_t header_len = 0;
+  void* data = nullptr;     // eager payload, HOST memory from the memory resource; ownership passes to the callee
+  size_t data_len = 0;      // total payload bytes
+  bool rndv = false;
+  uint64_t msg_id = 0;
+  uint32_t seg_count = 0;   // > 0 only for scatter-gather sends
+  ucx_memory_type_t sender_mem_type = ucx_memory_type::HOST;
+};
+
+struct ConnRequest {
+  int fd = -1;
+  uint64_t client_id = 0;
+  std::string peer_name;   // "ip:port" of the remote socket
+  std::string worker_name; // name of the remote worker
+  WorkerAddress remote{};
+  std::chrono::steady_clock::time_point arrival;
+  std::vector<char> pending;  // bytes already read past the HELLO frame
+};
+
+struct WorkerOptions {
+  std::string name = "default";
+  uint64_t client_id = 0;
+  int device = -1;               // CUDA device of this worker, -1 = none
+  size_t eager_limit = 8192;     // payloads below this travel inline (host memory)
+  size_t send_copy_limit = 8192; // inline payloads up to this size are copied, so the send completes at once
+};
+
+class Endpoint {
+ public:
+  enum class State { kConnecting, kHelloSent, kConnected, kClosed, kFailed };
+  uint64_t id() const { return reinterpret_cast<uint64_t>(this); }
+  State state() const { return state_; }
+  const std::string& peer_name() const { return peer_name_; }
+  const std::string& remote_worker_name() const { return remote_.name_str; }
+  uint32_t remote_pid() const { return remote_.addr.pid; }
+  int remote_device() const { return remote_.addr.device; }
+  uint64_t remote_client_id() const { return remote_client_id_; }
+  void* user_data = nullptr;  // the UcxConnection that wraps this endpoint
+
+ private:
+  friend class Worker;
+  struct SendItem {
+    std::vector<char> owned;      // frame header + AM header + metadata (+ copied payload)
+    std::vector<ucx_buffer_t> segs;  // user memory that follows `owned` on the wire
+    size_t seg_idx = 0, seg_off = 0, owned_off = 0;
+    Completion done;              // fired when the last byte is written (may be empty)
+    std::shared_ptr<void> keep;   // staging buffer kept alive until written
+  };
+  struct PendingSend {             // rendezvous send waiting for CTS / FIN
+    std::vector<ucx_buffer_t> segs;
+    ucx_memory_type_t mem_type;
+    Completion done;
+  };
+  struct PendingRecv {             // posted rendezvous receive waiting for DATA
+    std::vector<ucx_buffer_t> segs;
+    ucx_memory_type_t mem_type;
+    Completion done;
+    std::shared_ptr<void> bounce;  // host staging when the destination is device memory
+    std::vector<ucx_buffer_t> dev_dsts;  // the real destinations behind the bounce buffer
+    size_t total = 0;
+  };
+  struct RtsInfo {                 // what an RTS said, kept until the receive is posted
+    uint64_t payload_len = 0;
+    ucx_memory_type_t mem_type = ucx_memory_type::HOST;
+    std::vector<uint64_t> seg_sizes;
+    std::vector<PeerRegionDesc> regions;
+  };
+  struct RemoteInfo {
+    WorkerAddress addr{};
+    std::string name_str;
+  };
+
+  Worker* worker_ = nullptr;
+  int fd_ = -1;
+  State state_ = State::kConnecting;
+  std::string peer_name_;
+  RemoteInfo remote_;
+  uint64_t remote_client_id_ = 0;
+  uint64_t next_msg_id_ = 1;
+  std::deque<SendItem> sendq_;
+  bool want_write_ = false;
+  // receive state machine
+  std::vector<char> rbuf_;         // bytes read but not yet consumed
+  size_t rpos_ = 0;
+  bool direct_active_ = false;     // DATA body is being read straight into a posted receive
+  uint64_t direct_msg_ = 0;
+  size_t direct_seg_ = 0, direct_off_ = 0, direct_left_ = 0;
+  std::unordered_map<uint64_t, PendingSend> pending_sends_;
+  std::unordered_map<uint64_t, PendingRecv> pending_recvs_;
+  std::unordered_map<uint64_t, RtsInfo> rts_;
+  Completion on_connected_;
+  bool auto_accepted_ = false;
+};
+
+class Worker {
+ public:
+  Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt);
+  ~Worker();
+  Worker(const Worker&) = delete;
+
+  // ---- callbacks into the context (set once, before progress()) ----
+  std::function<void(AmArrival&&)> on_am;                     // active message arrived
+  std::function<void(ConnRequest&&)> on_conn_request;         // HELLO on an explicit listener
+  std::function<void(Endpoint*)> on_auto_accept;              // connection made through the worker address
+  std::function<void(Endpoint*, int status)> on_ep_error;     // endpoint failed / closed by peer
+
+  // Poll sockets and device completions once; returns the number of events handled.
+  int progress();
+
+  WorkerAddress address() const { return addr_; }
+  const WorkerOptions& options() const { return opt_; }
+  UcxMemoryResourceManager& mr() { return mr_; }
+
+  // Explicit listener (accept_endpoint); returns a UCS status.
+  int listen(const sockaddr* addr, socklen_t len);
+  int listen(uint16_t port);
+  void stop_listening();
+
+  // Start connecting; `done(status)` fires from progress() when the handshake ends.
+  Endpoint* connect(const sockaddr* dst, socklen_t len, const sockaddr* src, socklen_t src_len, Completion done, int* status);
+  Endpoint* connect(const WorkerAddress& addr, Completion done, int* status);
+  Endpoint* accept(ConnRequest&& req, int* status);
+  void reject(ConnRequest&& req);
+  void close(Endpoint* ep, bool notify_peer = true);
+  void destroy(Endpoint* ep);  // free a closed/failed endpoint
+
+  // Active message send. `segs` must stay valid until `done` fires. Returns UCS_OK when
+  // the send completed inline (done is NOT called), UCS_INPROGRESS when it will complete
+  // later, or an error (done is NOT called).
+  int am_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t* segs, size_t seg_count,
+              ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out = nullptr);
+  // Complete a rendezvous receive into `segs` (of `mem_type`). Same return convention.
+  int rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, size_t seg_count, ucx_memory_type_t mem_type,
+                Completion done);
+  // Drop a rendezvous message that will never be received (tells the sender).
+  void rndv_discard(Endpoint* ep, uint64_t msg_id);
+  // Segment sizes announced by the sender of a rendezvous message (empty if unknown).
+  std::vector<uint64_t> rndv_segment_sizes(Endpoint* ep, uint64_t msg_id) const;
+  // Withdraw a pending operation. true: it is gone and its callback will never fire;
+  // false: it is past the point of no return and will complete by itself.
+  bool cancel_send(Endpoint* ep, uint64_t msg_id);
+  bool cancel_recv(Endpoint* ep, uint64_t msg_id);
+
+  size_t endpoint_count() const { return eps_.size(); }
+
+ private:
+  struct Listener {
+    int fd = -1;
+    bool implicit = false;
+  };
+  struct HelloWait {  // accepted socket that has not sent its HELLO yet
+    int fd;
+    bool implicit;
+    std::string peer;
+    std::vector<char> buf;
+    std::chrono::steady_clock::time_point since;
+  };
+  struct DeviceOp {   // transfer kernel in flight
+    uint64_t seq;
+    Endpoint* ep;
+    uint64_t msg_id;
+    Completion done;
+  };
+  Endpoint* new_endpoint(int fd);
+  void fail(Endpoint* ep, int status);
+  void handle_readable(Endpoint* ep);
+  void handle_writable(Endpoint* ep);
+  bool parse_frames(Endpoint* ep);
+  void dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* body);
+  void enqueue(Endpoint* ep, Endpoint::SendItem&& item);
+  void flush(Endpoint* ep);
+  void send_control(Endpoint* ep, uint8_t type, uint8_t flags, uint64_t msg_id, int32_t status = 0);
+  void send_hello(Endpoint* ep, uint8_t type);
+  void accept_pending(Listener& l);
+  void poll_hellos();
+  void start_data_send(Endpoint* ep, uint64_t msg_id, bool staged);
+  int device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
+                  Completion& done);
+  bool ensure_device();
+  void poll_device();
+  void update_interest(Endpoint* ep);
+
+  UcxMemoryResourceManager& mr_;
+  UcxCudaMemoryResourceManager* cuda_mr_ = nullptr;  // non-null when the manager can export/import
+  WorkerOptions opt_;
+  WorkerAddress addr_{};
+  int epfd_ = -1;
+  std::vector<Listener> listeners_;
+  std::list<HelloWait> hellos_;
+  std::unordered_map<Endpoint*, std::unique_ptr<Endpoint>> eps_;
+  std::vector<Endpoint*> graveyard_;
+  std::vector<Endpoint*> reparse_;
+  // device side
+  bool device_ready_ = false, device_failed_ = false;
+  void* stream_ = nullptr;
+  uint64_t* flag_host_ = nullptr;  // mapped pinned memory written by kernels
+  uint64_t* flag_dev_ = nullptr;
+  uint32_t* counter_dev_ = nullptr;
+  uint64_t device_seq_ = 0;
+  std::deque<DeviceOp> device_ops_;
+};
+
+}  // namespace eux::ucxx::transport

@@ -1,0 +1,147 @@
+// RAII buffers, memory resource, lock-free queue, connection manager (CPU only).
+#include <cstring>
+#include <thread>
+
+#include "check.hpp"
+#include "eux/ucxx/lock_free_queue.hpp"
+#include "eux/ucxx/ucx_context_data.hpp"
+#include "eux/ucxx/ucx_status.hpp"
+
+using namespace eux::ucxx;
+
+// counts what is outstanding so leaks and double frees show up
+struct TrackingMr : DefaultUcxMemoryResourceManager {
+  long live = 0;
+  void* allocate(ucx_memory_type_t t, size_t n, size_t a = 8) override {
+    ++live;
+    return DefaultUcxMemoryResourceManager::allocate(t, n, a);
+  }
+  void deallocate(ucx_memory_type_t t, void* p, size_t n, size_t a = 8) override {
+    if (p) --live;
+    DefaultUcxMemoryResourceManager::deallocate(t, p, n, a);
+  }
+};
+
+EUX_TEST(buffer_ownership_and_moves) {
+  TrackingMr mr;
+  {
+    UcxBuffer a(mr, ucx_memory_type::HOST, 128);
+    CHECK(a.data() != nullptr && a.size() == 128 && a.own_buffer());
+    UcxBuffer b(std::move(a));
+    CHECK(a.data() == nullptr && !a.own_buffer());
+    CHECK(b.size() == 128);
+    UcxBuffer c(mr, ucx_memory_type::HOST, 16);
+    c = std::move(b);
+    CHECK_EQ(mr.live, 1);
+  }
+  CHECK_EQ(mr.live, 0);
+  int released = 0;
+  char local[8];
+  {
+    UcxBuffer v(mr, ucx_memory_type::HOST, local, 8, nullptr, true, [&](void* p) { released += (p == local); });
+    UcxBuffer w(std::move(v));
+  }
+  CHECK_EQ(released, 1);  // exactly once, by the last owner
+  {
+    UcxBuffer view(mr, ucx_memory_type::HOST, local, 8, nullptr, false);
+  }
+  CHECK_EQ(mr.live, 0);
+}
+
+EUX_TEST(to_buffer_vec_is_zero_copy_and_checked) {
+  TrackingMr mr;
+  {
+    UcxBuffer big(mr, ucx_memory_type::HOST, 100);
+    char* base = static_cast<char*>(big.data());
+    for (int i = 0; i < 100; ++i) base[i] = char(i);
+    UcxBufferVec v = std::move(big).to_buffer_vec({10, 20, 70});
+    CHECK(v.has_backing_buffer() && v.size() == 3);
+    CHECK(v[0].data == base && v[1].data == base + 10 && v[2].data == base + 30);
+    CHECK_EQ(v.total_size(), 100u);
+    CHECK_THROWS(std::move(v).ExtractBuffers());
+    UcxBufferVec moved(std::move(v));
+    CHECK_EQ(static_cast<char*>(moved[2].data)[0], char(30));
+  }
+  CHECK_EQ(mr.live, 0);
+  UcxBuffer small(mr, ucx_memory_type::HOST, 10);
+  CHECK_THROWS(std::move(small).to_buffer_vec({8, 8}));
+}
+
+EUX_TEST(buffer_vec_extract_and_am_types) {
+  TrackingMr mr;
+  {
+    UcxBufferVec v(mr, ucx_memory_type::HOST, std::vector<size_t>{4, 8, 16});
+    CHECK_EQ(mr.live, 3);
+    auto bufs = std::move(v).ExtractBuffers();
+    CHECK_EQ(bufs.size(), 3u);
+    CHECK(bufs[2].size() == 16 && bufs[2].own_buffer());
+    UcxBufferVec again(std::move(bufs));
+    CHECK_EQ(again.size(), 3u);
+  }
+  CHECK_EQ(mr.live, 0);
+  {
+    UcxAmData d(mr, 16, 64, ucx_memory_type::HOST);
+    CHECK(d.get()->header.size == 16 && d.get()->buffer.size == 64);
+    UcxHeader h = d.move_header();
+    UcxBuffer b = d.move_buffer();
+    CHECK(h.size() == 16 && b.size() == 64 && !d.own_buffer() && !d.owns_header());
+    UcxAmData re(mr, std::move(h), std::move(b));
+    CHECK(re.get()->buffer.size == 64);
+    UcxAmIovec io(mr, 8, {32, 32}, ucx_memory_type::HOST);
+    CHECK_EQ(io.get()->buffer_count, 2u);
+    UcxAmIovec io2(std::move(io));
+    auto vec = io2.move_buffers();
+    CHECK_EQ(vec.size(), 2u);
+  }
+  CHECK_EQ(mr.live, 0);
+}
+
+EUX_TEST(memory_resource_tables) {
+  DefaultUcxMemoryResourceManager mr;
+  CHECK(mr.get_memory_resource(ucx_memory_type::HOST) != nullptr);
+  CHECK(mr.get_memory_resource(ucx_memory_type::CUDA) == nullptr);
+  CHECK_THROWS(mr.allocate(ucx_memory_type::CUDA, 16));
+  char a[4] = {1, 2, 3, 4}, b[4] = {};
+  mr.memcpy(ucx_memory_type::HOST, b, ucx_memory_type::HOST, a, 4);
+  CHECK_EQ(b[3], 4);
+  CHECK_THROWS(mr.memcpy(ucx_memory_type::CUDA, b, ucx_memory_type::HOST, a, 4));
+  int calls = 0;
+  mr.register_memcpy_fn(ucx_memory_type::CUDA, ucx_memory_type::HOST, [&](void* d, const void* s, size_t n) { ++calls; return std::memcpy(d, s, n); });
+  mr.memcpy(ucx_memory_type::CUDA, b, ucx_memory_type::HOST, a, 4);
+  CHECK_EQ(calls, 1);
+}
+
+EUX_TEST(status_category) {
+  std::error_code ok = make_error_code(UCS_OK), prog = make_error_code(UCS_INPROGRESS), to = make_error_code(UCS_ERR_TIMED_OUT);
+  CHECK(std::string(ok.category().name()) == "UCX");
+  CHECK(ok == std::error_condition(0, std::generic_category()));
+  CHECK(prog == std::error_condition(0, std::generic_category()));
+  CHECK(to == std::errc::timed_out);
+  CHECK(to.message() == "Operation timed out");
+}
+
+EUX_TEST(lock_free_queue_mpmc) {
+  LockFreeQueue<int> q;
+  CHECK(!q.pop().has_value());
+  const int P = 4, N = 20000;
+  std::atomic<long> sum{0};
+  std::atomic<int> popped{0};
+  std::vector<std::thread> th;
+  for (int p = 0; p < P; ++p) th.emplace_back([&, p] { for (int i = 0; i < N; ++i) q.push(p * N + i); });
+  for (int c = 0; c < P; ++c)
+    th.emplace_back([&] {
+      while (popped.load() < P * N) {
+        if (auto v = q.pop()) {
+          sum += *v;
+          popped.fetch_add(1);
+        }
+      }
+    });
+  for (auto& t : th) t.join();
+  long want = 0;
+  for (long i = 0; i < long(P) * N; ++i) want += i;
+  CHECK_EQ(sum.load(), want);
+  CHECK(q.empty());
+}
+
+EUX_TEST_MAIN()
