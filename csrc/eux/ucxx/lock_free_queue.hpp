@@ -3,18 +3,35 @@
 // ucx_context/lock_free_queue.hpp:35-166. Nodes retired by pop() are kept on a
 // lock-free free list and reused, so a node's memory is never returned to the
 // allocator while another thread may still dereference it (that also removes
-// the per-push allocation); counted pointers guard against ABA.
+// the per-push allocation); counted pointers guard against ABA. A consumer reads
+// the value before it tries to win the head, and a reused node may be refilled
+// while a slow consumer still reads it (its compare-exchange then fails and the
+// value is dropped), so values live in a relaxed atomic word: T must be
+// trivially copyable and at most 8 bytes (indices, ids, pointers).
 #pragma once
 
 #include <atomic>
 #include <cstdint>
+#include <cstring>
 #include <optional>
+#include <type_traits>
 #include <utility>
 
 namespace eux::ucxx {
 
 template <class T>
 class LockFreeQueue {
+  static_assert(std::is_trivially_copyable_v<T> && sizeof(T) <= 8, "LockFreeQueue holds small trivially copyable values");
+  static std::uint64_t to_word(const T& v) {
+    std::uint64_t w = 0;
+    std::memcpy(&w, &v, sizeof(T));
+    return w;
+  }
+  static T from_word(std::uint64_t w) {
+    T v;
+    std::memcpy(&v, &w, sizeof(T));
+    return v;
+  }
   struct Node;
   // Counted pointer packed into one 64-bit word (48-bit address, 16-bit tag) so
   // that every compare-exchange is a plain lock-free 8-byte operation.
@@ -55,7 +72,7 @@ class LockFreeQueue {
   };
   struct Node {
     AtomicPtr next;
-    std::optional<T> value;
+    std::atomic<std::uint64_t> value{0};
   };
 
  public:
@@ -80,7 +97,7 @@ class LockFreeQueue {
 
   void push(T v) {
     Node* n = acquire();
-    n->value.emplace(std::move(v));
+    n->value.store(to_word(v), std::memory_order_relaxed);
     for (;;) {
       Ptr tail = tail_.load(std::memory_order_acquire);
       Ptr next = tail.p->next.load(std::memory_order_acquire);
@@ -108,10 +125,10 @@ class LockFreeQueue {
         tail_.compare_exchange_strong(tail, Ptr{next.p, tail.tag + 1}, std::memory_order_release);
         continue;
       }
-      // Only the thread whose CAS wins may touch next.p->value.
+      // read first: once the head moves past next.p another consumer may retire and refill it
+      const std::uint64_t word = next.p->value.load(std::memory_order_relaxed);
       if (head_.compare_exchange_weak(head, Ptr{next.p, head.tag + 1}, std::memory_order_acq_rel)) {
-        std::optional<T> out(std::move(*next.p->value));
-        next.p->value.reset();
+        std::optional<T> out(from_word(word));
         release(head.p);
         size_.fetch_sub(1, std::memory_order_relaxed);
         return out;
