@@ -1,0 +1,291 @@
+// rpc_core: wire image (hand-derived golden bytes), dispatcher, builders, async
+// dispatcher, hybrid logical clock (CPU only).
+#include <cstring>
+#include <random>
+
+#include "check.hpp"
+#include "eux/exec/contexts.hpp"
+#include "eux/rpc/async_rpc_dispatcher.hpp"
+#include "eux/rpc/rpc_facade_helpers.hpp"
+
+using namespace eux::rpc;
+using eux::ucxx::DefaultUcxMemoryResourceManager;
+using eux::ucxx::UcxBuffer;
+using eux::ucxx::UcxBufferVec;
+namespace ex = eux::exec;
+
+static int64_t i64_at(const byte_buf& b, size_t pos) { int64_t v; std::memcpy(&v, b.data() + pos, 8); return v; }
+static uint32_t u32_at(const byte_buf& b, size_t pos) { uint32_t v; std::memcpy(&v, b.data() + pos, 4); return v; }
+
+// Layout derived by hand from the offset-mode rules: 56-byte root, params vector at 32,
+// one 104-byte ParamMeta appended at 56 (8-aligned), long strings appended after it.
+EUX_TEST(golden_request_image) {
+  RpcRequestHeader h;
+  h.session_id = session_id_t{0x11223344};
+  h.request_id = request_id_t{7};
+  h.function_id = function_id_t{0xabcd};
+  h.hlc = HybridLogicalClock(0x0102030405060708ull);
+  h.workflow_id = workflow_id_t{9};
+  h.AddParam(int32_t(-5));
+  byte_buf b = Serialize(h);
+  CHECK_EQ(b.size(), 56u + 104u);
+  CHECK_EQ(GetSerializedSize(h), b.size());
+  CHECK_EQ(u32_at(b, 0), 0x11223344u);
+  CHECK_EQ(u32_at(b, 4), 7u);
+  CHECK_EQ(u32_at(b, 8), 0xabcdu);
+  CHECK_EQ(u32_at(b, 12), 0u);  // padding before the 8-aligned clock
+  CHECK_EQ((uint64_t)i64_at(b, 16), 0x0102030405060708ull);
+  CHECK_EQ(u32_at(b, 24), 9u);
+  CHECK_EQ(i64_at(b, 32), 56 - 32);  // vector.el_: distance from the field to the element array
+  CHECK_EQ(u32_at(b, 40), 1u);       // used
+  CHECK_EQ(u32_at(b, 44), 1u);       // allocated
+  CHECK_EQ(b[48], 0);                // self_allocated
+  // ParamMeta at 56: type u8, value variant at +8 {index 0 -> PrimitiveValue {index 3 (int32), storage +8}}, name at +88
+  CHECK_EQ(b[56], (uint8_t)ParamType::PRIMITIVE_INT32);
+  CHECK_EQ(b[64], 0);
+  CHECK_EQ(b[72], 3);
+  int32_t v;
+  std::memcpy(&v, b.data() + 80, 4);
+  CHECK_EQ(v, -5);
+  CHECK_EQ(b[56 + 88], 1);  // empty name = short string
+  CHECK_EQ(b[56 + 89], 0);
+}
+
+EUX_TEST(golden_strings_and_empty_vector) {
+  RpcResponseHeader r;
+  r.session_id = session_id_t{1};
+  r.request_id = request_id_t{2};
+  r.status = RpcStatus(make_error_code(RpcErrc::NOT_FOUND));  // category "RPC": short string
+  byte_buf b = Serialize(r);
+  CHECK_EQ(b.size(), 72u);
+  int32_t sv;
+  std::memcpy(&sv, b.data() + 24, 4);
+  CHECK_EQ(sv, 5);
+  CHECK_EQ(b[32], 1);
+  CHECK(std::memcmp(b.data() + 33, "RPC\0", 4) == 0);
+  CHECK_EQ(i64_at(b, 48), std::numeric_limits<int64_t>::min());  // empty vector: null pointer
+  CHECK_EQ(u32_at(b, 56), 0u);
+  // a string longer than 15 characters goes to the heap form
+  r.AddResult(data::string("a string that is definitely longer than fifteen"));
+  b = Serialize(r);
+  const size_t pm = 72, str = pm + 8 + 8;  // ParamMeta at 72; value storage at +16
+  CHECK_EQ(b[pm], (uint8_t)ParamType::STRING);
+  CHECK_EQ(b[pm + 8], 2);  // variant index of string
+  CHECK_EQ(b[str], 0);     // long form
+  CHECK_EQ(u32_at(b, str + 4), 47u);
+  size_t target = size_t(int64_t(str + 8) + i64_at(b, str + 8));
+  CHECK_EQ(target, 72u + 104u);
+  CHECK(std::memcmp(b.data() + target, "a string that", 13) == 0);
+  CHECK_EQ(b.size(), 72u + 104u + 47u);
+}
+
+EUX_TEST(round_trip_all_kinds) {
+  RpcRequestHeader h;
+  h.session_id = session_id_t{3};
+  h.AddParam(true);
+  h.AddParam(int8_t(-1));
+  h.AddParam(uint16_t(65000));
+  h.AddParam(int64_t(-1234567890123));
+  h.AddParam(3.5f);
+  h.AddParam(2.25);
+  h.AddParam(data::string("short"));
+  h.AddParam(std::string(100, 'x'));
+  h.AddParam(data::vector<int32_t>{1, 2, 3});
+  h.AddParam(data::vector<double>{});
+  h.AddParam(data::vector<bool>{true, false, true});
+  h.AddParam(nullptr);
+  TensorMeta tm;
+  tm.device = {kDLCUDA, 3};
+  tm.ndim = 2;
+  tm.dtype = {kDLBfloat, 16, 1};
+  tm.shape = {4, 8};
+  tm.strides = {8, 1};
+  h.AddParam(tm);
+  TensorMetaVec tv{tm, tm};
+  tv[1].shape = {2, 2};
+  h.AddParam(tv);
+  h.params.back().name = data::string("tensors");
+  byte_buf b = Serialize(h);
+  CHECK_EQ(GetSerializedSize(h), b.size());
+  std::vector<uint8_t> fixed(b.size());
+  FixedBufferWriter w(fixed.data(), fixed.size());
+  CHECK_EQ(SerializeInto(w, h), b.size());
+  CHECK(std::memcmp(fixed.data(), b.data(), b.size()) == 0);
+  std::vector<uint8_t> small(b.size() - 1);
+  FixedBufferWriter w2(small.data(), small.size());
+  CHECK_THROWS(SerializeInto(w2, h));
+  auto d = Deserialize<RpcRequestHeader>(b);
+  CHECK_EQ(d.params.size(), h.params.size());
+  CHECK_EQ(d.GetPrimitive<bool>(0), true);
+  CHECK_EQ(d.GetPrimitive<int8_t>(1), -1);
+  CHECK_EQ(d.GetPrimitive<uint16_t>(2), 65000);
+  CHECK_EQ(d.GetPrimitive<int64_t>(3), -1234567890123);
+  CHECK_EQ(d.GetPrimitive<float>(4), 3.5f);
+  CHECK_EQ(d.GetPrimitive<double>(5), 2.25);
+  CHECK(d.GetString(6) == "short");
+  CHECK_EQ(d.GetString(7).size(), 100u);
+  CHECK((d.GetVector<int32_t>(8) == data::vector<int32_t>{1, 2, 3}));
+  CHECK(d.GetVector<double>(9).empty());
+  CHECK_EQ(d.GetVector<bool>(10).size(), 3u);
+  CHECK(d.GetVector<bool>(10)[2]);
+  CHECK(d.params[11].type == ParamType::VOID);
+  CHECK(d.GetTensor(12) == tm);
+  CHECK(d.GetTensorVec(13)[1].shape == (data::vector<int64_t>{2, 2}));
+  CHECK(d.params[13].name == "tensors");
+  CHECK_THROWS(d.GetPrimitive<int32_t>(0));
+  CHECK_THROWS(d.GetString(99));
+  CHECK_THROWS(Deserialize<RpcRequestHeader>(b.data(), 20));
+  // truncation anywhere must throw or parse, never read outside
+  for (size_t n = 0; n < b.size(); n += 7) {
+    try { (void)Deserialize<RpcRequestHeader>(b.data(), n); } catch (const std::exception&) {}
+  }
+}
+
+static int32_t add(int32_t a, int32_t b) { return a + b; }
+
+EUX_TEST(thousand_add_calls) {
+  RpcDispatcher disp("calc");
+  CHECK(disp.RegisterFunction(function_id_t{1}, &add, data::string("add")));
+  CHECK(!disp.RegisterFunction(function_id_t{1}, &add, data::string("add")));
+  std::mt19937 rng(42);
+  std::uniform_int_distribution<int32_t> dist(-(1 << 20), 1 << 20);
+  RpcRequestBuilder rb;
+  for (int i = 0; i < 1000; ++i) {
+    int32_t a = dist(rng), b = dist(rng);
+    auto req = rb.PrepareRequest({session_id_t{1}, request_id_t{uint32_t(i)}, function_id_t{1}}, a, b);
+    auto res = disp.Dispatch<std::monostate>(Serialize(req));  // through the wire form
+    CHECK(res.header.status.ok());
+    CHECK_EQ(res.header.request_id.v_, uint32_t(i));
+    CHECK_EQ(res.header.GetPrimitive<int32_t>(0), a + b);
+  }
+  auto sig = disp.GetSignature(function_id_t{1});
+  CHECK(sig.has_value());
+  CHECK((sig->param_types == data::vector<ParamType>{ParamType::PRIMITIVE_INT32, ParamType::PRIMITIVE_INT32}));
+  CHECK((sig->return_types == data::vector<ParamType>{ParamType::PRIMITIVE_INT32}));
+  auto blob = disp.GetAllSignatures();
+  auto sigs = RpcDispatcher::DeserializeSignatures(blob.data(), blob.size());
+  CHECK_EQ(sigs.size(), 1u);
+  CHECK(sigs[0].function_name == "add" && sigs[0].instance_name == "calc");
+  // signature-checked request building
+  CHECK_THROWS(rb.PrepareRequest(*sig, {}, int32_t(1)));
+  CHECK_THROWS(rb.PrepareRequest(*sig, {}, int32_t(1), 2.0));
+  auto ok = rb.PrepareRequest(*sig, {}, int32_t(1), int32_t(2));
+  CHECK_EQ(ok.function_id.v_, 1u);
+}
+
+EUX_TEST(dispatch_errors_and_argument_kinds) {
+  DefaultUcxMemoryResourceManager mr;
+  RpcDispatcher disp("svc");
+  auto missing = disp.Dispatch(RpcRequestBuilder{}.PrepareRequest({session_id_t{5}, request_id_t{6}, function_id_t{99}}));
+  CHECK_EQ(missing.header.status.value, int(RpcErrc::NOT_FOUND));
+  CHECK(std::string(missing.header.status.category_name) == "RPC");
+  CHECK_EQ(missing.header.session_id.v_, 5u);
+  CHECK(!missing.header.GetString(0).empty());
+  disp.RegisterFunction(function_id_t{2}, [](int32_t) -> int32_t { throw std::runtime_error("kaput"); }, data::string("thrower"));
+  auto thrown = disp.Dispatch(RpcRequestBuilder{}.PrepareRequest({{}, {}, function_id_t{2}}, int32_t(1)));
+  CHECK_EQ(thrown.header.status.value, int(RpcErrc::INTERNAL));
+  CHECK(thrown.header.GetString(0) == "kaput");
+  auto wrong = disp.Dispatch(RpcRequestBuilder{}.PrepareRequest({{}, {}, function_id_t{2}}, 2.5));
+  CHECK(!wrong.header.status.ok());
+  // header, builder, string, vector, tensor meta and payload by reference
+  disp.RegisterFunction(
+      function_id_t{3},
+      [](const RpcRequestHeader& req, const data::string& s, const data::vector<float>& v, const TensorMeta& m, UcxBuffer& buf,
+         const RpcResponseBuilder& b) {
+        float sum = 0;
+        for (float x : v) sum += x;
+        static_cast<char*>(buf.data())[0] = 'Z';
+        return b.PrepareResponse(req.session_id, req.request_id, data::string(s.str() + "!"), sum, int64_t(m.shape[0]));
+      },
+      data::string("mixed"));
+  TensorMeta m;
+  m.ndim = 1;
+  m.shape = {16};
+  m.strides = {1};
+  UcxBuffer buf(mr, ucx_memory_type::HOST, 16);
+  auto [req, payload] = RpcRequestBuilder{}.PrepareRequest({session_id_t{8}, request_id_t{9}, function_id_t{3}}, data::string("hey"),
+                                                          data::vector<float>{1.f, 2.f}, m, std::move(buf));
+  CHECK(RpcDispatcher::ValidateTensorPayloadConstraints(req.params, payload).ok());
+  auto res = disp.Dispatch(req, payload);
+  CHECK(res.header.status.ok());
+  CHECK(res.header.GetString(0) == "hey!");
+  CHECK_EQ(res.header.GetPrimitive<float>(1), 3.f);
+  CHECK_EQ(res.header.GetPrimitive<int64_t>(2), 16);
+  CHECK_EQ(static_cast<char*>(std::get<UcxBuffer>(payload).data())[0], 'Z');
+  // payload by value needs DispatchMove; payload returned in a tuple
+  disp.RegisterFunction(function_id_t{4}, [&mr](UcxBuffer in) {
+    UcxBufferVec out(mr, ucx_memory_type::HOST, std::vector<size_t>{in.size(), 4});
+    return std::tuple<int32_t, UcxBufferVec>(int32_t(in.size()), std::move(out));
+  }, data::string("consume"));
+  UcxBuffer b2(mr, ucx_memory_type::HOST, 32);
+  auto r4req = RpcRequestBuilder{}.PrepareRequest({{}, {}, function_id_t{4}});
+  CHECK(!disp.Dispatch(r4req, b2).header.status.ok());
+  auto r4 = disp.DispatchMove<UcxBufferVec>(r4req, std::move(b2));
+  CHECK_EQ(r4.header.GetPrimitive<int32_t>(0), 32);
+  CHECK_EQ(r4.payload.size(), 2u);
+  auto sig = disp.GetSignature(function_id_t{4});
+  CHECK(sig->input_payload_type == PayloadType::UCX_BUFFER && sig->return_payload_type == PayloadType::UCX_BUFFER_VEC);
+  // mismatching metadata is caught
+  TensorMeta big = m;
+  big.shape = {1 << 20};
+  data::vector<ParamMeta> ps;
+  ps.emplace_back(big);
+  CHECK(!RpcDispatcher::ValidateTensorPayloadConstraints(ps, payload).ok());
+  // dynamic registration
+  disp.RegisterFunction(function_id_t{5}, data::string("dyn"), {ParamType::PRIMITIVE_INT32}, {ParamType::PRIMITIVE_INT32}, PayloadType::NO_PAYLOAD,
+                        PayloadType::NO_PAYLOAD, [](const RpcRequestHeader& rq, RpcContextPtr, const RpcResponseBuilder& b) -> DynamicRpcResult {
+                          return {b.PrepareResponse(rq.session_id, rq.request_id, int32_t(rq.GetPrimitive<int32_t>(0) * 2)), ReturnedPayload{}};
+                        });
+  CHECK_EQ(disp.Dispatch(RpcRequestBuilder{}.PrepareRequest({{}, {}, function_id_t{5}}, int32_t(21))).header.GetPrimitive<int32_t>(0), 42);
+  CHECK_EQ(disp.FunctionCount(), 4u);
+  static_assert(accepts_every_payload_v<decltype([](auto&&) {})>);
+}
+
+EUX_TEST(async_dispatcher_senders) {
+  ex::static_thread_pool pool(2);
+  AsyncRpcDispatcher disp("async");
+  disp.RegisterFunction(function_id_t{1}, [&](int32_t a, int32_t b) { return ex::on(pool.get_scheduler(), ex::just(a * b)); }, data::string("mul"));
+  disp.RegisterFunction(function_id_t{2}, [](int32_t a) { return a + 1; }, data::string("inc"));
+  disp.RegisterFunction(function_id_t{3}, [&](int32_t) { return ex::on(pool.get_scheduler(), ex::just_from([]() -> int32_t { throw RpcException(RpcErrc::FAILED_PRECONDITION, "nope"); })); },
+                        data::string("fail"));
+  RpcRequestBuilder rb;
+  auto r1 = ex::sync_wait(disp.Dispatch(rb.PrepareRequest({{}, request_id_t{4}, function_id_t{1}}, int32_t(6), int32_t(7))));
+  CHECK(r1 && r1->header.status.ok());
+  CHECK_EQ(r1->header.GetPrimitive<int32_t>(0), 42);
+  CHECK_EQ(r1->header.request_id.v_, 4u);
+  auto r2 = ex::sync_wait(disp.Dispatch(Serialize(rb.PrepareRequest({{}, {}, function_id_t{2}}, int32_t(1)))));
+  CHECK_EQ(r2->header.GetPrimitive<int32_t>(0), 2);
+  auto r3 = ex::sync_wait(disp.Dispatch(rb.PrepareRequest({{}, {}, function_id_t{3}}, int32_t(1))));
+  CHECK_EQ(r3->header.status.value, int(RpcErrc::FAILED_PRECONDITION));
+  CHECK(r3->header.GetString(0) == "nope");
+  auto r4 = ex::sync_wait(disp.Dispatch(rb.PrepareRequest({{}, {}, function_id_t{77}})));
+  CHECK_EQ(r4->header.status.value, int(RpcErrc::NOT_FOUND));
+}
+
+// Fork/join across three simulated nodes: every effect is later than its cause.
+EUX_TEST(hybrid_logical_clock_causality) {
+  using eux::rpc::utils::HybridLogicalClock;
+  HybridLogicalClock a(1000, 0), b(900, 5), c(1000, 7);
+  a.TickLocal(1000);
+  CHECK_EQ(a.PhysicalTimeMs(), 1000u);
+  CHECK_EQ(a.LogicalCounter(), 1);
+  a.TickLocal(1005);
+  CHECK(a == HybridLogicalClock(1005, 0));
+  HybridLogicalClock sent = a;
+  b.Merge(sent, 950);  // b's wall clock is behind: it still moves past the sender
+  CHECK(b > sent);
+  c.Merge(sent, 1001);
+  CHECK(c > sent);
+  HybridLogicalClock join = b;
+  join.Merge(c, 1002);
+  CHECK(join > b && join > c);
+  HybridLogicalClock x(5, 0xffff);
+  x.TickLocal(5);  // counter exhausted: physical part advances
+  CHECK(x == HybridLogicalClock(6, 0));
+  CHECK_EQ(HybridLogicalClock(123, 45).Raw(), (123ull << 16) | 45);
+  HybridLogicalClock now = HybridLogicalClock::Now(), later = now;
+  later.TickLocal();
+  CHECK(later > now);
+}
+
+EUX_TEST_MAIN()
