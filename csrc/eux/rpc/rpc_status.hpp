@@ -102,15 +102,14 @@ class RpcCategoryRegistry {
   std::unordered_map<std::string, const std::error_category*> categories_;
 };
 
-class RpcException : public std::exception {
+// A std::system_error (so generic code can recover the error_code) whose text is the remote or local description.
+class RpcException : public std::system_error {
  public:
-  RpcException(std::error_code ec, std::string what = {}) : ec_(ec), what_(what.empty() ? ec.message() : std::move(what)) {}
+  RpcException(std::error_code ec, std::string what = {}) : std::system_error(ec), what_(what.empty() ? ec.message() : std::move(what)) {}
   RpcException(RpcErrc e, std::string what = {}) : RpcException(make_error_code(e), std::move(what)) {}
   const char* what() const noexcept override { return what_.c_str(); }
-  const std::error_code& code() const noexcept { return ec_; }
 
  private:
-  std::error_code ec_;
   std::string what_;
 };
 

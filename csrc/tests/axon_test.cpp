@@ -1,0 +1,316 @@
+// AxonWorker end to end: two workers over loopback in one process, and a
+// client/server pair in forked processes (address through a pipe).
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <numeric>
+
+#include "check.hpp"
+#include "eux/axon/axon_runtime.hpp"
+
+using namespace eux::axon;
+using namespace eux::rpc;
+using eux::ucxx::DefaultUcxMemoryResourceManager;
+using eux::ucxx::UcxBuffer;
+using eux::ucxx::UcxBufferVec;
+namespace ex = eux::exec;
+namespace autils = eux::axon::utils;
+using namespace std::chrono_literals;
+
+static TensorMeta f32_meta(int64_t n) {
+  TensorMeta m;
+  m.ndim = 1;
+  m.dtype = {kDLFloat, 32, 1};
+  m.shape = {n};
+  m.strides = {1};
+  return m;
+}
+
+struct Pair {
+  std::shared_ptr<DefaultUcxMemoryResourceManager> mr = std::make_shared<DefaultUcxMemoryResourceManager>();
+  AxonWorker server{mr, "server", 4, 2000ms};
+  AxonWorker client{mr, "client", 2, 2000ms};
+  void connect() {
+    CHECK(!server.StartServer());
+    CHECK(!client.StartClient());
+    client.ConnectEndpoint(server.GetLocalAddress(), "server");
+    auto sigs = server.GetLocalSignatures();
+    CHECK(client.RegisterEndpointSignatures("server", sigs.data(), sigs.size()));
+  }
+};
+
+EUX_TEST(hash_contract) {
+  // same inputs, same ids on both ends; different names, different ids
+  uint32_t a = autils::FunctionIdFromName("echo", "server"), b = autils::FunctionIdFromName("echo", "server");
+  CHECK_EQ(a, b);
+  CHECK(a != autils::FunctionIdFromName("echo", "other"));
+  CHECK(a != autils::FunctionIdFromName("echp", "server"));
+  CHECK(autils::StringHash("abc") == autils::DataHash("abc", 3));
+  CHECK(!(autils::StringHash("abc") == autils::StringHash("abd")));
+}
+
+EUX_TEST(ring_buffer_and_slot_map) {
+  autils::RingBuffer<int, 8> rb;
+  CHECK(rb.emplace(3, 30));
+  CHECK(!rb.emplace(11, 110));  // 11 & 7 == 3: slot taken
+  CHECK(!rb.take(11).has_value());
+  CHECK(!rb.take_if(3, [](int v) { return v == 0; }).has_value());
+  CHECK_EQ(*rb.take(3), 30);
+  CHECK(rb.emplace(11, 110));
+  CHECK_EQ(rb.size(), 1u);
+  autils::SlotMap<std::string> sm;
+  auto k1 = sm.insert("one");
+  CHECK(*sm.find(k1) == "one");
+  CHECK(sm.erase(k1));
+  auto k2 = sm.insert("two");
+  CHECK_EQ(k2.index, k1.index);
+  CHECK(sm.find(k1) == nullptr);  // stale generation
+  CHECK(*sm.find(k2) == "two");
+}
+
+EUX_TEST(echo_primitives_and_small_tensor) {
+  Pair p;
+  p.server.RegisterFunction(function_id_t{1}, [](int32_t a, int32_t b) { return a + b; }, "add");
+  p.server.RegisterFunction(function_id_t{2}, [](const TensorMeta& m, UcxBuffer& buf) {
+    float* f = static_cast<float*>(buf.data());
+    for (int64_t i = 0; i < m.shape[0]; ++i) f[i] += 1.0f;
+    UcxBuffer out(buf.mr(), buf.type(), buf.size());
+    std::memcpy(out.data(), buf.data(), buf.size());
+    return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out));
+  }, "plus_one");
+  p.connect();
+  auto r = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{5}, ClientMemoryPolicy{}, int32_t(2), int32_t(40)));
+  CHECK(r.has_value());
+  CHECK(r->header.status.ok());
+  CHECK_EQ(r->header.GetPrimitive<int32_t>(0), 42);
+  CHECK_EQ(r->header.workflow_id.v_, 5u);
+  CHECK(r->header.hlc.Raw() > 0);
+  // eager tensor (256 floats) and rendezvous tensor (64 Ki floats)
+  for (int64_t n : {int64_t(256), int64_t(65536)}) {
+    UcxBuffer buf(*p.mr, ucx_memory_type::HOST, size_t(n) * 4);
+    float* f = static_cast<float*>(buf.data());
+    for (int64_t i = 0; i < n; ++i) f[i] = float(i);
+    auto t = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}, f32_meta(n), std::move(buf)));
+    CHECK(t.has_value() && t->header.status.ok());
+    auto& out = std::get<UcxBuffer>(t->payload);
+    CHECK_EQ(out.size(), size_t(n) * 4);
+    const float* g = static_cast<const float*>(out.data());
+    for (int64_t i = 0; i < n; i += 37) CHECK_EQ(g[i], float(i) + 1.0f);
+    CHECK(t->header.GetTensor(0).shape[0] == n);
+  }
+  // the signature the client learned from the server
+  auto sig = p.client.GetEndpointSignature("server", function_id_t{2});
+  CHECK(sig && sig->function_name == "plus_one" && sig->input_payload_type == PayloadType::UCX_BUFFER);
+}
+
+EUX_TEST(errors_deadline_and_unknown_worker) {
+  Pair p;
+  p.server.RegisterFunction(function_id_t{1}, [](int32_t) -> int32_t { throw RpcException(RpcErrc::FAILED_PRECONDITION, "not today"); }, "fail");
+  p.server.RegisterFunction(function_id_t{2}, [](int32_t ms) {
+    std::this_thread::sleep_for(std::chrono::milliseconds(ms));
+    return ms;
+  }, "sleep");
+  p.connect();
+  auto r = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(1)));
+  CHECK(r && r->header.status.value == int(RpcErrc::FAILED_PRECONDITION));
+  CHECK(r->header.GetString(0) == "not today");
+  auto nf = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{77}, workflow_id_t{}, ClientMemoryPolicy{}));
+  CHECK(nf && nf->header.status.value == int(RpcErrc::NOT_FOUND));
+  CHECK_THROWS(ex::sync_wait(p.client.InvokeRpc("nobody", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{})));
+  // client deadline
+  p.client.SetTimeout(50ms);
+  auto t0 = std::chrono::steady_clock::now();
+  bool deadline = false;
+  try {
+    ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(400)));
+  } catch (const RpcException& e) {
+    deadline = e.code() == make_error_code(RpcErrc::DEADLINE_EXCEEDED);
+  }
+  CHECK(deadline);
+  CHECK(std::chrono::steady_clock::now() - t0 < 350ms);
+  CHECK_EQ(p.client.PendingRpcCount(), 0u);
+  // server deadline: the handler overruns, the caller gets DEADLINE_EXCEEDED from the server
+  p.client.SetTimeout(3000ms);
+  p.server.SetTimeout(50ms);
+  auto sd = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(300)));
+  CHECK(sd && sd->header.status.value == int(RpcErrc::DEADLINE_EXCEEDED));
+  std::this_thread::sleep_for(350ms);  // let the overrunning handler end before the workers go away
+}
+
+EUX_TEST(concurrent_calls_and_buffer_vec) {
+  Pair p;
+  p.server.RegisterFunction(function_id_t{1}, [](int32_t a) { return a * 2; }, "dbl");
+  p.server.RegisterFunction(function_id_t{3}, [](const TensorMetaVec& metas, UcxBufferVec& bufs) {
+    int64_t total = 0;
+    for (size_t i = 0; i < bufs.size(); ++i) {
+      const float* f = static_cast<const float*>(bufs[i].data);
+      for (int64_t k = 0; k < metas[i].shape[0]; ++k) total += int64_t(f[k]);
+    }
+    return total;
+  }, "sum_all");
+  p.connect();
+  // 64 calls in flight at once
+  ex::async_scope scope;
+  std::atomic<int> ok{0};
+  for (int i = 0; i < 64; ++i) {
+    scope.spawn_detached(ex::upon_error(ex::then(p.client.InvokeRpc("server", session_id_t{9}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(i)),
+                                                 [&ok, i](InvokeResult r) {
+                                                   if (r.header.status.ok() && r.header.GetPrimitive<int32_t>(0) == 2 * i) ok.fetch_add(1);
+                                                 }),
+                                        [](std::exception_ptr) {}));
+  }
+  ex::sync_wait(scope.join());
+  CHECK_EQ(ok.load(), 64);
+  // three tensors as one scatter-gather payload
+  TensorMetaVec metas{f32_meta(10), f32_meta(5000), f32_meta(3)};
+  UcxBufferVec bufs(*p.mr, ucx_memory_type::HOST, std::vector<size_t>{40, 20000, 12});
+  int64_t want = 0;
+  for (size_t i = 0; i < 3; ++i) {
+    float* f = static_cast<float*>(bufs[i].data);
+    for (int64_t k = 0; k < metas[i].shape[0]; ++k) {
+      f[k] = float(k % 7);
+      want += k % 7;
+    }
+  }
+  auto r = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{9}, function_id_t{3}, workflow_id_t{}, ClientMemoryPolicy{}, metas, std::move(bufs)));
+  CHECK(r && r->header.status.ok());
+  CHECK_EQ(r->header.GetPrimitive<int64_t>(0), want);
+}
+
+EUX_TEST(memory_policy_backpressure_and_retention) {
+  Pair p;
+  std::atomic<int> provider_calls{0};
+  // the server chooses the receive buffer itself for large payloads
+  CustomMemoryPolicy<UcxBuffer> provider = [&](eux::rpc::utils::TensorMetaSpan metas) {
+    provider_calls.fetch_add(1);
+    return UcxBuffer(*p.mr, ucx_memory_type::HOST, eux::rpc::utils::CalculateTensorSize(metas[0]));
+  };
+  std::vector<uint64_t> retained_ids;
+  RetentionPolicy keep = [&](std::shared_ptr<autils::AxonRequest> req, autils::AxonMessageID id) {
+    retained_ids.push_back(id);
+    return req->header.GetTensor(0).shape[0] > 100000 ? LifecycleStatus::Preserve : LifecycleStatus::Discard;
+  };
+  std::atomic<int> handled{0};
+  p.server.RegisterFunction<UcxBuffer>(function_id_t{1}, [&](const TensorMeta& m, const UcxBuffer& b) {
+    handled.fetch_add(1);
+    return int64_t(b.size());
+  }, "sink", provider, keep);
+  p.server.RegisterFunction(function_id_t{2}, [] { return int32_t(1); }, "control");
+  p.connect();
+  auto call = [&](int64_t n) {
+    UcxBuffer buf(*p.mr, ucx_memory_type::HOST, size_t(n) * 4);
+    std::memset(buf.data(), 1, buf.size());
+    return ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, f32_meta(n), std::move(buf)));
+  };
+  auto small = call(16);  // eager: the provider is not consulted
+  CHECK(small && small->header.GetPrimitive<int64_t>(0) == 64);
+  CHECK_EQ(provider_calls.load(), 0);
+  auto big = call(200000);  // rendezvous: provider picks the buffer, retention keeps the request
+  CHECK(big && big->header.GetPrimitive<int64_t>(0) == 800000);
+  CHECK_EQ(provider_calls.load(), 1);
+  CHECK_EQ(p.server.GetStorage().size(), 1u);
+  CHECK_EQ(retained_ids.size(), 2u);
+  // stored requests can be run again and checkpointed
+  CHECK_EQ(p.server.ProcessStoredRequests(), 1u);
+  CHECK_EQ(handled.load(), 3);
+  char dir[] = "/tmp/eux_axon_XXXXXX";
+  CHECK(mkdtemp(dir) != nullptr);
+  std::string path = p.server.GetStorage().save(*p.mr, dir, "ckpt");
+  eux::axon::storage::AxonStorage restored;
+  CHECK_EQ(restored.load(*p.mr, path), 1u);
+  auto snap = restored.snapshot();
+  CHECK_EQ(std::get<UcxBuffer>(snap[0].second->payload).size(), 800000u);
+  CHECK(snap[0].second->header.GetTensor(0).shape[0] == 200000);
+  unlink(path.c_str());
+  rmdir(dir);
+  CHECK_EQ(p.server.ProcessStoredRequests([](auto, auto) { return LifecycleStatus::Discard; }), 1u);
+  CHECK_EQ(p.server.GetStorage().size(), 0u);
+  // back-pressure with a bypass for the control function
+  p.server.SetRejectMessages(true);
+  p.server.SetBypassRejectionFunction([](const RpcRequestHeader& h) { return h.function_id.v_ == 2; });
+  auto rejected = call(16);
+  CHECK(rejected && !rejected->header.status.ok());
+  CHECK(std::string(rejected->header.status.category_name) == "AxonErrc");
+  CHECK_EQ(rejected->header.status.value, int(errors::AxonErrc::StorageBackpressure));
+  auto ctl = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}));
+  CHECK(ctl && ctl->header.status.ok());
+  p.server.SetRejectMessages(false);
+  CHECK(call(16)->header.status.ok());
+}
+
+EUX_TEST(stop_client_cancels_pending_and_peer_loss_is_an_error) {
+  auto p = std::make_unique<Pair>();
+  p->server.RegisterFunction(function_id_t{1}, [](int32_t ms) {
+    std::this_thread::sleep_for(std::chrono::milliseconds(ms));
+    return ms;
+  }, "sleep");
+  p->connect();
+  p->client.SetTimeout(5000ms);
+  ex::async_scope scope;
+  std::atomic<int> cancelled{0};
+  scope.spawn_detached(ex::upon_error(ex::then(p->client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(300)),
+                                               [](InvokeResult) {}),
+                                      [&](std::exception_ptr e) {
+                                        if (ex::error_code_of(e) == make_error_code(RpcErrc::CANCELLED)) cancelled.fetch_add(1);
+                                      }));
+  std::this_thread::sleep_for(30ms);
+  p->client.StopClient();
+  ex::sync_wait(scope.join());
+  CHECK_EQ(cancelled.load(), 1);
+  std::this_thread::sleep_for(350ms);
+  p.reset();
+}
+
+// Server and client in separate processes; the address travels through a pipe.
+EUX_TEST(forked_processes_echo) {
+  int addr_pipe[2], ctl_pipe[2];
+  CHECK(pipe(addr_pipe) == 0 && pipe(ctl_pipe) == 0);
+  pid_t pid = fork();
+  CHECK(pid >= 0);
+  if (pid == 0) {  // server child
+    close(addr_pipe[0]);
+    close(ctl_pipe[1]);
+    int rc = 1;
+    {
+      AxonRuntime rt("forked_server", 2, 2000ms);
+      rt.RegisterFunction(function_id_t{1}, [](const data::string& s, const data::vector<int64_t>& v) {
+        int64_t sum = std::accumulate(v.begin(), v.end(), int64_t(0));
+        return std::tuple<data::string, int64_t>(data::string(s.str() + "/ok"), sum);
+      }, std::string("join"));
+      if (!rt.StartServer()) {
+        auto addr = rt.GetLocalAddress();
+        uint32_t n = addr.size();
+        if (write(addr_pipe[1], &n, 4) == 4 && write(addr_pipe[1], addr.data(), n) == (ssize_t)n) {
+          char c;
+          rc = read(ctl_pipe[0], &c, 1) == 1 ? 0 : 2;  // wait for the shutdown byte
+        }
+      }
+      rt.Stop();
+    }
+    _exit(rc);
+  }
+  close(addr_pipe[1]);
+  close(ctl_pipe[0]);
+  uint32_t n = 0;
+  CHECK(read(addr_pipe[0], &n, 4) == 4 && n > 0 && n < 4096);
+  std::vector<std::byte> addr(n);
+  CHECK(read(addr_pipe[0], addr.data(), n) == (ssize_t)n);
+  {
+    AxonRuntime rt("forked_client", 2, 2000ms);
+    CHECK(!rt.StartClient());
+    rt.ConnectEndpoint(addr, "forked_server");
+    auto r = ex::sync_wait(rt.InvokeRpc("forked_server", session_id_t{3}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, data::string("ping"),
+                                        data::vector<int64_t>{1, 2, 3, 4}));
+    CHECK(r && r->header.status.ok());
+    CHECK(r->header.GetString(0) == "ping/ok");
+    CHECK_EQ(r->header.GetPrimitive<int64_t>(1), 10);
+    rt.Stop();
+  }
+  CHECK(write(ctl_pipe[1], "x", 1) == 1);
+  int status = 0;
+  CHECK(waitpid(pid, &status, 0) == pid);
+  CHECK(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+}
+
+EUX_TEST_MAIN()
