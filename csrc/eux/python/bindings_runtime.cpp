@@ -1,0 +1,443 @@
+// Python bindings, part 2: memory managers and the AxonRuntime class with its
+// asyncio integration (reference: axon/python/src/bindings_runtime.cpp,
+// async_bridge.hpp, bindings_runtime_wrapper.cpp, memory_policy_helpers.cpp).
+//
+// Threads: Python calls arrive on the asyncio thread with the GIL. Completions
+// come from the runtime's C++ threads; they are turned into closures that the
+// wake manager runs on the asyncio thread, where futures are resolved and
+// Python handlers are started as tasks.
+#include <cuda_runtime_api.h>
+
+#include "bindings_common.hpp"
+#include "eux/ucxx/cuda/ucx_cuda_context.hpp"
+#include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
+
+namespace eux::python {
+
+namespace ex = eux::exec;
+using axon::ClientMemoryPolicy;
+using axon::InvokeResult;
+using axon::ServerMemoryPolicy;
+using rpc::PayloadVariant;
+using ucxx::UcxBuffer;
+using ucxx::UcxBufferVec;
+
+namespace {
+
+std::shared_ptr<ucxx::UcxMemoryResourceManager>& default_manager() {
+  static std::shared_ptr<ucxx::UcxMemoryResourceManager> mr = std::make_shared<ucxx::DefaultUcxMemoryResourceManager>();
+  return mr;
+}
+
+std::chrono::milliseconds parse_timeout(py::handle t) {
+  if (t.is_none()) return std::chrono::milliseconds(300);
+  if (py::isinstance<py::int_>(t)) return std::chrono::milliseconds(t.cast<int64_t>());           // int: milliseconds
+  if (py::isinstance<py::float_>(t)) return std::chrono::milliseconds(int64_t(t.cast<double>() * 1000.0));  // float: seconds
+  if (py::hasattr(t, "total_seconds")) return std::chrono::milliseconds(int64_t(t.attr("total_seconds")().cast<double>() * 1000.0));
+  throw py::type_error("timeout must be int (ms), float (s), datetime.timedelta or None");
+}
+
+// payload argument of invoke_raw / result of a Python handler -> PayloadVariant
+PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj) {
+  if (obj.is_none()) return {};
+  if (py::isinstance<PyBuffer>(obj)) {
+    auto& b = obj.cast<PyBuffer&>();
+    if (!b.buf) return {};
+    // a view that keeps the shared buffer alive
+    auto keep = b.buf;
+    return UcxBuffer(mr, keep->type(), keep->data(), keep->size(), nullptr, true, [keep](void*) mutable { keep.reset(); });
+  }
+  if (py::isinstance<PyBufferVec>(obj)) {
+    auto keep = obj.cast<PyBufferVec&>().vec;
+    if (!keep) return {};
+    return UcxBufferVec(mr, keep->type(), std::vector<ucx_buffer_t>(keep->buffers()), nullptr, true, [keep](void*) mutable { keep.reset(); });
+  }
+  if (py::isinstance<py::list>(obj) || py::isinstance<py::tuple>(obj)) {
+    std::vector<ImportedTensor> ts;
+    for (auto item : obj) ts.push_back(import_tensor(item));
+    return to_ucx_buffer_vec(mr, std::move(ts));
+  }
+  return to_ucx_buffer(mr, import_tensor(obj));
+}
+
+py::object payload_to_python(PayloadVariant&& p, int device_id) {
+  if (auto* b = std::get_if<UcxBuffer>(&p)) return py::cast(PyBuffer{std::make_shared<UcxBuffer>(std::move(*b)), device_id});
+  if (auto* v = std::get_if<UcxBufferVec>(&p)) return py::cast(PyBufferVec{std::make_shared<UcxBufferVec>(std::move(*v)), device_id});
+  return py::none();
+}
+
+std::string error_text(const std::exception_ptr& e) {
+  try {
+    std::rethrow_exception(e);
+  } catch (const std::exception& ex) {
+    return ex.what();
+  } catch (...) {
+    return "unknown error";
+  }
+}
+
+}  // namespace
+
+class PyAxonRuntime {
+ public:
+  PyAxonRuntime(const std::string& worker_name, size_t thread_pool_size, py::object timeout, py::object device,
+                std::shared_ptr<ucxx::UcxMemoryResourceManager> mr)
+      : name_(worker_name) {
+    std::unique_ptr<ucxx::UcxAutoDeviceContext> dev;
+    if (!device.is_none()) {
+      std::string kind = py::hasattr(device, "kind") ? device.attr("kind").cast<std::string>() : std::string(py::str(device));
+      int index = py::hasattr(device, "index") ? device.attr("index").cast<int>() : 0;
+      if (kind == "cuda") {
+        device_id_ = index;
+        dev = std::make_unique<ucxx::UcxAutoCudaDeviceContext>(index);
+        if (!mr) {
+          ucxx::UcxCudaMemoryResourceManager::Options opt;
+          opt.device = index;
+          mr = std::make_shared<ucxx::UcxCudaMemoryResourceManager>(opt);
+        }
+      } else if (kind != "cpu") {
+        throw py::value_error("this build drives cpu and cuda devices; got '" + kind + "'");
+      }
+    }
+    mr_ = mr ? mr : default_manager();
+    if (thread_pool_size == 0) thread_pool_size = axon::AxonWorker::DefaultThreadPoolSize();
+    rt_ = std::make_unique<axon::AxonRuntime>(worker_name, thread_pool_size, parse_timeout(timeout), std::move(dev), mr_);
+  }
+  ~PyAxonRuntime() {
+    try {
+      stop();
+    } catch (...) {
+    }
+  }
+
+  // ---- lifecycle ----
+  void attach_loop() {
+    py::object asyncio = py::module_::import("asyncio");
+    py::object loop;
+    try {
+      loop = asyncio.attr("get_running_loop")();
+    } catch (py::error_already_set&) {
+      loop = asyncio.attr("get_event_loop")();
+    }
+    wake_.attach(loop);
+  }
+  void start() {
+    attach_loop();
+    throw_if(rt_->Start());
+  }
+  void start_server() {
+    attach_loop();
+    throw_if(rt_->StartServer());
+  }
+  void start_client() {
+    attach_loop();
+    throw_if(rt_->StartClient());
+  }
+  void stop() {
+    if (!rt_) return;
+    {
+      py::gil_scoped_release nogil;  // worker threads may be waiting for the GIL to finish their callbacks
+      rt_->Stop();
+      ex::sync_wait(scope_.cleanup());
+    }
+    wake_.process_queue();
+    wake_.detach();
+  }
+  void stop_server() {
+    py::gil_scoped_release nogil;
+    rt_->StopServer();
+  }
+  void stop_client() {
+    py::gil_scoped_release nogil;
+    rt_->StopClient();
+  }
+  py::bytes get_local_address() {
+    auto a = rt_->GetLocalAddress();
+    return py::bytes(reinterpret_cast<const char*>(a.data()), a.size());
+  }
+  py::bytes get_local_signatures() {
+    auto b = rt_->GetLocalSignatures();
+    return py::bytes(reinterpret_cast<const char*>(b.data()), b.size());
+  }
+  bool register_endpoint_signatures(const std::string& worker_name, py::bytes data) {
+    std::string s = data;
+    return rt_->RegisterEndpointSignatures(worker_name, s.data(), s.size());
+  }
+  void set_timeout(py::object t) { rt_->SetTimeout(parse_timeout(t)); }
+  void set_reject_messages(bool r) { rt_->SetRejectMessages(r); }
+  std::string worker_name() const { return name_; }
+  size_t stored_request_count() { return rt_->worker().GetStorage().size(); }
+  std::string save_stored_requests(const std::string& dir, const std::string& prefix) {
+    py::gil_scoped_release nogil;
+    return rt_->worker().GetStorage().save(*mr_, dir, prefix);
+  }
+  size_t load_stored_requests(const std::string& path) {
+    py::gil_scoped_release nogil;
+    return rt_->worker().GetStorage().load(*mr_, path);
+  }
+  // Python handlers run on the event loop, so re-processing must not block it: the work runs on a
+  // helper thread and the caller awaits the returned future.
+  py::object process_stored_requests();
+
+  // ---- futures ----
+  // Run `sender`; resolve a new asyncio future with `convert(value)` on the loop thread.
+  template <class Sender, class Convert>
+  py::object future_from(Sender&& sender, Convert convert) {
+    attach_loop();
+    py::object fut = wake_.loop().attr("create_future")();
+    auto fut_box = gil_shared(fut);  // destroyed on the loop thread, under the GIL
+    auto settle = [this, fut_box](std::function<void(py::object&)> fn) {
+      wake_.enqueue([fut_box, fn = std::move(fn)] {
+        py::object f = *fut_box;
+        if (!f.attr("done")().cast<bool>()) fn(f);
+      });
+    };
+    using V = ex::value_t<Sender>;
+    auto on_value = [settle, convert](V v) mutable {
+      auto box = std::make_shared<V>(std::move(v));
+      settle([box, convert](py::object& f) mutable {
+        try {
+          f.attr("set_result")(convert(std::move(*box)));
+        } catch (py::error_already_set& e) {
+          f.attr("set_exception")(e.value());
+        } catch (const std::exception& e) {
+          f.attr("set_exception")(py::module_::import("builtins").attr("RuntimeError")(e.what()));
+        }
+      });
+    };
+    auto on_error = [settle](std::exception_ptr e) {
+      std::string text = error_text(e);
+      settle([text](py::object& f) { f.attr("set_exception")(py::module_::import("builtins").attr("RuntimeError")(text)); });
+    };
+    auto on_done = [settle] { settle([](py::object& f) { f.attr("cancel")(); }); };
+    {
+      py::gil_scoped_release nogil;
+      scope_.spawn_detached(ex::upon_done(ex::upon_error(ex::then(std::forward<Sender>(sender), std::move(on_value)), std::move(on_error)), std::move(on_done)));
+    }
+    return fut;
+  }
+
+  py::object connect_endpoint_async(py::object address, const std::string& worker_name) {
+    std::string bytes = py::isinstance<py::bytes>(address) ? std::string(address.cast<py::bytes>()) : std::string(py::bytes(py::bytearray(address)));
+    std::vector<std::byte> addr(bytes.size());
+    std::memcpy(addr.data(), bytes.data(), bytes.size());
+    return future_from(rt_->ConnectEndpointAsync(std::move(addr), worker_name), [](uint64_t conn) -> py::object { return py::int_(conn); });
+  }
+
+  // ---- memory policy from Python ----
+  // callable(list[TensorMeta]) -> tensor | list[tensor]; the returned objects are remembered so the
+  // caller gets the very same objects back once the data has landed in them.
+  ServerMemoryPolicy server_policy(py::object policy) {
+    ServerMemoryPolicy p;
+    if (policy.is_none()) return p;
+    p.on_host = false;
+    auto fn = gil_shared(policy);
+    auto* mr = mr_.get();
+    p.buffer_provider = [fn, mr](rpc::utils::TensorMetaSpan metas) -> UcxBuffer {
+      py::gil_scoped_acquire gil;
+      py::list lst;
+      for (auto& m : metas) lst.append(py::cast(m));
+      py::object out = (*fn)(lst);
+      if (py::isinstance<py::list>(out) || py::isinstance<py::tuple>(out)) out = py::reinterpret_borrow<py::sequence>(out)[0];
+      ImportedTensor t = import_tensor(out);
+      remember_owner(t.data, out);
+      return to_ucx_buffer(*mr, std::move(t));
+    };
+    p.buffer_vec_provider = [fn, mr](rpc::utils::TensorMetaSpan metas) -> UcxBufferVec {
+      py::gil_scoped_acquire gil;
+      py::list lst;
+      for (auto& m : metas) lst.append(py::cast(m));
+      py::object out = (*fn)(lst);
+      std::vector<ImportedTensor> ts;
+      if (py::isinstance<py::list>(out) || py::isinstance<py::tuple>(out)) {
+        for (auto item : out) {
+          ts.push_back(import_tensor(item));
+          remember_owner(ts.back().data, py::reinterpret_borrow<py::object>(item));
+        }
+      } else {
+        ts.push_back(import_tensor(out));
+        remember_owner(ts.back().data, out);
+      }
+      return to_ucx_buffer_vec(*mr, std::move(ts));
+    };
+    return p;
+  }
+  ClientMemoryPolicy client_policy(py::object policy, bool want_vec) {
+    ClientMemoryPolicy c;
+    c.want_vec = want_vec;
+    if (policy.is_none()) return c;
+    ServerMemoryPolicy s = server_policy(policy);
+    c.on_host = false;
+    c.buffer_provider = std::move(s.buffer_provider);
+    c.buffer_vec_provider = std::move(s.buffer_vec_provider);
+    return c;
+  }
+
+  // ---- invoke ----
+  py::object invoke_raw(const std::string& worker_name, rpc::RpcRequestHeader header, py::object payload, py::object memory_policy,
+                        bool response_as_list) {
+    PayloadVariant p = payload_from_python(*mr_, payload);
+    ClientMemoryPolicy pol = client_policy(memory_policy, response_as_list);
+    if (response_as_list && !memory_policy.is_none()) pol.buffer_provider = nullptr;
+    const int dev = device_id_;
+    return future_from(rt_->InvokeRpc(std::string_view(worker_name), std::move(header), std::move(p), std::move(pol)),
+                       [dev](InvokeResult r) -> py::object {
+                         py::object payload_obj = payload_to_python(std::move(r.payload), dev);
+                         return py::make_tuple(py::cast(std::move(r.header)), payload_obj);
+                       });
+  }
+
+  // ---- server-side functions ----
+  // `callable(header: RpcRequestHeader, payload) -> awaitable of (RpcResponseHeader | list of results, payload | None)`.
+  bool register_function_raw(uint32_t function_id, const std::string& function_name, std::vector<rpc::ParamType> param_types,
+                             std::vector<rpc::ParamType> return_types, rpc::PayloadType input_payload_type,
+                             rpc::PayloadType return_payload_type, py::object callable, py::object memory_policy, py::object lifecycle_policy) {
+    attach_loop();
+    auto fn = gil_shared(std::move(callable));
+    auto* self = this;
+    rpc::DynamicAsyncRpcFunction handler = [self, fn](const rpc::RpcRequestHeader& req, PayloadVariant&& payload,
+                                                     const rpc::RpcResponseBuilder& builder) -> rpc::AsyncInvokeSender {
+      struct State {
+        rpc::RpcRequestHeader req;
+        rpc::RpcResponseBuilder builder;
+        PayloadVariant payload;
+      };
+      auto st = std::make_shared<State>(State{req, builder, std::move(payload)});
+      return rpc::AsyncInvokeSender(ex::create<rpc::RpcInvokeResult<rpc::ReturnedPayload>>([self, fn, st](auto handle) {
+        // hop to the asyncio thread: start the coroutine as a task, finish the C++ call from its done-callback
+        self->wake_.enqueue([self, fn, st, handle]() mutable {
+          auto fail = [st, handle](std::error_code ec, const std::string& what) mutable {
+            py::gil_scoped_release nogil;
+            handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{
+                st->builder.PrepareError(st->req.session_id, st->req.request_id, ec, what), rpc::ReturnedPayload{}});
+          };
+          try {
+            py::object payload_obj = payload_to_python(std::move(st->payload), self->device_id_);
+            py::object coro = (*fn)(py::cast(st->req), payload_obj);
+            py::object task = py::module_::import("asyncio").attr("ensure_future")(coro, py::arg("loop") = self->wake_.loop());
+            task.attr("add_done_callback")(py::cpp_function([self, st, handle, fail](py::object t) mutable {
+              try {
+                if (t.attr("cancelled")().cast<bool>()) {
+                  fail(rpc::make_error_code(rpc::RpcErrc::CANCELLED), "the handler task was cancelled");
+                  return;
+                }
+                py::object exc = t.attr("exception")();
+                if (!exc.is_none()) {
+                  fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), std::string(py::str(py::type::of(exc).attr("__name__"))) + ": " + std::string(py::str(exc)));
+                  return;
+                }
+                py::object res = t.attr("result")();
+                py::object head = res, pay = py::none();
+                if (py::isinstance<py::tuple>(res) && py::len(res) == 2) {
+                  head = res.cast<py::tuple>()[0];
+                  pay = res.cast<py::tuple>()[1];
+                }
+                rpc::RpcResponseHeader h;
+                if (py::isinstance<rpc::RpcResponseHeader>(head)) {
+                  h = head.cast<rpc::RpcResponseHeader>();
+                } else {
+                  h = st->builder.PrepareResponse(st->req.session_id, st->req.request_id);
+                  if (!head.is_none())
+                    for (auto item : head) h.results.push_back(py::isinstance<rpc::ParamMeta>(item) ? item.cast<rpc::ParamMeta>() : python_to_param(item));
+                }
+                h.session_id = st->req.session_id;
+                h.request_id = st->req.request_id;
+                PayloadVariant out = payload_from_python(*self->mr_, pay);
+                py::gil_scoped_release nogil;
+                handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{std::move(h), std::move(out)});
+              } catch (py::error_already_set& e) {
+                fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
+              } catch (const std::exception& e) {
+                fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
+              }
+            }));
+          } catch (py::error_already_set& e) {
+            fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
+          } catch (const std::exception& e) {
+            fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
+          }
+        });
+      }));
+    };
+    axon::MessageLifecyclePolicy lc = axon::TransientPolicy{};
+    if (!lifecycle_policy.is_none()) {
+      auto lcf = gil_shared(lifecycle_policy);
+      lc = axon::RetentionPolicy([lcf](std::shared_ptr<axon::utils::AxonRequest> req, axon::utils::AxonMessageID id) {
+        py::gil_scoped_acquire gil;
+        py::object r = (*lcf)(py::cast(req->header), id);
+        if (py::isinstance<py::bool_>(r)) return r.cast<bool>() ? axon::LifecycleStatus::Preserve : axon::LifecycleStatus::Discard;
+        return static_cast<axon::LifecycleStatus>(r.cast<int>());
+      });
+    }
+    return rt_->RegisterFunction(rpc::function_id_t{function_id}, function_name, rpc::data::vector<rpc::ParamType>(param_types.begin(), param_types.end()),
+                                 rpc::data::vector<rpc::ParamType>(return_types.begin(), return_types.end()), input_payload_type,
+                                 return_payload_type, std::move(handler), server_policy(memory_policy), std::move(lc));
+  }
+
+ private:
+  static void throw_if(std::error_code ec) {
+    if (ec) throw std::runtime_error("axon: " + ec.message());
+  }
+  std::string name_;
+  int device_id_ = 0;
+  std::shared_ptr<ucxx::UcxMemoryResourceManager> mr_;
+  PythonWakeManager wake_;
+  ex::static_thread_pool helper_{1};
+  ex::async_scope scope_;
+  std::unique_ptr<axon::AxonRuntime> rt_;
+};
+
+py::object PyAxonRuntime::process_stored_requests() {
+  auto* worker = &rt_->worker();
+  return future_from(ex::on(helper_.get_scheduler(), ex::just_from([worker] { return worker->ProcessStoredRequests(); })),
+                     [](size_t n) -> py::object { return py::int_(n); });
+}
+
+void bind_runtime(py::module_& m) {
+  py::class_<ucxx::UcxMemoryResourceManager, std::shared_ptr<ucxx::UcxMemoryResourceManager>>(m, "UcxMemoryResourceManager");
+  py::class_<ucxx::DefaultUcxMemoryResourceManager, ucxx::UcxMemoryResourceManager, std::shared_ptr<ucxx::DefaultUcxMemoryResourceManager>>(
+      m, "DefaultUcxMemoryResourceManager")
+      .def(py::init<>());
+  py::class_<ucxx::UcxCudaMemoryResourceManager, ucxx::UcxMemoryResourceManager, std::shared_ptr<ucxx::UcxCudaMemoryResourceManager>>(
+      m, "CudaMemoryResourceManager")
+      .def(py::init([](int device, size_t arena_bytes) {
+             ucxx::UcxCudaMemoryResourceManager::Options o;
+             o.device = device;
+             o.arena_bytes = arena_bytes;
+             return std::make_shared<ucxx::UcxCudaMemoryResourceManager>(o);
+           }),
+           py::arg("device") = 0, py::arg("arena_bytes") = size_t(64) << 20)
+      .def("pooled_bytes", &ucxx::UcxCudaMemoryResourceManager::pooled_bytes)
+      .def("pooled_bytes_in_use", &ucxx::UcxCudaMemoryResourceManager::pooled_bytes_in_use);
+  m.def("get_default_resource_manager", [] { return default_manager(); });
+  m.def("get_device_context_handle", [](const std::string& kind) -> py::object {
+    if (kind != "cuda") return py::none();
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+      cudaGetLastError();
+      return py::none();
+    }
+    return py::int_(dev);
+  }, "The CUDA device current on the calling thread, or None.");
+
+  py::class_<PyAxonRuntime>(m, "AxonRuntime")
+      .def(py::init<const std::string&, size_t, py::object, py::object, std::shared_ptr<ucxx::UcxMemoryResourceManager>>(), py::arg("worker_name"),
+           py::arg("thread_pool_size") = 0, py::arg("timeout") = py::none(), py::arg("device") = py::none(), py::arg("resource_manager") = nullptr)
+      .def("start", &PyAxonRuntime::start).def("start_server", &PyAxonRuntime::start_server).def("start_client", &PyAxonRuntime::start_client)
+      .def("stop", &PyAxonRuntime::stop).def("stop_server", &PyAxonRuntime::stop_server).def("stop_client", &PyAxonRuntime::stop_client)
+      .def("get_local_address", &PyAxonRuntime::get_local_address).def("get_local_signatures", &PyAxonRuntime::get_local_signatures)
+      .def("register_endpoint_signatures", &PyAxonRuntime::register_endpoint_signatures)
+      .def("connect_endpoint_async", &PyAxonRuntime::connect_endpoint_async, py::arg("ucp_address"), py::arg("worker_name"))
+      .def("register_function_raw", &PyAxonRuntime::register_function_raw, py::arg("function_id"), py::arg("function_name"), py::arg("param_types"),
+           py::arg("return_types"), py::arg("input_payload_type"), py::arg("return_payload_type"), py::arg("callable"),
+           py::arg("memory_policy") = py::none(), py::arg("lifecycle_policy") = py::none())
+      .def("invoke_raw", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
+           py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false)
+      .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
+      .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)
+      .def("stored_request_count", &PyAxonRuntime::stored_request_count)
+      .def("save_stored_requests", &PyAxonRuntime::save_stored_requests, py::arg("directory"), py::arg("prefix") = "axon")
+      .def("load_stored_requests", &PyAxonRuntime::load_stored_requests).def("process_stored_requests", &PyAxonRuntime::process_stored_requests);
+}
+
+}  // namespace eux::python

@@ -1,0 +1,61 @@
+// DLPack interop for the Python bindings: tensors enter as zero-copy UcxBuffer
+// views that keep their Python owner alive through the release function, and
+// buffers leave as "dltensor" capsules following the consume-once protocol
+// (reference: axon/python/src/dlpack_helpers.{hpp,cpp}).
+#pragma once
+
+#include <pybind11/pybind11.h>
+
+#include <memory>
+#include <vector>
+
+#include "eux/dlpack.h"
+#include "eux/rpc/utils/tensor_meta.hpp"
+#include "eux/ucxx/ucx_context_data.hpp"
+
+namespace eux::python {
+
+namespace py = pybind11;
+
+ucx_memory_type_t memory_type_of(const DLDevice& dev);
+DLDevice device_of(ucx_memory_type_t type, int device_id);
+
+// The result of consuming obj.__dlpack__(): the managed tensor (owned by us now) and its metadata.
+struct ImportedTensor {
+  DLManagedTensor* managed = nullptr;
+  rpc::utils::TensorMeta meta;
+  void* data = nullptr;   // data pointer with byte_offset applied
+  size_t nbytes = 0;
+};
+// Calls obj.__dlpack__() (any object that implements the protocol), takes the capsule's tensor.
+// Throws when the tensor is not compact (dense row-major).
+ImportedTensor import_tensor(py::handle obj);
+// A non-copying buffer over the tensor; releasing it calls the DLPack deleter (under the GIL).
+ucxx::UcxBuffer to_ucx_buffer(ucxx::UcxMemoryResourceManager& mr, ImportedTensor&& t);
+// One buffer vector over several tensors (all on one device kind).
+ucxx::UcxBufferVec to_ucx_buffer_vec(ucxx::UcxMemoryResourceManager& mr, std::vector<ImportedTensor>&& ts);
+
+// A single-use holder of a DLPack capsule: frameworks' from_dlpack() call its __dlpack__().
+class DLPackCapsuleWrapper {
+ public:
+  DLPackCapsuleWrapper(py::capsule capsule, DLDevice device) : capsule_(std::move(capsule)), device_(device) {}
+  py::capsule dlpack(py::args, py::kwargs);  // __dlpack__(stream=None, ...)
+  py::tuple dlpack_device() const { return py::make_tuple(static_cast<int>(device_.device_type), device_.device_id); }
+  bool consumed() const { return consumed_; }
+
+ private:
+  py::capsule capsule_;
+  DLDevice device_;
+  bool consumed_ = false;
+};
+
+// Export `bytes [offset, offset+size)` of a shared buffer as a tensor described by `meta`.
+// The capsule keeps the buffer alive until the consumer's deleter runs.
+py::capsule make_capsule(std::shared_ptr<void> keep_alive, void* data, const rpc::utils::TensorMeta& meta);
+
+// Python owners of buffers that were supplied by a Python memory policy: when such a buffer
+// comes back with data, the very same Python object is handed to the caller.
+void remember_owner(const void* data, py::object owner);
+py::object take_owner(const void* data);  // None when unknown
+
+}  // namespace eux::python

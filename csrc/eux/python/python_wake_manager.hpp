@@ -1,0 +1,87 @@
+// Hands closures from C++ threads to the asyncio thread: a mutex-protected queue
+// plus an eventfd that the event loop watches with loop.add_reader(). The
+// closures run on the loop's thread with the GIL held
+// (reference: axon/python/src/python_wake_manager.{hpp,cpp}).
+#pragma once
+
+#include <pybind11/functional.h>
+#include <pybind11/pybind11.h>
+#include <sys/eventfd.h>
+#include <unistd.h>
+
+#include <deque>
+#include <functional>
+#include <mutex>
+
+namespace eux::python {
+
+namespace py = pybind11;
+
+class PythonWakeManager {
+ public:
+  PythonWakeManager() {
+    fd_ = ::eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+    if (fd_ < 0) throw std::runtime_error("eventfd failed");
+  }
+  ~PythonWakeManager() {
+    if (fd_ >= 0) ::close(fd_);
+  }
+  PythonWakeManager(const PythonWakeManager&) = delete;
+
+  // Register with the loop (must run on the loop's thread, GIL held). Idempotent per loop.
+  void attach(py::object loop) {
+    if (!loop_.is_none() && loop_.is(loop)) return;
+    detach();
+    loop_ = loop;
+    loop_.attr("add_reader")(fd_, py::cpp_function([this] { process_queue(); }));
+  }
+  void detach() {
+    if (loop_.is_none()) return;
+    try {
+      if (!loop_.attr("is_closed")().cast<bool>()) loop_.attr("remove_reader")(fd_);
+    } catch (py::error_already_set& e) {
+      e.discard_as_unraisable("PythonWakeManager.detach");
+    }
+    loop_ = py::none();
+  }
+  py::object loop() const { return loop_; }
+  bool attached() const { return !loop_.is_none(); }
+
+  // Any thread, no GIL needed.
+  void enqueue(std::function<void()> fn) {
+    {
+      std::lock_guard lk(mu_);
+      queue_.push_back(std::move(fn));
+    }
+    uint64_t one = 1;
+    (void)!::write(fd_, &one, sizeof(one));
+  }
+
+  // Loop thread, GIL held.
+  void process_queue() {
+    uint64_t n;
+    (void)!::read(fd_, &n, sizeof(n));
+    std::deque<std::function<void()>> batch;
+    {
+      std::lock_guard lk(mu_);
+      batch.swap(queue_);
+    }
+    for (auto& fn : batch) {
+      try {
+        fn();
+      } catch (py::error_already_set& e) {
+        e.discard_as_unraisable("axon callback");
+      } catch (const std::exception& e) {
+        py::print("axon: callback failed:", e.what());
+      }
+    }
+  }
+
+ private:
+  int fd_ = -1;
+  std::mutex mu_;
+  std::deque<std::function<void()>> queue_;
+  py::object loop_ = py::none();
+};
+
+}  // namespace eux::python

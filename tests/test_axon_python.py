@@ -1,0 +1,149 @@
+"""Python API of the runtime: two AxonRuntime objects (server + client) over loopback in one process."""
+import asyncio
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def axon(native_build):
+    from execution_ucx_b200 import axon as ax
+    return ax
+
+
+def run(coro):
+    loop = asyncio.new_event_loop()
+    try:
+        asyncio.set_event_loop(loop)
+        return loop.run_until_complete(coro)
+    finally:
+        loop.close()
+
+
+def test_types_and_param_inference(axon):
+    h = axon.RpcRequestHeader()
+    h.session_id, h.function_id = 5, 9
+    for v in (True, 7, 2.5, "text", b"\x00\x01", [1, 2, 3], [1.0, 2], [True, False], None):
+        h.AddParam(v)
+    kinds = [t for t, _, _ in h.params]
+    P = axon.ParamType
+    assert kinds == [P.PRIMITIVE_BOOL, P.PRIMITIVE_INT64, P.PRIMITIVE_FLOAT64, P.STRING, P.VECTOR_UINT8, P.VECTOR_INT64,
+                     P.VECTOR_FLOAT64, P.VECTOR_BOOL, P.VOID]
+    back = axon.RpcRequestHeader.deserialize(h.serialize())
+    assert [v for _, v, _ in back.params] == [True, 7, 2.5, "text", b"\x00\x01", [1, 2, 3], [1.0, 2.0], [True, False], None]
+    assert back.session_id == 5 and back.function_id == 9
+    m = axon.TensorMeta.from_tensor(np.zeros((3, 4), dtype=np.float32))
+    assert m.shape == [3, 4] and m.dtype.bits == 32 and m.nbytes() == 48
+    with pytest.raises(ValueError):
+        axon.TensorMeta.from_tensor(np.zeros((4, 4))[:, ::2])
+    assert axon.function_id_from_name("f", "w") == axon.function_id_from_name("f", "w") != axon.function_id_from_name("g", "w")
+    assert isinstance(axon.auto_detect(), axon.Device) and str(axon.cuda(1)) == "cuda:1"
+
+
+def test_invoke_numpy_eager_and_rendezvous(axon):
+    async def main():
+        server = axon.AxonRuntime("py_server", timeout=5000)
+        client = axon.AxonRuntime("py_client", timeout=5000)
+
+        async def add_scaled(x: np.ndarray, k: int, bias: float) -> np.ndarray:
+            return x * k + bias
+
+        async def stats(xs: List[np.ndarray], tag: str) -> Tuple[str, float, List[int]]:
+            return tag + "!", float(sum(a.sum() for a in xs)), [a.size for a in xs]
+
+        async def boom(n: int) -> int:
+            raise ValueError("bad input %d" % n)
+
+        server.register_function(add_scaled)
+        server.register_function(stats)
+        server.register_function(boom)
+        server.start_server()
+        client.start_client()
+        conn = await client.connect_endpoint_async(server.get_local_address(), "py_server")
+        assert conn != 0
+        sigs = axon.deserialize_signatures(server.get_local_signatures())
+        assert sorted(s.function_name for s in sigs) == ["add_scaled", "boom", "stats"]
+        for n in (16, 200_000):  # small (inline) and large (rendezvous) payloads
+            x = np.arange(n, dtype=np.float32)
+            y = await client.invoke(x, 3, 0.5, worker_name="py_server", session_id=1, function="add_scaled")
+            assert isinstance(y, np.ndarray) and y.dtype == np.float32
+            np.testing.assert_array_equal(y, x * 3 + 0.5)
+        a, b = np.ones(10, dtype=np.float64), np.full(50_000, 2.0)
+        tag, total, sizes = await client.invoke([a, b], "t", worker_name="py_server", session_id=1, function="stats")
+        assert tag == "t!" and total == 10 + 100_000 and sizes == [10, 50_000]
+        with pytest.raises(RuntimeError) as e:
+            await client.invoke(4, worker_name="py_server", session_id=2, function="boom")
+        assert "bad input 4" in str(e.value) and "(session_id: 2)" in str(e.value)
+        with pytest.raises(RuntimeError):
+            await client.invoke(1, worker_name="py_server", session_id=2, function="missing_function")
+        client.stop()
+        server.stop()
+
+    from typing import List, Tuple  # noqa: F401  (used by the annotations above)
+    globals().update(List=List, Tuple=Tuple)
+    run(main())
+
+
+def test_memory_policy_returns_the_same_object(axon):
+    async def main():
+        server = axon.AxonRuntime("mp_server", timeout=5000)
+        client = axon.AxonRuntime("mp_client", timeout=5000)
+
+        async def double(x: np.ndarray) -> np.ndarray:
+            return x * 2
+
+        server.register_function(double)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "mp_server")
+        made = []
+
+        def policy(metas):
+            t = np.empty(metas[0].shape, dtype=np.float32)
+            made.append(t)
+            return t
+
+        x = np.arange(100_000, dtype=np.float32)
+        y = await client.invoke(x, worker_name="mp_server", session_id=1, function="double", memory_policy=policy)
+        assert len(made) == 1 and y is made[0]          # the rendezvous path fills the policy's tensor
+        np.testing.assert_array_equal(y, x * 2)
+        small = await client.invoke(x[:8].copy(), worker_name="mp_server", session_id=1, function="double", memory_policy=policy)
+        assert len(made) == 1                            # small results do not consult the policy
+        np.testing.assert_array_equal(small, x[:8] * 2)
+        client.stop()
+        server.stop()
+
+    run(main())
+
+
+def test_raw_api_retention_and_checkpoint(axon, tmp_path):
+    async def main():
+        server = axon.AxonRuntime("raw_server", timeout=5000)
+        client = axon.AxonRuntime("raw_client", timeout=5000)
+        seen = []
+
+        async def handler(header, payload):
+            seen.append([v for _, v, _ in header.params])
+            return [sum(header.params[0][1])], None
+
+        P = axon.ParamType
+        server.register_function_raw(77, "sum", [P.VECTOR_INT64], [P.PRIMITIVE_INT64], axon.PayloadType.NO_PAYLOAD,
+                                     axon.PayloadType.NO_PAYLOAD, handler, None, lambda header, msg_id: True)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "raw_server")
+        h = axon.RpcRequestHeader()
+        h.session_id, h.function_id = 3, 77
+        h.AddParam([1, 2, 3, 4])
+        resp, payload = await client.invoke_raw("raw_server", h)
+        assert resp.ok and payload is None and resp.results[0][1] == 10
+        assert server.stored_request_count() == 1       # the retention policy kept the request
+        path = server.save_stored_requests(str(tmp_path), "keep")
+        assert path.endswith(".avro")
+        assert await server.process_stored_requests() == 1 and len(seen) == 2
+        other = axon.AxonRuntime("restore", timeout=1000)
+        assert other.load_stored_requests(path) == 1 and other.stored_request_count() == 1
+        client.stop()
+        server.stop()
+
+    run(main())
