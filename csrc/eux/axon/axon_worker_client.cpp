@@ -270,8 +270,10 @@ void AxonWorker::ClientFinishWithPayload(std::shared_ptr<ClientCall> call) {
   auto metas = utils::GetTensorMetas(call->response.results);
   const auto* desc = client_ctx_->view_pending_am_desc(key);
   const size_t total = desc ? desc->data_length : 0;
-  const bool as_vec = call->mem.want_vec || (!call->mem.on_host && call->mem.buffer_vec_provider && !call->mem.buffer_provider) ||
-                      (desc && desc->seg_count > 1 && call->mem.on_host && metas.size() > 1);
+  // a response that describes its payload with a TENSOR_META_VEC is received as separate buffers
+  bool meta_vec = false;
+  for (auto& r : call->response.results) meta_vec = meta_vec || r.type == rpc::ParamType::TENSOR_META_VEC;
+  const bool as_vec = call->mem.want_vec || meta_vec || (!call->mem.on_host && call->mem.buffer_vec_provider && !call->mem.buffer_provider);
   auto fail = [this, call, key](std::exception_ptr e) {
     client_pipe_failed_.fetch_add(1);
     client_ctx_->release_rndv_am_desc(key);

@@ -60,9 +60,13 @@ PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handl
   return to_ucx_buffer(mr, import_tensor(obj));
 }
 
-py::object payload_to_python(PayloadVariant&& p, int device_id) {
-  if (auto* b = std::get_if<UcxBuffer>(&p)) return py::cast(PyBuffer{std::make_shared<UcxBuffer>(std::move(*b)), device_id});
-  if (auto* v = std::get_if<UcxBufferVec>(&p)) return py::cast(PyBufferVec{std::make_shared<UcxBufferVec>(std::move(*v)), device_id});
+// Buffers handed to Python may outlive the runtime that received them (a result tensor kept
+// after `stop()`), and they return their bytes to the memory resource: each one keeps it alive.
+py::object payload_to_python(PayloadVariant&& p, int device_id, std::shared_ptr<ucxx::UcxMemoryResourceManager> mr) {
+  if (auto* b = std::get_if<UcxBuffer>(&p))
+    return py::cast(PyBuffer{std::shared_ptr<UcxBuffer>(new UcxBuffer(std::move(*b)), [mr](UcxBuffer* x) { delete x; }), device_id});
+  if (auto* v = std::get_if<UcxBufferVec>(&p))
+    return py::cast(PyBufferVec{std::shared_ptr<UcxBufferVec>(new UcxBufferVec(std::move(*v)), [mr](UcxBufferVec* x) { delete x; }), device_id});
   return py::none();
 }
 
@@ -280,9 +284,10 @@ class PyAxonRuntime {
     ClientMemoryPolicy pol = client_policy(memory_policy, response_as_list);
     if (response_as_list && !memory_policy.is_none()) pol.buffer_provider = nullptr;
     const int dev = device_id_;
+    auto mr = mr_;
     return future_from(rt_->InvokeRpc(std::string_view(worker_name), std::move(header), std::move(p), std::move(pol)),
-                       [dev](InvokeResult r) -> py::object {
-                         py::object payload_obj = payload_to_python(std::move(r.payload), dev);
+                       [dev, mr](InvokeResult r) -> py::object {
+                         py::object payload_obj = payload_to_python(std::move(r.payload), dev, mr);
                          return py::make_tuple(py::cast(std::move(r.header)), payload_obj);
                        });
   }
@@ -312,7 +317,7 @@ class PyAxonRuntime {
                 st->builder.PrepareError(st->req.session_id, st->req.request_id, ec, what), rpc::ReturnedPayload{}});
           };
           try {
-            py::object payload_obj = payload_to_python(std::move(st->payload), self->device_id_);
+            py::object payload_obj = payload_to_python(std::move(st->payload), self->device_id_, self->mr_);
             py::object coro = (*fn)(py::cast(st->req), payload_obj);
             py::object task = py::module_::import("asyncio").attr("ensure_future")(coro, py::arg("loop") = self->wake_.loop());
             task.attr("add_done_callback")(py::cpp_function([self, st, handle, fail](py::object t) mutable {

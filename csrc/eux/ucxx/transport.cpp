@@ -1025,7 +1025,8 @@ bool Worker::ensure_device() {
     return false;
   }
   void *h = nullptr, *d = nullptr, *c = nullptr;
-  if (eux_host_alloc_mapped(&h, &d, 4096) != 0 || cudaMalloc(&c, 256) != cudaSuccess || cudaMemset(c, 0, 256) != cudaSuccess) {
+  if (eux_host_alloc_mapped(&h, &d, 4096) != 0 || cudaMalloc(&c, 256) != cudaSuccess || cudaMemsetAsync(c, 0, 256, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
     cudaGetLastError();
     device_failed_ = true;
     return false;

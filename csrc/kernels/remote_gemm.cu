@@ -47,6 +47,10 @@ struct GemmParams {
   uint64_t timeout_ns;
   uint32_t* status;
   int copy_ctas;
+  // block-scaled fp8 only
+  const float* x_scale_src;   // [M, K/128], caller's (may be peer)
+  float* x_scale_stage;       // local copy used by the epilogue (== x_scale_src when X is local)
+  const float* w_scale;       // [N/128, K/128], local
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -160,25 +164,31 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
 
 // Copy CTAs: all of them work on one panel at a time, in order, so the first
 // panel is complete after 1/copy_ctas of its transfer time.
-__device__ void copy_role(const GemmParams& p) {
+__device__ void copy_role_n(const GemmParams& p, const int nthreads) {
   const size_t row_bytes = (size_t)p.K * p.elem_bytes;
   const size_t panel_vec = (size_t)BM * row_bytes / 16;
   const int panels = p.M / BM;
   const size_t per_cta = (panel_vec + p.copy_ctas - 1) / p.copy_ctas;
+  if (p.x_scale_src && p.x_scale_stage && p.x_scale_src != p.x_scale_stage) {
+    // the row scales travel first: each CTA copies its slice before it reports any panel
+    const size_t n = (size_t)p.M * (p.K / 128);
+    for (size_t i = (size_t)blockIdx.x * nthreads + threadIdx.x; i < n; i += (size_t)p.copy_ctas * nthreads)
+      p.x_scale_stage[i] = __ldcg(p.x_scale_src + i);
+  }
   for (int pn = 0; pn < panels; ++pn) {
     const uint4* s = reinterpret_cast<const uint4*>(p.x_src + (size_t)pn * BM * row_bytes);
     uint4* d = reinterpret_cast<uint4*>(p.x_stage + (size_t)pn * BM * row_bytes);
     const size_t lo = (size_t)blockIdx.x * per_cta;
     const size_t hi = min(panel_vec, lo + per_cta);
     size_t i = lo + threadIdx.x;
-    for (; i + 7 * GEMM_THREADS < hi; i += 8 * GEMM_THREADS) {
+    for (; i + 7 * (size_t)nthreads < hi; i += 8 * (size_t)nthreads) {
       uint4 v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = ld_cg_u4(s + i + j * GEMM_THREADS);
+      for (int j = 0; j < 8; ++j) v[j] = ld_cg_u4(s + i + j * nthreads);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) st_u4(d + i + j * GEMM_THREADS, v[j]);
+      for (int j = 0; j < 8; ++j) st_u4(d + i + j * nthreads, v[j]);
     }
-    for (; i < hi; i += GEMM_THREADS) st_u4(d + i, ld_cg_u4(s + i));
+    for (; i < hi; i += nthreads) st_u4(d + i, ld_cg_u4(s + i));
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
@@ -187,6 +197,8 @@ __device__ void copy_role(const GemmParams& p) {
     }
   }
 }
+
+__device__ __forceinline__ void copy_role(const GemmParams& p) { copy_role_n(p, GEMM_THREADS); }
 
 __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
   __syncthreads();
@@ -363,6 +375,192 @@ remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   finish_cta(p, ok);
 }
 
+
+// ---------------------------------------------------------------------------
+// Block-scaled fp8 (e4m3) variant: X carries one fp32 scale per row per 128
+// elements of K, W one per 128x128 block. The tensor cores cannot apply fp32
+// scales, so every 128-wide K block is multiplied on its own into one of two
+// TMEM buffers (accumulate off) and the epilogue warps add it, scaled by
+// sx[row, kb] * sw[nb, kb], into fp32 registers while the next block is being
+// multiplied. Tile 128 x 128, one stage = one K block (128 B per row).
+// ---------------------------------------------------------------------------
+constexpr int BN8 = 128;
+constexpr int STAGES8 = 6;
+constexpr int A8_STAGE_BYTES = BM * BKB;
+constexpr int B8_STAGE_BYTES = BN8 * BKB;
+constexpr int GEMM8_THREADS = 384;  // warp 0 TMA, warp 1 MMA, warps 4..11 epilogue (two per TMEM lane group)
+constexpr int TMEM8_COLS = 256;
+constexpr size_t GEMM8_SMEM = (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES) + 1024 + 256;
+
+__global__ void __launch_bounds__(GEMM8_THREADS, 1)
+remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  if ((int)blockIdx.x < p.copy_ctas) {
+    copy_role_n(p, GEMM8_THREADS);
+    finish_cta(p, true);
+    return;
+  }
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + (size_t)STAGES8 * A8_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES));
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES8 + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES8 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES8 + 2 + b); };
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES8; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)TMEM8_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  const int m_blocks = p.M / BM, n_blocks = p.N / BN8;
+  const int total = m_blocks * n_blocks;
+  const int k_blocks = p.K / 128;
+  const int first = (int)blockIdx.x - p.copy_ctas;
+  const int step = (int)gridDim.x - p.copy_ctas;
+  volatile int* abort = &s_abort;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int tile = first; tile < total && !*abort; tile += step) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        if (p.copy_ctas > 0) {
+          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)p.copy_ctas, p.timeout_ns)) {
+            *abort = 1;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int k = 0; k < k_blocks; ++k) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort, p.timeout_ns)) break;
+          mbar_expect_tx(full_bar(s), A8_STAGE_BYTES + B8_STAGE_BYTES);
+          tma_load_2d(smem_u32(sA + (size_t)s * A8_STAGE_BYTES), &map_a, full_bar(s), k * 128, mb * BM);
+          tma_load_2d(smem_u32(sB + (size_t)s * B8_STAGE_BYTES), &map_b, full_bar(s), k * 128, nb * BN8);
+          if (++s == STAGES8) s = 0, ph ^= 1u;
+        }
+      }
+      if (*abort) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<true, BN8>();
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t blk = 0;  // running K-block count: selects the TMEM buffer and its phase
+      for (int tile = first; tile < total && !*abort; tile += step) {
+        for (int k = 0; k < k_blocks && !*abort; ++k, ++blk) {
+          const int buf = blk & 1;
+          const uint32_t tph = (blk >> 1) & 1u;
+          if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abort, p.timeout_ns)) break;
+          if (!mbar_wait(full_bar(s), ph, abort, p.timeout_ns)) break;
+          tc_fence_after();
+          const uint32_t tacc = tmem_base + (uint32_t)buf * BN8;
+          const uint32_t a0 = smem_u32(sA + (size_t)s * A8_STAGE_BYTES);
+          const uint32_t b0 = smem_u32(sB + (size_t)s * B8_STAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BKB / 32; ++kk)
+            umma<true>(tacc, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), idesc, (uint32_t)(kk != 0));
+          umma_commit(empty_bar(s));
+          umma_commit(tfull_bar(buf));
+          if (++s == STAGES8) s = 0, ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    const int lg = (warp - 4) & 3;    // TMEM lane group
+    const int half = (warp - 4) >> 2;  // which 64 columns of the tile
+    uint32_t blk = 0;
+    const int kscales = p.K / 128;
+    for (int tile = first; tile < total && !*abort; tile += step) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      const int row = mb * BM + lg * 32 + lane;
+      const float* sx = p.x_scale_stage + (size_t)row * kscales;
+      const float* sw = p.w_scale + (size_t)nb * kscales;
+      float acc[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      bool ok = true;
+      for (int k = 0; k < k_blocks; ++k, ++blk) {
+        const int buf = blk & 1;
+        const uint32_t tph = (blk >> 1) & 1u;
+        if (!mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        // read only now: when X is pulled from a peer, the row scales are known to have landed once
+        // the products of this panel exist (the producer waited for the panel before loading it)
+        const float scale = __ldcg(sx + k) * __ldg(sw + k);
+        const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)buf * BN8 + (uint32_t)half * 64;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tbase, r0);
+        tmem_ld32(tbase + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));  // the buffer is in registers: the next block may overwrite it
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          acc[j] = fmaf(scale, __uint_as_float(r0[j]), acc[j]);
+          acc[32 + j] = fmaf(scale, __uint_as_float(r1[j]), acc[32 + j]);
+        }
+      }
+      if (!ok) break;
+      __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)row * p.N + (size_t)nb * BN8 + half * 64;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 o;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[c * 8 + 2 * j], acc[c * 8 + 2 * j + 1]);
+        st_u4(reinterpret_cast<uint4*>(yrow + c * 8), o);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM8_COLS)
+                 : "memory");
+  }
+  const bool ok = s_abort == 0;
+  if (!ok && threadIdx.x == 0) {
+    set_status(p.status, EUX_ST_TIMEOUT, 21);
+    atomicExch(p.sched + 1, 1u);
+  }
+  finish_cta(p, ok);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -406,17 +604,19 @@ extern "C" int eux_gemm_num_sms(void) {
 
 extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   if (!d || !d->x_stage || !d->w_t || !d->y_dst || !d->sched || !d->panel_flags) return EUX_ERR_BAD_ARG;
-  if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->M % BM || d->N % BN) return EUX_ERR_BAD_ARG;
-  if (d->fp8) return EUX_ERR_UNSUPPORTED;  // the block-scaled variant has its own entry point
-  const int eb = 2;
+  const int bn = d->fp8 ? BN8 : BN;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->M % BM || d->N % bn) return EUX_ERR_BAD_ARG;
+  const int eb = d->fp8 ? 1 : 2;
   if ((d->K * eb) % BKB) return EUX_ERR_BAD_ARG;
+  if (d->fp8 && (d->K % 128 || !d->x_scale || !d->w_scale)) return EUX_ERR_BAD_ARG;
   const bool pull = d->x_src && d->x_src != d->x_stage;
+  if (d->fp8 && pull && !d->x_scale_stage) return EUX_ERR_BAD_ARG;
   int copy_ctas = pull ? (d->copy_ctas > 0 ? d->copy_ctas : 12) : 0;
   const int sms = eux_gemm_num_sms();
   if (copy_ctas >= sms) return EUX_ERR_BAD_ARG;
   CUtensorMap ma, mb;
   if (int rc = make_map(&ma, d->x_stage, eb, (uint64_t)d->M, (uint64_t)d->K, BM)) return rc;
-  if (int rc = make_map(&mb, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, BN)) return rc;
+  if (int rc = make_map(&mb, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, bn)) return rc;
   GemmParams p;
   p.x_src = (const unsigned char*)d->x_src;
   p.x_stage = (unsigned char*)d->x_stage;
@@ -425,17 +625,22 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   p.panel_flags = d->panel_flags, p.sched = d->sched;
   p.done_flag = d->done_flag, p.done_value = d->done_value;
   p.timeout_ns = d->wait_timeout_ns, p.status = d->status, p.copy_ctas = copy_ctas;
-  static bool attr_set[64] = {false};
+  p.x_scale_src = d->fp8 ? d->x_scale : nullptr;
+  p.x_scale_stage = d->fp8 ? (pull ? d->x_scale_stage : const_cast<float*>(d->x_scale)) : nullptr;
+  p.w_scale = d->w_scale;
+  static bool attr_set[64][2] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return EUX_ERR_BAD_ARG;
-  if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(remote_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+  if (!attr_set[dev][d->fp8 ? 1 : 0]) {
+    cudaError_t e = d->fp8 ? cudaFuncSetAttribute(remote_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM8_SMEM)
+                           : cudaFuncSetAttribute(remote_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev] = true;
+    attr_set[dev][d->fp8 ? 1 : 0] = true;
   }
-  const int tiles = (d->M / BM) * (d->N / BN);
+  const int tiles = (d->M / BM) * (d->N / bn);
   int grid = copy_ctas + (tiles < sms - copy_ctas ? tiles : sms - copy_ctas);
-  remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
+  if (d->fp8) remote_gemm_fp8_kernel<<<grid, GEMM8_THREADS, GEMM8_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
+  else remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }

@@ -40,7 +40,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fvisibility=hidden", "-I", str(CSRC),
 ]
 CXX_FLAGS = [
-    "-std=c++23", "-O2", "-g", "-fPIC", "-Wall", "-Wno-unused-function",
+    "-std=c++23", "-O2", "-g1", "-fPIC", "-Wall", "-Wno-unused-function",
     "-Wno-interference-size", "-pthread", "-I", str(CSRC), "-I", str(CUDA_HOME / "include"),
 ]
 

@@ -152,8 +152,17 @@ def _classify(args: Sequence[Any]):
 
 
 def _contiguous(t):
+    """Dense row-major form of the tensor, ready to be read by another stream or process."""
     if hasattr(t, "is_contiguous") and not t.is_contiguous():
-        return t.contiguous()
+        t = t.contiguous()
+    if getattr(t, "is_cuda", False):
+        # the transfer kernel runs on the runtime's own stream (possibly in another process):
+        # everything queued on the producer's stream must have finished writing the tensor
+        import torch
+        torch.cuda.current_stream(t.device).synchronize()
+        return t
+    if hasattr(t, "is_contiguous"):
+        return t
     flags = getattr(t, "flags", None)
     if flags is not None and not flags["C_CONTIGUOUS"]:
         import numpy

@@ -58,6 +58,73 @@ class RemoteGemm:
             raise RuntimeError(f"remote gemm status code={s & 0xff} where={s >> 8}")
 
 
+def quantize_rows_1x128(x: torch.Tensor):
+    """X[M,K] -> (e4m3 values [M,K], fp32 scales [M,K/128]): one scale per row per 128 columns."""
+    m, k = x.shape
+    g = x.float().view(m, k // 128, 128)
+    scale = g.abs().amax(-1).clamp_min(1e-10) * (1.0 / 448.0)
+    q = (g * (1.0 / scale).unsqueeze(-1)).to(torch.float8_e4m3fn).view(m, k)
+    return q.contiguous(), scale.contiguous()
+
+
+def quantize_blocks_128x128(w_t: torch.Tensor):
+    """Wt[N,K] -> (e4m3 values [N,K], fp32 scales [N/128,K/128]): one scale per 128x128 block."""
+    n, k = w_t.shape
+    g = w_t.float().view(n // 128, 128, k // 128, 128)
+    scale = g.abs().amax(dim=(1, 3)).clamp_min(1e-10) * (1.0 / 448.0)
+    q = (g * (1.0 / scale)[:, None, :, None]).to(torch.float8_e4m3fn).view(n, k)
+    return q.contiguous(), scale.contiguous()
+
+
+def dequantized_reference(xq, xs, wq_t, ws) -> torch.Tensor:
+    """fp32 statement of the block-scaled product: (xq * xs) @ (wq * ws)^T."""
+    m, k = xq.shape
+    n = wq_t.shape[0]
+    x = xq.float().view(m, k // 128, 128) * xs.unsqueeze(-1)
+    w = wq_t.float().view(n // 128, 128, k // 128, 128) * ws[:, None, :, None]
+    return x.view(m, k) @ w.view(n, k).t()
+
+
+class RemoteGemmFp8:
+    """Block-scaled e4m3 variant: X with 1x128 scales (sent by the caller), W with 128x128 scales (resident)."""
+
+    def __init__(self, w: torch.Tensor, max_m: int):
+        assert w.dim() == 2 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0
+        self.K, self.N = w.shape
+        self.w_q_t, self.w_scale = quantize_blocks_128x128(w.t().contiguous())
+        dev = w.device
+        self.max_m = max_m
+        self.x_stage = torch.empty(max_m, self.K, dtype=torch.uint8, device=dev)
+        self.x_scale_stage = torch.empty(max_m, self.K // 128, dtype=torch.float32, device=dev)
+        self.panel_flags = torch.zeros(max(1, max_m // 128), dtype=torch.int32, device=dev)
+        self.sched = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def __call__(self, xq_ptr: int, xs_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
+                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000) -> None:
+        global _launches
+        if m > self.max_m:
+            raise ValueError("m exceeds the staging buffer")
+        d = _native.GemmDesc()
+        d.x_src = xq_ptr
+        d.x_stage = xq_ptr if x_is_local else self.x_stage.data_ptr()
+        d.x_scale = xs_ptr
+        d.x_scale_stage = xs_ptr if x_is_local else self.x_scale_stage.data_ptr()
+        d.w_t, d.w_scale, d.y_dst = self.w_q_t.data_ptr(), self.w_scale.data_ptr(), y_ptr
+        d.M, d.N, d.K, d.fp8 = m, self.N, self.K, 1
+        d.panel_flags, d.sched = self.panel_flags.data_ptr(), self.sched.data_ptr()
+        d.done_flag, d.done_value = done_flag_ptr or None, done_value
+        d.wait_timeout_ns, d.status, d.copy_ctas = timeout_ns, self.status.data_ptr(), copy_ctas
+        _native.check(_native.load().eux_gemm_launch(C.byref(d), C.c_void_p(_native.current_stream_ptr())),
+                      "eux_gemm_launch(fp8)")
+        _launches += 1
+
+    def check_status(self) -> None:
+        s = int(self.status.item())
+        if s:
+            raise RuntimeError(f"remote gemm (fp8) status code={s & 0xff} where={s >> 8}")
+
+
 def smoke(device) -> None:
     x = torch.randn(256, 256, device=device).to(torch.bfloat16)
     w = (torch.randn(256, 512, device=device) * 0.05).to(torch.bfloat16)

@@ -27,3 +27,30 @@ def test_gemm_matches_fp32(cuda_device, m, n, k, pull):
         if pull:
             assert torch.equal(g.x_stage[:m].view(torch.int16), x.view(torch.int16))
         assert int(g.panel_flags.sum()) == 0 and int(g.sched.sum()) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (512, 1024, 4096)])
+@pytest.mark.parametrize("pull", [False, True])
+def test_block_scaled_fp8_matches_fp32(cuda_device, m, n, k, pull):
+    from execution_ucx_b200.ops import remote_gemm as rg
+    torch.manual_seed(m * 3 + n + k)
+    x = torch.randn(m, k, device=cuda_device)
+    w = torch.randn(k, n, device=cuda_device) * 0.02
+    g = rg.RemoteGemmFp8(w, m)
+    xq, xs = rg.quantize_rows_1x128(x)
+    y = torch.zeros(m, n, dtype=torch.bfloat16, device=cuda_device)
+    done = torch.zeros(1, dtype=torch.int64, device=cuda_device)
+    for rnd in range(2):
+        y.zero_()
+        g(xq.data_ptr(), xs.data_ptr(), m, y.data_ptr(), x_is_local=not pull, done_flag_ptr=done.data_ptr(), done_value=rnd + 1,
+          copy_ctas=2 if pull else 0)
+        torch.cuda.synchronize()
+        g.check_status()
+        assert int(done.item()) == rnd + 1
+        ref = rg.dequantized_reference(xq, xs, g.w_q_t, g.w_scale)
+        # the kernel differs from the reference only by fp32 summation order and the bf16 output rounding
+        torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+        # and the quantised product stays close to the unquantised one
+        full = x @ w
+        assert float((y.float() - full).abs().max()) < 0.15 * float(full.abs().max()) + 0.05
+        assert int(g.panel_flags.sum()) == 0 and int(g.sched.sum()) == 0
