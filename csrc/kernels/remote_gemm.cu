@@ -644,3 +644,50 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   else remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// eux_gemm_bf16_noalloc: the GEMM for callers that cannot allocate (see eux_no_alloc.h).
+// The scratch the kernel needs lives in this static device array. In host code the
+// name `g_noalloc_gemm_scratch` is only a stand-in: the address a kernel can use is
+// obtained per device with cudaGetSymbolAddress below.
+// ---------------------------------------------------------------------------
+#include "eux_no_alloc.h"
+
+static __device__ __align__(256) uint32_t g_noalloc_gemm_scratch[EUX_NOALLOC_GEMM_SCRATCH_BYTES / 4];
+
+extern "C" int eux_gemm_bf16_noalloc(const void* x, const void* w_t, void* y, int M, int N, int K, uint32_t* status,
+                                     uint64_t wait_timeout_ns, void* stream) {
+  if (!x || !w_t || !y || M <= 0 || N <= 0 || K <= 0) return EUX_ERR_BAD_ARG;
+  if (M > EUX_NOALLOC_GEMM_MAX_M) return EUX_ERR_TOO_LARGE;  // one counter per 128 rows is all the static array holds
+  // Set-up, once per device, with that device current: the device address of the static array.
+  static uint32_t* scratch_addr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return EUX_ERR_BAD_ARG;
+  if (!scratch_addr[dev]) {
+    uint32_t* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_gemm_scratch);
+    if (e != cudaSuccess) return (int)e;
+    scratch_addr[dev] = ptr;
+  }
+  uint32_t* scratch = scratch_addr[dev];
+  // The array keeps whatever the previous call (or an interrupted kernel) left: counters must start at zero.
+  const size_t used = ((size_t)M / 128 + 64) * sizeof(uint32_t);
+  e = cudaMemsetAsync(scratch, 0, used, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  eux_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.x_src = x;
+  d.x_stage = const_cast<void*>(x);  // X is local: no staging, no copy CTAs
+  d.w_t = w_t;
+  d.y_dst = y;
+  d.M = M, d.N = N, d.K = K;
+  d.fp8 = 0;
+  d.sched = scratch;             // first 64 words: completion counters
+  d.panel_flags = scratch + 64;  // then one word per 128-row panel
+  d.wait_timeout_ns = wait_timeout_ns;
+  d.status = status;
+  d.copy_ctas = 0;
+  return eux_gemm_launch(&d, stream);
+}

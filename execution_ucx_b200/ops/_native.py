@@ -99,6 +99,9 @@ def load():
     if hasattr(lib, "eux_gemm_launch"):
         lib.eux_gemm_launch.argtypes = [C.POINTER(GemmDesc), P]
         lib.eux_gemm_num_sms.argtypes = []
+    if hasattr(lib, "eux_gemm_bf16_noalloc"):
+        lib.eux_gemm_bf16_noalloc.argtypes = [P, P, P, I, I, I, P, U64, P]
+        lib.eux_gemm_bf16_noalloc.restype = I
     _lib = lib
     return lib
 
