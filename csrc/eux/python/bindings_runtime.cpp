@@ -93,6 +93,7 @@ class PyAxonRuntime {
       int index = py::hasattr(device, "index") ? device.attr("index").cast<int>() : 0;
       if (kind == "cuda") {
         device_id_ = index;
+        is_cuda_ = true;
         dev = std::make_unique<ucxx::UcxAutoCudaDeviceContext>(index);
         if (!mr) {
           ucxx::UcxCudaMemoryResourceManager::Options opt;
@@ -237,7 +238,11 @@ class PyAxonRuntime {
     p.on_host = false;
     auto fn = gil_shared(policy);
     auto* mr = mr_.get();
-    p.buffer_provider = [fn, mr](rpc::utils::TensorMetaSpan metas) -> UcxBuffer {
+    // The policy runs on a pool thread whose current CUDA device is the default one; tensor
+    // libraries refuse to export a tensor of another device, so the thread adopts the runtime's.
+    const int cuda_dev = is_cuda_ ? device_id_ : -1;
+    p.buffer_provider = [fn, mr, cuda_dev](rpc::utils::TensorMetaSpan metas) -> UcxBuffer {
+      if (cuda_dev >= 0) cudaSetDevice(cuda_dev);
       py::gil_scoped_acquire gil;
       py::list lst;
       for (auto& m : metas) lst.append(py::cast(m));
@@ -247,7 +252,8 @@ class PyAxonRuntime {
       remember_owner(t.data, out);
       return to_ucx_buffer(*mr, std::move(t));
     };
-    p.buffer_vec_provider = [fn, mr](rpc::utils::TensorMetaSpan metas) -> UcxBufferVec {
+    p.buffer_vec_provider = [fn, mr, cuda_dev](rpc::utils::TensorMetaSpan metas) -> UcxBufferVec {
+      if (cuda_dev >= 0) cudaSetDevice(cuda_dev);
       py::gil_scoped_acquire gil;
       py::list lst;
       for (auto& m : metas) lst.append(py::cast(m));
@@ -385,6 +391,7 @@ class PyAxonRuntime {
   }
   std::string name_;
   int device_id_ = 0;
+  bool is_cuda_ = false;
   std::shared_ptr<ucxx::UcxMemoryResourceManager> mr_;
   PythonWakeManager wake_;
   ex::static_thread_pool helper_{1};

@@ -3,7 +3,7 @@
  * Every function returns 0 on success or a cudaError_t / EUX_ERR_* value.
  * Pointers named *_peer may point into another GPU's memory that has been
  * mapped into this process (CUDA IPC or peer access); kernels only ever touch
- * such memory with plain loads/stores or non-multicast bulk copies.
+ * such memory with plain loads/stores or per-CTA bulk copies.
  *
  * All device-side waits are bounded: when a wait runs out the kernel writes
  * EUX_ST_TIMEOUT (plus a location code) into the caller's status word and

@@ -8,7 +8,7 @@
 //     caller's memory into a local staging buffer with plain 16-byte loads and
 //     stores and publish a per-panel arrival count;
 //   * GEMM CTAs: warp 0 = TMA producer (waits for the panel, then loads A and B
-//     tiles with non-multicast cp.async.bulk.tensor, 128B swizzle), warp 1 =
+//     tiles with plain per-CTA cp.async.bulk.tensor loads, 128B swizzle), warp 1 =
 //     tcgen05.mma issuer (accumulators in TMEM, two 256-column buffers),
 //     warps 4..7 = epilogue (tcgen05.ld -> bf16 -> 16-byte stores into Y,
 //     which may be peer memory).

@@ -78,6 +78,10 @@ class TensorRpcEcho:
         if s:
             raise RuntimeError(f"tensor rpc status code={s & 0xff} where={s >> 8}")
 
+    def close(self):
+        """Collective: every rank calls it."""
+        self.g.free(self.arena, self.flags)
+
 
 class DevicePingPong:
     """Latency/bandwidth of the data plane alone: one kernel per GPU runs the
@@ -111,46 +115,80 @@ class DevicePingPong:
             raise RuntimeError("ping-pong wait ran out")
         return ts[1:] - ts[:-1]
 
+    def close(self):
+        """Collective: every rank calls it."""
+        self.g.free(self.buf, self.scratch, self.flags)
+
 
 class RemoteGemmRpc:
     """Remote-GEMM RPC: this rank is callee for its partner's X and caller of
     its partner's weight. X lives in the caller's arena; the callee kernel pulls
-    it panel by panel while computing and stores Y into the caller's arena."""
+    it panel by panel while computing and stores Y into the caller's arena.
+    With ``fp8`` the caller sends e4m3 rows with one fp32 scale per 128 elements
+    and the resident weight is e4m3 with 128x128 block scales. A single rank
+    has nothing to pull: its kernel reads X in place."""
 
-    def __init__(self, group: PeerGroup, m: int, n: int, k: int, copy_ctas: int = 12):
-        self.g, self.m, self.n, self.k, self.copy_ctas = group, m, n, k, copy_ctas
+    def __init__(self, group: PeerGroup, m: int, n: int, k: int, copy_ctas: int = 12, fp8: bool = False):
+        self.g, self.m, self.n, self.k, self.copy_ctas, self.fp8 = group, m, n, k, copy_ctas, fp8
         self.peer = _partner(group.rank, group.world)
         dev = group.device
-        self.x_buf = group.alloc(m * k * 2)
+        self.x_buf = group.alloc(m * k * (1 if fp8 else 2))
         self.y_buf = group.alloc(m * n * 2)
         self.flags = group.alloc(256)
-        self.x = self.x_buf.view(torch.bfloat16, m * k).view(m, k)
         self.y = self.y_buf.view(torch.bfloat16, m * n).view(m, n)
         g = torch.Generator(device=dev).manual_seed(1234 + group.rank)
-        self.x.copy_(torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16))
+        x = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
         self.w = (torch.randn(k, n, device=dev, generator=g) * 0.02).to(torch.bfloat16)
-        self.gemm = gemm_ops.RemoteGemm(self.w, m)
+        if fp8:
+            xq, xs = gemm_ops.quantize_rows_1x128(x)
+            self.xs_buf = group.alloc(m * (k // 128) * 4)
+            self.xq = self.x_buf.view(torch.uint8, m * k).view(m, k)
+            self.xs = self.xs_buf.view(torch.float32, m * (k // 128)).view(m, k // 128)
+            self.xq.copy_(xq.view(torch.uint8))
+            self.xs.copy_(xs)
+            self.gemm = gemm_ops.RemoteGemmFp8(self.w, m)
+            self.x = x
+        else:
+            self.x = self.x_buf.view(torch.bfloat16, m * k).view(m, k)
+            self.x.copy_(x)
+            self.gemm = gemm_ops.RemoteGemm(self.w, m)
         self.seq = 0
         self.sink = torch.empty(8, dtype=torch.bfloat16, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
         group.barrier()
 
     def step(self) -> torch.Tensor:
         self.seq += 1
         p = self.peer
         local = self.g.world == 1
+        kw = dict(x_is_local=local, done_flag_ptr=self.flags.peer_ptrs[p], done_value=self.seq,
+                  copy_ctas=0 if local else self.copy_ctas)
         # callee: consume the partner's X from its memory, write Y into the partner's memory
-        self.gemm(self.x_buf.peer_ptrs[p], self.m, self.y_buf.peer_ptrs[p], x_is_local=False,
-                  done_flag_ptr=self.flags.peer_ptrs[p], done_value=self.seq, copy_ctas=self.copy_ctas)
+        if self.fp8:
+            self.gemm(self.x_buf.peer_ptrs[p], self.xs_buf.peer_ptrs[p], self.m, self.y_buf.peer_ptrs[p], **kw)
+        else:
+            self.gemm(self.x_buf.peer_ptrs[p], self.m, self.y_buf.peer_ptrs[p], **kw)
         # caller: wait until the partner has delivered Y here
         tx.push(self.y.view(-1)[:8], self.sink, wait_flag_ptr=self.flags.local_ptr, wait_value=self.seq,
                 status_ptr=self.status.data_ptr())
         return self.y
 
+    def reference_rows(self, rows: int = 256) -> torch.Tensor:
+        """fp32 reference of the first rows (single rank: X and W are both local)."""
+        if self.fp8:
+            return gemm_ops.dequantized_reference(self.xq[:rows].view(torch.float8_e4m3fn), self.xs[:rows],
+                                                  self.gemm.w_q_t, self.gemm.w_scale)
+        return self.x[:rows].float() @ self.w.float()
+
     def check(self):
         self.gemm.check_status()
         if int(self.status.item()):
             raise RuntimeError("remote gemm completion wait ran out")
+
+    def close(self):
+        """Collective: every rank calls it."""
+        self.g.free(self.x_buf, self.y_buf, self.flags, getattr(self, "xs_buf", None))
 
 
 class MoeDispatchCombine:
@@ -179,3 +217,84 @@ class MoeDispatchCombine:
 
     def bytes_per_direction(self) -> int:
         return self.a2a.n_tokens * self.a2a.topk * self.a2a.row_bytes
+
+
+class AxonTensorRpc:
+    """Tensor echo through the public RPC API: ``AxonRuntime.register_function`` on the serving
+    side, ``AxonRuntime.invoke`` on the calling side, device tensors both ways.
+
+    With one rank the server and the client runtime live in this process on the same GPU; with more,
+    every rank runs one runtime that serves ``echo`` and calls it on its partner (rank r with r^1).
+    Request and response land in buffers that the memory policies hand out, allocated once per shape,
+    so the steady state allocates nothing. The control messages travel over the runtime's TCP
+    connections; the tensor bytes are pulled by the transfer kernel from the sender's memory.
+    """
+
+    def __init__(self, group: PeerGroup, dtype=torch.bfloat16, timeout_ms: int = 60000):
+        from .. import axon
+        self.axon, self.group, self.dtype = axon, group, dtype
+        self.dev = group.device
+        self.rank, self.world = group.rank, group.world
+        self._srv_bufs, self._cli_bufs = {}, {}
+        self.server = self.client = None
+        self.partner_name = None
+        self.timeout_ms = timeout_ms
+
+    def _policy(self, cache):
+        def policy(metas):
+            key = tuple(metas[0].shape)
+            buf = cache.get(key)
+            if buf is None:
+                buf = cache[key] = torch.empty(key, dtype=self.dtype, device=self.dev)
+            return buf
+        return policy
+
+    async def start(self):
+        axon = self.axon
+        index = self.dev.index or 0
+        device = (lambda i: axon.cuda(i)) if self.dev.type == "cuda" else (lambda i: None)
+
+        async def echo(x: torch.Tensor) -> torch.Tensor:
+            return x
+
+        if self.world == 1:
+            self.server = axon.AxonRuntime("axon_srv", timeout=self.timeout_ms, device=device(index))
+            self.client = axon.AxonRuntime("axon_cli", timeout=self.timeout_ms, device=device(index))
+            self.server.register_function(echo, memory_policy=self._policy(self._srv_bufs))
+            self.server.start_server()
+            self.client.start_client()
+            self.partner_name = "axon_srv"
+            await self.client.connect_endpoint_async(self.server.get_local_address(), self.partner_name)
+            return
+        import torch.distributed as dist
+        me = f"axon{self.rank}"
+        rt = axon.AxonRuntime(me, timeout=self.timeout_ms, device=device(index))
+        rt.register_function(echo, memory_policy=self._policy(self._srv_bufs))
+        rt.start()
+        self.server = self.client = rt
+        addrs = [None] * self.world
+        dist.all_gather_object(addrs, bytes(rt.get_local_address()))
+        partner = _partner(self.rank, self.world)
+        self.partner_name = f"axon{partner}"
+        await rt.connect_endpoint_async(addrs[partner], self.partner_name)
+        await self.barrier()
+
+    async def barrier(self):
+        """A barrier that keeps this rank's event loop (and so its ``echo`` handler) running."""
+        import asyncio
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+        work = dist.barrier(async_op=True)
+        while not work.is_completed():
+            await asyncio.sleep(0.0005)
+
+    async def step(self, x: torch.Tensor) -> torch.Tensor:
+        return await self.client.invoke(x, worker_name=self.partner_name, session_id=1, function="echo",
+                                        memory_policy=self._policy(self._cli_bufs))
+
+    def stop(self):
+        if self.client is not None:
+            self.client.stop()
+        if self.server is not None and self.server is not self.client:
+            self.server.stop()

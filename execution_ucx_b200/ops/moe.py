@@ -54,6 +54,10 @@ class MoeAllToAll:
         self.seq = 0
         self._x = self._idx = self._w = None
 
+    def close(self) -> None:
+        """Collective release of the peer-mapped buffers: every rank calls it."""
+        self.group.free(self.arena, self.meta, self.flags)
+
     @classmethod
     def emulated(cls, world: int, n_tokens: int, hidden: int, topk: int, n_experts: int, fp8: bool = False,
                  capacity: Optional[int] = None) -> List["MoeAllToAll"]:

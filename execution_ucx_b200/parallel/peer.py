@@ -29,7 +29,9 @@ from ..ops import _native
 class _RawCudaBuffer:
     """Owner of one cudaMalloc allocation, viewable as a torch tensor."""
 
-    def __init__(self, nbytes: int):
+    def __init__(self, nbytes: int, free_on_del: bool = True):
+        # free_on_del is off for memory that other processes map: its release is collective
+        self.free_on_del = free_on_del
         lib = _native.load()
         p = C.c_void_p()
         _native.check(lib.eux_device_malloc(C.byref(p), nbytes), "cudaMalloc")
@@ -46,7 +48,8 @@ class _RawCudaBuffer:
 
     def __del__(self):
         try:
-            self.free()
+            if self.free_on_del:
+                self.free()
         except Exception:
             pass
 
@@ -71,14 +74,23 @@ class SymmetricBuffer:
         esz = torch.empty((), dtype=dtype).element_size()
         return self.local[byte_offset:byte_offset + numel * esz].view(dtype)
 
-    def close(self):
+    def unmap_peers(self):
         lib = _native.load()
         for p in self._opened:
             lib.eux_ipc_close(C.c_void_p(p))
         self._opened.clear()
+
+    def free_local(self):
         for o in self._owners:
             o.free()
         self._owners.clear()
+
+    def close(self):
+        """Single-process teardown. With several ranks use ``PeerGroup.free``: a rank must not free
+        its copy while a peer still has it mapped (the next allocation could get the same memory,
+        and the peer could not map it a second time)."""
+        self.unmap_peers()
+        self.free_local()
 
 
 class PeerGroup:
@@ -103,12 +115,27 @@ class PeerGroup:
         return cls(0, world, emulated=True)
 
     # -- allocation ---------------------------------------------------------
+    def free(self, *bufs: "SymmetricBuffer") -> None:
+        """Collective release: every rank drops its mappings of the peers' copies, then (after a
+        barrier) frees its own copy. Memory is not given back when a buffer is merely dropped."""
+        torch.cuda.synchronize()
+        self.barrier()
+        for b in bufs:
+            if b is not None:
+                b.unmap_peers()
+        self.barrier()
+        for b in bufs:
+            if b is not None:
+                b.free_local()
+        self.barrier()
+
     def alloc(self, nbytes: int) -> SymmetricBuffer:
-        nbytes = (nbytes + 255) // 256 * 256
+        # whole 2 MiB blocks: an allocation then never shares its exported block with another one
+        nbytes = (nbytes + (2 << 20) - 1) // (2 << 20) * (2 << 20)
         if self.emulated_mode:
             raise RuntimeError("use alloc_emulated() on an emulated group")
         lib = _native.load()
-        own = _RawCudaBuffer(nbytes)
+        own = _RawCudaBuffer(nbytes, free_on_del=self.world == 1)
         local = torch.as_tensor(own, device=self.device)
         local.zero_()
         torch.cuda.synchronize()

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import json
+import os
 import statistics
 import subprocess
 import threading
@@ -72,28 +73,77 @@ def percentile(xs: List[float], q: float) -> float:
 
 
 class ClockSampler:
-    """Samples SM clock / power / throttle reasons with nvidia-smi while a timed
-    region runs. Only reads; never changes a setting."""
+    """Samples SM clock, power and throttle reasons while a timed region runs: through NVML from a
+    thread of this process (10 ms period by default), or through an `nvidia-smi -lms` child when NVML cannot be loaded. Only reads; never
+    changes a setting."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 100):
+    def __init__(self, gpu_index: int = 0, period_ms: Optional[float] = None):
+        # EUX_CLOCK_PERIOD_MS overrides the period; queries take driver locks, so a very short
+        # period can delay the launches it is meant to observe
+        if period_ms is None:
+            period_ms = float(os.environ.get("EUX_CLOCK_PERIOD_MS", "10"))
         self.gpu_index, self.period_ms = gpu_index, period_ms
         self.rows: List[List[str]] = []
         self._proc = None
         self._thread = None
+        self._stop = threading.Event()
+        self._sm: List[float] = []
+        self._power: List[float] = []
+        self._max = None
+        self._reasons = set()
+        self._source = None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
 
     def start(self):
         try:
+            nv, h = self._nvml_handle()
+            self._max = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self._sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                        bits = int(reasons_fn(h))
+                        for name, bit in self.REASON_BITS.items():
+                            if bits & bit:
+                                self._reasons.add(name)
+                        self._power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                    except Exception:
+                        pass
+                    self._stop.wait(self.period_ms / 1000.0)
+
+            self._source = "nvml"
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return self
+        except Exception:
+            self._source = None
+        try:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
+                 "--format=csv,noheader,nounits", "-lms", str(max(10, int(self.period_ms)))],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self._proc = None
             return self
+        self._source = "nvidia-smi"
 
         def reader():
             for line in self._proc.stdout:
@@ -103,9 +153,22 @@ class ClockSampler:
         self._thread.start()
         return self
 
+    def mark(self) -> None:
+        """Forget what was sampled so far: the timed region starts here."""
+        self._sm.clear()
+        self._power.clear()
+        self._reasons.clear()
+        self.rows.clear()
+
     def stop(self) -> Dict:
+        if self._source == "nvml":
+            self._stop.set()
+            self._thread.join(timeout=2)
+            return {"sm_mhz": statistics.median(self._sm) if self._sm else None, "sm_max_mhz": self._max,
+                    "samples": len(self._sm), "reasons": sorted(self._reasons),
+                    "power_w_median": round(statistics.median(self._power), 1) if self._power else None, "source": "nvml"}
         if self._proc is not None:
-            time.sleep(self.period_ms / 1000.0)
+            time.sleep(0.05)
             self._proc.terminate()
             try:
                 self._proc.wait(timeout=5)
@@ -124,4 +187,6 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
+
+
