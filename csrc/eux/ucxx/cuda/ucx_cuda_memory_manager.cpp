@@ -76,14 +76,34 @@ UcxCudaMemoryResourceManager::~UcxCudaMemoryResourceManager() {
   std::lock_guard lk(mu_);
   for (auto& a : arenas_) cudaFree(a.base);
   for (auto& [p, n] : dedicated_) cudaFree(p);
+  for (auto& [n, p] : large_idle_) cudaFree(p);
 }
 
 void* UcxCudaMemoryResourceManager::pool_alloc(size_t bytes) {
   bytes = round_up(bytes ? bytes : 1, kGranule);
   std::lock_guard lk(mu_);
   if (bytes > opt_.arena_bytes / 2) {
+    bytes = round_up(bytes, size_t(2) << 20);
+    // an idle block of at most twice the size serves the request
+    if (auto it = large_idle_.lower_bound(bytes); it != large_idle_.end() && it->first <= 2 * bytes) {
+      void* p = it->second;
+      dedicated_[p] = it->first;
+      large_idle_bytes_ -= it->first;
+      large_idle_.erase(it);
+      return p;
+    }
     void* p = nullptr;
-    if (cudaMalloc(&p, bytes) != cudaSuccess) throw std::bad_alloc();
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      // give the idle blocks back and try once more
+      for (auto& [n, q] : large_idle_) {
+        regs_.erase(reinterpret_cast<uintptr_t>(q));
+        cudaFree(q);
+      }
+      large_idle_.clear();
+      large_idle_bytes_ = 0;
+      if (cudaMalloc(&p, bytes) != cudaSuccess) throw std::bad_alloc();
+    }
     dedicated_[p] = bytes;
     return p;
   }
@@ -112,9 +132,15 @@ void* UcxCudaMemoryResourceManager::pool_alloc(size_t bytes) {
 bool UcxCudaMemoryResourceManager::pool_free(void* p, size_t bytes) {
   std::lock_guard lk(mu_);
   if (auto it = dedicated_.find(p); it != dedicated_.end()) {
-    regs_.erase(reinterpret_cast<uintptr_t>(p));
-    cudaFree(p);
+    const size_t n = it->second;
     dedicated_.erase(it);
+    if (large_idle_bytes_ + n <= opt_.large_cache_bytes) {
+      large_idle_.emplace(n, p);  // the registration (and its export handle) stays
+      large_idle_bytes_ += n;
+    } else {
+      regs_.erase(reinterpret_cast<uintptr_t>(p));
+      cudaFree(p);
+    }
     return true;
   }
   bytes = round_up(bytes ? bytes : 1, kGranule);

@@ -43,6 +43,10 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
     int device = 0;
     size_t arena_bytes = size_t(64) << 20;
     bool pinned_host = false;  // HOST allocations from cudaHostAlloc (staging buffers)
+    // Blocks too large for an arena are kept after they are freed and handed out again for a
+    // request of a similar size (cudaMalloc/cudaFree synchronise the device, and a reused block
+    // keeps its export handle, so the peers' mappings stay valid). Up to this many idle bytes.
+    size_t large_cache_bytes = size_t(32) << 30;
   };
   struct Registration {
     void* base = nullptr;
@@ -87,7 +91,9 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
   Options opt_;
   mutable std::mutex mu_;
   std::vector<Arena> arenas_;
-  std::unordered_map<void*, size_t> dedicated_;  // oversize allocations
+  std::unordered_map<void*, size_t> dedicated_;  // oversize allocations in use (rounded size)
+  std::multimap<size_t, void*> large_idle_;      // oversize allocations waiting for reuse
+  size_t large_idle_bytes_ = 0;
   std::map<uintptr_t, Registration> regs_;       // by base address
   struct ImportKey {
     uint32_t pid;

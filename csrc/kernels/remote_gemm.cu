@@ -5,8 +5,8 @@
 //
 // One persistent launch, one CTA per SM, three kinds of CTA / warp:
 //   * copy CTAs (blockIdx < copy_ctas): stream 128-row panels of X from the
-//     caller's memory into a local staging buffer with plain 16-byte loads and
-//     stores and publish a per-panel arrival count;
+//     caller's memory into a local staging buffer with bulk asynchronous copies
+//     through shared memory and publish a per-panel arrival count;
 //   * GEMM CTAs: warp 0 = TMA producer (waits for the panel, then loads A and B
 //     tiles with plain per-CTA cp.async.bulk.tensor loads, 128B swizzle), warp 1 =
 //     tcgen05.mma issuer (accumulators in TMEM, two 256-column buffers),
@@ -32,7 +32,7 @@ constexpr int B_STAGE_BYTES = BN * BKB;   // 32 KiB
 constexpr int GEMM_THREADS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
-constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
+constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * 16384 /* output slabs */ + 1024 + 256;
 
 struct GemmParams {
   const unsigned char* x_src;
@@ -162,43 +162,142 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
          ((uint32_t)(BM >> 4) << 24);
 }
 
+// ---- bulk asynchronous copies (TMA, no tensor map): global -> shared -> global ----
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x),
+               "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void epi_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// OR of `flag` over the 128 threads of a named barrier: the epilogue warps leave their loop together
+__device__ __forceinline__ bool epi_vote_any(int id, bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %2, 0;\n\t"
+      "bar.red.or.pred q, %1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"((uint32_t)flag)
+      : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ void st_shared_u4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Output staging for the epilogue: slabs of 128 rows x 64 bf16 columns (128 B per row) in the
+// 128B-swizzled layout that the tensor map of Y expects; a slab leaves as one TMA store, so Y
+// (which may be the caller's memory across NVLink) is written in full 128-byte lines.
+constexpr int EPI_SLAB_BYTES = BM * 128;
+constexpr int EPI_SLABS = 2;
+
+constexpr int CP_CHUNK = 16384;   // bytes per bulk copy
+constexpr int CP_STAGES = 12;     // 192 KiB of shared memory in flight per copy CTA
+
 // Copy CTAs: all of them work on one panel at a time, in order, so the first
-// panel is complete after 1/copy_ctas of its transfer time.
-__device__ void copy_role_n(const GemmParams& p, const int nthreads) {
+// panel is complete after 1/copy_ctas of its transfer time. The bytes move as
+// bulk asynchronous copies through a ring of shared-memory chunks: one thread
+// issues the loads from the caller's (peer) memory, another one the stores into
+// the local staging buffer. A load over NVLink takes microseconds to come back,
+// so what matters is the number of bytes in flight: 12 x 16 KiB per CTA, which
+// register-held loads of a whole CTA cannot reach.
+__device__ bool copy_role_n(const GemmParams& p, const int nthreads, unsigned char* smem_raw_base) {
+  __shared__ uint64_t cp_bars[2 * CP_STAGES];
+  __shared__ int cp_abort;
   const size_t row_bytes = (size_t)p.K * p.elem_bytes;
-  const size_t panel_vec = (size_t)BM * row_bytes / 16;
+  const size_t panel_bytes = (size_t)BM * row_bytes;
   const int panels = p.M / BM;
-  const size_t per_cta = (panel_vec + p.copy_ctas - 1) / p.copy_ctas;
   if (p.x_scale_src && p.x_scale_stage && p.x_scale_src != p.x_scale_stage) {
     // the row scales travel first: each CTA copies its slice before it reports any panel
     const size_t n = (size_t)p.M * (p.K / 128);
     for (size_t i = (size_t)blockIdx.x * nthreads + threadIdx.x; i < n; i += (size_t)p.copy_ctas * nthreads)
       p.x_scale_stage[i] = __ldcg(p.x_scale_src + i);
+    __threadfence();
   }
-  for (int pn = 0; pn < panels; ++pn) {
-    const uint4* s = reinterpret_cast<const uint4*>(p.x_src + (size_t)pn * BM * row_bytes);
-    uint4* d = reinterpret_cast<uint4*>(p.x_stage + (size_t)pn * BM * row_bytes);
-    const size_t lo = (size_t)blockIdx.x * per_cta;
-    const size_t hi = min(panel_vec, lo + per_cta);
-    size_t i = lo + threadIdx.x;
-    for (; i + 7 * (size_t)nthreads < hi; i += 8 * (size_t)nthreads) {
-      uint4 v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = ld_cg_u4(s + i + j * nthreads);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) st_u4(d + i + j * nthreads, v[j]);
+  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw_base + 127) & ~(uintptr_t)127);
+  const uint32_t ring0 = smem_u32(ring);
+  const uint32_t bar0 = smem_u32(cp_bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (CP_STAGES + s); };
+  if (threadIdx.x == 0) {
+    cp_abort = 0;
+    for (int s = 0; s < CP_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
     }
-    for (; i < hi; i += nthreads) st_u4(d + i, ld_cg_u4(s + i));
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abort = &cp_abort;
+  // this CTA's slice of every panel, in 16-byte units
+  const size_t panel_vec = panel_bytes / 16;
+  const size_t per_cta = (panel_vec + p.copy_ctas - 1) / p.copy_ctas;
+  const size_t lo = min(panel_vec, (size_t)blockIdx.x * per_cta) * 16;
+  const size_t hi = min(panel_vec, (size_t)blockIdx.x * per_cta + per_cta) * 16;
+
+  if (threadIdx.x == 0) {
+    // ---- loads from the caller's memory ----
+    uint32_t c = 0;
+    for (int pn = 0; pn < panels && !*abort; ++pn) {
+      const unsigned char* src = p.x_src + (size_t)pn * panel_bytes;
+      for (size_t off = lo; off < hi; off += CP_CHUNK, ++c) {
+        const int st = (int)(c % CP_STAGES);
+        const uint32_t ph = (c / CP_STAGES) & 1u;
+        if (!mbar_wait(empty_bar(st), ph ^ 1u, abort, p.timeout_ns)) break;
+        const uint32_t n = (uint32_t)min((size_t)CP_CHUNK, hi - off);
+        mbar_expect_tx(full_bar(st), n);
+        bulk_g2s(ring0 + (uint32_t)st * CP_CHUNK, src + off, n, full_bar(st));
+      }
+    }
+    if (*abort) {  // loads that were issued still write shared memory: give them time to land
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+  } else if (threadIdx.x == 32) {
+    // ---- stores into the local staging buffer, and the per-panel report ----
+    uint32_t c = 0, released = 0;
+    for (int pn = 0; pn < panels && !*abort; ++pn) {
+      unsigned char* dst = p.x_stage + (size_t)pn * panel_bytes;
+      for (size_t off = lo; off < hi; off += CP_CHUNK, ++c) {
+        const int st = (int)(c % CP_STAGES);
+        const uint32_t ph = (c / CP_STAGES) & 1u;
+        if (!mbar_wait(full_bar(st), ph, abort, p.timeout_ns)) break;
+        const uint32_t n = (uint32_t)min((size_t)CP_CHUNK, hi - off);
+        bulk_s2g(dst + off, ring0 + (uint32_t)st * CP_CHUNK, n);
+        bulk_commit();
+        bulk_wait_read_1();  // every store but the newest has finished reading its chunk
+        for (; released < c; ++released) mbar_arrive(empty_bar((int)(released % CP_STAGES)));
+      }
+      if (*abort) break;
+      bulk_wait_all();  // this panel's slice is in the staging buffer
+      for (; released < c; ++released) mbar_arrive(empty_bar((int)(released % CP_STAGES)));
       asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence();
       red_release_gpu_add(p.panel_flags + pn, 1u);
     }
+    bulk_wait_all();
+    if (*abort) {
+      if (p.status) set_status(p.status, EUX_ST_TIMEOUT, 9);
+      atomicExch(p.sched + 1, 1u);
+    }
   }
+  __syncthreads();
+  return cp_abort == 0;
 }
-
-__device__ __forceinline__ void copy_role(const GemmParams& p) { copy_role_n(p, GEMM_THREADS); }
 
 __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
   __syncthreads();
@@ -217,17 +316,20 @@ __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
 
 template <bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_y, GemmParams p) {
   if ((int)blockIdx.x < p.copy_ctas) {
-    copy_role(p);
-    finish_cta(p, true);
+    extern __shared__ unsigned char copy_smem[];
+    const bool ok = copy_role_n(p, GEMM_THREADS, copy_smem);
+    finish_cta(p, ok);
     return;
   }
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;
   unsigned char* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  unsigned char* sEpi = smem + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);  // 1024-aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_SLABS * EPI_SLAB_BYTES);
   // bars: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
@@ -330,33 +432,57 @@ remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   } else if (warp >= 4) {
     // ---------------- epilogue ----------------
     const int lg = warp - 4;  // TMEM lane group of this warp
+    const int row_local = lg * 32 + lane;
+    const bool elected = warp == 4 && lane == 0;  // issues (and so owns) the TMA stores
+    const uint32_t epi0 = smem_u32(sEpi);
     int it = 0;
+    uint32_t slab = 0;
     for (int tile = first; tile < total && !*abort; tile += step, ++it) {
       int mb, nb;
       tile_coords(tile, m_blocks, n_blocks, mb, nb);
       const int buf = it & 1;
       const uint32_t tph = (uint32_t)(it >> 1) & 1u;
-      if (!mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns)) break;
+      const bool got = mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns);
+      if (epi_vote_any(1, !got)) break;  // all four warps or none: the slab barriers below need everyone
       tc_fence_after();
-      const int row = mb * BM + lg * 32 + lane;
-      __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)row * p.N + (size_t)nb * BN;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)buf * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tbase + c * 32, r);
-        tmem_ld_wait();
-        uint4 o[4];
-        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(o);
+      for (int sl = 0; sl < BN / 64; ++sl, ++slab) {
+        const uint32_t sbuf = epi0 + (slab & 1u) * EPI_SLAB_BYTES;
+        if (elected) bulk_wait_read_1();  // the store that used this slab two steps ago has read it
+        epi_bar_sync(1);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) q[j] = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-        uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(tbase + sl * 64 + h * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) st_u4(dst + j, o[j]);
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              q[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+            const int chunk = h * 4 + j;  // 16-byte chunk of this row's 128 bytes
+            st_shared_u4(sbuf + (uint32_t)row_local * 128u + (uint32_t)((chunk ^ (row_local & 7)) * 16), o);
+          }
+        }
+        if (sl == BN / 64 - 1) {  // the accumulator is out of TMEM: the next tile may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epi_bar_sync(1);
+        if (elected) {
+          tma_store_2d(&map_y, sbuf, nb * BN + sl * 64, mb * BM);
+          bulk_commit();
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+    if (elected) {  // Y is complete before this CTA reports
+      bulk_wait_all();
+      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
 
@@ -390,20 +516,23 @@ constexpr int A8_STAGE_BYTES = BM * BKB;
 constexpr int B8_STAGE_BYTES = BN8 * BKB;
 constexpr int GEMM8_THREADS = 384;  // warp 0 TMA, warp 1 MMA, warps 4..11 epilogue (two per TMEM lane group)
 constexpr int TMEM8_COLS = 256;
-constexpr size_t GEMM8_SMEM = (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES) + 1024 + 256;
+constexpr size_t GEMM8_SMEM = (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES) + 2 * 16384 /* output slabs */ + 1024 + 256;
 
 __global__ void __launch_bounds__(GEMM8_THREADS, 1)
-remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_y, GemmParams p) {
   if ((int)blockIdx.x < p.copy_ctas) {
-    copy_role_n(p, GEMM8_THREADS);
-    finish_cta(p, true);
+    extern __shared__ unsigned char copy_smem[];
+    const bool ok = copy_role_n(p, GEMM8_THREADS, copy_smem);
+    finish_cta(p, ok);
     return;
   }
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;
   unsigned char* sB = smem + (size_t)STAGES8 * A8_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES));
+  unsigned char* sEpi = smem + (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES);  // 1024-aligned, one slab per half
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_SLABS * EPI_SLAB_BYTES);
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -497,6 +626,9 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   } else if (warp >= 4) {
     const int lg = (warp - 4) & 3;    // TMEM lane group
     const int half = (warp - 4) >> 2;  // which 64 columns of the tile
+    const int row_local = lg * 32 + lane;
+    const bool elected = lg == 0 && lane == 0;  // one per half: issues (and owns) that half's TMA stores
+    const uint32_t sbuf = smem_u32(sEpi) + (uint32_t)half * EPI_SLAB_BYTES;
     uint32_t blk = 0;
     const int kscales = p.K / 128;
     for (int tile = first; tile < total && !*abort; tile += step) {
@@ -534,16 +666,26 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           acc[32 + j] = fmaf(scale, __uint_as_float(r1[j]), acc[32 + j]);
         }
       }
-      if (!ok) break;
-      __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)row * p.N + (size_t)nb * BN8 + half * 64;
+      if (elected) bulk_wait_read_0();  // the previous tile's store has read this half's slab
+      if (epi_vote_any(1 + half, !ok)) break;  // the four warps of a half leave together
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint4 o;
         __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[c * 8 + 2 * j], acc[c * 8 + 2 * j + 1]);
-        st_u4(reinterpret_cast<uint4*>(yrow + c * 8), o);
+        st_shared_u4(sbuf + (uint32_t)row_local * 128u + (uint32_t)((c ^ (row_local & 7)) * 16), o);
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      epi_bar_sync(1 + half);
+      if (elected) {
+        tma_store_2d(&map_y, sbuf, nb * BN8 + half * 64, mb * BM);
+        bulk_commit();
+      }
+    }
+    if (elected) {  // Y is complete before this CTA reports
+      bulk_wait_all();
+      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
   tc_fence_before();
@@ -617,6 +759,8 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   CUtensorMap ma, mb;
   if (int rc = make_map(&ma, d->x_stage, eb, (uint64_t)d->M, (uint64_t)d->K, BM)) return rc;
   if (int rc = make_map(&mb, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, bn)) return rc;
+  CUtensorMap my;  // Y[M,N] bf16 in slabs of 128 rows x 64 columns
+  if (int rc = make_map(&my, d->y_dst, 2, (uint64_t)d->M, (uint64_t)d->N, BM)) return rc;
   GemmParams p;
   p.x_src = (const unsigned char*)d->x_src;
   p.x_stage = (unsigned char*)d->x_stage;
@@ -640,8 +784,8 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   }
   const int tiles = (d->M / BM) * (d->N / bn);
   int grid = copy_ctas + (tiles < sms - copy_ctas ? tiles : sms - copy_ctas);
-  if (d->fp8) remote_gemm_fp8_kernel<<<grid, GEMM8_THREADS, GEMM8_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
-  else remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, p);
+  if (d->fp8) remote_gemm_fp8_kernel<<<grid, GEMM8_THREADS, GEMM8_SMEM, (cudaStream_t)stream>>>(ma, mb, my, p);
+  else remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, my, p);
   return (int)cudaGetLastError();
 }
 
