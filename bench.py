@@ -295,12 +295,41 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
                     "experts": w.a2a.n_experts}
         return run
 
+    def baselines():
+        """The same three workloads with library calls only (NCCL, cuBLAS through torch)."""
+        from execution_ucx_b200.models import baselines as bl
+        out = {"note": "library baselines measured in this run: none of this package's kernels on these paths"}
+        n = src.numel() * 2
+        echo = bl.NcclEcho(rank, world, n, dev)
+        ts = timing.time_cuda(lambda: echo.step(src), iters=10, warmup=3, before=group.barrier if world > 1 else None)
+        ms = group.max_over_ranks(timing.percentile(ts, 50))
+        out["echo_1GiB"] = {"what": "NCCL send/recv there and back" if world > 1 else "two torch D2D copies",
+                            "ms_p50": round(ms, 4), "one_way_GBps_aggregate": round(n / (ms / 2 * 1e-3) / 1e9 * world, 1)}
+        del echo
+        m = nn = k = 8192
+        gm = bl.RecvGemmSend(rank, world, m, nn, k, dev)
+        ts = timing.time_cuda(gm.step, iters=10, warmup=3, flush=flush, before=group.barrier if world > 1 else None)
+        ms = group.max_over_ranks(timing.percentile(ts, 50))
+        out["remote_gemm_bf16"] = {"what": "NCCL recv X + cuBLAS + NCCL send Y" if world > 1 else "cuBLAS (torch.matmul)",
+                                   "ms_p50": round(ms, 4), "tflops_per_gpu": round(2.0 * m * nn * k / (ms * 1e-3) / 1e12, 1)}
+        del gm
+        w = MoeDispatchCombine(group, fp8=False)
+        mo = bl.AllToAllMoe(rank, world, w.x, w.idx, w.w, w.a2a.n_experts)
+        ts = timing.time_cuda(mo.step, iters=10, warmup=3, flush=flush, before=group.barrier if world > 1 else None)
+        us = group.max_over_ranks(timing.percentile(ts, 50)) * 1e3
+        err = float((mo.out.float() - w.reference()).abs().max())
+        out["moe_bf16"] = {"what": "torch sort/gather + all_to_all_single x2 + index_add_", "dispatch_combine_us_p50": round(us, 1),
+                           "max_abs_err": err}
+        w.a2a.close()
+        return out
+
     guarded("latency_sweep_device", sweep)
     guarded("tensor_rpc_sweep", rpc_sweep)
     guarded("remote_gemm_rpc_bf16", gemm(False))
     guarded("remote_gemm_rpc_fp8_block_scaled", gemm(True))
     guarded("moe_bf16", moe(False))
     guarded("moe_fp8", moe(True))
+    guarded("library_baselines", baselines)
     return extra
 
 

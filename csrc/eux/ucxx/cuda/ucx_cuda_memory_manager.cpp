@@ -35,6 +35,20 @@ bool address_range(const void* ptr, void** base, size_t* size) {
   return true;
 }
 
+// Allocation and release run on whatever thread asks (a pool thread, the caller's thread): the
+// manager's device becomes current for the duration, whatever that thread had before.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int want) {
+    if (want < 0) return;
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != want) switched = cudaSetDevice(want) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
 class PinnedHostResource final : public std::pmr::memory_resource {
   void* do_allocate(size_t bytes, size_t) override {
     void* p = nullptr;
@@ -74,6 +88,7 @@ UcxCudaMemoryResourceManager::UcxCudaMemoryResourceManager(const Options& opt) :
 UcxCudaMemoryResourceManager::~UcxCudaMemoryResourceManager() {
   release_imports();
   std::lock_guard lk(mu_);
+  DeviceGuard on_device(opt_.device);
   for (auto& a : arenas_) cudaFree(a.base);
   for (auto& [p, n] : dedicated_) cudaFree(p);
   for (auto& [n, p] : large_idle_) cudaFree(p);
@@ -82,6 +97,7 @@ UcxCudaMemoryResourceManager::~UcxCudaMemoryResourceManager() {
 void* UcxCudaMemoryResourceManager::pool_alloc(size_t bytes) {
   bytes = round_up(bytes ? bytes : 1, kGranule);
   std::lock_guard lk(mu_);
+  DeviceGuard on_device(opt_.device);
   if (bytes > opt_.arena_bytes / 2) {
     bytes = round_up(bytes, size_t(2) << 20);
     // an idle block of at most twice the size serves the request
@@ -131,6 +147,7 @@ void* UcxCudaMemoryResourceManager::pool_alloc(size_t bytes) {
 
 bool UcxCudaMemoryResourceManager::pool_free(void* p, size_t bytes) {
   std::lock_guard lk(mu_);
+  DeviceGuard on_device(opt_.device);
   if (auto it = dedicated_.find(p); it != dedicated_.end()) {
     const size_t n = it->second;
     dedicated_.erase(it);
@@ -172,6 +189,7 @@ void* UcxCudaMemoryResourceManager::allocate(ucx_memory_type_t type, size_t byte
   switch (type) {
     case ucx_memory_type::CUDA: return pool_alloc(bytes);
     case ucx_memory_type::CUDA_MANAGED: {
+      DeviceGuard on_device(opt_.device);
       void* p = nullptr;
       if (cudaMallocManaged(&p, bytes ? bytes : 1) != cudaSuccess) throw std::bad_alloc();
       return p;
@@ -278,6 +296,7 @@ void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d) {
   }
   if (!d.exportable) return nullptr;
   std::lock_guard lk(mu_);
+  DeviceGuard on_device(opt_.device);
   ImportKey key{d.pid, d.base};
   auto it = imports_.find(key);
   if (it == imports_.end()) {
@@ -295,6 +314,7 @@ void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d) {
 
 void UcxCudaMemoryResourceManager::release_imports() {
   std::lock_guard lk(mu_);
+  DeviceGuard on_device(opt_.device);
   for (auto& [k, p] : imports_) cudaIpcCloseMemHandle(p);
   imports_.clear();
 }

@@ -135,11 +135,10 @@ static int run_client(AxonRuntime& cli, const std::string& server_name, const Op
   for (size_t bytes : o.sizes) {
     std::vector<float> host(bytes / 4);
     for (size_t i = 0; i < host.size(); ++i) host[i] = float(i % 1000);
-    auto make_payload = [&] {
-      UcxBuffer b(*mr, type, bytes);
-      mr->memcpy(type, b.data(), ucx_memory_type::HOST, host.data(), bytes);
-      return b;
-    };
+    // every request sends the same resident tensor: a view that does not own the bytes
+    UcxBuffer resident(*mr, type, bytes);
+    mr->memcpy(type, resident.data(), ucx_memory_type::HOST, host.data(), bytes);
+    auto make_payload = [&] { return UcxBuffer(*mr, type, resident.data(), bytes, nullptr, false); };
     auto call = [&] {
       return cli.InvokeRpc(server_name, session_id_t{1}, function_id_t{1}, workflow_id_t{}, client_policy(cli, o), f32_meta(bytes), make_payload());
     };
