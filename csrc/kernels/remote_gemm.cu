@@ -641,17 +641,38 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc[j] = 0.f;
       bool ok = true;
-      for (int k = 0; k < k_blocks; ++k, ++blk) {
+      // When X is pulled from a peer its row scales travel with it: they are known to have landed
+      // once the panel is reported, so the warp checks the panel itself before it reads any of them
+      // (the loads below run ahead of the MMA, which is what hides their latency).
+      if (p.copy_ctas > 0) {
+        int arrived = 1;
+        if (lane == 0) arrived = wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)p.copy_ctas, p.timeout_ns) ? 1 : 0;
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (!arrived) {
+          *abort = 1;
+          ok = false;
+        }
+      }
+      // scales two K-blocks ahead of their use
+      float s0 = 0.f, s1 = 0.f;
+      if (ok) {
+        s0 = __ldcg(sx) * __ldg(sw);
+        if (k_blocks > 1) s1 = __ldcg(sx + 1) * __ldg(sw + 1);
+      }
+      for (int k = 0; ok && k < k_blocks; ++k, ++blk) {
         const int buf = blk & 1;
         const uint32_t tph = (blk >> 1) & 1u;
+        float sx2 = 0.f, sw2 = 0.f;
+        if (k + 2 < k_blocks) {
+          sx2 = __ldcg(sx + k + 2);
+          sw2 = __ldg(sw + k + 2);
+        }
         if (!mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        // read only now: when X is pulled from a peer, the row scales are known to have landed once
-        // the products of this panel exist (the producer waited for the panel before loading it)
-        const float scale = __ldcg(sx + k) * __ldg(sw + k);
+        const float scale = s0;
         const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)buf * BN8 + (uint32_t)half * 64;
         uint32_t r0[32], r1[32];
         tmem_ld32(tbase, r0);
@@ -665,6 +686,8 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           acc[j] = fmaf(scale, __uint_as_float(r0[j]), acc[j]);
           acc[32 + j] = fmaf(scale, __uint_as_float(r1[j]), acc[32 + j]);
         }
+        s0 = s1;
+        s1 = sx2 * sw2;
       }
       if (elected) bulk_wait_read_0();  // the previous tile's store has read this half's slab
       if (epi_vote_any(1 + half, !ok)) break;  // the four warps of a half leave together
