@@ -1,6 +1,7 @@
 // Client pipeline of AxonWorker: endpoints, InvokeRpc, response handling
 // (reference: axon/include/axon/axon_worker.hpp:1052-1208, axon/src/axon_worker.cpp:1424-1667).
 #include "eux/axon/axon_worker_detail.hpp"
+#include "eux/ucxx/nvtx_range.hpp"
 #include "eux/ucxx/ucx_context_logger.hpp"
 
 namespace eux::axon {
@@ -231,6 +232,7 @@ struct AxonWorker::invoke_sender {
 };
 
 InvokeSender AxonWorker::InvokeRpc(std::string_view worker_name, RpcRequestHeader&& header, PayloadVariant&& payload, ClientMemoryPolicy mem_policy) {
+  ucxx::NvtxRange range("axon.client.invoke");
   if (!client_running_.load() || !client_ctx_)
     return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::WorkerStartFailed), "the client is not running"));
   auto conn = GetConnectionId(worker_name);
@@ -265,6 +267,7 @@ InvokeSender AxonWorker::InvokeRpc(std::string_view worker_name, RpcRequestHeade
 
 // The response announced a rendezvous payload: receive it where the caller's policy says, then finish.
 void AxonWorker::ClientFinishWithPayload(std::shared_ptr<ClientCall> call) {
+  ucxx::NvtxRange range("axon.client.receive_payload");
   auto sched = client_ctx_->get_scheduler();
   const size_t key = *call->rndv_key;
   auto metas = utils::GetTensorMetas(call->response.results);

@@ -2,6 +2,7 @@
 #include <ctime>
 
 #include "eux/axon/axon_worker_detail.hpp"
+#include "eux/ucxx/nvtx_range.hpp"
 #include "eux/ucxx/ucx_context_logger.hpp"
 
 namespace eux::axon {
@@ -136,6 +137,7 @@ void AxonWorker::ServerHandleArrival(ucxx::recv_header_result_t&& arrival) {
 
 // Rendezvous: choose where the payload lands, receive it, then dispatch.
 void AxonWorker::ServerRunRequest(std::shared_ptr<ServerCall> call) {
+  ucxx::NvtxRange range("axon.server.receive_payload");
   auto sched = server_ctx_->get_scheduler();
   const size_t key = *call->rndv_key;
   const bool wants_vec = call->signature.input_payload_type == rpc::PayloadType::UCX_BUFFER_VEC;
@@ -191,6 +193,7 @@ void AxonWorker::ServerRunRequest(std::shared_ptr<ServerCall> call) {
 
 // Lifecycle policy, handler on the pool under the deadline, response.
 void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
+  ucxx::NvtxRange range("axon.server.dispatch");
   PayloadVariant for_handler;
   if (auto* retention = std::get_if<RetentionPolicy>(&call->lifecycle); retention && *retention) {
     const utils::AxonMessageID id = call->req.hlc.Raw();
@@ -267,6 +270,7 @@ void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
 }
 
 void AxonWorker::ServerSendResponse(std::shared_ptr<ServerCall> call, RpcResponseHeader&& header, PayloadVariant&& payload) {
+  ucxx::NvtxRange range("axon.server.send_response");
   if (!server_ctx_) return;
   header.session_id = call->req.session_id;
   header.request_id = call->req.request_id;

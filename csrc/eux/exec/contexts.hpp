@@ -255,7 +255,10 @@ class timed_single_thread_context {
         it->fire(it, cancelled);
         lk.lock();
       } else {
-        cv_.wait_until(lk, first->first);
+        // a copy: the wait re-reads its deadline after the lock is retaken, and the node that
+        // holds `first->first` may have been erased by cancel() in the meantime
+        const time_point due = first->first;
+        cv_.wait_until(lk, due);
       }
     }
   }

@@ -14,6 +14,7 @@
 #include <cstring>
 #include <random>
 
+#include "eux/ucxx/nvtx_range.hpp"
 #include "eux/ucxx/ucx_context_logger.hpp"
 #include "kernels/eux_kernels.h"
 
@@ -458,7 +459,32 @@ void Worker::destroy(Endpoint* ep) {
   graveyard_.push_back(ep);
 }
 
+namespace {
+std::mutex g_fault_mu;
+std::shared_ptr<FaultHook> g_fault_hook;  // null when no test has installed one
+std::atomic<bool> g_fault_on{false};
+}  // namespace
+
+void set_fault_hook(FaultHook hook) {
+  std::lock_guard lk(g_fault_mu);
+  g_fault_hook = hook ? std::make_shared<FaultHook>(std::move(hook)) : nullptr;
+  g_fault_on.store(g_fault_hook != nullptr, std::memory_order_release);
+}
+
 void Worker::enqueue(Endpoint* ep, Endpoint::SendItem&& item) {
+  if (g_fault_on.load(std::memory_order_acquire) && item.owned.size() >= sizeof(FrameHeader)) {
+    std::shared_ptr<FaultHook> hook;
+    {
+      std::lock_guard lk(g_fault_mu);
+      hook = g_fault_hook;
+    }
+    FrameHeader fh;
+    std::memcpy(&fh, item.owned.data(), sizeof(fh));
+    if (hook && (*hook)(opt_.name, fh.type, fh.msg_id)) {
+      if (item.done) item.done(UCS_OK);  // lost on the wire: the sender cannot tell
+      return;
+    }
+  }
   ep->sendq_.push_back(std::move(item));
   if (ep->state_ == Endpoint::State::kConnected || ep->state_ == Endpoint::State::kHelloSent) flush(ep);
 }
@@ -1045,6 +1071,7 @@ bool Worker::ensure_device() {
 int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
                         Completion& done) {
   if (!cuda_mr_ || !ensure_device()) return UCS_ERR_UNSUPPORTED;
+  NvtxRange range("eux.transport.device_pull");
   std::vector<void*> srcs(info.regions.size());
   for (size_t i = 0; i < info.regions.size(); ++i) {
     srcs[i] = cuda_mr_->import_region(info.regions[i]);

@@ -30,7 +30,9 @@
 #include <deque>
 #include <functional>
 #include <list>
+#include <atomic>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -46,6 +48,13 @@ class Worker;
 class Endpoint;
 
 using Completion = std::function<void(int status)>;
+
+// Test shim for fault injection on the host: when set, every outgoing frame is shown to the hook
+// (the sending worker's name, the frame type, the message id); a frame for which it returns true
+// is dropped as if the wire had lost it (its local completion still fires). Process-wide; tests
+// install it, run a scenario, and clear it again with an empty function.
+using FaultHook = std::function<bool(const std::string& worker_name, uint8_t frame_type, uint64_t msg_id)>;
+void set_fault_hook(FaultHook hook);
 
 constexpr uint32_t kFrameMagic = 0x46585545u;  // "EUXF"
 enum FrameType : uint8_t {

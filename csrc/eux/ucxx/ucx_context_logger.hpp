@@ -5,6 +5,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <memory>
 #include <mutex>
 #include <sstream>
@@ -67,7 +68,16 @@ class UcxLoggerManager {
   }
 
  private:
-  UcxLoggerManager() : logger_(std::make_shared<DefaultUcxLogger>()) {}
+  // EUX_LOG_LEVEL=TRACE|DEBUG|INFO|WARN|ERROR|FATAL|OFF sets the default logger's threshold
+  UcxLoggerManager() : logger_(std::make_shared<DefaultUcxLogger>(level_from_env())) {}
+  static LogLevel level_from_env() {
+    const char* e = std::getenv("EUX_LOG_LEVEL");
+    if (!e) return LogLevel::ERROR;
+    const std::string_view v(e);
+    for (int l = 0; l <= static_cast<int>(LogLevel::OFF); ++l)
+      if (v == to_string(static_cast<LogLevel>(l))) return static_cast<LogLevel>(l);
+    return LogLevel::ERROR;
+  }
   std::mutex mu_;
   std::shared_ptr<UcxLogger> logger_;
 };

@@ -87,6 +87,9 @@ EUX_API int eux_xfer_launch(const eux_xfer_desc* d, uint32_t* scratch_counter, i
 
 /* Batch of independent small transfers in one launch: CTA i handles descs[i]
  * (device-resident array of n descriptors). No scratch needed: one CTA each. */
+/* Same contract as eux_xfer_launch for a dense same-type copy of 16-byte aligned buffers, moved by the
+ * bulk-copy engine (TMA) through shared memory instead of by register loads and stores. */
+EUX_API int eux_xfer_bulk_launch(const eux_xfer_desc* desc, uint32_t* scratch_counter, int max_ctas, void* stream);
 EUX_API int eux_xfer_batch_launch(const eux_xfer_desc* descs_dev, int n, void* stream);
 
 /* Device-driven ping-pong between two GPUs (or loopback on one): see

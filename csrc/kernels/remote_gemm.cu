@@ -19,6 +19,7 @@
 // EUX_ST_TIMEOUT in the status word.
 #include <cuda.h>
 
+#include "eux_bulk.cuh"
 #include "eux_device.cuh"
 
 namespace eux {
@@ -52,47 +53,6 @@ struct GemmParams {
   float* x_scale_stage;       // local copy used by the epilogue (== x_scale_src when X is local)
   const float* w_scale;       // [N/128, K/128], local
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; returns false (and raises *abort) when the limit passes or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, uint64_t timeout_ns) {
-  if (mbar_try(bar, parity)) return true;
-  const uint64_t limit = timeout_ns ? timeout_ns : 2000000000ull;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 255u) == 255u) {
-      if (*abort) return false;
-      if (globaltimer_ns() - t0 > limit) {
-        *abort = 1;
-        return false;
-      }
-    }
-  }
-  *abort = 1;
-  return false;
-}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
@@ -162,26 +122,22 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
          ((uint32_t)(BM >> 4) << 24);
 }
 
-// ---- bulk asynchronous copies (TMA, no tensor map): global -> shared -> global ----
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x),
                "r"(y)
                : "memory");
 }
 __device__ __forceinline__ void epi_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// Two fp32 multiply-adds in one instruction: (a0, a1) += (x0, x1) * s
+__device__ __forceinline__ void ffma2(float& a0, float& a1, float x0, float x1, float s) {
+  asm("{\n\t.reg .b64 va, vx, vs;\n\t"
+      "mov.b64 va, {%0, %1};\n\tmov.b64 vx, {%2, %3};\n\tmov.b64 vs, {%4, %4};\n\t"
+      "fma.rn.f32x2 va, vx, vs, va;\n\t"
+      "mov.b64 {%0, %1}, va;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(x0), "f"(x1), "f"(s));
+}
+
 // OR of `flag` over the 128 threads of a named barrier: the epilogue warps leave their loop together
 __device__ __forceinline__ bool epi_vote_any(int id, bool flag) {
   uint32_t out;
@@ -515,7 +471,8 @@ constexpr int STAGES8 = 6;
 constexpr int A8_STAGE_BYTES = BM * BKB;
 constexpr int B8_STAGE_BYTES = BN8 * BKB;
 constexpr int GEMM8_THREADS = 384;  // warp 0 TMA, warp 1 MMA, warps 4..11 epilogue (two per TMEM lane group)
-constexpr int TMEM8_COLS = 256;
+constexpr int TMEM8_COLS = 512;
+constexpr int TBUF8 = 4;  // partial products in flight: four 128-column TMEM buffers
 constexpr size_t GEMM8_SMEM = (size_t)STAGES8 * (A8_STAGE_BYTES + B8_STAGE_BYTES) + 2 * 16384 /* output slabs */ + 1024 + 256;
 
 __global__ void __launch_bounds__(GEMM8_THREADS, 1)
@@ -540,14 +497,14 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES8 + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES8 + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES8 + 2 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES8 + TBUF8 + b); };
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES8; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < TBUF8; ++b) {
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), 8);
     }
@@ -606,8 +563,8 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       uint32_t blk = 0;  // running K-block count: selects the TMEM buffer and its phase
       for (int tile = first; tile < total && !*abort; tile += step) {
         for (int k = 0; k < k_blocks && !*abort; ++k, ++blk) {
-          const int buf = blk & 1;
-          const uint32_t tph = (blk >> 1) & 1u;
+          const int buf = blk & (TBUF8 - 1);
+          const uint32_t tph = (blk / TBUF8) & 1u;
           if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abort, p.timeout_ns)) break;
           if (!mbar_wait(full_bar(s), ph, abort, p.timeout_ns)) break;
           tc_fence_after();
@@ -660,8 +617,8 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (k_blocks > 1) s1 = __ldcg(sx + 1) * __ldg(sw + 1);
       }
       for (int k = 0; ok && k < k_blocks; ++k, ++blk) {
-        const int buf = blk & 1;
-        const uint32_t tph = (blk >> 1) & 1u;
+        const int buf = blk & (TBUF8 - 1);
+        const uint32_t tph = (blk / TBUF8) & 1u;
         float sx2 = 0.f, sw2 = 0.f;
         if (k + 2 < k_blocks) {
           sx2 = __ldcg(sx + k + 2);
@@ -682,9 +639,9 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));  // the buffer is in registers: the next block may overwrite it
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          acc[j] = fmaf(scale, __uint_as_float(r0[j]), acc[j]);
-          acc[32 + j] = fmaf(scale, __uint_as_float(r1[j]), acc[32 + j]);
+        for (int j = 0; j < 32; j += 2) {
+          ffma2(acc[j], acc[j + 1], __uint_as_float(r0[j]), __uint_as_float(r0[j + 1]), scale);
+          ffma2(acc[32 + j], acc[33 + j], __uint_as_float(r1[j]), __uint_as_float(r1[j + 1]), scale);
         }
         s0 = s1;
         s1 = sx2 * sw2;

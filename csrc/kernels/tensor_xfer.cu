@@ -8,6 +8,7 @@
 // dtype cast -> dense store into the destination (normally a slot of the
 // peer's receive arena, mapped into this process) -> system-scope release of
 // a sequence flag. Nothing is staged through the host.
+#include "eux_bulk.cuh"
 #include "eux_device.cuh"
 
 namespace eux {
@@ -83,24 +84,26 @@ __device__ __forceinline__ void cta_publish(const eux_xfer_desc& d, uint32_t* co
   if (last && ok && d.flag) st_release_sys(d.flag, d.flag_value);
 }
 
-// Dense byte copy, 16 B per access, 4 accesses in flight per thread.
+// Dense byte copy, 16 B per access, 8 accesses in flight per thread. A CTA works on one
+// contiguous block of 8 x blockDim x 16 B at a time (64 KiB with 512 threads), so that what it has
+// in flight stays inside a few DRAM pages; the blocks are dealt round-robin to the CTAs.
 __device__ __forceinline__ void copy_bytes_grid(const unsigned char* src, unsigned char* dst, uint64_t nbytes,
                                                 uint64_t tid, uint64_t nthreads) {
+  constexpr int U = 8;
   const uint64_t nvec = nbytes >> 4;
   const uint4* s4 = reinterpret_cast<const uint4*>(src);
   uint4* d4 = reinterpret_cast<uint4*>(dst);
-  uint64_t i = tid;
-  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
-    uint4 a = ld_cg_u4(s4 + i);
-    uint4 b = ld_cg_u4(s4 + i + nthreads);
-    uint4 c = ld_cg_u4(s4 + i + 2 * nthreads);
-    uint4 e = ld_cg_u4(s4 + i + 3 * nthreads);
-    st_u4(d4 + i, a);
-    st_u4(d4 + i + nthreads, b);
-    st_u4(d4 + i + 2 * nthreads, c);
-    st_u4(d4 + i + 3 * nthreads, e);
+  const uint64_t block_vec = (uint64_t)blockDim.x * U;
+  const uint64_t nblocks = nvec / block_vec;
+  for (uint64_t b = blockIdx.x; b < nblocks; b += gridDim.x) {
+    const uint64_t i = b * block_vec + threadIdx.x;
+    uint4 v[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) v[j] = ld_cg_u4(s4 + i + (uint64_t)j * blockDim.x);
+#pragma unroll
+    for (int j = 0; j < U; ++j) st_u4(d4 + i + (uint64_t)j * blockDim.x, v[j]);
   }
-  for (; i < nvec; i += nthreads) st_u4(d4 + i, ld_cg_u4(s4 + i));
+  for (uint64_t i = nblocks * block_vec + tid; i < nvec; i += nthreads) st_u4(d4 + i, ld_cg_u4(s4 + i));
   for (uint64_t b = (nvec << 4) + tid; b < nbytes; b += nthreads) dst[b] = src[b];
 }
 
@@ -113,6 +116,78 @@ __global__ void __launch_bounds__(kXferThreads) xfer_bytes_kernel(XferArgs a) {
                     (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
   }
   cta_publish(d, a.counter, ok);
+}
+
+// Dense byte copy on the bulk-copy engine: two threads per CTA drive a ring of shared-memory
+// chunks (loads from the source with completion on an mbarrier, stores to the destination in
+// bulk groups). The SMs issue almost no instructions, and the bytes in flight per CTA (the whole
+// ring) do not depend on how many threads there are, which is what a source across NVLink needs.
+constexpr int kBulkChunk = 16384;
+constexpr int kBulkStages = 6;  // 96 KiB of ring per CTA: two CTAs per SM
+constexpr int kBulkThreads = 128;
+constexpr size_t kBulkSmem = (size_t)kBulkChunk * kBulkStages + 128;
+
+__global__ void __launch_bounds__(kBulkThreads) xfer_bulk_kernel(XferArgs a) {
+  extern __shared__ unsigned char xb_raw[];
+  __shared__ uint64_t xb_bars[2 * kBulkStages];
+  __shared__ int xb_abort;
+  const eux_xfer_desc& d = a.d;
+  bool ok = cta_wait_arrival(d);
+  const uint32_t ring0 = smem_u32(reinterpret_cast<unsigned char*>(((uintptr_t)xb_raw + 127) & ~(uintptr_t)127));
+  const uint32_t bar0 = smem_u32(xb_bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kBulkStages + s); };
+  if (threadIdx.x == 0) {
+    xb_abort = 0;
+    for (int s = 0; s < kBulkStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abort = &xb_abort;
+  const uint64_t nbytes = d.n_elems * (uint64_t)dtype_size(d.src_dtype);
+  const uint64_t body = nbytes & ~(uint64_t)15;
+  const uint64_t nchunks = (body + kBulkChunk - 1) / kBulkChunk;
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src);
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
+  if (ok && threadIdx.x == 0) {
+    uint32_t c = 0;
+    for (uint64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x, ++c) {
+      const int st = (int)(c % kBulkStages);
+      if (!mbar_wait(empty_bar(st), ((c / kBulkStages) & 1u) ^ 1u, abort, d.wait_timeout_ns)) break;
+      const uint64_t off = ch * kBulkChunk;
+      const uint32_t n = (uint32_t)min((uint64_t)kBulkChunk, body - off);
+      mbar_expect_tx(full_bar(st), n);
+      bulk_g2s(ring0 + (uint32_t)st * kBulkChunk, src + off, n, full_bar(st));
+    }
+    if (*abort) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+  } else if (ok && threadIdx.x == 32) {
+    uint32_t c = 0, released = 0;
+    for (uint64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x, ++c) {
+      const int st = (int)(c % kBulkStages);
+      if (!mbar_wait(full_bar(st), (c / kBulkStages) & 1u, abort, d.wait_timeout_ns)) break;
+      const uint64_t off = ch * kBulkChunk;
+      const uint32_t n = (uint32_t)min((uint64_t)kBulkChunk, body - off);
+      bulk_s2g(dst + off, ring0 + (uint32_t)st * kBulkChunk, n);
+      bulk_commit();
+      bulk_wait_read_1();
+      for (; released < c; ++released) mbar_arrive(empty_bar((int)(released % kBulkStages)));
+    }
+    bulk_wait_all();  // the stores have been performed
+    asm volatile("fence.proxy.async;" ::: "memory");
+    if (*abort) set_status(d.status, EUX_ST_TIMEOUT, 2);
+  } else if (ok && blockIdx.x == 0 && threadIdx.x >= 64 && threadIdx.x < 64 + (nbytes & 15)) {
+    const uint64_t b = body + (threadIdx.x - 64);
+    dst[b] = src[b];
+  }
+  __syncthreads();
+  cta_publish(d, a.counter, ok && xb_abort == 0);
 }
 
 // Dense typed path: 8 elements per step, cast + handler fused.
@@ -383,6 +458,29 @@ extern "C" int eux_xfer_launch(const eux_xfer_desc* d, uint32_t* scratch_counter
     if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
     xfer_strided_kernel<<<grid, kXferThreads, 0, st>>>(a);
   }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int eux_xfer_bulk_launch(const eux_xfer_desc* d, uint32_t* scratch_counter, int max_ctas, void* stream) {
+  if (!d || !d->src || !d->dst || d->ndim != 0) return EUX_ERR_BAD_ARG;
+  if (d->src_dtype != d->dst_dtype || d->op != EUX_OP_NONE) return EUX_ERR_BAD_ARG;
+  if ((((uintptr_t)d->src) | ((uintptr_t)d->dst)) & 15u) return EUX_ERR_BAD_ARG;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return EUX_ERR_BAD_ARG;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(xfer_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSmem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
+  }
+  const uint64_t bytes = d->n_elems * (uint64_t)dtype_size(d->src_dtype);
+  if (max_ctas <= 0) max_ctas = 2 * num_sms();
+  uint64_t want = (bytes + kBulkChunk - 1) / kBulkChunk;
+  int grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
+  if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
+  XferArgs a{*d, scratch_counter};
+  xfer_bulk_kernel<<<grid, kBulkThreads, kBulkSmem, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
 

@@ -7,6 +7,7 @@
 #include <numeric>
 
 #include "check.hpp"
+#include "eux/ucxx/transport.hpp"
 #include "eux/axon/axon_runtime.hpp"
 
 using namespace eux::axon;
@@ -263,6 +264,87 @@ EUX_TEST(stop_client_cancels_pending_and_peer_loss_is_an_error) {
 }
 
 // Server and client in separate processes; the address travels through a pipe.
+// Fault injection on the host: a response frame lost on the wire, a rendezvous reply lost, and
+// a memory policy that cannot allocate. Each ends as an error at the caller within its deadline;
+// nothing hangs, and the same workers serve the next call.
+EUX_TEST(injected_faults_end_as_errors) {
+  namespace tr = eux::ucxx::transport;
+  Pair p;
+  p.server.RegisterFunction(function_id_t{1}, [](int32_t a) { return a + 1; }, "inc");
+  std::atomic<int> provider_calls{0};
+  CustomMemoryPolicy<UcxBuffer> flaky = [&](eux::rpc::utils::TensorMetaSpan metas) -> UcxBuffer {
+    if (provider_calls.fetch_add(1) == 0) throw std::bad_alloc();
+    return UcxBuffer(*p.mr, ucx_memory_type::HOST, eux::rpc::utils::CalculateTensorSize(metas[0]));
+  };
+  p.server.RegisterFunction<UcxBuffer>(function_id_t{2}, [](const TensorMeta&, const UcxBuffer& b) { return int64_t(b.size()); }, "size_of",
+                                       flaky, MessageLifecyclePolicy{});
+  p.connect();
+  p.client.SetTimeout(200ms);
+  auto call_inc = [&](int32_t v) {
+    return ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, v));
+  };
+  CHECK_EQ(call_inc(1)->header.GetPrimitive<int32_t>(0), 2);
+
+  // 1. the server's next eager frame (the response) is lost
+  std::atomic<int> dropped{0};
+  tr::set_fault_hook([&](const std::string& worker, uint8_t type, uint64_t) {
+    return worker == "server" && type == tr::kAmEager && dropped.fetch_add(1) == 0;
+  });
+  bool deadline = false;
+  auto t0 = std::chrono::steady_clock::now();
+  try {
+    call_inc(5);
+  } catch (const RpcException& e) {
+    deadline = e.code() == make_error_code(RpcErrc::DEADLINE_EXCEEDED);
+  }
+  CHECK(deadline);
+  CHECK(std::chrono::steady_clock::now() - t0 < 2000ms);
+  tr::set_fault_hook(nullptr);
+  CHECK_EQ(dropped.load() >= 1, true);
+  CHECK_EQ(call_inc(7)->header.GetPrimitive<int32_t>(0), 8);
+  CHECK_EQ(p.client.PendingRpcCount(), 0u);
+
+  // 2. the memory policy fails once: the caller gets an error status, the next call goes through
+  auto send_tensor = [&] {
+    const int64_t n = 65536;
+    UcxBuffer buf(*p.mr, ucx_memory_type::HOST, size_t(n) * 4);
+    std::memset(buf.data(), 0, buf.size());
+    return ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}, f32_meta(n), std::move(buf)));
+  };
+  p.client.SetTimeout(2000ms);
+  bool failed = false;
+  try {
+    auto r = send_tensor();
+    failed = r && !r->header.status.ok();
+  } catch (const std::exception&) {
+    failed = true;
+  }
+  CHECK(failed);
+  auto ok = send_tensor();
+  CHECK(ok && ok->header.status.ok());
+  CHECK_EQ(ok->header.GetPrimitive<int64_t>(0), int64_t(65536 * 4));
+
+  // 3. the receiver's clear-to-send for a rendezvous payload is lost: the caller's deadline ends the call
+  p.client.SetTimeout(200ms);
+  std::atomic<int> cts_dropped{0};
+  tr::set_fault_hook([&](const std::string& worker, uint8_t type, uint64_t) {
+    return worker == "server" && type == tr::kRndvCts && cts_dropped.fetch_add(1) == 0;
+  });
+  bool timed_out = false;
+  try {
+    auto r = send_tensor();
+    timed_out = r && !r->header.status.ok();
+  } catch (const std::exception&) {
+    timed_out = true;
+  }
+  tr::set_fault_hook(nullptr);
+  CHECK(timed_out);
+  CHECK_EQ(cts_dropped.load() >= 1, true);
+  p.client.SetTimeout(2000ms);
+  auto again = send_tensor();
+  CHECK(again && again->header.status.ok());
+}
+
 EUX_TEST(forked_processes_echo) {
   int addr_pipe[2], ctl_pipe[2];
   CHECK(pipe(addr_pipe) == 0 && pipe(ctl_pipe) == 0);

@@ -177,6 +177,39 @@ def build_python_module(verbose: bool = False) -> Path:
     return out
 
 
+def build_sanitized(kind: str = "thread", verbose: bool = False):
+    """Host runtime and C++ tests under a sanitizer (``thread``, ``address`` or ``undefined``), for
+    CPU-only runs: ``python -m execution_ucx_b200._build --sanitize thread`` builds
+    ``build/sanitize-<kind>/eux_*_test``. The CUDA kernels are not instrumented (device code is
+    checked by its numerics tests and by the bounded waits)."""
+    if kind not in ("thread", "address", "undefined"):
+        raise ValueError("sanitizer must be thread, address or undefined")
+    out_dir = ROOT / "build" / f"sanitize-{kind}"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    build_kernels(verbose)
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + ["-O1", "-g", f"-fsanitize={kind}", "-fno-omit-frame-pointer"]
+    deps = _headers(CSRC / "eux", CSRC / "kernels")
+    # the sanitizer runtimes ship with the distribution's compiler
+    san_cxx = os.environ.get("EUX_SANITIZE_CXX", "/usr/bin/g++" if Path("/usr/bin/g++").exists() else CXX)
+
+    def cc(s, o):
+        return [san_cxx, *flags, "-c", s, "-o", o]
+
+    objs, _ = _compile_objects(_runtime_sources(), cc, f"rt-{kind}", deps, verbose)
+    outs = []
+
+    def one(s):
+        out = out_dir / ("eux_" + s.stem)
+        if _newer([s, *deps, *objs], out):
+            _run([san_cxx, *flags, s, *objs, "-o", out, "-L", LIB, "-leux_kernels", "-L", CUDA_HOME / "lib64", "-lcudart",
+                  "-ldl", "-lrt", "-Wl,-rpath," + str(LIB), "-Wl,-rpath," + str(CUDA_HOME / "lib64")], verbose)
+        return out
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        outs = list(ex.map(one, sorted((CSRC / "tests").glob("*.cpp"))))
+    return outs
+
+
 def build_all(verbose: bool = False) -> None:
     if shutil.which(NVCC) is None and not Path(NVCC).exists():
         raise RuntimeError(f"nvcc not found at {NVCC}")
@@ -187,5 +220,10 @@ def build_all(verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    build_all(verbose="-q" not in sys.argv)
-    print("build ok")
+    if "--sanitize" in sys.argv:
+        kind = sys.argv[sys.argv.index("--sanitize") + 1]
+        for b in build_sanitized(kind, verbose="-q" not in sys.argv):
+            print(b)
+    else:
+        build_all(verbose="-q" not in sys.argv)
+        print("build ok")

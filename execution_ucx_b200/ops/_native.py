@@ -79,6 +79,7 @@ def load():
     lib = C.CDLL(str(_LIB_PATH), mode=C.RTLD_GLOBAL)
     P, I, U64 = C.c_void_p, C.c_int, C.c_uint64
     lib.eux_xfer_launch.argtypes = [C.POINTER(XferDesc), P, I, P]
+    lib.eux_xfer_bulk_launch.argtypes = [C.POINTER(XferDesc), P, I, P]
     lib.eux_xfer_batch_launch.argtypes = [P, I, P]
     lib.eux_pingpong_launch.argtypes = [C.POINTER(PingPongDesc), I, P]
     lib.eux_ipc_export.argtypes = [P, C.c_char_p]

@@ -66,11 +66,14 @@ def make_desc(src: torch.Tensor, dst_ptr: int, dst_dtype: torch.dtype, op: int =
 
 def push(src: torch.Tensor, dst, *, dst_dtype: Optional[torch.dtype] = None, op: int = OP_NONE,
          op_arg: float = 0.0, flag_ptr: int = 0, flag_value: int = 0, wait_flag_ptr: int = 0,
-         wait_value: int = 0, wait_timeout_ns: int = 0, status_ptr: int = 0, max_ctas: int = 0) -> None:
+         wait_value: int = 0, wait_timeout_ns: int = 0, status_ptr: int = 0, max_ctas: int = 0,
+         bulk: bool = False) -> None:
     """Launch one transfer on the current stream.
 
     ``dst`` is a tensor (its dtype is the destination dtype) or a raw device
-    address (then ``dst_dtype`` is required); it may be peer memory.
+    address (then ``dst_dtype`` is required); it may be peer memory. ``bulk`` moves a dense
+    same-type copy of 16-byte aligned buffers with the bulk-copy engine instead of register
+    loads and stores.
     """
     global _launches
     if not src.is_cuda:
@@ -86,8 +89,9 @@ def push(src: torch.Tensor, dst, *, dst_dtype: Optional[torch.dtype] = None, op:
                   wait_timeout_ns, status_ptr)
     counter = _scratch_counter(src.device)
     lib = _native.load()
-    _native.check(lib.eux_xfer_launch(C.byref(d), C.c_void_p(counter.data_ptr()), max_ctas,
-                                      C.c_void_p(_native.current_stream_ptr())), "eux_xfer_launch")
+    fn = lib.eux_xfer_bulk_launch if bulk else lib.eux_xfer_launch
+    _native.check(fn(C.byref(d), C.c_void_p(counter.data_ptr()), max_ctas,
+                     C.c_void_p(_native.current_stream_ptr())), "eux_xfer_bulk_launch" if bulk else "eux_xfer_launch")
     _launches += 1
 
 
