@@ -84,36 +84,71 @@ __device__ __forceinline__ void cta_publish(const eux_xfer_desc& d, uint32_t* co
   if (last && ok && d.flag) st_release_sys(d.flag, d.flag_value);
 }
 
-// Dense byte copy, 16 B per access, 8 accesses in flight per thread. A CTA works on one
-// contiguous block of 8 x blockDim x 16 B at a time (64 KiB with 512 threads), so that what it has
-// in flight stays inside a few DRAM pages; the blocks are dealt round-robin to the CTAs.
-__device__ __forceinline__ void copy_bytes_grid(const unsigned char* src, unsigned char* dst, uint64_t nbytes,
-                                                uint64_t tid, uint64_t nthreads) {
-  constexpr int U = 8;
-  const uint64_t nvec = nbytes >> 4;
-  const uint4* s4 = reinterpret_cast<const uint4*>(src);
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
-  const uint64_t block_vec = (uint64_t)blockDim.x * U;
-  const uint64_t nblocks = nvec / block_vec;
-  for (uint64_t b = blockIdx.x; b < nblocks; b += gridDim.x) {
-    const uint64_t i = b * block_vec + threadIdx.x;
-    uint4 v[U];
-#pragma unroll
-    for (int j = 0; j < U; ++j) v[j] = ld_cg_u4(s4 + i + (uint64_t)j * blockDim.x);
-#pragma unroll
-    for (int j = 0; j < U; ++j) st_u4(d4 + i + (uint64_t)j * blockDim.x, v[j]);
-  }
-  for (uint64_t i = nblocks * block_vec + tid; i < nvec; i += nthreads) st_u4(d4 + i, ld_cg_u4(s4 + i));
-  for (uint64_t b = (nvec << 4) + tid; b < nbytes; b += nthreads) dst[b] = src[b];
+// Dense byte copy. A CTA works on one contiguous block at a time and the blocks are dealt
+// round-robin to the CTAs, so that what a CTA has in flight stays inside a few DRAM pages.
+// With 32-byte aligned buffers each thread moves two 32-byte vectors per block (measured best
+// on B200: 3.31 TB/s each way for a local copy, above cudaMemcpy's 3.26; four or eight 16-byte
+// accesses in flight per thread reach 3.17 and 3.01); otherwise four 16-byte vectors.
+__device__ __forceinline__ void ld_v8(const void* p, uint32_t (&v)[8]) {
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void st_v8(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
 }
 
+// `cta` of `nctas` CTAs share the copy (the whole grid for one message, a single CTA for one
+// descriptor of a batch).
+template <bool V32>
+__device__ __forceinline__ void copy_bytes_grid(const unsigned char* src, unsigned char* dst, uint64_t nbytes,
+                                                uint32_t cta, uint32_t nctas) {
+  const uint64_t tid = (uint64_t)cta * blockDim.x + threadIdx.x;
+  const uint64_t nthreads = (uint64_t)nctas * blockDim.x;
+  uint64_t done = 0;  // bytes handled by the blocked loops
+  if (V32) {
+    constexpr int U = 2;
+    const uint64_t block_bytes = (uint64_t)blockDim.x * U * 32;
+    const uint64_t nblocks = nbytes / block_bytes;
+    for (uint64_t b = cta; b < nblocks; b += nctas) {
+      const uint64_t off = b * block_bytes + (uint64_t)threadIdx.x * 32;
+      uint32_t v[U][8];
+#pragma unroll
+      for (int j = 0; j < U; ++j) ld_v8(src + off + (uint64_t)j * blockDim.x * 32, v[j]);
+#pragma unroll
+      for (int j = 0; j < U; ++j) st_v8(dst + off + (uint64_t)j * blockDim.x * 32, v[j]);
+    }
+    done = nblocks * block_bytes;
+  } else {
+    constexpr int U = 4;
+    const uint64_t block_bytes = (uint64_t)blockDim.x * U * 16;
+    const uint64_t nblocks = nbytes / block_bytes;
+    for (uint64_t b = cta; b < nblocks; b += nctas) {
+      const uint64_t off = b * block_bytes + (uint64_t)threadIdx.x * 16;
+      uint4 v[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) v[j] = ld_cg_u4(src + off + (uint64_t)j * blockDim.x * 16);
+#pragma unroll
+      for (int j = 0; j < U; ++j) st_u4(dst + off + (uint64_t)j * blockDim.x * 16, v[j]);
+    }
+    done = nblocks * block_bytes;
+  }
+  // what is left of the last block: 16-byte vectors, then single bytes
+  const uint64_t nvec = (nbytes - done) >> 4;
+  for (uint64_t i = tid; i < nvec; i += nthreads) st_u4(dst + done + i * 16, ld_cg_u4(src + done + i * 16));
+  for (uint64_t b = done + (nvec << 4) + tid; b < nbytes; b += nthreads) dst[b] = src[b];
+}
+
+template <bool V32>
 __global__ void __launch_bounds__(kXferThreads) xfer_bytes_kernel(XferArgs a) {
   const eux_xfer_desc& d = a.d;
   bool ok = cta_wait_arrival(d);
   if (ok) {
     const uint64_t nbytes = d.n_elems * (uint64_t)dtype_size(d.src_dtype);
-    copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.src), reinterpret_cast<unsigned char*>(d.dst), nbytes,
-                    (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
+    copy_bytes_grid<V32>(reinterpret_cast<const unsigned char*>(d.src), reinterpret_cast<unsigned char*>(d.dst), nbytes,
+                         blockIdx.x, gridDim.x);
   }
   cta_publish(d, a.counter, ok);
 }
@@ -286,8 +321,8 @@ __global__ void __launch_bounds__(256) xfer_batch_kernel(const eux_xfer_desc* de
     const bool raw = d.src_dtype == d.dst_dtype && d.op == EUX_OP_NONE;
     const bool al16 = ((((uintptr_t)d.src) | ((uintptr_t)d.dst)) & 15u) == 0;
     if (dense && raw && al16) {
-      copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.src), reinterpret_cast<unsigned char*>(d.dst),
-                      d.n_elems * esz, threadIdx.x, blockDim.x);
+      copy_bytes_grid<false>(reinterpret_cast<const unsigned char*>(d.src), reinterpret_cast<unsigned char*>(d.dst),
+                             d.n_elems * esz, 0, 1);
     } else if (dense && al16 && d.src_dtype == EUX_DT_F32 && d.dst_dtype == EUX_DT_F32) {
       const float4* s = reinterpret_cast<const float4*>(d.src);
       float4* t = reinterpret_cast<float4*>(d.dst);
@@ -364,12 +399,12 @@ __global__ void __launch_bounds__(kXferThreads) pingpong_kernel(eux_pingpong_des
       __syncthreads();
       if (!s_ok) { alive = false; break; }
     }
-    copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.local_buf), reinterpret_cast<unsigned char*>(d.peer_buf),
-                    d.nbytes, tid, nthreads);
+    copy_bytes_grid<false>(reinterpret_cast<const unsigned char*>(d.local_buf), reinterpret_cast<unsigned char*>(d.peer_buf),
+                           d.nbytes, blockIdx.x, gridDim.x);
     if (!grid_barrier(d.grid_bar, gen, d.wait_timeout_ns)) { alive = false; break; }
     if (d.initiator == 2) {
-      copy_bytes_grid(reinterpret_cast<const unsigned char*>(d.peer_buf), reinterpret_cast<unsigned char*>(d.local_buf),
-                      d.nbytes, tid, nthreads);
+      copy_bytes_grid<false>(reinterpret_cast<const unsigned char*>(d.peer_buf), reinterpret_cast<unsigned char*>(d.local_buf),
+                             d.nbytes, blockIdx.x, gridDim.x);
       if (!grid_barrier(d.grid_bar, gen, d.wait_timeout_ns)) { alive = false; break; }
       continue;
     }
@@ -428,17 +463,20 @@ extern "C" int eux_xfer_launch(const eux_xfer_desc* d, uint32_t* scratch_counter
   cudaStream_t st = (cudaStream_t)stream;
   XferArgs a{*d, scratch_counter};
   const int sms = num_sms();
-  if (max_ctas <= 0) max_ctas = 2 * sms;
+  const bool ctas_given = max_ctas > 0;
+  if (!ctas_given) max_ctas = 2 * sms;
   const uint64_t src_bytes = d->n_elems * (uint64_t)dtype_size(d->src_dtype);
   const bool raw = d->src_dtype == d->dst_dtype && d->op == EUX_OP_NONE;
   const uintptr_t al = ((uintptr_t)d->src) | ((uintptr_t)d->dst);
   int grid;
   if (d->ndim == 0 && raw && (al & 15u) == 0) {
-    // 64 B per thread per step; small messages stay on one CTA (no counter traffic)
+    // 64 B per thread per step, one CTA per SM; small messages stay on one CTA (no counter traffic)
+    if (!ctas_given) max_ctas = sms;
     uint64_t want = (src_bytes + (uint64_t)kXferThreads * 64 - 1) / ((uint64_t)kXferThreads * 64);
     grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
     if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
-    xfer_bytes_kernel<<<grid, kXferThreads, 0, st>>>(a);
+    if ((al & 31u) == 0) xfer_bytes_kernel<true><<<grid, kXferThreads, 0, st>>>(a);
+    else xfer_bytes_kernel<false><<<grid, kXferThreads, 0, st>>>(a);
   } else if (d->ndim == 0 && d->src_dtype != EUX_DT_BYTES && (al & 15u) == 0) {
     uint64_t want = (d->n_elems / 8 + kXferThreads - 1) / kXferThreads;
     grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));

@@ -81,6 +81,21 @@ def test_batch(cuda_device):
         assert int(flags[i]) == i + 1
 
 
+def test_batch_large_raw_copies(cuda_device):
+    """Each descriptor of a batch is copied whole by its own CTA, also when it spans many copy blocks."""
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    srcs, dsts, descs = [], [], []
+    for i, n in enumerate((1 << 18, (1 << 20) + 40, 3 * (1 << 16) + 8, 1000)):
+        s = torch.randint(0, 255, (n,), dtype=torch.uint8, device=cuda_device)
+        d = torch.zeros_like(s)
+        srcs.append(s), dsts.append(d)
+        descs.append(tx.make_desc(s, d.data_ptr(), torch.uint8))
+    tx.push_batch(descs)
+    torch.cuda.synchronize()
+    for s, d in zip(srcs, dsts):
+        assert torch.equal(d, s)
+
+
 def test_bounded_wait_reports_timeout(cuda_device):
     """A wait that nothing satisfies ends by itself with a status, not a hang."""
     from execution_ucx_b200.ops import tensor_xfer as tx
