@@ -6,6 +6,7 @@
 // (reference: rpc_core/rpc_dispatcher.hpp:242-1089).
 #pragma once
 
+#include <typeindex>
 #include <algorithm>
 #include <functional>
 #include <memory>
@@ -173,6 +174,37 @@ void fill_return_signature(RpcFunctionSignature& s) {
 
 }  // namespace detail
 
+// ---- natural call (reference: GetCaller under EUX_RPC_ENABLE_NATURAL_CALL, rpc_core/rpc_dispatcher.hpp:335-673) ----
+// A registered native callable can be fetched back and called with ordinary C++ arguments, without a
+// request header in between: `(*dispatcher.GetCaller<int(int, int)>(id))(20, 22)`.
+namespace detail {
+template <class R, class ArgsTuple>
+struct canon_fn;
+template <class R, class... A>
+struct canon_fn<R, std::tuple<A...>> {
+  using type = std::function<R(std::remove_cvref_t<A>&...)>;  // every argument by lvalue reference to its decayed type
+};
+// hands the canonical lvalue on the way the declared parameter wants it: by reference as it is, by value as an rvalue
+template <class Decl, class T>
+constexpr decltype(auto) pass_as(T& v) {
+  if constexpr (std::is_lvalue_reference_v<Decl>) return (v);
+  else return std::move(v);
+}
+}  // namespace detail
+
+template <class Sig>
+class NaturalCaller;
+template <class R, class... A>
+class NaturalCaller<R(A...)> {
+ public:
+  using canon_type = typename detail::canon_fn<R, std::tuple<A...>>::type;
+  explicit NaturalCaller(std::shared_ptr<canon_type> fn) : fn_(std::move(fn)) {}
+  R operator()(A... a) const { return (*fn_)(const_cast<std::remove_cvref_t<A>&>(a)...); }
+
+ private:
+  std::shared_ptr<canon_type> fn_;
+};
+
 class RpcDispatcher {
  public:
   explicit RpcDispatcher(std::string instance_name = "default") : instance_name_(std::move(instance_name)) {}
@@ -212,7 +244,32 @@ class RpcDispatcher {
     sig.function_name = name;
     detail::signature_of_args<typename Traits::args_tuple>::fill(sig);
     detail::fill_return_signature<typename Traits::return_type>(sig);
-    return insert(id, std::move(sig), MakeRpcWrapper(std::forward<F>(f)));
+    using Callable = std::remove_cvref_t<F>;
+    if constexpr (std::is_copy_constructible_v<Callable>) {
+      // one copy serves the serialised path, the other the natural call
+      auto [native, tag] = make_native<typename Traits::return_type, typename Traits::args_tuple>(Callable(f));
+      return insert(id, std::move(sig), MakeRpcWrapper(std::forward<F>(f)), std::move(native), tag);
+    } else {
+      return insert(id, std::move(sig), MakeRpcWrapper(std::forward<F>(f)));
+    }
+  }
+  // The registered native callable as something callable with ordinary arguments. Throws
+  // std::runtime_error when the id is unknown, when the function was registered in its dynamic
+  // (type-erased) form, or when `Sig` differs from the registered signature in more than
+  // const / reference qualifiers. Exceptions of the callable reach the caller unchanged.
+  template <class Sig>
+  std::shared_ptr<NaturalCaller<Sig>> GetCaller(function_id_t id) const {
+    std::shared_ptr<Entry> e;
+    {
+      std::shared_lock lk(mu_);
+      auto it = functions_.find(id);
+      if (it != functions_.end()) e = it->second;
+    }
+    if (!e) throw std::runtime_error("GetCaller: function " + std::to_string(id.v_) + " is not registered");
+    using Canon = typename NaturalCaller<Sig>::canon_type;
+    if (!e->native || e->native_type != std::type_index(typeid(Canon)))
+      throw std::runtime_error("GetCaller: function " + std::to_string(id.v_) + " has no native form with this signature");
+    return std::make_shared<NaturalCaller<Sig>>(std::static_pointer_cast<Canon>(e->native));
   }
   template <class C, class R, class... A>
   bool RegisterFunction(function_id_t id, R (C::*mf)(A...), C* obj, const data::string& name = {}) {
@@ -389,9 +446,23 @@ class RpcDispatcher {
   struct Entry {
     RpcFunctionSignature signature;
     DynamicRpcFunction fn;
+    std::shared_ptr<void> native;                         // canon_fn of the registered callable, if it has one
+    std::type_index native_type = std::type_index(typeid(void));
   };
-  bool insert(function_id_t id, RpcFunctionSignature&& sig, DynamicRpcFunction&& fn) {
-    auto e = std::make_shared<Entry>(Entry{std::move(sig), std::move(fn)});
+  template <class R, class ArgsTuple, class Callable>
+  static std::pair<std::shared_ptr<void>, std::type_index> make_native(Callable&& c) {
+    return make_native_impl<R>(std::forward<Callable>(c), static_cast<ArgsTuple*>(nullptr));
+  }
+  template <class R, class Callable, class... A>
+  static std::pair<std::shared_ptr<void>, std::type_index> make_native_impl(Callable&& c, std::tuple<A...>*) {
+    using Canon = typename detail::canon_fn<R, std::tuple<A...>>::type;
+    auto shared = std::make_shared<std::remove_cvref_t<Callable>>(std::forward<Callable>(c));
+    auto canon = std::make_shared<Canon>([shared](std::remove_cvref_t<A>&... a) -> R { return (*shared)(detail::pass_as<A>(a)...); });
+    return {std::static_pointer_cast<void>(canon), std::type_index(typeid(Canon))};
+  }
+  bool insert(function_id_t id, RpcFunctionSignature&& sig, DynamicRpcFunction&& fn, std::shared_ptr<void> native = nullptr,
+              std::type_index native_type = std::type_index(typeid(void))) {
+    auto e = std::make_shared<Entry>(Entry{std::move(sig), std::move(fn), std::move(native), native_type});
     std::unique_lock lk(mu_);
     return functions_.emplace(id, std::move(e)).second;
   }

@@ -202,6 +202,11 @@ class Endpoint {
 
 class Worker {
  public:
+  // 0 keeps the current value
+  void set_limits(size_t eager_limit, size_t send_copy_limit) {
+    if (eager_limit) opt_.eager_limit = eager_limit;
+    if (send_copy_limit) opt_.send_copy_limit = send_copy_limit;
+  }
   Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt);
   ~Worker();
   Worker(const Worker&) = delete;

@@ -34,6 +34,29 @@ ucx_am_context::ucx_am_context(UcxMemoryResourceManager& mr, std::string_view na
   worker_->on_ep_error = [this](transport::Endpoint* ep, int status) { on_endpoint_error(ep, status); };
 }
 
+ucx_am_context::ucx_am_context(UcxMemoryResourceManager& mr, ucp_context_h sharedContext, std::string_view name,
+                               std::chrono::milliseconds connectionTimeout, bool connectionHandleError, uint64_t clientId,
+                               std::unique_ptr<UcxAutoDeviceContext> deviceContext)
+    : ucx_am_context(mr, name, connectionTimeout, connectionHandleError, clientId, std::move(deviceContext)) {
+  if (sharedContext) worker_->set_limits(sharedContext->eager_limit, sharedContext->send_copy_limit);
+}
+
+ucs_status_t ucx_am_context::init_ucp_context(std::string_view name, ucp_context_h& ucpContext, bool mtWorkersShared,
+                                              bool printConfig) {
+  auto* c = new eux_shared_transport_context();
+  c->name = std::string(name);
+  c->mt_workers_shared = mtWorkersShared;
+  if (const char* e = std::getenv("EUX_EAGER_LIMIT")) c->eager_limit = std::strtoull(e, nullptr, 10);
+  if (const char* e = std::getenv("UCX_RNDV_THRESH")) c->eager_limit = std::strtoull(e, nullptr, 10);
+  if (printConfig)
+    UCX_CTX_INFO << "shared transport context '" << c->name << "': eager_limit=" << c->eager_limit
+                 << " send_copy_limit=" << c->send_copy_limit << " (0 = default)";
+  ucpContext = c;
+  return UCS_OK;
+}
+
+void ucx_am_context::destroy_ucp_context(ucp_context_h ucpContext) { delete ucpContext; }
+
 ucx_am_context::~ucx_am_context() {
   for (auto& [k, d] : am_desc_map_) d.release(mr_);
   for (auto& d : am_queue_) d.release(mr_);

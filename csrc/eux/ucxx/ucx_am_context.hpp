@@ -106,6 +106,15 @@ class active_message_iovec_buffer_bundle {
 using recv_header_result_t = std::variant<std::pair<size_t, UcxHeader>, active_message_header_buffer_bundle>;
 
 // ---- the context ----------------------------------------------------------------------
+// Settings shared by the contexts of a process: what stands in for a UCP context here.
+struct eux_shared_transport_context {
+  std::string name;
+  bool mt_workers_shared = false;
+  size_t eager_limit = 0;      // 0 = the worker's default
+  size_t send_copy_limit = 0;  // 0 = the worker's default
+};
+using ucp_context_h = eux_shared_transport_context*;
+
 class ucx_am_context {
  public:
   using clock_t = std::chrono::steady_clock;
@@ -133,6 +142,20 @@ class ucx_am_context {
                           std::chrono::milliseconds connectionTimeout = std::chrono::milliseconds(300),
                           bool connectionHandleError = false, uint64_t clientId = 0,
                           std::unique_ptr<UcxAutoDeviceContext> deviceContext = nullptr);
+  // The same with transport settings shared between several contexts of a process
+  // (reference: the overload that takes an external ucp_context_h,
+  // ucx_context/ucx_am_context/ucx_am_context.hpp:424-452). The shared context must outlive
+  // the contexts built on it.
+  ucx_am_context(UcxMemoryResourceManager& mr, ucp_context_h sharedContext, std::string_view name = "default",
+                 std::chrono::milliseconds connectionTimeout = std::chrono::milliseconds(300),
+                 bool connectionHandleError = false, uint64_t clientId = 0,
+                 std::unique_ptr<UcxAutoDeviceContext> deviceContext = nullptr);
+  // Creates / destroys a shared transport context: the eager and copy limits (from the
+  // environment: EUX_EAGER_LIMIT, UCX_RNDV_THRESH) are read once, `printConfig` logs them.
+  // `mtWorkersShared` is recorded for parity; every context still owns its worker thread.
+  static ucs_status_t init_ucp_context(std::string_view name, ucp_context_h& ucpContext, bool mtWorkersShared = false,
+                                       bool printConfig = false);
+  static void destroy_ucp_context(ucp_context_h ucpContext);
   ~ucx_am_context();
   ucx_am_context(const ucx_am_context&) = delete;
 

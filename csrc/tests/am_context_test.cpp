@@ -220,6 +220,50 @@ EUX_TEST(connect_by_worker_address_and_echo) {
   for (size_t i = 0; i < v.size(); i += 997) CHECK_EQ(f[i], float(i) / 2.0f);
 }
 
+// Two contexts built on one shared transport context: its eager limit applies to both
+// (a 256-byte payload goes by rendezvous when the limit is 64).
+EUX_TEST(shared_transport_context) {
+  ucp_context_h shared = nullptr;
+  setenv("EUX_EAGER_LIMIT", "64", 1);
+  CHECK_EQ(ucx_am_context::init_ucp_context("shared", shared, true, false), UCS_OK);
+  unsetenv("EUX_EAGER_LIMIT");
+  CHECK(shared != nullptr && shared->eager_limit == 64 && shared->mt_workers_shared);
+  {
+    DefaultUcxMemoryResourceManager mr;
+    ucx_am_context a(mr, shared, "shared_a", 300ms, true), b(mr, shared, "shared_b", 300ms, true);
+    ex::inplace_stop_source stop;
+    std::thread ta([&] { a.run(stop.get_token()); }), tb([&] { b.run(stop.get_token()); });
+    ex::sync_wait(a.get_scheduler().schedule());
+    ex::sync_wait(b.get_scheduler().schedule());
+    std::vector<std::byte> addr;
+    b.get_ucp_address(addr);
+    auto c = ex::sync_wait(connect_endpoint(a.get_scheduler(), addr));
+    CHECK(c.has_value());
+    uint32_t h = 7;
+    std::vector<char> body(256, 'x');
+    ucx_am_data d{};
+    d.header = {&h, 4};
+    d.buffer = {body.data(), body.size()};
+    d.buffer_type = ucx_memory_type::HOST;
+    ex::async_scope scope;
+    scope.spawn_detached(ex::upon_error(connection_send(a.get_scheduler(), *c, d), [](std::exception_ptr) {}));
+    auto got = ex::sync_wait(connection_recv_header(b.get_scheduler()));
+    CHECK(got.has_value());
+    // above the limit the header arrives first and the payload waits for a buffer
+    CHECK(got->index() == 0);
+    if (got->index() == 0) {
+      auto& [key, hdr] = std::get<0>(*got);
+      auto buf = ex::sync_wait(connection_recv_buffer(b.get_scheduler(), key, ucx_memory_type::HOST));
+      CHECK(buf.has_value() && buf->buffer().size() == 256);
+    }
+    ex::sync_wait(scope.cleanup());
+    stop.request_stop();
+    ta.join();
+    tb.join();
+  }
+  ucx_am_context::destroy_ucp_context(shared);
+}
+
 EUX_TEST(unroutable_address_reports_error) {
   Runner cli("cli", true, 100ms);
   auto* in = new sockaddr_in{};

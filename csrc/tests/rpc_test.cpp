@@ -241,6 +241,48 @@ EUX_TEST(dispatch_errors_and_argument_kinds) {
   static_assert(accepts_every_payload_v<decltype([](auto&&) {})>);
 }
 
+// Natural call: the registered native callables fetched back and called with plain arguments.
+EUX_TEST(get_caller_natural_syntax) {
+  DefaultUcxMemoryResourceManager mr;
+  RpcDispatcher d("natural");
+  d.RegisterFunction(function_id_t{1}, [](int a, int b) { return a + b; }, "add");
+  d.RegisterFunction(function_id_t{2}, [] {}, "no_op");
+  d.RegisterFunction(function_id_t{3}, [] { return std::tuple<int, data::string, float>(123, data::string("hello"), 3.14f); }, "multi");
+  d.RegisterFunction(function_id_t{4}, [&mr] { return UcxBufferVec(mr, ucx_memory_type::HOST, std::vector<size_t>{128, 256}); }, "vec");
+  d.RegisterFunction(function_id_t{5}, [](const UcxBufferVec& v) { return uint64_t(v.total_size()); }, "sum");
+  d.RegisterFunction(function_id_t{6}, [&mr] { return std::tuple<int, UcxBufferVec>(456, UcxBufferVec(mr, ucx_memory_type::HOST, std::vector<size_t>{16, 32})); }, "multi_payload");
+  d.RegisterFunction(function_id_t{7}, []() -> void { throw std::runtime_error("Something went wrong"); }, "boom");
+  d.RegisterFunction(function_id_t{8}, [](UcxBuffer b) { return uint64_t(b.size()); }, "consume");
+
+  CHECK_EQ((*d.GetCaller<int(int, int)>(function_id_t{1}))(20, 22), 42);
+  (*d.GetCaller<void()>(function_id_t{2}))();
+  auto [i, s, f] = (*d.GetCaller<std::tuple<int, data::string, float>()>(function_id_t{3}))();
+  CHECK(i == 123 && s == "hello" && f == 3.14f);
+  auto vec = (*d.GetCaller<UcxBufferVec()>(function_id_t{4}))();
+  CHECK(vec.size() == 2 && vec[0].size == 128 && vec[1].size == 256);
+  UcxBufferVec in(mr, ucx_memory_type::HOST, std::vector<size_t>{100, 200, 300});
+  CHECK_EQ((*d.GetCaller<uint64_t(const UcxBufferVec&)>(function_id_t{5}))(in), uint64_t(600));
+  CHECK_EQ(in.size(), 3u);  // passed by const reference: untouched
+  auto [val, pv] = (*d.GetCaller<std::tuple<int, UcxBufferVec>()>(function_id_t{6}))();
+  CHECK(val == 456 && pv.size() == 2 && pv[1].size == 32);
+  // a by-value payload parameter takes the caller's buffer
+  UcxBuffer gift(mr, ucx_memory_type::HOST, 77);
+  CHECK_EQ((*d.GetCaller<uint64_t(UcxBuffer)>(function_id_t{8}))(std::move(gift)), uint64_t(77));
+  // unknown id, wrong signature, and an exception that comes through as it is
+  CHECK_THROWS(d.GetCaller<void()>(function_id_t{999}));
+  CHECK_THROWS(d.GetCaller<int(int)>(function_id_t{1}));
+  bool same_text = false;
+  try {
+    (*d.GetCaller<void()>(function_id_t{7}))();
+  } catch (const std::runtime_error& e) {
+    same_text = std::string(e.what()) == "Something went wrong";
+  }
+  CHECK(same_text);
+  // the serialised path still works for the same registration
+  auto resp = d.Dispatch(RpcRequestBuilder{}.PrepareRequest({session_id_t{1}, request_id_t{1}, function_id_t{1}}, int(2), int(3)));
+  CHECK(resp.header.status.ok() && resp.header.GetPrimitive<int>(0) == 5);
+}
+
 EUX_TEST(async_dispatcher_senders) {
   ex::static_thread_pool pool(2);
   AsyncRpcDispatcher disp("async");
