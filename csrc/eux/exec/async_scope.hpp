@@ -227,12 +227,14 @@ class async_scope {
   }
 
  private:
+  // The count drops under the mutex that join() checks it under: a joiner that sees zero may
+  // destroy the scope at once, so nothing here may touch the scope after the count is zero and
+  // the lock is released (the waiter is called from a local copy).
   void done_one() noexcept {
-    if (outstanding_.fetch_sub(1, std::memory_order_acq_rel) != 1) return;
     std::function<void()> w;
     {
       std::lock_guard lk(mu_);
-      if (outstanding_.load(std::memory_order_acquire) != 0) return;
+      if (outstanding_.fetch_sub(1, std::memory_order_acq_rel) != 1) return;
       w = std::move(waiter_);
       waiter_ = nullptr;
     }

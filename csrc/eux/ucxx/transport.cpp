@@ -109,6 +109,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
     unsigned long long v = std::strtoull(e, &end, 10);
     if (end != e && v > 0) opt_.eager_limit = v;
   }
+  if (const char* e = std::getenv("EUX_SHM")) opt_.use_shm = e[0] != '0';
   epfd_ = epoll_create1(EPOLL_CLOEXEC);
   if (epfd_ < 0) throw std::system_error(errno, std::generic_category(), "epoll_create1");
   addr_.pid = static_cast<uint32_t>(getpid());
@@ -237,16 +238,63 @@ Endpoint* Worker::connect(const WorkerAddress& addr, Completion done, int* statu
   return connect(reinterpret_cast<sockaddr*>(&in), sizeof(in), nullptr, 0, std::move(done), status);
 }
 
-void Worker::send_hello(Endpoint* ep, uint8_t type) {
+constexpr size_t kShmNameWire = 48;
+
+void Worker::send_hello(Endpoint* ep, uint8_t type, uint8_t flags, const std::string& shm_name) {
   Endpoint::SendItem it;
   FrameHeader fh;
   fh.type = type;
-  fh.header_len = 8 + kAddrWire;
-  it.owned.resize(sizeof(fh) + fh.header_len);
+  fh.flags = flags;
+  const bool offer = (flags & kFlagShmOffer) && !shm_name.empty() && shm_name.size() < kShmNameWire;
+  fh.header_len = 8 + kAddrWire + (offer ? kShmNameWire : 0);
+  it.owned.assign(sizeof(fh) + fh.header_len, 0);
   std::memcpy(it.owned.data(), &fh, sizeof(fh));
   std::memcpy(it.owned.data() + sizeof(fh), &opt_.client_id, 8);
   put_addr(it.owned.data() + sizeof(fh) + 8, addr_);
+  if (offer) std::memcpy(it.owned.data() + sizeof(fh) + 8 + kAddrWire, shm_name.data(), shm_name.size());
+  it.switch_to_shm = type == kHelloAck && (flags & kFlagShmAccept);
   enqueue(ep, std::move(it));
+}
+
+void Worker::activate_shm(Endpoint* ep) {
+  if (!ep->shm_ || ep->shm_active_) return;
+  ep->shm_active_ = true;
+  shm_eps_.push_back(ep);
+}
+
+// Socket-like I/O on whichever channel the endpoint uses.
+ssize_t Worker::io_read(Endpoint* ep, void* buf, size_t n) {
+  return ep->shm_active_ ? ep->shm_->read(buf, n) : ::read(ep->fd_, buf, n);
+}
+ssize_t Worker::io_readv(Endpoint* ep, const iovec* iov, int cnt) {
+  if (!ep->shm_active_) return ::readv(ep->fd_, iov, cnt);
+  ssize_t total = 0;
+  for (int i = 0; i < cnt; ++i) {
+    ssize_t n = ep->shm_->read(iov[i].iov_base, iov[i].iov_len);
+    if (n < 0) break;
+    total += n;
+    if (static_cast<size_t>(n) < iov[i].iov_len) break;
+  }
+  if (total == 0) {
+    errno = EAGAIN;
+    return -1;
+  }
+  return total;
+}
+ssize_t Worker::io_writev(Endpoint* ep, const iovec* iov, int cnt) {
+  if (!ep->shm_active_) return ::writev(ep->fd_, iov, cnt);
+  ssize_t total = 0;
+  for (int i = 0; i < cnt; ++i) {
+    ssize_t n = ep->shm_->write(iov[i].iov_base, iov[i].iov_len);
+    if (n < 0) break;
+    total += n;
+    if (static_cast<size_t>(n) < iov[i].iov_len) break;
+  }
+  if (total == 0) {
+    errno = EAGAIN;
+    return -1;
+  }
+  return total;
 }
 
 Endpoint* Worker::accept(ConnRequest&& req, int* status) {
@@ -262,7 +310,8 @@ Endpoint* Worker::accept(ConnRequest&& req, int* status) {
   ep->remote_client_id_ = req.client_id;
   ep->state_ = Endpoint::State::kConnected;
   ep->rbuf_ = std::move(req.pending);
-  send_hello(ep, kHelloAck);
+  if (opt_.use_shm && !req.shm_name.empty()) ep->shm_ = ShmChannel::open(req.shm_name);  // null on another host
+  send_hello(ep, kHelloAck, ep->shm_ ? kFlagShmAccept : 0);
   *status = UCS_OK;
   if (!ep->rbuf_.empty()) reparse_.push_back(ep);  // frames that came in right behind the HELLO
   return ep;
@@ -293,13 +342,23 @@ void Worker::poll_hellos() {
       ssize_t n = ::read(it->fd, tmp, sizeof(tmp));
       if (n > 0) {
         it->buf.insert(it->buf.end(), tmp, tmp + n);
-        if (it->buf.size() >= sizeof(FrameHeader) + 8 + kAddrWire) break;
+        if (it->buf.size() >= sizeof(FrameHeader)) {
+          FrameHeader peek;
+          std::memcpy(&peek, it->buf.data(), sizeof(peek));
+          if (peek.magic != kFrameMagic || it->buf.size() >= sizeof(FrameHeader) + peek.header_len) break;
+        }
         continue;
       }
       if (n == 0 || (errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) dead = true;
       break;
     }
-    const size_t need = sizeof(FrameHeader) + 8 + kAddrWire;
+    size_t need = sizeof(FrameHeader) + 8 + kAddrWire;
+    if (it->buf.size() >= sizeof(FrameHeader)) {
+      FrameHeader peek;
+      std::memcpy(&peek, it->buf.data(), sizeof(peek));
+      if (peek.magic == kFrameMagic && peek.header_len >= 8 + kAddrWire && peek.header_len <= 8 + kAddrWire + kShmNameWire)
+        need = sizeof(FrameHeader) + peek.header_len;
+    }
     if (!dead && it->buf.size() < need) {
       if (std::chrono::steady_clock::now() - it->since > std::chrono::seconds(5)) dead = true;
       else {
@@ -316,6 +375,10 @@ void Worker::poll_hellos() {
         dead = true;
       } else {
         std::memcpy(&req.client_id, it->buf.data() + sizeof(fh), 8);
+        if ((fh.flags & kFlagShmOffer) && fh.header_len >= 8 + kAddrWire + kShmNameWire) {
+          const char* nm = it->buf.data() + sizeof(fh) + 8 + kAddrWire;
+          req.shm_name.assign(nm, strnlen(nm, kShmNameWire - 1));
+        }
         req.fd = it->fd;
         req.peer_name = it->peer;
         req.worker_name = req.remote.name;
@@ -378,7 +441,30 @@ int Worker::progress() {
     }
     if (evs[i].events & EPOLLOUT) handle_writable(ep);
     if (ep->state_ == Endpoint::State::kFailed || ep->state_ == Endpoint::State::kClosed) continue;
-    if (evs[i].events & (EPOLLIN | EPOLLRDHUP)) handle_readable(ep);
+    if (evs[i].events & (EPOLLIN | EPOLLRDHUP)) {
+      handle_readable(ep);
+      if (ep->shm_active_ && eps_.count(ep) && ep->state_ == Endpoint::State::kConnected && ep->fd_ >= 0) {
+        // the frames travel through the rings; the socket only tells us when the peer is gone
+        char probe;
+        ssize_t r = ::recv(ep->fd_, &probe, 1, MSG_PEEK | MSG_DONTWAIT);
+        if (r == 0 || (r < 0 && errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) fail(ep, UCS_ERR_CONNECTION_RESET);
+      }
+    }
+  }
+  // rings are polled: nothing wakes epoll when a peer writes into shared memory
+  for (size_t i = 0; i < shm_eps_.size();) {
+    Endpoint* ep = shm_eps_[i];
+    if (!eps_.count(ep) || !ep->shm_active_ || ep->state_ == Endpoint::State::kFailed || ep->state_ == Endpoint::State::kClosed) {
+      shm_eps_[i] = shm_eps_.back();
+      shm_eps_.pop_back();
+      continue;
+    }
+    if (ep->shm_->readable()) {
+      ++handled;
+      handle_readable(ep);
+    }
+    if (eps_.count(ep) && ep->state_ == Endpoint::State::kConnected && !ep->sendq_.empty()) flush(ep);
+    ++i;
   }
   if (!hellos_.empty()) poll_hellos();
   if (!device_ops_.empty()) poll_device();
@@ -398,6 +484,8 @@ void Worker::fail(Endpoint* ep, int status) {
     ::close(ep->fd_);
     ep->fd_ = -1;
   }
+  ep->shm_active_ = false;
+  ep->shm_.reset();
   // every operation in flight ends with the endpoint's status
   std::vector<Completion> cbs;
   for (auto& it : ep->sendq_)
@@ -425,7 +513,8 @@ void Worker::close(Endpoint* ep, bool notify_peer) {
     FrameHeader fh;
     fh.type = kClose;
     // best effort, blocking for at most the socket buffer: the frame is 40 bytes
-    (void)!::write(ep->fd_, &fh, sizeof(fh));
+    if (ep->shm_active_) (void)ep->shm_->write(&fh, sizeof(fh));
+    else (void)!::write(ep->fd_, &fh, sizeof(fh));
   }
   if (ep->fd_ >= 0) {
     epoll_ctl(epfd_, EPOLL_CTL_DEL, ep->fd_, nullptr);
@@ -433,6 +522,8 @@ void Worker::close(Endpoint* ep, bool notify_peer) {
     ::close(ep->fd_);
     ep->fd_ = -1;
   }
+  ep->shm_active_ = false;
+  ep->shm_.reset();
   if (ep->state_ != Endpoint::State::kFailed) {
     ep->state_ = Endpoint::State::kClosed;
     std::vector<Completion> cbs;
@@ -525,9 +616,9 @@ void Worker::flush(Endpoint* ep) {
       if (done) done(UCS_OK);
       continue;
     }
-    ssize_t n = ::writev(ep->fd_, iov, cnt);
+    ssize_t n = io_writev(ep, iov, cnt);
     if (n < 0) {
-      if (errno == EAGAIN || errno == EWOULDBLOCK) return;  // EPOLLOUT (edge) will call us again
+      if (errno == EAGAIN || errno == EWOULDBLOCK) return;  // EPOLLOUT (edge) or the ring poll will call us again
       if (errno == EINTR) continue;
       fail(ep, UCS_ERR_CONNECTION_RESET);
       return;
@@ -549,7 +640,9 @@ void Worker::flush(Endpoint* ep) {
     while (it.seg_idx < it.segs.size() && it.segs[it.seg_idx].size == 0) ++it.seg_idx;
     if (it.owned_off == it.owned.size() && it.seg_idx >= it.segs.size()) {
       Completion done = std::move(it.done);
+      const bool to_shm = it.switch_to_shm;
       ep->sendq_.pop_front();
+      if (to_shm) activate_shm(ep);  // the accepting reply is on the wire: everything after it uses the rings
       if (done) done(UCS_OK);
     }
   }
@@ -565,7 +658,15 @@ void Worker::handle_writable(Endpoint* ep) {
       return;
     }
     ep->state_ = Endpoint::State::kHelloSent;
-    send_hello(ep, kHello);
+    if (opt_.use_shm) {
+      static std::atomic<uint64_t> counter{0};
+      std::random_device rd;
+      char name[kShmNameWire];
+      std::snprintf(name, sizeof(name), "/eux-%d-%llx-%08x", (int)getpid(),
+                    (unsigned long long)counter.fetch_add(1), (unsigned)rd());
+      ep->shm_ = ShmChannel::create(name);
+    }
+    send_hello(ep, kHello, ep->shm_ ? kFlagShmOffer : 0, ep->shm_ ? ep->shm_->name() : std::string());
     return;
   }
   flush(ep);
@@ -579,7 +680,7 @@ void Worker::handle_readable(Endpoint* ep) {
       auto pit = ep->pending_recvs_.find(ep->direct_msg_);
       if (pit == ep->pending_recvs_.end()) {  // cancelled meanwhile: drain into a scratch buffer
         char sink[65536];
-        ssize_t n = ::read(ep->fd_, sink, std::min(sizeof(sink), ep->direct_left_));
+        ssize_t n = io_read(ep, sink, std::min(sizeof(sink), ep->direct_left_));
         if (n > 0) {
           ep->direct_left_ -= static_cast<size_t>(n);
           if (ep->direct_left_ == 0) ep->direct_active_ = false;
@@ -613,7 +714,7 @@ void Worker::handle_readable(Endpoint* ep) {
         if (done) done(UCS_ERR_MESSAGE_TRUNCATED);
         continue;
       }
-      ssize_t n = ::readv(ep->fd_, iov, cnt);
+      ssize_t n = io_readv(ep, iov, cnt);
       if (n <= 0) {
         if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) return;
         if (n < 0 && errno == EINTR) continue;
@@ -658,7 +759,7 @@ void Worker::handle_readable(Endpoint* ep) {
       ep->rpos_ = 0;
     }
     char tmp[65536];
-    ssize_t n = ::read(ep->fd_, tmp, sizeof(tmp));
+    ssize_t n = io_read(ep, tmp, sizeof(tmp));
     if (n > 0) {
       ep->rbuf_.insert(ep->rbuf_.end(), tmp, tmp + n);
       if (!parse_frames(ep)) return;
@@ -709,6 +810,10 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
         std::memcpy(&ep->remote_client_id_, body, 8);
         get_addr(body + 8, fh.header_len - 8, &ep->remote_.addr);
         ep->remote_.name_str = ep->remote_.addr.name;
+      }
+      if (ep->shm_) {
+        if (fh.flags & kFlagShmAccept) activate_shm(ep);  // the peer mapped it: both directions switch here
+        else ep->shm_.reset();                            // another host, or the peer does not want it
       }
       if (ep->state_ == Endpoint::State::kHelloSent) {
         ep->state_ = Endpoint::State::kConnected;

@@ -30,6 +30,8 @@
 #include <deque>
 #include <functional>
 #include <list>
+#include <sys/uio.h>
+
 #include <atomic>
 #include <memory>
 #include <mutex>
@@ -39,6 +41,7 @@
 
 #include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
 #include "eux/ucxx/ucx_context_def.h"
+#include "eux/ucxx/shm_channel.hpp"
 #include "eux/ucxx/ucx_memory_resource.hpp"
 #include "eux/ucxx/ucx_status.hpp"
 
@@ -70,6 +73,8 @@ enum FrameType : uint8_t {
 enum FrameFlags : uint8_t {
   kFlagDeviceRegions = 1,  // RTS carries PeerRegionDesc per segment
   kFlagStage = 2,          // CTS: send the payload through host memory
+  kFlagShmOffer = 4,       // HELLO: the name of a shared-memory channel follows the address
+  kFlagShmAccept = 8,      // HELLO_ACK: the channel is mapped; frames travel through it from now on
 };
 
 #pragma pack(push, 1)
@@ -123,6 +128,7 @@ struct ConnRequest {
   WorkerAddress remote{};
   std::chrono::steady_clock::time_point arrival;
   std::vector<char> pending;  // bytes already read past the HELLO frame
+  std::string shm_name;       // shared-memory channel offered by the peer, if any
 };
 
 struct WorkerOptions {
@@ -131,6 +137,7 @@ struct WorkerOptions {
   int device = -1;               // CUDA device of this worker, -1 = none
   size_t eager_limit = 8192;     // payloads below this travel inline (host memory)
   size_t send_copy_limit = 8192; // inline payloads up to this size are copied, so the send completes at once
+  bool use_shm = true;           // peers on this host talk through shared-memory rings (EUX_SHM=0 turns it off)
 };
 
 class Endpoint {
@@ -153,6 +160,7 @@ class Endpoint {
     size_t seg_idx = 0, seg_off = 0, owned_off = 0;
     Completion done;              // fired when the last byte is written (may be empty)
     std::shared_ptr<void> keep;   // staging buffer kept alive until written
+    bool switch_to_shm = false;   // the HELLO_ACK that accepts a channel: what follows it goes through the rings
   };
   struct PendingSend {             // rendezvous send waiting for CTS / FIN
     std::vector<ucx_buffer_t> segs;
@@ -198,6 +206,8 @@ class Endpoint {
   std::unordered_map<uint64_t, RtsInfo> rts_;
   Completion on_connected_;
   bool auto_accepted_ = false;
+  std::unique_ptr<ShmChannel> shm_;  // offered or mapped channel
+  bool shm_active_ = false;          // frames go through shm_ instead of the socket
 };
 
 class Worker {
@@ -283,7 +293,7 @@ class Worker {
   void enqueue(Endpoint* ep, Endpoint::SendItem&& item);
   void flush(Endpoint* ep);
   void send_control(Endpoint* ep, uint8_t type, uint8_t flags, uint64_t msg_id, int32_t status = 0);
-  void send_hello(Endpoint* ep, uint8_t type);
+  void send_hello(Endpoint* ep, uint8_t type, uint8_t flags = 0, const std::string& shm_name = {});
   void accept_pending(Listener& l);
   void poll_hellos();
   void start_data_send(Endpoint* ep, uint64_t msg_id, bool staged);
@@ -296,6 +306,11 @@ class Worker {
   UcxMemoryResourceManager& mr_;
   UcxCudaMemoryResourceManager* cuda_mr_ = nullptr;  // non-null when the manager can export/import
   WorkerOptions opt_;
+  std::vector<Endpoint*> shm_eps_;  // endpoints whose rings are polled by progress()
+  void activate_shm(Endpoint* ep);
+  ssize_t io_read(Endpoint* ep, void* buf, size_t n);
+  ssize_t io_readv(Endpoint* ep, const struct iovec* iov, int cnt);
+  ssize_t io_writev(Endpoint* ep, const struct iovec* iov, int cnt);
   WorkerAddress addr_{};
   int epfd_ = -1;
   std::vector<Listener> listeners_;

@@ -262,6 +262,24 @@ std::optional<UcxAmDesc> ucx_am_context::pop_pending_am_desc(size_t key) {
 }
 
 void ucx_am_context::release_rndv_am_desc(size_t key) {
+  // The descriptor map and the transport belong to the loop's thread. A caller on another
+  // thread (an error path of a worker-pool continuation, say) hands the release over to it.
+  if (running_ && std::this_thread::get_id() != io_thread_.load(std::memory_order_relaxed)) {
+    struct release_op : operation_base {
+      ucx_am_context* ctx;
+      size_t key;
+    };
+    auto* op = new release_op();
+    op->ctx = this;
+    op->key = key;
+    op->execute = [](operation_base* b) noexcept {
+      auto* self = static_cast<release_op*>(b);
+      self->ctx->release_rndv_am_desc(self->key);
+      delete self;
+    };
+    schedule_remote(op);
+    return;
+  }
   auto d = pop_pending_am_desc(key);
   if (!d) return;
   if (auto* c = conn_mgr_.get_connection(d->conn_id)) c->release_rndv(*d);
