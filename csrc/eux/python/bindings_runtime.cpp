@@ -284,16 +284,20 @@ class PyAxonRuntime {
   }
 
   // ---- invoke ----
+  // `transform(response_header, payload)`, when given, runs on the loop thread and its result (or
+  // the exception it raises) settles the future: one loop iteration instead of a chained future.
   py::object invoke_raw(const std::string& worker_name, rpc::RpcRequestHeader header, py::object payload, py::object memory_policy,
-                        bool response_as_list) {
+                        bool response_as_list, py::object transform) {
     PayloadVariant p = payload_from_python(*mr_, payload);
     ClientMemoryPolicy pol = client_policy(memory_policy, response_as_list);
     if (response_as_list && !memory_policy.is_none()) pol.buffer_provider = nullptr;
     const int dev = device_id_;
     auto mr = mr_;
+    std::shared_ptr<py::object> tf = transform.is_none() ? nullptr : gil_shared(transform);
     return future_from(rt_->InvokeRpc(std::string_view(worker_name), std::move(header), std::move(p), std::move(pol)),
-                       [dev, mr](InvokeResult r) -> py::object {
+                       [dev, mr, tf](InvokeResult r) -> py::object {
                          py::object payload_obj = payload_to_python(std::move(r.payload), dev, mr);
+                         if (tf) return (*tf)(py::cast(std::move(r.header)), payload_obj);
                          return py::make_tuple(py::cast(std::move(r.header)), payload_obj);
                        });
   }
@@ -325,8 +329,18 @@ class PyAxonRuntime {
           try {
             py::object payload_obj = payload_to_python(std::move(st->payload), self->device_id_, self->mr_);
             py::object coro = (*fn)(py::cast(st->req), payload_obj);
-            py::object task = py::module_::import("asyncio").attr("ensure_future")(coro, py::arg("loop") = self->wake_.loop());
-            task.attr("add_done_callback")(py::cpp_function([self, st, handle, fail](py::object t) mutable {
+            // The first step of the coroutine runs right here (eager start): a handler that awaits
+            // nothing is finished when the constructor returns, and its reply leaves in this loop
+            // iteration instead of two iterations later.
+            py::object asyncio = py::module_::import("asyncio");
+            py::object task;
+            try {
+              task = asyncio.attr("Task")(coro, py::arg("loop") = self->wake_.loop(), py::arg("eager_start") = true);
+            } catch (py::error_already_set& e) {
+              if (!e.matches(PyExc_TypeError)) throw;
+              task = asyncio.attr("ensure_future")(coro, py::arg("loop") = self->wake_.loop());  // interpreters before 3.12
+            }
+            auto finish = py::cpp_function([self, st, handle, fail](py::object t) mutable {
               try {
                 if (t.attr("cancelled")().cast<bool>()) {
                   fail(rpc::make_error_code(rpc::RpcErrc::CANCELLED), "the handler task was cancelled");
@@ -361,7 +375,9 @@ class PyAxonRuntime {
               } catch (const std::exception& e) {
                 fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
               }
-            }));
+            });
+            if (task.attr("done")().cast<bool>()) finish(task);
+            else task.attr("add_done_callback")(finish);
           } catch (py::error_already_set& e) {
             fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
           } catch (const std::exception& e) {
@@ -444,7 +460,7 @@ void bind_runtime(py::module_& m) {
            py::arg("return_types"), py::arg("input_payload_type"), py::arg("return_payload_type"), py::arg("callable"),
            py::arg("memory_policy") = py::none(), py::arg("lifecycle_policy") = py::none())
       .def("invoke_raw", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
-           py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false)
+           py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none())
       .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
       .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)
       .def("stored_request_count", &PyAxonRuntime::stored_request_count)

@@ -320,27 +320,9 @@ class AxonRuntime(_axon.AxonRuntime):
                 header.add_param_typed(ParamType.TENSOR_META_VEC, metas, "")
                 payload = tensors
         fn = from_dlpack_fn or (_default_from_dlpack(sample) if sample is not None else None)
-        raw = self.invoke_raw(worker_name, header, payload, memory_policy)
-        loop = raw.get_loop()
-        out = loop.create_future()
-
-        def done(f):
-            if out.done():
-                return
-            if f.cancelled():
-                out.cancel()
-                return
-            exc = f.exception()
-            if exc is not None:
-                out.set_exception(exc)
-                return
-            resp, pay = f.result()
-            try:
-                out.set_result(_unpack_response(resp, pay, fn, fid, session_id))
-            except Exception as e:  # noqa: BLE001
-                out.set_exception(e)
-        raw.add_done_callback(done)
-        return out
+        # the response is unpacked on the loop thread by the binding itself and settles the future
+        return self.invoke_raw(worker_name, header, payload, memory_policy, False,
+                               lambda resp, pay: _unpack_response(resp, pay, fn, fid, session_id))
 
 
 def _unpack_response(resp, payload, from_dlpack_fn, fid, session_id):
