@@ -28,7 +28,10 @@ constexpr int kMoeThreads = 512;
 constexpr int kMaxWorld = 16;
 
 __host__ __device__ __forceinline__ size_t moe_row_bytes(int hidden, int fp8) {
-  return fp8 ? (size_t)hidden + (size_t)(hidden / 128) * 4 : (size_t)hidden * 2;
+  // fp8 rows: values, then one fp32 scale per 128 values, padded to whole 128-byte lines so that
+  // a warp's 512-byte stores into a row never straddle a line (a straddling store costs an extra
+  // NVLink packet)
+  return fp8 ? (((size_t)hidden + (size_t)(hidden / 128) * 4 + 127) / 128) * 128 : (size_t)hidden * 2;
 }
 
 // ---- routing: slot assignment, grouped by expert (single CTA) --------------
@@ -41,10 +44,29 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(eux_moe_desc d) {
   const int E = d.n_experts, W = d.world, EPR = E / W;
   const int n = d.n_tokens * d.topk;
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0, cur[e] = 0;
+  // Up to 32 routing entries per thread are fetched once, all loads in flight together, and
+  // serve both passes from registers (a single CTA is latency bound: 64 dependent global loads
+  // per thread otherwise). Larger batches fall back to re-reading.
+  constexpr int kCache = 32;
+  const bool cached = n <= kCache * (int)blockDim.x;
+  int ev[kCache];
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < kCache; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      ev[j] = i < n ? __ldg(d.topk_idx + i) : -1;
+    }
+  }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    int e = d.topk_idx[i];
-    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < kCache; ++j)
+      if (ev[j] >= 0 && ev[j] < E) atomicAdd(&cnt[ev[j]], 1);
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      int e = d.topk_idx[i];
+      if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -60,14 +82,29 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(eux_moe_desc d) {
     d.counters[r] = s < d.capacity ? s : d.capacity;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    int e = d.topk_idx[i];
-    int slot = -1;
-    if (e >= 0 && e < E) {
-      slot = off[e] + atomicAdd(&cur[e], 1);
-      if (slot >= d.capacity) slot = -1;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < kCache; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i >= n) continue;
+      const int e = ev[j];
+      int slot = -1;
+      if (e >= 0 && e < E) {
+        slot = off[e] + atomicAdd(&cur[e], 1);
+        if (slot >= d.capacity) slot = -1;
+      }
+      d.slot_of[i] = slot;
     }
-    d.slot_of[i] = slot;
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      int e = d.topk_idx[i];
+      int slot = -1;
+      if (e >= 0 && e < E) {
+        slot = off[e] + atomicAdd(&cur[e], 1);
+        if (slot >= d.capacity) slot = -1;
+      }
+      d.slot_of[i] = slot;
+    }
   }
 }
 
@@ -224,6 +261,113 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_fp8_kernel(eux_moe_d
         h.w = (uint32_t)d.rank;
         st_u4(reinterpret_cast<uint4*>(d.meta_peer[dst]) + row, h);
       }
+    }
+  }
+  moe_publish(d);
+}
+
+// ---- dispatch, e4m3 rows, one warp per token row -------------------------------
+// Same bytes as moe_dispatch_fp8_kernel, but the 4-byte scales of a row are collected in
+// registers (lane L keeps groups L, 32+L, ...) and leave as one coalesced store per destination
+// at the end of the row: across NVLink a 4-byte store costs a packet of its own, and the
+// per-group stores of the kernel above made a fifth of all packets.
+__device__ __forceinline__ float pick4(const float (&r)[4], int i) {
+  return i == 0 ? r[0] : (i == 1 ? r[1] : (i == 2 ? r[2] : r[3]));
+}
+__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_fp8_rows_kernel(eux_moe_desc d) {
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int upr = (d.hidden + 511) / 512;
+  const int ngroups = d.hidden / 128;
+  const size_t row_bytes = moe_row_bytes(d.hidden, 1);
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = warp; t < d.n_tokens; t += nwarps) {
+    int my_e = -1, my_slot = -1;
+    float my_w = 0.f;
+    if (lane < K) {
+      my_e = d.topk_idx[t * K + lane];
+      my_slot = d.slot_of[t * K + lane];
+      my_w = d.topk_w[t * K + lane];
+    }
+    // this lane's destination row, for k = lane
+    unsigned char* my_out = nullptr;
+    if (my_slot >= 0) {
+      const int dst = my_e / EPR;
+      my_out = reinterpret_cast<unsigned char*>(d.arena_peer[dst]) + ((size_t)d.rank * d.capacity + my_slot) * row_bytes;
+    }
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* xrow = reinterpret_cast<const __nv_bfloat16*>(d.x) + (size_t)t * d.hidden;
+    for (int part = 0; part < upr; ++part) {
+      const int e0 = part * 512 + lane * 16;
+      const bool in = e0 < d.hidden;
+      float f[16];
+      if (in) {
+        const uint4* src = reinterpret_cast<const uint4*>(xrow + e0);
+        uint4 a = ld_stream_u4(src), b = ld_stream_u4(src + 1);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 x = __bfloat1622float2(pa[j]), y = __bfloat1622float2(pb[j]);
+          f[2 * j] = x.x, f[2 * j + 1] = x.y, f[8 + 2 * j] = y.x, f[8 + 2 * j + 1] = y.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) f[j] = 0.f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+      const float inv = 1.0f / scale;
+      uint32_t w4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j] * inv, f[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j + 2] * inv, f[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        w4[j] = lo | (hi << 16);
+      }
+      const uint4 q = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      // the four scales of this part go to the lanes that keep them
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float sj = __shfl_sync(0xffffffffu, scale, 8 * j);
+        const int gi = part * 4 + j;
+        if (lane == (gi & 31)) {
+          const int r = gi >> 5;
+          if (r == 0) sc[0] = sj;
+          else if (r == 1) sc[1] = sj;
+          else if (r == 2) sc[2] = sj;
+          else sc[3] = sj;
+        }
+      }
+      for (int k = 0; k < K; ++k) {
+        unsigned char* out = (unsigned char*)__shfl_sync(0xffffffffu, (unsigned long long)my_out, k);
+        if (out && in) st_u4(out + e0, q);
+      }
+    }
+    for (int k = 0; k < K; ++k) {
+      unsigned char* out = (unsigned char*)__shfl_sync(0xffffffffu, (unsigned long long)my_out, k);
+      if (!out) continue;
+      float* so = reinterpret_cast<float*>(out + d.hidden);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int g = r * 32 + lane;
+        if (g < ngroups) so[g] = sc[r];
+      }
+    }
+    if (my_out) {  // lane k writes the header of the k-th destination row
+      const int dst = my_e / EPR;
+      uint4 h;
+      h.x = (uint32_t)t;
+      h.y = (uint32_t)lane | ((uint32_t)(my_e - dst * EPR) << 16);
+      h.z = __float_as_uint(my_w);
+      h.w = (uint32_t)d.rank;
+      st_u4(reinterpret_cast<uint4*>(d.meta_peer[dst]) + ((size_t)d.rank * d.capacity + my_slot), h);
     }
   }
   moe_publish(d);
@@ -411,6 +555,90 @@ __global__ void __launch_bounds__(kMoeThreads) moe_combine_fp8_kernel(eux_moe_de
   }
 }
 
+// ---- combine, fp8 rows, one warp per token (top-k <= 8, hidden <= 16384) -----------------
+// The scales of the k rows are fetched once per row (two coalesced loads per row instead of one
+// small load per 512 elements), already multiplied by the gate weight.
+__global__ void __launch_bounds__(kMoeThreads) moe_combine_fp8_rows_kernel(eux_moe_desc d) {
+  if (!moe_wait_experts(d)) return;
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int upr = (d.hidden + 511) / 512;
+  const int ngroups = d.hidden / 128;
+  const size_t row_bytes = moe_row_bytes(d.hidden, 1);
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = warp; t < d.n_tokens; t += nwarps) {
+    const unsigned char* my_row = nullptr;
+    float my_w = 0.f;
+    if (lane < K) {
+      int e = d.topk_idx[t * K + lane];
+      int slot = d.slot_of[t * K + lane];
+      if (slot >= 0) {
+        int dst = e / EPR;
+        my_row = reinterpret_cast<const unsigned char*>(d.arena_peer[dst]) + ((size_t)d.rank * d.capacity + slot) * row_bytes;
+        my_w = d.topk_w[t * K + lane];
+      }
+    }
+    const unsigned char* rows[8];
+    float scw[8][4];  // gate weight x scale, lane L keeps groups L, 32+L, 64+L, 96+L of row k
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      rows[k] = (const unsigned char*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, k);
+      const float wk = __shfl_sync(0xffffffffu, my_w, k);
+      if (k >= K) rows[k] = nullptr;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int g = r * 32 + lane;
+        scw[k][r] = (rows[k] && g < ngroups) ? wk * __ldcg(reinterpret_cast<const float*>(rows[k] + d.hidden) + g) : 0.f;
+      }
+    }
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(d.out) + (size_t)t * d.hidden;
+    for (int part = 0; part < upr; ++part) {
+      const int e0 = part * 512 + lane * 16;
+      const bool in = e0 < d.hidden;
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[k] = make_uint4(0, 0, 0, 0);
+        if (rows[k] && in) v[k] = ld_cg_u4(rows[k] + e0);
+      }
+      float acc[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+      const int gi = part * 4 + (lane >> 3);  // scale group of this lane's 16 elements
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float wk = __shfl_sync(0xffffffffu, pick4(scw[k], gi >> 5), gi & 31);
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(&v[k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(p[j] & 0xffffu), __NV_E4M3);
+          __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(p[j] >> 16), __NV_E4M3);
+          float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+          float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+          acc[4 * j] = fmaf(wk, a.x, acc[4 * j]);
+          acc[4 * j + 1] = fmaf(wk, a.y, acc[4 * j + 1]);
+          acc[4 * j + 2] = fmaf(wk, b.x, acc[4 * j + 2]);
+          acc[4 * j + 3] = fmaf(wk, b.y, acc[4 * j + 3]);
+        }
+      }
+      if (in) {
+        uint4 o0, o1;
+        __nv_bfloat162* q0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+        __nv_bfloat162* q1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          q0[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          q1[j] = __floats2bfloat162_rn(acc[8 + 2 * j], acc[8 + 2 * j + 1]);
+        }
+        uint4* out = reinterpret_cast<uint4*>(orow + e0);
+        st_stream_u4(out, o0);
+        st_stream_u4(out + 1, o1);
+      }
+    }
+  }
+}
+
 static int moe_check(const eux_moe_desc* d) {
   if (!d || d->world < 1 || d->world > kMaxWorld || d->rank < 0 || d->rank >= d->world) return EUX_ERR_BAD_ARG;
   if (d->n_experts % d->world || d->hidden % 128 || d->hidden <= 0 || d->topk < 1 || d->topk > 32) return EUX_ERR_BAD_ARG;
@@ -429,7 +657,8 @@ extern "C" int eux_moe_dispatch_launch(const eux_moe_desc* d, int ctas, void* st
   cudaStream_t st = (cudaStream_t)stream;
   if (ctas <= 0) ctas = 296;
   moe_route_kernel<<<1, 1024, 3 * d->n_experts * sizeof(int), st>>>(*d);
-  if (d->fp8) moe_dispatch_fp8_kernel<<<ctas, kMoeThreads, 0, st>>>(*d);
+  if (d->fp8 && d->hidden <= 16384) moe_dispatch_fp8_rows_kernel<<<ctas, kMoeThreads, 0, st>>>(*d);
+  else if (d->fp8) moe_dispatch_fp8_kernel<<<ctas, kMoeThreads, 0, st>>>(*d);
   else moe_dispatch_bf16_kernel<<<ctas, kMoeThreads, 0, st>>>(*d);
   return (int)cudaGetLastError();
 }
@@ -443,7 +672,8 @@ extern "C" int eux_moe_expert_ready_launch(const eux_moe_desc* d, void* stream) 
 extern "C" int eux_moe_combine_launch(const eux_moe_desc* d, int ctas, void* stream) {
   if (int rc = moe_check(d)) return rc;
   if (ctas <= 0) ctas = 296;
-  if (d->fp8) moe_combine_fp8_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
+  if (d->fp8 && d->topk <= 8 && d->hidden <= 16384) moe_combine_fp8_rows_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
+  else if (d->fp8) moe_combine_fp8_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
   else moe_combine_bf16_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
   return (int)cudaGetLastError();
 }

@@ -36,3 +36,32 @@ def run(device: torch.device) -> None:
         remote_gemm = None
     if remote_gemm is not None:
         remote_gemm.smoke(device)
+    _axon_round_trip(device)
+
+
+def _axon_round_trip(device: torch.device) -> None:
+    """One RPC with a device tensor through the runtime and its Python binding."""
+    import asyncio
+
+    from .. import axon
+
+    async def main():
+        index = device.index or 0
+        server = axon.AxonRuntime("smoke_server", timeout=10000, device=axon.cuda(index))
+        client = axon.AxonRuntime("smoke_client", timeout=10000, device=axon.cuda(index))
+
+        async def add_one(x: torch.Tensor) -> torch.Tensor:
+            return x + 1.0
+
+        policy = lambda metas: torch.empty(metas[0].shape, dtype=torch.float32, device=device)  # noqa: E731
+        server.register_function(add_one, memory_policy=policy)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "smoke_server")
+        x = torch.rand(1 << 16, device=device)
+        y = await client.invoke(x, worker_name="smoke_server", session_id=1, function="add_one", memory_policy=policy)
+        assert y.is_cuda and torch.equal(y, x + 1.0)
+        client.stop()
+        server.stop()
+
+    asyncio.run(main())

@@ -24,7 +24,8 @@ def launch_count() -> int:
 
 
 def row_bytes(hidden: int, fp8: bool) -> int:
-    return hidden + hidden // 128 * 4 if fp8 else hidden * 2
+    """Bytes of one row in a receive arena (the kernels' layout: ``eux_moe_row_bytes``)."""
+    return int(_native.load().eux_moe_row_bytes(hidden, 1 if fp8 else 0))
 
 
 class MoeAllToAll:
