@@ -128,7 +128,7 @@ class RemoteGemmRpc:
     and the resident weight is e4m3 with 128x128 block scales. A single rank
     has nothing to pull: its kernel reads X in place."""
 
-    def __init__(self, group: PeerGroup, m: int, n: int, k: int, copy_ctas: int = 12, fp8: bool = False):
+    def __init__(self, group: PeerGroup, m: int, n: int, k: int, copy_ctas: int = 0, fp8: bool = False):
         self.g, self.m, self.n, self.k, self.copy_ctas, self.fp8 = group, m, n, k, copy_ctas, fp8
         self.peer = _partner(group.rank, group.world)
         dev = group.device
