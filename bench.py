@@ -323,6 +323,35 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
         w.a2a.close()
         return out
 
+    def rpc_storm():
+        """All-to-all small-message RPC storm through the C++ runtime: every rank serves `+1.0` on an fp32
+        device tensor and keeps 64 calls in flight to every other rank (sizes log-uniform 256 B - 64 KiB)."""
+        import re
+        import shutil
+        import subprocess
+        import tempfile
+        import torch.distributed as dist
+        if world < 2:
+            return {"skipped": "needs at least two ranks"}
+        binary = ROOT / "execution_ucx_b200" / "_lib" / "eux_axon_rpc_perf"
+        box = [tempfile.mkdtemp(prefix="eux_mesh_") if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        out = subprocess.run([str(binary), "--mesh", "--rank", str(rank), "--world", str(world), "--dir", box[0], "-m", "cuda",
+                              "-d", str(dev.index), "-n", "4000", "-o", "64"], capture_output=True, text=True, timeout=300)
+        group.barrier()
+        if rank == 0:
+            shutil.rmtree(box[0], ignore_errors=True)
+        m = re.search(r"calls=(\d+) failed=(\d+) seconds=([\d.]+) calls_per_s=([\d.]+) payload_GBps=([\d.]+) p50_us=([\d.]+) p99_us=([\d.]+)", out.stdout)
+        if not m:
+            raise RuntimeError("storm failed: " + (out.stderr or out.stdout)[-500:])
+        calls, failed, secs, cps, gbps, p50, p99 = (float(x) for x in m.groups())
+        t = torch.tensor([cps, gbps, failed], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        return {"calls_per_s_all_ranks": round(float(t[0])), "payload_GBps_all_ranks": round(float(t[1]), 2),
+                "failed": int(t[2]), "p50_us_max_over_ranks": round(group.max_over_ranks(p50), 1),
+                "p99_us_max_over_ranks": round(group.max_over_ranks(p99), 1), "outstanding_per_ordered_pair": 64,
+                "calls_per_rank_per_peer": 4000, "timing": "host clock inside eux_axon_rpc_perf --mesh (one process per GPU)"}
+
     guarded("latency_sweep_device", sweep)
     guarded("tensor_rpc_sweep", rpc_sweep)
     guarded("remote_gemm_rpc_bf16", gemm(False))
@@ -330,6 +359,7 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
     guarded("moe_bf16", moe(False))
     guarded("moe_fp8", moe(True))
     guarded("library_baselines", baselines)
+    guarded("small_rpc_storm_all_to_all", rpc_storm)
     return extra
 
 

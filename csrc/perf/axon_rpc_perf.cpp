@@ -4,6 +4,12 @@
 //
 //   eux_axon_rpc_perf [-m host|cuda] [-d device] [-s bytes[,bytes...]] [-n requests] [-o outstanding]
 //                     [-w warmup] [--server | --client <address-hex>]
+//   eux_axon_rpc_perf --mesh --rank R --world N --dir DIR [-m host|cuda] [-d device] [-n requests-per-peer]
+//                     [-o outstanding-per-peer]
+//
+// --mesh is the all-to-all storm: N processes (one per GPU), each serving `plus_one` and calling it on
+// every other rank with `outstanding` requests in flight per peer; tensor sizes are log-uniform in
+// 256 B - 64 KiB. The ranks find each other through files in DIR (address, ready and done markers).
 //
 // Without --server/--client both runtimes live in this process. For every size it prints the
 // round-trip latency with one request in flight (p50 / p99) and the request rate and payload
@@ -12,6 +18,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <iostream>
@@ -40,6 +47,9 @@ struct Options {
   int requests = 2000, outstanding = 64, warmup = 50;
   bool server = false;
   std::string client_addr;
+  bool mesh = false;
+  int rank = 0, world = 1;
+  std::string dir;
 };
 
 static TensorMeta f32_meta(size_t bytes) {
@@ -55,6 +65,7 @@ static std::shared_ptr<eux::ucxx::UcxMemoryResourceManager> make_mr(const Option
   if (!o.cuda) return std::make_shared<eux::ucxx::DefaultUcxMemoryResourceManager>();
   eux::ucxx::UcxCudaMemoryResourceManager::Options mo;
   mo.device = o.device;
+  if (o.mesh) mo.arena_bytes = size_t(256) << 20;  // hundreds of 64 KiB tensors in flight
   return std::make_shared<eux::ucxx::UcxCudaMemoryResourceManager>(mo);
 }
 
@@ -213,6 +224,124 @@ static std::string to_hex(const std::vector<std::byte>& b) {
   return s;
 }
 
+// ---- all-to-all storm -------------------------------------------------------------------------
+#include <fstream>
+#include <random>
+#include <sys/stat.h>
+
+static bool file_exists(const std::string& p) {
+  struct stat st{};
+  return ::stat(p.c_str(), &st) == 0;
+}
+static void write_file(const std::string& p, const std::string& text) {
+  const std::string tmp = p + ".tmp";
+  {
+    std::ofstream f(tmp);
+    f << text;
+  }
+  ::rename(tmp.c_str(), p.c_str());
+}
+static bool wait_for_all(const std::string& dir, const std::string& stem, int world, int seconds) {
+  const auto limit = clk::now() + std::chrono::seconds(seconds);
+  for (;;) {
+    int have = 0;
+    for (int r = 0; r < world; ++r) have += file_exists(dir + "/" + stem + "." + std::to_string(r));
+    if (have == world) return true;
+    if (clk::now() > limit) return false;
+    std::this_thread::sleep_for(std::chrono::milliseconds(2));
+  }
+}
+
+static int run_mesh(const Options& o) {
+  using namespace std::chrono_literals;
+  const std::string me = "mesh" + std::to_string(o.rank);
+  AxonRuntime rt(me, 8, 30000ms, make_dev(o), make_mr(o));
+  register_plus_one(rt, o);
+  if (auto ec = rt.Start()) throw std::runtime_error(ec.message());
+  write_file(o.dir + "/addr." + std::to_string(o.rank), to_hex(rt.GetLocalAddress()));
+  if (!wait_for_all(o.dir, "addr", o.world, 120)) throw std::runtime_error("not every rank published its address");
+  std::vector<std::string> peers;
+  for (int r = 0; r < o.world; ++r) {
+    if (r == o.rank) continue;
+    std::ifstream f(o.dir + "/addr." + std::to_string(r));
+    std::string hex;
+    f >> hex;
+    const std::string name = "mesh" + std::to_string(r);
+    rt.ConnectEndpoint(from_hex(hex), name);
+    peers.push_back(name);
+  }
+  write_file(o.dir + "/ready." + std::to_string(o.rank), "1");
+  if (!wait_for_all(o.dir, "ready", o.world, 120)) throw std::runtime_error("not every rank got ready");
+
+  auto mr = rt.memory_resource();
+  const auto type = o.cuda ? ucx_memory_type::CUDA : ucx_memory_type::HOST;
+  const size_t max_bytes = 65536;
+  UcxBuffer resident(*mr, type, max_bytes);
+  {
+    std::vector<float> host(max_bytes / 4);
+    std::mt19937 rng(1234 + o.rank);
+    std::uniform_real_distribution<float> u(-1.f, 1.f);
+    for (auto& v : host) v = u(rng);
+    mr->memcpy(type, resident.data(), ucx_memory_type::HOST, host.data(), max_bytes);
+  }
+  std::mt19937_64 rng(99 + o.rank);
+  std::uniform_real_distribution<double> logu(std::log(256.0), std::log(65536.0));
+  const int P = static_cast<int>(peers.size());
+  std::vector<std::atomic<int>> inflight(P);
+  for (auto& a : inflight) a.store(0);
+  std::atomic<int> failed{0};
+  std::mutex lat_mu;
+  std::vector<double> lat_us;
+  lat_us.reserve(size_t(P) * o.requests);
+  uint64_t bytes_total = 0;
+  ex::async_scope scope;
+  std::vector<int> issued(P, 0);
+  int remaining = P * o.requests;
+  const auto t0 = clk::now();
+  while (remaining > 0) {
+    bool any = false;
+    for (int p = 0; p < P; ++p) {
+      if (issued[p] >= o.requests || inflight[p].load(std::memory_order_acquire) >= o.outstanding) continue;
+      const size_t bytes = std::min<size_t>(max_bytes, (static_cast<size_t>(std::exp(logu(rng))) + 3) / 4 * 4);
+      bytes_total += 2 * bytes;
+      ++issued[p];
+      --remaining;
+      any = true;
+      inflight[p].fetch_add(1);
+      const auto start = clk::now();
+      auto fin = [&, p, start](bool ok) {
+        const double us = std::chrono::duration<double, std::micro>(clk::now() - start).count();
+        {
+          std::lock_guard lk(lat_mu);
+          lat_us.push_back(us);
+        }
+        if (!ok) failed.fetch_add(1);
+        inflight[p].fetch_sub(1, std::memory_order_release);
+      };
+      scope.spawn_detached(ex::upon_error(
+          ex::then(rt.InvokeRpc(peers[p], session_id_t{1}, function_id_t{1}, workflow_id_t{}, client_policy(rt, o), f32_meta(bytes),
+                                UcxBuffer(*mr, type, resident.data(), bytes, nullptr, false)),
+                   [fin](InvokeResult r) mutable { fin(r.header.status.ok()); }),
+          [fin](std::exception_ptr) mutable { fin(false); }));
+    }
+    if (!any) std::this_thread::yield();
+  }
+  ex::sync_wait(scope.join());
+  const double secs = std::chrono::duration<double>(clk::now() - t0).count();
+  write_file(o.dir + "/done." + std::to_string(o.rank), "1");
+  // keep serving until every rank has finished its own calls
+  wait_for_all(o.dir, "done", o.world, 120);
+  const size_t calls = lat_us.size();
+  std::printf("mesh rank=%d world=%d memory=%s outstanding_per_peer=%d calls=%zu failed=%d seconds=%.4f calls_per_s=%.0f "
+              "payload_GBps=%.3f p50_us=%.1f p99_us=%.1f\n",
+              o.rank, o.world, o.cuda ? "cuda" : "host", o.outstanding, calls, failed.load(), secs, calls / secs,
+              bytes_total / secs / 1e9, pct(lat_us, 0.5), pct(lat_us, 0.99));
+  std::fflush(stdout);
+  std::this_thread::sleep_for(50ms);
+  rt.Stop();
+  return failed.load() ? 1 : 0;
+}
+
 int main(int argc, char** argv) {
   Options o;
   for (int i = 1; i < argc; ++i) {
@@ -233,7 +362,11 @@ int main(int argc, char** argv) {
         o.sizes.push_back(std::stoul(list.substr(pos, comma - pos)) / 4 * 4);
         pos = comma + 1;
       }
-    } else if (a == "--server") o.server = true;
+    } else if (a == "--mesh") o.mesh = true;
+    else if (a == "--rank") o.rank = std::stoi(next());
+    else if (a == "--world") o.world = std::stoi(next());
+    else if (a == "--dir") o.dir = next();
+    else if (a == "--server") o.server = true;
     else if (a == "--client") o.client_addr = next();
     else {
       std::fprintf(stderr, "usage: %s [-m host|cuda] [-d dev] [-s bytes,...] [-n requests] [-o outstanding] [-w warmup] [--server|--client hex]\n", argv[0]);
@@ -243,6 +376,13 @@ int main(int argc, char** argv) {
   using namespace std::chrono_literals;
   try {
     if (o.cuda) cudaSetDevice(o.device);
+    if (o.mesh) {
+      if (o.dir.empty() || o.world < 2 || o.rank < 0 || o.rank >= o.world) {
+        std::fprintf(stderr, "--mesh needs --rank R --world N (N >= 2) --dir DIR\n");
+        return 2;
+      }
+      return run_mesh(o);
+    }
     if (o.server) {
       AxonRuntime srv("perf_server", 4, 30000ms, make_dev(o), make_mr(o));
       register_plus_one(srv, o);
