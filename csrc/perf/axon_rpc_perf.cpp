@@ -287,6 +287,20 @@ static int run_mesh(const Options& o) {
   std::mt19937_64 rng(99 + o.rank);
   std::uniform_real_distribution<double> logu(std::log(256.0), std::log(65536.0));
   const int P = static_cast<int>(peers.size());
+  // untimed warm-up: the first transfers between two processes map each other's memory and
+  // switch on peer access, which takes a good fraction of a second
+  {
+    ex::async_scope warm;
+    for (int i = 0; i < std::max(1, o.warmup); ++i)
+      for (int p = 0; p < P; ++p)
+        warm.spawn_detached(ex::upon_error(ex::then(rt.InvokeRpc(peers[p], session_id_t{1}, function_id_t{1}, workflow_id_t{}, client_policy(rt, o),
+                                                                 f32_meta(max_bytes), UcxBuffer(*mr, type, resident.data(), max_bytes, nullptr, false)),
+                                                    [](InvokeResult) {}),
+                                           [](std::exception_ptr) {}));
+    ex::sync_wait(warm.join());
+  }
+  write_file(o.dir + "/warm." + std::to_string(o.rank), "1");
+  if (!wait_for_all(o.dir, "warm", o.world, 120)) throw std::runtime_error("not every rank finished its warm-up");
   std::vector<std::atomic<int>> inflight(P);
   for (auto& a : inflight) a.store(0);
   std::atomic<int> failed{0};
