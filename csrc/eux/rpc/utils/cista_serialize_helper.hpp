@@ -54,6 +54,9 @@ class SizeCounter {
   size_t size_ = 0;
 };
 
+// the name the reference uses for the counting sink (rpc_core/utils/cista_serialize_helper.hpp:43-78)
+using CistaSizeCalculator = SizeCounter;
+
 class FixedBufferWriter {
  public:
   FixedBufferWriter(void* buf, size_t capacity) : buf_(static_cast<uint8_t*>(buf)), cap_(capacity) {}

@@ -8,6 +8,7 @@
 
 #include "check.hpp"
 #include "eux/exec/async_scope.hpp"
+#include "eux/exec/stream.hpp"
 #include "eux/exec/contexts.hpp"
 #include "eux/ucxx/ucx_am_context.hpp"
 
@@ -77,6 +78,37 @@ EUX_TEST(accept_cancelled_by_stop_token) {
   auto r = ex::sync_wait(ex::stop_when(acc.next(), ex::schedule_after(timer.get_scheduler(), 30ms)));
   CHECK(!r.has_value());
   ex::sync_wait(acc.cleanup());
+}
+
+// The accept stream with the stream algorithms, as a server loop is usually written:
+// for_each(take_until(accept_endpoint(...), single(stop_on_request(token))), on_batch).
+EUX_TEST(accept_stream_with_for_each_and_take_until) {
+  Runner srv("srv", true), cli("cli", true);
+  const uint16_t port = free_port();
+  ex::inplace_stop_source stop;
+  std::atomic<int> accepted{0};
+  ex::async_scope scope;
+  scope.spawn_detached(ex::upon_error(
+      ex::for_each(ex::take_until(accept_endpoint(srv.ctx.get_scheduler(), port), ex::single(ex::stop_on_request(stop.get_token()))),
+                   [&](std::vector<std::pair<uint64_t, std::error_code>>&& batch) {
+                     for (auto& [id, ec] : batch)
+                       if (id != 0 && !ec) accepted.fetch_add(1);
+                   }),
+      [](std::exception_ptr) {}));
+  int connected = 0;
+  for (int attempt = 0; attempt < 200 && connected < 2; ++attempt) {
+    try {
+      auto c = ex::sync_wait(connect_endpoint(cli.ctx.get_scheduler(), nullptr, loopback(port), sizeof(sockaddr_in)));
+      if (c) ++connected;
+    } catch (...) {
+      std::this_thread::sleep_for(5ms);
+    }
+  }
+  CHECK_EQ(connected, 2);
+  for (int i = 0; i < 400 && accepted.load() < 2; ++i) std::this_thread::sleep_for(5ms);
+  CHECK_EQ(accepted.load(), 2);
+  stop.request_stop();  // ends the pending next(), then the stream is cleaned up
+  ex::sync_wait(scope.join());
 }
 
 struct Pair {

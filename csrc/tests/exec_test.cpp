@@ -7,8 +7,10 @@
 #include "eux/exec/async_scope.hpp"
 #include "eux/exec/contexts.hpp"
 #include "eux/exec/exec.hpp"
+#include "eux/exec/stream.hpp"
 
 using namespace eux::exec;
+namespace ex = eux::exec;
 using namespace std::chrono_literals;
 
 EUX_TEST(just_then_pipe) {
@@ -175,6 +177,74 @@ EUX_TEST(coroutine_task) {
   CHECK_EQ(out, 121);
   auto d = sync_wait(cancelled_inside());
   CHECK(!d.has_value());
+}
+
+// A stream that counts: next() yields 0, 1, 2, ... (after a short timer each when `ctx` is given),
+// ends after `limit` elements when limit >= 0.
+struct return_int {
+  int v;
+  int operator()() const { return v; }
+};
+struct counting_stream {
+  ex::timed_single_thread_context* ctx = nullptr;
+  int limit = -1;
+  int next_value = 0;
+  int* cleanups = nullptr;
+  auto next() {
+    using timed = decltype(ex::then(ex::schedule_after(ctx->get_scheduler(), 1ms), return_int{0}));
+    using out = ex::variant_sender<timed, ex::just_sender<int>, ex::just_done_sender<int>>;
+    if (limit >= 0 && next_value >= limit) return out(ex::just_done<int>());
+    const int v = next_value++;
+    if (ctx) return out(ex::then(ex::schedule_after(ctx->get_scheduler(), 1ms), return_int{v}));
+    return out(ex::just(v));
+  }
+  auto cleanup() {
+    return ex::just_from([c = cleanups] {
+      if (c) ++*c;
+    });
+  }
+};
+
+EUX_TEST(streams_for_each_take_until_single) {
+  // for_each over a finite stream, cleanup exactly once
+  int cleanups = 0, sum = 0;
+  ex::sync_wait(ex::for_each(counting_stream{nullptr, 5, 0, &cleanups}, [&](int v) { sum += v; }));
+  CHECK_EQ(sum, 0 + 1 + 2 + 3 + 4);
+  CHECK_EQ(cleanups, 1);
+  // an endless timed stream, ended from another thread through take_until(single(stop_on_request))
+  ex::timed_single_thread_context ctx;
+  ex::inplace_stop_source stop;
+  std::atomic<int> seen{0};
+  int cleanups2 = 0;
+  std::thread stopper([&] {
+    while (seen.load() < 5) std::this_thread::sleep_for(1ms);
+    stop.request_stop();
+  });
+  auto t0 = std::chrono::steady_clock::now();
+  ex::sync_wait(ex::for_each(ex::take_until(counting_stream{&ctx, -1, 0, &cleanups2}, ex::single(ex::stop_on_request(stop.get_token()))),
+                             [&](int) { seen.fetch_add(1); }));
+  stopper.join();
+  CHECK(seen.load() >= 5);
+  CHECK_EQ(cleanups2, 1);
+  CHECK(std::chrono::steady_clock::now() - t0 < 5s);
+  // a trigger that is already set ends the stream before its first element
+  ex::inplace_stop_source set;
+  set.request_stop();
+  int n = 0;
+  ex::sync_wait(ex::for_each(ex::take_until(counting_stream{&ctx, -1, 0, nullptr}, ex::single(ex::stop_on_request(set.get_token()))),
+                             [&](int) { ++n; }));
+  CHECK(n <= 1);
+  // an error thrown by the callback reaches the caller, after cleanup
+  int cleanups3 = 0;
+  CHECK_THROWS(ex::sync_wait(ex::for_each(counting_stream{nullptr, 3, 0, &cleanups3}, [&](int v) {
+    if (v == 1) throw std::runtime_error("boom");
+  })));
+  CHECK_EQ(cleanups3, 1);
+  // stop_if_requested and variant_sender on their own
+  CHECK(ex::sync_wait(ex::stop_if_requested()).has_value());
+  CHECK(!ex::sync_wait(ex::with_query_value(ex::stop_if_requested(), ex::get_stop_token, set.get_token())).has_value());
+  ex::variant_sender<ex::just_sender<int>, ex::just_done_sender<int>> vs(ex::just(7));
+  CHECK_EQ(*ex::sync_wait(std::move(vs)), 7);
 }
 
 EUX_TEST_MAIN()
