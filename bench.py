@@ -272,6 +272,21 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
                     else "same GPU, read in place"}
         return run
 
+    def gemm_all_peers():
+        """Every rank is caller of every other rank's GEMM and callee for every other rank."""
+        from execution_ucx_b200.models.workloads import RemoteGemmAllPeers
+        if world < 3:
+            return {"skipped": "same as the pair measurement below three ranks"}
+        m = n = k = 8192
+        w = RemoteGemmAllPeers(group, m, n, k)
+        ts = timing.time_cuda(w.step, iters=5, warmup=2, flush=flush, before=group.barrier)
+        w.check()
+        ms = group.max_over_ranks(timing.percentile(ts, 50))
+        calls = world - 1
+        w.close()
+        return {"shape": [m, n, k], "calls_served_per_rank": calls, "ms_per_round_p50": round(ms, 3),
+                "ms_per_call": round(ms / calls, 4), "tflops_per_gpu": round(2.0 * m * n * k * calls / (ms * 1e-3) / 1e12, 1)}
+
     def moe(fp8):
         def run():
             w = MoeDispatchCombine(group, fp8=fp8)
@@ -356,6 +371,7 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
     guarded("tensor_rpc_sweep", rpc_sweep)
     guarded("remote_gemm_rpc_bf16", gemm(False))
     guarded("remote_gemm_rpc_fp8_block_scaled", gemm(True))
+    guarded("remote_gemm_rpc_bf16_all_peers", gemm_all_peers)
     guarded("moe_bf16", moe(False))
     guarded("moe_fp8", moe(True))
     guarded("library_baselines", baselines)

@@ -191,6 +191,52 @@ class RemoteGemmRpc:
         self.g.free(self.x_buf, self.y_buf, self.flags, getattr(self, "xs_buf", None))
 
 
+class RemoteGemmAllPeers:
+    """Every rank calls the remote GEMM of every other rank: as callee a rank runs one fused
+    kernel per caller (pulling that caller's X, storing Y into the caller's slot for this callee),
+    as caller it waits for the world-1 results. Callers are served in a rotated order so that no
+    rank's X is pulled by everybody at once."""
+
+    def __init__(self, group: PeerGroup, m: int, n: int, k: int):
+        self.g, self.m, self.n, self.k = group, m, n, k
+        dev, w = group.device, group.world
+        self.x_buf = group.alloc(m * k * 2)
+        self.y_slot = m * n * 2
+        self.y_buf = group.alloc(self.y_slot * w)
+        self.flags = group.alloc(8 * w)
+        gen = torch.Generator(device=dev).manual_seed(77 + group.rank)
+        self.x = self.x_buf.view(torch.bfloat16, m * k).view(m, k)
+        self.x.copy_(torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16))
+        self.w = (torch.randn(k, n, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        self.gemm = gemm_ops.RemoteGemm(self.w, m)
+        self.order = [(group.rank + 1 + i) % w for i in range(w - 1)]
+        self.seq = 0
+        self.sink = torch.empty(8, dtype=torch.bfloat16, device=dev)
+        self.probe = torch.zeros(8, dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        group.barrier()
+
+    def step(self) -> None:
+        self.seq += 1
+        r = self.g.rank
+        for p in self.order:      # callee for caller p
+            self.gemm(self.x_buf.peer_ptrs[p], self.m, self.y_buf.peer_ptrs[p] + r * self.y_slot, x_is_local=False,
+                      done_flag_ptr=self.flags.peer_ptrs[p] + 8 * r, done_value=self.seq)
+        for p in self.order:      # caller: the result of callee p has landed in slot p
+            tx.push(self.probe, self.sink, wait_flag_ptr=self.flags.local_ptr + 8 * p, wait_value=self.seq,
+                    status_ptr=self.status.data_ptr())
+
+    def check(self):
+        self.gemm.check_status()
+        if int(self.status.item()):
+            raise RuntimeError("a remote gemm result did not arrive in time")
+
+    def close(self):
+        """Collective: every rank calls it."""
+        self.g.free(self.x_buf, self.y_buf, self.flags)
+
+
 class MoeDispatchCombine:
     """MoE token dispatch -> identity expert -> gate-weighted combine on all ranks."""
 
