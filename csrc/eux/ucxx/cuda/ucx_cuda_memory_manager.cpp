@@ -234,8 +234,39 @@ const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::
   return nullptr;
 }
 
+bool UcxCudaMemoryResourceManager::is_pool_base(const void* base) const {
+  for (auto& a : arenas_)
+    if (a.base == base) return true;
+  if (dedicated_.count(const_cast<void*>(base))) return true;
+  for (auto& [n, p] : large_idle_)
+    if (p == base) return true;
+  return false;
+}
+
 const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::register_memory(const void* ptr, size_t) {
-  if (auto* r = find_registration(ptr)) return r;
+  if (auto* r = find_registration(ptr)) {
+    bool ours;
+    {
+      std::lock_guard lk(mu_);
+      ours = is_pool_base(r->base);
+    }
+    if (ours) return r;
+    // Memory of somebody else's allocator (a tensor library's cache, say) can be freed and handed
+    // out again at the same address: the remembered range and handle are checked against the
+    // allocation that is there now.
+    void* base = nullptr;
+    size_t size = 0;
+    if (address_range(ptr, &base, &size) && base == r->base && size == r->size) {
+      cudaIpcMemHandle_t h;
+      if (cudaIpcGetMemHandle(&h, base) == cudaSuccess) {
+        if (std::memcmp(&h, r->handle, 64) == 0 && r->exportable) return r;
+      } else {
+        cudaGetLastError();
+        if (!r->exportable) return r;
+      }
+    }
+    unregister_memory(r->base);
+  }
   void* base = nullptr;
   size_t size = 0;
   if (!address_range(ptr, &base, &size)) return nullptr;
@@ -299,23 +330,30 @@ void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d) {
   DeviceGuard on_device(opt_.device);
   ImportKey key{d.pid, d.base};
   auto it = imports_.find(key);
+  if (it != imports_.end() && std::memcmp(it->second.handle, d.handle, 64) != 0) {
+    // the peer's allocation at this address is no longer the one that was mapped
+    cudaIpcCloseMemHandle(it->second.mapped);
+    imports_.erase(it);
+    it = imports_.end();
+  }
   if (it == imports_.end()) {
     cudaIpcMemHandle_t h;
     std::memcpy(&h, d.handle, 64);
-    void* mapped = nullptr;
-    if (cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    Imported imp;
+    if (cudaIpcOpenMemHandle(&imp.mapped, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
       cudaGetLastError();
       return nullptr;
     }
-    it = imports_.emplace(key, mapped).first;
+    std::memcpy(imp.handle, d.handle, 64);
+    it = imports_.emplace(key, imp).first;
   }
-  return static_cast<char*>(it->second) + d.offset;
+  return static_cast<char*>(it->second.mapped) + d.offset;
 }
 
 void UcxCudaMemoryResourceManager::release_imports() {
   std::lock_guard lk(mu_);
   DeviceGuard on_device(opt_.device);
-  for (auto& [k, p] : imports_) cudaIpcCloseMemHandle(p);
+  for (auto& [k, p] : imports_) cudaIpcCloseMemHandle(p.mapped);
   imports_.clear();
 }
 

@@ -100,7 +100,12 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
     uint64_t base;
     bool operator<(const ImportKey& o) const { return pid != o.pid ? pid < o.pid : base < o.base; }
   };
-  std::map<ImportKey, void*> imports_;
+  struct Imported {
+    void* mapped = nullptr;
+    unsigned char handle[64] = {0};  // the handle this mapping was opened with
+  };
+  std::map<ImportKey, Imported> imports_;
+  bool is_pool_base(const void* base) const;  // mu_ held
 };
 
 }  // namespace eux::ucxx
