@@ -4,6 +4,7 @@
 
 #include "check.hpp"
 #include "eux/ucxx/lock_free_queue.hpp"
+#include "eux/ucxx/shm_channel.hpp"
 #include "eux/ucxx/ucx_context_data.hpp"
 #include "eux/ucxx/ucx_status.hpp"
 
@@ -142,6 +143,63 @@ EUX_TEST(lock_free_queue_mpmc) {
   for (long i = 0; i < long(P) * N; ++i) want += i;
   CHECK_EQ(sum.load(), want);
   CHECK(q.empty());
+}
+
+// The shared-memory byte rings: a producer thread streams 16 MiB of a known sequence through a 2 MiB
+// ring in odd-sized pieces while the consumer reads odd-sized pieces; every byte arrives in order,
+// in both directions, and a full ring reports EAGAIN instead of overwriting.
+EUX_TEST(shm_channel_streams_bytes_both_ways) {
+  using eux::ucxx::transport::ShmChannel;
+  const std::string name = "/eux-test-" + std::to_string(getpid());
+  auto a = ShmChannel::create(name);
+  CHECK(a != nullptr);
+  auto b = ShmChannel::open(name);
+  CHECK(b != nullptr);
+  CHECK(ShmChannel::open(name) == nullptr);  // the name is gone once the peer has mapped it
+  // full ring
+  std::vector<char> big(ShmChannel::kRingBytes + 100, 'x');
+  CHECK_EQ(a->write(big.data(), big.size()), ssize_t(ShmChannel::kRingBytes));
+  errno = 0;
+  CHECK(a->write(big.data(), 1) == -1 && errno == EAGAIN);
+  std::vector<char> sink(ShmChannel::kRingBytes);
+  CHECK_EQ(b->read(sink.data(), sink.size()), ssize_t(ShmChannel::kRingBytes));
+  CHECK(!b->readable());
+  auto stream = [](ShmChannel* tx, ShmChannel* rx) {
+    const size_t total = size_t(16) << 20;
+    std::thread producer([&] {
+      size_t sent = 0, piece = 1;
+      std::vector<unsigned char> buf(70001);
+      while (sent < total) {
+        size_t n = std::min(total - sent, piece % buf.size() + 1);
+        for (size_t i = 0; i < n; ++i) buf[i] = static_cast<unsigned char>((sent + i) * 2654435761u >> 24);
+        size_t off = 0;
+        while (off < n) {
+          ssize_t w = tx->write(buf.data() + off, n - off);
+          if (w > 0) off += size_t(w);
+          else std::this_thread::yield();
+        }
+        sent += n;
+        piece = piece * 7 + 13;
+      }
+    });
+    size_t got = 0, piece = 3;
+    bool ok = true;
+    std::vector<unsigned char> buf(90001);
+    while (got < total) {
+      ssize_t r = rx->read(buf.data(), piece % buf.size() + 1);
+      if (r <= 0) {
+        std::this_thread::yield();
+        continue;
+      }
+      for (ssize_t i = 0; i < r; ++i) ok = ok && buf[i] == static_cast<unsigned char>((got + i) * 2654435761u >> 24);
+      got += size_t(r);
+      piece = piece * 5 + 11;
+    }
+    producer.join();
+    return ok;
+  };
+  CHECK(stream(a.get(), b.get()));
+  CHECK(stream(b.get(), a.get()));
 }
 
 EUX_TEST_MAIN()
