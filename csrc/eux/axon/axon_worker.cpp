@@ -32,7 +32,9 @@ std::error_code AxonWorker::StartServer() {
     return errors::make_error_code(errors::AxonErrc::WorkerStartFailed);
   }
   server_loop_stop_ = std::make_unique<ex::inplace_stop_source>();
-  server_thread_ = std::thread([this] { server_ctx_->run(server_stop_.get_token()); });
+  server_stop_ = std::make_unique<ex::inplace_stop_source>();
+  server_scope_ = std::make_unique<ex::async_scope>();
+  server_thread_ = std::thread([this] { server_ctx_->run(server_stop_->get_token()); });
   ex::sync_wait(server_ctx_->get_scheduler().schedule());  // the loop is up
   ServerLoopStart();
   return {};
@@ -48,7 +50,9 @@ std::error_code AxonWorker::StartClient() {
     return errors::make_error_code(errors::AxonErrc::WorkerStartFailed);
   }
   client_loop_stop_ = std::make_unique<ex::inplace_stop_source>();
-  client_thread_ = std::thread([this] { client_ctx_->run(client_stop_.get_token()); });
+  client_stop_ = std::make_unique<ex::inplace_stop_source>();
+  client_scope_ = std::make_unique<ex::async_scope>();
+  client_thread_ = std::thread([this] { client_ctx_->run(client_stop_->get_token()); });
   ex::sync_wait(client_ctx_->get_scheduler().schedule());
   ClientLoopStart();
   return {};
@@ -57,12 +61,12 @@ std::error_code AxonWorker::StartClient() {
 void AxonWorker::StopServer() {
   if (!server_running_.exchange(false)) return;
   server_loop_stop_->request_stop();
-  server_scope_.request_stop();
+  server_scope_->request_stop();
   // handlers in flight get the time of one deadline to finish, then the context goes down under them
-  ex::sync_wait(ex::stop_when(server_scope_.join(), ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout() + std::chrono::milliseconds(200))));
-  server_stop_.request_stop();
+  ex::sync_wait(ex::stop_when(server_scope_->join(), ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout() + std::chrono::milliseconds(200))));
+  server_stop_->request_stop();
   if (server_thread_.joinable()) server_thread_.join();
-  ex::sync_wait(server_scope_.join());
+  ex::sync_wait(server_scope_->join());
   server_ctx_.reset();
 }
 
@@ -73,11 +77,11 @@ void AxonWorker::StopClient() {
   pending_rpcs_.drain([](uint64_t, PendingRpc&& p) {
     if (p.complete) p.complete(std::nullopt, rpc_error(rpc::make_error_code(RpcErrc::CANCELLED), "the client was stopped"));
   });
-  client_scope_.request_stop();
-  ex::sync_wait(ex::stop_when(client_scope_.join(), ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout() + std::chrono::milliseconds(200))));
-  client_stop_.request_stop();
+  client_scope_->request_stop();
+  ex::sync_wait(ex::stop_when(client_scope_->join(), ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout() + std::chrono::milliseconds(200))));
+  client_stop_->request_stop();
   if (client_thread_.joinable()) client_thread_.join();
-  ex::sync_wait(client_scope_.join());
+  ex::sync_wait(client_scope_->join());
   {
     std::lock_guard lk(endpoints_mu_);
     endpoint_by_name_.clear();

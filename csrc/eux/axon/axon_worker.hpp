@@ -219,12 +219,15 @@ class AxonWorker {
 
   std::unique_ptr<ucxx::ucx_am_context> server_ctx_, client_ctx_;
   std::thread server_thread_, client_thread_;
-  exec::inplace_stop_source server_stop_, client_stop_;
+  // re-created by every StartServer / StartClient: a stop source and a scope cannot be un-stopped
+  std::unique_ptr<exec::inplace_stop_source> server_stop_ = std::make_unique<exec::inplace_stop_source>(),
+                                             client_stop_ = std::make_unique<exec::inplace_stop_source>();
   std::unique_ptr<exec::inplace_stop_source> server_loop_stop_, client_loop_stop_;
   std::atomic<bool> server_running_{false}, client_running_{false};
   exec::static_thread_pool pool_;
   exec::timed_single_thread_context time_ctx_;
-  exec::async_scope server_scope_, client_scope_;
+  std::unique_ptr<exec::async_scope> server_scope_ = std::make_unique<exec::async_scope>(),
+                                     client_scope_ = std::make_unique<exec::async_scope>();
 
   rpc::AsyncRpcDispatcher dispatcher_;
   mutable std::mutex policies_mu_;

@@ -93,7 +93,7 @@ void AxonWorker::ClientLoopStart() {
     return ex::upon_error(ex::then(ucxx::connection_recv_header(sched), [this](ucxx::recv_header_result_t arrival) { ClientHandleArrival(std::move(arrival)); }),
                           [this](std::exception_ptr e) { UCX_CTX_WARN << name_ << ": client receive failed: " << ex::what_of(e); });
   });
-  client_scope_.spawn_detached(ex::with_query_value(ex::repeat_effect_until(std::move(one), [stop] { return stop->stop_requested(); }),
+  client_scope_->spawn_detached(ex::with_query_value(ex::repeat_effect_until(std::move(one), [stop] { return stop->stop_requested(); }),
                                                     ex::get_stop_token, stop->get_token()));
 }
 
@@ -218,8 +218,8 @@ struct AxonWorker::invoke_sender {
           p->complete(std::nullopt, rpc_error(ex::error_code_of(e), "request could not be sent: " + ex::what_of(e)));
       };
       try {
-        if (c->out->iovec) worker->client_scope_.spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, c->conn_id, *c->out->iovec->get()), sent), send_failed));
-        else worker->client_scope_.spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, c->conn_id, *c->out->data->get()), sent), send_failed));
+        if (c->out->iovec) worker->client_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, c->conn_id, *c->out->iovec->get()), sent), send_failed));
+        else worker->client_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, c->conn_id, *c->out->data->get()), sent), send_failed));
       } catch (...) {
         send_failed(std::current_exception());
       }
@@ -295,8 +295,8 @@ void AxonWorker::ClientFinishWithPayload(std::shared_ptr<ClientCall> call) {
         call->finish_value(InvokeResult{std::move(call->response), PayloadVariant(b.move_buffer())});
       });
     };
-    if (custom) client_scope_.spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
-    else client_scope_.spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
+    if (custom) client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
+    else client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
     return;
   }
   auto done = [call](ucxx::active_message_buffer_bundle b) {
@@ -312,12 +312,12 @@ void AxonWorker::ClientFinishWithPayload(std::shared_ptr<ClientCall> call) {
       opaque.strides = {1};
       return call->mem.buffer_provider(utils::TensorMetaSpan{&opaque, 1});
     };
-    client_scope_.spawn_detached(ex::upon_error(
+    client_scope_->spawn_detached(ex::upon_error(
         ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)),
                       [sched, key, done](UcxBuffer& buf) { return ex::then(ucxx::connection_recv_buffer(sched, key, std::move(buf)), done); }),
         fail));
   } else {
-    client_scope_.spawn_detached(ex::upon_error(ex::then(ucxx::connection_recv_buffer(sched, key, ucx_memory_type::HOST), done), fail));
+    client_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_recv_buffer(sched, key, ucx_memory_type::HOST), done), fail));
   }
 }
 

@@ -17,7 +17,7 @@ void AxonWorker::ServerLoopStart() {
     return ex::upon_error(ex::then(ucxx::connection_recv_header(sched), [this](ucxx::recv_header_result_t arrival) { ServerHandleArrival(std::move(arrival)); }),
                           [this](std::exception_ptr e) { UCX_CTX_WARN << name_ << ": receive failed: " << ex::what_of(e); });
   });
-  server_scope_.spawn_detached(ex::with_query_value(ex::repeat_effect_until(std::move(one), [stop] { return stop->stop_requested(); }),
+  server_scope_->spawn_detached(ex::with_query_value(ex::repeat_effect_until(std::move(one), [stop] { return stop->stop_requested(); }),
                                                     ex::get_stop_token, stop->get_token()));
 }
 
@@ -163,8 +163,8 @@ void AxonWorker::ServerRunRequest(std::shared_ptr<ServerCall> call) {
         ServerDispatch(call);
       });
     };
-    if (custom) server_scope_.spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
-    else server_scope_.spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
+    if (custom) server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
+    else server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
     return;
   }
   auto done = [this, call](ucxx::active_message_buffer_bundle b) {
@@ -182,12 +182,12 @@ void AxonWorker::ServerRunRequest(std::shared_ptr<ServerCall> call) {
       opaque.strides = {1};
       return call->mem.buffer_provider(utils::TensorMetaSpan{&opaque, 1});
     };
-    server_scope_.spawn_detached(ex::upon_error(
+    server_scope_->spawn_detached(ex::upon_error(
         ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)),
                       [sched, key, done](UcxBuffer& buf) { return ex::then(ucxx::connection_recv_buffer(sched, key, std::move(buf)), done); }),
         fail));
   } else {
-    server_scope_.spawn_detached(ex::upon_error(ex::then(ucxx::connection_recv_buffer(sched, key, ucx_memory_type::HOST), done), fail));
+    server_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_recv_buffer(sched, key, ucx_memory_type::HOST), done), fail));
   }
 }
 
@@ -262,8 +262,8 @@ void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
     if (respond)
       ServerSendError(call->conn_id, call->req, rpc::make_error_code(RpcErrc::DEADLINE_EXCEEDED), "the handler did not finish before the deadline");
   };
-  server_scope_.spawn_detached(ex::upon_done(ex::upon_error(ex::then(std::move(run), finish), on_error), on_done));
-  server_scope_.spawn_detached(ex::upon_done(
+  server_scope_->spawn_detached(ex::upon_done(ex::upon_error(ex::then(std::move(run), finish), on_error), on_done));
+  server_scope_->spawn_detached(ex::upon_done(
       ex::with_query_value(ex::then(ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout()), on_deadline), ex::get_stop_token,
                            race->stop_timer.get_token()),
       [race] {}));
@@ -303,8 +303,8 @@ void AxonWorker::ServerSendResponse(std::shared_ptr<ServerCall> call, RpcRespons
     ectx.what = "response could not be sent: " + ex::what_of(e);
     ReportError(std::move(ectx));
   };
-  if (out->msg.iovec) server_scope_.spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, conn, *out->msg.iovec->get()), after), failed));
-  else server_scope_.spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, conn, *out->msg.data->get()), after), failed));
+  if (out->msg.iovec) server_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, conn, *out->msg.iovec->get()), after), failed));
+  else server_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_send(sched, conn, *out->msg.data->get()), after), failed));
 }
 
 // ---- retained requests ---------------------------------------------------------------------

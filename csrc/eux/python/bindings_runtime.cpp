@@ -8,6 +8,9 @@
 // Python handlers are started as tasks.
 #include <cuda_runtime_api.h>
 
+#include <atomic>
+#include <unordered_map>
+
 #include "bindings_common.hpp"
 #include "eux/ucxx/cuda/ucx_cuda_context.hpp"
 #include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
@@ -122,7 +125,14 @@ class PyAxonRuntime {
     try {
       loop = asyncio.attr("get_running_loop")();
     } catch (py::error_already_set&) {
-      loop = asyncio.attr("get_event_loop")();
+      // outside a running loop (registration before the program's loop exists): use the thread's
+      // current loop if it is usable, otherwise wait for the next call made from inside a loop
+      try {
+        loop = asyncio.attr("get_event_loop")();
+      } catch (py::error_already_set&) {
+        return;
+      }
+      if (loop.attr("is_closed")().cast<bool>()) return;
     }
     wake_.attach(loop);
   }
@@ -140,6 +150,17 @@ class PyAxonRuntime {
   }
   void stop() {
     if (!rt_) return;
+    // handlers that are still awaiting are answered with CANCELLED and their tasks cancelled
+    auto running = std::move(running_tasks_);
+    running_tasks_.clear();
+    for (auto& [id, t] : running) {
+      t.answer_cancelled();
+      try {
+        t.task.attr("cancel")();
+      } catch (py::error_already_set&) {
+      }
+    }
+    running.clear();
     {
       py::gil_scoped_release nogil;  // worker threads may be waiting for the GIL to finish their callbacks
       rt_->Stop();
@@ -321,7 +342,10 @@ class PyAxonRuntime {
       return rpc::AsyncInvokeSender(ex::create<rpc::RpcInvokeResult<rpc::ReturnedPayload>>([self, fn, st](auto handle) {
         // hop to the asyncio thread: start the coroutine as a task, finish the C++ call from its done-callback
         self->wake_.enqueue([self, fn, st, handle]() mutable {
-          auto fail = [st, handle](std::error_code ec, const std::string& what) mutable {
+          // the call is answered exactly once: by the task's completion, or by stop() while it still runs
+          auto settled = std::make_shared<std::atomic<bool>>(false);
+          auto fail = [st, handle, settled](std::error_code ec, const std::string& what) mutable {
+            if (settled->exchange(true)) return;
             py::gil_scoped_release nogil;
             handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{
                 st->builder.PrepareError(st->req.session_id, st->req.request_id, ec, what), rpc::ReturnedPayload{}});
@@ -340,8 +364,11 @@ class PyAxonRuntime {
               if (!e.matches(PyExc_TypeError)) throw;
               task = asyncio.attr("ensure_future")(coro, py::arg("loop") = self->wake_.loop());  // interpreters before 3.12
             }
-            auto finish = py::cpp_function([self, st, handle, fail](py::object t) mutable {
+            const uint64_t task_id = self->next_task_id_++;
+            auto finish = py::cpp_function([self, st, handle, fail, settled, task_id](py::object t) mutable {
+              self->running_tasks_.erase(task_id);
               try {
+                if (settled->load()) return;  // stop() answered for this task
                 if (t.attr("cancelled")().cast<bool>()) {
                   fail(rpc::make_error_code(rpc::RpcErrc::CANCELLED), "the handler task was cancelled");
                   return;
@@ -368,6 +395,7 @@ class PyAxonRuntime {
                 h.session_id = st->req.session_id;
                 h.request_id = st->req.request_id;
                 PayloadVariant out = payload_from_python(*self->mr_, pay);
+                if (settled->exchange(true)) return;
                 py::gil_scoped_release nogil;
                 handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{std::move(h), std::move(out)});
               } catch (py::error_already_set& e) {
@@ -376,8 +404,16 @@ class PyAxonRuntime {
                 fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
               }
             });
-            if (task.attr("done")().cast<bool>()) finish(task);
-            else task.attr("add_done_callback")(finish);
+            if (task.attr("done")().cast<bool>()) {
+              finish(task);
+            } else {
+              // still running (it awaits something): stop() must be able to answer for it, because a
+              // stop() on the loop's thread cannot wait for a task that needs the loop
+              self->running_tasks_.emplace(task_id, RunningTask{task, [fail]() mutable {
+                fail(rpc::make_error_code(rpc::RpcErrc::CANCELLED), "the runtime stopped while the handler was running");
+              }});
+              task.attr("add_done_callback")(finish);
+            }
           } catch (py::error_already_set& e) {
             fail(rpc::make_error_code(rpc::RpcErrc::INTERNAL), e.what());
           } catch (const std::exception& e) {
@@ -410,6 +446,12 @@ class PyAxonRuntime {
   bool is_cuda_ = false;
   std::shared_ptr<ucxx::UcxMemoryResourceManager> mr_;
   PythonWakeManager wake_;
+  struct RunningTask {
+    py::object task;
+    std::function<void()> answer_cancelled;
+  };
+  std::unordered_map<uint64_t, RunningTask> running_tasks_;  // touched on the loop thread only (under the GIL)
+  uint64_t next_task_id_ = 1;
   ex::static_thread_pool helper_{1};
   ex::async_scope scope_;
   std::unique_ptr<axon::AxonRuntime> rt_;

@@ -264,6 +264,27 @@ EUX_TEST(stop_client_cancels_pending_and_peer_loss_is_an_error) {
 }
 
 // Server and client in separate processes; the address travels through a pipe.
+// Stop and start again: the same workers serve new connections after a restart of either side.
+EUX_TEST(client_and_server_restart) {
+  Pair p;
+  p.server.RegisterFunction(function_id_t{1}, [](int32_t a) { return a + 1; }, "inc");
+  p.connect();
+  auto call = [&] {
+    auto r = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(1)));
+    return r && r->header.status.ok() && r->header.GetPrimitive<int32_t>(0) == 2;
+  };
+  CHECK(call());
+  p.client.StopClient();
+  CHECK(!p.client.StartClient());
+  p.client.ConnectEndpoint(p.server.GetLocalAddress(), "server");
+  CHECK(call());
+  p.server.StopServer();
+  CHECK(!p.server.StartServer());
+  p.client.DisconnectEndpoint("server");
+  p.client.ConnectEndpoint(p.server.GetLocalAddress(), "server");
+  CHECK(call());
+}
+
 // Fault injection on the host: a response frame lost on the wire, a rendezvous reply lost, and
 // a memory policy that cannot allocate. Each ends as an error at the caller within its deadline;
 // nothing hangs, and the same workers serve the next call.

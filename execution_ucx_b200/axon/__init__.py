@@ -164,9 +164,14 @@ def _contiguous(t):
     if hasattr(t, "is_contiguous"):
         return t
     flags = getattr(t, "flags", None)
-    if flags is not None and not flags["C_CONTIGUOUS"]:
+    if flags is not None:
         import numpy
-        return numpy.ascontiguousarray(t)
+        if not flags["C_CONTIGUOUS"]:
+            t = numpy.ascontiguousarray(t)
+        if not t.flags["WRITEABLE"]:
+            # DLPack cannot say "read only": numpy refuses to export such an array (a view of a received
+            # tensor, for instance), so it travels as a copy
+            t = t.copy()
     return t
 
 
