@@ -113,13 +113,19 @@ def check(rc: int, what: str) -> None:
         raise RuntimeError(f"{what} failed: {msg} ({rc})")
 
 
+_DTYPE_CODES = None
+
+
 def torch_dtype_code(dtype) -> int:
-    import torch
-    table = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16,
-             torch.float8_e4m3fn: DT_F8E4M3, torch.uint8: DT_BYTES, torch.int8: DT_BYTES}
-    if dtype not in table:
-        raise TypeError(f"dtype {dtype} is not supported by the transfer kernels")
-    return table[dtype]
+    global _DTYPE_CODES
+    if _DTYPE_CODES is None:
+        import torch
+        _DTYPE_CODES = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16,
+                        torch.float8_e4m3fn: DT_F8E4M3, torch.uint8: DT_BYTES, torch.int8: DT_BYTES}
+    try:
+        return _DTYPE_CODES[dtype]
+    except KeyError:
+        raise TypeError(f"dtype {dtype} is not supported by the transfer kernels") from None
 
 
 def current_stream_ptr() -> int:
