@@ -28,9 +28,9 @@ sys.path.insert(0, str(ROOT))
 def reference_arm(args) -> int:
     # The reference is a Bazel project (no setup.py / pyproject.toml) whose build fetches OpenUCX,
     # libunifex, cista, nanobind, ... from the network; the one permitted offline install fails.
-    why = ("pip install --no-index --target baseline/_ref /root/reference: 'not installable: neither setup.py nor "
+    why = ("pip install --no-index --target baseline/_ref <reference tree>: 'not installable: neither setup.py nor "
            "pyproject.toml found'; the reference builds only with Bazel plus network fetches of OpenUCX/libunifex/"
-           "cista/nanobind, none of which exist on this box")
+           "cista/nanobind, none of which are available offline")
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0

@@ -139,7 +139,7 @@ typedef struct eux_moe_desc {
   int32_t* slot_of;           /* [n_tokens, topk] scratch+output: slot inside (src,dst) region */
   int32_t* counters;          /* scratch [world + n_experts + 8] zero on entry, zero on exit */
   void* out;                  /* combine output [n_tokens, hidden] bf16 */
-  uint64_t seq;               /* flag value for this round (monotonic) */
+  uint64_t seq;               /* flag value of this dispatch/combine exchange (monotonic) */
   uint64_t wait_timeout_ns;
   uint32_t* status;
 } eux_moe_desc;
