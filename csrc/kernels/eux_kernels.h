@@ -166,8 +166,10 @@ typedef struct eux_gemm_desc {
   uint64_t wait_timeout_ns;
   uint32_t* status;
   int32_t copy_ctas;     /* CTAs that stream X from the peer; 0 when x_stage == x_src */
-  int32_t reserved;
+  int32_t flags;         /* EUX_GEMM_FLAG_* */
 } eux_gemm_desc;
+/* bf16 with local X and M % 256 == 0: tiles of 256 x 256 computed by pairs of CTAs (cta_group::2) */
+#define EUX_GEMM_FLAG_CTA_PAIRS 1
 EUX_API int eux_gemm_launch(const eux_gemm_desc* d, void* stream);
 EUX_API int eux_gemm_num_sms(void);
 

@@ -19,6 +19,8 @@
 // EUX_ST_TIMEOUT in the status word.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "eux_bulk.cuh"
 #include "eux_device.cuh"
 
@@ -723,6 +725,233 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   finish_cta(p, ok);
 }
 
+// ---------------------------------------------------------------------------
+// bf16, two CTAs per tile (cta_group::2): a cluster of two CTAs computes a 256 x 256 tile. Each CTA
+// loads its 128 rows of A and its 128 of the tile's 256 rows of Wt, the even CTA issues
+// tcgen05.mma.cta_group::2 over both CTAs' shared memory, and each CTA ends up with its 128 rows of
+// the accumulator in its own TMEM. Per CTA and K-step that is 32 KiB of operands instead of 48 KiB,
+// so six stages fit where the one-CTA kernel has four: more bytes in flight against the L2 latency
+// and two thirds of the shared-memory reads per flop. X must be local (M a multiple of 256).
+// All loads are per-CTA loads that signal the even CTA's barrier; no load is broadcast.
+// ---------------------------------------------------------------------------
+constexpr int STAGES2 = 6;
+constexpr int B2_STAGE_BYTES = (BN / 2) * BKB;  // this CTA's half of the Wt tile: 16 KiB
+constexpr size_t GEMM2_SMEM = (size_t)STAGES2 * (A_STAGE_BYTES + B2_STAGE_BYTES) + 2 * 16384 + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// per-CTA tile load of a CTA pair: the bytes land in this CTA, the completion is counted on `bar`, a
+// shared::cluster address (the even CTA's barrier)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on one barrier (shared::cluster address) when the pair's MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ CUtensorMap map_y, GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + (size_t)STAGES2 * A_STAGE_BYTES;
+  unsigned char* sEpi = smem + (size_t)STAGES2 * (A_STAGE_BYTES + B2_STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_SLABS * EPI_SLAB_BYTES);
+  // bars: [0,S) full (used in the even CTA), [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty (even CTA)
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES2 + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES2 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES2 + 2 + b); };
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);  // four epilogue warps in each CTA of the pair
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // one warp of each CTA, together
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int m_blocks = p.M / (2 * BM), n_blocks = p.N / BN;
+  const int total = m_blocks * n_blocks;
+  const int k_iters = p.K * 2 / BKB;
+  const int kelems = BKB / 2;
+  const int first = (int)blockIdx.x >> 1;
+  const int step = (int)gridDim.x >> 1;
+  volatile int* abort = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- loads: both CTAs, completion counted in the even CTA ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int tile = first; tile < total && !*abort; tile += step) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort, p.timeout_ns)) break;
+          const uint32_t full_leader = map_to_cta(full_bar(s), 0);
+          if (leader) mbar_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + B2_STAGE_BYTES));
+          tma_load_2d_pair(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_a, full_leader, k * kelems, mb * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(smem_u32(sB + (size_t)s * B2_STAGE_BYTES), &map_b, full_leader, k * kelems, nb * BN + (int)rank * (BN / 2));
+          if (++s == STAGES2) s = 0, ph ^= 1u;
+        }
+      }
+      if (*abort) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA: the even CTA issues for the pair ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      for (int tile = first; tile < total && !*abort; tile += step, ++it) {
+        const int buf = it & 1;
+        const uint32_t tph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abort, p.timeout_ns)) break;
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + (uint32_t)buf * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(full_bar(s), ph, abort, p.timeout_ns)) break;
+          tc_fence_after();
+          const uint32_t a0 = smem_u32(sA + (size_t)s * A_STAGE_BYTES);
+          const uint32_t b0 = smem_u32(sB + (size_t)s * B2_STAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BKB / 32; ++kk)
+            umma_pair(tacc, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), idesc, (uint32_t)((k | kk) != 0));
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(empty_bar(s));
+          umma_commit_pair(map_to_cta(empty_bar(s), 1));
+          if (++s == STAGES2) s = 0, ph ^= 1u;
+        }
+        umma_commit_pair(tfull_bar(buf));
+        umma_commit_pair(map_to_cta(tfull_bar(buf), 1));
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- epilogue: each CTA stores its 128 rows ----------------
+    const int lg = warp - 4;
+    const int row_local = lg * 32 + lane;
+    const bool elected = warp == 4 && lane == 0;
+    const uint32_t epi0 = smem_u32(sEpi);
+    int it = 0;
+    uint32_t slab = 0;
+    for (int tile = first; tile < total; tile += step, ++it) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      const int buf = it & 1;
+      const uint32_t tph = (uint32_t)(it >> 1) & 1u;
+      const bool got = !*abort && mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns);
+      if (epi_vote_any(1, !got)) break;
+      tc_fence_after();
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)buf * BN;
+#pragma unroll 1
+      for (int sl = 0; sl < BN / 64; ++sl, ++slab) {
+        const uint32_t sbuf = epi0 + (slab & 1u) * EPI_SLAB_BYTES;
+        if (elected) bulk_wait_read_1();
+        epi_bar_sync(1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(tbase + sl * 64 + h * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              q[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+            const int chunk = h * 4 + j;
+            st_shared_u4(sbuf + (uint32_t)row_local * 128u + (uint32_t)((chunk ^ (row_local & 7)) * 16), o);
+          }
+        }
+        if (sl == BN / 64 - 1) {  // this CTA's half of the accumulator is out of TMEM
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote(map_to_cta(tempty_bar(buf), 0));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epi_bar_sync(1);
+        if (elected) {
+          tma_store_2d(&map_y, sbuf, nb * BN + sl * 64, mb * 2 * BM + (int)rank * BM);
+          bulk_commit();
+        }
+      }
+    }
+    if (elected) {
+      bulk_wait_all();
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its shared memory or TMEM
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+  }
+  const bool ok = s_abort == 0;
+  if (!ok && threadIdx.x == 0) {
+    set_status(p.status, EUX_ST_TIMEOUT, 22);
+    atomicExch(p.sched + 1, 1u);
+  }
+  finish_cta(p, ok);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -803,6 +1032,22 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
                            : cudaFuncSetAttribute(remote_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev][d->fp8 ? 1 : 0] = true;
+  }
+  // local bf16 with M in whole 256-row blocks can run on CTA pairs (bit 0 of the descriptor's flags)
+  const bool want_pairs = (d->flags & EUX_GEMM_FLAG_CTA_PAIRS) != 0;
+  if (want_pairs && !d->fp8 && !pull && d->M % (2 * BM) == 0) {
+    static bool attr2_set[64] = {false};
+    if (!attr2_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(remote_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM2_SMEM);
+      if (e != cudaSuccess) return (int)e;
+      attr2_set[dev] = true;
+    }
+    CUtensorMap mb2;  // this CTA's half of a Wt tile: 128 rows
+    if (int rc = make_map(&mb2, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, BN / 2)) return rc;
+    const int tiles2 = (d->M / (2 * BM)) * (d->N / BN);
+    const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+    remote_gemm_2cta_kernel<<<2 * pairs, GEMM_THREADS, GEMM2_SMEM, (cudaStream_t)stream>>>(ma, mb2, my, p);
+    return (int)cudaGetLastError();
   }
   const int tiles = (d->M / BM) * (d->N / bn);
   int grid = copy_ctas + (tiles < sms - copy_ctas ? tiles : sms - copy_ctas);

@@ -58,7 +58,7 @@ class GemmDesc(C.Structure):
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("fp8", C.c_int32),
         ("panel_flags", C.c_void_p), ("sched", C.c_void_p),
         ("done_flag", C.c_void_p), ("done_value", C.c_uint64), ("wait_timeout_ns", C.c_uint64),
-        ("status", C.c_void_p), ("copy_ctas", C.c_int32), ("reserved", C.c_int32),
+        ("status", C.c_void_p), ("copy_ctas", C.c_int32), ("flags", C.c_int32),
     ]
 
 

@@ -35,8 +35,11 @@ class RemoteGemm:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def __call__(self, x_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
-                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000) -> None:
-        """Y[m,N] (at ``y_ptr``) = X[m,K] (at ``x_ptr``) @ W. Both addresses may be peer memory."""
+                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000,
+                 cta_pairs: bool = False) -> None:
+        """Y[m,N] (at ``y_ptr``) = X[m,K] (at ``x_ptr``) @ W. Both addresses may be peer memory.
+        ``cta_pairs`` asks for the kernel that computes 256 x 256 tiles on pairs of CTAs
+        (local X, ``m`` a multiple of 256; ignored otherwise)."""
         global _launches
         if m > self.max_m:
             raise ValueError("m exceeds the staging buffer")
@@ -48,6 +51,7 @@ class RemoteGemm:
         d.panel_flags, d.sched = self.panel_flags.data_ptr(), self.sched.data_ptr()
         d.done_flag, d.done_value = done_flag_ptr or None, done_value
         d.wait_timeout_ns, d.status, d.copy_ctas = timeout_ns, self.status.data_ptr(), copy_ctas
+        d.flags = 1 if cta_pairs else 0
         _native.check(_native.load().eux_gemm_launch(C.byref(d), C.c_void_p(_native.current_stream_ptr())),
                       "eux_gemm_launch")
         _launches += 1
