@@ -752,6 +752,38 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void st_shared_remote_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// like mbar_wait, but what the arriving CTA of the cluster wrote before its arrive is visible afterwards
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort, uint64_t timeout_ns) {
+  auto try_once = [&]() {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+  };
+  if (try_once()) return true;
+  const uint64_t limit = timeout_ns ? timeout_ns : 2000000000ull;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
+    if (try_once()) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort) return false;
+      if (globaltimer_ns() - t0 > limit) {
+        *abort = 1;
+        return false;
+      }
+    }
+  }
+  *abort = 1;
+  return false;
+}
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -779,14 +811,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_y, GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
+  bool copy_ok = true;
+  if ((int)blockIdx.x < p.copy_ctas) {
+    // whole pairs copy X first (copy_ctas is even). A CTA whose copy failed still walks through the
+    // rest with its abort flag set: its partner waits for it at the cluster barriers.
+    copy_ok = copy_role_n(p, GEMM_THREADS, smem_raw);
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncthreads();
+  }
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;
   unsigned char* sB = smem + (size_t)STAGES2 * A_STAGE_BYTES;
   unsigned char* sEpi = smem + (size_t)STAGES2 * (A_STAGE_BYTES + B2_STAGE_BYTES);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_SLABS * EPI_SLAB_BYTES);
-  // bars: [0,S) full (used in the even CTA), [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty (even CTA)
+  // bars: [0,S) full (used in the even CTA), [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty (even CTA),
+  // then TILE_RING tile slots
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ int s_tiles[TILE_RING];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
   const bool leader = rank == 0;
@@ -795,8 +837,10 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES2 + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES2 + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES2 + 2 + b); };
+  auto tile_bar = [&](int i) { return bar0 + 8u * (2 * STAGES2 + 4 + i); };
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort = copy_ok ? 0 : 1;
+    for (int i = 0; i < TILE_RING; ++i) mbar_init(tile_bar(i), 1);
     for (int s = 0; s < STAGES2; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -824,18 +868,41 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   const int total = m_blocks * n_blocks;
   const int k_iters = p.K * 2 / BKB;
   const int kelems = BKB / 2;
-  const int first = (int)blockIdx.x >> 1;
-  const int step = (int)gridDim.x >> 1;
   volatile int* abort = &s_abort;
+  // The even CTA draws the pair's next tile from the global counter and puts it into both CTAs'
+  // rings (its own, and the partner's through distributed shared memory).
+  auto next_tile = [&](int it) -> int {
+    if (!mbar_wait_cluster(tile_bar(it & (TILE_RING - 1)), (uint32_t)(it / TILE_RING) & 1u, abort, p.timeout_ns)) return total;
+    return *(volatile int*)&s_tiles[it & (TILE_RING - 1)];
+  };
 
   if (warp == 0) {
     // ---------------- loads: both CTAs, completion counted in the even CTA ----------------
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (int tile = first; tile < total && !*abort; tile += step) {
+      for (int it = 0;; ++it) {
+        int tile;
+        if (leader) {
+          tile = *abort ? total : (int)atomicAdd(p.sched + 2, 1u);
+          const int slot = it & (TILE_RING - 1);
+          s_tiles[slot] = tile;
+          mbar_arrive(tile_bar(slot));
+          st_shared_remote_u32(map_to_cta(smem_u32(&s_tiles[slot]), 1), (uint32_t)tile);
+          mbar_arrive_remote(map_to_cta(tile_bar(slot), 1));
+        } else {
+          tile = next_tile(it);
+        }
+        if (tile >= total) break;
         int mb, nb;
         tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        if (p.copy_ctas > 0) {  // this CTA's 128 rows of the 256-row block
+          if (!wait_u32_ge_gpu(p.panel_flags + 2 * mb + (int)rank, (uint32_t)p.copy_ctas, p.timeout_ns)) {
+            *abort = 1;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int k = 0; k < k_iters; ++k) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort, p.timeout_ns)) break;
           const uint32_t full_leader = map_to_cta(full_bar(s), 0);
@@ -856,8 +923,8 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
       int s = 0;
       uint32_t ph = 0;
-      int it = 0;
-      for (int tile = first; tile < total && !*abort; tile += step, ++it) {
+      for (int it = 0;; ++it) {
+        if (next_tile(it) >= total || *abort) break;
         const int buf = it & 1;
         const uint32_t tph = (uint32_t)(it >> 1) & 1u;
         if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abort, p.timeout_ns)) break;
@@ -886,9 +953,10 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const int row_local = lg * 32 + lane;
     const bool elected = warp == 4 && lane == 0;
     const uint32_t epi0 = smem_u32(sEpi);
-    int it = 0;
     uint32_t slab = 0;
-    for (int tile = first; tile < total; tile += step, ++it) {
+    for (int it = 0;; ++it) {
+      const int tile = next_tile(it);
+      if (epi_vote_any(1, tile >= total)) break;
       int mb, nb;
       tile_coords(tile, m_blocks, n_blocks, mb, nb);
       const int buf = it & 1;
@@ -1035,7 +1103,7 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   }
   // local bf16 with M in whole 256-row blocks can run on CTA pairs (bit 0 of the descriptor's flags)
   const bool want_pairs = (d->flags & EUX_GEMM_FLAG_CTA_PAIRS) != 0;
-  if (want_pairs && !d->fp8 && !pull && d->M % (2 * BM) == 0) {
+  if (want_pairs && !d->fp8 && d->M % (2 * BM) == 0) {
     static bool attr2_set[64] = {false};
     if (!attr2_set[dev]) {
       cudaError_t e = cudaFuncSetAttribute(remote_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM2_SMEM);
@@ -1045,7 +1113,12 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
     CUtensorMap mb2;  // this CTA's half of a Wt tile: 128 rows
     if (int rc = make_map(&mb2, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, BN / 2)) return rc;
     const int tiles2 = (d->M / (2 * BM)) * (d->N / BN);
-    const int pairs = tiles2 < sms / 2 ? tiles2 : sms / 2;
+    int copy_pairs = pull ? (copy_ctas + 1) / 2 : 0;
+    if (copy_pairs > sms / 2 - 1) copy_pairs = sms / 2 - 1;
+    p.copy_ctas = 2 * copy_pairs;
+    // every pair computes (the copying ones after their transfer), and they all have to be resident:
+    // pairs that copy must not wait for a slot behind pairs that wait for their panels
+    const int pairs = pull ? sms / 2 : (tiles2 < sms / 2 ? tiles2 : sms / 2);
     remote_gemm_2cta_kernel<<<2 * pairs, GEMM_THREADS, GEMM2_SMEM, (cudaStream_t)stream>>>(ma, mb2, my, p);
     return (int)cudaGetLastError();
   }

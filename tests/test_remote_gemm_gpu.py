@@ -56,9 +56,11 @@ def test_block_scaled_fp8_matches_fp32(cuda_device, m, n, k, pull):
         assert int(g.panel_flags.sum()) == 0 and int(g.sched.sum()) == 0
 
 
+@pytest.mark.parametrize("pull", [False, True])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 1024), (1024, 512, 2048)])
-def test_bf16_local_cta_pairs(cuda_device, m, n, k):
-    """The kernel that computes 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2) against fp32 PyTorch."""
+def test_bf16_cta_pairs(cuda_device, m, n, k, pull):
+    """The kernel that computes 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2) against fp32 PyTorch,
+    with X read in place and with X streamed in by copying pairs that then join the GEMM."""
     from execution_ucx_b200.ops.remote_gemm import RemoteGemm
     torch.manual_seed(m + n + k)
     x = torch.randn(m, k, device=cuda_device).to(torch.bfloat16)
@@ -67,9 +69,13 @@ def test_bf16_local_cta_pairs(cuda_device, m, n, k):
     y = torch.zeros(m, n, dtype=torch.bfloat16, device=cuda_device)
     done = torch.zeros(1, dtype=torch.int64, device=cuda_device)
     for call in range(2):      # twice: the scratch counters are left clean
-        g(x.data_ptr(), m, y.data_ptr(), x_is_local=True, cta_pairs=True, done_flag_ptr=done.data_ptr(), done_value=call + 1)
+        g(x.data_ptr(), m, y.data_ptr(), x_is_local=not pull, cta_pairs=True, done_flag_ptr=done.data_ptr(), done_value=call + 1,
+          copy_ctas=4 if pull else 0)
         torch.cuda.synchronize()
         g.check_status()
         assert int(done.item()) == call + 1
         torch.testing.assert_close(y.float(), x.float() @ w.float(), rtol=2e-2, atol=2e-2)
+        if pull:
+            assert torch.equal(g.x_stage[:m].view(torch.int16), x.view(torch.int16))
+        assert int(g.panel_flags.sum()) == 0 and int(g.sched.sum()) == 0
         y.zero_()
