@@ -731,7 +731,9 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 // tcgen05.mma.cta_group::2 over both CTAs' shared memory, and each CTA ends up with its 128 rows of
 // the accumulator in its own TMEM. Per CTA and K-step that is 32 KiB of operands instead of 48 KiB,
 // so six stages fit where the one-CTA kernel has four: more bytes in flight against the L2 latency
-// and two thirds of the shared-memory reads per flop. X must be local (M a multiple of 256).
+// and two thirds of the shared-memory reads per flop. M must be a multiple of 256. With a remote X the first
+// copy_ctas CTAs (whole pairs) copy it before they join, and the even CTA of each pair draws the pair's
+// tiles from the global counter and hands them to its partner through distributed shared memory.
 // All loads are per-CTA loads that signal the even CTA's barrier; no load is broadcast.
 // ---------------------------------------------------------------------------
 constexpr int STAGES2 = 6;
@@ -1101,7 +1103,7 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
     if (e != cudaSuccess) return (int)e;
     attr_set[dev][d->fp8 ? 1 : 0] = true;
   }
-  // local bf16 with M in whole 256-row blocks can run on CTA pairs (bit 0 of the descriptor's flags)
+  // bf16 with M in whole 256-row blocks can run on CTA pairs (bit 0 of the descriptor's flags)
   const bool want_pairs = (d->flags & EUX_GEMM_FLAG_CTA_PAIRS) != 0;
   if (want_pairs && !d->fp8 && d->M % (2 * BM) == 0) {
     static bool attr2_set[64] = {false};
@@ -1173,5 +1175,6 @@ extern "C" int eux_gemm_bf16_noalloc(const void* x, const void* w_t, void* y, in
   d.wait_timeout_ns = wait_timeout_ns;
   d.status = status;
   d.copy_ctas = 0;
+  d.flags = EUX_GEMM_FLAG_CTA_PAIRS;  // taken when M is a multiple of 256
   return eux_gemm_launch(&d, stream);
 }

@@ -36,10 +36,11 @@ class RemoteGemm:
 
     def __call__(self, x_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
                  done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000,
-                 cta_pairs: bool = False) -> None:
+                 cta_pairs: bool = True) -> None:
         """Y[m,N] (at ``y_ptr``) = X[m,K] (at ``x_ptr``) @ W. Both addresses may be peer memory.
-        ``cta_pairs`` asks for the kernel that computes 256 x 256 tiles on pairs of CTAs
-        (local X, ``m`` a multiple of 256; ignored otherwise)."""
+        ``cta_pairs`` selects the kernel that computes 256 x 256 tiles on pairs of CTAs
+        (tcgen05 cta_group::2) whenever ``m`` is a multiple of 256; other shapes, and
+        ``cta_pairs=False``, run the kernel with one CTA per 128 x 256 tile."""
         global _launches
         if m > self.max_m:
             raise ValueError("m exceeds the staging buffer")
