@@ -168,8 +168,14 @@ typedef struct eux_gemm_desc {
   int32_t copy_ctas;     /* CTAs that stream X from the peer; 0 when x_stage == x_src */
   int32_t flags;         /* EUX_GEMM_FLAG_* */
 } eux_gemm_desc;
-/* bf16 with local X and M % 256 == 0: tiles of 256 x 256 computed by pairs of CTAs (cta_group::2) */
+/* bf16 with M % 256 == 0: tiles of 256 x 256 computed by pairs of CTAs (cta_group::2) */
 #define EUX_GEMM_FLAG_CTA_PAIRS 1
+/* With a remote X: two spare warps of every CTA copy X (and its scales) beside the GEMM's warps, instead of
+   copy_ctas CTAs that copy first and compute afterwards. */
+#define EUX_GEMM_FLAG_COPY_WARPS 2
+/* With a remote X the first group of tiles is only a few row blocks tall, so that the first wave of
+   CTAs waits for the first panels only. EUX_GEMM_FLAG_HEAD(n) overrides that height (0: no short group). */
+#define EUX_GEMM_FLAG_HEAD(n) ((((n) + 1) & 0xff) << 8)
 EUX_API int eux_gemm_launch(const eux_gemm_desc* d, void* stream);
 EUX_API int eux_gemm_num_sms(void);
 

@@ -50,6 +50,8 @@ struct GemmParams {
   uint64_t timeout_ns;
   uint32_t* status;
   int copy_ctas;
+  int head_blocks;  // height of the first tile group in row blocks (0: like the others)
+  int copy_warps;   // warps (two per CTA) that copy X beside the GEMM's own warps; 0 when copy CTAs do it
   // block-scaled fp8 only
   const float* x_scale_src;   // [M, K/128], caller's (may be peer)
   float* x_scale_stage;       // local copy used by the epilogue (== x_scale_src when X is local)
@@ -109,11 +111,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
+// Tiles in groups of GROUP_M row blocks (row block fastest inside a group) so that one wave of CTAs
+// shares few panels of X and few of W in L2. `head` > 0 makes the first group only `head` blocks tall:
+// while X is still arriving from the caller, the first wave then waits for the first few panels only.
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int head, int& mb, int& nb) {
+  int base = 0;
+  if (head > 0 && head < m_blocks) {
+    if (tile < head * n_blocks) {
+      mb = tile % head;
+      nb = tile / head;
+      return;
+    }
+    tile -= head * n_blocks;
+    base = head;
+    m_blocks -= head;
+  }
   const int per_group = GROUP_M * n_blocks;
   const int g = tile / per_group, r = tile - g * per_group;
   const int rows = min(GROUP_M, m_blocks - g * GROUP_M);
-  mb = g * GROUP_M + r % rows;
+  mb = base + g * GROUP_M + r % rows;
   nb = r / rows;
 }
 
@@ -263,6 +279,63 @@ __device__ bool copy_role_n(const GemmParams& p, const int nthreads, unsigned ch
   return cp_abort == 0;
 }
 
+// Two otherwise idle warps of every CTA copy X while the CTA's other warps compute: the transfer is spread
+// over all SMs' load/store units (a few dedicated CTAs moving it with bulk copies reach about half the link
+// rate), and no CTA is lost to the GEMM. X is cut into 1 KiB pieces handed round-robin to the copy warps of
+// the grid, in address order, so the panels complete in the order in which the tiles need them. A warp adds
+// one to a panel's counter once it has no piece of that panel left; a panel is complete at copy_warps.
+__device__ __forceinline__ void ld_v8_b32(const void* ptr, uint32_t (&v)[8]) {
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "l"(ptr));
+}
+__device__ __forceinline__ void st_v8_b32(void* ptr, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+__device__ __forceinline__ void copy_warp_role(const GemmParams& p, uint32_t warp_id, int lane) {
+  constexpr int U = 8;  // pieces in flight per warp: 8 KiB
+  const uint32_t nw = (uint32_t)p.copy_warps;
+  const int panels = p.M / BM;
+  const uint32_t pieces_per_panel = (uint32_t)(((size_t)BM * p.K * p.elem_bytes) >> 10);
+  const uint32_t total = (uint32_t)panels * pieces_per_panel;
+  if (p.x_scale_src && p.x_scale_stage && p.x_scale_src != p.x_scale_stage) {
+    // the row scales travel first: every warp copies its slice before it reports any panel
+    const size_t n4 = (size_t)p.M * (p.K / 128) / 4;  // K / 128 scales per row, M a multiple of 128: whole float4s
+    const float4* s4 = reinterpret_cast<const float4*>(p.x_scale_src);
+    float4* d4 = reinterpret_cast<float4*>(p.x_scale_stage);
+    for (size_t i = (size_t)warp_id * 32 + lane; i < n4; i += (size_t)nw * 32) d4[i] = __ldcg(s4 + i);
+  }
+  const unsigned char* src = p.x_src + (size_t)lane * 32;
+  unsigned char* dst = p.x_stage + (size_t)lane * 32;
+  // Panels are reported one batch late: the fence that makes a batch's stores visible then runs while
+  // the next batch's loads are in flight, and costs nothing on top of them.
+  int signalled = 0, ready = 0;
+  auto report = [&](int upto) {
+    if (upto <= signalled) return;
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      for (int q = signalled; q < upto; ++q) red_release_gpu_add(p.panel_flags + q, 1u);
+    }
+    signalled = upto;
+  };
+  for (uint32_t r = warp_id; r < total; r += nw * U) {
+    uint32_t v[U][8];
+#pragma unroll
+    for (int j = 0; j < U; ++j)
+      if (r + j * nw < total) ld_v8_b32(src + ((size_t)(r + j * nw) << 10), v[j]);
+    report(ready);
+#pragma unroll
+    for (int j = 0; j < U; ++j)
+      if (r + j * nw < total) st_v8_b32(dst + ((size_t)(r + j * nw) << 10), v[j]);
+    const uint64_t next = (uint64_t)r + (uint64_t)nw * U;
+    ready = next >= total ? panels : (int)(next / pieces_per_panel);  // no piece of these panels is left for this warp
+  }
+  report(panels);  // a warp without a piece of the last panels (or of any) still counts for them
+}
+
 __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
   __syncthreads();
   if (threadIdx.x != 0) return;
@@ -359,9 +432,9 @@ remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         mbar_arrive(tile_bar(it & (TILE_RING - 1)));
         if (tile >= total) break;
         int mb, nb;
-        tile_coords(tile, m_blocks, n_blocks, mb, nb);
-        if (p.copy_ctas > 0) {
-          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)p.copy_ctas, p.timeout_ns)) {
+        tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
+        if (p.copy_ctas + p.copy_warps > 0) {
+          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns)) {
             *abort = 1;
             break;
           }
@@ -408,7 +481,10 @@ remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         umma_commit(tfull_bar(buf));
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    // warps 2 and 3: X (and its scales) from the caller's memory into the staging buffer
+    if (p.copy_warps > 0) copy_warp_role(p, (uint32_t)blockIdx.x * 2u + (uint32_t)(warp - 2), lane);
+  } else {
     // ---------------- epilogue ----------------
     const int lg = warp - 4;  // TMEM lane group of this warp
     const int row_local = lg * 32 + lane;
@@ -421,7 +497,7 @@ remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int tile = next_tile(it);
       if (epi_vote_any(1, tile >= total)) break;
       int mb, nb;
-      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
       const int buf = it & 1;
       const uint32_t tph = (uint32_t)(it >> 1) & 1u;
       const bool got = mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns);
@@ -573,9 +649,9 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         mbar_arrive(tile_bar(it & (TILE_RING - 1)));
         if (tile >= total) break;
         int mb, nb;
-        tile_coords(tile, m_blocks, n_blocks, mb, nb);
-        if (p.copy_ctas > 0) {
-          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)p.copy_ctas, p.timeout_ns)) {
+        tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
+        if (p.copy_ctas + p.copy_warps > 0) {
+          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns)) {
             *abort = 1;
             break;
           }
@@ -620,7 +696,10 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    // warps 2 and 3: X (and its scales) from the caller's memory into the staging buffer
+    if (p.copy_warps > 0) copy_warp_role(p, (uint32_t)blockIdx.x * 2u + (uint32_t)(warp - 2), lane);
+  } else {
     const int lg = (warp - 4) & 3;    // TMEM lane group
     const int half = (warp - 4) >> 2;  // which 64 columns of the tile
     const int row_local = lg * 32 + lane;
@@ -632,7 +711,7 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const int tile = next_tile(it);
       if (epi_vote_any(1 + half, tile >= total)) break;  // the four warps of a half leave together
       int mb, nb;
-      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
       const int row = mb * BM + lg * 32 + lane;
       const float* sx = p.x_scale_stage + (size_t)row * kscales;
       const float* sw = p.w_scale + (size_t)nb * kscales;
@@ -643,9 +722,9 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       // When X is pulled from a peer its row scales travel with it: they are known to have landed
       // once the panel is reported, so the warp checks the panel itself before it reads any of them
       // (the loads below run ahead of the MMA, which is what hides their latency).
-      if (p.copy_ctas > 0) {
+      if (p.copy_ctas + p.copy_warps > 0) {
         int arrived = 1;
-        if (lane == 0) arrived = wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)p.copy_ctas, p.timeout_ns) ? 1 : 0;
+        if (lane == 0) arrived = wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns) ? 1 : 0;
         arrived = __shfl_sync(0xffffffffu, arrived, 0);
         if (!arrived) {
           *abort = 1;
@@ -897,9 +976,9 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
         if (tile >= total) break;
         int mb, nb;
-        tile_coords(tile, m_blocks, n_blocks, mb, nb);
-        if (p.copy_ctas > 0) {  // this CTA's 128 rows of the 256-row block
-          if (!wait_u32_ge_gpu(p.panel_flags + 2 * mb + (int)rank, (uint32_t)p.copy_ctas, p.timeout_ns)) {
+        tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
+        if (p.copy_ctas + p.copy_warps > 0) {  // this CTA's 128 rows of the 256-row block
+          if (!wait_u32_ge_gpu(p.panel_flags + 2 * mb + (int)rank, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns)) {
             *abort = 1;
             break;
           }
@@ -949,7 +1028,10 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         umma_commit_pair(map_to_cta(tfull_bar(buf), 1));
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    // ---------------- warps 2 and 3: X from the caller's memory into the staging buffer ----------------
+    if (p.copy_warps > 0) copy_warp_role(p, (uint32_t)blockIdx.x * 2u + (uint32_t)(warp - 2), lane);
+  } else {
     // ---------------- epilogue: each CTA stores its 128 rows ----------------
     const int lg = warp - 4;
     const int row_local = lg * 32 + lane;
@@ -960,7 +1042,7 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const int tile = next_tile(it);
       if (epi_vote_any(1, tile >= total)) break;
       int mb, nb;
-      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
       const int buf = it & 1;
       const uint32_t tph = (uint32_t)(it >> 1) & 1u;
       const bool got = !*abort && mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns);
@@ -1072,8 +1154,9 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   if (d->fp8 && (d->K % 128 || !d->x_scale || !d->w_scale)) return EUX_ERR_BAD_ARG;
   const bool pull = d->x_src && d->x_src != d->x_stage;
   if (d->fp8 && pull && !d->x_scale_stage) return EUX_ERR_BAD_ARG;
-  // measured on two B200s (8192^3): 16 copy CTAs are best for bf16 (0.875 ms), 48 for fp8 (0.928 ms);
-  // they turn into GEMM CTAs once X is here
+  // Copy CTAs (when the flags do not ask for copy warps) turn into GEMM CTAs once X is here. Measured on
+  // two B200s (8192^3): 16 are best for bf16, 48 for fp8; two copy warps in every CTA beat both, by 4 %
+  // (bf16 on pairs) and 7 % (fp8).
   int copy_ctas = pull ? (d->copy_ctas > 0 ? d->copy_ctas : (d->fp8 ? 48 : 16)) : 0;
   const int sms = eux_gemm_num_sms();
   if (copy_ctas >= sms) return EUX_ERR_BAD_ARG;
@@ -1093,6 +1176,10 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   p.x_scale_src = d->fp8 ? d->x_scale : nullptr;
   p.x_scale_stage = d->fp8 ? (pull ? d->x_scale_stage : const_cast<float*>(d->x_scale)) : nullptr;
   p.w_scale = d->w_scale;
+  // bits 8..15 of the flags: 1 + the height of the first tile group, 0 for the default
+  const int head_arg = (int)((d->flags >> 8) & 0xffu) - 1;
+  p.copy_warps = 0;
+  p.head_blocks = !pull ? 0 : head_arg >= 0 ? head_arg : d->fp8 ? 2 : 4;
   static bool attr_set[64][2] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1118,6 +1205,11 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
     int copy_pairs = pull ? (copy_ctas + 1) / 2 : 0;
     if (copy_pairs > sms / 2 - 1) copy_pairs = sms / 2 - 1;
     p.copy_ctas = 2 * copy_pairs;
+    if (pull && head_arg < 0) p.head_blocks = 4;  // of 256 rows; measured best of 0, 2, 4, 8 on two B200s
+    if (pull && (d->flags & EUX_GEMM_FLAG_COPY_WARPS)) {  // two warps of every CTA copy, no CTA only copies
+      p.copy_ctas = 0;
+      p.copy_warps = 2 * 2 * (sms / 2);
+    }
     // every pair computes (the copying ones after their transfer), and they all have to be resident:
     // pairs that copy must not wait for a slot behind pairs that wait for their panels
     const int pairs = pull ? sms / 2 : (tiles2 < sms / 2 ? tiles2 : sms / 2);
@@ -1126,6 +1218,11 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   }
   const int tiles = (d->M / BM) * (d->N / bn);
   int grid = copy_ctas + (tiles < sms - copy_ctas ? tiles : sms - copy_ctas);
+  if (pull && (d->flags & EUX_GEMM_FLAG_COPY_WARPS)) {  // every SM takes part in the copy, with or without a tile
+    grid = sms;
+    p.copy_ctas = 0;
+    p.copy_warps = 2 * grid;
+  }
   if (d->fp8) remote_gemm_fp8_kernel<<<grid, GEMM8_THREADS, GEMM8_SMEM, (cudaStream_t)stream>>>(ma, mb, my, p);
   else remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, my, p);
   return (int)cudaGetLastError();

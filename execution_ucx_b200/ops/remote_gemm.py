@@ -36,11 +36,16 @@ class RemoteGemm:
 
     def __call__(self, x_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
                  done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000,
-                 cta_pairs: bool = True) -> None:
+                 cta_pairs: bool = True, head_blocks: Optional[int] = None,
+                 copy_warps: Optional[bool] = None) -> None:
         """Y[m,N] (at ``y_ptr``) = X[m,K] (at ``x_ptr``) @ W. Both addresses may be peer memory.
         ``cta_pairs`` selects the kernel that computes 256 x 256 tiles on pairs of CTAs
         (tcgen05 cta_group::2) whenever ``m`` is a multiple of 256; other shapes, and
-        ``cta_pairs=False``, run the kernel with one CTA per 128 x 256 tile."""
+        ``cta_pairs=False``, run the kernel with one CTA per 128 x 256 tile. ``head_blocks``
+        overrides the height (in row blocks) of the first group of tiles when X is remote.
+        A remote X is copied into the staging buffer by two spare warps of every CTA while the
+        other warps compute (``copy_warps``, the default), or, when ``copy_ctas`` > 0 is given, by
+        that many CTAs that copy first and compute afterwards."""
         global _launches
         if m > self.max_m:
             raise ValueError("m exceeds the staging buffer")
@@ -52,7 +57,9 @@ class RemoteGemm:
         d.panel_flags, d.sched = self.panel_flags.data_ptr(), self.sched.data_ptr()
         d.done_flag, d.done_value = done_flag_ptr or None, done_value
         d.wait_timeout_ns, d.status, d.copy_ctas = timeout_ns, self.status.data_ptr(), copy_ctas
-        d.flags = 1 if cta_pairs else 0
+        if copy_warps is None:
+            copy_warps = copy_ctas == 0
+        d.flags = (1 if cta_pairs else 0) | (2 if copy_warps else 0) | (0 if head_blocks is None else ((head_blocks + 1) & 0xff) << 8)
         _native.check(_native.load().eux_gemm_launch(C.byref(d), C.c_void_p(_native.current_stream_ptr())),
                       "eux_gemm_launch")
         _launches += 1
@@ -106,11 +113,15 @@ class RemoteGemmFp8:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def __call__(self, xq_ptr: int, xs_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
-                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000) -> None:
+                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000,
+                 copy_warps: Optional[bool] = None, head_blocks: Optional[int] = None) -> None:
         global _launches
         if m > self.max_m:
             raise ValueError("m exceeds the staging buffer")
         d = _native.GemmDesc()
+        if copy_warps is None:
+            copy_warps = copy_ctas == 0
+        d.flags = (2 if copy_warps else 0) | (0 if head_blocks is None else ((head_blocks + 1) & 0xff) << 8)
         d.x_src = xq_ptr
         d.x_stage = xq_ptr if x_is_local else self.x_stage.data_ptr()
         d.x_scale = xs_ptr
