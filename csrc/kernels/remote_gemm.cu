@@ -815,9 +815,21 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 // tiles from the global counter and hands them to its partner through distributed shared memory.
 // All loads are per-CTA loads that signal the even CTA's barrier; no load is broadcast.
 // ---------------------------------------------------------------------------
-constexpr int STAGES2 = 6;
 constexpr int B2_STAGE_BYTES = (BN / 2) * BKB;  // this CTA's half of the Wt tile: 16 KiB
-constexpr size_t GEMM2_SMEM = (size_t)STAGES2 * (A_STAGE_BYTES + B2_STAGE_BYTES) + 2 * 16384 + 1024 + 256;
+// The MX variant (e4m3 values, one power-of-two scale per 32 elements along K, applied by the tensor core:
+// tcgen05.mma kind::mxf8f6f4.block_scale) runs on the same frame. A K-step is again 128 bytes of every row,
+// now 128 elements, and each stage also carries the step's scale factors: 512 bytes for this CTA's 128 rows
+// of X and 1024 for the tile's 256 rows of Wt, in the order in which tcgen05.cp puts them into TMEM
+// (byte (r % 32) * 16 + (r / 32) * 4 + j for row r and 32-element block j of the step). The scale factors
+// take TMEM columns too, so the MX variant has one accumulator buffer where bf16 has two.
+constexpr int SF_STAGE_BYTES = 512 + 1024;
+template <bool MX> struct PairCfg {
+  static constexpr int STAGES = MX ? 5 : 6;
+  static constexpr int NBUF = MX ? 1 : 2;  // accumulator buffers of BN columns in TMEM
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B2_STAGE_BYTES + (MX ? SF_STAGE_BYTES : 0);
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 2 * 16384 + 1024 + 256;
+};
+constexpr uint32_t SF_TMEM_COL = 2 * BN - 16;  // 4 columns of X scales, then 8 of Wt scales (MX has one accumulator: 256..511 are free)
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
@@ -888,9 +900,31 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
 }
 
+// 128 rows x 4 scale bytes (512 bytes of shared memory, rows of 16 bytes, 8-row groups 128 bytes apart) into
+// four TMEM columns of every lane quarter, in both CTAs of the pair
+__device__ __forceinline__ void sf_to_tmem_pair(uint32_t tmem_col, uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)(128u >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;            // descriptor version; no swizzle
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(d) : "memory");
+}
+__device__ __forceinline__ void umma_mx_pair(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tmem_sfa,
+                                             uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_c),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
+template <bool MX>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ CUtensorMap map_y, GemmParams p) {
+                        const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_sfa,
+                        const __grid_constant__ CUtensorMap map_sfb, GemmParams p) {
+  constexpr int STAGES2 = PairCfg<MX>::STAGES;
+  constexpr int NBUF = PairCfg<MX>::NBUF;
   extern __shared__ unsigned char smem_raw[];
   bool copy_ok = true;
   if ((int)blockIdx.x < p.copy_ctas) {
@@ -903,8 +937,9 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;
   unsigned char* sB = smem + (size_t)STAGES2 * A_STAGE_BYTES;
-  unsigned char* sEpi = smem + (size_t)STAGES2 * (A_STAGE_BYTES + B2_STAGE_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_SLABS * EPI_SLAB_BYTES);
+  unsigned char* sEpi = smem + (size_t)STAGES2 * (A_STAGE_BYTES + B2_STAGE_BYTES);  // 1024-aligned: the stores are swizzled
+  unsigned char* sSF = sEpi + EPI_SLABS * EPI_SLAB_BYTES;                           // MX only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + (MX ? (size_t)STAGES2 * SF_STAGE_BYTES : 0));
   // bars: [0,S) full (used in the even CTA), [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty (even CTA),
   // then TILE_RING tile slots
   __shared__ uint32_t s_tmem_base;
@@ -947,8 +982,8 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
   const int m_blocks = p.M / (2 * BM), n_blocks = p.N / BN;
   const int total = m_blocks * n_blocks;
-  const int k_iters = p.K * 2 / BKB;
-  const int kelems = BKB / 2;
+  const int k_iters = p.K * p.elem_bytes / BKB;
+  const int kelems = BKB / p.elem_bytes;
   volatile int* abort = &s_abort;
   // The even CTA draws the pair's next tile from the global counter and puts it into both CTAs'
   // rings (its own, and the partner's through distributed shared memory).
@@ -987,9 +1022,14 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         for (int k = 0; k < k_iters; ++k) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort, p.timeout_ns)) break;
           const uint32_t full_leader = map_to_cta(full_bar(s), 0);
-          if (leader) mbar_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + B2_STAGE_BYTES));
+          if (leader) mbar_expect_tx(full_bar(s), 2 * PairCfg<MX>::STAGE_BYTES);
           tma_load_2d_pair(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_a, full_leader, k * kelems, mb * 2 * BM + (int)rank * BM);
           tma_load_2d_pair(smem_u32(sB + (size_t)s * B2_STAGE_BYTES), &map_b, full_leader, k * kelems, nb * BN + (int)rank * (BN / 2));
+          if (MX) {  // this CTA's X scales of the step, and the whole tile's Wt scales (each CTA needs all 256 in its TMEM)
+            const uint32_t sf = smem_u32(sSF + (size_t)s * SF_STAGE_BYTES);
+            tma_load_2d_pair(sf, &map_sfa, full_leader, 0, (mb * 2 + (int)rank) * k_iters + k);
+            tma_load_2d_pair(sf + 512, &map_sfb, full_leader, 0, k * (p.N / 128) + nb * 2);
+          }
           if (++s == STAGES2) s = 0, ph ^= 1u;
         }
       }
@@ -1001,13 +1041,16 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   } else if (warp == 1) {
     // ---------------- MMA: the even CTA issues for the pair ----------------
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      // bf16: D fp32 (bit 4), A and B bf16 (bits 7, 10). MX: A and B e4m3 (zero), scales UE8M0 (bit 23); the
+      // 32-element block of the K-step goes into bits 29..30 (X scales) and 4..5 (Wt scales) per instruction.
+      constexpr uint32_t idesc = (MX ? (1u << 23) : ((1u << 4) | (1u << 7) | (1u << 10))) | ((uint32_t)(BN >> 3) << 17) |
+                                 ((uint32_t)((2 * BM) >> 4) << 24);
       int s = 0;
       uint32_t ph = 0;
       for (int it = 0;; ++it) {
         if (next_tile(it) >= total || *abort) break;
-        const int buf = it & 1;
-        const uint32_t tph = (uint32_t)(it >> 1) & 1u;
+        const int buf = it % NBUF;
+        const uint32_t tph = (uint32_t)(it / NBUF) & 1u;
         if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abort, p.timeout_ns)) break;
         tc_fence_after();
         const uint32_t tacc = tmem_base + (uint32_t)buf * BN;
@@ -1016,9 +1059,22 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           tc_fence_after();
           const uint32_t a0 = smem_u32(sA + (size_t)s * A_STAGE_BYTES);
           const uint32_t b0 = smem_u32(sB + (size_t)s * B2_STAGE_BYTES);
+          if (MX) {
+            // the step's scale factors into TMEM, in both CTAs; the tensor pipe runs them before the MMAs below
+            const uint32_t sf = smem_u32(sSF + (size_t)s * SF_STAGE_BYTES);
+            const uint32_t tsf = tmem_base + SF_TMEM_COL;
+            sf_to_tmem_pair(tsf, sf);
+            sf_to_tmem_pair(tsf + 4, sf + 512);
+            sf_to_tmem_pair(tsf + 8, sf + 1024);
 #pragma unroll
-          for (int kk = 0; kk < BKB / 32; ++kk)
-            umma_pair(tacc, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), idesc, (uint32_t)((k | kk) != 0));
+            for (int kk = 0; kk < BKB / 32; ++kk)
+              umma_mx_pair(tacc, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32),
+                           idesc | ((uint32_t)kk << 29) | ((uint32_t)kk << 4), tsf, tsf + 4, (uint32_t)((k | kk) != 0));
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < BKB / 32; ++kk)
+              umma_pair(tacc, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), idesc, (uint32_t)((k | kk) != 0));
+          }
           // the stage is free in both CTAs once these MMAs have read it
           umma_commit_pair(empty_bar(s));
           umma_commit_pair(map_to_cta(empty_bar(s), 1));
@@ -1043,8 +1099,8 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       if (epi_vote_any(1, tile >= total)) break;
       int mb, nb;
       tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
-      const int buf = it & 1;
-      const uint32_t tph = (uint32_t)(it >> 1) & 1u;
+      const int buf = it % NBUF;
+      const uint32_t tph = (uint32_t)(it / NBUF) & 1u;
       const bool got = !*abort && mbar_wait(tfull_bar(buf), tph, abort, p.timeout_ns);
       if (epi_vote_any(1, !got)) break;
       tc_fence_after();
@@ -1134,6 +1190,20 @@ static int make_map(CUtensorMap* m, const void* base, int elem_bytes, uint64_t r
   return r == CUDA_SUCCESS ? 0 : EUX_ERR_BAD_ARG;
 }
 
+// scale factors of the MX variant: `chunks` blocks of 512 bytes, `box_chunks` of them per load, no swizzle
+static int make_map_sf(CUtensorMap* m, const void* base, uint64_t chunks, uint32_t box_chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return EUX_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {128, chunks};  // 128 words of 4 bytes
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, box_chunks};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : EUX_ERR_BAD_ARG;
+}
+
 }  // namespace eux
 
 using namespace eux;
@@ -1147,7 +1217,9 @@ extern "C" int eux_gemm_num_sms(void) {
 
 extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   if (!d || !d->x_stage || !d->w_t || !d->y_dst || !d->sched || !d->panel_flags) return EUX_ERR_BAD_ARG;
-  const int bn = d->fp8 ? BN8 : BN;
+  const bool mx = d->fp8 == 2;  // e4m3 with one UE8M0 scale per 32 elements, scaled by the tensor core
+  if (mx && (d->M % (2 * BM) || d->N % BN)) return EUX_ERR_BAD_ARG;
+  const int bn = mx ? BN : d->fp8 ? BN8 : BN;
   if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->M % BM || d->N % bn) return EUX_ERR_BAD_ARG;
   const int eb = d->fp8 ? 1 : 2;
   if ((d->K * eb) % BKB) return EUX_ERR_BAD_ARG;
@@ -1192,12 +1264,15 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   }
   // bf16 with M in whole 256-row blocks can run on CTA pairs (bit 0 of the descriptor's flags)
   const bool want_pairs = (d->flags & EUX_GEMM_FLAG_CTA_PAIRS) != 0;
-  if (want_pairs && !d->fp8 && d->M % (2 * BM) == 0) {
-    static bool attr2_set[64] = {false};
-    if (!attr2_set[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(remote_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM2_SMEM);
+  if (mx || (want_pairs && !d->fp8 && d->M % (2 * BM) == 0)) {
+    static bool attr2_set[64][2] = {{false}};
+    if (!attr2_set[dev][mx ? 1 : 0]) {
+      cudaError_t e = mx ? cudaFuncSetAttribute(remote_gemm_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)PairCfg<true>::SMEM)
+                         : cudaFuncSetAttribute(remote_gemm_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)PairCfg<false>::SMEM);
       if (e != cudaSuccess) return (int)e;
-      attr2_set[dev] = true;
+      attr2_set[dev][mx ? 1 : 0] = true;
     }
     CUtensorMap mb2;  // this CTA's half of a Wt tile: 128 rows
     if (int rc = make_map(&mb2, d->w_t, eb, (uint64_t)d->N, (uint64_t)d->K, BN / 2)) return rc;
@@ -1213,7 +1288,14 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
     // every pair computes (the copying ones after their transfer), and they all have to be resident:
     // pairs that copy must not wait for a slot behind pairs that wait for their panels
     const int pairs = pull ? sms / 2 : (tiles2 < sms / 2 ? tiles2 : sms / 2);
-    remote_gemm_2cta_kernel<<<2 * pairs, GEMM_THREADS, GEMM2_SMEM, (cudaStream_t)stream>>>(ma, mb2, my, p);
+    if (mx) {
+      CUtensorMap msa, msb;
+      if (int rc = make_map_sf(&msa, p.x_scale_stage, (uint64_t)(d->M / 128) * (d->K / 128), 1)) return rc;
+      if (int rc = make_map_sf(&msb, d->w_scale, (uint64_t)(d->N / 128) * (d->K / 128), 2)) return rc;
+      remote_gemm_2cta_kernel<true><<<2 * pairs, GEMM_THREADS, PairCfg<true>::SMEM, (cudaStream_t)stream>>>(ma, mb2, my, msa, msb, p);
+    } else {
+      remote_gemm_2cta_kernel<false><<<2 * pairs, GEMM_THREADS, PairCfg<false>::SMEM, (cudaStream_t)stream>>>(ma, mb2, my, ma, ma, p);
+    }
     return (int)cudaGetLastError();
   }
   const int tiles = (d->M / BM) * (d->N / bn);

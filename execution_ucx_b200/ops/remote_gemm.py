@@ -141,6 +141,84 @@ class RemoteGemmFp8:
             raise RuntimeError(f"remote gemm (fp8) status code={s & 0xff} where={s >> 8}")
 
 
+def quantize_mx(x: torch.Tensor):
+    """X[R,K] -> (e4m3 values [R,K], UE8M0 exponents [R,K/32] as uint8): the OCP MXFP8 form, one
+    power-of-two scale per 32 elements along K, chosen so that the block's largest value fits e4m3."""
+    r, k = x.shape
+    g = x.float().view(r, k // 32, 32)
+    amax = g.abs().amax(-1).clamp_min(2.0 ** -100)
+    e = torch.ceil(torch.log2(amax * (1.0 / 448.0))).clamp(-127, 127)
+    q = (g * torch.exp2(-e).unsqueeze(-1)).to(torch.float8_e4m3fn).view(r, k)
+    return q.contiguous(), (e + 127).to(torch.uint8).contiguous()
+
+
+def mx_scale_chunks(sf: torch.Tensor, k_step_major: bool) -> torch.Tensor:
+    """Exponents [R,K/32] -> the 512-byte chunks the kernel loads: one chunk per 128 rows and 128
+    elements of K, byte (r % 32) * 16 + (r // 32) * 4 + j for row r and 32-element block j. Chunks are
+    ordered row block first (X: a panel's scales are contiguous) or K-step first (Wt: the two chunks of
+    a 256-row tile are adjacent)."""
+    r, kb = sf.shape
+    v = sf.view(r // 128, 4, 32, kb // 4, 4)            # [row block, r // 32, r % 32, K-step, j]
+    v = v.permute(3, 0, 2, 1, 4) if k_step_major else v.permute(0, 3, 2, 1, 4)
+    return v.contiguous().view(-1)
+
+
+def mx_dequantized_reference(xq, xsf, wq_t, wsf) -> torch.Tensor:
+    """fp32 statement of the MX product: (xq * 2^(xsf-127)) @ (wq * 2^(wsf-127))^T."""
+    def deq(q, sf):
+        r, k = q.shape
+        return (q.float().view(r, k // 32, 32) * torch.exp2(sf.float() - 127).unsqueeze(-1)).view(r, k)
+    return deq(xq, xsf) @ deq(wq_t, wsf).t()
+
+
+class RemoteGemmMx:
+    """MXFP8 variant: e4m3 values with one UE8M0 scale per 32 elements of K on both operands, applied by
+    the tensor core (tcgen05.mma kind::mxf8f6f4.block_scale) on pairs of CTAs. The caller sends X's values
+    and its scale chunks (``mx_scale_chunks(sf, False)``); the weight is resident. M and N in multiples
+    of 256, K of 128."""
+
+    def __init__(self, w: torch.Tensor, max_m: int):
+        assert w.dim() == 2 and w.shape[0] % 128 == 0 and w.shape[1] % 256 == 0 and max_m % 256 == 0
+        self.K, self.N = w.shape
+        self.w_q_t, self.w_sf = quantize_mx(w.t().contiguous())
+        self.w_chunks = mx_scale_chunks(self.w_sf, True)
+        dev = w.device
+        self.max_m = max_m
+        self.x_stage = torch.empty(max_m, self.K, dtype=torch.uint8, device=dev)
+        self.x_scale_stage = torch.empty(max_m * self.K // 32, dtype=torch.uint8, device=dev)
+        self.panel_flags = torch.zeros(max_m // 128, dtype=torch.int32, device=dev)
+        self.sched = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def __call__(self, xq_ptr: int, xs_ptr: int, m: int, y_ptr: int, *, x_is_local: bool, done_flag_ptr: int = 0,
+                 done_value: int = 0, copy_ctas: int = 0, timeout_ns: int = 2_000_000_000,
+                 copy_warps: Optional[bool] = None, head_blocks: Optional[int] = None) -> None:
+        global _launches
+        if m > self.max_m or m % 256:
+            raise ValueError("m exceeds the staging buffer or is not a multiple of 256")
+        d = _native.GemmDesc()
+        if copy_warps is None:
+            copy_warps = copy_ctas == 0
+        d.flags = (2 if copy_warps else 0) | (0 if head_blocks is None else ((head_blocks + 1) & 0xff) << 8)
+        d.x_src = xq_ptr
+        d.x_stage = xq_ptr if x_is_local else self.x_stage.data_ptr()
+        d.x_scale = xs_ptr
+        d.x_scale_stage = xs_ptr if x_is_local else self.x_scale_stage.data_ptr()
+        d.w_t, d.w_scale, d.y_dst = self.w_q_t.data_ptr(), self.w_chunks.data_ptr(), y_ptr
+        d.M, d.N, d.K, d.fp8 = m, self.N, self.K, 2
+        d.panel_flags, d.sched = self.panel_flags.data_ptr(), self.sched.data_ptr()
+        d.done_flag, d.done_value = done_flag_ptr or None, done_value
+        d.wait_timeout_ns, d.status, d.copy_ctas = timeout_ns, self.status.data_ptr(), copy_ctas
+        _native.check(_native.load().eux_gemm_launch(C.byref(d), C.c_void_p(_native.current_stream_ptr())),
+                      "eux_gemm_launch(mx)")
+        _launches += 1
+
+    def check_status(self) -> None:
+        s = int(self.status.item())
+        if s:
+            raise RuntimeError(f"remote gemm (mx) status code={s & 0xff} where={s >> 8}")
+
+
 def smoke(device) -> None:
     x = torch.randn(256, 256, device=device).to(torch.bfloat16)
     w = (torch.randn(256, 512, device=device) * 0.05).to(torch.bfloat16)
