@@ -260,7 +260,7 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
             tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
             # denominator: the measured cuBLAS bf16 burst; fp8 is reported against the same figure (no measured fp8 peak)
             t_compute = 2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12) * 1e3
-            x_bytes = m * k * (1 if fp8 else 2) + (m * (k // 128) * 4 if fp8 else 0)
+            x_bytes = m * k * (1 if fp8 else 2) + (m * (k // 128) * 4 if fp8 else 0)  # MX scales: m * k / 32, the same count
             t_link = x_bytes / (timing.NVLINK_PEER_GBS * 1e9) * 1e3 if world > 1 else 0.0
             err = float((w.y[:256].float() - w.reference_rows(256)).abs().max()) if world == 1 else None
             w.close()
@@ -371,6 +371,7 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
     guarded("tensor_rpc_sweep", rpc_sweep)
     guarded("remote_gemm_rpc_bf16", gemm(False))
     guarded("remote_gemm_rpc_fp8_block_scaled", gemm(True))
+    guarded("remote_gemm_rpc_mxfp8", gemm("mx"))
     guarded("remote_gemm_rpc_bf16_all_peers", gemm_all_peers)
     guarded("moe_bf16", moe(False))
     guarded("moe_fp8", moe(True))

@@ -1,7 +1,7 @@
 """Small, self-ending cases of each data-plane kernel, for profiler captures.
 
     python -m execution_ucx_b200.models.profile_case --kernel gemm
-    python -m execution_ucx_b200.models.profile_case --kernel gemm_fp8
+    python -m execution_ucx_b200.models.profile_case --kernel gemm_fp8   (or gemm_mx)
     python -m execution_ucx_b200.models.profile_case --kernel xfer
     python -m execution_ucx_b200.models.profile_case --kernel moe
 
@@ -17,7 +17,7 @@ import torch
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=["gemm", "gemm_fp8", "xfer", "moe", "moe_fp8"], required=True)
+    ap.add_argument("--kernel", choices=["gemm", "gemm_fp8", "gemm_mx", "xfer", "moe", "moe_fp8"], required=True)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -42,6 +42,19 @@ def main() -> None:
         y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         for _ in range(args.iters):
             g(xq.data_ptr(), xs.data_ptr(), m, y.data_ptr(), x_is_local=True)
+        torch.cuda.synchronize()
+        g.check_status()
+    elif args.kernel == "gemm_mx":
+        from ..ops.remote_gemm import RemoteGemmMx, quantize_mx, mx_scale_chunks
+        m, n, k = 4096, 4096, 4096
+        x = torch.randn(m, k, device=dev)
+        w = torch.randn(k, n, device=dev) * 0.02
+        g = RemoteGemmMx(w, m)
+        xq, xsf = quantize_mx(x)
+        xc = mx_scale_chunks(xsf, False)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        for _ in range(args.iters):
+            g(xq.data_ptr(), xc.data_ptr(), m, y.data_ptr(), x_is_local=True)
         torch.cuda.synchronize()
         g.check_status()
     elif args.kernel == "xfer":

@@ -125,8 +125,9 @@ class RemoteGemmRpc:
     its partner's weight. X lives in the caller's arena; the callee kernel pulls
     it panel by panel while computing and stores Y into the caller's arena.
     With ``fp8`` the caller sends e4m3 rows with one fp32 scale per 128 elements
-    and the resident weight is e4m3 with 128x128 block scales. A single rank
-    has nothing to pull: its kernel reads X in place."""
+    and the resident weight is e4m3 with 128x128 block scales; with ``fp8="mx"``
+    both operands are MXFP8 (a power-of-two scale per 32 elements, applied by the
+    tensor core). A single rank has nothing to pull: its kernel reads X in place."""
 
     def __init__(self, group: PeerGroup, m: int, n: int, k: int, copy_ctas: int = 0, fp8: bool = False):
         self.g, self.m, self.n, self.k, self.copy_ctas, self.fp8 = group, m, n, k, copy_ctas, fp8
@@ -139,7 +140,18 @@ class RemoteGemmRpc:
         g = torch.Generator(device=dev).manual_seed(1234 + group.rank)
         x = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
         self.w = (torch.randn(k, n, device=dev, generator=g) * 0.02).to(torch.bfloat16)
-        if fp8:
+        if fp8 == "mx":
+            xq, xsf = gemm_ops.quantize_mx(x)
+            chunks = gemm_ops.mx_scale_chunks(xsf, False)
+            self.xs_buf = group.alloc(chunks.numel())
+            self.xq = self.x_buf.view(torch.uint8, m * k).view(m, k)
+            self.xs = self.xs_buf.view(torch.uint8, chunks.numel())
+            self.xq.copy_(xq.view(torch.uint8))
+            self.xs.copy_(chunks)
+            self.x_sf = xsf
+            self.gemm = gemm_ops.RemoteGemmMx(self.w.float(), m)
+            self.x = x
+        elif fp8:
             xq, xs = gemm_ops.quantize_rows_1x128(x)
             self.xs_buf = group.alloc(m * (k // 128) * 4)
             self.xq = self.x_buf.view(torch.uint8, m * k).view(m, k)
@@ -176,6 +188,9 @@ class RemoteGemmRpc:
 
     def reference_rows(self, rows: int = 256) -> torch.Tensor:
         """fp32 reference of the first rows (single rank: X and W are both local)."""
+        if self.fp8 == "mx":
+            return gemm_ops.mx_dequantized_reference(self.xq[:rows].view(torch.float8_e4m3fn), self.x_sf[:rows],
+                                                     self.gemm.w_q_t, self.gemm.w_sf)
         if self.fp8:
             return gemm_ops.dequantized_reference(self.xq[:rows].view(torch.float8_e4m3fn), self.xs[:rows],
                                                   self.gemm.w_q_t, self.gemm.w_scale)
