@@ -1105,6 +1105,45 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       if (epi_vote_any(1, !got)) break;
       tc_fence_after();
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)buf * BN;
+      if (MX) {
+        // One accumulator buffer: the next tile's MMAs wait for this epilogue, so the whole row comes out of
+        // TMEM first, rounded to bf16 in registers (128 words per thread), and the buffer is handed back
+        // before anything is written; the slabs then leave while the tensor pipe works on the next tile.
+        uint32_t pk[BN / 2];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tbase + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            __nv_bfloat162 q = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+            pk[c * 16 + e] = *reinterpret_cast<uint32_t*>(&q);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_cta(tempty_bar(buf), 0));
+#pragma unroll
+        for (int sl = 0; sl < BN / 64; ++sl, ++slab) {
+          const uint32_t sbuf = epi0 + (slab & 1u) * EPI_SLAB_BYTES;
+          if (elected) bulk_wait_read_1();
+          epi_bar_sync(1);
+#pragma unroll
+          for (int chunk = 0; chunk < 8; ++chunk) {
+            const uint4 o = make_uint4(pk[sl * 32 + chunk * 4], pk[sl * 32 + chunk * 4 + 1], pk[sl * 32 + chunk * 4 + 2],
+                                       pk[sl * 32 + chunk * 4 + 3]);
+            st_shared_u4(sbuf + (uint32_t)row_local * 128u + (uint32_t)((chunk ^ (row_local & 7)) * 16), o);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          epi_bar_sync(1);
+          if (elected) {
+            tma_store_2d(&map_y, sbuf, nb * BN + sl * 64, mb * 2 * BM + (int)rank * BM);
+            bulk_commit();
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int sl = 0; sl < BN / 64; ++sl, ++slab) {
         const uint32_t sbuf = epi0 + (slab & 1u) * EPI_SLAB_BYTES;
