@@ -1,6 +1,6 @@
 """Small, self-ending cases of each data-plane kernel, for profiler captures.
 
-    python -m execution_ucx_b200.models.profile_case --kernel gemm
+    python -m execution_ucx_b200.models.profile_case --kernel gemm        (CTA pairs; gemm_1cta: one CTA per tile)
     python -m execution_ucx_b200.models.profile_case --kernel gemm_fp8   (or gemm_mx)
     python -m execution_ucx_b200.models.profile_case --kernel xfer
     python -m execution_ucx_b200.models.profile_case --kernel moe
@@ -17,11 +17,11 @@ import torch
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=["gemm", "gemm_fp8", "gemm_mx", "xfer", "moe", "moe_fp8"], required=True)
+    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "moe", "moe_fp8"], required=True)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
-    if args.kernel == "gemm":
+    if args.kernel in ("gemm", "gemm_1cta"):
         from ..ops.remote_gemm import RemoteGemm
         m, n, k = 4096, 4096, 4096  # 3 x 32 MiB operands/result: > L2 in total, milliseconds per launch
         x = torch.randn(m, k, device=dev).to(torch.bfloat16)
@@ -29,7 +29,7 @@ def main() -> None:
         g = RemoteGemm(w, m)
         y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         for _ in range(args.iters):
-            g(x.data_ptr(), m, y.data_ptr(), x_is_local=True)
+            g(x.data_ptr(), m, y.data_ptr(), x_is_local=True, cta_pairs=args.kernel == "gemm")
         torch.cuda.synchronize()
         g.check_status()
     elif args.kernel == "gemm_fp8":
