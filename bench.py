@@ -238,17 +238,26 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
         return {"timing": "device globaltimer inside one persistent kernel per GPU", "rows": rows}
 
     def rpc_sweep():
+        """Round trips are serialised by their data, so a sample times a run of them between two events
+        and divides: the ranks' launch skew (tens of microseconds after a host barrier) would otherwise
+        be most of a small message's figure. L2 is flushed between samples."""
         rows = []
         for lg in (12, 16, 20, 24, 28):
             n = 1 << lg
             s = src[: n // 2]
-            ts = timing.time_cuda(lambda: rpc.step(s), iters=20, warmup=3, flush=flush if n < (256 << 20) else None,
-                                  before=group.barrier if world > 1 else None)
+            inner = 32 if lg <= 20 else (8 if lg == 24 else 2)
+
+            def run_steps():
+                for _ in range(inner):
+                    rpc.step(s)
+            ts = timing.time_cuda(run_steps, iters=12, warmup=2, flush=flush, before=group.barrier if world > 1 else None)
+            ts = [t / inner for t in ts]
             p50 = group.max_over_ranks(timing.percentile(ts, 50)) * 1e3
             p99 = group.max_over_ranks(timing.percentile(ts, 99)) * 1e3
-            rows.append({"bytes": n, "rtt_p50_us": round(p50, 2), "rtt_p99_us": round(p99, 2),
+            rows.append({"bytes": n, "steps_per_sample": inner, "rtt_p50_us": round(p50, 2), "rtt_p99_us": round(p99, 2),
                          "one_way_GBps": round(n / (p50 / 2 * 1e-6) / 1e9, 2)})
-        return {"timing": "CUDA events around 3 launches (push, handler+push back, completion wait)", "rows": rows}
+        return {"timing": "CUDA events around a run of steps, one launch per step and rank (request push, handler + push "
+                          "back, completion wait as phases of one kernel), divided by the number of steps", "rows": rows}
 
     def gemm(fp8):
         def run():

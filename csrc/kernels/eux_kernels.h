@@ -90,6 +90,11 @@ EUX_API int eux_xfer_launch(const eux_xfer_desc* d, uint32_t* scratch_counter, i
 /* Same contract as eux_xfer_launch for a dense same-type copy of 16-byte aligned buffers, moved by the
  * bulk-copy engine (TMA) through shared memory instead of by register loads and stores. */
 EUX_API int eux_xfer_bulk_launch(const eux_xfer_desc* desc, uint32_t* scratch_counter, int max_ctas, void* stream);
+/* One echo step of a tensor RPC in one launch: `req` (push to the partner + flag), then `resp` (wait for the
+   partner's request, handler, push back + flag), then `done` (wait for the response flag; nothing is copied).
+   Dense, 16-byte aligned, one dtype; scratch3: three zeroed words, left zero. */
+EUX_API int eux_xfer_rpc_step_launch(const eux_xfer_desc* req, const eux_xfer_desc* resp, const eux_xfer_desc* done,
+                                     uint32_t* scratch3, int max_ctas, void* stream);
 EUX_API int eux_xfer_batch_launch(const eux_xfer_desc* descs_dev, int n, void* stream);
 
 /* Device-driven ping-pong between two GPUs (or loopback on one): see

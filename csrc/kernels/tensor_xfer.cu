@@ -227,36 +227,73 @@ __global__ void __launch_bounds__(kBulkThreads) xfer_bulk_kernel(XferArgs a) {
 
 // Dense typed path: 8 elements per step, cast + handler fused.
 template <typename S, typename D>
+__device__ __forceinline__ void typed_body(const eux_xfer_desc& d) {
+  const S* src = reinterpret_cast<const S*>(d.src);
+  D* dst = reinterpret_cast<D*>(d.dst);
+  const uint64_t n8 = d.n_elems >> 3;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
+  const int op = d.op;
+  const float arg = d.op_arg;
+  using PS = typename PackT<(8 * sizeof(S) >= 32 ? 16 : 8 * sizeof(S))>::type;
+  using PD = typename PackT<(8 * sizeof(D) >= 32 ? 16 : 8 * sizeof(D))>::type;
+  constexpr int NS = 8 * sizeof(S) / sizeof(PS);
+  constexpr int ND = 8 * sizeof(D) / sizeof(PD);
+  for (uint64_t i = tid; i < n8; i += nthreads) {
+    alignas(16) S sv[8];
+    alignas(16) D dv[8];
+#pragma unroll
+    for (int k = 0; k < NS; ++k) reinterpret_cast<PS*>(sv)[k] = __ldcg(reinterpret_cast<const PS*>(src + i * 8) + k);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dv[k] = Elem<D>::from(apply_op(Elem<S>::to(sv[k]), op, arg));
+#pragma unroll
+    for (int k = 0; k < ND; ++k) reinterpret_cast<PD*>(dst + i * 8)[k] = reinterpret_cast<PD*>(dv)[k];
+  }
+  for (uint64_t e = (n8 << 3) + tid; e < d.n_elems; e += nthreads)
+    dst[e] = Elem<D>::from(apply_op(Elem<S>::to(src[e]), op, arg));
+}
+
+template <typename S, typename D>
 __global__ void __launch_bounds__(kXferThreads) xfer_typed_kernel(XferArgs a) {
   const eux_xfer_desc& d = a.d;
   bool ok = cta_wait_arrival(d);
-  if (ok) {
-    const S* src = reinterpret_cast<const S*>(d.src);
-    D* dst = reinterpret_cast<D*>(d.dst);
-    const uint64_t n8 = d.n_elems >> 3;
-    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
-    const int op = d.op;
-    const float arg = d.op_arg;
-    using PS = typename PackT<(8 * sizeof(S) >= 32 ? 16 : 8 * sizeof(S))>::type;
-    using PD = typename PackT<(8 * sizeof(D) >= 32 ? 16 : 8 * sizeof(D))>::type;
-    constexpr int NS = 8 * sizeof(S) / sizeof(PS);
-    constexpr int ND = 8 * sizeof(D) / sizeof(PD);
-    for (uint64_t i = tid; i < n8; i += nthreads) {
-      alignas(16) S sv[8];
-      alignas(16) D dv[8];
-#pragma unroll
-      for (int k = 0; k < NS; ++k)
-        reinterpret_cast<PS*>(sv)[k] = __ldcg(reinterpret_cast<const PS*>(src + i * 8) + k);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) dv[k] = Elem<D>::from(apply_op(Elem<S>::to(sv[k]), op, arg));
-#pragma unroll
-      for (int k = 0; k < ND; ++k) reinterpret_cast<PD*>(dst + i * 8)[k] = reinterpret_cast<PD*>(dv)[k];
-    }
-    for (uint64_t e = (n8 << 3) + tid; e < d.n_elems; e += nthreads)
-      dst[e] = Elem<D>::from(apply_op(Elem<S>::to(src[e]), op, arg));
-  }
+  if (ok) typed_body<S, D>(d);
   cta_publish(d, a.counter, ok);
+}
+
+// One tensor-RPC echo step of a rank in a single launch: push the request into the partner's arena and
+// publish its flag; as the partner's server, wait for its request, apply the handler and push the response
+// back; as client again, wait for the response. Each phase is what xfer_bytes_kernel / xfer_typed_kernel
+// do in a launch of their own. The partner runs the same kernel on its GPU at the same time; no CTA waits
+// for a CTA of its own grid (a phase's flag is published by whichever CTA finishes it last), and the grid
+// is at most one CTA per SM, so every CTA is resident. All tensors dense, 16-byte aligned, of one dtype.
+struct RpcStepArgs {
+  eux_xfer_desc req, resp, done;
+  uint32_t* counter;  // three words
+};
+template <typename S>
+__device__ __forceinline__ void rpc_phase(const eux_xfer_desc& d, uint32_t* counter) {
+  bool ok = cta_wait_arrival(d);
+  if (ok && d.n_elems) {
+    if (d.op == EUX_OP_NONE) {
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src);
+      unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
+      const uint64_t nbytes = d.n_elems * (uint64_t)dtype_size(d.src_dtype);
+      if (((((uintptr_t)src) | ((uintptr_t)dst)) & 31u) == 0) copy_bytes_grid<true>(src, dst, nbytes, blockIdx.x, gridDim.x);
+      else copy_bytes_grid<false>(src, dst, nbytes, blockIdx.x, gridDim.x);
+    } else
+      typed_body<S, S>(d);
+  }
+  cta_publish(d, counter, ok);
+}
+template <typename S>
+__global__ void __launch_bounds__(kXferThreads) xfer_rpc_step_kernel(RpcStepArgs a) {
+  rpc_phase<S>(a.req, a.counter);
+  rpc_phase<S>(a.resp, a.counter + 1);
+  if (blockIdx.x == 0) {  // the completion: one CTA watches the response flag
+    const bool ok = cta_wait_arrival(a.done);
+    (void)ok;
+  }
 }
 
 // Strided gather (and the catch-all for unaligned bases): one element per step.
@@ -495,6 +532,35 @@ extern "C" int eux_xfer_launch(const eux_xfer_desc* d, uint32_t* scratch_counter
     grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
     if (grid > 1 && !scratch_counter) return EUX_ERR_BAD_ARG;
     xfer_strided_kernel<<<grid, kXferThreads, 0, st>>>(a);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int eux_xfer_rpc_step_launch(const eux_xfer_desc* req, const eux_xfer_desc* resp, const eux_xfer_desc* done,
+                                        uint32_t* scratch3, int max_ctas, void* stream) {
+  if (!req || !resp || !done || !scratch3 || !req->src || !req->dst || !resp->src || !resp->dst) return EUX_ERR_BAD_ARG;
+  const eux_xfer_desc* ds[2] = {req, resp};
+  for (const eux_xfer_desc* d : ds) {
+    if (d->ndim != 0 || d->src_dtype != d->dst_dtype) return EUX_ERR_BAD_ARG;
+    if ((((uintptr_t)d->src) | ((uintptr_t)d->dst)) & 15u) return EUX_ERR_BAD_ARG;
+    if (d->op != EUX_OP_NONE && d->src_dtype == EUX_DT_BYTES) return EUX_ERR_BAD_ARG;
+  }
+  if (req->src_dtype != resp->src_dtype) return EUX_ERR_BAD_ARG;
+  const int sms = num_sms();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;  // every CTA resident: see the kernel
+  const uint64_t bytes = req->n_elems * (uint64_t)dtype_size(req->src_dtype);
+  const uint64_t want = (bytes + (uint64_t)kXferThreads * 64 - 1) / ((uint64_t)kXferThreads * 64);
+  const int grid = (int)(want < 1 ? 1 : (want > (uint64_t)max_ctas ? max_ctas : want));
+  RpcStepArgs a{*req, *resp, *done, scratch3};
+  a.done.n_elems = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (req->src_dtype) {
+    case EUX_DT_F32: xfer_rpc_step_kernel<float><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_F16: xfer_rpc_step_kernel<__half><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_BF16: xfer_rpc_step_kernel<__nv_bfloat16><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_F8E4M3: xfer_rpc_step_kernel<__nv_fp8_e4m3><<<grid, kXferThreads, 0, st>>>(a); break;
+    case EUX_DT_BYTES: xfer_rpc_step_kernel<float><<<grid, kXferThreads, 0, st>>>(a); break;  // no handler: bytes only
+    default: return EUX_ERR_BAD_ARG;
   }
   return (int)cudaGetLastError();
 }

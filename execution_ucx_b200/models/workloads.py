@@ -28,11 +28,15 @@ class TensorRpcEcho:
     server's receive arena and publishes a sequence flag; the server's handler
     kernel (waiting on that flag, bounded) applies the handler and pushes the
     result straight back into the client's arena; the client's completion kernel
-    waits for the echo flag. Every rank is client and server for its partner."""
+    waits for the echo flag. Every rank is client and server for its partner.
+    With ``fused`` (the default) the three roles of a step run as the phases of one kernel launch per
+    rank; a strided or differently typed source takes the three launches."""
 
     def __init__(self, group: PeerGroup, max_bytes: int, dtype=torch.bfloat16, handler_op: int = tx.OP_NONE,
-                 handler_arg: float = 0.0):
+                 handler_arg: float = 0.0, fused: bool = True):
         self.g, self.dtype = group, dtype
+        self.fused = fused   # one launch per step where the source allows it (dense, arena dtype, 16-byte aligned)
+        self._steps = {}     # prepared descriptors per (source address, size)
         self.peer = _partner(group.rank, group.world)
         self.max_bytes = max_bytes
         # arena layout per rank: [request slot | response slot]
@@ -55,6 +59,20 @@ class TensorRpcEcho:
         assert nbytes <= self.max_bytes
         self.seq += 1
         p = self.peer
+        if self.fused and src.is_contiguous() and src.dtype == self.dtype and src.data_ptr() % 16 == 0:
+            key = (src.data_ptr(), nbytes)
+            hit = self._steps.get(key)
+            if hit is None:
+                if len(self._steps) >= 64:
+                    self._steps.clear()
+                hit = (tx.RpcEchoStep(src, self.arena.peer_ptrs[p], self.flags.peer_ptrs[p], self.request_view(nbytes),
+                                      self.arena.peer_ptrs[p] + self.max_bytes, self.flags.peer_ptrs[p] + 8,
+                                      self.flags.local_ptr, self.flags.local_ptr + 8, op=self.handler_op,
+                                      op_arg=self.handler_arg, status_ptr=self.status.data_ptr()),
+                       self.response_view(nbytes))
+                self._steps[key] = hit
+            hit[0].launch(self.seq)
+            return hit[1]
         # client: push request into the partner's request slot
         tx.push(src, self.arena.peer_ptrs[p], dst_dtype=self.dtype, flag_ptr=self.flags.peer_ptrs[p], flag_value=self.seq)
         # server: wait for the partner's request, run the handler, push the response back

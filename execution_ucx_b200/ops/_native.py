@@ -80,6 +80,7 @@ def load():
     P, I, U64 = C.c_void_p, C.c_int, C.c_uint64
     lib.eux_xfer_launch.argtypes = [C.POINTER(XferDesc), P, I, P]
     lib.eux_xfer_bulk_launch.argtypes = [C.POINTER(XferDesc), P, I, P]
+    lib.eux_xfer_rpc_step_launch.argtypes = [C.POINTER(XferDesc), C.POINTER(XferDesc), C.POINTER(XferDesc), P, I, P]
     lib.eux_xfer_batch_launch.argtypes = [P, I, P]
     lib.eux_pingpong_launch.argtypes = [C.POINTER(PingPongDesc), I, P]
     lib.eux_ipc_export.argtypes = [P, C.c_char_p]

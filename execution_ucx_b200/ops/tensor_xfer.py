@@ -95,6 +95,55 @@ def push(src: torch.Tensor, dst, *, dst_dtype: Optional[torch.dtype] = None, op:
     _launches += 1
 
 
+def rpc_echo_step(src: torch.Tensor, req_dst_ptr: int, req_flag_ptr: int, request: torch.Tensor, resp_dst_ptr: int,
+                  resp_flag_ptr: int, local_req_flag_ptr: int, local_resp_flag_ptr: int, seq: int, *, op: int = OP_NONE,
+                  op_arg: float = 0.0, status_ptr: int = 0, wait_timeout_ns: int = 0, max_ctas: int = 0) -> None:
+    """One echo step of a tensor RPC in ONE launch: push ``src`` into the partner's request slot and publish
+    ``seq`` there; wait for the partner's request (``request``, this rank's request slot), apply the handler
+    and push the result into the partner's response slot, publishing ``seq``; wait for this rank's response
+    flag. ``src`` and ``request`` are dense, 16-byte aligned and of one dtype. The partner launches the same
+    step on its GPU."""
+    global _launches
+    if not (src.is_cuda and src.is_contiguous() and request.is_contiguous() and src.dtype == request.dtype):
+        raise ValueError("rpc_echo_step() wants dense tensors of one dtype")
+    step = RpcEchoStep(src, req_dst_ptr, req_flag_ptr, request, resp_dst_ptr, resp_flag_ptr, local_req_flag_ptr,
+                       local_resp_flag_ptr, op=op, op_arg=op_arg, status_ptr=status_ptr, wait_timeout_ns=wait_timeout_ns,
+                       max_ctas=max_ctas)
+    step.launch(seq)
+
+
+class RpcEchoStep:
+    """The descriptors of ``rpc_echo_step`` built once: ``launch(seq)`` only writes the sequence number into
+    them and makes the one native call, which is what a small-message loop can afford per step."""
+
+    def __init__(self, src: torch.Tensor, req_dst_ptr: int, req_flag_ptr: int, request: torch.Tensor, resp_dst_ptr: int,
+                 resp_flag_ptr: int, local_req_flag_ptr: int, local_resp_flag_ptr: int, *, op: int = OP_NONE,
+                 op_arg: float = 0.0, status_ptr: int = 0, wait_timeout_ns: int = 0, max_ctas: int = 0):
+        if not (src.is_cuda and src.is_contiguous() and request.is_contiguous() and src.dtype == request.dtype):
+            raise ValueError("rpc_echo_step() wants dense tensors of one dtype")
+        self.req = make_desc(src, req_dst_ptr, src.dtype, OP_NONE, 0.0, req_flag_ptr, 0, 0, 0, wait_timeout_ns, status_ptr)
+        self.resp = make_desc(request, resp_dst_ptr, request.dtype, op, op_arg, resp_flag_ptr, 0, local_req_flag_ptr, 0,
+                              wait_timeout_ns, status_ptr)
+        self.done = make_desc(request[:0], resp_dst_ptr, request.dtype, OP_NONE, 0.0, 0, 0, local_resp_flag_ptr, 0,
+                              wait_timeout_ns, status_ptr)
+        self._keep = (src, request)
+        self._device = src.device
+        self._fn = _native.load().eux_xfer_rpc_step_launch
+        self._refs = (C.byref(self.req), C.byref(self.resp), C.byref(self.done))
+        self._max_ctas = max_ctas
+
+    def launch(self, seq: int) -> None:
+        global _launches
+        self.req.flag_value = seq
+        self.resp.flag_value = seq
+        self.resp.wait_value = seq
+        self.done.wait_value = seq
+        counter = _scratch_counter(self._device)
+        _native.check(self._fn(*self._refs, C.c_void_p(counter.data_ptr() + 16), self._max_ctas,
+                               C.c_void_p(_native.current_stream_ptr())), "eux_xfer_rpc_step_launch")
+        _launches += 1
+
+
 def push_batch(descs, stream_ptr: Optional[int] = None) -> None:
     """Many small transfers in one launch (one CTA per descriptor)."""
     global _launches
@@ -130,4 +179,4 @@ def pingpong(local_buf: torch.Tensor, peer_buf_ptr: int, nbytes: int, local_flag
     _launches += 1
 
 
-__all__ = ["push", "push_batch", "pingpong", "make_desc", "launch_count", "OP_NONE", "OP_ADD", "OP_MUL"]
+__all__ = ["push", "rpc_echo_step", "RpcEchoStep", "push_batch", "pingpong", "make_desc", "launch_count", "OP_NONE", "OP_ADD", "OP_MUL"]

@@ -134,3 +134,31 @@ def test_pingpong_loopback(cuda_device):
     assert int(bar.sum()) == 0
     d = (ts[1:] - ts[:-1]).tolist()
     assert all(x > 0 for x in d)
+
+
+@pytest.mark.parametrize("n,op,arg", [(2048, 0, 0.0), (1 << 20, 0, 0.0), ((1 << 22) + 24, 1, 1.5)])
+def test_rpc_echo_step_single_launch(cuda_device, n, op, arg):
+    """The three roles of an echo step as the phases of one launch, looped back on one GPU: the request lands in
+    the request slot, the handler's result in the response slot, both flags carry the sequence number."""
+    from execution_ucx_b200.ops import tensor_xfer as tx
+    src = torch.randn(n, device=cuda_device).to(torch.bfloat16)
+    req_slot = torch.zeros(n, dtype=torch.bfloat16, device=cuda_device)
+    resp_slot = torch.zeros(n, dtype=torch.bfloat16, device=cuda_device)
+    flags = torch.zeros(2, dtype=torch.int64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    for seq in (1, 2):
+        tx.rpc_echo_step(src, req_slot.data_ptr(), flags.data_ptr(), req_slot, resp_slot.data_ptr(), flags.data_ptr() + 8,
+                         flags.data_ptr(), flags.data_ptr() + 8, seq, op=[tx.OP_NONE, tx.OP_ADD][op], op_arg=arg,
+                         status_ptr=status.data_ptr())
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0 and flags.tolist() == [seq, seq]
+        assert torch.equal(req_slot, src)
+        want = src if op == 0 else (src.float() + arg).to(torch.bfloat16)
+        assert torch.equal(resp_slot, want)
+        resp_slot.zero_()
+    # a request that never arrives ends the step with a status; nothing is published
+    flags.zero_()
+    tx.rpc_echo_step(src, req_slot.data_ptr(), flags.data_ptr() + 8, req_slot, resp_slot.data_ptr(), flags.data_ptr() + 8,
+                     flags.data_ptr(), flags.data_ptr() + 8, 7, status_ptr=status.data_ptr(), wait_timeout_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert int(status[0]) & 0xff == 1 and int(flags[0]) == 0
