@@ -192,6 +192,8 @@ def main() -> int:
             "config": {"model": "axon tensor-RPC echo ping-pong (BASELINE config 2)", "message_bytes": nbytes,
                        "global_batch": world, "seq_len": nbytes // 2, "parallelism": f"p2p-pairs{world}",
                        "pairing": "rank r <-> r^1; n_gpus=1 is a same-GPU loopback through the same kernels",
+                       "scaling_note": "n_gpus=1 moves the bytes inside one GPU's HBM, n_gpus>=2 across NVLink (770 GB/s "
+                                       "measured per direction and GPU): the 1-GPU value is not the base of the multi-GPU ones",
                        "l2": "inputs (1 GiB) larger than L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches, "echo_verified": echo_ok,
             "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained", "source")},

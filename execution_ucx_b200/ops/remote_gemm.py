@@ -220,11 +220,22 @@ class RemoteGemmMx:
 
 
 def smoke(device) -> None:
+    """The pair kernel (bf16) with X pulled by the copy warps, the one-CTA kernel, and the MXFP8 kernel, on tiny shapes."""
     x = torch.randn(256, 256, device=device).to(torch.bfloat16)
     w = (torch.randn(256, 512, device=device) * 0.05).to(torch.bfloat16)
     g = RemoteGemm(w, 256)
     y = torch.empty(256, 512, dtype=torch.bfloat16, device=device)
-    g(x.data_ptr(), 256, y.data_ptr(), x_is_local=True)
+    for kw in (dict(x_is_local=True), dict(x_is_local=False), dict(x_is_local=True, cta_pairs=False)):
+        y.zero_()
+        g(x.data_ptr(), 256, y.data_ptr(), **kw)
+        torch.cuda.synchronize()
+        g.check_status()
+        torch.testing.assert_close(y.float(), x.float() @ w.float(), rtol=2e-2, atol=2e-2)
+    gx = RemoteGemmMx(w.float(), 256)
+    xq, xsf = quantize_mx(x.float())
+    chunks = mx_scale_chunks(xsf, False)
+    y.zero_()
+    gx(xq.data_ptr(), chunks.data_ptr(), 256, y.data_ptr(), x_is_local=True)
     torch.cuda.synchronize()
-    g.check_status()
-    torch.testing.assert_close(y.float(), x.float() @ w.float(), rtol=2e-2, atol=2e-2)
+    gx.check_status()
+    torch.testing.assert_close(y.float(), mx_dequantized_reference(xq, xsf, gx.w_q_t, gx.w_sf), rtol=2e-2, atol=2e-2)
