@@ -52,6 +52,7 @@ struct GemmParams {
   int copy_ctas;
   int head_blocks;  // height of the first tile group in row blocks (0: like the others)
   int copy_warps;   // warps (two per CTA) that copy X beside the GEMM's own warps; 0 when copy CTAs do it
+  uint32_t panel_target;  // count at which a panel of X is complete (0: X is local, nothing to wait for)
   // block-scaled fp8 only
   const float* x_scale_src;   // [M, K/128], caller's (may be peer)
   float* x_scale_stage;       // local copy used by the epilogue (== x_scale_src when X is local)
@@ -112,19 +113,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Tiles in groups of GROUP_M row blocks (row block fastest inside a group) so that one wave of CTAs
-// shares few panels of X and few of W in L2. `head` > 0 makes the first group only `head` blocks tall:
-// while X is still arriving from the caller, the first wave then waits for the first few panels only.
+// shares few panels of X and few of W in L2. While X is still arriving from the caller (`head` > 0) the
+// first groups are shorter, head, head and 2 * head blocks tall: measured on 8192^3 over NVLink, the
+// copy delivers a 256-row block every 8 us at first and every 12 us once the tensor cores are busy, a
+// wave of tiles takes 53 us, and with full-height groups the second and third waves wait for rows that
+// are still on their way.
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int head, int& mb, int& nb) {
   int base = 0;
-  if (head > 0 && head < m_blocks) {
-    if (tile < head * n_blocks) {
-      mb = tile % head;
-      nb = tile / head;
-      return;
+  if (head > 0) {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int h = i < 2 ? head : 2 * head;
+      if (h >= m_blocks - base) break;
+      if (tile < h * n_blocks) {
+        mb = base + tile % h;
+        nb = tile / h;
+        return;
+      }
+      tile -= h * n_blocks;
+      base += h;
     }
-    tile -= head * n_blocks;
-    base = head;
-    m_blocks -= head;
+    m_blocks -= base;
   }
   const int per_group = GROUP_M * n_blocks;
   const int g = tile / per_group, r = tile - g * per_group;
@@ -295,45 +304,60 @@ __device__ __forceinline__ void st_v8_b32(void* ptr, const uint32_t (&v)[8]) {
                : "memory");
 }
 __device__ __forceinline__ void copy_warp_role(const GemmParams& p, uint32_t warp_id, int lane) {
-  constexpr int U = 8;  // pieces in flight per warp: 8 KiB
+  constexpr int U = 8;  // 1 KiB pieces per unit of work: 8 KiB in flight per warp
   const uint32_t nw = (uint32_t)p.copy_warps;
   const int panels = p.M / BM;
-  const uint32_t pieces_per_panel = (uint32_t)(((size_t)BM * p.K * p.elem_bytes) >> 10);
-  const uint32_t total = (uint32_t)panels * pieces_per_panel;
+  const uint32_t units_per_panel = (uint32_t)(((size_t)BM * p.K * p.elem_bytes) >> 13);
+  const uint32_t total = (uint32_t)panels * units_per_panel;
   if (p.x_scale_src && p.x_scale_stage && p.x_scale_src != p.x_scale_stage) {
-    // the row scales travel first: every warp copies its slice before it reports any panel
-    const size_t n4 = (size_t)p.M * (p.K / 128) / 4;  // K / 128 scales per row, M a multiple of 128: whole float4s
+    // The row scales travel first. Every warp copies its slice and then counts once on every panel, so a
+    // panel is complete only when all scales are here too (the target is units per panel + copy warps).
+    const size_t n4 = (size_t)p.M * (p.K / 128) / 4;  // 4 bytes per row and 128 elements in either fp8 format
     const float4* s4 = reinterpret_cast<const float4*>(p.x_scale_src);
     float4* d4 = reinterpret_cast<float4*>(p.x_scale_stage);
     for (size_t i = (size_t)warp_id * 32 + lane; i < n4; i += (size_t)nw * 32) d4[i] = __ldcg(s4 + i);
+    __syncwarp();
+    __threadfence();
+    for (int q = lane; q < panels; q += 32) red_release_gpu_add(p.panel_flags + q, 1u);
   }
   const unsigned char* src = p.x_src + (size_t)lane * 32;
   unsigned char* dst = p.x_stage + (size_t)lane * 32;
-  // Panels are reported one batch late: the fence that makes a batch's stores visible then runs while
-  // the next batch's loads are in flight, and costs nothing on top of them.
-  int signalled = 0, ready = 0;
-  auto report = [&](int upto) {
-    if (upto <= signalled) return;
+  // Units of 8 KiB, in address order, are drawn from a counter: a warp that falls behind (its SM is busy with
+  // an epilogue, its loads queue behind the tile loads) holds up one unit, not a share of every panel. A unit
+  // is counted on its panel one unit late: the fence that makes its stores visible then runs while the next
+  // unit's loads are in flight.
+  auto draw = [&]() -> uint32_t {
+    uint32_t u = 0;
+    if (lane == 0) u = atomicAdd(p.sched + 3, 1u);
+    return __shfl_sync(0xffffffffu, u, 0);
+  };
+  int pending = -1;  // panel of the unit whose stores have been issued but not counted
+  uint32_t u = draw();
+  while (u < total) {
+    uint32_t v[U][8];
+    const size_t off = (size_t)u << 13;
+#pragma unroll
+    for (int j = 0; j < U; ++j) ld_v8_b32(src + off + ((size_t)j << 10), v[j]);
+    const uint32_t next = draw();
+    if (pending >= 0) {
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        red_release_gpu_add(p.panel_flags + pending, 1u);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) st_v8_b32(dst + off + ((size_t)j << 10), v[j]);
+    pending = (int)(u / units_per_panel);
+    u = next;
+  }
+  if (pending >= 0) {
     __syncwarp();
     if (lane == 0) {
       __threadfence();
-      for (int q = signalled; q < upto; ++q) red_release_gpu_add(p.panel_flags + q, 1u);
+      red_release_gpu_add(p.panel_flags + pending, 1u);
     }
-    signalled = upto;
-  };
-  for (uint32_t r = warp_id; r < total; r += nw * U) {
-    uint32_t v[U][8];
-#pragma unroll
-    for (int j = 0; j < U; ++j)
-      if (r + j * nw < total) ld_v8_b32(src + ((size_t)(r + j * nw) << 10), v[j]);
-    report(ready);
-#pragma unroll
-    for (int j = 0; j < U; ++j)
-      if (r + j * nw < total) st_v8_b32(dst + ((size_t)(r + j * nw) << 10), v[j]);
-    const uint64_t next = (uint64_t)r + (uint64_t)nw * U;
-    ready = next >= total ? panels : (int)(next / pieces_per_panel);  // no piece of these panels is left for this warp
   }
-  report(panels);  // a warp without a piece of the last panels (or of any) still counts for them
 }
 
 __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
@@ -347,6 +371,7 @@ __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
     p.sched[0] = 0;
     p.sched[1] = 0;
     p.sched[2] = 0;  // the tile counter
+    p.sched[3] = 0;  // the copy warps' unit counter
     __threadfence_system();
     if (all_ok && p.done_flag) st_release_sys(p.done_flag, p.done_value);
   }
@@ -433,8 +458,8 @@ remote_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (tile >= total) break;
         int mb, nb;
         tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
-        if (p.copy_ctas + p.copy_warps > 0) {
-          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns)) {
+        if (p.panel_target > 0) {
+          if (!wait_u32_ge_gpu(p.panel_flags + mb, p.panel_target, p.timeout_ns)) {
             *abort = 1;
             break;
           }
@@ -650,8 +675,8 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (tile >= total) break;
         int mb, nb;
         tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
-        if (p.copy_ctas + p.copy_warps > 0) {
-          if (!wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns)) {
+        if (p.panel_target > 0) {
+          if (!wait_u32_ge_gpu(p.panel_flags + mb, p.panel_target, p.timeout_ns)) {
             *abort = 1;
             break;
           }
@@ -722,9 +747,9 @@ remote_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       // When X is pulled from a peer its row scales travel with it: they are known to have landed
       // once the panel is reported, so the warp checks the panel itself before it reads any of them
       // (the loads below run ahead of the MMA, which is what hides their latency).
-      if (p.copy_ctas + p.copy_warps > 0) {
+      if (p.panel_target > 0) {
         int arrived = 1;
-        if (lane == 0) arrived = wait_u32_ge_gpu(p.panel_flags + mb, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns) ? 1 : 0;
+        if (lane == 0) arrived = wait_u32_ge_gpu(p.panel_flags + mb, p.panel_target, p.timeout_ns) ? 1 : 0;
         arrived = __shfl_sync(0xffffffffu, arrived, 0);
         if (!arrived) {
           *abort = 1;
@@ -1012,8 +1037,8 @@ remote_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (tile >= total) break;
         int mb, nb;
         tile_coords(tile, m_blocks, n_blocks, p.head_blocks, mb, nb);
-        if (p.copy_ctas + p.copy_warps > 0) {  // this CTA's 128 rows of the 256-row block
-          if (!wait_u32_ge_gpu(p.panel_flags + 2 * mb + (int)rank, (uint32_t)(p.copy_ctas + p.copy_warps), p.timeout_ns)) {
+        if (p.panel_target > 0) {  // this CTA's 128 rows of the 256-row block
+          if (!wait_u32_ge_gpu(p.panel_flags + 2 * mb + (int)rank, p.panel_target, p.timeout_ns)) {
             *abort = 1;
             break;
           }
@@ -1290,7 +1315,12 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   // bits 8..15 of the flags: 1 + the height of the first tile group, 0 for the default
   const int head_arg = (int)((d->flags >> 8) & 0xffu) - 1;
   p.copy_warps = 0;
-  p.head_blocks = !pull ? 0 : head_arg >= 0 ? head_arg : d->fp8 ? 2 : 4;
+  p.panel_target = (uint32_t)copy_ctas;
+  // copy warps: units of 8 KiB per 128-row panel, plus one count per warp when scales travel first
+  auto warp_target = [&](int warps) {
+    return (uint32_t)(((size_t)BM * d->K * eb) >> 13) + (d->fp8 ? (uint32_t)warps : 0u);
+  };
+  p.head_blocks = !pull ? 0 : head_arg >= 0 ? head_arg : 4;  // of 128 rows: groups of 4, 4, 8, then 8
   static bool attr_set[64][2] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1319,10 +1349,12 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
     int copy_pairs = pull ? (copy_ctas + 1) / 2 : 0;
     if (copy_pairs > sms / 2 - 1) copy_pairs = sms / 2 - 1;
     p.copy_ctas = 2 * copy_pairs;
-    if (pull && head_arg < 0) p.head_blocks = 4;  // of 256 rows; measured best of 0, 2, 4, 8 on two B200s
+    p.panel_target = (uint32_t)p.copy_ctas;
+    if (pull && head_arg < 0) p.head_blocks = 2;  // of 256 rows: groups of 2, 2, 4, then 8
     if (pull && (d->flags & EUX_GEMM_FLAG_COPY_WARPS)) {  // two warps of every CTA copy, no CTA only copies
       p.copy_ctas = 0;
       p.copy_warps = 2 * 2 * (sms / 2);
+      p.panel_target = warp_target(p.copy_warps);
     }
     // every pair computes (the copying ones after their transfer), and they all have to be resident:
     // pairs that copy must not wait for a slot behind pairs that wait for their panels
@@ -1343,6 +1375,7 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
     grid = sms;
     p.copy_ctas = 0;
     p.copy_warps = 2 * grid;
+    p.panel_target = warp_target(p.copy_warps);
   }
   if (d->fp8) remote_gemm_fp8_kernel<<<grid, GEMM8_THREADS, GEMM8_SMEM, (cudaStream_t)stream>>>(ma, mb, my, p);
   else remote_gemm_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ma, mb, my, p);

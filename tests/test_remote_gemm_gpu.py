@@ -60,7 +60,7 @@ def test_block_scaled_fp8_matches_fp32(cuda_device, m, n, k, pull):
 
 
 @pytest.mark.parametrize("pull", [False, True, "warps"])
-@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 1024), (1024, 512, 2048)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 1024), (1024, 512, 2048), (5120, 512, 128)])
 def test_bf16_cta_pairs(cuda_device, m, n, k, pull):
     """The kernel that computes 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2) against fp32 PyTorch,
     with X read in place, with X streamed in by copying pairs that then join the GEMM, and with X
