@@ -252,9 +252,11 @@ InvokeSender AxonWorker::InvokeRpc(std::string_view worker_name, RpcRequestHeade
   } catch (const std::exception& e) {
     return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::SerializeError), e.what()));
   }
-  // deadline: done caused by the timer becomes DEADLINE_EXCEEDED, any other done stays a cancellation
+  // deadline: done caused by the timer becomes DEADLINE_EXCEEDED, any other done stays a cancellation.
+  // The timer lives on the client context's own loop, where the call completes too: arming and
+  // withdrawing it costs a queue node, not a wake-up of another thread.
   auto timed_out = std::make_shared<std::atomic<bool>>(false);
-  auto deadline = ex::then(ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout()), [timed_out] { timed_out->store(true); });
+  auto deadline = ex::then(ex::schedule_after(client_ctx_->get_scheduler(), GetTimeout()), [timed_out] { timed_out->store(true); });
   const uint32_t fid = call->function_id, sid = call->session_id;
   return ex::let_done(ex::stop_when(invoke_sender{this, std::move(call)}, std::move(deadline)), [timed_out, fid, sid]() -> InvokeSender {
     if (timed_out->load())

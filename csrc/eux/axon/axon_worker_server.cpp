@@ -220,7 +220,8 @@ void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
   }
   if (obs) obs->OnDispatchStart(call->mctx, std::chrono::steady_clock::now());
   // The handler and the deadline race; the first one to finish answers, the other is ignored.
-  // (A handler that blocks its pool thread cannot be interrupted, so the deadline must not wait for it.)
+  // (A handler that blocks its pool thread cannot be interrupted, so the deadline must not wait for it.
+  // The timer runs on the server context's loop, which no handler can block.)
   struct Race {
     std::atomic<bool> answered{false};
     ex::inplace_stop_source stop_timer;
@@ -264,7 +265,7 @@ void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
   };
   server_scope_->spawn_detached(ex::upon_done(ex::upon_error(ex::then(std::move(run), finish), on_error), on_done));
   server_scope_->spawn_detached(ex::upon_done(
-      ex::with_query_value(ex::then(ex::schedule_after(time_ctx_.get_scheduler(), GetTimeout()), on_deadline), ex::get_stop_token,
+      ex::with_query_value(ex::then(ex::schedule_after(server_ctx_->get_scheduler(), GetTimeout()), on_deadline), ex::get_stop_token,
                            race->stop_timer.get_token()),
       [race] {}));
 }

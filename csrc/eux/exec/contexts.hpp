@@ -34,6 +34,7 @@ class static_thread_pool {
     {
       std::lock_guard lk(mu_);
       stop_ = true;
+      stop_hint_.store(true, std::memory_order_relaxed);
     }
     cv_.notify_all();
     for (auto& t : threads_) t.join();
@@ -76,28 +77,56 @@ class static_thread_pool {
   std::size_t size() const noexcept { return threads_.size(); }
 
  private:
+  // A futex wake per task costs the submitting thread a system call and the task a scheduler
+  // latency. So up to two idle workers keep polling the queue length for a short while before they
+  // sleep, and a submitter wakes a sleeper only when nobody polls. A worker that takes a task while
+  // more are queued wakes the next sleeper itself.
+  static constexpr int kMaxSpinners = 2;
+  static constexpr std::chrono::microseconds kSpinFor{200};
   void enqueue(detail::task_base* t) noexcept {
+    bool wake;
     {
       std::lock_guard lk(mu_);
       t->next = nullptr;
       if (tail_) tail_->next = t;
       else head_ = t;
       tail_ = t;
+      queued_.fetch_add(1, std::memory_order_release);
+      wake = sleepers_ > 0 && spinners_ == 0;
     }
-    cv_.notify_one();
+    if (wake) cv_.notify_one();
   }
   void run() {
     std::unique_lock lk(mu_);
     for (;;) {
-      cv_.wait(lk, [&] { return stop_ || head_; });
       if (!head_) {
         if (stop_) return;
+        if (spinners_ < kMaxSpinners) {
+          ++spinners_;
+          lk.unlock();
+          const auto until = std::chrono::steady_clock::now() + kSpinFor;
+          while (queued_.load(std::memory_order_acquire) == 0 && !stop_hint_.load(std::memory_order_relaxed) &&
+                 std::chrono::steady_clock::now() < until) {
+#if defined(__x86_64__) || defined(__i386__)
+            __builtin_ia32_pause();
+#endif
+          }
+          lk.lock();
+          --spinners_;
+          if (head_ || stop_) continue;
+        }
+        ++sleepers_;
+        cv_.wait(lk, [&] { return stop_ || head_; });
+        --sleepers_;
         continue;
       }
       detail::task_base* t = head_;
       head_ = t->next;
       if (!head_) tail_ = nullptr;
+      queued_.fetch_sub(1, std::memory_order_relaxed);
+      const bool wake_next = head_ && sleepers_ > 0 && spinners_ == 0;
       lk.unlock();
+      if (wake_next) cv_.notify_one();
       t->execute(t);
       lk.lock();
     }
@@ -106,6 +135,10 @@ class static_thread_pool {
   std::condition_variable cv_;
   detail::task_base* head_ = nullptr;
   detail::task_base* tail_ = nullptr;
+  std::atomic<int> queued_{0};
+  std::atomic<bool> stop_hint_{false};
+  int spinners_ = 0;
+  int sleepers_ = 0;
   bool stop_ = false;
   std::vector<std::thread> threads_;
 };

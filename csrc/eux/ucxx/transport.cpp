@@ -408,14 +408,24 @@ void Worker::poll_hellos() {
 // ---------------------------------------------------------------------------
 int Worker::progress() {
   int handled = 0;
+  if (!pull_batch_.empty()) flush_pull_batch();  // pulls posted by the context since the last pass
   if (!reparse_.empty()) {
     auto list = std::move(reparse_);
     reparse_.clear();
     for (Endpoint* ep : list)
       if (eps_.count(ep) && ep->state_ == Endpoint::State::kConnected) parse_frames(ep);
   }
+  // The sockets are looked at on every call while any endpoint still talks through one. Once all of them
+  // use the rings, a socket only reports a new connection or a peer that went away, and the system
+  // call is made every few microseconds instead.
   epoll_event evs[64];
-  int n = epoll_wait(epfd_, evs, 64, 0);
+  int n = 0;
+  const auto now = std::chrono::steady_clock::now();
+  last_progress_ = now;
+  if (eps_.size() > shm_eps_.size() || now - last_epoll_ >= std::chrono::microseconds(5)) {
+    last_epoll_ = now;
+    n = epoll_wait(epfd_, evs, 64, 0);
+  }
   for (int i = 0; i < n; ++i) {
     ++handled;
     if (evs[i].data.u64 >> 63) {
@@ -467,6 +477,7 @@ int Worker::progress() {
     ++i;
   }
   if (!hellos_.empty()) poll_hellos();
+  if (!pull_batch_.empty()) flush_pull_batch();
   if (!device_ops_.empty()) poll_device();
   if (!graveyard_.empty()) {
     for (Endpoint* ep : graveyard_) eps_.erase(ep);
@@ -1183,7 +1194,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
     if (!srcs[i]) return UCS_ERR_UNSUPPORTED;
   }
   // walk source regions and destination segments together
-  const uint64_t seq = ++device_seq_;
+  if (device_ops_.size() + 2 >= kFlagSlots) return UCS_ERR_UNSUPPORTED;  // every transfer in flight owns a flag slot
   size_t si = 0, so = 0, di = 0, dof = 0;
   struct Piece {
     const char* s;
@@ -1200,6 +1211,20 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
     if (so == info.regions[si].length) ++si, so = 0;
     if (dof == segs[di].size) ++di, dof = 0;
   }
+  if (pieces.empty()) {
+    send_control(ep, kRndvFin, 0, msg_id, UCS_OK);
+    return UCS_OK;
+  }
+  const uint64_t seq = ++device_seq_;
+  uint64_t* const flag = flag_dev_ + seq % kFlagSlots;
+  if (pieces.size() == 1 && pieces[0].n <= kBatchMaxBytes) {
+    // a small message: it leaves with the others of this pass in one launch
+    pull_batch_.push_back({pieces[0].s, pieces[0].d, pieces[0].n, flag, seq});
+    device_ops_.push_back({seq, ep, msg_id, std::move(done)});
+    if (pull_batch_.size() == EUX_PULL_BATCH_MAX) flush_pull_batch();
+    return UCS_INPROGRESS;
+  }
+  flush_pull_batch();  // launches stay in the order of their sequence numbers
   for (size_t i = 0; i < pieces.size(); ++i) {
     eux_xfer_desc d{};
     d.src = pieces[i].s;
@@ -1208,7 +1233,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
     d.src_dtype = d.dst_dtype = EUX_DT_BYTES;
     d.op = EUX_OP_NONE;
     if (i + 1 == pieces.size()) {
-      d.flag = flag_dev_;
+      d.flag = flag;
       d.flag_value = seq;
     }
     int rc = eux_xfer_launch(&d, counter_dev_, 0, stream_);
@@ -1217,17 +1242,44 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
       return UCS_ERR_IO_ERROR;
     }
   }
-  if (pieces.empty()) {
-    send_control(ep, kRndvFin, 0, msg_id, UCS_OK);
-    return UCS_OK;
-  }
   device_ops_.push_back({seq, ep, msg_id, std::move(done)});
   return UCS_INPROGRESS;
 }
 
+// One launch for all the small pulls collected since the last call. If the launch fails, those
+// transfers end with an error at both sides.
+void Worker::flush_pull_batch() {
+  if (pull_batch_.empty()) return;
+  NvtxRange range("eux.transport.device_pull_batch");
+  const int rc = eux_xfer_pull_batch_launch(pull_batch_.data(), static_cast<int>(pull_batch_.size()), stream_);
+  if (rc != 0) {
+    UCX_CONN_ERROR << "batched transfer kernel launch failed: " << eux_error_string(rc);
+    const uint64_t first = pull_batch_.front().flag_value, last = pull_batch_.back().flag_value;
+    std::vector<DeviceOp> failed;
+    for (auto it = device_ops_.begin(); it != device_ops_.end();) {
+      if (it->seq >= first && it->seq <= last) {
+        failed.push_back(std::move(*it));
+        it = device_ops_.erase(it);
+      } else {
+        ++it;
+      }
+    }
+    pull_batch_.clear();
+    for (auto& op : failed) {
+      if (op.ep && eps_.count(op.ep) && op.ep->state_ == Endpoint::State::kConnected)
+        send_control(op.ep, kRndvFin, 0, op.msg_id, UCS_ERR_IO_ERROR);
+      if (op.done) op.done(UCS_ERR_IO_ERROR);
+    }
+    return;
+  }
+  pull_batch_.clear();
+}
+
 void Worker::poll_device() {
-  const uint64_t reached = *static_cast<volatile uint64_t*>(flag_host_);
-  while (!device_ops_.empty() && device_ops_.front().seq <= reached) {
+  while (!device_ops_.empty()) {
+    const uint64_t seq = device_ops_.front().seq;
+    if (*static_cast<volatile uint64_t*>(flag_host_ + seq % kFlagSlots) != seq) break;
+    std::atomic_thread_fence(std::memory_order_acquire);
     DeviceOp op = std::move(device_ops_.front());
     device_ops_.pop_front();
     if (op.ep && eps_.count(op.ep) && op.ep->state_ == Endpoint::State::kConnected)

@@ -40,6 +40,7 @@
 #include <vector>
 
 #include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
+#include "kernels/eux_kernels.h"
 #include "eux/ucxx/ucx_context_def.h"
 #include "eux/ucxx/shm_channel.hpp"
 #include "eux/ucxx/ucx_memory_resource.hpp"
@@ -229,6 +230,8 @@ class Worker {
 
   // Poll sockets and device completions once; returns the number of events handled.
   int progress();
+  // steady_clock as read at the start of the last progress() call
+  std::chrono::steady_clock::time_point last_progress_time() const noexcept { return last_progress_; }
 
   WorkerAddress address() const { return addr_; }
   const WorkerOptions& options() const { return opt_; }
@@ -301,6 +304,7 @@ class Worker {
                   Completion& done);
   bool ensure_device();
   void poll_device();
+  void flush_pull_batch();
   void update_interest(Endpoint* ep);
 
   UcxMemoryResourceManager& mr_;
@@ -313,6 +317,8 @@ class Worker {
   ssize_t io_writev(Endpoint* ep, const struct iovec* iov, int cnt);
   WorkerAddress addr_{};
   int epfd_ = -1;
+  std::chrono::steady_clock::time_point last_epoll_{};
+  std::chrono::steady_clock::time_point last_progress_{};
   std::vector<Listener> listeners_;
   std::list<HelloWait> hellos_;
   std::unordered_map<Endpoint*, std::unique_ptr<Endpoint>> eps_;
@@ -326,6 +332,11 @@ class Worker {
   uint32_t* counter_dev_ = nullptr;
   uint64_t device_seq_ = 0;
   std::deque<DeviceOp> device_ops_;
+  // Small single-segment pulls wait here until the end of the current pass of the loop and then leave in
+  // one launch (one CTA each). Every transfer owns the flag slot `seq % kFlagSlots` until it is reaped.
+  static constexpr size_t kFlagSlots = 512;
+  static constexpr size_t kBatchMaxBytes = size_t(256) << 10;
+  std::vector<eux_pull_item> pull_batch_;
 };
 
 }  // namespace eux::ucxx::transport

@@ -152,7 +152,9 @@ bool ucx_am_context::cancel_timer(timer_op* op) noexcept {
 
 void ucx_am_context::update_timers() noexcept {
   if (timers_.empty()) return;
-  const auto now = clock_t::now();
+  // the clock as read by the transport's last progress() call: deadlines are milliseconds, one loop
+  // iteration of staleness does not matter, and a clock read per iteration is saved
+  const auto now = worker_->last_progress_time();
   while (!timers_.empty() && timers_.begin()->first <= now) {
     timer_op* op = timers_.begin()->second;
     timers_.erase(timers_.begin());

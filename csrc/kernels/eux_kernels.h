@@ -97,6 +97,21 @@ EUX_API int eux_xfer_rpc_step_launch(const eux_xfer_desc* req, const eux_xfer_de
                                      uint32_t* scratch3, int max_ctas, void* stream);
 EUX_API int eux_xfer_batch_launch(const eux_xfer_desc* descs_dev, int n, void* stream);
 
+/* Many small dense copies in ONE launch with the descriptors in the launch parameters (nothing is read
+ * from host or device memory to find the work): CTA i copies items[i] and then release-stores
+ * items[i].flag_value to items[i].flag at system scope, so the host learns of every copy on its own.
+ * The transport uses it to pull the payloads of all the small messages that arrived in one pass of its
+ * loop (sources are peers' memory). n <= EUX_PULL_BATCH_MAX; buffers of any alignment. */
+#define EUX_PULL_BATCH_MAX 48
+typedef struct eux_pull_item {
+  const void* src;
+  void* dst;
+  uint64_t nbytes;
+  uint64_t* flag; /* mapped pinned host memory or device memory; may be NULL */
+  uint64_t flag_value;
+} eux_pull_item;
+EUX_API int eux_xfer_pull_batch_launch(const eux_pull_item* items, int n, void* stream);
+
 /* Device-driven ping-pong between two GPUs (or loopback on one): see
  * tensor_xfer.cu. ts_out receives iters+1 globaltimer stamps (ns). */
 typedef struct eux_pingpong_desc {

@@ -588,6 +588,39 @@ extern "C" int eux_xfer_bulk_launch(const eux_xfer_desc* d, uint32_t* scratch_co
   return (int)cudaGetLastError();
 }
 
+// One CTA per item, the items in the launch parameters.
+struct PullBatchArgs {
+  eux_pull_item it[EUX_PULL_BATCH_MAX];
+};
+__global__ void __launch_bounds__(256) xfer_pull_batch_kernel(const __grid_constant__ PullBatchArgs a) {
+  const eux_pull_item& d = a.it[blockIdx.x];
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src);
+  unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
+  if (((((uintptr_t)src) | ((uintptr_t)dst)) & 15u) == 0) {
+    copy_bytes_grid<false>(src, dst, d.nbytes, 0, 1);
+  } else {
+    for (uint64_t b = threadIdx.x; b < d.nbytes; b += blockDim.x) dst[b] = src[b];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && d.flag) {
+    __threadfence_system();
+    st_release_sys(d.flag, d.flag_value);
+  }
+}
+
+extern "C" int eux_xfer_pull_batch_launch(const eux_pull_item* items, int n, void* stream) {
+  if (n <= 0) return 0;
+  if (!items || n > EUX_PULL_BATCH_MAX) return EUX_ERR_BAD_ARG;
+  PullBatchArgs a;
+  for (int i = 0; i < n; ++i) {
+    if (!items[i].src || !items[i].dst) return EUX_ERR_BAD_ARG;
+    a.it[i] = items[i];
+  }
+  for (int i = n; i < EUX_PULL_BATCH_MAX; ++i) a.it[i] = eux_pull_item{};
+  xfer_pull_batch_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int eux_xfer_batch_launch(const eux_xfer_desc* descs_dev, int n, void* stream) {
   if (n <= 0) return 0;
   if (!descs_dev) return EUX_ERR_BAD_ARG;

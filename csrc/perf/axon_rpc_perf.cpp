@@ -74,15 +74,24 @@ static std::unique_ptr<eux::ucxx::UcxAutoDeviceContext> make_dev(const Options& 
   return std::make_unique<eux::ucxx::UcxAutoCudaDeviceContext>(o.device);
 }
 
-// y = x + 1 on the device, on a stream of the calling thread
+// y = x + 1 on the device, on a stream of the calling thread. The kernel publishes a sequence number in
+// mapped pinned host memory when its stores are done and the thread watches that word: no call into the
+// driver while it waits, so handlers on other threads and the transport's launches are not held up.
 static void device_plus_one(const void* x, void* y, size_t bytes, int device) {
   thread_local cudaStream_t st = nullptr;
   thread_local uint32_t* counter = nullptr;
+  thread_local uint64_t* flag_host = nullptr;
+  thread_local uint64_t* flag_dev = nullptr;
+  thread_local uint64_t seq = 0;
   if (!st) {
     cudaSetDevice(device);
     cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
     cudaMalloc(reinterpret_cast<void**>(&counter), 256);
     cudaMemsetAsync(counter, 0, 256, st);
+    void *h = nullptr, *d = nullptr;
+    if (eux_host_alloc_mapped(&h, &d, 64) != 0) throw std::runtime_error("handler: no mapped host memory");
+    flag_host = static_cast<uint64_t*>(h);
+    flag_dev = static_cast<uint64_t*>(d);
   }
   eux_xfer_desc d{};
   d.src = x;
@@ -91,9 +100,18 @@ static void device_plus_one(const void* x, void* y, size_t bytes, int device) {
   d.src_dtype = d.dst_dtype = EUX_DT_F32;
   d.op = EUX_OP_ADD;
   d.op_arg = 1.0f;
+  d.flag = flag_dev;
+  d.flag_value = ++seq;
   int rc = eux_xfer_launch(&d, counter, 0, st);
   if (rc != 0) throw std::runtime_error(std::string("handler kernel: ") + eux_error_string(rc));
-  cudaStreamSynchronize(st);
+  const auto give_up = clk::now() + std::chrono::seconds(5);
+  while (*static_cast<volatile uint64_t*>(flag_host) != seq) {
+    if (clk::now() > give_up) {
+      if (cudaStreamSynchronize(st) != cudaSuccess) throw std::runtime_error("handler kernel failed");
+      break;
+    }
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
 }
 
 static void register_plus_one(AxonRuntime& rt, const Options& o) {
