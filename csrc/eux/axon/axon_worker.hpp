@@ -49,16 +49,21 @@ struct InvokeResult {
 using InvokeSender = exec::any_sender_of<InvokeResult>;
 
 // Either policy kind for either payload form, type-erased for the function table.
+// `provider_inline`: the provider neither blocks nor takes long (it takes a block from a pool, say), so it is
+// called on the context's own thread; otherwise it is user code of unknown cost and runs on the thread pool,
+// which costs every rendezvous message two hand-overs between threads.
 struct ServerMemoryPolicy {
   bool on_host = true;
   CustomMemoryPolicy<ucxx::UcxBuffer> buffer_provider;        // used when the function takes a UcxBuffer
   CustomMemoryPolicy<ucxx::UcxBufferVec> buffer_vec_provider;  // used when it takes a UcxBufferVec
+  bool provider_inline = false;
 };
 struct ClientMemoryPolicy {
   bool on_host = true;
   CustomMemoryPolicy<ucxx::UcxBuffer> buffer_provider;
   CustomMemoryPolicy<ucxx::UcxBufferVec> buffer_vec_provider;
   bool want_vec = false;  // receive a scatter-gather response as separate buffers
+  bool provider_inline = false;
 };
 
 class AxonWorker {

@@ -297,7 +297,8 @@ void AxonWorker::ClientFinishWithPayload(std::shared_ptr<ClientCall> call) {
         call->finish_value(InvokeResult{std::move(call->response), PayloadVariant(b.move_buffer())});
       });
     };
-    if (custom) client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
+    if (custom && !call->mem.provider_inline)
+      client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
     else client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
     return;
   }
@@ -314,10 +315,9 @@ void AxonWorker::ClientFinishWithPayload(std::shared_ptr<ClientCall> call) {
       opaque.strides = {1};
       return call->mem.buffer_provider(utils::TensorMetaSpan{&opaque, 1});
     };
-    client_scope_->spawn_detached(ex::upon_error(
-        ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)),
-                      [sched, key, done](UcxBuffer& buf) { return ex::then(ucxx::connection_recv_buffer(sched, key, std::move(buf)), done); }),
-        fail));
+    auto recv = [sched, key, done](UcxBuffer& buf) { return ex::then(ucxx::connection_recv_buffer(sched, key, std::move(buf)), done); };
+    if (call->mem.provider_inline) client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
+    else client_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
   } else {
     client_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_recv_buffer(sched, key, ucx_memory_type::HOST), done), fail));
   }

@@ -163,7 +163,8 @@ void AxonWorker::ServerRunRequest(std::shared_ptr<ServerCall> call) {
         ServerDispatch(call);
       });
     };
-    if (custom) server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
+    if (custom && !call->mem.provider_inline)
+      server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
     else server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
     return;
   }
@@ -182,10 +183,9 @@ void AxonWorker::ServerRunRequest(std::shared_ptr<ServerCall> call) {
       opaque.strides = {1};
       return call->mem.buffer_provider(utils::TensorMetaSpan{&opaque, 1});
     };
-    server_scope_->spawn_detached(ex::upon_error(
-        ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)),
-                      [sched, key, done](UcxBuffer& buf) { return ex::then(ucxx::connection_recv_buffer(sched, key, std::move(buf)), done); }),
-        fail));
+    auto recv = [sched, key, done](UcxBuffer& buf) { return ex::then(ucxx::connection_recv_buffer(sched, key, std::move(buf)), done); };
+    if (call->mem.provider_inline) server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::just_from(make), recv), fail));
+    else server_scope_->spawn_detached(ex::upon_error(ex::let_value(ex::on(pool_.get_scheduler(), ex::just_from(make)), recv), fail));
   } else {
     server_scope_->spawn_detached(ex::upon_error(ex::then(ucxx::connection_recv_buffer(sched, key, ucx_memory_type::HOST), done), fail));
   }

@@ -77,32 +77,49 @@ class static_thread_pool {
   std::size_t size() const noexcept { return threads_.size(); }
 
  private:
-  // A futex wake per task costs the submitting thread a system call and the task a scheduler
-  // latency. So up to two idle workers keep polling the queue length for a short while before they
-  // sleep, and a submitter wakes a sleeper only when nobody polls. A worker that takes a task while
-  // more are queued wakes the next sleeper itself.
-  static constexpr int kMaxSpinners = 2;
-  static constexpr std::chrono::microseconds kSpinFor{200};
+  // Submitting never takes the workers' lock: a task is pushed onto a lock-free list, which a worker
+  // moves (reversed, so oldest first) into the queue the workers share under their mutex. A futex wake
+  // per task would cost the submitting thread a system call and the task a scheduler latency, so one
+  // idle worker keeps polling the task count for a short while before it sleeps, and a
+  // submitter wakes a sleeper only when nobody polls. A worker that takes a task while more are
+  // waiting wakes the next sleeper itself.
+  static constexpr int kMaxSpinners = 1;
+  static constexpr std::chrono::microseconds kSpinFor{100};
   void enqueue(detail::task_base* t) noexcept {
-    bool wake;
-    {
-      std::lock_guard lk(mu_);
-      t->next = nullptr;
-      if (tail_) tail_->next = t;
-      else head_ = t;
-      tail_ = t;
-      queued_.fetch_add(1, std::memory_order_release);
-      wake = sleepers_ > 0 && spinners_ == 0;
+    detail::task_base* old = incoming_.load(std::memory_order_relaxed);
+    do {
+      t->next = old;
+    } while (!incoming_.compare_exchange_weak(old, t, std::memory_order_seq_cst, std::memory_order_relaxed));
+    queued_.fetch_add(1, std::memory_order_seq_cst);
+    if (sleepers_.load(std::memory_order_seq_cst) > 0 && spinners_.load(std::memory_order_seq_cst) == 0) {
+      { std::lock_guard lk(mu_); }  // a worker between its last check and its wait holds the mutex
+      cv_.notify_one();
     }
-    if (wake) cv_.notify_one();
+  }
+  // with mu_ held: move what was submitted into the shared queue
+  void take_incoming() noexcept {
+    detail::task_base* list = incoming_.exchange(nullptr, std::memory_order_seq_cst);
+    detail::task_base* rev = nullptr;
+    while (list) {
+      detail::task_base* n = list->next;
+      list->next = rev;
+      rev = list;
+      list = n;
+    }
+    if (!rev) return;
+    if (tail_) tail_->next = rev;
+    else head_ = rev;
+    while (rev->next) rev = rev->next;
+    tail_ = rev;
   }
   void run() {
     std::unique_lock lk(mu_);
     for (;;) {
+      if (!head_) take_incoming();
       if (!head_) {
         if (stop_) return;
-        if (spinners_ < kMaxSpinners) {
-          ++spinners_;
+        if (spinners_.load(std::memory_order_relaxed) < kMaxSpinners) {
+          spinners_.fetch_add(1, std::memory_order_seq_cst);
           lk.unlock();
           const auto until = std::chrono::steady_clock::now() + kSpinFor;
           while (queued_.load(std::memory_order_acquire) == 0 && !stop_hint_.load(std::memory_order_relaxed) &&
@@ -112,33 +129,34 @@ class static_thread_pool {
 #endif
           }
           lk.lock();
-          --spinners_;
-          if (head_ || stop_) continue;
+          spinners_.fetch_sub(1, std::memory_order_seq_cst);
+          if (queued_.load(std::memory_order_seq_cst) > 0 || stop_) continue;
         }
-        ++sleepers_;
-        cv_.wait(lk, [&] { return stop_ || head_; });
-        --sleepers_;
+        sleepers_.fetch_add(1, std::memory_order_seq_cst);
+        cv_.wait(lk, [&] { return stop_ || queued_.load(std::memory_order_seq_cst) > 0; });
+        sleepers_.fetch_sub(1, std::memory_order_seq_cst);
         continue;
       }
       detail::task_base* t = head_;
       head_ = t->next;
       if (!head_) tail_ = nullptr;
-      queued_.fetch_sub(1, std::memory_order_relaxed);
-      const bool wake_next = head_ && sleepers_ > 0 && spinners_ == 0;
+      const int left = queued_.fetch_sub(1, std::memory_order_seq_cst) - 1;
+      const bool wake_next = left > 0 && sleepers_.load(std::memory_order_relaxed) > 0 && spinners_.load(std::memory_order_relaxed) == 0;
       lk.unlock();
       if (wake_next) cv_.notify_one();
       t->execute(t);
       lk.lock();
     }
   }
-  std::mutex mu_;
+  std::mutex mu_;  // the workers' side: head_/tail_, sleeping and waking
   std::condition_variable cv_;
+  std::atomic<detail::task_base*> incoming_{nullptr};
   detail::task_base* head_ = nullptr;
   detail::task_base* tail_ = nullptr;
-  std::atomic<int> queued_{0};
+  std::atomic<int> queued_{0};  // submitted and not yet taken by a worker
   std::atomic<bool> stop_hint_{false};
-  int spinners_ = 0;
-  int sleepers_ = 0;
+  std::atomic<int> spinners_{0};
+  std::atomic<int> sleepers_{0};
   bool stop_ = false;
   std::vector<std::thread> threads_;
 };

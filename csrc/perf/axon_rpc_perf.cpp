@@ -133,7 +133,11 @@ static void register_plus_one(AxonRuntime& rt, const Options& o) {
     CustomMemoryPolicy<UcxBuffer> provider = [mr](eux::rpc::utils::TensorMetaSpan metas) {
       return UcxBuffer(*mr, ucx_memory_type::CUDA, eux::rpc::utils::CalculateTensorSize(metas[0]));
     };
-    rt.worker().RegisterFunction<UcxBuffer>(function_id_t{1}, handler, "plus_one", provider, MessageLifecyclePolicy{});
+    eux::axon::ServerMemoryPolicy mp;
+    mp.on_host = false;
+    mp.buffer_provider = provider;
+    mp.provider_inline = true;  // a block from the memory manager's pool: nothing that could hold up the context's thread
+    rt.worker().RegisterFunction(function_id_t{1}, handler, "plus_one", std::move(mp), MessageLifecyclePolicy{});
   } else {
     rt.RegisterFunction(function_id_t{1}, handler, "plus_one");
   }
@@ -144,6 +148,7 @@ static ClientMemoryPolicy client_policy(AxonRuntime& rt, const Options& o) {
   if (o.cuda) {
     auto mr = rt.memory_resource();
     p.on_host = false;
+    p.provider_inline = true;
     p.buffer_provider = [mr](eux::rpc::utils::TensorMetaSpan metas) {
       return UcxBuffer(*mr, ucx_memory_type::CUDA, eux::rpc::utils::CalculateTensorSize(metas[0]));
     };

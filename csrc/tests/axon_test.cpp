@@ -4,7 +4,10 @@
 #include <unistd.h>
 
 #include <cstring>
+#include <mutex>
 #include <numeric>
+#include <set>
+#include <thread>
 
 #include "check.hpp"
 #include "eux/ucxx/transport.hpp"
@@ -238,6 +241,67 @@ EUX_TEST(memory_policy_backpressure_and_retention) {
   CHECK(ctl && ctl->header.status.ok());
   p.server.SetRejectMessages(false);
   CHECK(call(16)->header.status.ok());
+}
+
+EUX_TEST(inline_buffer_providers_run_on_the_context_threads) {
+  // provider_inline: the providers are called by the server's and the client's context threads, never by a
+  // pool thread (handlers run on the pool, so a handler's thread id tells the two apart), and the payload
+  // still arrives in the buffers they returned.
+  Pair p;
+  std::mutex mu;
+  std::set<std::thread::id> provider_threads, handler_threads;
+  void* server_buffer = nullptr;
+  eux::axon::ServerMemoryPolicy smp;
+  smp.on_host = false;
+  smp.provider_inline = true;
+  smp.buffer_provider = [&](eux::rpc::utils::TensorMetaSpan metas) {
+    UcxBuffer b(*p.mr, ucx_memory_type::HOST, eux::rpc::utils::CalculateTensorSize(metas[0]));
+    std::lock_guard lk(mu);
+    provider_threads.insert(std::this_thread::get_id());
+    server_buffer = b.data();
+    return b;
+  };
+  p.server.RegisterFunction(function_id_t{1}, [&](const TensorMeta& m, UcxBuffer& b) {
+    {
+      std::lock_guard lk(mu);
+      handler_threads.insert(std::this_thread::get_id());
+      CHECK(b.data() == server_buffer);
+    }
+    UcxBuffer out(*p.mr, ucx_memory_type::HOST, b.size());
+    const float* f = static_cast<const float*>(b.data());
+    float* g = static_cast<float*>(out.data());
+    for (int64_t i = 0; i < m.shape[0]; ++i) g[i] = f[i] + 1.0f;
+    return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out));
+  }, "plus_one", std::move(smp));
+  p.connect();
+  void* client_buffer = nullptr;
+  ClientMemoryPolicy cmp;
+  cmp.on_host = false;
+  cmp.provider_inline = true;
+  cmp.buffer_provider = [&](eux::rpc::utils::TensorMetaSpan metas) {
+    UcxBuffer b(*p.mr, ucx_memory_type::HOST, eux::rpc::utils::CalculateTensorSize(metas[0]));
+    std::lock_guard lk(mu);
+    provider_threads.insert(std::this_thread::get_id());
+    client_buffer = b.data();
+    return b;
+  };
+  const int64_t n = 200000;  // rendezvous both ways
+  for (int round = 0; round < 3; ++round) {
+    UcxBuffer buf(*p.mr, ucx_memory_type::HOST, size_t(n) * 4);
+    float* f = static_cast<float*>(buf.data());
+    for (int64_t i = 0; i < n; ++i) f[i] = float(i % 977) + float(round);
+    auto r = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, cmp, f32_meta(n), std::move(buf)));
+    CHECK(r && r->header.status.ok());
+    const auto& out = std::get<UcxBuffer>(r->payload);
+    CHECK(out.data() == client_buffer);
+    const float* g = static_cast<const float*>(out.data());
+    bool same = true;
+    for (int64_t i = 0; i < n; ++i) same = same && g[i] == float(i % 977) + float(round) + 1.0f;
+    CHECK(same);
+  }
+  std::lock_guard lk(mu);
+  CHECK_EQ(provider_threads.size(), 2u);  // one context thread on each side
+  for (auto id : handler_threads) CHECK(provider_threads.count(id) == 0);
 }
 
 EUX_TEST(stop_client_cancels_pending_and_peer_loss_is_an_error) {
