@@ -57,6 +57,10 @@ struct ServerMemoryPolicy {
   CustomMemoryPolicy<ucxx::UcxBuffer> buffer_provider;        // used when the function takes a UcxBuffer
   CustomMemoryPolicy<ucxx::UcxBufferVec> buffer_vec_provider;  // used when it takes a UcxBufferVec
   bool provider_inline = false;
+  // The handler itself never blocks either (it only starts asynchronous work and returns a sender, as the
+  // Python binding's handlers do, which hand the call to the event loop): start it on the server context's
+  // thread as well instead of on the pool.
+  bool handler_inline = false;
 };
 struct ClientMemoryPolicy {
   bool on_host = true;

@@ -229,10 +229,10 @@ void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
   auto race = std::make_shared<Race>();
   auto payload_box = std::make_shared<PayloadVariant>(std::move(for_handler));
   const bool respond = call->respond;
-  auto run = ex::on(pool_.get_scheduler(), ex::defer([this, call, payload_box] {
-                      rpc::RpcResponseBuilder b(TickHlc(), call->req.workflow_id);
-                      return dispatcher_.InvokeAsyncFunction(call->req, std::move(*payload_box), b);
-                    }));
+  auto invoke = [this, call, payload_box] {
+    rpc::RpcResponseBuilder b(TickHlc(), call->req.workflow_id);
+    return dispatcher_.InvokeAsyncFunction(call->req, std::move(*payload_box), b);
+  };
   auto finish = [this, call, obs, race, respond](rpc::RpcInvokeResult<rpc::ReturnedPayload> r) {
     if (race->answered.exchange(true)) return;
     race->stop_timer.request_stop();
@@ -263,7 +263,11 @@ void AxonWorker::ServerDispatch(std::shared_ptr<ServerCall> call) {
     if (respond)
       ServerSendError(call->conn_id, call->req, rpc::make_error_code(RpcErrc::DEADLINE_EXCEEDED), "the handler did not finish before the deadline");
   };
-  server_scope_->spawn_detached(ex::upon_done(ex::upon_error(ex::then(std::move(run), finish), on_error), on_done));
+  if (call->mem.handler_inline)
+    server_scope_->spawn_detached(ex::upon_done(ex::upon_error(ex::then(ex::defer(invoke), finish), on_error), on_done));
+  else
+    server_scope_->spawn_detached(
+        ex::upon_done(ex::upon_error(ex::then(ex::on(pool_.get_scheduler(), ex::defer(invoke)), finish), on_error), on_done));
   server_scope_->spawn_detached(ex::upon_done(
       ex::with_query_value(ex::then(ex::schedule_after(server_ctx_->get_scheduler(), GetTimeout()), on_deadline), ex::get_stop_token,
                            race->stop_timer.get_token()),

@@ -11,6 +11,7 @@
 #include <atomic>
 #include <unordered_map>
 
+#include "eux/ucxx/nvtx_range.hpp"
 #include "bindings_common.hpp"
 #include "eux/ucxx/cuda/ucx_cuda_context.hpp"
 #include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
@@ -213,7 +214,9 @@ class PyAxonRuntime {
     py::object fut = wake_.loop().attr("create_future")();
     auto fut_box = gil_shared(fut);  // destroyed on the loop thread, under the GIL
     auto settle = [this, fut_box](std::function<void(py::object&)> fn) {
+      ucxx::nvtx_mark("axon.python.result_queued");
       wake_.enqueue([fut_box, fn = std::move(fn)] {
+        ucxx::NvtxRange range("axon.python.result_on_loop");
         py::object f = *fut_box;
         if (!f.attr("done")().cast<bool>()) fn(f);
       });
@@ -341,7 +344,9 @@ class PyAxonRuntime {
       auto st = std::make_shared<State>(State{req, builder, std::move(payload)});
       return rpc::AsyncInvokeSender(ex::create<rpc::RpcInvokeResult<rpc::ReturnedPayload>>([self, fn, st](auto handle) {
         // hop to the asyncio thread: start the coroutine as a task, finish the C++ call from its done-callback
+        ucxx::nvtx_mark("axon.python.handler_queued");
         self->wake_.enqueue([self, fn, st, handle]() mutable {
+          ucxx::NvtxRange range("axon.python.handler_on_loop");
           // the call is answered exactly once: by the task's completion, or by stop() while it still runs
           auto settled = std::make_shared<std::atomic<bool>>(false);
           auto fail = [st, handle, settled](std::error_code ec, const std::string& what) mutable {
@@ -432,9 +437,11 @@ class PyAxonRuntime {
         return static_cast<axon::LifecycleStatus>(r.cast<int>());
       });
     }
+    ServerMemoryPolicy mem = server_policy(memory_policy);
+    mem.handler_inline = true;  // the handler above only queues the call for the event loop
     return rt_->RegisterFunction(rpc::function_id_t{function_id}, function_name, rpc::data::vector<rpc::ParamType>(param_types.begin(), param_types.end()),
                                  rpc::data::vector<rpc::ParamType>(return_types.begin(), return_types.end()), input_payload_type,
-                                 return_payload_type, std::move(handler), server_policy(memory_policy), std::move(lc));
+                                 return_payload_type, std::move(handler), std::move(mem), std::move(lc));
   }
 
  private:

@@ -61,18 +61,24 @@ class PythonWakeManager {
   void process_queue() {
     uint64_t n;
     (void)!::read(fd_, &n, sizeof(n));
-    std::deque<std::function<void()>> batch;
-    {
-      std::lock_guard lk(mu_);
-      batch.swap(queue_);
-    }
-    for (auto& fn : batch) {
-      try {
-        fn();
-      } catch (py::error_already_set& e) {
-        e.discard_as_unraisable("axon callback");
-      } catch (const std::exception& e) {
-        py::print("axon: callback failed:", e.what());
+    // Closures that arrive while a batch runs (the reply to a request that one of them sent, for
+    // instance) run in this call too, instead of one trip through the event loop later. Bounded, so
+    // that a steady stream of them cannot keep the loop's other work waiting.
+    for (int round = 0; round < 4; ++round) {
+      std::deque<std::function<void()>> batch;
+      {
+        std::lock_guard lk(mu_);
+        batch.swap(queue_);
+      }
+      if (batch.empty()) return;
+      for (auto& fn : batch) {
+        try {
+          fn();
+        } catch (py::error_already_set& e) {
+          e.discard_as_unraisable("axon callback");
+        } catch (const std::exception& e) {
+          py::print("axon: callback failed:", e.what());
+        }
       }
     }
   }
