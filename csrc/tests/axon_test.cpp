@@ -183,6 +183,10 @@ EUX_TEST(concurrent_calls_and_buffer_vec) {
 }
 
 EUX_TEST(memory_policy_backpressure_and_retention) {
+  // written by the retention policy on the server's context thread; declared before the workers so that
+  // they outlive those threads
+  std::mutex ids_mu;
+  std::vector<uint64_t> retained_ids;
   Pair p;
   std::atomic<int> provider_calls{0};
   // the server chooses the receive buffer itself for large payloads
@@ -190,9 +194,11 @@ EUX_TEST(memory_policy_backpressure_and_retention) {
     provider_calls.fetch_add(1);
     return UcxBuffer(*p.mr, ucx_memory_type::HOST, eux::rpc::utils::CalculateTensorSize(metas[0]));
   };
-  std::vector<uint64_t> retained_ids;
   RetentionPolicy keep = [&](std::shared_ptr<autils::AxonRequest> req, autils::AxonMessageID id) {
-    retained_ids.push_back(id);
+    {
+      std::lock_guard lk(ids_mu);
+      retained_ids.push_back(id);
+    }
     return req->header.GetTensor(0).shape[0] > 100000 ? LifecycleStatus::Preserve : LifecycleStatus::Discard;
   };
   std::atomic<int> handled{0};
@@ -214,7 +220,10 @@ EUX_TEST(memory_policy_backpressure_and_retention) {
   CHECK(big && big->header.GetPrimitive<int64_t>(0) == 800000);
   CHECK_EQ(provider_calls.load(), 1);
   CHECK_EQ(p.server.GetStorage().size(), 1u);
-  CHECK_EQ(retained_ids.size(), 2u);
+  {
+    std::lock_guard lk(ids_mu);
+    CHECK_EQ(retained_ids.size(), 2u);
+  }
   // stored requests can be run again and checkpointed
   CHECK_EQ(p.server.ProcessStoredRequests(), 1u);
   CHECK_EQ(handled.load(), 3);
