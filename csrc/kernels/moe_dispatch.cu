@@ -480,6 +480,91 @@ __global__ void __launch_bounds__(kMoeThreads) moe_combine_bf16_kernel(eux_moe_d
   }
 }
 
+// ---- combine, bf16, top-k <= 8: a warp streams through a contiguous run of (token, 32-chunk) units with two
+// units in flight: the loads of the next unit are issued before the current one is accumulated and
+// stored, so a warp never sits out a whole memory round trip between units, and the routing entries
+// are read once per token instead of once per unit.
+struct CombineSlot {
+  uint4 v[8];
+  float my_w;  // lane k holds the gate weight of row k of this unit's token
+  int t, c;    // token and this lane's chunk; c < 0: nothing to store
+};
+__global__ void __launch_bounds__(kMoeThreads) moe_combine_bf16_stream_kernel(eux_moe_desc d) {
+  if (!moe_wait_experts(d)) return;
+  const int W = d.world, EPR = d.n_experts / W, K = d.topk;
+  const int chunks = d.hidden / 8;
+  const int upr = (chunks + 31) / 32;
+  const size_t row_bytes = (size_t)d.hidden * 2;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int64_t units = (int64_t)d.n_tokens * upr;
+  const int64_t per = (units + nwarps - 1) / nwarps;
+  const int64_t u0 = (int64_t)warp * per;
+  const int64_t u1 = u0 + per < units ? u0 + per : units;
+  int cur_t = -1;
+  const unsigned char* my_row = nullptr;
+  float my_w = 0.f;
+  auto issue = [&](int64_t u, CombineSlot& s) {
+    const int t = (int)(u / upr), part = (int)(u - (int64_t)t * upr);
+    if (t != cur_t) {
+      cur_t = t;
+      my_row = nullptr;
+      my_w = 0.f;
+      if (lane < K) {
+        const int e = d.topk_idx[t * K + lane];
+        const int slot = d.slot_of[t * K + lane];
+        if (slot >= 0) {
+          my_row = reinterpret_cast<const unsigned char*>(d.arena_peer[e / EPR]) + ((size_t)d.rank * d.capacity + slot) * row_bytes;
+          my_w = d.topk_w[t * K + lane];
+        }
+      }
+    }
+    const int c = part * 32 + lane;
+    s.t = t;
+    s.c = c < chunks ? c : -1;
+    s.my_w = my_w;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const unsigned char* row = (const unsigned char*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, k);
+      s.v[k] = make_uint4(0, 0, 0, 0);
+      if (row && c < chunks) s.v[k] = ld_cg_u4(reinterpret_cast<const uint4*>(row) + c);
+    }
+  };
+  auto finish = [&](const CombineSlot& s) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float w = __shfl_sync(0xffffffffu, s.my_w, k);  // 0 for a row that does not exist
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&s.v[k]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(p[j]);
+        acc[2 * j] = fmaf(w, a.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, a.y, acc[2 * j + 1]);
+      }
+    }
+    if (s.c >= 0) {
+      uint4 o;
+      __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      st_stream_u4(reinterpret_cast<uint4*>(d.out) + (size_t)s.t * chunks + s.c, o);
+    }
+  };
+  if (u0 >= u1) return;
+  CombineSlot a, b;
+  issue(u0, a);
+  for (int64_t u = u0; u < u1; u += 2) {
+    if (u + 1 < u1) issue(u + 1, b);
+    finish(a);
+    if (u + 2 < u1) issue(u + 2, a);
+    if (u + 1 < u1) finish(b);
+  }
+}
+
 // ---- combine, fp8 rows: lane owns 16 elements; dequantise while accumulating --
 __global__ void __launch_bounds__(kMoeThreads) moe_combine_fp8_kernel(eux_moe_desc d) {
   if (!moe_wait_experts(d)) return;
@@ -674,6 +759,7 @@ extern "C" int eux_moe_combine_launch(const eux_moe_desc* d, int ctas, void* str
   if (ctas <= 0) ctas = 296;
   if (d->fp8 && d->topk <= 8 && d->hidden <= 16384) moe_combine_fp8_rows_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
   else if (d->fp8) moe_combine_fp8_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
+  else if (d->topk <= 8) moe_combine_bf16_stream_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
   else moe_combine_bf16_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
   return (int)cudaGetLastError();
 }
