@@ -14,8 +14,14 @@ def _routing(t, topk, n_experts, dev, seed):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
-@pytest.mark.parametrize("world,t,hidden,topk,ne", [(1, 64, 512, 4, 8), (4, 96, 1024, 4, 16), (8, 40, 7168, 8, 256)])
+@pytest.mark.parametrize("world,t,hidden,topk,ne", [
+    (1, 64, 512, 4, 8), (4, 96, 1024, 4, 16), (8, 40, 7168, 8, 256),
+    # the general kernels: more than eight experts per token, rows wider than the streaming kernels take
+    (2, 48, 1024, 12, 16), (2, 33, 9216, 4, 8), (1, 70, 1152, 8, 8)])
 def test_dispatch_combine(cuda_device, fp8, world, t, hidden, topk, ne):
+    """Dispatch, identity expert and gate-weighted combine against fp32 PyTorch. The streaming combine
+    kernels (top-k <= 8; fp8 also hidden <= 8192) and the general ones are both reached; 1152 makes the
+    last unit of a row a partial one, and odd token counts leave warps with runs of different lengths."""
     from execution_ucx_b200.ops import moe
     ranks = moe.MoeAllToAll.emulated(world, t, hidden, topk, ne, fp8=fp8)
     xs, idxs, ws = [], [], []
