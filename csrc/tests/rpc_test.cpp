@@ -1,5 +1,6 @@
 // rpc_core: wire image (hand-derived golden bytes), dispatcher, builders, async
 // dispatcher, hybrid logical clock (CPU only).
+#include <atomic>
 #include <cstring>
 #include <random>
 
@@ -328,6 +329,255 @@ EUX_TEST(hybrid_logical_clock_causality) {
   HybridLogicalClock now = HybridLogicalClock::Now(), later = now;
   later.TickLocal();
   CHECK(later > now);
+}
+
+// Every return kind a handler may have, through the serialised request and back through the response bytes.
+EUX_TEST(return_kinds_and_response_wire_round_trip) {
+  DefaultUcxMemoryResourceManager mr;
+  RpcDispatcher d("kinds");
+  int side_effect = 0;
+  d.RegisterFunction(function_id_t{1}, [&](int32_t v) { side_effect = v; }, data::string("void_fn"));
+  d.RegisterFunction(function_id_t{2}, [](double x) { return x * 0.5; }, data::string("half"));
+  d.RegisterFunction(function_id_t{3}, [](int32_t a) { return std::tuple<int32_t, data::string, bool>(a + 1, data::string("ok"), true); }, data::string("triple"));
+  d.RegisterFunction(function_id_t{4}, [](const RpcRequestHeader& rq, const RpcResponseBuilder& b) {
+    return b.PrepareResponse(rq.session_id, rq.request_id, data::vector<int64_t>{1, 2, 3});
+  }, data::string("header_only"));
+  d.RegisterFunction(function_id_t{5}, [&mr](const RpcRequestHeader& rq, const RpcResponseBuilder& b) {
+    UcxBuffer out(mr, ucx_memory_type::HOST, 24);
+    std::memset(out.data(), 7, 24);
+    return b.PrepareResponse(rq.session_id, rq.request_id, int32_t(24), std::move(out));
+  }, data::string("header_and_payload"));
+  d.RegisterFunction(function_id_t{6}, [&mr] { return UcxBuffer(mr, ucx_memory_type::HOST, 40); }, data::string("payload_only"));
+  RpcRequestBuilder rb;
+  auto call = [&](uint32_t fid, auto... args) {
+    return d.Dispatch(Serialize(rb.PrepareRequest({session_id_t{3}, request_id_t{fid * 10}, function_id_t{fid}}, args...)));
+  };
+  auto r1 = call(1, int32_t(17));
+  CHECK(r1.header.status.ok() && r1.header.results.empty() && side_effect == 17);
+  CHECK(std::holds_alternative<std::monostate>(r1.payload));
+  CHECK_EQ(call(2, 5.0).header.GetPrimitive<double>(0), 2.5);
+  auto r3 = call(3, int32_t(9));
+  CHECK_EQ(r3.header.results.size(), 3u);
+  CHECK(r3.header.GetPrimitive<int32_t>(0) == 10 && r3.header.GetString(1) == "ok" && r3.header.GetPrimitive<bool>(2));
+  auto r4 = call(4);
+  CHECK((r4.header.GetVector<int64_t>(0) == data::vector<int64_t>{1, 2, 3}));
+  CHECK_EQ(r4.header.request_id.v_, 40u);
+  auto r5 = call(5);
+  CHECK_EQ(r5.header.GetPrimitive<int32_t>(0), 24);
+  CHECK_EQ(std::get<UcxBuffer>(r5.payload).size(), 24u);
+  CHECK_EQ(static_cast<unsigned char*>(std::get<UcxBuffer>(r5.payload).data())[23], 7);
+  CHECK_EQ(std::get<UcxBuffer>(call(6).payload).size(), 40u);
+  // the response header through its wire form, in all three serialising overloads
+  byte_buf bytes = RpcDispatcher::SerializeResponse(r3.header);
+  byte_buf bytes2;
+  RpcDispatcher::SerializeResponse(r3.header, bytes2);
+  CHECK(bytes == bytes2);
+  RpcResponseHeader back = RpcDispatcher::DeserializeResponse(bytes.data(), bytes.size());
+  CHECK(back.session_id.v_ == 3 && back.request_id.v_ == 30 && back.status.ok());
+  CHECK(back.GetPrimitive<int32_t>(0) == 10 && back.GetString(1) == "ok" && back.GetPrimitive<bool>(2));
+  eux::ucxx::UcxHeader hdr(mr, bytes.size());
+  std::memcpy(hdr.data(), bytes.data(), bytes.size());
+  RpcResponseHeader back2 = RpcDispatcher::DeerializeResponse(std::move(hdr));
+  CHECK(back2.GetString(1) == "ok");
+  // an error response keeps its category and text on the wire
+  RpcResponseHeader err = RpcResponseBuilder{}.PrepareError(session_id_t{1}, request_id_t{2}, make_error_code(RpcErrc::UNAVAILABLE), "try later");
+  byte_buf eb = RpcDispatcher::SerializeResponse(err);
+  RpcResponseHeader eback = RpcDispatcher::DeserializeResponse(eb.data(), eb.size());
+  CHECK(!eback.status.ok());
+  CHECK_EQ(eback.status.value, int(RpcErrc::UNAVAILABLE));
+  CHECK(std::string(eback.status.category_name) == "RPC" && eback.GetString(0) == "try later");
+}
+
+// The function table: queries, removal, names, member functions, ad-hoc calls.
+EUX_TEST(registry_queries_and_adhoc) {
+  struct Counter {
+    int total = 0;
+    int add(int v) { return total += v; }
+  } counter;
+  RpcDispatcher d("table");
+  CHECK_EQ(d.FunctionCount(), 0u);
+  CHECK(!d.IsRegistered(function_id_t{1}));
+  CHECK(!d.GetSignature(function_id_t{1}).has_value());
+  CHECK(d.RegisterFunction(function_id_t{1}, &Counter::add, &counter, data::string("counter.add")));
+  CHECK(d.RegisterFunction(function_id_t{2}, [](const data::vector<double>& v) { return double(v.size()); }, data::string("len")));
+  CHECK(d.IsRegistered(function_id_t{1}) && d.IsRegistered(function_id_t{2}));
+  CHECK_EQ(d.FunctionCount(), 2u);
+  RpcRequestBuilder rb;
+  CHECK_EQ(d.Dispatch(rb.PrepareRequest({{}, {}, function_id_t{1}}, int(5))).header.GetPrimitive<int>(0), 5);
+  CHECK_EQ(d.Dispatch(rb.PrepareRequest({{}, {}, function_id_t{1}}, int(6))).header.GetPrimitive<int>(0), 11);
+  CHECK_EQ(counter.total, 11);
+  auto by_name = d.GetSignature("len");
+  CHECK(by_name.has_value() && by_name->id.v_ == 2);
+  CHECK((by_name->param_types == data::vector<ParamType>{ParamType::VECTOR_FLOAT64}));
+  CHECK(!d.GetSignature("nothing").has_value());
+  auto blob = d.GetAllSignatures();
+  auto sigs = RpcDispatcher::DeserializeSignatures(blob.data(), blob.size());
+  CHECK_EQ(sigs.size(), 2u);
+  bool seen_add = false, seen_len = false;
+  for (auto& sg : sigs) {
+    seen_add = seen_add || (sg.function_name == "counter.add" && sg.id.v_ == 1 && sg.instance_name == "table");
+    seen_len = seen_len || (sg.function_name == "len" && sg.return_types == data::vector<ParamType>{ParamType::PRIMITIVE_FLOAT64});
+  }
+  CHECK(seen_add && seen_len);
+  CHECK(d.UnregisterFunction(function_id_t{1}));
+  CHECK(!d.UnregisterFunction(function_id_t{1}));
+  CHECK_EQ(d.FunctionCount(), 1u);
+  CHECK_EQ(d.Dispatch(rb.PrepareRequest({{}, {}, function_id_t{1}}, int(1))).header.status.value, int(RpcErrc::NOT_FOUND));
+  // a callable that was never registered, filled from the same header
+  auto adhoc = d.DispatchAdhoc([](int32_t a, const data::string& s) { return data::string(s.str() + std::to_string(a)); },
+                               rb.PrepareRequest({session_id_t{9}, request_id_t{8}, function_id_t{777}}, int32_t(4), data::string("n=")));
+  CHECK(adhoc.header.status.ok() && adhoc.header.GetString(0) == "n=4");
+  CHECK_EQ(adhoc.header.session_id.v_, 9u);
+  CHECK_EQ(d.FunctionCount(), 1u);
+}
+
+// Every allocation made on behalf of a call is returned: a memory manager that counts.
+EUX_TEST(dispatch_returns_all_memory) {
+  struct Tracking : DefaultUcxMemoryResourceManager {
+    std::atomic<long> live{0}, total{0};
+    void* allocate(ucx_memory_type_t t, size_t n, size_t a = 8) override {
+      ++live, ++total;
+      return DefaultUcxMemoryResourceManager::allocate(t, n, a);
+    }
+    void deallocate(ucx_memory_type_t t, void* p, size_t n, size_t a = 8) override {
+      if (p) --live;
+      DefaultUcxMemoryResourceManager::deallocate(t, p, n, a);
+    }
+  } mr;
+  {
+    RpcDispatcher d("mem");
+    d.RegisterFunction(function_id_t{1}, [&mr](const TensorMeta& m, const UcxBuffer& in) {
+      UcxBufferVec out(mr, ucx_memory_type::HOST, std::vector<size_t>{in.size(), in.size() / 2});
+      return std::tuple<int64_t, UcxBufferVec>(m.shape[0], std::move(out));
+    }, data::string("split"));
+    d.RegisterFunction(function_id_t{2}, [](UcxBufferVec taken) { return uint64_t(taken.size()); }, data::string("take"));
+    TensorMeta m;
+    m.ndim = 1;
+    m.shape = {64};
+    m.strides = {1};
+    for (int round = 0; round < 50; ++round) {
+      UcxBuffer in(mr, ucx_memory_type::HOST, 64);
+      auto r = d.Dispatch(RpcRequestBuilder{}.PrepareRequest({{}, request_id_t{uint32_t(round)}, function_id_t{1}}, m), in);
+      CHECK(r.header.status.ok());
+      CHECK_EQ(std::get<UcxBufferVec>(r.payload).size(), 2u);
+      auto r2 = d.DispatchMove(RpcRequestBuilder{}.PrepareRequest({{}, {}, function_id_t{2}}), std::move(std::get<UcxBufferVec>(r.payload)));
+      CHECK_EQ(r2.header.GetPrimitive<uint64_t>(0), 2u);
+      // a failing call must not keep anything either
+      UcxBuffer unused(mr, ucx_memory_type::HOST, 8);
+      CHECK(!d.Dispatch(RpcRequestBuilder{}.PrepareRequest({{}, {}, function_id_t{404}}), unused).header.status.ok());
+    }
+  }
+  CHECK(mr.total.load() >= 200);
+  CHECK_EQ(mr.live.load(), 0);
+}
+
+// The clock a request carries and the clock of its response, across a chain of services:
+// A calls B, B calls C and D (fork), joins their answers and replies. Every effect is later than its cause.
+EUX_TEST(hlc_causality_through_dispatch_chain) {
+  using eux::rpc::utils::HybridLogicalClock;
+  struct Node {
+    HybridLogicalClock clock;
+    RpcDispatcher disp;
+    uint64_t wall;
+    explicit Node(const char* name, uint64_t wall_ms) : clock(wall_ms, 0), disp(name), wall(wall_ms) {}
+    HybridLogicalClock tick() {
+      clock.TickLocal(wall);
+      return clock;
+    }
+    HybridLogicalClock observe(HybridLogicalClock remote) {
+      clock.Merge(remote, wall);
+      return clock;
+    }
+  };
+  // wall clocks disagree on purpose: C is 40 ms behind, D 15 ms ahead
+  Node a("a", 10'000), b("b", 10'003), c("c", 9'960), dnode("d", 10'015);
+  auto leaf = [](Node& n) {
+    return [&n](const RpcRequestHeader& rq, int32_t v) {
+      n.observe(rq.hlc);
+      RpcResponseBuilder rb(n.tick());
+      return rb.PrepareResponse(rq.session_id, rq.request_id, int32_t(v * 2));
+    };
+  };
+  c.disp.RegisterFunction(function_id_t{1}, leaf(c), data::string("leaf"));
+  dnode.disp.RegisterFunction(function_id_t{1}, leaf(dnode), data::string("leaf"));
+  std::vector<uint64_t> order;  // raw clocks in causal order of one path
+  b.disp.RegisterFunction(function_id_t{1}, [&](const RpcRequestHeader& rq, int32_t v) {
+    order.push_back(b.observe(rq.hlc).Raw());
+    RpcRequestBuilder rb;
+    auto to_c = rb.PrepareRequest({rq.session_id, request_id_t{1}, function_id_t{1}, b.tick()}, v);
+    auto to_d = rb.PrepareRequest({rq.session_id, request_id_t{2}, function_id_t{1}, b.tick()}, int32_t(v + 1));
+    CHECK(to_d.hlc > to_c.hlc);
+    auto from_c = c.disp.Dispatch(Serialize(to_c));
+    auto from_d = dnode.disp.Dispatch(Serialize(to_d));
+    CHECK(from_c.header.hlc > to_c.hlc);
+    CHECK(from_d.header.hlc > to_d.hlc);
+    b.observe(from_c.header.hlc);
+    auto joined = b.observe(from_d.header.hlc);
+    CHECK(joined > from_c.header.hlc && joined > from_d.header.hlc);
+    order.push_back(joined.Raw());
+    RpcResponseBuilder out(b.tick());
+    return out.PrepareResponse(rq.session_id, rq.request_id, int32_t(from_c.header.GetPrimitive<int32_t>(0) + from_d.header.GetPrimitive<int32_t>(0)));
+  }, data::string("fan_out"));
+  HybridLogicalClock sent = a.tick();
+  order.push_back(sent.Raw());
+  auto reply = b.disp.Dispatch(Serialize(RpcRequestBuilder{}.PrepareRequest({session_id_t{1}, request_id_t{7}, function_id_t{1}, sent}, int32_t(5))));
+  CHECK(reply.header.status.ok());
+  CHECK_EQ(reply.header.GetPrimitive<int32_t>(0), 10 + 12);
+  CHECK(reply.header.hlc > sent);
+  order.push_back(reply.header.hlc.Raw());
+  order.push_back(a.observe(reply.header.hlc).Raw());
+  for (size_t i = 1; i < order.size(); ++i) CHECK(order[i] > order[i - 1]);
+  // the node whose wall clock is behind never issued a stamp earlier than what it had seen
+  CHECK(c.clock > sent);
+  // hlc travels in the wire image
+  auto req = RpcRequestBuilder{}.PrepareRequest({session_id_t{1}, request_id_t{1}, function_id_t{1}, HybridLogicalClock(123456, 7), workflow_id_t{44}}, int32_t(1));
+  auto round = Deserialize<RpcRequestHeader>(Serialize(req));
+  CHECK(round.hlc == HybridLogicalClock(123456, 7));
+  CHECK_EQ(round.workflow_id.v_, 44u);
+}
+
+// Ordering, packing and merge rules of the clock on their own.
+EUX_TEST(hybrid_logical_clock_rules) {
+  using eux::rpc::utils::HybridLogicalClock;
+  HybridLogicalClock z;
+  CHECK_EQ(z.Raw(), 0u);
+  HybridLogicalClock p(77, 3);
+  CHECK(p.PhysicalTimeMs() == 77 && p.LogicalCounter() == 3);
+  CHECK(HybridLogicalClock(p.Raw()) == p);
+  CHECK(HybridLogicalClock(77, 4) > p && HybridLogicalClock(78, 0) > HybridLogicalClock(77, 0xffff));
+  CHECK(p != HybridLogicalClock(77, 4));
+  // local tick: wall clock ahead -> adopt it, counter 0; not ahead -> counter + 1
+  HybridLogicalClock l(100, 9);
+  l.TickLocal(150);
+  CHECK(l == HybridLogicalClock(150, 0));
+  l.TickLocal(150);
+  CHECK(l == HybridLogicalClock(150, 1));
+  l.TickLocal(120);  // the wall clock went backwards: the stamp does not
+  CHECK(l == HybridLogicalClock(150, 2));
+  // merge: the largest of local, remote and wall wins; ties on the physical part take the larger counter + 1
+  HybridLogicalClock m(200, 5);
+  m.Merge(HybridLogicalClock(200, 9), 100);
+  CHECK(m == HybridLogicalClock(200, 10));
+  m.Merge(HybridLogicalClock(150, 99), 100);  // an older remote: only the local counter moves
+  CHECK(m == HybridLogicalClock(200, 11));
+  m.Merge(HybridLogicalClock(300, 4), 100);  // a newer remote
+  CHECK(m == HybridLogicalClock(300, 5));
+  m.Merge(HybridLogicalClock(250, 0), 400);  // the wall clock is ahead of both
+  CHECK(m == HybridLogicalClock(400, 0));
+  m.Merge(m.Raw());  // raw form, real wall clock: never goes back
+  CHECK(m.PhysicalTimeMs() >= 400);
+  HybridLogicalClock r;
+  r.AssignRaw((55ull << 16) | 6);
+  CHECK(r == HybridLogicalClock(55, 6));
+  // a long run of ticks under a frozen wall clock stays strictly increasing through the counter wrap
+  HybridLogicalClock f(1, 0xfff0);
+  uint64_t prev = f.Raw();
+  for (int i = 0; i < 64; ++i) {
+    f.TickLocal(1);
+    CHECK(f.Raw() > prev);
+    prev = f.Raw();
+  }
+  CHECK(f.PhysicalTimeMs() == 2);
 }
 
 EUX_TEST_MAIN()
