@@ -174,6 +174,10 @@ class AxonWorker {
   size_t ProcessStoredRequests(const StoredRequestVisitor& visitor);
 
   ucxx::UcxMemoryResourceManager& DefaultMemoryProvider() { return *mr_; }
+  // The contexts that run the two pipelines (null before StartServer / StartClient): a handler that returns a
+  // sender can complete it on the server's loop, e.g. with its scheduler's schedule_when_flag().
+  ucxx::ucx_am_context* server_context() noexcept { return server_ctx_.get(); }
+  ucxx::ucx_am_context* client_context() noexcept { return client_ctx_.get(); }
   rpc::utils::HybridLogicalClock CurrentHlc() const;
   size_t PendingRpcCount() const { return pending_rpcs_.size(); }
 

@@ -150,6 +150,39 @@ bool ucx_am_context::cancel_timer(timer_op* op) noexcept {
   return false;
 }
 
+void ucx_am_context::watch_flag(flag_op* op) noexcept {
+  op->armed = true;
+  flag_ops_.push_back(op);
+}
+
+bool ucx_am_context::unwatch_flag(flag_op* op) noexcept {
+  if (!op->armed) return false;
+  for (auto& slot : flag_ops_) {
+    if (slot == op) {
+      slot = flag_ops_.back();
+      flag_ops_.pop_back();
+      op->armed = false;
+      return true;
+    }
+  }
+  return false;
+}
+
+void ucx_am_context::poll_flags() noexcept {
+  for (size_t i = 0; i < flag_ops_.size();) {
+    flag_op* op = flag_ops_[i];
+    // an acquire load: what the writer stored before the word is visible once the value is seen
+    if (__atomic_load_n(const_cast<const uint64_t*>(op->flag), __ATOMIC_ACQUIRE) >= op->at_least) {
+      flag_ops_[i] = flag_ops_.back();
+      flag_ops_.pop_back();
+      op->armed = false;
+      schedule_local(op);
+    } else {
+      ++i;
+    }
+  }
+}
+
 void ucx_am_context::update_timers() noexcept {
   if (timers_.empty()) return;
   // the clock as read by the transport's last progress() call: deadlines are milliseconds, one loop
@@ -363,6 +396,7 @@ void ucx_am_context::run_loop(const std::function<bool()>& should_stop) {
     execute_pending_local();
     acquire_completion_queue_items();
     update_timers();
+    if (!flag_ops_.empty()) poll_flags();
     acquire_remote_queued_items();
     const int events = worker_->progress();
     if (!conn_requests_.empty()) reject_stale_requests();
@@ -389,6 +423,12 @@ void ucx_am_context::teardown() {
     while (!timers_.empty()) {
       timer_op* op = timers_.begin()->second;
       timers_.erase(timers_.begin());
+      op->armed = false;
+      schedule_local(op);
+    }
+    while (!flag_ops_.empty()) {
+      flag_op* op = flag_ops_.back();
+      flag_ops_.pop_back();
       op->armed = false;
       schedule_local(op);
     }

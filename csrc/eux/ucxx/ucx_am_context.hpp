@@ -130,6 +130,13 @@ class ucx_am_context {
     time_point due;
     bool armed = false;
   };
+  // Waits for a 64-bit word in host memory (normally mapped pinned memory that a kernel writes when its
+  // work is done) to reach a value. The loop looks at every watched word once per pass.
+  struct flag_op : operation_base {
+    const volatile uint64_t* flag = nullptr;
+    uint64_t at_least = 0;
+    bool armed = false;
+  };
   // An operation that parks until a message / connection event arrives.
   struct parked_op : operation_base {
     parked_op* prev_parked = nullptr;
@@ -191,6 +198,8 @@ class ucx_am_context {
   void schedule_remote(operation_base* op) noexcept;  // any thread
   void schedule_timer(timer_op* op) noexcept;
   bool cancel_timer(timer_op* op) noexcept;
+  void watch_flag(flag_op* op) noexcept;
+  bool unwatch_flag(flag_op* op) noexcept;
   void park_recv(parked_op* op) noexcept { park(recv_waiters_head_, recv_waiters_tail_, op); }
   void unpark_recv(parked_op* op) noexcept { unpark(recv_waiters_head_, recv_waiters_tail_, op); }
   void park_accept(parked_op* op) noexcept { park(accept_waiters_head_, accept_waiters_tail_, op); }
@@ -218,6 +227,7 @@ class ucx_am_context {
   void execute_pending_local() noexcept;
   void acquire_remote_queued_items() noexcept;
   void update_timers() noexcept;
+  void poll_flags() noexcept;
   void acquire_completion_queue_items() noexcept;
   void on_am(transport::AmArrival&& a);
   void on_endpoint_error(transport::Endpoint* ep, int status);
@@ -243,6 +253,7 @@ class ucx_am_context {
   operation_base* local_tail_ = nullptr;
   std::atomic<operation_base*> remote_head_{nullptr};
   std::multimap<time_point, timer_op*> timers_;
+  std::vector<flag_op*> flag_ops_;
   ucx_am_cqe_t cq_entries_[kCompletionQueueEntryCount];
   size_t cq_head_ = 0, cq_tail_ = 0;
 

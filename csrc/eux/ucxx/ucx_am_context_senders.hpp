@@ -207,6 +207,53 @@ class ucx_am_context::scheduler {
     }
   };
 
+  // Completes (with no value) on the context's thread once `*flag >= at_least`. `flag` is host memory that
+  // something outside the CPU's threads writes, typically mapped pinned memory into which a kernel
+  // release-stores a sequence number after its last store: a handler launches its kernel, returns this
+  // sender followed by what builds the reply, and no thread waits for the GPU. Cancellable; completes
+  // with done when the context stops. The word must stay valid until the sender has completed.
+  struct flag_sender {
+    using value_type = void;
+    ucx_am_context* ctx;
+    const volatile uint64_t* flag;
+    uint64_t at_least;
+    template <class R>
+    struct op : detail::io_op_base<op<R>, R> {
+      using base = detail::io_op_base<op<R>, R>;
+      struct my_flag : ucx_am_context::flag_op {
+        op* self = nullptr;
+      } watch;
+      bool armed_once = false;
+      bool reached() const noexcept { return __atomic_load_n(const_cast<const uint64_t*>(watch.flag), __ATOMIC_ACQUIRE) >= watch.at_least; }
+      op(ucx_am_context* c, const volatile uint64_t* f, uint64_t v, R&& r_) : base(*c, std::move(r_)) {
+        watch.self = this;
+        watch.flag = f;
+        watch.at_least = v;
+        watch.execute = [](ucx_am_context::operation_base* b) noexcept { static_cast<my_flag*>(b)->self->fired(); };
+      }
+      void step() noexcept {
+        if (armed_once) return;
+        armed_once = true;
+        if (reached()) {
+          fired();
+          return;
+        }
+        this->ctx.watch_flag(&watch);
+      }
+      void fired() noexcept {
+        if (this->finished) return;
+        if (this->ctx.stopping() && !reached()) this->finish([this] { this->r.set_done(); });
+        else this->finish([this] { this->r.set_value(); });
+      }
+      bool try_cancel() noexcept { return !armed_once || this->ctx.unwatch_flag(&watch); }
+    };
+    template <class R>
+    auto connect(R&& r) const {
+      return op<std::decay_t<R>>(ctx, flag, at_least, std::decay_t<R>(std::forward<R>(r)));
+    }
+  };
+  flag_sender schedule_when_flag(const volatile uint64_t* flag, uint64_t at_least) const noexcept { return {ctx_, flag, at_least}; }
+
   schedule_sender schedule() const noexcept { return {ctx_}; }
   schedule_at_sender schedule_at(time_point tp) const noexcept { return {ctx_, tp, false, {}}; }
   template <class Rep, class Period>

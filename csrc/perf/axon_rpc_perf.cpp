@@ -75,9 +75,14 @@ static std::unique_ptr<eux::ucxx::UcxAutoDeviceContext> make_dev(const Options& 
 }
 
 // y = x + 1 on the device, on a stream of the calling thread. The kernel publishes a sequence number in
-// mapped pinned host memory when its stores are done and the thread watches that word: no call into the
-// driver while it waits, so handlers on other threads and the transport's launches are not held up.
-static void device_plus_one(const void* x, void* y, size_t bytes, int device) {
+// mapped pinned host memory when its stores are done; the caller gets the word and the number to wait for.
+// Nobody calls into the driver to wait, so handlers on other threads and the transport's launches are
+// not held up. Kernels of one thread run in order on its stream, so its numbers are reached in order.
+struct DeviceDone {
+  const volatile uint64_t* flag;
+  uint64_t seq;
+};
+static DeviceDone device_plus_one_start(const void* x, void* y, size_t bytes, int device) {
   thread_local cudaStream_t st = nullptr;
   thread_local uint32_t* counter = nullptr;
   thread_local uint64_t* flag_host = nullptr;
@@ -104,43 +109,41 @@ static void device_plus_one(const void* x, void* y, size_t bytes, int device) {
   d.flag_value = ++seq;
   int rc = eux_xfer_launch(&d, counter, 0, st);
   if (rc != 0) throw std::runtime_error(std::string("handler kernel: ") + eux_error_string(rc));
-  const auto give_up = clk::now() + std::chrono::seconds(5);
-  while (*static_cast<volatile uint64_t*>(flag_host) != seq) {
-    if (clk::now() > give_up) {
-      if (cudaStreamSynchronize(st) != cudaSuccess) throw std::runtime_error("handler kernel failed");
-      break;
-    }
-  }
-  std::atomic_thread_fence(std::memory_order_acquire);
+  return {flag_host, seq};
 }
 
 static void register_plus_one(AxonRuntime& rt, const Options& o) {
   auto mr = rt.memory_resource();
-  const bool cuda = o.cuda;
-  const int dev = o.device;
-  auto handler = [mr, cuda, dev](const TensorMeta& m, UcxBuffer& buf) {
-    UcxBuffer out(*mr, buf.type(), buf.size());
-    if (cuda) {
-      device_plus_one(buf.data(), out.data(), buf.size(), dev);
-    } else {
+  if (!o.cuda) {
+    auto handler = [mr](const TensorMeta& m, UcxBuffer& buf) {
+      UcxBuffer out(*mr, buf.type(), buf.size());
       const float* f = static_cast<const float*>(buf.data());
       float* g = static_cast<float*>(out.data());
       for (int64_t i = 0; i < m.shape[0]; ++i) g[i] = f[i] + 1.0f;
-    }
-    return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out));
-  };
-  if (cuda) {
-    CustomMemoryPolicy<UcxBuffer> provider = [mr](eux::rpc::utils::TensorMetaSpan metas) {
-      return UcxBuffer(*mr, ucx_memory_type::CUDA, eux::rpc::utils::CalculateTensorSize(metas[0]));
+      return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out));
     };
-    eux::axon::ServerMemoryPolicy mp;
-    mp.on_host = false;
-    mp.buffer_provider = provider;
-    mp.provider_inline = true;  // a block from the memory manager's pool: nothing that could hold up the context's thread
-    rt.worker().RegisterFunction(function_id_t{1}, handler, "plus_one", std::move(mp), MessageLifecyclePolicy{});
-  } else {
     rt.RegisterFunction(function_id_t{1}, handler, "plus_one");
+    return;
   }
+  // Device tensors: the handler launches its kernel and returns a sender that the server's loop completes
+  // when the kernel's flag shows up; the reply is built there. No thread waits for the GPU.
+  const int dev = o.device;
+  auto* worker = &rt.worker();
+  auto handler = [mr, dev, worker](const TensorMeta& m, UcxBuffer& buf) {
+    UcxBuffer out(*mr, buf.type(), buf.size());
+    const DeviceDone done = device_plus_one_start(buf.data(), out.data(), buf.size(), dev);
+    auto sched = worker->server_context()->get_scheduler();
+    return ex::then(sched.schedule_when_flag(done.flag, done.seq),
+                    [m, out = std::move(out)]() mutable { return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out)); });
+  };
+  CustomMemoryPolicy<UcxBuffer> provider = [mr](eux::rpc::utils::TensorMetaSpan metas) {
+    return UcxBuffer(*mr, ucx_memory_type::CUDA, eux::rpc::utils::CalculateTensorSize(metas[0]));
+  };
+  eux::axon::ServerMemoryPolicy mp;
+  mp.on_host = false;
+  mp.buffer_provider = provider;
+  mp.provider_inline = true;  // a block from the memory manager's pool: nothing that could hold up the context's thread
+  rt.worker().RegisterFunction(function_id_t{1}, handler, "plus_one", std::move(mp), MessageLifecyclePolicy{});
 }
 
 static ClientMemoryPolicy client_policy(AxonRuntime& rt, const Options& o) {

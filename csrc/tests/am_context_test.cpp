@@ -71,6 +71,47 @@ EUX_TEST(schedule_and_timers) {
   CHECK(std::chrono::steady_clock::now() - t0 < 2s);
 }
 
+// A word in host memory that somebody else writes (a kernel, through mapped pinned memory; here a thread).
+EUX_TEST(wait_for_a_flag_word) {
+  Runner a("a");
+  auto sch = a.ctx.get_scheduler();
+  alignas(64) static uint64_t word = 0;
+  static int published = 0;
+  word = 0;
+  published = 0;
+  const volatile uint64_t* flag = &word;
+  std::thread writer([] {
+    std::this_thread::sleep_for(15ms);
+    published = 42;
+    __atomic_store_n(&word, uint64_t(7), __ATOMIC_RELEASE);
+  });
+  auto t0 = std::chrono::steady_clock::now();
+  CHECK(ex::sync_wait(sch.schedule_when_flag(flag, 7)).has_value());
+  CHECK(std::chrono::steady_clock::now() - t0 >= 14ms);
+  CHECK_EQ(published, 42);  // what was written before the word is visible after it
+  writer.join();
+  // already there: completes at once, also for a smaller value
+  CHECK(ex::sync_wait(sch.schedule_when_flag(flag, 7)).has_value());
+  CHECK(ex::sync_wait(sch.schedule_when_flag(flag, 3)).has_value());
+  // never reached: the wait can be cancelled, and the context still serves afterwards
+  t0 = std::chrono::steady_clock::now();
+  CHECK(!ex::sync_wait(ex::stop_when(sch.schedule_when_flag(flag, 1000), sch.schedule_after(10ms))).has_value());
+  CHECK(std::chrono::steady_clock::now() - t0 < 2s);
+  // several waiters on a counter that grows: each completes once its value is reached
+  std::atomic<int> done8{0}, done9{0};
+  ex::async_scope scope;
+  scope.spawn_detached(ex::then(sch.schedule_when_flag(flag, 8), [&] { done8 = 1; }));
+  scope.spawn_detached(ex::then(sch.schedule_when_flag(flag, 9), [&] { done9 = 1; }));
+  std::this_thread::sleep_for(5ms);
+  CHECK(done8 == 0 && done9 == 0);
+  __atomic_store_n(&word, uint64_t(8), __ATOMIC_RELEASE);
+  for (int i = 0; i < 200 && !done8; ++i) std::this_thread::sleep_for(1ms);
+  CHECK(done8 == 1 && done9 == 0);
+  __atomic_store_n(&word, uint64_t(9), __ATOMIC_RELEASE);
+  ex::sync_wait(scope.join());
+  CHECK(done9 == 1);
+}
+
 EUX_TEST(accept_cancelled_by_stop_token) {
   Runner srv("srv", true);
   auto acc = accept_endpoint(srv.ctx.get_scheduler(), free_port());
