@@ -32,3 +32,26 @@ def test_pytorch_cuda_example(cuda_device):
     out = _run("execution_ucx_b200.axon.examples.pytorch_cuda_example")
     assert out.returncode == 0, out.stderr[-2000:]
     assert out.stdout.count("same object as the policy's tensor: True") == 2
+
+
+def test_text_trace_of_the_rpc_phases():
+    """EUX_TRACE=1 writes the begin and end of every RPC phase to stderr, in the order a call goes through them."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), EUX_TRACE="1")
+    out = subprocess.run([sys.executable, "-m", "execution_ucx_b200.axon.examples.pytorch_example"], env=env, cwd=str(ROOT),
+                         capture_output=True, text=True, timeout=180)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln.split() for ln in out.stderr.splitlines() if ln.startswith("eux-trace ")]
+    assert lines and all(len(ln) == 5 and ln[1] in ("B", "E", "M") and ln[3].isdigit() for ln in lines)
+    lines.sort(key=lambda ln: int(ln[3]))  # several threads write: order by the clock, not by arrival
+    names = [(ln[1], ln[2]) for ln in lines]
+    # one call: the client starts it, the server dispatches it, the handler runs on the loop, the reply leaves
+    # and the result is handed to the awaiting caller
+    chain = [("B", "axon.client.invoke"), ("B", "axon.server.dispatch"), ("B", "axon.python.handler_on_loop"),
+             ("B", "axon.server.send_response"), ("B", "axon.python.result_on_loop")]
+    pos = 0
+    for step in chain:
+        assert step in names[pos:], (step, names[:40])
+        pos = names.index(step, pos) + 1
+    stamps = [int(ln[3]) for ln in lines]
+    assert max(stamps) > min(stamps)
+    assert sum(1 for k, _ in names if k == "B") == sum(1 for k, _ in names if k == "E")
