@@ -18,6 +18,15 @@ OP_NONE, OP_ADD, OP_MUL = 0, 1, 2
 ST_OK, ST_TIMEOUT, ST_BAD_ARG, ST_OVERFLOW = 0, 1, 2, 3
 
 
+PULL_BATCH_MAX = 48
+
+
+class PullItem(C.Structure):
+    """eux_pull_item: one dense copy of a batch whose descriptors travel in the launch parameters."""
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("nbytes", C.c_uint64), ("flag", C.c_void_p),
+                ("flag_value", C.c_uint64)]
+
+
 class XferDesc(C.Structure):
     _fields_ = [
         ("src", C.c_void_p), ("dst", C.c_void_p), ("n_elems", C.c_uint64),
@@ -82,6 +91,7 @@ def load():
     lib.eux_xfer_bulk_launch.argtypes = [C.POINTER(XferDesc), P, I, P]
     lib.eux_xfer_rpc_step_launch.argtypes = [C.POINTER(XferDesc), C.POINTER(XferDesc), C.POINTER(XferDesc), P, I, P]
     lib.eux_xfer_batch_launch.argtypes = [P, I, P]
+    lib.eux_xfer_pull_batch_launch.argtypes = [C.POINTER(PullItem), I, P]
     lib.eux_pingpong_launch.argtypes = [C.POINTER(PingPongDesc), I, P]
     lib.eux_ipc_export.argtypes = [P, C.c_char_p]
     lib.eux_ipc_open.argtypes = [C.c_char_p, C.POINTER(P)]

@@ -161,6 +161,24 @@ def push_batch(descs, stream_ptr: Optional[int] = None) -> None:
     _launches += 1
 
 
+def pull_batch(items, stream_ptr: Optional[int] = None) -> None:
+    """Up to 48 dense copies in one launch, one CTA each, the descriptors in the launch parameters (nothing
+    is read from memory to find the work). `items`: (src_ptr, dst_ptr, nbytes, flag_ptr or 0, flag_value); a
+    copy's flag is written when that copy is done. This is what the transport uses for the small messages of
+    one pass of its loop."""
+    global _launches
+    n = len(items)
+    if n == 0:
+        return
+    arr = (_native.PullItem * n)()
+    for i, (src, dst, nbytes, flag, value) in enumerate(items):
+        arr[i].src, arr[i].dst, arr[i].nbytes, arr[i].flag, arr[i].flag_value = src, dst, nbytes, flag or None, value
+    lib = _native.load()
+    _native.check(lib.eux_xfer_pull_batch_launch(arr, n, C.c_void_p(stream_ptr or _native.current_stream_ptr())),
+                  "eux_xfer_pull_batch_launch")
+    _launches += 1
+
+
 def pingpong(local_buf: torch.Tensor, peer_buf_ptr: int, nbytes: int, local_flag_ptr: int, peer_flag_ptr: int,
              grid_bar: torch.Tensor, iters: int, initiator: int, base_seq: int = 0, ts_out: Optional[torch.Tensor] = None,
              status: Optional[torch.Tensor] = None, ctas: int = 0, wait_timeout_ns: int = 2_000_000_000) -> None:

@@ -96,6 +96,32 @@ def test_batch_large_raw_copies(cuda_device):
         assert torch.equal(d, s)
 
 
+def test_pull_batch_items_in_launch_parameters(cuda_device):
+    """The transport's batched pull: every item is copied whole (aligned or not, empty, a few bytes, many
+    blocks) and publishes its own flag value; more than the maximum per launch is refused."""
+    from execution_ucx_b200.ops import _native, tensor_xfer as tx
+    sizes = [0, 1, 15, 16, 17, 4096, 65536, 65536 + 3, 262144, 100_000] + [512 * (i + 1) for i in range(30)]
+    assert len(sizes) <= _native.PULL_BATCH_MAX
+    flags = torch.zeros(len(sizes), dtype=torch.int64, device=cuda_device)
+    srcs, dsts, items = [], [], []
+    for i, n in enumerate(sizes):
+        off_s, off_d = (i % 3) * 5, (i % 4) * 3          # some of the buffers are not 16-byte aligned
+        s = torch.randint(0, 255, (n + 64,), dtype=torch.uint8, device=cuda_device)
+        d = torch.full((n + 64,), 7, dtype=torch.uint8, device=cuda_device)
+        srcs.append(s[off_s: off_s + n]), dsts.append((d, off_d, n))
+        items.append((s.data_ptr() + off_s, d.data_ptr() + off_d, n, flags.data_ptr() + 8 * i, 1000 + i))
+    for rnd in range(2):
+        tx.pull_batch(items)
+        torch.cuda.synchronize()
+        for i, (s, (d, off, n)) in enumerate(zip(srcs, dsts)):
+            assert torch.equal(d[off: off + n], s)
+            assert bool((d[:off] == 7).all()) and bool((d[off + n:] == 7).all())   # nothing written outside
+            assert int(flags[i]) == 1000 + i
+        flags.zero_()
+    with pytest.raises(RuntimeError):
+        tx.pull_batch(items + items)
+
+
 def test_bounded_wait_reports_timeout(cuda_device):
     """A wait that nothing satisfies ends by itself with a status, not a hang."""
     from execution_ucx_b200.ops import tensor_xfer as tx
