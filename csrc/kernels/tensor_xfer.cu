@@ -592,7 +592,10 @@ extern "C" int eux_xfer_bulk_launch(const eux_xfer_desc* d, uint32_t* scratch_co
 struct PullBatchArgs {
   eux_pull_item it[EUX_PULL_BATCH_MAX];
 };
-__global__ void __launch_bounds__(256) xfer_pull_batch_kernel(const __grid_constant__ PullBatchArgs a) {
+// 1024 threads: a 64 KiB message is in flight at once (four 16-byte vectors per thread), so its CTA needs one
+// memory round trip for it and not four; the launch is as long as its largest item.
+constexpr int kPullBatchThreads = 1024;
+__global__ void __launch_bounds__(kPullBatchThreads) xfer_pull_batch_kernel(const __grid_constant__ PullBatchArgs a) {
   const eux_pull_item& d = a.it[blockIdx.x];
   const unsigned char* src = reinterpret_cast<const unsigned char*>(d.src);
   unsigned char* dst = reinterpret_cast<unsigned char*>(d.dst);
@@ -617,7 +620,7 @@ extern "C" int eux_xfer_pull_batch_launch(const eux_pull_item* items, int n, voi
     a.it[i] = items[i];
   }
   for (int i = n; i < EUX_PULL_BATCH_MAX; ++i) a.it[i] = eux_pull_item{};
-  xfer_pull_batch_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(a);
+  xfer_pull_batch_kernel<<<n, kPullBatchThreads, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
 

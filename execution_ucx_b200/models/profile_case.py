@@ -4,6 +4,7 @@
     python -m execution_ucx_b200.models.profile_case --kernel gemm_fp8   (or gemm_mx)
     python -m execution_ucx_b200.models.profile_case --kernel xfer
     python -m execution_ucx_b200.models.profile_case --kernel moe
+    python -m execution_ucx_b200.models.profile_case --kernel pull_batch  (the transport's batched small pulls)
 
 Each case keeps well under a few GB on the device, uses inputs larger than L2
 where DRAM figures matter, and launches the kernel of interest a handful of times.
@@ -17,7 +18,7 @@ import torch
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "moe", "moe_fp8"], required=True)
+    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "pull_batch", "moe", "moe_fp8"], required=True)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -66,6 +67,19 @@ def main() -> None:
         for i in range(args.iters):
             tx.push(src, dst, flag_ptr=flag.data_ptr(), flag_value=i + 1)
         torch.cuda.synchronize()
+    elif args.kernel == "pull_batch":
+        from ..ops import _native, tensor_xfer as tx
+        # one launch of the size the RPC storm produces: 48 messages, sizes log-uniform in 256 B - 64 KiB
+        g = torch.Generator(device="cpu").manual_seed(5)
+        sizes = [int(256 * (256.0 ** float(u))) // 4 * 4 for u in torch.rand(_native.PULL_BATCH_MAX, generator=g)]
+        flags = torch.zeros(len(sizes), dtype=torch.int64, device=dev)
+        srcs = [torch.randint(0, 255, (n,), dtype=torch.uint8, device=dev) for n in sizes]
+        dsts = [torch.empty_like(s) for s in srcs]
+        for it in range(args.iters):
+            tx.pull_batch([(s.data_ptr(), d.data_ptr(), s.numel(), flags.data_ptr() + 8 * i, it + 1)
+                           for i, (s, d) in enumerate(zip(srcs, dsts))])
+        torch.cuda.synchronize()
+        assert all(torch.equal(s, d) for s, d in zip(srcs, dsts))
     else:
         from ..ops import moe
         fp8 = args.kernel == "moe_fp8"
