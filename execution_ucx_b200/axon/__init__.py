@@ -256,7 +256,7 @@ class AxonRuntime(_axon.AxonRuntime):
         ret = hints.get("return", None)
         return_types, out_payload = _return_types(ret)
         order = list(sig.parameters)
-        tensor_names = [n for n, _ in tensor_params]
+        tensor_is_list = dict(tensor_params)   # parameter name -> takes a list of tensors
 
         async def wrapper(header, payload):
             values, metas, groups = [], [], None
@@ -272,8 +272,8 @@ class AxonRuntime(_axon.AxonRuntime):
             tensors = _tensors_from_payload(payload, metas, from_dlpack_fn)
             kwargs, vi, ti = {}, 0, 0
             for pname in order:
-                if pname in tensor_names:
-                    is_list = dict(tensor_params)[pname]
+                is_list = tensor_is_list.get(pname)
+                if is_list is not None:
                     if is_list:
                         take = groups.pop(0) if groups else len(tensors) - ti
                         kwargs[pname] = tensors[ti: ti + take]
