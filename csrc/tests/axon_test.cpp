@@ -313,6 +313,55 @@ EUX_TEST(inline_buffer_providers_run_on_the_context_threads) {
   for (auto id : handler_threads) CHECK(provider_threads.count(id) == 0);
 }
 
+EUX_TEST(inline_handlers_start_on_the_server_context_thread) {
+  // handler_inline: a handler that only starts asynchronous work is called on the server's context thread
+  // (the thread that also runs an inline buffer provider); without the flag it is called on a pool thread.
+  // Either way its sender may finish elsewhere, here on the pool, and the reply is the same.
+  Pair p;
+  ex::static_thread_pool elsewhere(1);
+  std::mutex mu;
+  std::thread::id inline_started, pooled_started, provider_thread;
+  auto make_handler = [&](std::thread::id& started) {
+    return [&, pstarted = &started](const TensorMeta& m, const UcxBuffer& b) {
+      {
+        std::lock_guard lk(mu);
+        *pstarted = std::this_thread::get_id();
+      }
+      const int64_t n = m.shape[0];
+      const float first = static_cast<const float*>(b.data())[0];
+      return ex::on(elsewhere.get_scheduler(), ex::just_from([n, first] { return std::tuple<int64_t, float>(n, first + 1.0f); }));
+    };
+  };
+  auto provider = [&](eux::rpc::utils::TensorMetaSpan metas) {
+    std::lock_guard lk(mu);
+    provider_thread = std::this_thread::get_id();
+    return UcxBuffer(*p.mr, ucx_memory_type::HOST, eux::rpc::utils::CalculateTensorSize(metas[0]));
+  };
+  eux::axon::ServerMemoryPolicy on_loop;
+  on_loop.on_host = false;
+  on_loop.provider_inline = true;
+  on_loop.handler_inline = true;
+  on_loop.buffer_provider = provider;
+  eux::axon::ServerMemoryPolicy on_pool = on_loop;
+  on_pool.handler_inline = false;
+  p.server.RegisterFunction(function_id_t{1}, make_handler(inline_started), "inline", std::move(on_loop));
+  p.server.RegisterFunction(function_id_t{2}, make_handler(pooled_started), "pooled", std::move(on_pool));
+  p.connect();
+  const int64_t n = 100000;  // rendezvous, so the provider runs
+  for (uint32_t fid : {1u, 2u}) {
+    UcxBuffer buf(*p.mr, ucx_memory_type::HOST, size_t(n) * 4);
+    static_cast<float*>(buf.data())[0] = 41.0f;
+    auto r = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{fid}, workflow_id_t{}, ClientMemoryPolicy{}, f32_meta(n), std::move(buf)));
+    CHECK(r && r->header.status.ok());
+    CHECK_EQ(r->header.GetPrimitive<int64_t>(0), n);
+    CHECK_EQ(r->header.GetPrimitive<float>(1), 42.0f);
+  }
+  std::lock_guard lk(mu);
+  CHECK(provider_thread != std::thread::id{});
+  CHECK(inline_started == provider_thread);
+  CHECK(pooled_started != provider_thread && pooled_started != std::thread::id{});
+}
+
 EUX_TEST(stop_client_cancels_pending_and_peer_loss_is_an_error) {
   auto p = std::make_unique<Pair>();
   p->server.RegisterFunction(function_id_t{1}, [](int32_t ms) {
