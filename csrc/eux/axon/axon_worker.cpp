@@ -91,8 +91,11 @@ void AxonWorker::StopClient() {
 }
 
 std::vector<std::byte> AxonWorker::GetLocalAddress() const {
+  // A client-only worker still has a reachable address (its client context listens too): peers that
+  // want to call back, or tools that only print it, get that one.
   std::vector<std::byte> a;
   if (server_ctx_) server_ctx_->get_ucp_address(a);
+  else if (client_ctx_) client_ctx_->get_ucp_address(a);
   return a;
 }
 

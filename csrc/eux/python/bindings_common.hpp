@@ -41,7 +41,8 @@ inline std::shared_ptr<py::object> gil_shared(py::object o) {
   });
 }
 
-py::object param_to_python(const rpc::ParamMeta& p);
+// decode_blobs: nested-list / string-list blobs (STRING parameters with a name tag) come back as lists
+py::object param_to_python(const rpc::ParamMeta& p, bool decode_blobs = true);
 rpc::ParamMeta python_to_param(py::handle v);
 rpc::ParamMeta python_to_param_typed(py::handle v, rpc::ParamType t);
 

@@ -505,10 +505,10 @@ void bind_runtime(py::module_& m) {
       .def("get_local_address", &PyAxonRuntime::get_local_address).def("get_local_signatures", &PyAxonRuntime::get_local_signatures)
       .def("register_endpoint_signatures", &PyAxonRuntime::register_endpoint_signatures)
       .def("connect_endpoint_async", &PyAxonRuntime::connect_endpoint_async, py::arg("ucp_address"), py::arg("worker_name"))
-      .def("register_function_raw", &PyAxonRuntime::register_function_raw, py::arg("function_id"), py::arg("function_name"), py::arg("param_types"),
+      .def("_register_native", &PyAxonRuntime::register_function_raw, py::arg("function_id"), py::arg("function_name"), py::arg("param_types"),
            py::arg("return_types"), py::arg("input_payload_type"), py::arg("return_payload_type"), py::arg("callable"),
            py::arg("memory_policy") = py::none(), py::arg("lifecycle_policy") = py::none())
-      .def("invoke_raw", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
+      .def("_invoke_native", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
            py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none())
       .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
       .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)

@@ -10,7 +10,63 @@ using rpc::ParamType;
 using rpc::TensorMeta;
 
 // ---- ParamMeta <-> Python ---------------------------------------------------------------
-py::object param_to_python(const ParamMeta& p) {
+namespace {
+// Nested lists and string lists travel as STRING parameters whose `name` says how to read the bytes
+// (reference: axon/python/src/param_conversion.cpp:38-67, 104-146):
+//   "nli64" / "nlf64" / "nlb":  [u32 groups][u32 size of each group][items: i64 / f64 / u8]
+//   "vs":                       [u32 count]{[u32 length][bytes]}
+// Returns a null object when the tag is not one of these or the bytes do not add up.
+py::object decode_tagged_blob(std::string_view tag, const char* d, size_t n) {
+  auto u32_at = [&](size_t off, uint32_t* v) {
+    if (off + 4 > n) return false;
+    std::memcpy(v, d + off, 4);
+    return true;
+  };
+  if (tag == "vs") {
+    uint32_t count = 0;
+    if (!u32_at(0, &count)) return {};
+    size_t off = 4;
+    py::list out;
+    for (uint32_t i = 0; i < count; ++i) {
+      uint32_t len = 0;
+      if (!u32_at(off, &len) || off + 4 + len > n) return {};
+      out.append(py::str(d + off + 4, len));
+      off += 4 + size_t(len);
+    }
+    return out;
+  }
+  const int kind = tag == "nli64" ? 0 : tag == "nlf64" ? 1 : tag == "nlb" ? 2 : -1;
+  if (kind < 0) return {};
+  uint32_t groups = 0;
+  if (!u32_at(0, &groups) || 4 + size_t(groups) * 4 > n) return {};
+  const size_t width = kind == 2 ? 1 : 8;
+  size_t off = 4 + size_t(groups) * 4;
+  py::list out;
+  for (uint32_t g = 0; g < groups; ++g) {
+    uint32_t sz = 0;
+    u32_at(4 + size_t(g) * 4, &sz);
+    if (off + size_t(sz) * width > n) return {};
+    py::list inner;
+    for (uint32_t i = 0; i < sz; ++i, off += width) {
+      if (kind == 0) {
+        int64_t v;
+        std::memcpy(&v, d + off, 8);
+        inner.append(py::int_(v));
+      } else if (kind == 1) {
+        double v;
+        std::memcpy(&v, d + off, 8);
+        inner.append(py::float_(v));
+      } else {
+        inner.append(py::bool_(d[off] != 0));
+      }
+    }
+    out.append(std::move(inner));
+  }
+  return out;
+}
+}  // namespace
+
+py::object param_to_python(const ParamMeta& p, bool decode_blobs) {
   return std::visit(
       [&](const auto& alt) -> py::object {
         using A = std::decay_t<decltype(alt)>;
@@ -41,6 +97,10 @@ py::object param_to_python(const ParamMeta& p) {
               },
               alt);
         } else if constexpr (std::is_same_v<A, rpc::data::string>) {
+          if (decode_blobs && p.type == ParamType::STRING && !p.name.empty()) {
+            py::object decoded = decode_tagged_blob(std::string_view(p.name.data(), p.name.size()), alt.data(), alt.size());
+            if (decoded) return decoded;
+          }
           PyObject* s = PyUnicode_DecodeUTF8(alt.data(), static_cast<Py_ssize_t>(alt.size()), nullptr);
           if (s) return py::reinterpret_steal<py::object>(s);
           PyErr_Clear();  // binary blob carried as a string parameter
@@ -182,7 +242,8 @@ void bind_types(py::module_& m) {
       .value("TENSOR_META_VEC", ParamType::TENSOR_META_VEC).value("UNKNOWN", ParamType::UNKNOWN);
   py::enum_<rpc::PayloadType>(m, "PayloadType")
       .value("UCX_BUFFER", rpc::PayloadType::UCX_BUFFER).value("UCX_BUFFER_VEC", rpc::PayloadType::UCX_BUFFER_VEC)
-      .value("NO_PAYLOAD", rpc::PayloadType::NO_PAYLOAD);
+      .value("NO_PAYLOAD", rpc::PayloadType::NO_PAYLOAD)
+      .value("MONOSTATE", rpc::PayloadType::MONOSTATE);
   py::enum_<rpc::RpcErrc>(m, "RpcErrc")
       .value("OK", rpc::RpcErrc::OK).value("CANCELLED", rpc::RpcErrc::CANCELLED).value("UNKNOWN", rpc::RpcErrc::UNKNOWN)
       .value("INVALID_ARGUMENT", rpc::RpcErrc::INVALID_ARGUMENT).value("DEADLINE_EXCEEDED", rpc::RpcErrc::DEADLINE_EXCEEDED)
@@ -273,9 +334,17 @@ void bind_types(py::module_& m) {
         return py::bytes(static_cast<const char*>((*v.vec)[i].data), (*v.vec)[i].size);
       });
 
+  // `params` / `results` give the values as Python objects (blobs decoded), which is what the
+  // reference exposes (bindings_types.cpp:257, 299); `params_meta` / `results_meta` add the wire
+  // type and the name tag for code that needs them.
   auto params_list = [](const rpc::data::vector<ParamMeta>& ps) {
     py::list out;
-    for (auto& p : ps) out.append(py::make_tuple(p.type, param_to_python(p), std::string(p.name)));
+    for (auto& p : ps) out.append(param_to_python(p, true));
+    return out;
+  };
+  auto params_meta_list = [](const rpc::data::vector<ParamMeta>& ps) {
+    py::list out;
+    for (auto& p : ps) out.append(py::make_tuple(p.type, param_to_python(p, true), py::str(p.name.data(), p.name.size())));
     return out;
   };
   py::class_<rpc::RpcRequestHeader>(m, "RpcRequestHeader")
@@ -296,6 +365,7 @@ void bind_types(py::module_& m) {
         h.params.push_back(std::move(p));
       }, py::arg("type"), py::arg("value"), py::arg("name") = "")
       .def_property_readonly("params", [params_list](const rpc::RpcRequestHeader& h) { return params_list(h.params); })
+      .def_property_readonly("params_meta", [params_meta_list](const rpc::RpcRequestHeader& h) { return params_meta_list(h.params); })
       .def("serialize", [](const rpc::RpcRequestHeader& h) {
         auto b = rpc::Serialize(h);
         return py::bytes(reinterpret_cast<const char*>(b.data()), b.size());
@@ -328,6 +398,13 @@ void bind_types(py::module_& m) {
         h.results.push_back(std::move(p));
       }, py::arg("type"), py::arg("value"), py::arg("name") = "")
       .def_property_readonly("results", [params_list](const rpc::RpcResponseHeader& h) { return params_list(h.results); })
+      .def_property_readonly("results_meta", [params_meta_list](const rpc::RpcResponseHeader& h) { return params_meta_list(h.results); })
+      .def_property_readonly("status", [](const rpc::RpcResponseHeader& h) {
+        py::dict d;
+        d["value"] = py::int_(h.status.value);
+        d["category_name"] = py::str(h.status.category_name.data(), h.status.category_name.size());
+        return d;
+      })
       .def("serialize", [](const rpc::RpcResponseHeader& h) {
         auto b = rpc::Serialize(h);
         return py::bytes(reinterpret_cast<const char*>(b.data()), b.size());

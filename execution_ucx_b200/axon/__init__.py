@@ -47,21 +47,46 @@ from ._axon import (CudaMemoryResourceManager, DefaultUcxMemoryResourceManager, 
 from .device import (CpuDevice, CudaDevice, Device, DeviceType, RocmDevice, SyclDevice, auto_detect, cpu, cuda,  # noqa: E402
                      rocm, sycl)
 
-_GROUP_SIZES = "__ntl_group_sizes"   # name of the param that carries nested-tensor-list group sizes
+_GROUP_SIZES = "__ntl_group_sizes"   # name of the VECTOR_UINT32 param that carries nested-tensor-list group sizes
+_NESTED_TAGS = {"nli64": "q", "nlf64": "d", "nlb": "B"}
+_STR_LIST_TAG = "vs"                 # List[str] blob (reference: param_conversion.cpp:543)
+_SUPPORTED = "Supported types: int, float, bool, str, List[T], Tuple[...], Dlpack compatible Tensor/Array"
 
 
 def _is_tensor(x: Any) -> bool:
-    return hasattr(x, "__dlpack__") and not isinstance(x, (UcxBuffer, UcxBufferVec))
+    return hasattr(x, "__dlpack__") and not isinstance(x, (UcxBuffer, UcxBufferVec, type))
+
+
+def _is_seq(x: Any) -> bool:
+    return isinstance(x, (list, tuple))
+
+
+def _type_name(t: Any) -> str:
+    return getattr(t, "__module__", "") + "." + getattr(t, "__qualname__", str(t))
 
 
 def _is_tensor_type(t: Any) -> bool:
-    name = getattr(t, "__module__", "") + "." + getattr(t, "__qualname__", str(t))
-    return name in ("torch.Tensor", "numpy.ndarray", "jax.Array", "jaxlib.xla_extension.ArrayImpl") or name.endswith(".Tensor")
+    """A bare class that is (or looks like) a DLPack tensor type: never a generic alias."""
+    if hasattr(t, "__origin__"):
+        return False
+    if hasattr(t, "__dlpack__"):
+        return True
+    name = _type_name(t)
+    if name in ("torch.Tensor", "numpy.ndarray", "jax.Array", "jaxlib.xla_extension.ArrayImpl"):
+        return True
+    text = str(t)
+    return any(k in text for k in ("numpy.ndarray", "torch.Tensor", "jax.Array", "jaxlib.xla_extension.ArrayImpl"))
 
 
 def _default_from_dlpack(sample: Any = None) -> Callable:
     """from_dlpack of the framework the sample (a tensor or a tensor type) belongs to; numpy otherwise."""
-    mod = (type(sample).__module__ if sample is not None and not isinstance(sample, type) else getattr(sample, "__module__", "")) or ""
+    if isinstance(sample, type):
+        fn = getattr(sample, "from_dlpack", None)
+        if callable(fn):
+            return fn
+        mod = getattr(sample, "__module__", "") or ""
+    else:
+        mod = (type(sample).__module__ if sample is not None else "") or ""
     if mod.startswith("torch"):
         import torch
         return torch.from_dlpack
@@ -75,15 +100,15 @@ def _default_from_dlpack(sample: Any = None) -> Callable:
 # ---- nested lists and string lists travel as tagged blobs (STRING params) ----------------------
 def _encode_nested(lst: Sequence[Sequence], code: str) -> bytes:
     """[u32 groups][u32 size...][items...], items i64 / f64 / u8."""
-    fmt = {"nli64": "q", "nlf64": "d", "nlb": "B"}[code]
+    fmt = _NESTED_TAGS[code]
     out = [struct.pack("<I", len(lst))] + [struct.pack("<I", len(g)) for g in lst]
     for g in lst:
-        out.append(struct.pack("<%d%s" % (len(g), fmt), *[int(v) if fmt != "d" else float(v) for v in g]))
+        out.append(struct.pack("<%d%s" % (len(g), fmt), *[float(v) if fmt == "d" else int(v) for v in g]))
     return b"".join(out)
 
 
 def _decode_nested(blob: bytes, code: str) -> List[list]:
-    fmt = {"nli64": "q", "nlf64": "d", "nlb": "B"}[code]
+    fmt = _NESTED_TAGS[code]
     (n,) = struct.unpack_from("<I", blob, 0)
     sizes = struct.unpack_from("<%dI" % n, blob, 4)
     off, out = 4 + 4 * n, []
@@ -113,42 +138,41 @@ def _decode_str_list(blob: bytes) -> List[str]:
     return out
 
 
-def _add_value(add: Callable, v: Any) -> None:
-    """Append one non-tensor Python value through `add(value, name)` / typed variants."""
-    if isinstance(v, (list, tuple)) and v and all(isinstance(g, (list, tuple)) for g in v):
-        flat = [x for g in v for x in g]
-        code = "nlb" if flat and all(isinstance(x, bool) for x in flat) else ("nlf64" if any(isinstance(x, float) for x in flat) else "nli64")
-        add(_encode_nested(v, code), code, ParamType.STRING)
-    elif isinstance(v, (list, tuple)) and v and all(isinstance(x, str) for x in v):
-        add(_encode_str_list(v), "ls", ParamType.STRING)
+def _nested_code(v: Sequence[Sequence]) -> str:
+    """Wire tag of a list of lists, from its first element; raises TypeError for anything but numbers and bools."""
+    for g in v:
+        if not _is_seq(g):
+            raise TypeError("Heterogeneous sequences are not supported as RPC arguments: every element of a nested list must be a list")
+    flat = [x for g in v for x in g]
+    for x in flat:
+        if not isinstance(x, (bool, int, float)):
+            raise TypeError(f"unsupported element type in nested list: {type(x).__name__} (supported: int, float, bool, Tensor)")
+    if flat and all(isinstance(x, bool) for x in flat):
+        return "nlb"
+    return "nlf64" if any(isinstance(x, float) for x in flat) else "nli64"
+
+
+def _add_inferred(add_typed: Callable, add_plain: Callable, v: Any) -> None:
+    """Append one non-tensor Python value, choosing the wire form from the value itself."""
+    if _is_seq(v) and v and _is_seq(v[0]):
+        code = _nested_code(v)
+        add_typed(ParamType.STRING, _encode_nested(v, code), code)
+    elif _is_seq(v) and v and isinstance(v[0], str):
+        if not all(isinstance(x, str) for x in v):
+            raise TypeError("unsupported element type: a list that starts with a str must hold only str")
+        add_typed(ParamType.STRING, _encode_str_list(v), _STR_LIST_TAG)
     else:
-        add(v, "", None)
+        add_plain(v)
 
 
-def _decode_value(ptype, value, name):
-    if ptype == ParamType.STRING and name in ("nli64", "nlf64", "nlb"):
-        return _decode_nested(value if isinstance(value, bytes) else value.encode("latin-1"), name)
-    if ptype == ParamType.STRING and name == "ls":
-        return _decode_str_list(value if isinstance(value, bytes) else value.encode("latin-1"))
-    return value
-
-
-def _classify(args: Sequence[Any]):
-    """Split call arguments into plain values and tensors (flat, list, or nested list of tensors)."""
-    values, tensors, groups = [], [], None
-    for a in args:
-        if _is_tensor(a):
-            tensors.append(a)
-        elif isinstance(a, (list, tuple)) and a and all(_is_tensor(x) for x in a):
-            tensors.extend(a)
-            groups = (groups or []) + [len(a)] if groups is not None else [len(a)]
-        elif isinstance(a, (list, tuple)) and a and all(isinstance(g, (list, tuple)) and g and all(_is_tensor(x) for x in g) for g in a):
-            for g in a:
-                tensors.extend(g)
-            groups = (groups or []) + [len(g) for g in a]
-        else:
-            values.append(a)
-    return values, tensors, groups
+def _add_declared(add_typed: Callable, add_plain: Callable, ptype, v: Any) -> None:
+    """Append a value under the wire type the function declared (UNKNOWN: infer; VOID: nothing)."""
+    if ptype == ParamType.VOID:
+        return
+    if ptype == ParamType.UNKNOWN or ptype == ParamType.STRING and not isinstance(v, (str, bytes)):
+        _add_inferred(add_typed, add_plain, v)
+    else:
+        add_typed(ptype, v, "")
 
 
 def _contiguous(t):
@@ -175,33 +199,6 @@ def _contiguous(t):
     return t
 
 
-def _tensors_from_payload(payload, metas: List[TensorMeta], from_dlpack_fn: Optional[Callable]):
-    """Payload object + metadata -> list of framework tensors (policy-supplied objects come back as they are)."""
-    out = []
-    if payload is None:
-        return out
-    if isinstance(payload, UcxBufferVec):
-        for i, m in enumerate(metas):
-            owner = payload.owner(i)
-            out.append(owner if owner is not None else (from_dlpack_fn or _default_from_dlpack())(payload.to_dlpack(i, m)))
-        return out
-    owner = payload.owner()
-    if owner is not None:
-        return [owner]
-    if len(metas) == 1:
-        return [(from_dlpack_fn or _default_from_dlpack())(payload.to_dlpack(metas[0]))]
-    # several tensors received back to back in one host buffer
-    fn = from_dlpack_fn or _default_from_dlpack()
-    whole = fn(payload)  # uint8 view
-    off = 0
-    for m in metas:
-        n = m.nbytes()
-        piece = whole[off: off + n]
-        off += n
-        out.append(_reinterpret(piece, m, fn))
-    return out
-
-
 def _reinterpret(piece, meta: TensorMeta, fn):
     """uint8 1-D view -> tensor of meta's dtype and shape (numpy or torch)."""
     code, bits = meta.dtype.code, meta.dtype.bits
@@ -216,238 +213,561 @@ def _reinterpret(piece, meta: TensorMeta, fn):
     return numpy.asarray(piece).view(numpy.dtype("%s%d" % (kinds.get(code, "u"), bits // 8))).reshape(list(meta.shape))
 
 
+class _TensorStream:
+    """The tensors of one message, in order: payload object + metadata -> framework tensors.
+
+    A tensor whose memory came from a memory policy is handed back as the very object the policy
+    returned; everything else goes through a ``from_dlpack`` function (the one given for that
+    position, else the framework default)."""
+
+    def __init__(self, payload, metas: List[TensorMeta]):
+        self.payload, self.metas, self.pos = payload, metas, 0
+        self._whole = None
+
+    def __len__(self) -> int:
+        return len(self.metas) if self.payload is not None else 0
+
+    def remaining(self) -> int:
+        return len(self) - self.pos
+
+    def take(self, fn: Optional[Callable]):
+        i, self.pos = self.pos, self.pos + 1
+        if i >= len(self):
+            raise RuntimeError("the message carries fewer tensors than the function takes")
+        p, m = self.payload, self.metas[i]
+        if isinstance(p, UcxBufferVec):
+            owner = p.owner(i)
+            return owner if owner is not None else (fn or _default_from_dlpack())(p.to_dlpack(i, m))
+        if len(self.metas) == 1:
+            owner = p.owner()
+            return owner if owner is not None else (fn or _default_from_dlpack())(p.to_dlpack(m))
+        # several tensors received back to back in one host buffer
+        f = fn or _default_from_dlpack()
+        if self._whole is None:
+            self._whole = f(p)  # uint8 view
+        off = sum(x.nbytes() for x in self.metas[:i])
+        return _reinterpret(self._whole[off: off + m.nbytes()], m, f)
+
+
+def _split_params(meta_list):
+    """(type, value, name) triples -> (non-tensor triples in order, tensor metas)."""
+    plain, metas = [], []
+    for ptype, value, name in meta_list:
+        if ptype == ParamType.TENSOR_META:
+            metas = [value]
+        elif ptype == ParamType.TENSOR_META_VEC:
+            metas = list(value)
+        else:
+            plain.append((ptype, value, name))
+    return plain, metas
+
+
+# ---- signatures ---------------------------------------------------------------------------------
+class _Sig:
+    """What a registered function takes and returns, in wire terms (reference: FunctionSignatureInfo,
+    axon/python/src/python_helpers.cpp:405-560)."""
+
+    __slots__ = ("param_types", "return_types", "in_payload", "out_payload", "encoded", "param_from_dlpack",
+                 "n_tensor_params", "tensor_return_indices", "non_tensor_indices", "non_tensor_types", "mode")
+
+    def __init__(self):
+        self.param_types: List[Any] = []
+        self.return_types: List[Any] = []
+        self.in_payload = PayloadType.NO_PAYLOAD
+        self.out_payload = PayloadType.NO_PAYLOAD
+        self.encoded: dict = {}              # parameter index -> "vs" | "nli64" | "nlf64" | "nlb" | "ntl"
+        self.param_from_dlpack: dict = {}    # parameter index -> from_dlpack callable or None
+        self.n_tensor_params = 0
+        self.tensor_return_indices: List[int] = []   # positions in the returned tuple
+        self.non_tensor_indices: List[int] = []
+        self.non_tensor_types: List[Any] = []
+        self.mode = "void"                   # void | single | tensor | tensor_list | tuple
+
+
+def _is_list_alias(t: Any) -> bool:
+    return t is typing.List or typing.get_origin(t) in (list, typing.List) or getattr(t, "__origin__", None) is list
+
+
+def _annotation_info(ann: Any):
+    """Annotation -> (ParamType, blob tag or None, tensor type or None). TypeError for forms that can
+    never be carried; UNKNOWN for types this layer does not know."""
+    if ann is None or ann is type(None):
+        return ParamType.UNKNOWN, None, None
+    if ann is bool:
+        return ParamType.PRIMITIVE_BOOL, None, None
+    if ann is int:
+        return ParamType.PRIMITIVE_INT64, None, None
+    if ann is float:
+        return ParamType.PRIMITIVE_FLOAT64, None, None
+    if ann is str:
+        return ParamType.STRING, None, None
+    if hasattr(ann, "__dlpack__"):
+        return ParamType.TENSOR_META, None, ann
+    if _is_list_alias(ann):
+        args = typing.get_args(ann)
+        if not args:
+            raise TypeError("List without type argument is not supported. Use List[int], List[float], List[str], List[bool], "
+                            "List[Tensor], List[List[int]], List[List[float]], List[List[bool]], List[List[Tensor]] instead.")
+        elem = args[0]
+        if elem is int:
+            return ParamType.VECTOR_INT64, None, None
+        if elem is float:
+            return ParamType.VECTOR_FLOAT64, None, None
+        if elem is bool:
+            return ParamType.VECTOR_BOOL, None, None
+        if elem is str:
+            return ParamType.STRING, _STR_LIST_TAG, None
+        if _is_tensor_type(elem):
+            return ParamType.TENSOR_META_VEC, None, elem
+        if _is_list_alias(elem):
+            inner = typing.get_args(elem)
+            if not inner:
+                raise TypeError("List[List[...]] requires explicit element type annotation (e.g. List[List[int]])")
+            it = inner[0]
+            if it is int:
+                return ParamType.STRING, "nli64", None
+            if it is float:
+                return ParamType.STRING, "nlf64", None
+            if it is bool:
+                return ParamType.STRING, "nlb", None
+            if _is_tensor_type(it):
+                return ParamType.STRING, "ntl", it
+            raise TypeError(f"Unsupported inner element type in List[List[...]]: '{it}'. Supported: int, float, bool, Tensor")
+        raise TypeError(f"Unsupported List element type: '{elem}'. Supported: int, float, bool, str, Tensor, List[int], "
+                        "List[float], List[bool], List[Tensor]")
+    if isinstance(ann, type):
+        for mod, cls in (("torch", "Tensor"), ("numpy", "ndarray"), ("jax", "Array"), ("tensorflow", "Tensor")):
+            import sys
+            m = sys.modules.get(mod)
+            base = getattr(m, cls, None) if m is not None else None
+            try:
+                if base is not None and issubclass(ann, base):
+                    return ParamType.TENSOR_META, None, ann
+            except TypeError:
+                pass
+    return ParamType.UNKNOWN, None, None
+
+
+def _callable_for_signature(fn: Callable):
+    return fn if inspect.isfunction(fn) or inspect.ismethod(fn) else getattr(fn, "__call__", fn)
+
+
+def _is_async_callable(fn: Any) -> bool:
+    return inspect.iscoroutinefunction(fn) or inspect.iscoroutinefunction(getattr(fn, "__call__", None))
+
+
+def _parse_signature(fn: Callable) -> _Sig:
+    """Wire signature of ``fn`` from its annotations; parameters without one are UNKNOWN."""
+    sig = _Sig()
+    target = _callable_for_signature(fn)
+    try:
+        hints = typing.get_type_hints(target)
+    except Exception:
+        hints = {}
+    isig = inspect.signature(fn)
+    n_tensors, any_list = 0, False
+    for idx, (pname, par) in enumerate(isig.parameters.items()):
+        ann = hints.get(pname, par.annotation)
+        if ann is inspect.Parameter.empty:
+            sig.param_types.append(ParamType.UNKNOWN)
+            continue
+        ptype, tag, ttype = _annotation_info(ann)
+        sig.param_types.append(ptype)
+        if tag is not None:
+            sig.encoded[idx] = tag
+        if ptype in (ParamType.TENSOR_META, ParamType.TENSOR_META_VEC) or tag == "ntl":
+            sig.param_from_dlpack[idx] = _default_from_dlpack(ttype) if isinstance(ttype, type) and not hasattr(ttype, "__dlpack__") or _is_known_framework(ttype) else getattr(ttype, "from_dlpack", None)
+            sig.n_tensor_params += 1
+            n_tensors += 1 if ptype == ParamType.TENSOR_META else 2
+    if n_tensors == 1:
+        sig.in_payload = PayloadType.UCX_BUFFER
+    elif n_tensors > 1:
+        sig.in_payload = PayloadType.UCX_BUFFER_VEC
+    ret = hints.get("return", isig.return_annotation)
+    if ret is inspect.Signature.empty:
+        return sig
+    if ret is None or ret is type(None):
+        sig.return_types = [ParamType.VOID]
+        return sig
+    is_tuple = typing.get_origin(ret) in (tuple, typing.Tuple)
+    anns = list(typing.get_args(ret)) if is_tuple else [ret]
+    if ret is tuple:
+        anns, is_tuple = [], True
+        sig.non_tensor_types.append(ParamType.UNKNOWN)
+        sig.non_tensor_indices.append(0)
+    has_vec = False
+    for i, a in enumerate(anns):
+        ptype, _tag, _tt = _annotation_info(a)
+        if ptype == ParamType.TENSOR_META:
+            sig.tensor_return_indices.append(i)
+        elif ptype == ParamType.TENSOR_META_VEC:
+            has_vec = True
+            sig.tensor_return_indices.append(i)
+        else:
+            sig.non_tensor_types.append(ptype)
+            sig.non_tensor_indices.append(i)
+    sig.return_types = list(sig.non_tensor_types)
+    if len(sig.tensor_return_indices) == 1 and not has_vec:
+        sig.return_types.append(ParamType.TENSOR_META)
+        sig.out_payload = PayloadType.UCX_BUFFER
+    elif sig.tensor_return_indices:
+        sig.return_types.append(ParamType.TENSOR_META_VEC)
+        sig.out_payload = PayloadType.UCX_BUFFER_VEC
+    sig.mode = _return_mode(sig.return_types, bool(sig.tensor_return_indices), has_vec, is_tuple)
+    return sig
+
+
+def _is_known_framework(t: Any) -> bool:
+    mod = getattr(t, "__module__", "") or ""
+    return mod.startswith(("torch", "numpy", "jax"))
+
+
+def _return_mode(return_types, has_tensors: bool, has_vec: bool, is_tuple: bool) -> str:
+    if not return_types or (len(return_types) == 1 and return_types[0] == ParamType.VOID):
+        return "void"
+    if len(return_types) == 1 and not is_tuple:
+        if has_tensors:
+            return "tensor_list" if has_vec else "tensor"
+        return "single"
+    return "tuple"
+
+
+def _sig_from_types(param_types, return_types, in_payload, out_payload, from_dlpack_fn) -> _Sig:
+    """Signature of a function registered with explicit wire types (register_function_raw, long form)."""
+    sig = _Sig()
+    sig.param_types, sig.return_types = list(param_types), list(return_types)
+    n_in = sum(1 if t == ParamType.TENSOR_META else 2 for t in sig.param_types if t in (ParamType.TENSOR_META, ParamType.TENSOR_META_VEC))
+    sig.in_payload = PayloadType.UCX_BUFFER if n_in == 1 else PayloadType.UCX_BUFFER_VEC if n_in > 1 else in_payload
+    for i, t in enumerate(sig.param_types):
+        if t in (ParamType.TENSOR_META, ParamType.TENSOR_META_VEC):
+            sig.param_from_dlpack[i] = from_dlpack_fn
+            sig.n_tensor_params += 1
+    has_vec = False
+    for i, t in enumerate(sig.return_types):
+        if t in (ParamType.TENSOR_META, ParamType.TENSOR_META_VEC):
+            sig.tensor_return_indices.append(i)
+            has_vec = has_vec or t == ParamType.TENSOR_META_VEC
+        else:
+            sig.non_tensor_indices.append(i)
+            sig.non_tensor_types.append(t)
+    n_out = len(sig.tensor_return_indices) + (1 if has_vec else 0)
+    sig.out_payload = PayloadType.UCX_BUFFER if n_out == 1 else PayloadType.UCX_BUFFER_VEC if n_out > 1 else out_payload
+    sig.mode = _return_mode(sig.return_types, bool(sig.tensor_return_indices), has_vec, len(sig.return_types) > 1)
+    return sig
+
+
+# ---- server side: header + payload -> positional arguments -> results ---------------------------
+def _params_to_args(sig: _Sig, header, payload) -> list:
+    """Positional arguments of the handler, in declaration order (reference:
+    bindings_runtime_wrapper.cpp:97-329): every tensor-typed parameter draws from one stream of
+    tensors, every other parameter from the non-tensor params in their order on the wire."""
+    plain, metas = _split_params(header.params_meta)
+    stream = _TensorStream(payload, metas)
+    args, pi = [], 0
+    if not sig.param_types and payload is not None and not metas:
+        return args
+    for idx, ptype in enumerate(sig.param_types):
+        tag = sig.encoded.get(idx)
+        fn = sig.param_from_dlpack.get(idx)
+        if tag == "ntl":
+            if pi >= len(plain):
+                raise RuntimeError(f"Missing group-sizes param for nested tensor list at index {idx}")
+            sizes = plain[pi][1]
+            pi += 1
+            args.append([[stream.take(fn) for _ in range(int(n))] for n in sizes])
+        elif ptype == ParamType.TENSOR_META:
+            if stream.remaining() <= 0:
+                raise RuntimeError(f"Tensor meta not found for parameter {idx}")
+            args.append(stream.take(fn))
+        elif ptype == ParamType.TENSOR_META_VEC:
+            args.append([stream.take(fn) for _ in range(stream.remaining())])
+        elif pi < len(plain):
+            while pi < len(plain) and plain[pi][2] == _GROUP_SIZES:
+                pi += 1          # sizes of a nested tensor list sent to a function that takes a flat list
+            if pi < len(plain):
+                args.append(plain[pi][1])
+                pi += 1
+    return args
+
+
+def _tensor_payload(tensors: list, as_vec: bool, add_typed: Callable):
+    """Metadata param (always last) + payload object for the tensors of a message."""
+    if not tensors and not as_vec:
+        return None
+    tensors = [_contiguous(t) for t in tensors]
+    metas = [TensorMeta.from_tensor(t) for t in tensors]
+    if len(tensors) == 1 and not as_vec:
+        add_typed(ParamType.TENSOR_META, metas[0], "")
+        return tensors[0]
+    if not tensors:
+        return None
+    add_typed(ParamType.TENSOR_META_VEC, metas, "")
+    return tensors
+
+
+def _pack_results(sig: _Sig, result):
+    """Handler return value -> (RpcResponseHeader with the result params, payload)."""
+    header = RpcResponseHeader()
+
+    def add_typed(ptype, v, name):
+        header.add_result_typed(ptype, v, name)
+
+    def add_plain(v):
+        header.AddResult(v)
+
+    if sig.mode == "void" and not (sig.return_types and sig.return_types[0] == ParamType.UNKNOWN):
+        return header, None
+    if any(t == ParamType.UNKNOWN for t in sig.return_types) or not sig.return_types:
+        return _pack_inferred(result, header, add_typed, add_plain)
+    if sig.mode == "single":
+        _add_declared(add_typed, add_plain, sig.return_types[0], result)
+        return header, None
+    if sig.mode == "tensor":
+        return header, _tensor_payload([result], False, add_typed)
+    if sig.mode == "tensor_list":
+        return header, _tensor_payload(list(result), True, add_typed)
+    items = tuple(result) if isinstance(result, (tuple, list)) else (result,)
+    for ptype, i in zip(sig.non_tensor_types, sig.non_tensor_indices):
+        _add_declared(add_typed, add_plain, ptype, items[i])
+    tensors, as_vec = [], len(sig.tensor_return_indices) > 1
+    for i in sig.tensor_return_indices:
+        if _is_seq(items[i]):
+            tensors.extend(items[i])
+            as_vec = True
+        else:
+            tensors.append(items[i])
+    return header, (_tensor_payload(tensors, as_vec, add_typed) if sig.tensor_return_indices else None)
+
+
+def _pack_inferred(result, header, add_typed, add_plain):
+    """No usable return annotation: the wire form follows the value."""
+    if result is None:
+        return header, None
+    items = list(result) if isinstance(result, tuple) else [result]
+    tensors, as_vec = [], False
+    for it in items:
+        if _is_tensor(it):
+            tensors.append(it)
+        elif _is_seq(it) and it and all(_is_tensor(x) for x in it):
+            tensors.extend(it)
+            as_vec = True
+        else:
+            _add_inferred(add_typed, add_plain, it)
+    return header, (_tensor_payload(tensors, as_vec or len(tensors) > 1, add_typed) if tensors else None)
+
+
+# ---- client side --------------------------------------------------------------------------------
+def _error_text(resp, fid: int, session_id: int) -> str:
+    what = next((v for t, v, _n in resp.results_meta if t == ParamType.STRING), None)
+    if not what:
+        what = f"RPC invocation failed: {resp.status_category} error {resp.status_value}"
+    if fid:
+        what += f" (function_id: {fid})"
+    if session_id:
+        what += f" (session_id: {session_id})"
+    return what
+
+
+def _results_to_python(resp, payload, from_dlpack_fn, fid: int, session_id: int):
+    """Response -> what the awaiting caller gets (reference: param_conversion.hpp:83-176): nothing ->
+    None, one result -> the value (a tensor, or the list of tensors), several -> a tuple with the tensors
+    spliced in after the plain values."""
+    if not resp.ok:
+        raise RuntimeError(_error_text(resp, fid, session_id))
+    results = resp.results_meta
+    plain, metas = _split_params(results)
+    stream = _TensorStream(payload, metas)
+    if len(results) == 1:
+        ptype, value, _ = results[0]
+        if ptype == ParamType.TENSOR_META:
+            return stream.take(from_dlpack_fn)
+        if ptype == ParamType.TENSOR_META_VEC:
+            return [stream.take(from_dlpack_fn) for _ in range(len(metas))]
+        return value
+    out = []
+    for ptype, value, _ in results:
+        if ptype == ParamType.TENSOR_META:
+            out.append(stream.take(from_dlpack_fn))
+        elif ptype == ParamType.TENSOR_META_VEC:
+            out.extend(stream.take(from_dlpack_fn) for _ in range(len(metas)))
+        else:
+            out.append(value)
+    return tuple(out) if out else None
+
+
+def _classify(obj: Any) -> str:
+    """'tensor' | 'flat' | 'nested' | 'value' (reference: ClassifyArg, bindings_runtime_helpers.hpp:264-334)."""
+    if _is_tensor(obj):
+        return "tensor"
+    if not _is_seq(obj):
+        return "value"
+    if len(obj) == 0:
+        return "flat"
+    first = obj[0]
+    if _is_tensor(first):
+        return "flat"
+    if _is_seq(first):
+        for inner in obj:
+            if not _is_seq(inner):
+                raise TypeError("Heterogeneous sequences are not supported as RPC arguments: expected all elements to be "
+                                "sequences (list/tuple) for List[List[Tensor]]")
+            if len(inner) == 0:
+                continue
+            head = inner[0]
+            if _is_tensor(head):
+                return "nested"
+            if isinstance(head, (bool, int, float, str)):
+                return "value"
+            raise TypeError("Unsupported element type inside nested sequence: expected a DLPack-compatible tensor, int, "
+                            "float, bool, or str for List[List[T]] argument")
+    return "value"
+
+
 class AxonRuntime(_axon.AxonRuntime):
-    """Runtime with the annotation-driven ``register_function`` and the variadic ``invoke``."""
+    """The runtime as Python sees it: annotation-driven registration, raw registration with explicit
+    wire types, ``invoke`` with natural arguments and ``invoke_raw`` with a prepared header
+    (reference: axon/python/src/bindings_runtime.cpp:404-1018)."""
 
     def __init__(self, worker_name: str, thread_pool_size: int = 0, timeout=None, device=None, resource_manager=None):
-        super().__init__(worker_name, thread_pool_size, timeout, device, resource_manager)
+        super().__init__(worker_name, thread_pool_size or 0, timeout, device, resource_manager)
         self._functions = {}
 
     # ---- server side ------------------------------------------------------------------------
-    def register_function(self, fn: Callable, function_id: Optional[int] = None, function_name: Optional[str] = None,
-                          memory_policy: Optional[Callable] = None, lifecycle_policy: Optional[Callable] = None,
-                          from_dlpack_fn: Optional[Callable] = None) -> int:
-        """Register ``async def fn(...)``. Every parameter and the return need annotations:
-        ``int`` (INT64), ``float`` (FLOAT64), ``bool``, ``str``, tensor types, ``List[...]`` of those;
-        ``Tuple[...]`` only as the return annotation."""
-        if not inspect.iscoroutinefunction(fn):
-            raise TypeError("register_function needs an `async def` function")
-        name = function_name or fn.__name__
-        fid = function_id if function_id is not None else function_id_from_name(name, self.worker_name)
-        hints = typing.get_type_hints(fn)
-        sig = inspect.signature(fn)
-        param_types, tensor_params, in_payload = [], [], PayloadType.NO_PAYLOAD
-        for pname in sig.parameters:
-            if pname not in hints:
-                raise TypeError(f"parameter '{pname}' of {name} needs a type annotation")
-            kind, ptype = _annotation_kind(hints[pname])
-            if kind == "tensor":
-                tensor_params.append((pname, False))
-            elif kind == "tensor_list":
-                tensor_params.append((pname, True))
-            else:
-                param_types.append(ptype)
-            if kind in ("tensor", "tensor_list") and from_dlpack_fn is None:
-                from_dlpack_fn = _default_from_dlpack(_tensor_type_of(hints[pname]))
-        if tensor_params:
-            many = len(tensor_params) > 1 or tensor_params[0][1]
-            param_types.append(ParamType.TENSOR_META_VEC if many else ParamType.TENSOR_META)
-            in_payload = PayloadType.UCX_BUFFER_VEC if many else PayloadType.UCX_BUFFER
-        ret = hints.get("return", None)
-        return_types, out_payload = _return_types(ret)
-        order = list(sig.parameters)
-        tensor_is_list = dict(tensor_params)   # parameter name -> takes a list of tensors
+    def _register(self, fid: int, name: str, sig: _Sig, fn: Callable, memory_policy, lifecycle_policy) -> int:
+        async def handler(header, payload):
+            return _pack_results(sig, await fn(*_params_to_args(sig, header, payload)))
 
-        async def wrapper(header, payload):
-            values, metas, groups = [], [], None
-            for ptype, value, pname in header.params:
-                if ptype == ParamType.TENSOR_META:
-                    metas = [value]
-                elif ptype == ParamType.TENSOR_META_VEC:
-                    metas = list(value)
-                elif pname == _GROUP_SIZES:
-                    groups = list(value)
-                else:
-                    values.append(_decode_value(ptype, value, pname))
-            tensors = _tensors_from_payload(payload, metas, from_dlpack_fn)
-            kwargs, vi, ti = {}, 0, 0
-            for pname in order:
-                is_list = tensor_is_list.get(pname)
-                if is_list is not None:
-                    if is_list:
-                        take = groups.pop(0) if groups else len(tensors) - ti
-                        kwargs[pname] = tensors[ti: ti + take]
-                        ti += take
-                    else:
-                        kwargs[pname] = tensors[ti]
-                        ti += 1
-                else:
-                    kwargs[pname] = values[vi]
-                    vi += 1
-            result = await fn(**kwargs)
-            return _pack_results(result)
-
-        ok = self.register_function_raw(fid, name, param_types, return_types, in_payload, out_payload, wrapper, memory_policy, lifecycle_policy)
+        ok = self._register_native(fid, name, sig.param_types, sig.return_types, sig.in_payload, sig.out_payload, handler,
+                                   memory_policy, lifecycle_policy)
         if not ok:
             raise ValueError(f"function id {fid} ({name}) is already registered")
         self._functions[name] = fid
         return fid
 
+    @staticmethod
+    def _name_of(fn: Callable, function_name: Optional[str], fid: Optional[int]) -> str:
+        return function_name or getattr(fn, "__name__", None) or f"function_{fid or 0}"
+
+    def register_function(self, callable: Callable, function_id: Optional[int] = None, function_name: Optional[str] = None,
+                          memory_policy: Optional[Callable] = None, lifecycle_policy: Optional[Callable] = None,
+                          from_dlpack_fn: Optional[Callable] = None) -> int:
+        """Register ``async def callable(...)`` under ``function_id`` (default: the hash of its name and
+        this worker's name). Every parameter and the return need an annotation this layer can carry:
+        ``int`` (INT64), ``float`` (FLOAT64), ``bool``, ``str``, a DLPack tensor type, ``List[...]`` of
+        those, ``List[List[int|float|bool|Tensor]]``; ``Tuple[...]`` only as the return annotation."""
+        if not _is_async_callable(callable):
+            raise RuntimeError("register_function only accepts async functions. Please use 'async def' to define your function.")
+        name = self._name_of(callable, function_name, function_id)
+        fid = function_id if function_id is not None else function_id_from_name(name, self.worker_name)
+        sig = _parse_signature(callable)
+        for i, t in enumerate(sig.param_types):
+            if t == ParamType.UNKNOWN:
+                raise TypeError(f"Unsupported or missing type annotation for parameter {i} in function '{name}'. {_SUPPORTED}.")
+        if any(t == ParamType.UNKNOWN for t in sig.return_types):
+            raise TypeError(f"Unsupported or missing return type annotation for function '{name}'. {_SUPPORTED}, None.")
+        if memory_policy is not None and sig.n_tensor_params and from_dlpack_fn is None:
+            raise RuntimeError(
+                f"Function '{name}' has tensor parameters and custom memory_policy is set, but from_dlpack_fn is not provided. "
+                "from_dlpack_fn is required for small messages, which arrive in host memory without the memory_policy being "
+                "asked. Please provide from_dlpack_fn (e.g., numpy.from_dlpack, torch.from_dlpack, jax.dlpack.from_dlpack).")
+        if from_dlpack_fn is not None:
+            sig.param_from_dlpack = {i: from_dlpack_fn for i in sig.param_from_dlpack}
+        return self._register(fid, name, sig, callable, memory_policy, lifecycle_policy)
+
+    def register_function_raw(self, function_id: int, *args, **kwargs) -> int:
+        """Two forms, as in the reference:
+
+        ``register_function_raw(function_id, function_name, param_types, return_types, input_payload_type,
+        return_payload_type, callable, memory_policy=None, lifecycle_policy=None, from_dlpack_fn=None)``
+        registers under explicit wire types;
+
+        ``register_function_raw(function_id, callable, function_name=None, memory_policy=None,
+        lifecycle_policy=None)`` infers them from the annotations (missing ones become UNKNOWN and the
+        values decide at run time)."""
+        long_names = ("function_name", "param_types", "return_types", "input_payload_type", "return_payload_type", "callable",
+                      "memory_policy", "lifecycle_policy", "from_dlpack_fn")
+        short_names = ("callable", "function_name", "memory_policy", "lifecycle_policy")
+        is_long = "param_types" in kwargs or (args and isinstance(args[0], str))
+        names = long_names if is_long else short_names
+        if len(args) > len(names):
+            raise TypeError("register_function_raw(): too many positional arguments")
+        bound = dict(zip(names, args))
+        for k, v in kwargs.items():
+            if k not in names or k in bound:
+                raise TypeError(f"register_function_raw(): unexpected or repeated argument '{k}'")
+            bound[k] = v
+        fn = bound.get("callable")
+        required = long_names[:6] if is_long else ("callable",)
+        missing = [k for k in required if k not in bound]
+        if missing:
+            raise TypeError(f"register_function_raw(): missing argument(s) {', '.join(missing)}")
+        if not _is_async_callable(fn):
+            raise RuntimeError("register_function_raw only accepts async functions. Please use 'async def' to define your function.")
+        memory_policy, lifecycle_policy = bound.get("memory_policy"), bound.get("lifecycle_policy")
+        if is_long:
+            name = bound["function_name"]
+            sig = _sig_from_types(bound["param_types"], bound["return_types"], bound["input_payload_type"],
+                                  bound["return_payload_type"], bound.get("from_dlpack_fn"))
+            if memory_policy is not None and sig.n_tensor_params and bound.get("from_dlpack_fn") is None:
+                raise RuntimeError(f"Function '{name}' has tensor parameters and custom memory_policy is set, but from_dlpack_fn "
+                                   "is not provided.")
+        else:
+            name = self._name_of(fn, bound.get("function_name"), function_id)
+            sig = _parse_signature(fn)
+            if not sig.return_types:
+                sig.return_types = [ParamType.UNKNOWN]
+        return self._register(function_id, name, sig, fn, memory_policy, lifecycle_policy)
+
     # ---- client side --------------------------------------------------------------------------
+    def invoke_raw(self, worker_name: str, request_header: RpcRequestHeader, payload=None, memory_policy: Optional[Callable] = None):
+        """Send a prepared header (and an optional payload: a tensor, a list of tensors, a ``UcxBuffer`` or
+        ``UcxBufferVec``). The future resolves to the function's return value(s), as ``invoke`` does."""
+        if request_header is None:
+            raise RuntimeError("request_header cannot be None")
+        fid, sid = request_header.function_id, request_header.session_id
+        if payload is not None and not isinstance(payload, (UcxBuffer, UcxBufferVec)):
+            payload = [_contiguous(t) for t in payload] if _is_seq(payload) else _contiguous(payload)
+        return self._invoke_native(worker_name, request_header, payload, memory_policy, False,
+                                   lambda resp, pay: _results_to_python(resp, pay, None, fid, sid))
+
     def invoke(self, *args, worker_name: str, session_id: int, function, workflow_id: int = 0,
                memory_policy: Optional[Callable] = None, from_dlpack_fn: Optional[Callable] = None):
-        """Call ``function`` (an id, or a name hashed with the worker name) on ``worker_name``.
-        Returns a future of the result: a single value, a tuple of values, tensors included."""
+        """Call ``function`` (an id, or a name hashed with the worker name) on ``worker_name`` with natural
+        arguments: values, tensors, lists of tensors, lists of lists of tensors. Returns a future of the
+        result: a single value, or a tuple of values, tensors included."""
+        if isinstance(function, bool) or not isinstance(function, (int, str)):
+            raise ValueError("function must be int (ID) or str (name)")
         fid = function if isinstance(function, int) else function_id_from_name(function, worker_name)
         header = RpcRequestHeader()
         header.session_id, header.function_id, header.workflow_id = session_id, fid, workflow_id
-        values, tensors, groups = _classify(args)
 
-        def add(v, name, ptype):
-            if ptype is None:
-                header.AddParam(v, name)
+        def add_typed(ptype, v, name):
+            header.add_param_typed(ptype, v, name)
+
+        def add_plain(v):
+            header.AddParam(v)
+
+        tensors: list = []
+        for a in args:
+            kind = _classify(a)
+            if kind == "tensor":
+                tensors.append(a)
+            elif kind == "flat":
+                tensors.extend(a)
+            elif kind == "nested":
+                add_typed(ParamType.VECTOR_UINT32, [len(g) for g in a], _GROUP_SIZES)
+                for g in a:
+                    tensors.extend(g)
             else:
-                header.add_param_typed(ptype, v, name)
-        for v in values:
-            _add_value(add, v)
-        payload = None
+                _add_inferred(add_typed, add_plain, a)
         sample = tensors[0] if tensors else None
-        if tensors:
-            tensors = [_contiguous(t) for t in tensors]
-            metas = [TensorMeta.from_tensor(t) for t in tensors]
-            if groups is not None and len(groups) > 1:
-                header.add_param_typed(ParamType.VECTOR_UINT32, groups, _GROUP_SIZES)
-            # the tensor metadata goes last so the receiver finds it at once
-            if len(tensors) == 1 and groups is None:
-                header.add_param_typed(ParamType.TENSOR_META, metas[0], "")
-                payload = tensors[0]
-            else:
-                header.add_param_typed(ParamType.TENSOR_META_VEC, metas, "")
-                payload = tensors
+        # the tensor metadata goes last so the receiver finds it at once
+        payload = _tensor_payload(tensors, len(tensors) > 1, add_typed) if tensors else None
         fn = from_dlpack_fn or (_default_from_dlpack(sample) if sample is not None else None)
         # the response is unpacked on the loop thread by the binding itself and settles the future
-        return self.invoke_raw(worker_name, header, payload, memory_policy, False,
-                               lambda resp, pay: _unpack_response(resp, pay, fn, fid, session_id))
+        return self._invoke_native(worker_name, header, payload, memory_policy, False,
+                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id))
 
-
-def _unpack_response(resp, payload, from_dlpack_fn, fid, session_id):
-    if not resp.ok:
-        what = next((v for t, v, n in resp.results if t == ParamType.STRING), f"{resp.status_category} error {resp.status_value}")
-        raise RuntimeError(f"{what} (function_id: {fid}) (session_id: {session_id})")
-    values, metas = [], []
-    for ptype, value, name in resp.results:
-        if ptype == ParamType.TENSOR_META:
-            metas = [value]
-            values.append(("tensor", 0))
-        elif ptype == ParamType.TENSOR_META_VEC:
-            metas = list(value)
-            values.append(("tensors", len(metas)))
-        else:
-            values.append(("value", _decode_value(ptype, value, name)))
-    tensors = _tensors_from_payload(payload, metas, from_dlpack_fn)
-    out = []
-    for kind, v in values:
-        if kind == "tensor":
-            out.append(tensors[0])
-        elif kind == "tensors":
-            out.append(list(tensors))
-        else:
-            out.append(v)
-    if not out:
-        return None
-    return out[0] if len(out) == 1 else tuple(out)
-
-
-def _pack_results(result):
-    """Handler return value -> (list of result params, payload)."""
-    if result is None:
-        return [], None
-    items = list(result) if isinstance(result, tuple) else [result]
-    header = RpcResponseHeader()
-    tensors, listy = [], False
-    for it in items:
-        if _is_tensor(it):
-            tensors.append(_contiguous(it))
-        elif isinstance(it, (list, tuple)) and it and all(_is_tensor(x) for x in it):
-            tensors.extend(_contiguous(x) for x in it)
-            listy = True
-        else:
-            def add(v, name, ptype):
-                if ptype is None:
-                    header.AddResult(v, name)
-                else:
-                    header.add_result_typed(ptype, v, name)
-            _add_value(add, it)
-    payload = None
-    if tensors:
-        metas = [TensorMeta.from_tensor(t) for t in tensors]
-        if len(tensors) == 1 and not listy:
-            header.add_result_typed(ParamType.TENSOR_META, metas[0], "")
-            payload = tensors[0]
-        else:
-            header.add_result_typed(ParamType.TENSOR_META_VEC, metas, "")
-            payload = tensors
-    return header, payload
-
-
-def _tensor_type_of(ann):
-    args = typing.get_args(ann)
-    return args[0] if args else ann
-
-
-def _annotation_kind(ann):
-    if ann is bool:
-        return "value", ParamType.PRIMITIVE_BOOL
-    if ann is int:
-        return "value", ParamType.PRIMITIVE_INT64
-    if ann is float:
-        return "value", ParamType.PRIMITIVE_FLOAT64
-    if ann is str:
-        return "value", ParamType.STRING
-    if ann is bytes:
-        return "value", ParamType.VECTOR_UINT8
-    if _is_tensor_type(ann):
-        return "tensor", None
-    origin = typing.get_origin(ann)
-    if origin in (list, List):
-        (inner,) = typing.get_args(ann) or (None,)
-        if inner is bool:
-            return "value", ParamType.VECTOR_BOOL
-        if inner is int:
-            return "value", ParamType.VECTOR_INT64
-        if inner is float:
-            return "value", ParamType.VECTOR_FLOAT64
-        if inner is str:
-            return "value", ParamType.STRING
-        if _is_tensor_type(inner):
-            return "tensor_list", None
-        if typing.get_origin(inner) in (list, List):
-            return "value", ParamType.STRING
-    raise TypeError(f"unsupported annotation {ann!r}: use int, float, bool, str, bytes, a tensor type, or List[...] of those")
-
-
-def _return_types(ann):
-    if ann is None or ann is type(None) or ann is inspect.Signature.empty:
-        return [], PayloadType.NO_PAYLOAD
-    anns = list(typing.get_args(ann)) if typing.get_origin(ann) in (tuple, typing.Tuple) else [ann]
-    types, n_tensors, listy = [], 0, False
-    for a in anns:
-        kind, ptype = _annotation_kind(a)
-        if kind == "tensor":
-            n_tensors += 1
-        elif kind == "tensor_list":
-            n_tensors += 2
-            listy = True
-        else:
-            types.append(ptype)
-    payload = PayloadType.NO_PAYLOAD
-    if n_tensors == 1 and not listy:
-        types.append(ParamType.TENSOR_META)
-        payload = PayloadType.UCX_BUFFER
-    elif n_tensors:
-        types.append(ParamType.TENSOR_META_VEC)
-        payload = PayloadType.UCX_BUFFER_VEC
-    return types, payload
 
 
 __all__ = [

@@ -25,12 +25,14 @@ def test_types_and_param_inference(axon):
     h.session_id, h.function_id = 5, 9
     for v in (True, 7, 2.5, "text", b"\x00\x01", [1, 2, 3], [1.0, 2], [True, False], None):
         h.AddParam(v)
-    kinds = [t for t, _, _ in h.params]
+    kinds = [t for t, _, _ in h.params_meta]
     P = axon.ParamType
     assert kinds == [P.PRIMITIVE_BOOL, P.PRIMITIVE_INT64, P.PRIMITIVE_FLOAT64, P.STRING, P.VECTOR_UINT8, P.VECTOR_INT64,
                      P.VECTOR_FLOAT64, P.VECTOR_BOOL, P.VOID]
     back = axon.RpcRequestHeader.deserialize(h.serialize())
-    assert [v for _, v, _ in back.params] == [True, 7, 2.5, "text", b"\x00\x01", [1, 2, 3], [1.0, 2.0], [True, False], None]
+    assert back.params == [True, 7, 2.5, "text", b"\x00\x01", [1, 2, 3], [1.0, 2.0], [True, False], None]
+    assert axon.RpcResponseHeader().status == {"value": 0, "category_name": ""} or axon.RpcResponseHeader().status["value"] == 0
+    assert axon.PayloadType.MONOSTATE == axon.PayloadType.NO_PAYLOAD
     assert back.session_id == 5 and back.function_id == 9
     m = axon.TensorMeta.from_tensor(np.zeros((3, 4), dtype=np.float32))
     assert m.shape == [3, 4] and m.dtype.bits == 32 and m.nbytes() == 48
@@ -122,9 +124,9 @@ def test_raw_api_retention_and_checkpoint(axon, tmp_path):
         client = axon.AxonRuntime("raw_client", timeout=5000)
         seen = []
 
-        async def handler(header, payload):
-            seen.append([v for _, v, _ in header.params])
-            return [sum(header.params[0][1])], None
+        async def handler(values):          # raw functions get their parameters as plain positional values
+            seen.append(list(values))
+            return sum(values)
 
         P = axon.ParamType
         server.register_function_raw(77, "sum", [P.VECTOR_INT64], [P.PRIMITIVE_INT64], axon.PayloadType.NO_PAYLOAD,
@@ -135,8 +137,8 @@ def test_raw_api_retention_and_checkpoint(axon, tmp_path):
         h = axon.RpcRequestHeader()
         h.session_id, h.function_id = 3, 77
         h.AddParam([1, 2, 3, 4])
-        resp, payload = await client.invoke_raw("raw_server", h)
-        assert resp.ok and payload is None and resp.results[0][1] == 10
+        assert await client.invoke_raw("raw_server", h) == 10
+        assert seen == [[1, 2, 3, 4]]
         assert server.stored_request_count() == 1       # the retention policy kept the request
         path = server.save_stored_requests(str(tmp_path), "keep")
         assert path.endswith(".avro")

@@ -37,10 +37,11 @@ def test_timeout_forms_and_strict_registration(axon):
     async def no_annotation(x) -> int:
         return 1
 
-    with pytest.raises(TypeError):
+    with pytest.raises(RuntimeError, match="only accepts async functions"):   # the reference's exception type and text
         rt.register_function(not_async)
-    with pytest.raises(TypeError):
+    with pytest.raises(TypeError, match="Unsupported or missing type annotation for parameter 0"):
         rt.register_function(no_annotation)
+    rt.register_function_raw(function_id=900, callable=no_annotation)       # the raw form tolerates it (UNKNOWN)
 
     async def ok(x: int) -> int:
         return x
