@@ -5,6 +5,7 @@
 #pragma once
 
 #include <chrono>
+#include <string>
 #include <cstdint>
 #include <tuple>
 
@@ -54,7 +55,20 @@ class HybridLogicalClock final {
     else logical = lp > rp ? LogicalCounter() : remote.LogicalCounter();
     Bump(top, static_cast<uint16_t>(logical));
   }
+  // The remote clock as its raw 64-bit value, with the wall clock the caller observed
+  // (reference: rpc_core/utils/hybrid_logical_clock.hpp:84-125).
+  void Merge(uint64_t remote_raw, uint64_t observed_physical_ms) noexcept {
+    Merge(HybridLogicalClock{remote_raw}, observed_physical_ms);
+  }
+  void Assign(uint64_t physical_ms, uint16_t logical) noexcept { raw_ = Pack(physical_ms, logical); }
   void AssignRaw(uint64_t raw) noexcept { raw_ = raw; }
+  // Next logical value under the same physical time; the 16-bit counter wraps to 0 on its own
+  // (no carry into the physical part: that is what the reference's BumpLogicalCounter does).
+  void BumpLogicalCounter() noexcept {
+    raw_ = (raw_ & ~kLogicalMask) | ((static_cast<uint64_t>(LogicalCounter()) + 1) & kLogicalMask);
+  }
+  // "<physical ms>.<logical>"
+  [[nodiscard]] std::string ToString() const { return std::to_string(PhysicalTimeMs()) + "." + std::to_string(LogicalCounter()); }
 
   [[nodiscard]] constexpr bool operator==(const HybridLogicalClock& o) const noexcept { return raw_ == o.raw_; }
   [[nodiscard]] constexpr bool operator!=(const HybridLogicalClock& o) const noexcept { return raw_ != o.raw_; }

@@ -314,17 +314,37 @@ bool UcxCudaMemoryResourceManager::export_region(const void* ptr, size_t len, Pe
   return true;
 }
 
-void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d) {
-  if (d.pid == static_cast<uint32_t>(getpid())) {
+namespace {
+// [p, p+len) lies inside one allocation known to the driver in this process
+bool range_is_mapped(const void* p, uint64_t len) {
+  void* base = nullptr;
+  size_t size = 0;
+  if (!p || !address_range(p, &base, &size)) return false;
+  const auto a = reinterpret_cast<uintptr_t>(p), b = reinterpret_cast<uintptr_t>(base);
+  return a >= b && len <= size && a - b <= size - len;
+}
+}  // namespace
+
+void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d, bool same_process) {
+  if (d.offset + d.length < d.offset) return nullptr;  // wraps
+  if (same_process) {
     if (d.device != opt_.device) {
       int can = 0;
       if (cudaDeviceCanAccessPeer(&can, opt_.device, d.device) != cudaSuccess || !can) return nullptr;
+      DeviceGuard on_device(opt_.device);
       cudaError_t e = cudaDeviceEnablePeerAccess(d.device, 0);
       if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return nullptr;
       cudaGetLastError();
     }
-    return reinterpret_cast<void*>(d.base + d.offset);
+    void* p = reinterpret_cast<void*>(d.base + d.offset);
+    if (!range_is_mapped(p, d.length)) {
+      cudaGetLastError();
+      return nullptr;  // not (or no longer) an allocation of this process: the caller stages through the host
+    }
+    return p;
   }
+  // A descriptor that names this process's pid without the caller vouching for it comes from another
+  // pid namespace or host (or is forged): its addresses mean nothing here. The IPC handle decides.
   if (!d.exportable) return nullptr;
   std::lock_guard lk(mu_);
   DeviceGuard on_device(opt_.device);
@@ -347,7 +367,12 @@ void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d) {
     std::memcpy(imp.handle, d.handle, 64);
     it = imports_.emplace(key, imp).first;
   }
-  return static_cast<char*>(it->second.mapped) + d.offset;
+  char* p = static_cast<char*>(it->second.mapped) + d.offset;
+  if (!range_is_mapped(p, d.length)) {
+    cudaGetLastError();
+    return nullptr;  // offset + length reach past the mapped allocation
+  }
+  return p;
 }
 
 void UcxCudaMemoryResourceManager::release_imports() {

@@ -72,7 +72,11 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
   // Describe [ptr, ptr+len) for a peer; registers the allocation on first use.
   bool export_region(const void* ptr, size_t len, PeerRegionDesc* out);
   // Map a peer's region into this process (cached per owner pid + allocation); nullptr on failure.
-  void* import_region(const PeerRegionDesc& d);
+  // `same_process` is the caller's own knowledge that the region's owner lives in this process (the
+  // transport derives it from its registry of live workers, never from the descriptor): only then
+  // is the descriptor's address used as it is, and only after the driver confirmed that the whole
+  // range lies inside one allocation of this process. A mapped region is checked the same way.
+  void* import_region(const PeerRegionDesc& d, bool same_process = false);
   void release_imports();
 
   int device() const { return opt_.device; }

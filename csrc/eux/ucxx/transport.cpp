@@ -59,6 +59,31 @@ uint64_t random_uid() {
 }
 bool is_device_type(ucx_memory_type_t t) { return t == ucx_memory_type::CUDA || t == ucx_memory_type::CUDA_MANAGED; }
 
+// Workers alive in this process, by their random uid. A peer is "this process" only when the uid it
+// presented in the handshake is found here: a pid alone says nothing (two containers, pid namespaces
+// or hosts routinely share one), and it arrives from the wire.
+std::mutex g_live_mu;
+std::unordered_map<uint64_t, int> g_live_uids;
+void live_add(uint64_t uid) {
+  std::lock_guard lk(g_live_mu);
+  ++g_live_uids[uid];
+}
+void live_remove(uint64_t uid) {
+  std::lock_guard lk(g_live_mu);
+  auto it = g_live_uids.find(uid);
+  if (it != g_live_uids.end() && --it->second <= 0) g_live_uids.erase(it);
+}
+bool live_has(uint64_t uid) {
+  std::lock_guard lk(g_live_mu);
+  return g_live_uids.count(uid) != 0;
+}
+
+// Limits on what a frame may claim. One frame from an unauthenticated socket must not be able to make
+// the receiver buffer or allocate without bound.
+constexpr size_t kMaxHeaderLen = size_t(16) << 20;   // AM header bytes (a serialized RPC header with its parameters)
+constexpr size_t kMaxSegCount = 4096;                // scatter-gather segments per message
+constexpr size_t kMinInlineCap = size_t(16) << 20;   // inline payloads: the larger of this and the eager limit
+
 // HELLO / HELLO_ACK body: u64 client id, then the worker address (fixed 60-byte form)
 constexpr size_t kAddrWire = 4 + 4 + 2 + 2 + 4 + 4 + 8 + 32;
 
@@ -115,6 +140,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
   addr_.pid = static_cast<uint32_t>(getpid());
   addr_.device = opt_.device;
   addr_.uid = random_uid();
+  live_add(addr_.uid);
   std::strncpy(addr_.name, opt_.name.c_str(), sizeof(addr_.name) - 1);
   // implicit listener: makes the worker reachable through its address blob
   sockaddr_in in{};
@@ -136,6 +162,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
 }
 
 Worker::~Worker() {
+  live_remove(addr_.uid);
   for (auto& [p, ep] : eps_)
     if (ep->fd_ >= 0) ::close(ep->fd_);
   for (auto& l : listeners_)
@@ -748,8 +775,9 @@ void Worker::handle_readable(Endpoint* ep) {
         ep->direct_active_ = false;
         Endpoint::PendingRecv fin = std::move(pr);
         ep->pending_recvs_.erase(pit);
-        int st = UCS_OK;
-        if (fin.bounce) {  // staged through host memory: scatter into the device destinations
+        int st = ep->direct_total_ == fin.total ? UCS_OK : UCS_ERR_MESSAGE_TRUNCATED;
+        if (st != UCS_OK) ++stats_.truncated;
+        if (fin.bounce && st == UCS_OK) {  // staged through host memory: scatter into the device destinations
           try {
             const char* src = static_cast<const char*>(fin.bounce.get());
             for (auto& d : fin.dev_dsts) {
@@ -796,6 +824,14 @@ bool Worker::parse_frames(Endpoint* ep) {
     FrameHeader fh;
     std::memcpy(&fh, ep->rbuf_.data() + ep->rpos_, sizeof(fh));
     if (fh.magic != kFrameMagic) {
+      fail(ep, UCS_ERR_IO_ERROR);
+      return false;
+    }
+    const size_t inline_cap = std::max(opt_.eager_limit, kMinInlineCap);
+    if (fh.header_len > kMaxHeaderLen || fh.seg_count > kMaxSegCount || (fh.type == kAmEager && fh.payload_len > inline_cap)) {
+      UCX_CONN_ERROR << "frame from " << ep->peer_name_ << " refused: header " << fh.header_len << " B, " << fh.seg_count
+                     << " segments, inline payload " << (fh.type == kAmEager ? fh.payload_len : 0) << " B";
+      ++stats_.frames_refused;
       fail(ep, UCS_ERR_IO_ERROR);
       return false;
     }
@@ -861,9 +897,24 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
       info.seg_sizes.resize(fh.seg_count);
       if (fh.seg_count) std::memcpy(info.seg_sizes.data(), p, size_t(fh.seg_count) * 8);
       p += size_t(fh.seg_count) * 8;
-      if (fh.flags & kFlagDeviceRegions) {
+      uint64_t seg_sum = 0;
+      for (uint64_t sz : info.seg_sizes) seg_sum += sz;
+      if (fh.seg_count && seg_sum != fh.payload_len) {
+        UCX_CONN_ERROR << "RTS from " << ep->peer_name_ << " refused: segment sizes add up to " << seg_sum << ", payload is " << fh.payload_len;
+        ++stats_.frames_refused;
+        fail(ep, UCS_ERR_IO_ERROR);
+        break;
+      }
+      if ((fh.flags & kFlagDeviceRegions) && !peer_is_local(ep)) ++stats_.regions_ignored;
+      if ((fh.flags & kFlagDeviceRegions) && peer_is_local(ep)) {
+        // Device regions are addresses and handles of the sender's process: they mean something only
+        // when the handshake showed that the sender runs on this host. From anyone else they are
+        // ignored and the payload takes the staged host protocol.
         info.regions.resize(fh.seg_count);
         std::memcpy(info.regions.data(), p, size_t(fh.seg_count) * sizeof(PeerRegionDesc));
+        uint64_t reg_sum = 0;
+        for (auto& r : info.regions) reg_sum += r.length;
+        if (reg_sum != fh.payload_len) info.regions.clear();
       }
       ep->rts_[fh.msg_id] = std::move(info);
       AmArrival a;
@@ -888,6 +939,7 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
       ep->direct_seg_ = 0;
       ep->direct_off_ = 0;
       ep->direct_left_ = fh.payload_len;
+      ep->direct_total_ = fh.payload_len;
       // bytes of the payload that are already in the buffer
       size_t have = std::min<size_t>(ep->rbuf_.size() - ep->rpos_, ep->direct_left_);
       if (pit != ep->pending_recvs_.end()) {
@@ -914,8 +966,9 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
         if (pit != ep->pending_recvs_.end()) {
           Endpoint::PendingRecv fin = std::move(pit->second);
           ep->pending_recvs_.erase(pit);
-          int st = UCS_OK;
-          if (fin.bounce) {
+          int st = fh.payload_len == fin.total ? UCS_OK : UCS_ERR_MESSAGE_TRUNCATED;
+          if (st != UCS_OK) ++stats_.truncated;
+          if (fin.bounce && st == UCS_OK) {
             try {
               const char* src = static_cast<const char*>(fin.bounce.get());
               for (auto& d : fin.dev_dsts) {
@@ -1000,7 +1053,7 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   fh.type = kAmRts;
   fh.seg_count = static_cast<uint32_t>(seg_count);
   std::vector<PeerRegionDesc> regions;
-  if (device && cuda_mr_) {
+  if (device && cuda_mr_ && peer_is_local(ep)) {
     regions.resize(seg_count);
     bool ok = true;
     for (size_t i = 0; i < seg_count && ok; ++i) ok = cuda_mr_->export_region(segs[i].data, segs[i].size, &regions[i]);
@@ -1089,8 +1142,13 @@ int Worker::rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, s
   const bool dst_device = is_device_type(mem_type);
   if (!info.regions.empty() && dst_device) {
     int st = device_pull(ep, msg_id, info, segs, seg_count, done);
-    if (st == UCS_INPROGRESS) return st;
-    // mapping or launch failed: fall back to the staged host protocol
+    if (st == UCS_INPROGRESS || st == UCS_OK) {
+      ++stats_.device_pulls;
+      return st;
+    }
+    note_staged(ep, "the sender's memory could not be mapped, or no flag slot or launch was to be had");
+  } else if (dst_device && is_device_type(info.mem_type)) {
+    note_staged(ep, "the sender announced no usable device regions (allocation not exportable, or peer not shown to be on this host)");
   }
   Endpoint::PendingRecv pr;
   pr.mem_type = mem_type;
@@ -1111,6 +1169,17 @@ int Worker::rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, s
   ep->pending_recvs_.emplace(msg_id, std::move(pr));
   send_control(ep, kRndvCts, is_device_type(info.mem_type) ? kFlagStage : 0, msg_id);
   return UCS_INPROGRESS;
+}
+
+// A device payload that goes device -> host -> wire -> host -> device is a silent factor of ten or
+// more: say so, once per endpoint, at a level the default logger shows.
+void Worker::note_staged(Endpoint* ep, const char* why) {
+  ++stats_.device_staged;
+  nvtx_mark("eux.transport.device_staged");
+  if (ep->staged_logged_) return;
+  ep->staged_logged_ = true;
+  UCX_CONN_ERROR << opt_.name << ": device payload from " << ep->remote_.name_str << " (" << ep->peer_name_
+                 << ") is staged through host memory: " << why << " (reported once per endpoint)";
 }
 
 void Worker::rndv_discard(Endpoint* ep, uint64_t msg_id) {
@@ -1157,6 +1226,14 @@ bool Worker::cancel_recv(Endpoint* ep, uint64_t msg_id) {
 // ---------------------------------------------------------------------------
 // device data plane
 // ---------------------------------------------------------------------------
+// The peer presented the uid of a worker that lives in this process (and this process's pid).
+bool Worker::peer_is_this_process(const Endpoint* ep) const {
+  return ep->remote_.addr.pid == addr_.pid && live_has(ep->remote_.addr.uid);
+}
+// Same host, shown by the handshake: the peer mapped the shared-memory channel that this side created
+// (or the other way round), which only a process on this host can do; or it is this very process.
+bool Worker::peer_is_local(const Endpoint* ep) const { return ep->shm_active_ || peer_is_this_process(ep); }
+
 bool Worker::ensure_device() {
   if (device_ready_) return true;
   if (device_failed_ || opt_.device < 0) return false;
@@ -1190,7 +1267,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
   NvtxRange range("eux.transport.device_pull");
   std::vector<void*> srcs(info.regions.size());
   for (size_t i = 0; i < info.regions.size(); ++i) {
-    srcs[i] = cuda_mr_->import_region(info.regions[i]);
+    srcs[i] = cuda_mr_->import_region(info.regions[i], peer_is_this_process(ep));
     if (!srcs[i]) return UCS_ERR_UNSUPPORTED;
   }
   // walk source regions and destination segments together

@@ -201,7 +201,7 @@ class Endpoint {
   size_t rpos_ = 0;
   bool direct_active_ = false;     // DATA body is being read straight into a posted receive
   uint64_t direct_msg_ = 0;
-  size_t direct_seg_ = 0, direct_off_ = 0, direct_left_ = 0;
+  size_t direct_seg_ = 0, direct_off_ = 0, direct_left_ = 0, direct_total_ = 0;
   std::unordered_map<uint64_t, PendingSend> pending_sends_;
   std::unordered_map<uint64_t, PendingRecv> pending_recvs_;
   std::unordered_map<uint64_t, RtsInfo> rts_;
@@ -209,6 +209,7 @@ class Endpoint {
   bool auto_accepted_ = false;
   std::unique_ptr<ShmChannel> shm_;  // offered or mapped channel
   bool shm_active_ = false;          // frames go through shm_ instead of the socket
+  bool staged_logged_ = false;       // the "staged through the host" line was printed for this endpoint
 };
 
 class Worker {
@@ -269,6 +270,16 @@ class Worker {
 
   size_t endpoint_count() const { return eps_.size(); }
 
+  // Counters of the decisions that cost performance or that refuse input; read from the worker's thread.
+  struct Stats {
+    uint64_t frames_refused = 0;   // frames whose sizes were beyond the limits (the endpoint was failed)
+    uint64_t regions_ignored = 0;  // device regions announced by a peer that did not prove it is on this host
+    uint64_t device_pulls = 0;     // device payloads moved by the transfer kernel
+    uint64_t device_staged = 0;    // device payloads that went through host memory instead
+    uint64_t truncated = 0;        // DATA frames whose length was not the posted one
+  };
+  const Stats& stats() const { return stats_; }
+
  private:
   struct Listener {
     int fd = -1;
@@ -302,6 +313,8 @@ class Worker {
   void start_data_send(Endpoint* ep, uint64_t msg_id, bool staged);
   int device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
                   Completion& done);
+  bool peer_is_this_process(const Endpoint* ep) const;
+  bool peer_is_local(const Endpoint* ep) const;
   bool ensure_device();
   void poll_device();
   void flush_pull_batch();
@@ -337,6 +350,8 @@ class Worker {
   static constexpr size_t kFlagSlots = 512;
   static constexpr size_t kBatchMaxBytes = size_t(256) << 10;
   std::vector<eux_pull_item> pull_batch_;
+  Stats stats_;
+  void note_staged(Endpoint* ep, const char* why);
 };
 
 }  // namespace eux::ucxx::transport

@@ -1388,6 +1388,8 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
 // name `g_noalloc_gemm_scratch` is only a stand-in: the address a kernel can use is
 // obtained per device with cudaGetSymbolAddress below.
 // ---------------------------------------------------------------------------
+#include <atomic>
+
 #include "eux_no_alloc.h"
 
 static __device__ __align__(256) uint32_t g_noalloc_gemm_scratch[EUX_NOALLOC_GEMM_SCRATCH_BYTES / 4];
@@ -1396,19 +1398,24 @@ extern "C" int eux_gemm_bf16_noalloc(const void* x, const void* w_t, void* y, in
                                      uint64_t wait_timeout_ns, void* stream) {
   if (!x || !w_t || !y || M <= 0 || N <= 0 || K <= 0) return EUX_ERR_BAD_ARG;
   if (M > EUX_NOALLOC_GEMM_MAX_M) return EUX_ERR_TOO_LARGE;  // one counter per 128 rows is all the static array holds
+  // The shapes the kernels take, checked here so that a call that is going to be refused has put
+  // nothing on the stream: the clear below touches the array that every call shares.
+  if (M % 128 || N % 256 || K % 64) return EUX_ERR_BAD_ARG;
   // Set-up, once per device, with that device current: the device address of the static array.
-  static uint32_t* scratch_addr[64] = {nullptr};
+  // Host threads may race to be first; they would all store the same address, atomically.
+  static std::atomic<uint32_t*> scratch_addr[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return EUX_ERR_BAD_ARG;
-  if (!scratch_addr[dev]) {
+  uint32_t* scratch = scratch_addr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     uint32_t* ptr = nullptr;
     e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_gemm_scratch);
     if (e != cudaSuccess) return (int)e;
-    scratch_addr[dev] = ptr;
+    scratch_addr[dev].store(ptr, std::memory_order_release);
+    scratch = ptr;
   }
-  uint32_t* scratch = scratch_addr[dev];
   // The array keeps whatever the previous call (or an interrupted kernel) left: counters must start at zero.
   const size_t used = ((size_t)M / 128 + 64) * sizeof(uint32_t);
   e = cudaMemsetAsync(scratch, 0, used, (cudaStream_t)stream);

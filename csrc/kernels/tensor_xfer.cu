@@ -67,15 +67,20 @@ __device__ __forceinline__ bool cta_wait_arrival(const eux_xfer_desc& d) {
   return s_ok != 0;
 }
 
-// All stores of this CTA are done; the last CTA of the grid publishes the flag.
+// All stores of this CTA are done; the last CTA of the grid publishes the flag, and only if no CTA
+// of the grid gave up: every CTA runs its own bounded wait, so near the deadline one can time out (and
+// skip its share of the copy) while the last one to arrive succeeded. The scratch word counts arrivals
+// in its low 31 bits; a CTA that failed sets the top bit before it counts itself.
 __device__ __forceinline__ void cta_publish(const eux_xfer_desc& d, uint32_t* counter, bool ok) {
   __syncthreads();
   if (threadIdx.x != 0) return;
   __threadfence_system();
   bool last = true;
   if (gridDim.x > 1) {
-    uint32_t old = atomicAdd(counter, 1u);
-    last = (old == gridDim.x - 1);
+    if (!ok) atomicOr(counter, 0x80000000u);
+    const uint32_t old = atomicAdd(counter, 1u);
+    last = ((old & 0x7fffffffu) == gridDim.x - 1);
+    if (old & 0x80000000u) ok = false;
     if (last) {
       *counter = 0;  // leave the scratch word clean for the next launch
       __threadfence();

@@ -45,6 +45,23 @@ CXX_FLAGS = [
 ]
 
 
+def _stdcxx_link_flags():
+    """Link against the system's shared libstdc++ and export nothing from static archives.
+
+    Some toolchain wrappers find only a static libstdc++.a: the runtime libraries would then carry
+    their own copy of the C++ runtime *and export it*, and a process that loads them before another
+    C++ library (PyTorch, say) would have that library's calls bound to the wrong copy."""
+    flags = ["-Wl,--exclude-libs,ALL"]
+    for cand in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/lib/x86_64-linux-gnu/libstdc++.so.6", "/usr/lib64/libstdc++.so.6"):
+        if Path(cand).exists():
+            flags.append(cand)
+            break
+    return flags
+
+
+STDCXX = _stdcxx_link_flags()
+
+
 def _newer(inputs, output: Path) -> bool:
     if not output.exists():
         return True
@@ -127,7 +144,7 @@ def build_runtime(verbose: bool = False) -> Path:
 
     objs, changed = _compile_objects(srcs, cc, "rt", deps, verbose)
     if changed or not out.exists():
-        _run([CXX, "-shared", "-o", out, *objs, "-L", LIB, "-leux_kernels",
+        _run([CXX, "-shared", "-o", out, *objs, *STDCXX, "-L", LIB, "-leux_kernels",
               "-L", CUDA_HOME / "lib64", "-lcudart", "-ldl", "-lrt", "-pthread",
               "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + str(CUDA_HOME / "lib64")], verbose)
     return out
@@ -143,7 +160,7 @@ def build_binaries(verbose: bool = False):
     def one(s):
         out = LIB / ("eux_" + s.stem)
         if _newer([s, *deps] + ([rt] if rt.exists() else []), out):
-            _run([CXX, *CXX_FLAGS, s, "-o", out, "-L", LIB, "-leux_runtime", "-leux_kernels",
+            _run([CXX, *CXX_FLAGS, s, "-o", out, *STDCXX, "-L", LIB, "-leux_runtime", "-leux_kernels",
                   "-L", CUDA_HOME / "lib64", "-lcudart", "-ldl", "-lrt",
                   "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + str(CUDA_HOME / "lib64")], verbose)
         return out
@@ -171,7 +188,7 @@ def build_python_module(verbose: bool = False) -> Path:
     objs, changed = _compile_objects(srcs, cc, "py", deps, verbose)
     rt = LIB / "libeux_runtime.so"
     if changed or _newer([rt], out):
-        _run([CXX, "-shared", "-o", out, *objs, "-L", LIB, "-leux_runtime", "-leux_kernels",
+        _run([CXX, "-shared", "-o", out, *objs, *STDCXX, "-L", LIB, "-leux_runtime", "-leux_kernels",
               "-L", CUDA_HOME / "lib64", "-lcudart", "-Wl,-rpath,$ORIGIN/../_lib",
               "-Wl,-rpath," + str(CUDA_HOME / "lib64")], verbose)
     return out

@@ -665,7 +665,10 @@ class AxonRuntime(_axon.AxonRuntime):
                 raise TypeError(f"Unsupported or missing type annotation for parameter {i} in function '{name}'. {_SUPPORTED}.")
         if any(t == ParamType.UNKNOWN for t in sig.return_types):
             raise TypeError(f"Unsupported or missing return type annotation for function '{name}'. {_SUPPORTED}, None.")
-        if memory_policy is not None and sig.n_tensor_params and from_dlpack_fn is None:
+        # Small messages arrive in host memory without the memory_policy being asked, so they need a
+        # from_dlpack function. The reference demands an explicit one here; this layer only does so when
+        # the annotations give it nothing to derive one from (torch / numpy / jax types do).
+        if memory_policy is not None and from_dlpack_fn is None and any(f is None for f in sig.param_from_dlpack.values()):
             raise RuntimeError(
                 f"Function '{name}' has tensor parameters and custom memory_policy is set, but from_dlpack_fn is not provided. "
                 "from_dlpack_fn is required for small messages, which arrive in host memory without the memory_policy being "
@@ -708,9 +711,6 @@ class AxonRuntime(_axon.AxonRuntime):
             name = bound["function_name"]
             sig = _sig_from_types(bound["param_types"], bound["return_types"], bound["input_payload_type"],
                                   bound["return_payload_type"], bound.get("from_dlpack_fn"))
-            if memory_policy is not None and sig.n_tensor_params and bound.get("from_dlpack_fn") is None:
-                raise RuntimeError(f"Function '{name}' has tensor parameters and custom memory_policy is set, but from_dlpack_fn "
-                                   "is not provided.")
         else:
             name = self._name_of(fn, bound.get("function_name"), function_id)
             sig = _parse_signature(fn)

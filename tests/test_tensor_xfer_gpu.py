@@ -122,10 +122,12 @@ def test_pull_batch_items_in_launch_parameters(cuda_device):
         tx.pull_batch(items + items)
 
 
-def test_bounded_wait_reports_timeout(cuda_device):
-    """A wait that nothing satisfies ends by itself with a status, not a hang."""
+@pytest.mark.parametrize("n", [1024, 1 << 22])   # one CTA; a grid of many CTAs, each with its own bounded wait
+def test_bounded_wait_reports_timeout(cuda_device, n):
+    """A wait that nothing satisfies ends by itself with a status, not a hang, and the completion
+    flag is not published, however many CTAs shared the transfer."""
     from execution_ucx_b200.ops import tensor_xfer as tx
-    src = torch.ones(1024, device=cuda_device)
+    src = torch.ones(n, device=cuda_device)
     dst = torch.zeros_like(src)
     never = _flag(cuda_device)
     status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
