@@ -99,6 +99,24 @@ std::vector<std::byte> AxonWorker::GetLocalAddress() const {
   return a;
 }
 
+ucxx::transport::Worker::Stats AxonWorker::GetTransportStats() const {
+  ucxx::transport::Worker::Stats t;
+  for (auto* ctx : {server_ctx_.get(), client_ctx_.get()}) {
+    if (!ctx) continue;
+    const auto& s = ctx->worker().stats();
+    t.frames_refused += s.frames_refused;
+    t.regions_ignored += s.regions_ignored;
+    t.device_pulls += s.device_pulls;
+    t.device_staged += s.device_staged;
+    t.truncated += s.truncated;
+    t.device_eager_sent += s.device_eager_sent;
+    t.device_eager_recv += s.device_eager_recv;
+    t.device_pushes += s.device_pushes;
+    t.device_push_recv += s.device_push_recv;
+  }
+  return t;
+}
+
 // ---- clock, hooks -----------------------------------------------------------------------
 rpc::utils::HybridLogicalClock AxonWorker::TickHlc() {
   std::lock_guard lk(hlc_mu_);

@@ -168,6 +168,10 @@ class AxonWorker {
 
   // ---- retained requests ----
   storage::AxonStorage& GetStorage() { return *storage_; }
+  // Counters of the transports under the server and the client context, added up (how many device
+  // payloads were pulled, pushed, sent eagerly, staged through the host, ...). Read without
+  // synchronisation: meant for tests and monitoring between calls.
+  ucxx::transport::Worker::Stats GetTransportStats() const;
   // Re-run every stored request through its registered handler (responses are dropped); returns how many ran.
   size_t ProcessStoredRequests();
   // Show every stored request to a visitor; Discard removes it from the storage.

@@ -193,6 +193,20 @@ class PyAxonRuntime {
   void set_timeout(py::object t) { rt_->SetTimeout(parse_timeout(t)); }
   void set_reject_messages(bool r) { rt_->SetRejectMessages(r); }
   std::string worker_name() const { return name_; }
+  py::dict transport_stats() {
+    const auto s = rt_->worker().GetTransportStats();
+    py::dict d;
+    d["frames_refused"] = s.frames_refused;
+    d["regions_ignored"] = s.regions_ignored;
+    d["device_pulls"] = s.device_pulls;
+    d["device_staged"] = s.device_staged;
+    d["truncated"] = s.truncated;
+    d["device_eager_sent"] = s.device_eager_sent;
+    d["device_eager_recv"] = s.device_eager_recv;
+    d["device_pushes"] = s.device_pushes;
+    d["device_push_recv"] = s.device_push_recv;
+    return d;
+  }
   size_t stored_request_count() { return rt_->worker().GetStorage().size(); }
   std::string save_stored_requests(const std::string& dir, const std::string& prefix) {
     py::gil_scoped_release nogil;
@@ -512,6 +526,8 @@ void bind_runtime(py::module_& m) {
            py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none())
       .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
       .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)
+      .def("transport_stats", &PyAxonRuntime::transport_stats,
+           "Counters of the transports under this runtime: device payloads pulled / pushed / sent eagerly / staged through the host, frames refused.")
       .def("stored_request_count", &PyAxonRuntime::stored_request_count)
       .def("save_stored_requests", &PyAxonRuntime::save_stored_requests, py::arg("directory"), py::arg("prefix") = "axon")
       .def("load_stored_requests", &PyAxonRuntime::load_stored_requests).def("process_stored_requests", &PyAxonRuntime::process_stored_requests);

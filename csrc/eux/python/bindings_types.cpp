@@ -212,7 +212,8 @@ py::object PyBuffer::to_capsule_wrapper(const TensorMeta& meta) const {
   if (!buf) throw py::value_error("empty buffer");
   if (rpc::utils::CalculateTensorSize(meta) > buf->size()) throw py::value_error("the metadata describes more bytes than the buffer holds");
   TensorMeta m = meta;
-  m.device = device_of(buf->type(), m.device.device_id);
+  // the bytes are where this runtime received them: its device, whatever device the sender's tensor was on
+  m.device = device_of(buf->type(), device_id);
   return py::cast(DLPackCapsuleWrapper(make_capsule(buf, buf->data(), m), m.device));
 }
 TensorMeta PyBuffer::bytes_meta() const {
@@ -321,7 +322,7 @@ void bind_types(py::module_& m) {
         if (!v.vec || i >= v.vec->size()) throw py::index_error("segment index out of range");
         if (rpc::utils::CalculateTensorSize(meta) > (*v.vec)[i].size) throw py::value_error("the metadata describes more bytes than the segment holds");
         TensorMeta m = meta;
-        m.device = device_of(v.vec->type(), m.device.device_id);
+        m.device = device_of(v.vec->type(), v.device_id);
         return DLPackCapsuleWrapper(make_capsule(v.vec, (*v.vec)[i].data, m), m.device);
       })
       .def("owner", [](const PyBufferVec& v, size_t i) {

@@ -5,6 +5,12 @@
 // then on both write their frames into the rings and poll them from their progress loop. The TCP
 // socket stays open as the liveness signal. The reference gets the same effect from UCX's
 // shared-memory transports (posix/sysv/cma) under ucp_am_send_nbx.
+//
+// Behind the rings the segment holds two pages of 64-bit flag words, one page per direction. A side
+// whose worker drives a GPU registers them with CUDA, so that a kernel on its GPU can store a
+// sequence number that the peer's *host* thread reads with a plain load: the completion signal of a
+// pushed payload crosses process boundaries without a control frame. A second set of words per
+// direction is written and read by the two host threads only (receive-ring credits).
 #pragma once
 
 #include <fcntl.h>
@@ -32,6 +38,8 @@ class ShmChannel {
  public:
   static constexpr uint32_t kMagic = 0x4d485345u;  // "ESHM"
   static constexpr size_t kRingBytes = size_t(2) << 20;
+  static constexpr size_t kFlagWords = 512;          // device-written completion words per direction (one page)
+  static constexpr size_t kHostWords = 512;          // host-written words per direction (credits and the like)
 
   // The offering side: creates a fresh segment; the name is what the peer needs to map it.
   static std::unique_ptr<ShmChannel> create(const std::string& name) {
@@ -107,6 +115,17 @@ class ShmChannel {
     r->head.store(head + n, std::memory_order_release);
     return static_cast<ssize_t>(n);
   }
+  // ---- flag pages -------------------------------------------------------------------------
+  // Words that this side's GPU writes and the peer's host reads / the other way round.
+  volatile uint64_t* out_flags() { return flag_page(creator_ ? 0 : 1); }
+  volatile uint64_t* in_flags() { return flag_page(creator_ ? 1 : 0); }
+  // Words written by this side's host thread and read by the peer's / the other way round.
+  std::atomic<uint64_t>* out_words() { return reinterpret_cast<std::atomic<uint64_t>*>(const_cast<uint64_t*>(flag_page(creator_ ? 2 : 3))); }
+  std::atomic<uint64_t>* in_words() { return reinterpret_cast<std::atomic<uint64_t>*>(const_cast<uint64_t*>(flag_page(creator_ ? 3 : 2))); }
+  // The page-aligned range that holds the device-written words of both directions (for cudaHostRegister).
+  void* flag_area() { return base_ + flags_offset(); }
+  static constexpr size_t flag_area_bytes() { return 2 * kPage; }
+
   bool readable() const {
     const ShmRing* r = const_cast<ShmChannel*>(this)->in_ring();
     return r->tail.load(std::memory_order_acquire) != r->head.load(std::memory_order_relaxed);
@@ -118,7 +137,11 @@ class ShmChannel {
     uint32_t ring_bytes;
     char pad[56];
   };
-  static size_t total_bytes() { return sizeof(Header) + 2 * sizeof(ShmRing) + 2 * kRingBytes; }
+  static constexpr size_t kPage = 4096;
+  static_assert(kFlagWords * 8 == kPage && kHostWords * 8 == kPage);
+  static size_t flags_offset() { return (sizeof(Header) + 2 * sizeof(ShmRing) + 2 * kRingBytes + kPage - 1) / kPage * kPage; }
+  static size_t total_bytes() { return flags_offset() + 4 * kPage; }
+  volatile uint64_t* flag_page(int i) { return reinterpret_cast<volatile uint64_t*>(base_ + flags_offset() + size_t(i) * kPage); }
   static std::unique_ptr<ShmChannel> map(int fd, const std::string& name, bool creator) {
     void* p = ::mmap(nullptr, total_bytes(), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
     if (p == MAP_FAILED) return nullptr;

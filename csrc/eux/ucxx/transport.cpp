@@ -84,6 +84,15 @@ constexpr size_t kMaxHeaderLen = size_t(16) << 20;   // AM header bytes (a seria
 constexpr size_t kMaxSegCount = 4096;                // scatter-gather segments per message
 constexpr size_t kMinInlineCap = size_t(16) << 20;   // inline payloads: the larger of this and the eager limit
 
+// Device channel geometry. The shared flag page of a direction (512 words) is split: the first 256 words
+// signal pushed rendezvous payloads (the receiver picks the word), the next kEagerSlots the eager ring's slots.
+constexpr uint32_t kPushWords = 256;
+constexpr uint32_t kEagerSlots = 32;                 // one bit each in a 64-bit free mask
+constexpr uint32_t kEagerSlotBytes = 64 << 10;
+constexpr uint32_t kEagerWordBase = kPushWords;
+static_assert(kEagerWordBase + kEagerSlots <= ShmChannel::kFlagWords);
+constexpr auto kEagerArrivalTimeout = std::chrono::seconds(10);
+
 // HELLO / HELLO_ACK body: u64 client id, then the worker address (fixed 60-byte form)
 constexpr size_t kAddrWire = 4 + 4 + 2 + 2 + 4 + 4 + 8 + 32;
 
@@ -135,6 +144,9 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
     if (end != e && v > 0) opt_.eager_limit = v;
   }
   if (const char* e = std::getenv("EUX_SHM")) opt_.use_shm = e[0] != '0';
+  if (const char* e = std::getenv("EUX_DEV_EAGER_LIMIT")) opt_.dev_eager_limit = std::strtoull(e, nullptr, 10);
+  if (const char* e = std::getenv("EUX_PUSH_THRESH")) opt_.push_threshold = std::strtoull(e, nullptr, 10);
+  if (opt_.dev_eager_limit > kEagerSlotBytes) opt_.dev_eager_limit = kEagerSlotBytes;
   epfd_ = epoll_create1(EPOLL_CLOEXEC);
   if (epfd_ < 0) throw std::system_error(errno, std::generic_category(), "epoll_create1");
   addr_.pid = static_cast<uint32_t>(getpid());
@@ -163,6 +175,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
 
 Worker::~Worker() {
   live_remove(addr_.uid);
+  for (auto& [p, ep] : eps_) teardown_device_channel(p);
   for (auto& [p, ep] : eps_)
     if (ep->fd_ >= 0) ::close(ep->fd_);
   for (auto& l : listeners_)
@@ -287,6 +300,7 @@ void Worker::activate_shm(Endpoint* ep) {
   if (!ep->shm_ || ep->shm_active_) return;
   ep->shm_active_ = true;
   shm_eps_.push_back(ep);
+  setup_device_channel(ep);
 }
 
 // Socket-like I/O on whichever channel the endpoint uses.
@@ -504,8 +518,21 @@ int Worker::progress() {
     ++i;
   }
   if (!hellos_.empty()) poll_hellos();
+  if (!awaiting_ring_.empty()) {
+    for (size_t i = 0; i < awaiting_ring_.size();) {
+      Endpoint* ep = awaiting_ring_[i];
+      const bool alive = eps_.count(ep) && ep->state_ == Endpoint::State::kConnected && ep->await_dev_ring_;
+      if (alive && now <= ep->dev_ring_deadline_) {
+        ++i;
+        continue;
+      }
+      awaiting_ring_[i] = awaiting_ring_.back();
+      awaiting_ring_.pop_back();
+      if (alive) finish_connect(ep);  // the peer stayed silent: go on without its ring
+    }
+  }
   if (!pull_batch_.empty()) flush_pull_batch();
-  if (!device_ops_.empty()) poll_device();
+  if (!device_ops_.empty() || !eager_waits_.empty() || !push_waits_.empty()) poll_device();
   if (!graveyard_.empty()) {
     for (Endpoint* ep : graveyard_) eps_.erase(ep);
     graveyard_.clear();
@@ -515,13 +542,15 @@ int Worker::progress() {
 
 void Worker::fail(Endpoint* ep, int status) {
   if (ep->state_ == Endpoint::State::kFailed || ep->state_ == Endpoint::State::kClosed) return;
-  const bool was_connecting = ep->state_ == Endpoint::State::kConnecting || ep->state_ == Endpoint::State::kHelloSent;
+  const bool was_connecting = ep->state_ == Endpoint::State::kConnecting || ep->state_ == Endpoint::State::kHelloSent || ep->await_dev_ring_;
+  ep->await_dev_ring_ = false;
   ep->state_ = Endpoint::State::kFailed;
   if (ep->fd_ >= 0) {
     epoll_ctl(epfd_, EPOLL_CTL_DEL, ep->fd_, nullptr);
     ::close(ep->fd_);
     ep->fd_ = -1;
   }
+  teardown_device_channel(ep);
   ep->shm_active_ = false;
   ep->shm_.reset();
   // every operation in flight ends with the endpoint's status
@@ -560,6 +589,7 @@ void Worker::close(Endpoint* ep, bool notify_peer) {
     ::close(ep->fd_);
     ep->fd_ = -1;
   }
+  teardown_device_channel(ep);
   ep->shm_active_ = false;
   ep->shm_.reset();
   if (ep->state_ != Endpoint::State::kFailed) {
@@ -837,6 +867,7 @@ bool Worker::parse_frames(Endpoint* ep) {
     }
     size_t meta = fh.header_len;
     if (fh.type == kAmRts) meta += size_t(fh.seg_count) * 8 + ((fh.flags & kFlagDeviceRegions) ? size_t(fh.seg_count) * sizeof(PeerRegionDesc) : 0);
+    if (fh.type == kAmDevEager) meta += 8;  // the flag value that the payload's arrival will carry
     size_t body = meta + (fh.type == kAmEager ? fh.payload_len : 0);
     if (avail < sizeof(fh) + body) break;  // wait for the rest (eager bodies are small)
     const char* b = ep->rbuf_.data() + ep->rpos_ + sizeof(fh);
@@ -864,9 +895,15 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
       }
       if (ep->state_ == Endpoint::State::kHelloSent) {
         ep->state_ = Endpoint::State::kConnected;
-        Completion c = std::move(ep->on_connected_);
-        ep->on_connected_ = nullptr;
-        if (c) c(UCS_OK);
+        // Two GPU workers on one host: the caller learns "connected" once the peer has said where its
+        // device receive ring is (it follows the HELLO_ACK through the rings), or after a short wait.
+        if (ep->shm_active_ && opt_.device >= 0 && cuda_mr_ && ep->remote_.addr.device >= 0 && ep->on_connected_) {
+          ep->await_dev_ring_ = true;
+          ep->dev_ring_deadline_ = std::chrono::steady_clock::now() + std::chrono::seconds(3);
+          awaiting_ring_.push_back(ep);
+        } else {
+          finish_connect(ep);
+        }
         if (eps_.count(ep) && ep->state_ == Endpoint::State::kConnected) flush(ep);
       }
       break;
@@ -893,6 +930,7 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
       Endpoint::RtsInfo info;
       info.payload_len = fh.payload_len;
       info.mem_type = static_cast<ucx_memory_type_t>(fh.mem_type);
+      info.push_ok = (fh.flags & kFlagPushOk) != 0;
       const char* p = body + fh.header_len;
       info.seg_sizes.resize(fh.seg_count);
       if (fh.seg_count) std::memcpy(info.seg_sizes.data(), p, size_t(fh.seg_count) * 8);
@@ -931,7 +969,12 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
       else if (a.header) mr_.deallocate(ucx_memory_type::HOST, a.header, a.header_len);
       break;
     }
-    case kRndvCts: start_data_send(ep, fh.msg_id, (fh.flags & kFlagStage) != 0); break;
+    case kRndvCts:
+      if (fh.flags & kFlagPush) on_push_cts(ep, fh, body);
+      else start_data_send(ep, fh.msg_id, (fh.flags & kFlagStage) != 0);
+      break;
+    case kDevRing: on_dev_ring(ep, fh, body); break;
+    case kAmDevEager: on_dev_eager(ep, fh, body); break;
     case kRndvData: {
       auto pit = ep->pending_recvs_.find(fh.msg_id);
       ep->direct_active_ = true;
@@ -990,7 +1033,10 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
     }
     case kRndvFin: {
       // receiver -> sender: the payload was pulled (or refused); sender -> receiver: the send was withdrawn
-      auto it = ep->pending_sends_.find(fh.msg_id);
+      // Both sides number their messages from 1: a FIN that comes from the *sender* of a message (it
+      // withdrew the send, or cannot push it) must not be mistaken for the answer to this side's own
+      // message of the same number.
+      auto it = (fh.flags & kFlagFromSender) ? ep->pending_sends_.end() : ep->pending_sends_.find(fh.msg_id);
       if (it != ep->pending_sends_.end()) {
         Completion c = std::move(it->second.done);
         ep->pending_sends_.erase(it);
@@ -998,6 +1044,22 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
         break;
       }
       ep->rts_.erase(fh.msg_id);
+      for (auto pw = push_waits_.begin(); pw != push_waits_.end(); ++pw) {
+        if (pw->ep != ep || pw->msg_id != fh.msg_id) continue;
+        // the sender could not push after all (or withdrew the send): take the other roads
+        PushWait w = std::move(*pw);
+        push_waits_.erase(pw);
+        if (ep->push_inflight_) --ep->push_inflight_;
+        if (fh.status == UCS_ERR_UNSUPPORTED) {
+          w.info.push_ok = false;
+          ep->rts_[w.msg_id] = std::move(w.info);
+          int st = rndv_recv(ep, w.msg_id, w.segs.data(), w.segs.size(), ucx_memory_type::CUDA, w.done);
+          if (st != UCS_INPROGRESS && w.done) w.done(st);
+        } else if (w.done) {
+          w.done(fh.status);
+        }
+        return;
+      }
       auto pr = ep->pending_recvs_.find(fh.msg_id);
       if (pr != ep->pending_recvs_.end() && fh.status != UCS_OK) {
         Completion c = std::move(pr->second.done);
@@ -1023,6 +1085,10 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   const bool rndv = total > 0 && (force_rndv || device || seg_count > 1 || total >= opt_.eager_limit);
   const uint64_t id = ep->next_msg_id_++;
   if (msg_id_out) *msg_id_out = id;
+  if (device && !force_rndv && seg_count == 1 && total > 0 && total <= opt_.dev_eager_limit && ep->tx_ring_ && ep->out_flags_dev_) {
+    int st = dev_eager_send(ep, header, header_len, segs[0], mem_type, id, done);
+    if (st != UCS_ERR_NO_RESOURCE) return st;  // no free slot right now: the rendezvous takes it
+  }
   FrameHeader fh;
   fh.header_len = static_cast<uint32_t>(header_len);
   fh.payload_len = total;
@@ -1059,6 +1125,7 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
     for (size_t i = 0; i < seg_count && ok; ++i) ok = cuda_mr_->export_region(segs[i].data, segs[i].size, &regions[i]);
     if (ok) fh.flags |= kFlagDeviceRegions;
     else regions.clear();
+    if (ok && ep->out_flags_dev_ && opt_.push_threshold && total >= opt_.push_threshold) fh.flags |= kFlagPushOk;
   }
   it.owned.resize(sizeof(fh) + header_len + seg_count * 8 + regions.size() * sizeof(PeerRegionDesc));
   char* p = it.owned.data();
@@ -1140,6 +1207,10 @@ int Worker::rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, s
     return UCS_ERR_MESSAGE_TRUNCATED;
   }
   const bool dst_device = is_device_type(mem_type);
+  if (info.push_ok && dst_device && !info.regions.empty() && ep->shm_active_ && opt_.push_threshold) {
+    int st = request_push(ep, msg_id, info, segs, seg_count, done);
+    if (st == UCS_INPROGRESS) return st;  // otherwise: pull it
+  }
   if (!info.regions.empty() && dst_device) {
     int st = device_pull(ep, msg_id, info, segs, seg_count, done);
     if (st == UCS_INPROGRESS || st == UCS_OK) {
@@ -1196,7 +1267,7 @@ bool Worker::cancel_send(Endpoint* ep, uint64_t msg_id) {
   auto it = ep->pending_sends_.find(msg_id);
   if (it != ep->pending_sends_.end()) {
     ep->pending_sends_.erase(it);
-    if (ep->state_ == Endpoint::State::kConnected) send_control(ep, kRndvFin, 0, msg_id, UCS_ERR_CANCELED);
+    if (ep->state_ == Endpoint::State::kConnected) send_control(ep, kRndvFin, kFlagFromSender, msg_id, UCS_ERR_CANCELED);
     return true;
   }
   for (auto s = ep->sendq_.begin(); s != ep->sendq_.end(); ++s) {
@@ -1218,7 +1289,9 @@ bool Worker::cancel_send(Endpoint* ep, uint64_t msg_id) {
 bool Worker::cancel_recv(Endpoint* ep, uint64_t msg_id) {
   if (!eps_.count(ep)) return true;
   for (auto& d : device_ops_)
-    if (d.ep == ep && d.msg_id == msg_id) return false;
+    if (d.ep == ep && d.msg_id == msg_id && d.send_fin) return false;
+  for (auto& w : push_waits_)
+    if (w.ep == ep && w.msg_id == msg_id) return false;  // the peer's kernel may be writing the buffers
   ep->pending_recvs_.erase(msg_id);
   return true;
 }
@@ -1226,6 +1299,13 @@ bool Worker::cancel_recv(Endpoint* ep, uint64_t msg_id) {
 // ---------------------------------------------------------------------------
 // device data plane
 // ---------------------------------------------------------------------------
+void Worker::finish_connect(Endpoint* ep) {
+  ep->await_dev_ring_ = false;
+  Completion c = std::move(ep->on_connected_);
+  ep->on_connected_ = nullptr;
+  if (c && ep->state_ == Endpoint::State::kConnected) c(UCS_OK);
+}
+
 // The peer presented the uid of a worker that lives in this process (and this process's pid).
 bool Worker::peer_is_this_process(const Endpoint* ep) const {
   return ep->remote_.addr.pid == addr_.pid && live_has(ep->remote_.addr.uid);
@@ -1359,10 +1439,389 @@ void Worker::poll_device() {
     std::atomic_thread_fence(std::memory_order_acquire);
     DeviceOp op = std::move(device_ops_.front());
     device_ops_.pop_front();
-    if (op.ep && eps_.count(op.ep) && op.ep->state_ == Endpoint::State::kConnected)
+    if (op.send_fin && op.ep && eps_.count(op.ep) && op.ep->state_ == Endpoint::State::kConnected)
       send_control(op.ep, kRndvFin, 0, op.msg_id, UCS_OK);
     if (op.done) op.done(UCS_OK);
   }
+  // payloads that peers push: small ones into ring slots, large ones into posted buffers. The peer's
+  // kernel stores the flag word (in the shared page) after its data stores; this thread reads it.
+  if (!eager_waits_.empty()) {
+    const auto now = last_progress_;
+    for (auto it = eager_waits_.begin(); it != eager_waits_.end();) {
+      const bool arrived = it->shm->in_flags()[kEagerWordBase + it->slot] == it->seq;
+      if (arrived) {
+        std::atomic_thread_fence(std::memory_order_acquire);
+        EagerWait w = std::move(*it);
+        it = eager_waits_.erase(it);
+        ++stats_.device_eager_recv;
+        if (on_am && w.ep) on_am(std::move(w.arrival));
+        else if (w.arrival.header) mr_.deallocate(ucx_memory_type::HOST, w.arrival.header, w.arrival.header_len);
+        continue;  // the slot goes back when the arrival's keep-alive token is dropped
+      }
+      if (now > it->deadline) {
+        UCX_CONN_ERROR << opt_.name << ": the payload of an eager device message (slot " << it->slot << ") never arrived; dropped";
+        if (it->arrival.header) mr_.deallocate(ucx_memory_type::HOST, it->arrival.header, it->arrival.header_len);
+        it = eager_waits_.erase(it);
+        continue;
+      }
+      ++it;
+    }
+  }
+  if (!push_waits_.empty()) {
+    const auto now = last_progress_;
+    for (auto it = push_waits_.begin(); it != push_waits_.end();) {
+      const bool arrived = it->shm->in_flags()[it->word] == it->value;
+      if (!arrived && now <= it->deadline) {
+        ++it;
+        continue;
+      }
+      std::atomic_thread_fence(std::memory_order_acquire);
+      PushWait w = std::move(*it);
+      it = push_waits_.erase(it);
+      if (w.ep && eps_.count(w.ep) && w.ep->push_inflight_) --w.ep->push_inflight_;
+      if (arrived) ++stats_.device_push_recv;
+      else UCX_CONN_ERROR << opt_.name << ": a pushed payload (message " << w.msg_id << ") did not arrive in time";
+      if (w.done) w.done(arrived ? UCS_OK : UCS_ERR_TIMED_OUT);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// device channel: flag pages registered with CUDA, eager receive rings, pushed rendezvous
+// ---------------------------------------------------------------------------
+Endpoint::DevRing::~DevRing() {
+  try {
+    if (mr && base) mr->deallocate(ucx_memory_type::CUDA, base, bytes);
+  } catch (...) {
+  }
+}
+
+// Runs once per endpoint, when its shared-memory channel becomes active (so the peer is on this host)
+// and this worker drives a GPU: registers the channel's flag pages with CUDA, allocates the receive ring
+// for small device payloads and tells the peer where it is.
+void Worker::setup_device_channel(Endpoint* ep) {
+  if (ep->dev_tried_ || opt_.device < 0 || !cuda_mr_ || !ep->shm_) return;
+  ep->dev_tried_ = true;
+  // Whatever comes of the set-up, the peer is told (a ring, or "none"): a connecting peer holds its
+  // "connected" back until it knows, so that its first message already finds the fast paths.
+  PeerRegionDesc d;
+  uint32_t geo[2] = {0, 0};
+  auto announce = [&] {
+    FrameHeader fh;
+    fh.type = kDevRing;
+    fh.header_len = sizeof(PeerRegionDesc) + 8;
+    Endpoint::SendItem it;
+    it.owned.resize(sizeof(fh) + fh.header_len);
+    std::memcpy(it.owned.data(), &fh, sizeof(fh));
+    std::memcpy(it.owned.data() + sizeof(fh), &d, sizeof(d));
+    std::memcpy(it.owned.data() + sizeof(fh) + sizeof(d), geo, 8);
+    enqueue(ep, std::move(it));
+  };
+  if ((!opt_.dev_eager_limit && !opt_.push_threshold) || !ensure_device()) {
+    announce();
+    return;
+  }
+  if (cudaHostRegister(ep->shm_->flag_area(), ShmChannel::flag_area_bytes(), cudaHostRegisterMapped | cudaHostRegisterPortable) != cudaSuccess) {
+    cudaGetLastError();
+    UCX_CONN_WARN << opt_.name << ": the shared flag page could not be registered with CUDA; device payloads will be pulled";
+    announce();
+    return;
+  }
+  ep->flags_registered_ = true;
+  void* dev = nullptr;
+  if (cudaHostGetDevicePointer(&dev, const_cast<uint64_t*>(ep->shm_->out_flags()), 0) != cudaSuccess || !dev) {
+    cudaGetLastError();
+    announce();
+    return;
+  }
+  ep->out_flags_dev_ = static_cast<uint64_t*>(dev);
+  if (opt_.dev_eager_limit) {
+    // the ring: kEagerSlots slots, allocated from the pooled (already exportable) device memory
+    auto ring = std::make_shared<Endpoint::DevRing>();
+    try {
+      ring->bytes = size_t(kEagerSlots) * kEagerSlotBytes;
+      ring->base = mr_.allocate(ucx_memory_type::CUDA, ring->bytes);
+      ring->mr = &mr_;
+      if (cuda_mr_->export_region(ring->base, ring->bytes, &d)) {
+        ep->rx_ring_ = std::move(ring);
+        geo[0] = kEagerSlots;
+        geo[1] = kEagerSlotBytes;
+      }
+    } catch (...) {
+    }
+  }
+  announce();
+}
+
+// The peer's ring: map it and mark every slot free.
+void Worker::on_dev_ring(Endpoint* ep, const FrameHeader& fh, const char* body) {
+  // a connect that was held back for this frame completes now, whatever the frame says
+  struct Release {
+    Worker* w;
+    Endpoint* ep;
+    ~Release() { w->finish_connect(ep); }
+  } release{this, ep};
+  if (fh.header_len < sizeof(PeerRegionDesc) + 8 || !cuda_mr_ || !peer_is_local(ep) || !ep->out_flags_dev_) return;
+  PeerRegionDesc d;
+  uint32_t geo[2];
+  std::memcpy(&d, body, sizeof(d));
+  std::memcpy(geo, body + sizeof(d), 8);
+  if (geo[0] == 0 || geo[0] > 64 || geo[1] == 0 || uint64_t(geo[0]) * geo[1] != d.length) return;
+  void* p = cuda_mr_->import_region(d, peer_is_this_process(ep));
+  if (!p) return;
+  ep->tx_ring_ = static_cast<char*>(p);
+  ep->tx_slots_ = geo[0];
+  ep->tx_slot_bytes_ = geo[1];
+  ep->tx_free_ = geo[0] == 64 ? ~uint64_t(0) : ((uint64_t(1) << geo[0]) - 1);
+}
+
+// Before the shared segment is unmapped nothing on the GPU may still write into its flag page.
+void Worker::teardown_device_channel(Endpoint* ep) {
+  for (auto it = eager_waits_.begin(); it != eager_waits_.end();) {
+    if (it->ep != ep) {
+      ++it;
+      continue;
+    }
+    if (it->arrival.header) mr_.deallocate(ucx_memory_type::HOST, it->arrival.header, it->arrival.header_len);
+    it = eager_waits_.erase(it);
+  }
+  std::vector<Completion> cbs;
+  for (auto it = push_waits_.begin(); it != push_waits_.end();) {
+    if (it->ep != ep) {
+      ++it;
+      continue;
+    }
+    if (it->done) cbs.push_back(std::move(it->done));
+    it = push_waits_.erase(it);
+  }
+  ep->push_inflight_ = 0;
+  ep->tx_ring_ = nullptr;
+  ep->tx_free_ = 0;
+  ep->out_flags_dev_ = nullptr;
+  if (ep->flags_registered_ && ep->shm_) {
+    if (stream_) cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));  // kernels of this worker that target the page (bounded)
+    cudaHostUnregister(ep->shm_->flag_area());
+    cudaGetLastError();
+    ep->flags_registered_ = false;
+  }
+  ep->rx_ring_.reset();  // slots still held by the application keep the ring alive through their tokens
+  for (auto& cb : cbs) cb(UCS_ERR_CONNECTION_RESET);
+}
+
+// Small device payload: one CTA of the next batched launch stores it into a free slot of the peer's ring,
+// then raises the slot's flag in the shared page (the peer's host polls it) and this worker's own
+// completion word. The active-message header travels at once through the control ring.
+int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t& seg, ucx_memory_type_t mem_type,
+                           uint64_t msg_id, Completion& done) {
+  if (!ensure_device() || device_ops_.size() + 2 >= kFlagSlots) return UCS_ERR_NO_RESOURCE;
+  if (seg.size > ep->tx_slot_bytes_) return UCS_ERR_NO_RESOURCE;
+  ep->tx_free_ |= ep->shm_->in_words()[0].exchange(0, std::memory_order_acquire);  // slots the peer has handed back
+  if (!ep->tx_free_) return UCS_ERR_NO_RESOURCE;
+  const uint32_t slot = static_cast<uint32_t>(__builtin_ctzll(ep->tx_free_));
+  ep->tx_free_ &= ep->tx_free_ - 1;
+  const uint64_t value = ++ep->tx_seq_;
+  const uint64_t seq = ++device_seq_;
+  eux_pull_item item{};
+  item.src = seg.data;
+  item.dst = ep->tx_ring_ + size_t(slot) * ep->tx_slot_bytes_;
+  item.nbytes = seg.size;
+  item.flag = ep->out_flags_dev_ + kEagerWordBase + slot;
+  item.flag_value = value;
+  item.flag2 = flag_dev_ + seq % kFlagSlots;
+  item.flag2_value = seq;
+  if (seg.size) {
+    pull_batch_.push_back(item);
+    device_ops_.push_back({seq, ep, msg_id, std::move(done), false});
+    if (pull_batch_.size() == EUX_PULL_BATCH_MAX) flush_pull_batch();
+  } else {
+    --device_seq_;
+  }
+  FrameHeader fh;
+  fh.type = kAmDevEager;
+  fh.header_len = static_cast<uint32_t>(header_len);
+  fh.payload_len = seg.size;
+  fh.msg_id = msg_id;
+  fh.mem_type = static_cast<uint32_t>(mem_type);
+  fh.status = static_cast<int32_t>(slot);
+  Endpoint::SendItem it;
+  it.owned.resize(sizeof(fh) + header_len + 8);
+  std::memcpy(it.owned.data(), &fh, sizeof(fh));
+  if (header_len) std::memcpy(it.owned.data() + sizeof(fh), header, header_len);
+  std::memcpy(it.owned.data() + sizeof(fh) + header_len, &value, 8);
+  enqueue(ep, std::move(it));
+  ++stats_.device_eager_sent;
+  nvtx_mark("eux.transport.device_eager_send");
+  return ep->state_ == Endpoint::State::kConnected ? UCS_INPROGRESS : UCS_ERR_CONNECTION_RESET;
+}
+
+void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body) {
+  const uint32_t slot = static_cast<uint32_t>(fh.status);
+  if (!ep->rx_ring_ || !ep->shm_ || slot >= kEagerSlots || fh.payload_len > kEagerSlotBytes) {
+    UCX_CONN_ERROR << opt_.name << ": eager device frame from " << ep->peer_name_ << " names a slot this worker never offered";
+    ++stats_.frames_refused;
+    fail(ep, UCS_ERR_IO_ERROR);
+    return;
+  }
+  EagerWait w;
+  w.ep = ep;
+  w.shm = ep->shm_;
+  w.ring = ep->rx_ring_;
+  w.slot = slot;
+  std::memcpy(&w.seq, body + fh.header_len, 8);
+  w.deadline = std::chrono::steady_clock::now() + kEagerArrivalTimeout;
+  AmArrival& a = w.arrival;
+  a.ep = ep;
+  a.header_len = fh.header_len;
+  a.header = fh.header_len ? mr_.allocate(ucx_memory_type::HOST, fh.header_len) : nullptr;
+  if (fh.header_len) std::memcpy(a.header, body, fh.header_len);
+  a.data = static_cast<char*>(w.ring->base) + size_t(slot) * kEagerSlotBytes;
+  a.data_len = fh.payload_len;
+  a.msg_id = fh.msg_id;
+  a.sender_mem_type = static_cast<ucx_memory_type_t>(fh.mem_type);
+  a.data_mem_type = ucx_memory_type::CUDA;
+  // Dropping the token hands the slot back: a bit in the word the sender's host thread collects. It
+  // may be dropped on any thread, long after the endpoint is gone: it owns what it touches.
+  struct SlotToken {
+    std::shared_ptr<ShmChannel> shm;
+    std::shared_ptr<Endpoint::DevRing> ring;
+    uint32_t slot;
+    SlotToken(std::shared_ptr<ShmChannel> s, std::shared_ptr<Endpoint::DevRing> r, uint32_t i) : shm(std::move(s)), ring(std::move(r)), slot(i) {}
+    SlotToken(const SlotToken&) = delete;  // exactly one object stands for the slot: its end hands the slot back
+    SlotToken& operator=(const SlotToken&) = delete;
+    ~SlotToken() { shm->out_words()[0].fetch_or(uint64_t(1) << slot, std::memory_order_release); }
+  };
+  a.data_keep = std::make_shared<SlotToken>(w.shm, w.ring, slot);
+  eager_waits_.push_back(std::move(w));
+}
+
+// Receiver side of a pushed rendezvous: answer the RTS with the posted buffers' regions and the flag word
+// the sender's kernel shall raise when the bytes are in place.
+int Worker::request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
+                         Completion& done) {
+  if (!cuda_mr_ || ep->push_inflight_ + 1 >= kPushWords || seg_count > kMaxSegCount) return UCS_ERR_UNSUPPORTED;
+  std::vector<PeerRegionDesc> regions;
+  uint64_t left = info.payload_len;
+  for (size_t i = 0; i < seg_count && left > 0; ++i) {
+    const uint64_t n = std::min<uint64_t>(segs[i].size, left);
+    PeerRegionDesc d;
+    if (!cuda_mr_->export_region(segs[i].data, n, &d) || !d.exportable) return UCS_ERR_UNSUPPORTED;
+    regions.push_back(d);
+    left -= n;
+  }
+  if (left != 0 || regions.empty()) return UCS_ERR_UNSUPPORTED;
+  const uint64_t value = ++ep->push_seq_;
+  const uint32_t word = static_cast<uint32_t>(value % kPushWords);
+  ++ep->push_inflight_;
+  FrameHeader fh;
+  fh.type = kRndvCts;
+  fh.flags = kFlagPush;
+  fh.msg_id = msg_id;
+  fh.seg_count = static_cast<uint32_t>(regions.size());
+  fh.header_len = static_cast<uint32_t>(regions.size() * sizeof(PeerRegionDesc));
+  fh.payload_len = value;
+  fh.status = static_cast<int32_t>(word);
+  Endpoint::SendItem it;
+  it.owned.resize(sizeof(fh) + fh.header_len);
+  std::memcpy(it.owned.data(), &fh, sizeof(fh));
+  std::memcpy(it.owned.data() + sizeof(fh), regions.data(), fh.header_len);
+  PushWait w;
+  w.ep = ep;
+  w.shm = ep->shm_;
+  w.msg_id = msg_id;
+  w.word = word;
+  w.value = value;
+  w.done = std::move(done);
+  w.segs.assign(segs, segs + seg_count);
+  // a bound that no healthy transfer comes near: 30 s plus a second per GiB
+  w.deadline = std::chrono::steady_clock::now() + std::chrono::seconds(30 + (info.payload_len >> 30));
+  w.info = std::move(info);
+  push_waits_.push_back(std::move(w));
+  enqueue(ep, std::move(it));
+  return UCS_INPROGRESS;
+}
+
+// Sender side: CTS(push) arrived. Map the receiver's regions and copy the payload into them with the
+// transfer kernel; the last launch raises the receiver's flag word and this worker's own.
+void Worker::on_push_cts(Endpoint* ep, const FrameHeader& fh, const char* body) {
+  auto pit = ep->pending_sends_.find(fh.msg_id);
+  if (pit == ep->pending_sends_.end()) return;  // withdrawn meanwhile; the FIN(cancelled) is on its way
+  const uint32_t word = static_cast<uint32_t>(fh.status);
+  auto refuse = [&] { send_control(ep, kRndvFin, kFlagFromSender, fh.msg_id, UCS_ERR_UNSUPPORTED); };  // the send stays pending: the receiver pulls
+  if (!peer_is_local(ep) || !ep->out_flags_dev_ || !cuda_mr_ || word >= kPushWords || fh.seg_count == 0 ||
+      fh.header_len != size_t(fh.seg_count) * sizeof(PeerRegionDesc) || !ensure_device() || device_ops_.size() + 2 >= kFlagSlots) {
+    refuse();
+    return;
+  }
+  std::vector<PeerRegionDesc> regions(fh.seg_count);
+  std::memcpy(regions.data(), body, fh.header_len);
+  std::vector<char*> dsts(regions.size());
+  uint64_t room = 0;
+  for (size_t i = 0; i < regions.size(); ++i) {
+    dsts[i] = static_cast<char*>(cuda_mr_->import_region(regions[i], peer_is_this_process(ep)));
+    if (!dsts[i]) {
+      refuse();
+      return;
+    }
+    room += regions[i].length;
+  }
+  auto& ps = pit->second;
+  uint64_t total = 0;
+  for (auto& sgm : ps.segs) total += sgm.size;
+  if (room < total) {
+    refuse();
+    return;
+  }
+  NvtxRange range("eux.transport.device_push");
+  // walk source segments and destination regions together
+  std::vector<std::pair<const void*, void*>> ptrs;
+  std::vector<size_t> lens;
+  size_t si = 0, so = 0, di = 0, dof = 0;
+  while (si < ps.segs.size() && di < regions.size()) {
+    const size_t sl = ps.segs[si].size - so, dl = regions[di].length - dof;
+    const size_t n = std::min(sl, dl);
+    if (n) {
+      ptrs.emplace_back(static_cast<const char*>(ps.segs[si].data) + so, dsts[di] + dof);
+      lens.push_back(n);
+    }
+    so += n;
+    dof += n;
+    if (so == ps.segs[si].size) ++si, so = 0;
+    if (dof == regions[di].length) ++di, dof = 0;
+  }
+  const uint64_t seq = ++device_seq_;
+  flush_pull_batch();  // launches stay in the order of their sequence numbers
+  int rc = launch_pieces(ptrs, lens, ep->out_flags_dev_ + word, fh.payload_len, flag_dev_ + seq % kFlagSlots, seq);
+  if (rc != 0) {
+    --device_seq_;
+    UCX_CONN_ERROR << "transfer kernel launch failed: " << eux_error_string(rc);
+    refuse();
+    return;
+  }
+  Endpoint::PendingSend sent = std::move(ps);
+  ep->pending_sends_.erase(pit);
+  device_ops_.push_back({seq, ep, fh.msg_id, std::move(sent.done), false});
+  ++stats_.device_pushes;
+}
+
+int Worker::launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs, const std::vector<size_t>& lens, uint64_t* flag,
+                          uint64_t flag_value, uint64_t* flag2, uint64_t flag2_value) {
+  for (size_t i = 0; i < ptrs.size(); ++i) {
+    eux_xfer_desc d{};
+    d.src = ptrs[i].first;
+    d.dst = ptrs[i].second;
+    d.n_elems = lens[i];
+    d.src_dtype = d.dst_dtype = EUX_DT_BYTES;
+    d.op = EUX_OP_NONE;
+    if (i + 1 == ptrs.size()) {
+      d.flag = flag;
+      d.flag_value = flag_value;
+      d.flag2 = flag2;
+      d.flag2_value = flag2_value;
+    }
+    int rc = eux_xfer_launch(&d, counter_dev_, 0, stream_);
+    if (rc != 0) return rc;
+  }
+  return 0;
 }
 
 void Worker::update_interest(Endpoint*) {}

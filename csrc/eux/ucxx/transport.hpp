@@ -70,12 +70,17 @@ enum FrameType : uint8_t {
   kRndvData = 6,
   kRndvFin = 7,
   kClose = 8,
+  kDevRing = 9,     // same-host peers with GPUs: "this is my device receive ring" (one PeerRegionDesc + geometry)
+  kAmDevEager = 10, // active message whose small device payload is being pushed into the receiver's ring slot
 };
 enum FrameFlags : uint8_t {
   kFlagDeviceRegions = 1,  // RTS carries PeerRegionDesc per segment
   kFlagStage = 2,          // CTS: send the payload through host memory
   kFlagShmOffer = 4,       // HELLO: the name of a shared-memory channel follows the address
   kFlagShmAccept = 8,      // HELLO_ACK: the channel is mapped; frames travel through it from now on
+  kFlagPushOk = 16,        // RTS: the sender can push the payload itself and signal through the shared flag page
+  kFlagFromSender = 64,    // FIN: sent by the sender of the message (send withdrawn / cannot push), not by its receiver
+  kFlagPush = 32,          // CTS: "push it here": the receiver's regions follow, status = flag word, payload_len = flag value
 };
 
 #pragma pack(push, 1)
@@ -119,6 +124,11 @@ struct AmArrival {
   uint64_t msg_id = 0;
   uint32_t seg_count = 0;   // > 0 only for scatter-gather sends
   ucx_memory_type_t sender_mem_type = ucx_memory_type::HOST;
+  // Where `data` lives. HOST: memory of the worker's resource, to be deallocated by the callee.
+  // CUDA: a slot of this worker's device receive ring; the callee drops `data_keep` when it is done
+  // with the bytes (that returns the slot to the sender), and never deallocates `data`.
+  ucx_memory_type_t data_mem_type = ucx_memory_type::HOST;
+  std::shared_ptr<void> data_keep;
 };
 
 struct ConnRequest {
@@ -139,6 +149,14 @@ struct WorkerOptions {
   size_t eager_limit = 8192;     // payloads below this travel inline (host memory)
   size_t send_copy_limit = 8192; // inline payloads up to this size are copied, so the send completes at once
   bool use_shm = true;           // peers on this host talk through shared-memory rings (EUX_SHM=0 turns it off)
+  // Device payloads up to this size go out eagerly: one CTA of a batched launch stores them into a slot of
+  // the peer's device receive ring and raises a flag the peer's host thread polls. No RTS, no FIN.
+  // 0 turns the path off (EUX_DEV_EAGER_LIMIT). At most the ring's slot size.
+  size_t dev_eager_limit = size_t(64) << 10;
+  // Device payloads from this size on are pushed by the sender's kernel (the receiver answers the RTS with
+  // its own regions) instead of pulled by the receiver's: with traffic in both directions stores keep
+  // the links fuller than loads. 0 turns pushing off (EUX_PUSH_THRESH).
+  size_t push_threshold = size_t(4) << 20;
 };
 
 class Endpoint {
@@ -181,6 +199,7 @@ class Endpoint {
     ucx_memory_type_t mem_type = ucx_memory_type::HOST;
     std::vector<uint64_t> seg_sizes;
     std::vector<PeerRegionDesc> regions;
+    bool push_ok = false;          // the sender offered to push the payload itself
   };
   struct RemoteInfo {
     WorkerAddress addr{};
@@ -207,8 +226,27 @@ class Endpoint {
   std::unordered_map<uint64_t, RtsInfo> rts_;
   Completion on_connected_;
   bool auto_accepted_ = false;
-  std::unique_ptr<ShmChannel> shm_;  // offered or mapped channel
+  std::shared_ptr<ShmChannel> shm_;  // offered or mapped channel (buffers handed to the application may outlive the endpoint)
   bool shm_active_ = false;          // frames go through shm_ instead of the socket
+  // ---- device channel: set up after the shared-memory channel when both workers drive a GPU ----
+  struct DevRing {                   // this side's receive ring in device memory
+    UcxMemoryResourceManager* mr = nullptr;
+    void* base = nullptr;
+    size_t bytes = 0;
+    ~DevRing();
+  };
+  bool dev_tried_ = false;           // set-up was attempted (whatever came of it)
+  bool flags_registered_ = false;    // the channel's flag pages are registered with CUDA in this process
+  uint64_t* out_flags_dev_ = nullptr;  // device alias of shm_->out_flags()
+  std::shared_ptr<DevRing> rx_ring_;   // slots the peer pushes eager payloads into
+  char* tx_ring_ = nullptr;            // the peer's ring, mapped here
+  uint32_t tx_slots_ = 0, tx_slot_bytes_ = 0;
+  uint64_t tx_free_ = 0;               // bit i: slot i of the peer's ring is free
+  uint64_t tx_seq_ = 0;                // flag values of eager pushes (per endpoint, increasing)
+  uint64_t push_seq_ = 0;              // flag values handed out for payloads the peer pushes to this side
+  uint32_t push_inflight_ = 0;
+  bool await_dev_ring_ = false;        // connect completion held back until the peer's kDevRing frame
+  std::chrono::steady_clock::time_point dev_ring_deadline_{};
   bool staged_logged_ = false;       // the "staged through the host" line was printed for this endpoint
 };
 
@@ -277,6 +315,10 @@ class Worker {
     uint64_t device_pulls = 0;     // device payloads moved by the transfer kernel
     uint64_t device_staged = 0;    // device payloads that went through host memory instead
     uint64_t truncated = 0;        // DATA frames whose length was not the posted one
+    uint64_t device_eager_sent = 0;  // small device payloads pushed into a peer's ring
+    uint64_t device_eager_recv = 0;  // ... and received through this worker's rings
+    uint64_t device_pushes = 0;      // large device payloads pushed by this worker's kernel on a CTS(push)
+    uint64_t device_push_recv = 0;   // ... and received that way
   };
   const Stats& stats() const { return stats_; }
 
@@ -297,6 +339,27 @@ class Worker {
     Endpoint* ep;
     uint64_t msg_id;
     Completion done;
+    bool send_fin = true;  // a pull answers the sender with FIN; a push or an eager send tells nobody
+  };
+  struct EagerWait {  // kAmDevEager frame received, its payload still on the way into the ring slot
+    Endpoint* ep;
+    std::shared_ptr<ShmChannel> shm;
+    std::shared_ptr<Endpoint::DevRing> ring;
+    uint32_t slot;
+    uint64_t seq;
+    AmArrival arrival;
+    std::chrono::steady_clock::time_point deadline;
+  };
+  struct PushWait {   // CTS(push) sent: the peer's kernel writes into the posted buffers and then the flag word
+    Endpoint* ep;
+    std::shared_ptr<ShmChannel> shm;
+    uint64_t msg_id;
+    uint32_t word;
+    uint64_t value;
+    Completion done;
+    Endpoint::RtsInfo info;               // kept for the fall-back when the peer cannot push after all
+    std::vector<ucx_buffer_t> segs;
+    std::chrono::steady_clock::time_point deadline;
   };
   Endpoint* new_endpoint(int fd);
   void fail(Endpoint* ep, int status);
@@ -317,6 +380,17 @@ class Worker {
   bool peer_is_local(const Endpoint* ep) const;
   bool ensure_device();
   void poll_device();
+  void setup_device_channel(Endpoint* ep);
+  void finish_connect(Endpoint* ep);
+  void teardown_device_channel(Endpoint* ep);
+  void on_dev_ring(Endpoint* ep, const FrameHeader& fh, const char* body);
+  void on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body);
+  void on_push_cts(Endpoint* ep, const FrameHeader& fh, const char* body);
+  int dev_eager_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t& seg, ucx_memory_type_t mem_type,
+                     uint64_t msg_id, Completion& done);
+  int request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count, Completion& done);
+  int launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs, const std::vector<size_t>& lens, uint64_t* flag, uint64_t flag_value,
+                    uint64_t* flag2, uint64_t flag2_value);
   void flush_pull_batch();
   void update_interest(Endpoint* ep);
 
@@ -350,6 +424,9 @@ class Worker {
   static constexpr size_t kFlagSlots = 512;
   static constexpr size_t kBatchMaxBytes = size_t(256) << 10;
   std::vector<eux_pull_item> pull_batch_;
+  std::vector<Endpoint*> awaiting_ring_;
+  std::deque<EagerWait> eager_waits_;
+  std::deque<PushWait> push_waits_;
   Stats stats_;
   void note_staged(Endpoint* ep, const char* why);
 };

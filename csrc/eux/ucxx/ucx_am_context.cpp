@@ -256,6 +256,8 @@ void ucx_am_context::on_am(transport::AmArrival&& a) {
   d.msg_id = a.msg_id;
   d.seg_count = a.seg_count;
   d.sender_mem_type = a.sender_mem_type;
+  d.data_mem_type = a.data_mem_type;
+  d.data_keep = std::move(a.data_keep);
   am_queue_.push_back(d);
   wake_one(recv_waiters_head_, recv_waiters_tail_);
 }

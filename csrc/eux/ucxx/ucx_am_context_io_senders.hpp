@@ -340,7 +340,7 @@ struct recv_sender : recv_args {
           raw.header = {desc.header, desc.header_length};
           raw.buffer_type = s.data_type;
           desc.header = nullptr;
-          if (!desc.rndv && s.data_type == ucx_memory_type::HOST) {
+          if (!desc.rndv && s.data_type == ucx_memory_type::HOST && desc.data_mem_type == ucx_memory_type::HOST) {
             raw.buffer = {desc.data, desc.data_length};
             desc.data = nullptr;
           } else {
@@ -350,7 +350,9 @@ struct recv_sender : recv_args {
         }
         ucx_am_data& target = s.user ? *s.user : *msg->get();
         if (!desc.rndv) {
-          if (desc.data && desc.data_length) mr.memcpy(target.buffer_type, target.buffer.data, ucx_memory_type::HOST, desc.data, desc.data_length);
+          // eager bytes sit in host memory, or (small device payloads between GPUs of one host) in a slot of
+          // the worker's device receive ring
+          if (desc.data && desc.data_length) mr.memcpy(target.buffer_type, target.buffer.data, desc.data_mem_type, desc.data, desc.data_length);
           desc.release(mr);
           deliver();
           return;

@@ -34,7 +34,11 @@ struct recv_header_sender {
         return;
       }
       UcxConnection* conn = ctx.connections().get_connection(d.conn_id);
-      UcxBuffer buffer(mr, ucx_memory_type::HOST, d.data, d.data_length, nullptr, true);
+      // Eager bytes: host memory owned by the buffer from here on, or a slot of the device receive ring,
+      // which goes back to the sender when the buffer drops its keep-alive token.
+      UcxBuffer buffer = d.data_keep ? UcxBuffer(mr, d.data_mem_type, d.data, d.data_length, nullptr, true,
+                                                 [keep = std::move(d.data_keep)](void*) mutable { keep.reset(); })
+                                     : UcxBuffer(mr, ucx_memory_type::HOST, d.data, d.data_length, nullptr, true);
       auto res = std::make_shared<recv_header_result_t>(
           std::in_place_index<1>, active_message_header_buffer_bundle(std::move(header), std::move(buffer), d.conn_id, conn));
       this->finish([this, res] { this->r.set_value(std::move(*res)); });

@@ -7,7 +7,8 @@ namespace eux::ucxx {
 void UcxAmDesc::release(UcxMemoryResourceManager& mr) noexcept {
   try {
     if (header) mr.deallocate(ucx_memory_type::HOST, header, header_length);
-    if (data) mr.deallocate(ucx_memory_type::HOST, data, data_length);
+    if (data && !data_keep) mr.deallocate(ucx_memory_type::HOST, data, data_length);
+    data_keep.reset();
   } catch (...) {
   }
   header = data = nullptr;

@@ -34,6 +34,11 @@ struct UcxAmDesc {
   uint64_t msg_id = 0;
   uint32_t seg_count = 0;
   ucx_memory_type_t sender_mem_type = ucx_memory_type::HOST;
+  // Eager data is HOST memory of the context's resource, unless `data_keep` is set: then it is a slot
+  // of the transport's device receive ring (`data_mem_type`), never deallocated, and handed back to the
+  // sender when the last copy of the token is dropped.
+  ucx_memory_type_t data_mem_type = ucx_memory_type::HOST;
+  std::shared_ptr<void> data_keep;
   void release(UcxMemoryResourceManager& mr) noexcept;  // frees header/data that are still attached
 };
 

@@ -79,6 +79,9 @@ typedef struct eux_xfer_desc {
   uint64_t wait_value;
   uint64_t wait_timeout_ns;
   uint32_t* status; /* local device (or mapped host) word; may be NULL */
+  uint64_t* flag2;  /* a second word published together with `flag` (the sender's own completion word when
+                       `flag` belongs to the receiver); may be NULL */
+  uint64_t flag2_value;
 } eux_xfer_desc;
 
 /* scratch: one zero-initialised uint32 counter per in-flight transfer, used to
@@ -101,7 +104,9 @@ EUX_API int eux_xfer_batch_launch(const eux_xfer_desc* descs_dev, int n, void* s
  * from host or device memory to find the work): CTA i copies items[i] and then release-stores
  * items[i].flag_value to items[i].flag at system scope, so the host learns of every copy on its own.
  * The transport uses it to pull the payloads of all the small messages that arrived in one pass of its
- * loop (sources are peers' memory). n <= EUX_PULL_BATCH_MAX; buffers of any alignment. */
+ * loop (sources are peers' memory), and in the other direction to push small device payloads into the
+ * receive ring of a peer (destinations and `flag` are the peer's, `flag2` is the sender's own completion
+ * word). n <= EUX_PULL_BATCH_MAX; buffers of any alignment. */
 #define EUX_PULL_BATCH_MAX 48
 typedef struct eux_pull_item {
   const void* src;
@@ -109,6 +114,8 @@ typedef struct eux_pull_item {
   uint64_t nbytes;
   uint64_t* flag; /* mapped pinned host memory or device memory; may be NULL */
   uint64_t flag_value;
+  uint64_t* flag2; /* a second word published with the first (sender-side completion of a push); may be NULL */
+  uint64_t flag2_value;
 } eux_pull_item;
 EUX_API int eux_xfer_pull_batch_launch(const eux_pull_item* items, int n, void* stream);
 

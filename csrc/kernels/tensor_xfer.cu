@@ -87,6 +87,7 @@ __device__ __forceinline__ void cta_publish(const eux_xfer_desc& d, uint32_t* co
     }
   }
   if (last && ok && d.flag) st_release_sys(d.flag, d.flag_value);
+  if (last && ok && d.flag2) st_release_sys(d.flag2, d.flag2_value);
 }
 
 // Dense byte copy. A CTA works on one contiguous block at a time and the blocks are dealt
@@ -610,9 +611,10 @@ __global__ void __launch_bounds__(kPullBatchThreads) xfer_pull_batch_kernel(cons
     for (uint64_t b = threadIdx.x; b < d.nbytes; b += blockDim.x) dst[b] = src[b];
   }
   __syncthreads();
-  if (threadIdx.x == 0 && d.flag) {
+  if (threadIdx.x == 0 && (d.flag || d.flag2)) {
     __threadfence_system();
-    st_release_sys(d.flag, d.flag_value);
+    if (d.flag) st_release_sys(d.flag, d.flag_value);
+    if (d.flag2) st_release_sys(d.flag2, d.flag2_value);
   }
 }
 

@@ -24,7 +24,7 @@ PULL_BATCH_MAX = 48
 class PullItem(C.Structure):
     """eux_pull_item: one dense copy of a batch whose descriptors travel in the launch parameters."""
     _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("nbytes", C.c_uint64), ("flag", C.c_void_p),
-                ("flag_value", C.c_uint64)]
+                ("flag_value", C.c_uint64), ("flag2", C.c_void_p), ("flag2_value", C.c_uint64)]
 
 
 class XferDesc(C.Structure):
@@ -35,7 +35,7 @@ class XferDesc(C.Structure):
         ("shape", C.c_int64 * EUX_MAX_DIMS), ("stride", C.c_int64 * EUX_MAX_DIMS),
         ("flag", C.c_void_p), ("flag_value", C.c_uint64),
         ("wait_flag", C.c_void_p), ("wait_value", C.c_uint64), ("wait_timeout_ns", C.c_uint64),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("flag2", C.c_void_p), ("flag2_value", C.c_uint64),
     ]
 
 

@@ -52,12 +52,31 @@ def test_cuda_tensor_echo_same_process(cuda_device):
             made.append(t)
             return t
 
-        for n in (64, 4096, 1 << 20, (1 << 24) + 3):
+        for n in (64, 4096, 1 << 19, (1 << 24) + 3):
             x = torch.rand(n, device="cuda:0")
             y = await client.invoke(x, worker_name="gpu_server", session_id=1, function="plus_one", memory_policy=client_policy)
             assert y.is_cuda and y.shape == x.shape
-            assert y is made[-1], "device results land in the tensor the policy returned"
+            if n * 4 > 64 << 10:
+                assert y is made[-1], "large device results land in the tensor the policy returned"
+            else:
+                assert not made, "small device results arrive eagerly in the receive ring; the policy is not asked"
             torch.testing.assert_close(y, x + 1.0, rtol=0, atol=0)
+            del y
+        cs, ss = client.transport_stats(), server.transport_stats()
+        # 256 B and 16 KiB went out as eager device messages in both directions (no rendezvous), 2 MiB was
+        # pulled by the receiver's kernel, 64 MiB pushed by the sender's; nothing went through host memory
+        assert cs["device_eager_sent"] == 2 and ss["device_eager_recv"] == 2, (cs, ss)
+        assert ss["device_eager_sent"] == 2 and cs["device_eager_recv"] == 2, (cs, ss)
+        assert cs["device_pushes"] == 1 and ss["device_push_recv"] == 1 and ss["device_pushes"] == 1 and cs["device_push_recv"] == 1, (cs, ss)
+        assert ss["device_pulls"] == 1 and cs["device_pulls"] == 1, (cs, ss)
+        assert cs["device_staged"] == 0 and ss["device_staged"] == 0, (cs, ss)
+        # more eager messages than the ring has slots, all in flight at once: the surplus takes the rendezvous
+        xs = [torch.full((256,), float(i), device="cuda:0") for i in range(80)]
+        ys = await asyncio.gather(*[client.invoke(x, worker_name="gpu_server", session_id=2, function="plus_one", memory_policy=client_policy)
+                                    for x in xs])
+        for i, y in enumerate(ys):
+            assert float(y[0]) == i + 1.0 and float(y[-1]) == i + 1.0
+        del ys
         # 2-D, non-contiguous input is packed before it is sent
         x2 = torch.rand(300, 70, device="cuda:0").t()
         y2 = await client.invoke(x2, worker_name="gpu_server", session_id=1, function="plus_one", memory_policy=client_policy)
@@ -80,7 +99,8 @@ def test_cuda_tensor_echo_same_process(cuda_device):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_processes_two_gpus():
-    """Server on GPU 1 in a child process, client on GPU 0 here: the payload crosses NVLink by the pull kernel."""
+    """Server on GPU 1 in a child process, client on GPU 0 here: the payloads cross NVLink by the transfer
+    kernels (eager into the ring, pulled, pushed), signalled through the shared flag page."""
     env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
     child = subprocess.Popen([sys.executable, "-m", "execution_ucx_b200.models.echo_server", "--device", "1", "--name", "peer"],
                              stdout=subprocess.PIPE, stdin=subprocess.PIPE, env=env, cwd=str(ROOT))
@@ -95,10 +115,15 @@ def test_two_processes_two_gpus():
             client.start_client()
             await client.connect_endpoint_async(address, "peer")
             policy = lambda metas: torch.empty(metas[0].shape, dtype=torch.bfloat16, device="cuda:0")  # noqa: E731
-            for n in (1024, 1 << 22):
+            for n in (1024, 1 << 20, 1 << 24):      # 2 KiB: eager into the peer's ring; 2 MiB: pulled; 32 MiB: pushed
                 x = torch.randn(n, device="cuda:0").to(torch.bfloat16)
                 y = await client.invoke(x, worker_name="peer", session_id=1, function="echo", memory_policy=policy)
                 assert y.device.index == 0 and torch.equal(y.view(torch.int16), x.view(torch.int16))
+                del y
+            st = client.transport_stats()
+            assert st["device_eager_sent"] == 1 and st["device_eager_recv"] == 1, st
+            assert st["device_pulls"] == 1 and st["device_pushes"] == 1 and st["device_push_recv"] == 1, st
+            assert st["device_staged"] == 0, st
             client.stop()
 
         run(main())
