@@ -6,10 +6,11 @@ other named workloads (latency sweep, remote-GEMM RPC, MoE dispatch+combine).
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
 
-One step = one echo round trip of a 1 GiB bf16 tensor on every rank (rank r
-with rank r^1; a single rank loops back through the same kernels on its own
-GPU). The timed region is bracketed by barrier + synchronize, timed with CUDA
-events on the launching stream, max over ranks. Rank 0 prints one JSON line.
+One step = one echo RPC of a 1 GiB bf16 tensor through `AxonRuntime.invoke` on
+every rank (rank r calls rank r^1's runtime; a single rank runs a server and a
+client runtime on its own GPU). The timed region is bracketed by barrier +
+synchronize, timed with CUDA events on the calling stream, max over ranks.
+Rank 0 prints one JSON line.
 """
 from __future__ import annotations
 
@@ -83,55 +84,53 @@ def main() -> int:
         group.barrier()
         torch.cuda.synchronize()
 
-    # ---------------- headline: tensor RPC echo of `nbytes` ----------------
-    rpc = TensorRpcEcho(group, nbytes)
-    src = torch.randn(nbytes // 2, device=dev).to(torch.bfloat16)       # N(0,1) bf16, larger than L2
-    for _ in range(warmup):
-        rpc.step(src)
-    # the sampler starts (and loads NVML) before the barrier, so that no rank enters the timed region late
-    sampler = timing.ClockSampler(local_rank).start() if rank == 0 else None
-    sync_all()
-    if sampler:
-        sampler.mark()
-    l0 = launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        rpc.step(src)
-    e1.record()
-    sync_all()
-    gpu_launches = launches() - l0
-    clocks = sampler.stop() if sampler else None
-    ms_total = group.max_over_ranks(e0.elapsed_time(e1))
-    rpc.check_status()
-    ms_per_step = ms_total / steps
-    one_way_gbs_per_rank = nbytes / (ms_per_step / 2 * 1e-3) / 1e9
-    value = one_way_gbs_per_rank * world
-    resp = rpc.response_view(nbytes)
-    echo_ok = bool(torch.equal(resp[:4096].view(torch.int16), src[:4096].view(torch.int16))) if world == 1 else True
-
-    # ---------------- end to end through the public API: AxonRuntime.invoke ----------------
-    # Every step: pinned host -> device copy of the request tensor, one RPC (`echo`) to the partner's
-    # runtime with the device tensor as payload, and a device -> host read of the head of the reply.
     import asyncio
-    host_in = torch.empty(nbytes // 2, dtype=torch.bfloat16).pin_memory()
-    host_in.copy_(src[: nbytes // 2].cpu())
-    host_out = torch.empty(2048, dtype=torch.bfloat16).pin_memory()
-    dev_in = torch.empty_like(src)
-    e2e_steps = max(3, min(steps, 10))
-    e2e = {}
 
-    async def e2e_main():
+    src = torch.randn(nbytes // 2, device=dev).to(torch.bfloat16)       # N(0,1) bf16, larger than L2
+    host_in = torch.empty(nbytes // 2, dtype=torch.bfloat16).pin_memory()
+    host_in.copy_(src.cpu())
+    host_out = torch.empty(nbytes // 2, dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.empty_like(src)
+    res = {}
+
+    # ---------------- headline: the echo RPC through the public API ----------------
+    # One step = `await AxonRuntime.invoke(tensor, function="echo")` on every rank at once, each to its
+    # partner's runtime (a Python handler registered with `register_function`), device tensors both ways.
+    # The bytes move by the runtime's transfer kernels (pushed by the sender's kernel into the buffer the
+    # receiver's memory policy returned; completion through a flag the receiver's worker thread polls).
+    async def api_main():
         api = AxonTensorRpc(group)
         await api.start()
+        for _ in range(warmup):
+            y = await api.step(src)
+        torch.cuda.synchronize()
+        await api.barrier()
+        if sampler:
+            sampler.mark()
+        l0 = api.kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            y = await api.step(src)       # resolves when the reply has landed in this rank's buffer
+        e1.record()
+        torch.cuda.synchronize()
+        res["host_ms"] = (time.perf_counter() - t0) * 1e3
+        res["event_ms"] = e0.elapsed_time(e1)
+        res["launches"] = api.kernel_launches() - l0
+        await api.barrier()
+        res["echo_ok"] = bool(torch.equal(y.view(torch.int16), src.view(torch.int16)))      # every byte of the last reply
+        res["stats"] = api.transport_stats()
 
+        # ---- end to end: pinned host -> device, the RPC, the whole reply device -> pinned host, every step ----
         async def e2e_step():
             dev_in.copy_(host_in, non_blocking=True)
             r = await api.step(dev_in)
-            host_out.copy_(r[:2048], non_blocking=True)
+            host_out.copy_(r, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             return float(host_out[0])
 
+        e2e_steps = max(3, min(steps, 10))
         for _ in range(3):
             await e2e_step()
         torch.cuda.synchronize()
@@ -140,48 +139,67 @@ def main() -> int:
         for _ in range(e2e_steps):
             await e2e_step()
         torch.cuda.synchronize()
-        dt_ms = (time.perf_counter() - t0) * 1e3
+        res["e2e_ms"] = (time.perf_counter() - t0) * 1e3 / e2e_steps
         await api.barrier()
-        ok = bool(torch.equal(host_out.view(torch.int16), host_in[:2048].view(torch.int16)))
-        # the same call without the host copies: what the RPC layer itself costs per size
+        res["e2e_ok"] = bool(torch.equal(host_out.view(torch.int16), host_in.view(torch.int16)))
+        # ---- the same call at every size (no host copies): latency and bandwidth of the RPC layer ----
         rows = []
-        for lg in (12, 16, 20, 24, 27, 30):
-            n = min(1 << lg, nbytes)
-            x = dev_in[: n // 2]
-            for _ in range(3):
-                await api.step(x)
-            await api.barrier()
-            ts = []
-            for _ in range(20 if lg <= 24 else 5):
-                torch.cuda.synchronize()
-                t = time.perf_counter()
-                y = await api.step(x)
-                torch.cuda.synchronize()
-                ts.append((time.perf_counter() - t) * 1e6)
-            await api.barrier()
-            ts.sort()
-            p50 = ts[len(ts) // 2]
-            rows.append({"bytes": n, "rtt_p50_us": round(p50, 1), "one_way_GBps": round(n / (p50 / 2 * 1e-6) / 1e9, 2)})
+        if not args.no_extras:
+            for lg in range(12, 31):
+                n = min(1 << lg, nbytes)
+                x = src[: n // 2]
+                iters = 100 if lg <= 20 else (20 if lg <= 26 else 5)
+                for _ in range(3):
+                    await api.step(x)
+                await api.barrier()
+                ts = []
+                for _ in range(iters):
+                    t = time.perf_counter()
+                    y = await api.step(x)
+                    ts.append((time.perf_counter() - t) * 1e6)
+                del y
+                await api.barrier()
+                ts.sort()
+                p50 = group.max_over_ranks(ts[len(ts) // 2])
+                p99 = group.max_over_ranks(ts[min(len(ts) - 1, int(len(ts) * 0.99))])
+                rows.append({"bytes": n, "rtt_p50_us": round(p50, 1), "rtt_p99_us": round(p99, 1),
+                             "one_way_GBps": round(n / (p50 / 2 * 1e-6) / 1e9, 2)})
+                if n == nbytes:
+                    break
+        res["api_rows"] = rows
         api.stop()
-        return dt_ms, ok, rows
 
-    try:
-        dt_ms, e2e_ok, api_rows = asyncio.run(e2e_main())
-        e2e_ms = group.max_over_ranks(dt_ms) / e2e_steps
-        e2e_value = nbytes / (e2e_ms / 2 * 1e-3) / 1e9 * world
-        e2e = {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
-               "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
-               "api": "execution_ucx_b200.axon.AxonRuntime.invoke('echo') with a device tensor",
-               "echo_verified": e2e_ok, "timing": "host clock around the steps, max over ranks",
-               "invoke_only_sweep": api_rows}
-    except Exception as e:  # the headline stays valid without it; the failure is reported, not hidden
-        e2e = {"error": f"{type(e).__name__}: {e}", "trace": traceback.format_exc(limit=4)}
-    del host_in, dev_in
-    extra = {}
+    # the sampler starts (and loads NVML) before the barrier, so that no rank enters the timed region late
+    sampler = timing.ClockSampler(local_rank).start() if rank == 0 else None
+    asyncio.run(api_main())
+    clocks = sampler.stop() if sampler else None
+    gpu_launches = res["launches"]
+    # CUDA events on the calling stream bracket the steps (the kernels themselves run on the runtimes' streams,
+    # in this process and in the partner's); the host clock around the same region is reported beside them
+    ms_total = group.max_over_ranks(res["event_ms"])
+    ms_per_step = ms_total / steps
+    one_way_gbs_per_rank = nbytes / (ms_per_step / 2 * 1e-3) / 1e9
+    value = one_way_gbs_per_rank * world
+    echo_ok = bool(group.max_over_ranks(0.0 if res["echo_ok"] else 1.0) == 0.0)
+    e2e_ms = group.max_over_ranks(res["e2e_ms"])
+    e2e = {"value": round(nbytes / (e2e_ms / 2 * 1e-3) / 1e9 * world, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
+           "api": "execution_ucx_b200.axon.AxonRuntime.invoke('echo'): request copied from pinned host memory, whole reply copied back",
+           "echo_verified": bool(group.max_over_ranks(0.0 if res["e2e_ok"] else 1.0) == 0.0),
+           "timing": "host clock around the steps, max over ranks"}
+    del host_in, host_out, dev_in
+
+    extra = {"api_sweep": {"what": "AxonRuntime.invoke('echo') of a device tensor, every rank to its partner at once; host clock per call, max over ranks",
+                           "rows": res["api_rows"]},
+             "headline_host_clock_ms_per_step": round(group.max_over_ranks(res["host_ms"]) / steps, 5),
+             "transport_counters_rank0": res["stats"]}
     if not args.no_extras:
-        extra = side_measurements(group, dev, rank, world, peaks, rpc, src)
-    rpc.close()
-    del rpc, src
+        # the data plane alone (no header, no dispatcher, no runtime): what the kernels do when nothing else is in the way
+        rpc = TensorRpcEcho(group, nbytes)
+        extra.update(side_measurements(group, dev, rank, world, peaks, rpc, src))
+        rpc.close()
+        del rpc
+    del src
 
     if rank == 0:
         out = {
@@ -191,7 +209,8 @@ def main() -> int:
             "data": "synthetic N(0,1) bf16, random-init weights",
             "config": {"model": "axon tensor-RPC echo ping-pong (BASELINE config 2)", "message_bytes": nbytes,
                        "global_batch": world, "seq_len": nbytes // 2, "parallelism": f"p2p-pairs{world}",
-                       "pairing": "rank r <-> r^1; n_gpus=1 is a same-GPU loopback through the same kernels",
+                       "path": "AxonRuntime.invoke -> RPC header -> active message -> transfer kernel -> Python handler -> and back",
+                       "pairing": "rank r <-> r^1; n_gpus=1 is two runtimes on one GPU (a loopback through the same code)",
                        "scaling_note": "n_gpus=1 moves the bytes inside one GPU's HBM, n_gpus>=2 across NVLink (770 GB/s "
                                        "measured per direction and GPU): the 1-GPU value is not the base of the multi-GPU ones",
                        "l2": "inputs (1 GiB) larger than L2; no flush needed"},
@@ -244,8 +263,10 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
         and divides: the ranks' launch skew (tens of microseconds after a host barrier) would otherwise
         be most of a small message's figure. L2 is flushed between samples."""
         rows = []
-        for lg in (12, 16, 20, 24, 28):
+        for lg in (12, 16, 20, 24, 28, 30):
             n = 1 << lg
+            if n > src.numel() * 2:
+                break
             s = src[: n // 2]
             inner = 32 if lg <= 20 else (8 if lg == 24 else 2)
 
@@ -258,7 +279,8 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
             p99 = group.max_over_ranks(timing.percentile(ts, 99)) * 1e3
             rows.append({"bytes": n, "steps_per_sample": inner, "rtt_p50_us": round(p50, 2), "rtt_p99_us": round(p99, 2),
                          "one_way_GBps": round(n / (p50 / 2 * 1e-6) / 1e9, 2)})
-        return {"timing": "CUDA events around a run of steps, one launch per step and rank (request push, handler + push "
+        return {"what": "the data plane alone: no header, no dispatcher, no runtime; buffers exchanged once at set-up",
+                "timing": "CUDA events around a run of steps, one launch per step and rank (request push, handler + push "
                           "back, completion wait as phases of one kernel), divided by the number of steps", "rows": rows}
 
     def gemm(fp8):
@@ -346,6 +368,35 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
         out["remote_gemm_bf16"] = {"what": "NCCL recv X + cuBLAS + NCCL send Y" if world > 1 else "cuBLAS (torch.matmul)",
                                    "ms_p50": round(ms, 4), "tflops_per_gpu": round(2.0 * m * nn * k / (ms * 1e-3) / 1e12, 1)}
         del gm
+        try:
+            sm = bl.ScaledMmBaseline(m, nn, k, dev)
+            ts = timing.time_cuda(sm.step, iters=10, warmup=3, flush=flush)
+            ms = group.max_over_ranks(timing.percentile(ts, 50))
+            out["gemm_fp8_scaled_mm"] = {"what": "torch._scaled_mm (cuBLASLt), e4m3 x e4m3, per-tensor scales, local operands",
+                                         "ms_p50": round(ms, 4), "tflops_per_gpu": round(2.0 * m * nn * k / (ms * 1e-3) / 1e12, 1)}
+            del sm
+        except Exception as e:
+            out["gemm_fp8_scaled_mm"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        # ping-pong at every size: NCCL send/recv there and back, and the copy engine (cudaMemcpyPeerAsync, one way, doubled)
+        pp = bl.PingPongSweep(group, src.numel() * 2)
+        rows = []
+        for lg in range(12, 31):
+            nb = 1 << lg
+            if nb > src.numel() * 2:
+                break
+            sv = src[: nb // 2]
+            iters = 30 if lg <= 24 else 8
+            tn = timing.time_cuda(lambda: pp.nccl_round_trip(sv), iters=iters, warmup=3, before=group.barrier if world > 1 else None)
+            tc = timing.time_cuda(lambda: pp.copy_engine_one_way(sv), iters=iters, warmup=3, before=group.barrier if world > 1 else None)
+            n50 = group.max_over_ranks(timing.percentile(tn, 50)) * 1e3
+            n99 = group.max_over_ranks(timing.percentile(tn, 99)) * 1e3
+            c50 = group.max_over_ranks(timing.percentile(tc, 50)) * 1e3 * 2
+            rows.append({"bytes": nb, "nccl_rtt_p50_us": round(n50, 1), "nccl_rtt_p99_us": round(n99, 1),
+                         "nccl_one_way_GBps": round(nb / (n50 / 2 * 1e-6) / 1e9, 2),
+                         "copy_engine_2x_one_way_us": round(c50, 1), "copy_engine_GBps": round(nb / (c50 / 2 * 1e-6) / 1e9, 2)})
+        pp.close()
+        out["pingpong_sweep"] = {"timing": "CUDA events around one call, launch included, max over ranks; both ranks of a pair at once",
+                                 "rows": rows}
         w = MoeDispatchCombine(group, fp8=False)
         mo = bl.AllToAllMoe(rank, world, w.x, w.idx, w.w, w.a2a.n_experts)
         ts = timing.time_cuda(mo.step, iters=10, warmup=3, flush=flush, before=group.barrier if world > 1 else None)

@@ -113,6 +113,7 @@ ucxx::transport::Worker::Stats AxonWorker::GetTransportStats() const {
     t.device_eager_recv += s.device_eager_recv;
     t.device_pushes += s.device_pushes;
     t.device_push_recv += s.device_push_recv;
+    t.kernel_launches += s.kernel_launches;
   }
   return t;
 }

@@ -41,8 +41,10 @@ std::chrono::milliseconds parse_timeout(py::handle t) {
   throw py::type_error("timeout must be int (ms), float (s), datetime.timedelta or None");
 }
 
-// payload argument of invoke_raw / result of a Python handler -> PayloadVariant
-PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj) {
+// payload argument of invoke_raw / result of a Python handler -> PayloadVariant. With `metas`, the
+// metadata of every tensor that is imported is appended there (one __dlpack__ call per tensor serves
+// both the bytes and the description).
+PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj, rpc::TensorMetaVec* metas = nullptr) {
   if (obj.is_none()) return {};
   if (py::isinstance<PyBuffer>(obj)) {
     auto& b = obj.cast<PyBuffer&>();
@@ -58,10 +60,25 @@ PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handl
   }
   if (py::isinstance<py::list>(obj) || py::isinstance<py::tuple>(obj)) {
     std::vector<ImportedTensor> ts;
-    for (auto item : obj) ts.push_back(import_tensor(item));
+    for (auto item : obj) {
+      ts.push_back(import_tensor(item));
+      if (metas) metas->push_back(ts.back().meta);
+    }
     return to_ucx_buffer_vec(mr, std::move(ts));
   }
-  return to_ucx_buffer(mr, import_tensor(obj));
+  ImportedTensor t = import_tensor(obj);
+  if (metas) metas->push_back(t.meta);
+  return to_ucx_buffer(mr, std::move(t));
+}
+
+// The tensor description(s) go last in the parameter list, where the receiver looks first:
+// 1: one TENSOR_META, 2: one TENSOR_META_VEC.
+void append_tensor_metas(rpc::data::vector<rpc::ParamMeta>& params, rpc::TensorMetaVec&& metas, int add_meta) {
+  if (add_meta == 1 && metas.size() == 1) {
+    params.push_back(rpc::ParamMeta(rpc::ParamType::TENSOR_META, rpc::ParamValue(std::in_place_type<rpc::TensorMeta>, std::move(metas[0]))));
+  } else if (add_meta != 0) {
+    params.push_back(rpc::ParamMeta(rpc::ParamType::TENSOR_META_VEC, rpc::ParamValue(std::in_place_type<rpc::TensorMetaVec>, std::move(metas))));
+  }
 }
 
 // Buffers handed to Python may outlive the runtime that received them (a result tensor kept
@@ -205,6 +222,7 @@ class PyAxonRuntime {
     d["device_eager_recv"] = s.device_eager_recv;
     d["device_pushes"] = s.device_pushes;
     d["device_push_recv"] = s.device_push_recv;
+    d["kernel_launches"] = s.kernel_launches;
     return d;
   }
   size_t stored_request_count() { return rt_->worker().GetStorage().size(); }
@@ -274,6 +292,10 @@ class PyAxonRuntime {
     ServerMemoryPolicy p;
     if (policy.is_none()) return p;
     p.on_host = false;
+    // Called on the context's own thread (with the GIL taken there) instead of on a pool thread: waking a
+    // pool thread and bouncing back costs about 100 us per message, the call itself a few. The loop
+    // thread holds the GIL only while Python code runs, and while it does no handler could run either.
+    p.provider_inline = true;
     auto fn = gil_shared(policy);
     auto* mr = mr_.get();
     // The policy runs on a pool thread whose current CUDA device is the default one; tensor
@@ -324,9 +346,12 @@ class PyAxonRuntime {
   // ---- invoke ----
   // `transform(response_header, payload)`, when given, runs on the loop thread and its result (or
   // the exception it raises) settles the future: one loop iteration instead of a chained future.
+  // `add_meta` (1: TENSOR_META, 2: TENSOR_META_VEC): describe the payload tensors in the header here.
   py::object invoke_raw(const std::string& worker_name, rpc::RpcRequestHeader header, py::object payload, py::object memory_policy,
-                        bool response_as_list, py::object transform) {
-    PayloadVariant p = payload_from_python(*mr_, payload);
+                        bool response_as_list, py::object transform, int add_meta) {
+    rpc::TensorMetaVec metas;
+    PayloadVariant p = payload_from_python(*mr_, payload, add_meta ? &metas : nullptr);
+    if (add_meta) append_tensor_metas(header.params, std::move(metas), add_meta);
     ClientMemoryPolicy pol = client_policy(memory_policy, response_as_list);
     if (response_as_list && !memory_policy.is_none()) pol.buffer_provider = nullptr;
     const int dev = device_id_;
@@ -399,9 +424,12 @@ class PyAxonRuntime {
                 }
                 py::object res = t.attr("result")();
                 py::object head = res, pay = py::none();
-                if (py::isinstance<py::tuple>(res) && py::len(res) == 2) {
-                  head = res.cast<py::tuple>()[0];
-                  pay = res.cast<py::tuple>()[1];
+                int add_meta = 0;  // third element: describe the payload tensors in the header here (see invoke_raw)
+                if (py::isinstance<py::tuple>(res) && py::len(res) >= 2) {
+                  auto tup = res.cast<py::tuple>();
+                  head = tup[0];
+                  pay = tup[1];
+                  if (py::len(res) >= 3) add_meta = tup[2].cast<int>();
                 }
                 rpc::RpcResponseHeader h;
                 if (py::isinstance<rpc::RpcResponseHeader>(head)) {
@@ -413,7 +441,9 @@ class PyAxonRuntime {
                 }
                 h.session_id = st->req.session_id;
                 h.request_id = st->req.request_id;
-                PayloadVariant out = payload_from_python(*self->mr_, pay);
+                rpc::TensorMetaVec metas;
+                PayloadVariant out = payload_from_python(*self->mr_, pay, add_meta ? &metas : nullptr);
+                if (add_meta) append_tensor_metas(h.results, std::move(metas), add_meta);
                 if (settled->exchange(true)) return;
                 py::gil_scoped_release nogil;
                 handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{std::move(h), std::move(out)});
@@ -523,7 +553,8 @@ void bind_runtime(py::module_& m) {
            py::arg("return_types"), py::arg("input_payload_type"), py::arg("return_payload_type"), py::arg("callable"),
            py::arg("memory_policy") = py::none(), py::arg("lifecycle_policy") = py::none())
       .def("_invoke_native", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
-           py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none())
+           py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none(),
+           py::arg("add_meta") = 0)
       .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
       .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)
       .def("transport_stats", &PyAxonRuntime::transport_stats,

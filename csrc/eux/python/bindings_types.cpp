@@ -300,6 +300,13 @@ void bind_types(py::module_& m) {
       .def_property_readonly("memory_type", [](const PyBuffer& b) { return b.buf ? b.buf->type() : ucx_memory_type::UNKNOWN; })
       .def_property_readonly("data_ptr", [](const PyBuffer& b) { return b.buf ? reinterpret_cast<uintptr_t>(b.buf->data()) : 0; })
       .def("to_dlpack", &PyBuffer::to_capsule_wrapper, py::arg("meta"), "A single-use DLPack holder that views this buffer as the tensor `meta` describes.")
+      .def("to_capsule", [](const PyBuffer& b, const TensorMeta& meta) {
+        if (!b.buf) throw py::value_error("empty buffer");
+        if (rpc::utils::CalculateTensorSize(meta) > b.buf->size()) throw py::value_error("the metadata describes more bytes than the buffer holds");
+        TensorMeta m = meta;
+        m.device = device_of(b.buf->type(), b.device_id);
+        return make_capsule(b.buf, b.buf->data(), m);
+      }, py::arg("meta"), "The bare 'dltensor' capsule of the same view, for consumers that take capsules (torch.from_dlpack does, and skips its stream handling then).")
       .def("__dlpack__", [](const PyBuffer& b, py::args, py::kwargs) {
         auto m = b.bytes_meta();
         return make_capsule(b.buf, b.buf->data(), m);
@@ -324,6 +331,13 @@ void bind_types(py::module_& m) {
         TensorMeta m = meta;
         m.device = device_of(v.vec->type(), v.device_id);
         return DLPackCapsuleWrapper(make_capsule(v.vec, (*v.vec)[i].data, m), m.device);
+      })
+      .def("to_capsule", [](const PyBufferVec& v, size_t i, const TensorMeta& meta) {
+        if (!v.vec || i >= v.vec->size()) throw py::index_error("segment index out of range");
+        if (rpc::utils::CalculateTensorSize(meta) > (*v.vec)[i].size) throw py::value_error("the metadata describes more bytes than the segment holds");
+        TensorMeta m = meta;
+        m.device = device_of(v.vec->type(), v.device_id);
+        return make_capsule(v.vec, (*v.vec)[i].data, m);
       })
       .def("owner", [](const PyBufferVec& v, size_t i) {
         if (!v.vec || i >= v.vec->size()) throw py::index_error("segment index out of range");

@@ -35,6 +35,26 @@ bool address_range(const void* ptr, void** base, size_t* size) {
   return true;
 }
 
+// CU_POINTER_ATTRIBUTE_BUFFER_ID: a number the driver gives every allocation and never reuses, so a
+// remembered allocation can be told from a new one at the same address in about a microsecond
+// (asking for the IPC handle again, the other way to tell, costs tens of microseconds per message).
+bool buffer_id_of(const void* ptr, uint64_t* id) {
+  using Fn = int (*)(void*, int, unsigned long long);
+  static Fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<Fn>(p);
+  }();
+  if (!fn) return false;
+  unsigned long long v = 0;
+  constexpr int kBufferId = 9;  // CU_POINTER_ATTRIBUTE_BUFFER_ID
+  if (fn(&v, kBufferId, reinterpret_cast<unsigned long long>(ptr)) != 0) return false;
+  *id = v;
+  return true;
+}
+
 // Allocation and release run on whatever thread asks (a pool thread, the caller's thread): the
 // manager's device becomes current for the duration, whatever that thread had before.
 struct DeviceGuard {
@@ -254,6 +274,8 @@ const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::
     // Memory of somebody else's allocator (a tensor library's cache, say) can be freed and handed
     // out again at the same address: the remembered range and handle are checked against the
     // allocation that is there now.
+    uint64_t id = 0;
+    if (r->buffer_id && buffer_id_of(ptr, &id) && id == r->buffer_id) return r;  // the very allocation that was registered
     void* base = nullptr;
     size_t size = 0;
     if (address_range(ptr, &base, &size) && base == r->base && size == r->size) {
@@ -275,6 +297,7 @@ const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::
   reg.size = size;
   cudaPointerAttributes attr{};
   reg.device = cudaPointerGetAttributes(&attr, ptr) == cudaSuccess ? attr.device : opt_.device;
+  if (!buffer_id_of(base, &reg.buffer_id)) reg.buffer_id = 0;
   cudaIpcMemHandle_t h;
   if (cudaIpcGetMemHandle(&h, base) == cudaSuccess) {
     static_assert(sizeof(h) == 64);

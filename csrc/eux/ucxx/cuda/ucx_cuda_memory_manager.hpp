@@ -54,6 +54,7 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
     int device = -1;
     bool exportable = false;
     unsigned char handle[64] = {0};
+    uint64_t buffer_id = 0;  // the driver's id of the allocation (0: unknown), to recognise it again cheaply
   };
 
   UcxCudaMemoryResourceManager();

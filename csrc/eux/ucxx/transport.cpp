@@ -927,6 +927,7 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
       break;
     }
     case kAmRts: {
+      nvtx_mark("eux.transport.rts_received");
       Endpoint::RtsInfo info;
       info.payload_len = fh.payload_len;
       info.mem_type = static_cast<ucx_memory_type_t>(fh.mem_type);
@@ -1082,6 +1083,7 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   size_t total = 0;
   for (size_t i = 0; i < seg_count; ++i) total += segs[i].size;
   const bool device = is_device_type(mem_type);
+  if (device) nvtx_mark("eux.transport.am_send_device");
   const bool rndv = total > 0 && (force_rndv || device || seg_count > 1 || total >= opt_.eager_limit);
   const uint64_t id = ep->next_msg_id_++;
   if (msg_id_out) *msg_id_out = id;
@@ -1398,6 +1400,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
       UCX_CONN_ERROR << "transfer kernel launch failed: " << eux_error_string(rc);
       return UCS_ERR_IO_ERROR;
     }
+    ++stats_.kernel_launches;
   }
   device_ops_.push_back({seq, ep, msg_id, std::move(done)});
   return UCS_INPROGRESS;
@@ -1409,6 +1412,7 @@ void Worker::flush_pull_batch() {
   if (pull_batch_.empty()) return;
   NvtxRange range("eux.transport.device_pull_batch");
   const int rc = eux_xfer_pull_batch_launch(pull_batch_.data(), static_cast<int>(pull_batch_.size()), stream_);
+  if (rc == 0) ++stats_.kernel_launches;
   if (rc != 0) {
     UCX_CONN_ERROR << "batched transfer kernel launch failed: " << eux_error_string(rc);
     const uint64_t first = pull_batch_.front().flag_value, last = pull_batch_.back().flag_value;
@@ -1454,6 +1458,7 @@ void Worker::poll_device() {
         EagerWait w = std::move(*it);
         it = eager_waits_.erase(it);
         ++stats_.device_eager_recv;
+        nvtx_mark("eux.transport.device_eager_arrived");
         if (on_am && w.ep) on_am(std::move(w.arrival));
         else if (w.arrival.header) mr_.deallocate(ucx_memory_type::HOST, w.arrival.header, w.arrival.header_len);
         continue;  // the slot goes back when the arrival's keep-alive token is dropped
@@ -1479,6 +1484,7 @@ void Worker::poll_device() {
       PushWait w = std::move(*it);
       it = push_waits_.erase(it);
       if (w.ep && eps_.count(w.ep) && w.ep->push_inflight_) --w.ep->push_inflight_;
+      if (arrived) nvtx_mark("eux.transport.device_push_arrived");
       if (arrived) ++stats_.device_push_recv;
       else UCX_CONN_ERROR << opt_.name << ": a pushed payload (message " << w.msg_id << ") did not arrive in time";
       if (w.done) w.done(arrived ? UCS_OK : UCS_ERR_TIMED_OUT);
@@ -1737,6 +1743,7 @@ int Worker::request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info,
   w.info = std::move(info);
   push_waits_.push_back(std::move(w));
   enqueue(ep, std::move(it));
+  nvtx_mark("eux.transport.cts_push_sent");
   return UCS_INPROGRESS;
 }
 
@@ -1820,6 +1827,7 @@ int Worker::launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs
     }
     int rc = eux_xfer_launch(&d, counter_dev_, 0, stream_);
     if (rc != 0) return rc;
+    ++stats_.kernel_launches;
   }
   return 0;
 }

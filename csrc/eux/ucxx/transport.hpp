@@ -319,6 +319,7 @@ class Worker {
     uint64_t device_eager_recv = 0;  // ... and received through this worker's rings
     uint64_t device_pushes = 0;      // large device payloads pushed by this worker's kernel on a CTS(push)
     uint64_t device_push_recv = 0;   // ... and received that way
+    uint64_t kernel_launches = 0;    // launches of the transfer kernels by this worker
   };
   const Stats& stats() const { return stats_; }
 

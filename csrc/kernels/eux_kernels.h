@@ -147,6 +147,8 @@ EUX_API int eux_device_free(void* p);
 EUX_API int eux_host_alloc_mapped(void** host_ptr, void** dev_ptr, size_t bytes);
 EUX_API int eux_host_free(void* host_ptr);
 EUX_API const char* eux_error_string(int err);
+/* cudaMemcpyPeerAsync, for the copy-engine baseline of the benchmarks (not used by the data plane) */
+EUX_API int eux_memcpy_peer_async(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream);
 
 /* ---- MoE dispatch / combine (moe_dispatch.cu) ---- */
 typedef struct eux_moe_desc {

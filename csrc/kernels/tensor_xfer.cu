@@ -665,6 +665,9 @@ extern "C" int eux_ipc_open(const unsigned char handle[64], void** dev_ptr_out) 
   return (int)cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess);
 }
 extern "C" int eux_ipc_close(void* dev_ptr) { return (int)cudaIpcCloseMemHandle(dev_ptr); }
+extern "C" int eux_memcpy_peer_async(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream) {
+  return (int)cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, (cudaStream_t)stream);
+}
 extern "C" int eux_enable_peer_access(int this_dev, int peer_dev) {
   int can = 0;
   cudaError_t e = cudaDeviceCanAccessPeer(&can, this_dev, peer_dev);

@@ -97,6 +97,14 @@ def _default_from_dlpack(sample: Any = None) -> Callable:
     return numpy.from_dlpack
 
 
+def _takes_capsule(fn: Callable) -> bool:
+    """torch.from_dlpack accepts the bare capsule and then skips its device and stream queries: the bytes
+    are complete when the runtime hands them over, so nothing needs to be ordered."""
+    import sys
+    t = sys.modules.get("torch")
+    return t is not None and fn is t.from_dlpack
+
+
 # ---- nested lists and string lists travel as tagged blobs (STRING params) ----------------------
 def _encode_nested(lst: Sequence[Sequence], code: str) -> bytes:
     """[u32 groups][u32 size...][items...], items i64 / f64 / u8."""
@@ -237,10 +245,16 @@ class _TensorStream:
         p, m = self.payload, self.metas[i]
         if isinstance(p, UcxBufferVec):
             owner = p.owner(i)
-            return owner if owner is not None else (fn or _default_from_dlpack())(p.to_dlpack(i, m))
+            if owner is not None:
+                return owner
+            f = fn or _default_from_dlpack()
+            return f(p.to_capsule(i, m)) if _takes_capsule(f) else f(p.to_dlpack(i, m))
         if len(self.metas) == 1:
             owner = p.owner()
-            return owner if owner is not None else (fn or _default_from_dlpack())(p.to_dlpack(m))
+            if owner is not None:
+                return owner
+            f = fn or _default_from_dlpack()
+            return f(p.to_capsule(m)) if _takes_capsule(f) else f(p.to_dlpack(m))
         # several tensors received back to back in one host buffer
         f = fn or _default_from_dlpack()
         if self._whole is None:
@@ -490,23 +504,20 @@ def _params_to_args(sig: _Sig, header, payload) -> list:
     return args
 
 
-def _tensor_payload(tensors: list, as_vec: bool, add_typed: Callable):
-    """Metadata param (always last) + payload object for the tensors of a message."""
-    if not tensors and not as_vec:
-        return None
-    tensors = [_contiguous(t) for t in tensors]
-    metas = [TensorMeta.from_tensor(t) for t in tensors]
-    if len(tensors) == 1 and not as_vec:
-        add_typed(ParamType.TENSOR_META, metas[0], "")
-        return tensors[0]
+def _tensor_payload(tensors: list, as_vec: bool):
+    """(payload object, add_meta) for the tensors of a message. The native layer describes the tensors in
+    the header itself (1: one TENSOR_META, 2: one TENSOR_META_VEC; always the last param), from the same
+    DLPack export it takes the bytes from."""
     if not tensors:
-        return None
-    add_typed(ParamType.TENSOR_META_VEC, metas, "")
-    return tensors
+        return None, 0
+    tensors = [_contiguous(t) for t in tensors]
+    if len(tensors) == 1 and not as_vec:
+        return tensors[0], 1
+    return tensors, 2
 
 
 def _pack_results(sig: _Sig, result):
-    """Handler return value -> (RpcResponseHeader with the result params, payload)."""
+    """Handler return value -> (RpcResponseHeader with the plain result params, payload, add_meta)."""
     header = RpcResponseHeader()
 
     def add_typed(ptype, v, name):
@@ -516,16 +527,16 @@ def _pack_results(sig: _Sig, result):
         header.AddResult(v)
 
     if sig.mode == "void" and not (sig.return_types and sig.return_types[0] == ParamType.UNKNOWN):
-        return header, None
+        return header, None, 0
     if any(t == ParamType.UNKNOWN for t in sig.return_types) or not sig.return_types:
         return _pack_inferred(result, header, add_typed, add_plain)
     if sig.mode == "single":
         _add_declared(add_typed, add_plain, sig.return_types[0], result)
-        return header, None
+        return header, None, 0
     if sig.mode == "tensor":
-        return header, _tensor_payload([result], False, add_typed)
+        return (header, *_tensor_payload([result], False))
     if sig.mode == "tensor_list":
-        return header, _tensor_payload(list(result), True, add_typed)
+        return (header, *_tensor_payload(list(result), True))
     items = tuple(result) if isinstance(result, (tuple, list)) else (result,)
     for ptype, i in zip(sig.non_tensor_types, sig.non_tensor_indices):
         _add_declared(add_typed, add_plain, ptype, items[i])
@@ -536,13 +547,13 @@ def _pack_results(sig: _Sig, result):
             as_vec = True
         else:
             tensors.append(items[i])
-    return header, (_tensor_payload(tensors, as_vec, add_typed) if sig.tensor_return_indices else None)
+    return (header, *_tensor_payload(tensors, as_vec))
 
 
 def _pack_inferred(result, header, add_typed, add_plain):
     """No usable return annotation: the wire form follows the value."""
     if result is None:
-        return header, None
+        return header, None, 0
     items = list(result) if isinstance(result, tuple) else [result]
     tensors, as_vec = [], False
     for it in items:
@@ -553,7 +564,7 @@ def _pack_inferred(result, header, add_typed, add_plain):
             as_vec = True
         else:
             _add_inferred(add_typed, add_plain, it)
-    return header, (_tensor_payload(tensors, as_vec or len(tensors) > 1, add_typed) if tensors else None)
+    return (header, *_tensor_payload(tensors, as_vec or len(tensors) > 1))
 
 
 # ---- client side --------------------------------------------------------------------------------
@@ -761,12 +772,11 @@ class AxonRuntime(_axon.AxonRuntime):
             else:
                 _add_inferred(add_typed, add_plain, a)
         sample = tensors[0] if tensors else None
-        # the tensor metadata goes last so the receiver finds it at once
-        payload = _tensor_payload(tensors, len(tensors) > 1, add_typed) if tensors else None
+        payload, add_meta = _tensor_payload(tensors, len(tensors) > 1)
         fn = from_dlpack_fn or (_default_from_dlpack(sample) if sample is not None else None)
         # the response is unpacked on the loop thread by the binding itself and settles the future
         return self._invoke_native(worker_name, header, payload, memory_policy, False,
-                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id))
+                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id), add_meta)
 
 
 

@@ -96,3 +96,63 @@ class AllToAllMoe:
         acc.index_add_(0, tok, back.float() * self.w.reshape(-1)[order].unsqueeze(1))
         self.out.copy_(acc)
         return self.out
+
+
+class PingPongSweep:
+    """Echo ping-pong at one size after another with library calls only.
+
+    ``nccl_round_trip``: NCCL send/recv there and back (both ranks of a pair at once, as in the product's
+    sweep). ``copy_engine_one_way``: ``cudaMemcpyPeerAsync`` of the same bytes into a buffer of the
+    partner (mapped through CUDA IPC), both ranks at once; a round trip by the copy engine is taken as
+    twice that, which leaves out whatever signalling a real protocol would need between the two legs.
+    """
+
+    def __init__(self, group, max_bytes: int):
+        self.g = group
+        self.rank, self.world, self.peer = group.rank, group.world, _partner(group.rank, group.world)
+        dev = group.device
+        self.a = torch.empty(max_bytes // 2, dtype=torch.bfloat16, device=dev)
+        self.b = torch.empty(max_bytes // 2, dtype=torch.bfloat16, device=dev)
+        self.inbox = group.alloc(max_bytes)      # the partner's copy of this buffer is the copy engine's target
+        self.max_bytes = max_bytes
+
+    def nccl_round_trip(self, src: torch.Tensor):
+        n = src.numel()
+        if self.world == 1:
+            self.a[:n].copy_(src)
+            self.b[:n].copy_(self.a[:n])
+            return
+        for work in dist.batch_isend_irecv([dist.P2POp(dist.isend, src, self.peer), dist.P2POp(dist.irecv, self.a[:n], self.peer)]):
+            work.wait()
+        for work in dist.batch_isend_irecv([dist.P2POp(dist.isend, self.a[:n], self.peer), dist.P2POp(dist.irecv, self.b[:n], self.peer)]):
+            work.wait()
+
+    def copy_engine_one_way(self, src: torch.Tensor):
+        """The driver's peer copy on the current stream; no kernel of any library touches the peer's memory."""
+        import ctypes as C
+
+        from ..ops import _native
+        lib = _native.load()
+        nbytes = src.numel() * src.element_size()
+        peer_dev = self.peer if self.world > 1 else self.g.device.index or 0   # one process per GPU, rank == device ordinal
+        _native.check(lib.eux_memcpy_peer_async(C.c_void_p(self.inbox.peer_ptrs[self.peer]), peer_dev, C.c_void_p(src.data_ptr()),
+                                                self.g.device.index or 0, nbytes, C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                      "cudaMemcpyPeerAsync")
+
+    def close(self):
+        self.g.free(self.inbox)
+
+
+class ScaledMmBaseline:
+    """fp8 GEMM the library way: ``torch._scaled_mm`` (cuBLASLt) on e4m3 operands with per-tensor scales:
+    the closest library call to the block-scaled remote GEMM. Absent kernels raise, and the caller reports that."""
+
+    def __init__(self, m: int, n: int, k: int, device):
+        g = torch.Generator(device=device).manual_seed(99)
+        self.x = torch.randn(m, k, device=device, generator=g).to(torch.float8_e4m3fn)
+        self.w = (torch.randn(n, k, device=device, generator=g) * 0.02).to(torch.float8_e4m3fn)
+        self.sx = torch.ones((), device=device)
+        self.sw = torch.ones((), device=device)
+
+    def step(self):
+        return torch._scaled_mm(self.x, self.w.t(), scale_a=self.sx, scale_b=self.sw, out_dtype=torch.bfloat16)

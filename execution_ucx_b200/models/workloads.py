@@ -372,6 +372,18 @@ class AxonTensorRpc:
         return await self.client.invoke(x, worker_name=self.partner_name, session_id=1, function="echo",
                                         memory_policy=self._policy(self._cli_bufs))
 
+    def transport_stats(self) -> dict:
+        """Counters of this rank's runtime(s), added up."""
+        out = dict(self.client.transport_stats())
+        if self.server is not self.client:
+            for k, v in self.server.transport_stats().items():
+                out[k] = out.get(k, 0) + v
+        return out
+
+    def kernel_launches(self) -> int:
+        """Transfer-kernel launches made so far by this rank's runtime(s)."""
+        return int(self.transport_stats()["kernel_launches"])
+
     def stop(self):
         if self.client is not None:
             self.client.stop()

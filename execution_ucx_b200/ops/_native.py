@@ -93,6 +93,7 @@ def load():
     lib.eux_xfer_batch_launch.argtypes = [P, I, P]
     lib.eux_xfer_pull_batch_launch.argtypes = [C.POINTER(PullItem), I, P]
     lib.eux_pingpong_launch.argtypes = [C.POINTER(PingPongDesc), I, P]
+    lib.eux_memcpy_peer_async.argtypes = [P, I, P, I, C.c_size_t, P]
     lib.eux_ipc_export.argtypes = [P, C.c_char_p]
     lib.eux_ipc_open.argtypes = [C.c_char_p, C.POINTER(P)]
     lib.eux_ipc_close.argtypes = [P]
