@@ -15,6 +15,8 @@
 #include "bindings_common.hpp"
 #include "eux/ucxx/cuda/ucx_cuda_context.hpp"
 #include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
+#include "eux/axon/services/peer_memory_service.hpp"
+#include "eux/axon/services/remote_gemm_service.hpp"
 
 namespace eux::python {
 
@@ -365,6 +367,54 @@ class PyAxonRuntime {
                        });
   }
 
+  // ---- remote GEMM service (see eux/axon/services/remote_gemm_service.hpp) ----
+  axon::services::RemoteGemmService& gemm_service() {
+    if (!gemm_) {
+      auto cuda_mr = std::dynamic_pointer_cast<ucxx::UcxCudaMemoryResourceManager>(mr_);
+      if (!cuda_mr) throw std::runtime_error("the remote GEMM service needs a runtime on a cuda device");
+      gemm_ = std::make_unique<axon::services::RemoteGemmService>(rt_->worker(), cuda_mr);
+    }
+    return *gemm_;
+  }
+  void gemm_add_weight(uint32_t weight_id, uintptr_t w_t, int n, int k, int format, int max_m, uintptr_t w_scale) {
+    axon::services::GemmWeight w;
+    w.w_t = reinterpret_cast<const void*>(w_t);
+    w.w_scale = reinterpret_cast<const void*>(w_scale);
+    w.n = n;
+    w.k = k;
+    w.format = static_cast<axon::services::GemmFormat>(format);
+    w.max_m = max_m;
+    auto& svc = gemm_service();
+    svc.AddWeight(weight_id, w);
+    if (!svc.Register()) throw std::runtime_error("the remote GEMM function could not be registered");
+  }
+  uint64_t gemm_launches() { return gemm_ ? gemm_->launches() : 0; }
+  py::object remote_gemm(const std::string& worker_name, uint32_t weight_id, int m, uintptr_t x, size_t x_bytes, uintptr_t y, size_t y_bytes,
+                         uintptr_t xs, size_t xs_bytes) {
+    return future_from(gemm_service().Call(worker_name, weight_id, m, reinterpret_cast<const void*>(x), x_bytes, reinterpret_cast<void*>(y),
+                                           y_bytes, reinterpret_cast<const void*>(xs), xs_bytes),
+                       [](int32_t status) -> py::object { return py::int_(status); });
+  }
+
+  // ---- symmetric peer memory (see eux/axon/services/peer_memory_service.hpp) ----
+  void peer_memory_init(int rank, int world) {
+    auto cuda_mr = std::dynamic_pointer_cast<ucxx::UcxCudaMemoryResourceManager>(mr_);
+    if (!cuda_mr) throw std::runtime_error("peer memory needs a runtime on a cuda device");
+    peer_mem_ = std::make_unique<axon::services::PeerMemoryService>(rt_->worker(), cuda_mr, rank, world);
+    if (!peer_mem_->Register()) throw std::runtime_error("the peer-memory function could not be registered");
+  }
+  axon::services::PeerMemoryService& peer_memory() {
+    if (!peer_mem_) throw std::runtime_error("call peer_memory_init(rank, world) first");
+    return *peer_mem_;
+  }
+  uintptr_t peer_memory_alloc(uint32_t tag, size_t nbytes) { return reinterpret_cast<uintptr_t>(peer_memory().Allocate(tag, nbytes)); }
+  py::object peer_memory_publish(const std::string& worker_name, uint32_t tag) {
+    return future_from(peer_memory().Publish(worker_name, tag), [](int32_t v) -> py::object { return py::int_(v); });
+  }
+  int peer_memory_arrived(uint32_t tag) { return peer_memory().Arrived(tag); }
+  std::vector<uintptr_t> peer_memory_resolve(uint32_t tag) { return peer_memory().Resolve(tag); }
+  void peer_memory_free(uint32_t tag) { peer_memory().Free(tag); }
+
   // ---- server-side functions ----
   // `callable(header: RpcRequestHeader, payload) -> awaitable of (RpcResponseHeader | list of results, payload | None)`.
   bool register_function_raw(uint32_t function_id, const std::string& function_name, std::vector<rpc::ParamType> param_types,
@@ -506,6 +556,8 @@ class PyAxonRuntime {
   ex::static_thread_pool helper_{1};
   ex::async_scope scope_;
   std::unique_ptr<axon::AxonRuntime> rt_;
+  std::unique_ptr<axon::services::PeerMemoryService> peer_mem_;
+  std::unique_ptr<axon::services::RemoteGemmService> gemm_;  // declared after rt_: destroyed before the worker it is registered on
 };
 
 py::object PyAxonRuntime::process_stored_requests() {
@@ -555,6 +607,17 @@ void bind_runtime(py::module_& m) {
       .def("_invoke_native", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
            py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none(),
            py::arg("add_meta") = 0)
+      .def("_gemm_add_weight", &PyAxonRuntime::gemm_add_weight, py::arg("weight_id"), py::arg("w_t"), py::arg("n"), py::arg("k"), py::arg("format"),
+           py::arg("max_m"), py::arg("w_scale") = 0)
+      .def("_remote_gemm", &PyAxonRuntime::remote_gemm, py::arg("worker_name"), py::arg("weight_id"), py::arg("m"), py::arg("x"), py::arg("x_bytes"),
+           py::arg("y"), py::arg("y_bytes"), py::arg("x_scale") = 0, py::arg("x_scale_bytes") = 0)
+      .def("peer_memory_init", &PyAxonRuntime::peer_memory_init, py::arg("rank"), py::arg("world"))
+      .def("peer_memory_alloc", &PyAxonRuntime::peer_memory_alloc, py::arg("tag"), py::arg("nbytes"))
+      .def("peer_memory_publish", &PyAxonRuntime::peer_memory_publish, py::arg("worker_name"), py::arg("tag"))
+      .def("peer_memory_arrived", &PyAxonRuntime::peer_memory_arrived, py::arg("tag"))
+      .def("peer_memory_resolve", &PyAxonRuntime::peer_memory_resolve, py::arg("tag"))
+      .def("peer_memory_free", &PyAxonRuntime::peer_memory_free, py::arg("tag"))
+      .def("gemm_launches", &PyAxonRuntime::gemm_launches, "GEMM kernels launched by this runtime's remote-GEMM handler so far.")
       .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
       .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)
       .def("transport_stats", &PyAxonRuntime::transport_stats,

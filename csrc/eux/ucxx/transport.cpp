@@ -624,6 +624,8 @@ std::shared_ptr<FaultHook> g_fault_hook;  // null when no test has installed one
 std::atomic<bool> g_fault_on{false};
 }  // namespace
 
+bool is_live_local_uid(uint64_t uid) { return live_has(uid); }
+
 void set_fault_hook(FaultHook hook) {
   std::lock_guard lk(g_fault_mu);
   g_fault_hook = hook ? std::make_shared<FaultHook>(std::move(hook)) : nullptr;

@@ -60,6 +60,10 @@ using Completion = std::function<void(int status)>;
 using FaultHook = std::function<bool(const std::string& worker_name, uint8_t frame_type, uint64_t msg_id)>;
 void set_fault_hook(FaultHook hook);
 
+// True when a worker with this uid (the random number in its address) is alive in this process. A peer
+// is taken to be "this process" only on that evidence, never on a pid that came over the wire.
+bool is_live_local_uid(uint64_t uid);
+
 constexpr uint32_t kFrameMagic = 0x46585545u;  // "EUXF"
 enum FrameType : uint8_t {
   kHello = 1,

@@ -729,6 +729,44 @@ class AxonRuntime(_axon.AxonRuntime):
                 sig.return_types = [ParamType.UNKNOWN]
         return self._register(function_id, name, sig, fn, memory_policy, lifecycle_policy)
 
+    # ---- remote GEMM: a weight resident on this runtime's GPU, callable by peers -----------------
+    GEMM_FORMATS = {"bf16": 0, "fp8_block": 1, "mxfp8": 2}
+
+    def serve_gemm(self, weight_id: int, w, fmt: str = "bf16", max_m: int = 8192) -> None:
+        """Make ``W[K, N]`` (a bf16 or fp32 tensor on this runtime's GPU) callable by peers as ``weight_id``.
+
+        ``fmt``: ``"bf16"``; ``"fp8_block"`` (e4m3 with one fp32 scale per 128x128 block of W, callers send e4m3
+        rows with one fp32 scale per 128 elements); ``"mxfp8"`` (e4m3 with one power-of-two scale per 32 elements
+        of K on both operands, scaled inside the tensor core). The weight is converted once, here. A call is served by
+        one kernel that reads the caller's X across NVLink while it computes and writes Y into the caller's memory."""
+        import torch
+
+        from ..ops import remote_gemm as g
+        code = self.GEMM_FORMATS[fmt]
+        k, n = w.shape
+        if fmt == "bf16":
+            w_t, scale = w.to(torch.bfloat16).t().contiguous(), None
+        elif fmt == "fp8_block":
+            w_t, scale = g.quantize_blocks_128x128(w.to(torch.bfloat16).t().contiguous())
+        else:
+            w_t, sf = g.quantize_mx(w.float().t().contiguous())
+            scale = g.mx_scale_chunks(sf, True)
+        self._gemm_add_weight(weight_id, w_t.data_ptr(), n, k, code, max_m, scale.data_ptr() if scale is not None else 0)
+        if not hasattr(self, "_gemm_weights"):
+            self._gemm_weights = {}
+        self._gemm_weights[weight_id] = (w_t, scale)      # the kernel reads them for as long as the weight is served
+
+    def remote_gemm(self, x, y, *, worker_name: str, weight_id: int, x_scale=None):
+        """``y[M, N] = x[M, K] @ W`` on ``worker_name``, where W is what that worker serves as ``weight_id``.
+        ``x`` and ``y`` (and ``x_scale`` for the fp8 formats) are device tensors of this process that the callee's
+        kernel reads and writes directly; they must stay untouched until the returned future resolves (to the
+        kernel's status word, 0 when all went well). Whatever produced ``x`` on the current stream is waited for first."""
+        import torch
+        torch.cuda.current_stream(x.device).synchronize()
+        nb = lambda t: t.numel() * t.element_size()  # noqa: E731
+        return self._remote_gemm(worker_name, weight_id, x.shape[0], x.data_ptr(), nb(x), y.data_ptr(), nb(y),
+                                 x_scale.data_ptr() if x_scale is not None else 0, nb(x_scale) if x_scale is not None else 0)
+
     # ---- client side --------------------------------------------------------------------------
     def invoke_raw(self, worker_name: str, request_header: RpcRequestHeader, payload=None, memory_policy: Optional[Callable] = None):
         """Send a prepared header (and an optional payload: a tensor, a list of tensors, a ``UcxBuffer`` or

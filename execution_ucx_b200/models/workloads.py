@@ -224,6 +224,74 @@ class RemoteGemmRpc:
         self.g.free(self.x_buf, self.y_buf, self.flags, getattr(self, "xs_buf", None))
 
 
+class RemoteGemmAxon:
+    """The remote-GEMM RPC through the runtime: every rank serves its weight with ``AxonRuntime.serve_gemm``
+    and calls its partner's with ``AxonRuntime.remote_gemm``. The request is a small active message that
+    describes the caller's X and Y regions (exported by the memory resource); the callee's handler maps them
+    and launches the GEMM kernel on them; the reply is the kernel's status. ``peers="all"``: every rank calls
+    every other rank's weight in one step (world - 1 calls in flight per rank)."""
+
+    def __init__(self, api: "AxonTensorRpc", m: int, n: int, k: int, fmt: str = "bf16", peers: str = "partner",
+                 weight_id: Optional[int] = None):
+        self.api, self.m, self.n, self.k, self.fmt = api, m, n, k, fmt
+        g = api.group
+        dev = g.device
+        gen = torch.Generator(device=dev).manual_seed(1234 + g.rank)
+        x = torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16)
+        self.w = (torch.randn(k, n, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        self.x_ref = x
+        self.x_scale = None
+        if fmt == "bf16":
+            self.x = x
+        elif fmt == "fp8_block":
+            self.x, self.x_scale = gemm_ops.quantize_rows_1x128(x)
+        else:
+            self.x, sf = gemm_ops.quantize_mx(x)
+            self.x_sf = sf
+            self.x_scale = gemm_ops.mx_scale_chunks(sf, False)
+        self.weight_id = weight_id if weight_id is not None else {"bf16": 1, "fp8_block": 2, "mxfp8": 3}[fmt]
+        api.server.serve_gemm(self.weight_id, self.w, fmt, max_m=m)
+        if g.world == 1:
+            self.targets = [api.partner_name]
+        elif peers == "all":
+            self.targets = [f"axon{(g.rank + 1 + i) % g.world}" for i in range(g.world - 1)]
+        else:
+            self.targets = [api.partner_name]
+        self.ys = [torch.zeros(m, n, dtype=torch.bfloat16, device=dev) for _ in self.targets]
+        torch.cuda.synchronize()
+
+    async def step(self):
+        import asyncio
+        futs = [self.api.client.remote_gemm(self.x, y, worker_name=t, weight_id=self.weight_id, x_scale=self.x_scale)
+                for t, y in zip(self.targets, self.ys)]
+        status = await asyncio.gather(*futs)
+        if any(status):
+            raise RuntimeError(f"remote gemm kernel status {status}")
+        return self.ys[0]
+
+    def callee_seed_rank(self, target: str) -> int:
+        return int(target[4:]) if target.startswith("axon") and target[4:].isdigit() else self.api.group.rank
+
+    def reference_rows(self, target_index: int = 0, rows: int = 256) -> torch.Tensor:
+        """fp32 reference of the first rows of the result of ``targets[target_index]``: the callee's weight is
+        rebuilt here from its seed, so the check needs nothing from the callee but the result itself."""
+        dev = self.api.group.device
+        r = self.callee_seed_rank(self.targets[target_index])
+        gen = torch.Generator(device=dev).manual_seed(1234 + r)
+        torch.randn(self.m, self.k, device=dev, generator=gen)                 # the callee's own X comes first in its stream
+        w = (torch.randn(self.k, self.n, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        if self.fmt == "bf16":
+            return self.x_ref[:rows].float() @ w.float()
+        if self.fmt == "fp8_block":
+            wq, ws = gemm_ops.quantize_blocks_128x128(w.t().contiguous())
+            return gemm_ops.dequantized_reference(self.x[:rows], self.x_scale[:rows], wq, ws)
+        wq, wsf = gemm_ops.quantize_mx(w.float().t().contiguous())
+        return gemm_ops.mx_dequantized_reference(self.x[:rows], self.x_sf[:rows], wq, wsf)
+
+    def max_abs_err(self, rows: int = 256) -> float:
+        return max(float((y[:rows].float() - self.reference_rows(i, rows)).abs().max()) for i, y in enumerate(self.ys))
+
+
 class RemoteGemmAllPeers:
     """Every rank calls the remote GEMM of every other rank: as callee a rank runs one fused
     kernel per caller (pulling that caller's X, storing Y into the caller's slot for this callee),
@@ -270,6 +338,61 @@ class RemoteGemmAllPeers:
         self.g.free(self.x_buf, self.y_buf, self.flags)
 
 
+class MoeAxon:
+    """MoE dispatch -> expert -> gate-weighted combine whose arenas, row headers and flag blocks come from the
+    runtime's CUDA memory resource and whose handles were exchanged by Axon calls (``AxonPeerMemory``), not by
+    ``torch.distributed``. The kernels are the same as ``MoeDispatchCombine``'s. ``expert_scale``: the expert is
+    not the identity but multiplies what it received for local expert e by ``1 + e / 256``, so that a combine
+    which paired a row with the wrong weight or the wrong expert's copy cannot pass for correct."""
+
+    @classmethod
+    async def create(cls, api: "AxonTensorRpc", n_tokens: int = 4096, hidden: int = 7168, topk: int = 8, n_experts: int = 256,
+                     fp8: bool = False, seed: int = 0) -> "MoeAxon":
+        from ..parallel.axon_peer import AxonPeerMemory
+        self = cls()
+        g = api.group
+        self.api, self.g, self.fp8 = api, g, fp8
+        rt = api.server
+        if getattr(api, "peer_memory", None) is None:
+            api.peer_memory = AxonPeerMemory(rt, g.rank, g.world, api.names, g.device)
+            await api.barrier()        # every rank serves the announcement function before anybody announces
+        pm = self.pm = api.peer_memory
+        rb = moe_ops.row_bytes(hidden, fp8)
+        cap = n_tokens * topk
+        epr = n_experts // g.world
+        arena = await pm.alloc(g.world * cap * rb)
+        meta = await pm.alloc(g.world * cap * 16)
+        flags = await pm.alloc((3 * g.world + g.world * epr) * 8)
+        self.bufs = (arena, meta, flags)
+        self.a2a = moe_ops.MoeAllToAll(g, n_tokens, hidden, topk, n_experts, fp8=fp8, capacity=cap, buffers=self.bufs)
+        dev = g.device
+        gen = torch.Generator(device=dev).manual_seed(seed + 17 * g.rank)
+        self.x = torch.randn(n_tokens, hidden, device=dev, generator=gen).to(torch.bfloat16)
+        scores = torch.rand(n_tokens, n_experts, device=dev, generator=gen)
+        self.idx = scores.topk(topk, dim=-1).indices.to(torch.int32)
+        self.w = torch.softmax(torch.randn(n_tokens, topk, device=dev, generator=gen), dim=-1)
+        torch.cuda.synchronize()
+        await api.barrier()
+        return self
+
+    def step(self) -> torch.Tensor:
+        self.a2a.dispatch(self.x, self.idx, self.w)
+        self.a2a.expert_ready()
+        return self.a2a.combine()
+
+    def reference(self) -> torch.Tensor:
+        return moe_ops.reference_dispatch_combine(self.x, self.idx, self.w, self.fp8)
+
+    def bytes_per_direction(self) -> int:
+        return self.a2a.n_tokens * self.a2a.topk * self.a2a.row_bytes
+
+    async def close(self):
+        torch.cuda.synchronize()
+        await self.api.barrier()
+        self.pm.free(*self.bufs)
+        await self.api.barrier()
+
+
 class MoeDispatchCombine:
     """MoE token dispatch -> identity expert -> gate-weighted combine on all ranks."""
 
@@ -312,6 +435,7 @@ class AxonTensorRpc:
     def __init__(self, group: PeerGroup, dtype=torch.bfloat16, timeout_ms: int = 60000):
         from .. import axon
         self.axon, self.group, self.dtype = axon, group, dtype
+        self.g = group
         self.dev = group.device
         self.rank, self.world = group.rank, group.world
         self._srv_bufs, self._cli_bufs = {}, {}
@@ -328,7 +452,8 @@ class AxonTensorRpc:
             return buf
         return policy
 
-    async def start(self):
+    async def start(self, connect_all: bool = False):
+        """``connect_all``: connect to every rank's runtime, not only to the partner's (the all-to-all workloads)."""
         axon = self.axon
         index = self.dev.index or 0
         device = (lambda i: axon.cuda(i)) if self.dev.type == "cuda" else (lambda i: None)
@@ -343,6 +468,7 @@ class AxonTensorRpc:
             self.server.start_server()
             self.client.start_client()
             self.partner_name = "axon_srv"
+            self.names = ["axon_srv"]
             await self.client.connect_endpoint_async(self.server.get_local_address(), self.partner_name)
             return
         import torch.distributed as dist
@@ -355,7 +481,12 @@ class AxonTensorRpc:
         dist.all_gather_object(addrs, bytes(rt.get_local_address()))
         partner = _partner(self.rank, self.world)
         self.partner_name = f"axon{partner}"
+        self.names = [f"axon{r}" for r in range(self.world)]
         await rt.connect_endpoint_async(addrs[partner], self.partner_name)
+        if connect_all:
+            for r in range(self.world):
+                if r not in (self.rank, partner):
+                    await rt.connect_endpoint_async(addrs[r], self.names[r])
         await self.barrier()
 
     async def barrier(self):

@@ -71,3 +71,47 @@ def test_capacity_overflow_is_reported(cuda_device):
     rk.dispatch(x, idx, w)
     torch.cuda.synchronize()
     assert int(rk.status.item()) & 0xff == 3
+
+
+@pytest.mark.parametrize("world,t,hidden,topk,ne", [(4, 96, 1024, 4, 16), (8, 40, 7168, 8, 256), (2, 48, 1024, 12, 16)])
+def test_combine_pairs_each_row_with_its_own_weight_and_expert(cuda_device, world, t, hidden, topk, ne):
+    """A non-identity expert: every expert rank multiplies the rows it received for local expert e by
+    (1 + (e + rank * experts_per_rank) / 256) before the sources combine. The fp32 reference applies the
+    same factor per (token, k-slot). With the identity expert the combine is x * sum(w), and a combine that
+    took another k-slot's weight, or another expert's copy of the token, would still pass; here it cannot."""
+    from execution_ucx_b200.ops import moe
+    ranks = moe.MoeAllToAll.emulated(world, t, hidden, topk, ne, fp8=False)
+    epr = ne // world
+    xs, idxs, ws = [], [], []
+    for r in range(world):
+        xs.append(torch.randn(t, hidden, device=cuda_device).to(torch.bfloat16))
+        i, w = _routing(t, topk, ne, cuda_device, 300 + r)
+        idxs.append(i), ws.append(w)
+    for r in range(world):
+        ranks[r].dispatch(xs[r], idxs[r], ws[r])
+    for r in range(world):
+        ranks[r].expert_ready()
+    torch.cuda.synchronize()
+    # the "expert": scale every received row in place, by its expert's factor (read from the row headers)
+    for dst in range(world):
+        counts = ranks[dst].recv_counts().tolist()
+        for src in range(world):
+            n = counts[src]
+            if n == 0:
+                continue
+            meta = ranks[dst].recv_meta(src, n)
+            le = (meta[:, 1] >> 16).long()
+            factor = 1.0 + (le + dst * epr).float() / 256.0
+            rows = ranks[dst].recv_rows(src, n).view(torch.bfloat16).view(n, hidden)
+            rows.copy_((rows.float() * factor.unsqueeze(1)).to(torch.bfloat16))
+    outs = [ranks[r].combine().clone() for r in range(world)]
+    torch.cuda.synchronize()
+    for r in range(world):
+        ranks[r].check_status()
+        x = xs[r].float()
+        ref = torch.zeros_like(x)
+        for k in range(topk):
+            f = 1.0 + idxs[r][:, k].float() / 256.0
+            y = (x * f.unsqueeze(1)).to(torch.bfloat16).float()      # what the expert stored for this (token, k)
+            ref += ws[r][:, k].unsqueeze(1) * y
+        torch.testing.assert_close(outs[r].float(), ref, rtol=2e-2, atol=2e-2)
