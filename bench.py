@@ -100,7 +100,7 @@ def main() -> int:
     # receiver's memory policy returned; completion through a flag the receiver's worker thread polls).
     async def api_main():
         api = AxonTensorRpc(group)
-        await api.start()
+        await api.start(connect_all=not args.no_extras)
         for _ in range(warmup):
             y = await api.step(src)
         torch.cuda.synchronize()
@@ -167,6 +167,12 @@ def main() -> int:
                 if n == nbytes:
                     break
         res["api_rows"] = rows
+        if not args.no_extras:
+            try:
+                res["services"] = await service_measurements(api, group, peaks)
+            except Exception as e:  # a failed side measurement must not hide the headline
+                traceback.print_exc()
+                res["services"] = {"error": f"{type(e).__name__}: {e}", "trace": traceback.format_exc(limit=4)}
         api.stop()
 
     # the sampler starts (and loads NVML) before the barrier, so that no rank enters the timed region late
@@ -192,7 +198,7 @@ def main() -> int:
     extra = {"api_sweep": {"what": "AxonRuntime.invoke('echo') of a device tensor, every rank to its partner at once; host clock per call, max over ranks",
                            "rows": res["api_rows"]},
              "headline_host_clock_ms_per_step": round(group.max_over_ranks(res["host_ms"]) / steps, 5),
-             "transport_counters_rank0": res["stats"]}
+             "transport_counters_rank0": res["stats"], **res.get("services", {})}
     if not args.no_extras:
         # the data plane alone (no header, no dispatcher, no runtime): what the kernels do when nothing else is in the way
         rpc = TensorRpcEcho(group, nbytes)
@@ -223,6 +229,77 @@ def main() -> int:
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+async def service_measurements(api, group, peaks):
+    """Remote-GEMM RPC and MoE dispatch+combine through the runtime: the GEMM is an Axon function of the
+    callee (`AxonRuntime.serve_gemm` / `remote_gemm`), the MoE buffers were announced by Axon calls."""
+    import torch
+    from execution_ucx_b200.models.workloads import MoeAxon, RemoteGemmAxon
+    from execution_ucx_b200.utils import timing
+    world = group.world
+    out = {}
+    m = n = k = 8192
+    flush = timing.L2Flusher(group.device)
+
+    async def timed_calls(w, iters=10, warm=3):
+        ts = []
+        for i in range(warm + iters):
+            flush()
+            torch.cuda.synchronize()
+            await api.barrier()
+            t0 = time.perf_counter()
+            await w.step()
+            if i >= warm:
+                ts.append((time.perf_counter() - t0) * 1e3)
+        return group.max_over_ranks(timing.percentile(ts, 50))
+
+    wid = 20
+    for fmt, key in (("bf16", "remote_gemm_axon_bf16"), ("fp8_block", "remote_gemm_axon_fp8_block_scaled"), ("mxfp8", "remote_gemm_axon_mxfp8")):
+        wid += 1
+        w = RemoteGemmAxon(api, m, n, k, fmt=fmt, weight_id=wid)
+        await api.barrier()
+        ms = await timed_calls(w)
+        err = group.max_over_ranks(w.max_abs_err(256))
+        t_compute = 2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12) * 1e3
+        x_bytes = m * k * (2 if fmt == "bf16" else 1)
+        t_link = x_bytes / (timing.NVLINK_PEER_GBS * 1e9) * 1e3 if world > 1 else 0.0
+        out[key] = {"shape": [m, n, k], "ms_p50": round(ms, 4), "tflops_per_gpu": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1),
+                    "roofline_ms_vs_bf16_peak": round(max(t_compute, t_link), 4),
+                    "fraction_of_bf16_roofline_of_" + peaks.get("source", "measured"): round(max(t_compute, t_link) / ms, 3),
+                    "max_abs_err_vs_fp32_first_256_rows": err,
+                    "timing": "host clock around `await remote_gemm(...)` (request, kernel, reply), max over ranks",
+                    "path": "Axon call with the caller's region descriptors -> callee's handler launches the GEMM on the caller's memory -> reply"}
+        del w
+    if world > 2:
+        w = RemoteGemmAxon(api, m, n, k, fmt="bf16", peers="all", weight_id=30)
+        await api.barrier()
+        ms = await timed_calls(w, iters=5, warm=2)
+        calls = world - 1
+        out["remote_gemm_axon_bf16_all_peers"] = {"shape": [m, n, k], "calls_served_per_rank": calls, "ms_per_round_p50": round(ms, 3),
+                                                   "ms_per_call": round(ms / calls, 4), "max_abs_err_vs_fp32_first_256_rows": group.max_over_ranks(w.max_abs_err(256)),
+                                                   "tflops_per_gpu": round(2.0 * m * n * k * calls / (ms * 1e-3) / 1e12, 1)}
+        del w
+    torch.cuda.empty_cache()
+    for fp8, key in ((False, "moe_axon_bf16"), (True, "moe_axon_fp8")):
+        mo = await MoeAxon.create(api, fp8=fp8)
+        ts = timing.time_cuda(mo.step, iters=10, warmup=3, flush=flush, before=group.barrier if world > 1 else None)
+        mo.a2a.check_status()
+        us = group.max_over_ranks(timing.percentile(ts, 50)) * 1e3
+        err = float((mo.a2a.out.float() - mo.reference()).abs().max())
+        remote = mo.bytes_per_direction() * (world - 1) / world
+        if world > 1:
+            roof_us = 2 * remote / (timing.NVLINK_PEER_GBS * 1e9) * 1e6
+            bound = "nvlink (measured 770 GB/s per direction)"
+        else:
+            roof_us = 2 * (mo.bytes_per_direction() + mo.x.numel() * 2) / (peaks["hbm_gbs"] * 1e9) * 1e6
+            bound = "hbm copy (read+write)"
+        out[key] = {"dispatch_combine_us_p50": round(us, 1), "roofline_us": round(roof_us, 1), "bound": bound,
+                    "fraction_of_roofline": round(roof_us / us, 3), "max_abs_err": err, "tokens_per_rank": mo.a2a.n_tokens,
+                    "hidden": mo.a2a.hidden, "topk": mo.a2a.topk, "experts": mo.a2a.n_experts,
+                    "buffers": "allocated from the runtime's CUDA memory resource, announced to the peers by Axon calls"}
+        await mo.close()
+    return out
 
 
 def side_measurements(group, dev, rank, world, peaks, rpc, src):

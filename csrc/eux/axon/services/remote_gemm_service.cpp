@@ -74,6 +74,12 @@ bool RemoteGemmService::EnsureDevice() {
     return false;
   }
   std::memset(h, 0, 256);
+  // the handler launches on behalf of a peer: its kernels are loaded now, not by their first launch
+  if (int rc = eux_gemm_preload(); rc != 0) {
+    eux_host_free(h);
+    cudaStreamDestroy(st);
+    return false;
+  }
   flag_host_ = static_cast<uint64_t*>(h);
   flag_dev_ = static_cast<uint64_t*>(d);
   stream_ = st;
@@ -124,7 +130,9 @@ RemoteGemmService::Done RemoteGemmService::Launch(Resident& r, int32_t m, const 
   d.wait_timeout_ns = 2'000'000'000ull;
   d.status = reinterpret_cast<uint32_t*>(flag_dev_ + 8);
   d.copy_ctas = 0;
-  d.flags = EUX_GEMM_FLAG_CTA_PAIRS | EUX_GEMM_FLAG_COPY_WARPS;  // pairs where M allows; X copied by the spare warps of every CTA
+  // pairs where M allows; X copied by the spare warps of every CTA; the flag is raised after a failed run too:
+  // the call is answered with the kernel's status instead of running into the caller's deadline
+  d.flags = EUX_GEMM_FLAG_CTA_PAIRS | EUX_GEMM_FLAG_COPY_WARPS | EUX_GEMM_FLAG_DONE_ALWAYS;
   cudaSetDevice(mr_->device());
   const int rc = eux_gemm_launch(&d, stream_);
   if (rc != 0) {
@@ -170,6 +178,7 @@ bool RemoteGemmService::Register() {
     auto sched = self->worker_.server_context()->get_scheduler();
     // no thread waits for the GPU: the server's loop completes the call when the kernel's flag shows up
     return ex::then(sched.schedule_when_flag(done.flag, done.seq), [done]() -> int32_t {
+      ucxx::nvtx_mark("axon.remote_gemm.kernel_done");
       const uint32_t st = *done.status;
       if (st) *const_cast<volatile uint32_t*>(done.status) = 0;
       return static_cast<int32_t>(st);

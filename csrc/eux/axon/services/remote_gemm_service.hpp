@@ -15,6 +15,7 @@
 // :522-584 sends the response). This service is the fused replacement of that sequence.
 #pragma once
 
+#include <array>
 #include <cstdint>
 #include <memory>
 #include <mutex>
@@ -57,6 +58,10 @@ class RemoteGemmService {
   bool Register();
   // Kernel launches made by this service's handler so far.
   uint64_t launches() const { return launches_.load(); }
+  // (launches issued, completion sequence the kernels have reached, status word): for diagnostics
+  std::array<uint64_t, 3> progress() const {
+    return {seq_, flag_host_ ? *static_cast<volatile uint64_t*>(flag_host_) : 0, flag_host_ ? static_cast<uint64_t>(*reinterpret_cast<volatile uint32_t*>(flag_host_ + 8)) : 0};
+  }
 
   // ---- caller ----
   // Y[m, N] = X[m, K] * W(weight_id) on worker `worker_name` (an endpoint of this worker's client side).

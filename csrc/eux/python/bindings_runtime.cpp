@@ -389,6 +389,7 @@ class PyAxonRuntime {
     if (!svc.Register()) throw std::runtime_error("the remote GEMM function could not be registered");
   }
   uint64_t gemm_launches() { return gemm_ ? gemm_->launches() : 0; }
+  std::array<uint64_t, 3> gemm_progress() { return gemm_ ? gemm_->progress() : std::array<uint64_t, 3>{0, 0, 0}; }
   py::object remote_gemm(const std::string& worker_name, uint32_t weight_id, int m, uintptr_t x, size_t x_bytes, uintptr_t y, size_t y_bytes,
                          uintptr_t xs, size_t xs_bytes) {
     return future_from(gemm_service().Call(worker_name, weight_id, m, reinterpret_cast<const void*>(x), x_bytes, reinterpret_cast<void*>(y),
@@ -617,6 +618,7 @@ void bind_runtime(py::module_& m) {
       .def("peer_memory_arrived", &PyAxonRuntime::peer_memory_arrived, py::arg("tag"))
       .def("peer_memory_resolve", &PyAxonRuntime::peer_memory_resolve, py::arg("tag"))
       .def("peer_memory_free", &PyAxonRuntime::peer_memory_free, py::arg("tag"))
+      .def("gemm_progress", &PyAxonRuntime::gemm_progress, "(launches issued, completions seen, kernel status word) of the remote-GEMM handler")
       .def("gemm_launches", &PyAxonRuntime::gemm_launches, "GEMM kernels launched by this runtime's remote-GEMM handler so far.")
       .def("set_timeout", &PyAxonRuntime::set_timeout).def("set_reject_messages", &PyAxonRuntime::set_reject_messages)
       .def_property_readonly("worker_name", &PyAxonRuntime::worker_name)

@@ -1334,6 +1334,7 @@ bool Worker::ensure_device() {
     device_failed_ = true;
     return false;
   }
+  if (int rc = eux_xfer_preload(); rc != 0) UCX_CONN_WARN << opt_.name << ": transfer kernels could not be loaded ahead of use: " << eux_error_string(rc);
   stream_ = st;
   flag_host_ = static_cast<uint64_t*>(h);
   flag_dev_ = static_cast<uint64_t*>(d);

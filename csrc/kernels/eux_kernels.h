@@ -147,6 +147,11 @@ EUX_API int eux_device_free(void* p);
 EUX_API int eux_host_alloc_mapped(void** host_ptr, void** dev_ptr, size_t bytes);
 EUX_API int eux_host_free(void* host_ptr);
 EUX_API const char* eux_error_string(int err);
+/* Load the kernels of a family on the current device now, so that no later launch has to (a first launch that
+ * loads can deadlock against a running kernel that waits for a peer: see tensor_xfer.cu). */
+EUX_API int eux_xfer_preload(void);
+EUX_API int eux_moe_preload(void);
+EUX_API int eux_gemm_preload(void);
 /* cudaMemcpyPeerAsync, for the copy-engine baseline of the benchmarks (not used by the data plane) */
 EUX_API int eux_memcpy_peer_async(void* dst, int dst_device, const void* src, int src_device, size_t bytes, void* stream);
 
@@ -202,6 +207,9 @@ typedef struct eux_gemm_desc {
 /* With a remote X: two spare warps of every CTA copy X (and its scales) beside the GEMM's warps, instead of
    copy_ctas CTAs that copy first and compute afterwards. */
 #define EUX_GEMM_FLAG_COPY_WARPS 2
+/* Store done_value to done_flag when the kernel ends, whether or not it succeeded (the status word tells):
+   for callers that must learn of the end either way. Without it the flag means "Y is complete". */
+#define EUX_GEMM_FLAG_DONE_ALWAYS 4
 /* With a remote X the first group of tiles is only a few row blocks tall, so that the first wave of
    CTAs waits for the first panels only. EUX_GEMM_FLAG_HEAD(n) overrides that height (0: no short group). */
 #define EUX_GEMM_FLAG_HEAD(n) ((((n) + 1) & 0xff) << 8)

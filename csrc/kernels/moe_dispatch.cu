@@ -894,3 +894,18 @@ extern "C" int eux_moe_combine_launch(const eux_moe_desc* d, int ctas, void* str
   else moe_combine_bf16_kernel<<<ctas, kMoeThreads, 0, (cudaStream_t)stream>>>(*d);
   return (int)cudaGetLastError();
 }
+
+
+// Loads every kernel of this file (see eux_xfer_preload for why a first launch must not be the one that loads).
+extern "C" int eux_moe_preload(void) {
+  cudaFuncAttributes attr;
+  const void* kernels[] = {(const void*)moe_route_kernel,          (const void*)moe_dispatch_bf16_kernel,   (const void*)moe_dispatch_fp8_kernel,
+                           (const void*)moe_dispatch_fp8_rows_kernel, (const void*)moe_expert_ready_kernel, (const void*)moe_combine_bf16_kernel,
+                           (const void*)moe_combine_bf16_stream_kernel, (const void*)moe_combine_fp8_kernel, (const void*)moe_combine_fp8_rows_kernel,
+                           (const void*)moe_combine_fp8_stream_kernel};
+  for (const void* k : kernels) {
+    cudaError_t e = cudaFuncGetAttributes(&attr, k);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}

@@ -53,6 +53,7 @@ struct GemmParams {
   int head_blocks;  // height of the first tile group in row blocks (0: like the others)
   int copy_warps;   // warps (two per CTA) that copy X beside the GEMM's own warps; 0 when copy CTAs do it
   uint32_t panel_target;  // count at which a panel of X is complete (0: X is local, nothing to wait for)
+  int done_always;        // publish the done flag after a failed run too (the status word says which it was)
   // block-scaled fp8 only
   const float* x_scale_src;   // [M, K/128], caller's (may be peer)
   float* x_scale_stage;       // local copy used by the epilogue (== x_scale_src when X is local)
@@ -290,9 +291,9 @@ __device__ bool copy_role_n(const GemmParams& p, const int nthreads, unsigned ch
 
 // Two otherwise idle warps of every CTA copy X while the CTA's other warps compute: the transfer is spread
 // over all SMs' load/store units (a few dedicated CTAs moving it with bulk copies reach about half the link
-// rate), and no CTA is lost to the GEMM. X is cut into 1 KiB pieces handed round-robin to the copy warps of
-// the grid, in address order, so the panels complete in the order in which the tiles need them. A warp adds
-// one to a panel's counter once it has no piece of that panel left; a panel is complete at copy_warps.
+// rate), and no CTA is lost to the GEMM. X is cut into units of 8 KiB that the copy warps draw from a counter,
+// in address order, so the panels complete in the order in which the tiles need them; every unit counts once
+// on its panel, and a panel is complete at its number of units.
 __device__ __forceinline__ void ld_v8_b32(const void* ptr, uint32_t (&v)[8]) {
   asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
@@ -305,21 +306,17 @@ __device__ __forceinline__ void st_v8_b32(void* ptr, const uint32_t (&v)[8]) {
 }
 __device__ __forceinline__ void copy_warp_role(const GemmParams& p, uint32_t warp_id, int lane) {
   constexpr int U = 8;  // 1 KiB pieces per unit of work: 8 KiB in flight per warp
-  const uint32_t nw = (uint32_t)p.copy_warps;
   const int panels = p.M / BM;
   const uint32_t units_per_panel = (uint32_t)(((size_t)BM * p.K * p.elem_bytes) >> 13);
-  const uint32_t total = (uint32_t)panels * units_per_panel;
-  if (p.x_scale_src && p.x_scale_stage && p.x_scale_src != p.x_scale_stage) {
-    // The row scales travel first. Every warp copies its slice and then counts once on every panel, so a
-    // panel is complete only when all scales are here too (the target is units per panel + copy warps).
-    const size_t n4 = (size_t)p.M * (p.K / 128) / 4;  // 4 bytes per row and 128 elements in either fp8 format
-    const float4* s4 = reinterpret_cast<const float4*>(p.x_scale_src);
-    float4* d4 = reinterpret_cast<float4*>(p.x_scale_stage);
-    for (size_t i = (size_t)warp_id * 32 + lane; i < n4; i += (size_t)nw * 32) d4[i] = __ldcg(s4 + i);
-    __syncwarp();
-    __threadfence();
-    for (int q = lane; q < panels; q += 32) red_release_gpu_add(p.panel_flags + q, 1u);
-  }
+  // The scales of a panel's rows (fp32 per 1x128, or MX chunks: K * 4 bytes per 128 rows in either format,
+  // contiguous) travel as extra units in front of the panel's data units. Nothing here depends on how many
+  // CTAs of the grid are running: whichever copy warps are resident draw the units in order, so a grid that
+  // shares the device with some other kernel (and does not get every SM) still completes every panel.
+  const bool scales = p.x_scale_src && p.x_scale_stage && p.x_scale_src != p.x_scale_stage;
+  const size_t scale_panel_bytes = scales ? (size_t)p.K * 4 : 0;
+  const uint32_t scale_units = (uint32_t)((scale_panel_bytes + 8191) >> 13);
+  const uint32_t per_panel = units_per_panel + scale_units;
+  const uint32_t total = (uint32_t)panels * per_panel;
   const unsigned char* src = p.x_src + (size_t)lane * 32;
   unsigned char* dst = p.x_stage + (size_t)lane * 32;
   // Units of 8 KiB, in address order, are drawn from a counter: a warp that falls behind (its SM is busy with
@@ -331,33 +328,42 @@ __device__ __forceinline__ void copy_warp_role(const GemmParams& p, uint32_t war
     if (lane == 0) u = atomicAdd(p.sched + 3, 1u);
     return __shfl_sync(0xffffffffu, u, 0);
   };
-  int pending = -1;  // panel of the unit whose stores have been issued but not counted
-  uint32_t u = draw();
-  while (u < total) {
-    uint32_t v[U][8];
-    const size_t off = (size_t)u << 13;
-#pragma unroll
-    for (int j = 0; j < U; ++j) ld_v8_b32(src + off + ((size_t)j << 10), v[j]);
-    const uint32_t next = draw();
-    if (pending >= 0) {
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence();
-        red_release_gpu_add(p.panel_flags + pending, 1u);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < U; ++j) st_v8_b32(dst + off + ((size_t)j << 10), v[j]);
-    pending = (int)(u / units_per_panel);
-    u = next;
-  }
-  if (pending >= 0) {
+  auto count = [&](int panel) {
     __syncwarp();
     if (lane == 0) {
       __threadfence();
-      red_release_gpu_add(p.panel_flags + pending, 1u);
+      red_release_gpu_add(p.panel_flags + panel, 1u);
     }
+  };
+  int pending = -1;  // panel of the unit whose stores have been issued but not counted
+  uint32_t u = draw();
+  while (u < total) {
+    const uint32_t panel = u / per_panel, w = u % per_panel;
+    if (w < scale_units) {
+      // a slice of this panel's scales: few and small, copied and counted at once
+      const size_t begin = (size_t)panel * scale_panel_bytes + ((size_t)w << 13);
+      const size_t end = min((size_t)panel * scale_panel_bytes + scale_panel_bytes, begin + 8192);
+      const unsigned char* ss = reinterpret_cast<const unsigned char*>(p.x_scale_src);
+      unsigned char* sd = reinterpret_cast<unsigned char*>(p.x_scale_stage);
+      for (size_t i = begin + (size_t)lane * 16; i < end; i += 512)
+        *reinterpret_cast<uint4*>(sd + i) = __ldcg(reinterpret_cast<const uint4*>(ss + i));
+      const uint32_t next = draw();
+      count((int)panel);
+      u = next;
+      continue;
+    }
+    uint32_t v[U][8];
+    const size_t off = ((size_t)panel * units_per_panel + (w - scale_units)) << 13;
+#pragma unroll
+    for (int j = 0; j < U; ++j) ld_v8_b32(src + off + ((size_t)j << 10), v[j]);
+    const uint32_t next = draw();
+    if (pending >= 0) count(pending);
+#pragma unroll
+    for (int j = 0; j < U; ++j) st_v8_b32(dst + off + ((size_t)j << 10), v[j]);
+    pending = (int)panel;
+    u = next;
   }
+  if (pending >= 0) count(pending);
 }
 
 __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
@@ -373,7 +379,9 @@ __device__ __forceinline__ void finish_cta(const GemmParams& p, bool ok) {
     p.sched[2] = 0;  // the tile counter
     p.sched[3] = 0;  // the copy warps' unit counter
     __threadfence_system();
-    if (all_ok && p.done_flag) st_release_sys(p.done_flag, p.done_value);
+    // done_always: a caller that reads the status word learns of the end of the kernel either way (an RPC
+    // handler must answer); otherwise the flag means "Y is complete" and stays silent after a failure
+    if ((all_ok || p.done_always) && p.done_flag) st_release_sys(p.done_flag, p.done_value);
   }
 }
 
@@ -1315,10 +1323,11 @@ extern "C" int eux_gemm_launch(const eux_gemm_desc* d, void* stream) {
   // bits 8..15 of the flags: 1 + the height of the first tile group, 0 for the default
   const int head_arg = (int)((d->flags >> 8) & 0xffu) - 1;
   p.copy_warps = 0;
+  p.done_always = (d->flags & EUX_GEMM_FLAG_DONE_ALWAYS) ? 1 : 0;
   p.panel_target = (uint32_t)copy_ctas;
-  // copy warps: units of 8 KiB per 128-row panel, plus one count per warp when scales travel first
-  auto warp_target = [&](int warps) {
-    return (uint32_t)(((size_t)BM * d->K * eb) >> 13) + (d->fp8 ? (uint32_t)warps : 0u);
+  // copy warps: units of 8 KiB per 128-row panel, plus the units that carry the panel's scales (K * 4 bytes)
+  auto warp_target = [&](int) {
+    return (uint32_t)(((size_t)BM * d->K * eb) >> 13) + (d->fp8 ? (uint32_t)(((size_t)d->K * 4 + 8191) >> 13) : 0u);
   };
   p.head_blocks = !pull ? 0 : head_arg >= 0 ? head_arg : 4;  // of 128 rows: groups of 4, 4, 8, then 8
   static bool attr_set[64][2] = {{false}};
@@ -1435,4 +1444,18 @@ extern "C" int eux_gemm_bf16_noalloc(const void* x, const void* w_t, void* y, in
   d.copy_ctas = 0;
   d.flags = EUX_GEMM_FLAG_CTA_PAIRS;  // taken when M is a multiple of 256
   return eux_gemm_launch(&d, stream);
+}
+
+
+// Loads every GEMM kernel (see eux_xfer_preload in tensor_xfer.cu for why a first launch must not be the one
+// that loads): a service that launches on behalf of a peer calls this when it is set up.
+extern "C" int eux_gemm_preload(void) {
+  cudaFuncAttributes attr;
+  const void* kernels[] = {(const void*)remote_gemm_kernel<false>, (const void*)remote_gemm_fp8_kernel, (const void*)remote_gemm_2cta_kernel<false>,
+                           (const void*)remote_gemm_2cta_kernel<true>};
+  for (const void* k : kernels) {
+    cudaError_t e = cudaFuncGetAttributes(&attr, k);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
 }

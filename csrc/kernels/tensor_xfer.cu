@@ -701,3 +701,43 @@ extern "C" const char* eux_error_string(int err) {
     default: return cudaGetErrorString((cudaError_t)err);
   }
 }
+
+
+// ---------------------------------------------------------------------------
+// Loading every kernel of this file up front. With lazy module loading (the default of the driver) the
+// first launch of a kernel loads it, and loading may have to wait for kernels that are running on the
+// device. A kernel of some other library that spins until a peer does something (a collective's barrier,
+// say) while that peer waits for the reply to a call whose handler launches one of these kernels for the
+// first time is then a deadlock. Everything that launches on behalf of a peer loads its kernels first.
+// ---------------------------------------------------------------------------
+namespace {
+template <class K>
+int preload_one(K kernel) {
+  cudaFuncAttributes attr;
+  return (int)cudaFuncGetAttributes(&attr, reinterpret_cast<const void*>(kernel));
+}
+template <typename S>
+int preload_typed() {
+  int rc = preload_one(xfer_typed_kernel<S, float>);
+  if (!rc) rc = preload_one(xfer_typed_kernel<S, __half>);
+  if (!rc) rc = preload_one(xfer_typed_kernel<S, __nv_bfloat16>);
+  if (!rc) rc = preload_one(xfer_typed_kernel<S, __nv_fp8_e4m3>);
+  if (!rc) rc = preload_one(xfer_rpc_step_kernel<S>);
+  return rc;
+}
+}  // namespace
+
+extern "C" int eux_xfer_preload(void) {
+  int rc = preload_one(xfer_bytes_kernel<true>);
+  if (!rc) rc = preload_one(xfer_bytes_kernel<false>);
+  if (!rc) rc = preload_one(xfer_bulk_kernel);
+  if (!rc) rc = preload_one(xfer_strided_kernel);
+  if (!rc) rc = preload_one(xfer_batch_kernel);
+  if (!rc) rc = preload_one(pingpong_kernel);
+  if (!rc) rc = preload_one(xfer_pull_batch_kernel);
+  if (!rc) rc = preload_typed<float>();
+  if (!rc) rc = preload_typed<__half>();
+  if (!rc) rc = preload_typed<__nv_bfloat16>();
+  if (!rc) rc = preload_typed<__nv_fp8_e4m3>();
+  return rc;
+}

@@ -116,7 +116,24 @@ def load():
         lib.eux_gemm_bf16_noalloc.argtypes = [P, P, P, I, I, I, P, U64, P]
         lib.eux_gemm_bf16_noalloc.restype = I
     _lib = lib
+    _preload(lib)
     return lib
+
+
+def _preload(lib) -> None:
+    """Load every kernel on the current device now. With the driver's lazy loading a kernel is loaded by
+    its first launch, which may have to wait for kernels that are running; a first launch made while some
+    library's kernel spins on a peer (a collective's barrier) that in turn waits for this launch is a
+    deadlock. Nothing is done where CUDA has not been brought up (CPU-only use of the package)."""
+    try:
+        import torch
+        if not (torch.cuda.is_available() and torch.cuda.is_initialized()):
+            return
+    except Exception:
+        return
+    for fn in ("eux_xfer_preload", "eux_moe_preload", "eux_gemm_preload"):
+        if hasattr(lib, fn):
+            getattr(lib, fn)()
 
 
 def check(rc: int, what: str) -> None:
