@@ -9,6 +9,7 @@
 #include <cuda_runtime_api.h>
 
 #include <atomic>
+#include <optional>
 #include <unordered_map>
 
 #include "eux/ucxx/nvtx_range.hpp"
@@ -310,6 +311,7 @@ class PyAxonRuntime {
       for (auto& m : metas) lst.append(py::cast(m));
       py::object out = (*fn)(lst);
       if (py::isinstance<py::list>(out) || py::isinstance<py::tuple>(out)) out = py::reinterpret_borrow<py::sequence>(out)[0];
+      if (auto direct = receive_buffer_of(*mr, out)) return std::move(*direct);
       ImportedTensor t = import_tensor(out);
       remember_owner(t.data, out);
       return to_ucx_buffer(*mr, std::move(t));
@@ -334,6 +336,25 @@ class PyAxonRuntime {
     };
     return p;
   }
+  // A tensor that says where it is (torch: data_ptr(), numel(), element_size(), is_contiguous(), is_cuda)
+  // becomes a receive buffer without a DLPack export: the export of a CUDA tensor orders streams and
+  // builds a capsule, tens of microseconds that a buffer about to be overwritten does not need.
+  static std::optional<UcxBuffer> receive_buffer_of(ucxx::UcxMemoryResourceManager& mr, py::object& out) {
+    if (!py::hasattr(out, "data_ptr") || !py::hasattr(out, "element_size") || !py::hasattr(out, "is_contiguous")) return std::nullopt;
+    try {
+      if (!out.attr("is_contiguous")().cast<bool>()) return std::nullopt;
+      void* data = reinterpret_cast<void*>(out.attr("data_ptr")().cast<uintptr_t>());
+      const size_t bytes = out.attr("numel")().cast<size_t>() * out.attr("element_size")().cast<size_t>();
+      const bool on_gpu = py::hasattr(out, "is_cuda") && out.attr("is_cuda").cast<bool>();
+      remember_owner(data, out);
+      auto keep = gil_shared(out);
+      return UcxBuffer(mr, on_gpu ? ucx_memory_type::CUDA : ucx_memory_type::HOST, data, bytes, nullptr, true,
+                       [keep](void*) mutable { keep.reset(); });
+    } catch (py::error_already_set&) {
+      return std::nullopt;  // not that kind of object after all: the DLPack road
+    }
+  }
+
   ClientMemoryPolicy client_policy(py::object policy, bool want_vec) {
     ClientMemoryPolicy c;
     c.want_vec = want_vec;

@@ -59,6 +59,29 @@ uint64_t random_uid() {
 }
 bool is_device_type(ucx_memory_type_t t) { return t == ucx_memory_type::CUDA || t == ucx_memory_type::CUDA_MANAGED; }
 
+// Large pushes of every worker of this process that target memory through one GPU leave through one
+// stream per device, in the order in which they were asked for. Two workers (a runtime's client and server
+// side) that push in the same direction at the same time would otherwise share the link, and the transfer
+// that the peer is waiting for would take twice as long; one after the other, each runs at the full rate
+// and the first is done in half the time.
+std::mutex g_bulk_mu;
+std::unordered_map<int, cudaStream_t> g_bulk_streams;
+cudaStream_t bulk_stream_for(int device) {
+  std::lock_guard lk(g_bulk_mu);
+  auto it = g_bulk_streams.find(device);
+  if (it != g_bulk_streams.end()) return it->second;
+  cudaStream_t st = nullptr;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    st = nullptr;
+  }
+  if (prev >= 0 && prev != device) cudaSetDevice(prev);
+  if (st) g_bulk_streams.emplace(device, st);  // lives as long as the process
+  return st;
+}
+
 // Workers alive in this process, by their random uid. A peer is "this process" only when the uid it
 // presented in the handshake is found here: a pid alone says nothing (two containers, pid namespaces
 // or hosts routinely share one), and it arrives from the wire.
@@ -1440,15 +1463,20 @@ void Worker::flush_pull_batch() {
 }
 
 void Worker::poll_device() {
-  while (!device_ops_.empty()) {
-    const uint64_t seq = device_ops_.front().seq;
-    if (*static_cast<volatile uint64_t*>(flag_host_ + seq % kFlagSlots) != seq) break;
+  // Every transfer in flight owns its flag word, and transfers run on two streams (the worker's own and
+  // the device's stream for large pushes), so they finish in any order: each is looked at on its own.
+  for (size_t i = 0; i < device_ops_.size();) {
+    const uint64_t seq = device_ops_[i].seq;
+    if (*static_cast<volatile uint64_t*>(flag_host_ + seq % kFlagSlots) != seq) {
+      ++i;
+      continue;
+    }
     std::atomic_thread_fence(std::memory_order_acquire);
-    DeviceOp op = std::move(device_ops_.front());
-    device_ops_.pop_front();
+    DeviceOp op = std::move(device_ops_[i]);
+    device_ops_.erase(device_ops_.begin() + static_cast<std::ptrdiff_t>(i));
     if (op.send_fin && op.ep && eps_.count(op.ep) && op.ep->state_ == Endpoint::State::kConnected)
       send_control(op.ep, kRndvFin, 0, op.msg_id, UCS_OK);
-    if (op.done) op.done(UCS_OK);
+    if (op.done) op.done(UCS_OK);  // may start new transfers: they are appended and looked at in this pass too
   }
   // payloads that peers push: small ones into ring slots, large ones into posted buffers. The peer's
   // kernel stores the flag word (in the shared page) after its data stores; this thread reads it.
@@ -1609,6 +1637,8 @@ void Worker::teardown_device_channel(Endpoint* ep) {
   ep->out_flags_dev_ = nullptr;
   if (ep->flags_registered_ && ep->shm_) {
     if (stream_) cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));  // kernels of this worker that target the page (bounded)
+    if (bulk_used_)
+      if (cudaStream_t b = bulk_stream_for(opt_.device)) cudaStreamSynchronize(b);
     cudaHostUnregister(ep->shm_->flag_area());
     cudaGetLastError();
     ep->flags_registered_ = false;
@@ -1815,6 +1845,12 @@ void Worker::on_push_cts(Endpoint* ep, const FrameHeader& fh, const char* body) 
 
 int Worker::launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs, const std::vector<size_t>& lens, uint64_t* flag,
                           uint64_t flag_value, uint64_t* flag2, uint64_t flag2_value) {
+  // the process-wide stream of this device (see bulk_stream_for), with a last-CTA counter of its own: the
+  // worker's other transfers run beside these on the worker's stream
+  cudaStream_t bulk = bulk_stream_for(opt_.device);
+  void* const st = bulk ? static_cast<void*>(bulk) : stream_;
+  uint32_t* const counter = bulk ? counter_dev_ + 16 : counter_dev_;
+  bulk_used_ = bulk_used_ || bulk != nullptr;
   for (size_t i = 0; i < ptrs.size(); ++i) {
     eux_xfer_desc d{};
     d.src = ptrs[i].first;
@@ -1828,7 +1864,7 @@ int Worker::launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs
       d.flag2 = flag2;
       d.flag2_value = flag2_value;
     }
-    int rc = eux_xfer_launch(&d, counter_dev_, 0, stream_);
+    int rc = eux_xfer_launch(&d, counter, 0, st);
     if (rc != 0) return rc;
     ++stats_.kernel_launches;
   }

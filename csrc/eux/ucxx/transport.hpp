@@ -422,6 +422,7 @@ class Worker {
   uint64_t* flag_host_ = nullptr;  // mapped pinned memory written by kernels
   uint64_t* flag_dev_ = nullptr;
   uint32_t* counter_dev_ = nullptr;
+  bool bulk_used_ = false;  // this worker has put pushes on the process-wide stream of its device
   uint64_t device_seq_ = 0;
   std::deque<DeviceOp> device_ops_;
   // Small single-segment pulls wait here until the end of the current pass of the loop and then leave in
