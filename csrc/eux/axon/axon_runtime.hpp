@@ -40,14 +40,19 @@ class AxonRuntime {
     return worker_->RegisterEndpointSignatures(worker_name, data, size);
   }
 
-  template <class... A>
+  // Every overload of the worker, the typed ones with their template arguments included:
+  // rt.InvokeRpc<ucxx::UcxBuffer>(...), rt.RegisterFunction<ucxx::UcxBuffer>(...).
+  template <class... T, class... A>
   bool RegisterFunction(A&&... a) {
-    return worker_->RegisterFunction(std::forward<A>(a)...);
+    if constexpr (sizeof...(T) == 0) return worker_->RegisterFunction(std::forward<A>(a)...);
+    else return worker_->template RegisterFunction<T...>(std::forward<A>(a)...);
   }
-  template <class... A>
-  InvokeSender InvokeRpc(A&&... a) {
-    return worker_->InvokeRpc(std::forward<A>(a)...);
+  template <class... T, class... A>
+  auto InvokeRpc(A&&... a) {
+    if constexpr (sizeof...(T) == 0) return worker_->InvokeRpc(std::forward<A>(a)...);
+    else return worker_->template InvokeRpc<T...>(std::forward<A>(a)...);
   }
+  std::optional<AxonWorker::WorkerKey> GetWorkerKey(std::string_view worker_name) const { return worker_->GetWorkerKey(worker_name); }
 
   void SetTimeout(std::chrono::milliseconds t) { worker_->SetTimeout(t); }
   void SetRejectMessages(bool r) { worker_->SetRejectMessages(r); }

@@ -70,6 +70,62 @@ struct ClientMemoryPolicy {
   bool provider_inline = false;
 };
 
+// What a call made through the typed overloads gives the caller: the response header and the payload in the
+// form that the caller named (reference: axon/include/axon/axon_worker.hpp:985-992).
+template <class RespBufferT>
+using TypedInvokeResult = std::pair<rpc::ResponseHeaderUniquePtr, RespBufferT>;
+
+namespace detail {
+template <class T>
+concept IsMonostate = std::is_same_v<std::decay_t<T>, std::monostate>;
+template <class T>
+concept IsBuffer = std::is_same_v<std::decay_t<T>, ucxx::UcxBuffer> || std::is_same_v<std::decay_t<T>, ucxx::UcxBufferVec>;
+template <class T>
+concept IsBufferOrVariant = IsBuffer<T> || std::is_same_v<std::decay_t<T>, rpc::PayloadVariant>;
+template <class T>
+concept ValidInvokePayload = IsBufferOrVariant<T> || IsMonostate<T>;
+template <class T>
+concept ValidInvokeResponse = IsBufferOrVariant<T> || IsMonostate<T>;
+template <class T>
+concept ValidRegisterBuffer = IsBufferOrVariant<T> || IsMonostate<T>;
+// A memory policy as such, whatever it is used with.
+template <class T>
+concept IsMemoryPolicy = std::is_same_v<std::decay_t<T>, AlwaysOnHostPolicy> || std::is_same_v<std::decay_t<T>, CustomMemoryPolicy<ucxx::UcxBuffer>> ||
+                         std::is_same_v<std::decay_t<T>, CustomMemoryPolicy<ucxx::UcxBufferVec>> ||
+                         std::is_same_v<std::decay_t<T>, ReceiverMemoryPolicy<ucxx::UcxBuffer>> ||
+                         std::is_same_v<std::decay_t<T>, ReceiverMemoryPolicy<ucxx::UcxBufferVec>>;
+// ... and one that fits the buffer form it is used with: a provider of single buffers cannot serve a call that
+// wants separate buffers and the other way round; a variant or no payload goes with either.
+template <class MemPolicyT, class BufferT>
+concept ValidMemPolicyFor =
+    IsMemoryPolicy<MemPolicyT> &&
+    (std::is_same_v<std::decay_t<MemPolicyT>, AlwaysOnHostPolicy> || IsMonostate<BufferT> || std::is_same_v<std::decay_t<BufferT>, rpc::PayloadVariant> ||
+     std::is_same_v<std::decay_t<MemPolicyT>, CustomMemoryPolicy<std::decay_t<BufferT>>> ||
+     std::is_same_v<std::decay_t<MemPolicyT>, ReceiverMemoryPolicy<std::decay_t<BufferT>>>);
+template <class... Args>
+struct first_arg_is_memory_policy : std::false_type {};
+template <class A, class... Rest>
+struct first_arg_is_memory_policy<A, Rest...> : std::bool_constant<IsMemoryPolicy<A>> {};
+
+template <class BufferT, class MemPolicyT, class Erased>
+Erased erase_policy(MemPolicyT&& p) {
+  Erased out;
+  using P = std::decay_t<MemPolicyT>;
+  if constexpr (std::is_same_v<std::decay_t<BufferT>, ucxx::UcxBufferVec> && requires { out.want_vec; }) out.want_vec = true;
+  if constexpr (std::is_same_v<P, CustomMemoryPolicy<ucxx::UcxBuffer>>) {
+    out.on_host = false;
+    out.buffer_provider = std::forward<MemPolicyT>(p);
+  } else if constexpr (std::is_same_v<P, CustomMemoryPolicy<ucxx::UcxBufferVec>>) {
+    out.on_host = false;
+    out.buffer_vec_provider = std::forward<MemPolicyT>(p);
+    if constexpr (requires { out.want_vec; }) out.want_vec = true;
+  } else if constexpr (!std::is_same_v<P, AlwaysOnHostPolicy>) {  // the variant of the two
+    std::visit([&](auto& alt) { out = erase_policy<BufferT, decltype(alt), Erased>(alt); }, p);
+  }
+  return out;
+}
+}  // namespace detail
+
 class AxonWorker {
  public:
   using BypassRejectionFunction = std::function<bool(const rpc::RpcRequestHeader&)>;
@@ -109,6 +165,12 @@ class AxonWorker {
   bool RegisterEndpointSignatures(std::string_view worker_name, const void* data, size_t size);
   std::optional<rpc::RpcFunctionSignature> GetEndpointSignature(std::string_view worker_name, rpc::function_id_t id) const;
   std::optional<uint64_t> GetConnectionId(std::string_view worker_name) const;
+  // An endpoint's key: stable while the endpoint exists, never reused for another one (the slot's generation
+  // differs), and cheaper to resolve than the name (reference: axon_worker.hpp:166, 1010-1042).
+  using WorkerKey = utils::SlotKey;
+  std::optional<WorkerKey> GetWorkerKey(std::string_view worker_name) const;
+  std::optional<uint64_t> GetConnectionId(WorkerKey key) const;
+  std::optional<std::string> GetWorkerName(WorkerKey key) const;
   bool DisconnectEndpoint(std::string_view worker_name);
 
   // ---- functions (server side) ----
@@ -120,14 +182,32 @@ class AxonWorker {
     if (!dispatcher_.RegisterFunction(id, std::forward<F>(f), rpc::data::string(name))) return false;
     return AddFunctionPolicies(id, std::move(mem_policy), std::move(lc_policy));
   }
-  template <class ReceivedBufferT, class F>
-  bool RegisterFunction(rpc::function_id_t id, F&& f, const std::string& name, CustomMemoryPolicy<ReceivedBufferT> provider,
-                        MessageLifecyclePolicy lc_policy = TransientPolicy{}) {
-    ServerMemoryPolicy mp;
-    mp.on_host = false;
-    if constexpr (std::is_same_v<ReceivedBufferT, ucxx::UcxBuffer>) mp.buffer_provider = std::move(provider);
-    else mp.buffer_vec_provider = std::move(provider);
-    return RegisterFunction(id, std::forward<F>(f), name, std::move(mp), std::move(lc_policy));
+  // RegisterFunction<ReceivedBufferT[, Fn, MemPolicyT, LcT]>(id, fn, name, policy, lifecycle): the reference's
+  // parameter list (axon_worker.hpp:432-443). ReceivedBufferT names the form in which a rendezvous payload is
+  // received for the policy: UcxBuffer, UcxBufferVec, PayloadVariant (either, as the sender's metadata says)
+  // or std::monostate (the function takes no payload).
+  template <class ReceivedBufferT, class Fn, class MemPolicyT = AlwaysOnHostPolicy, class LcT = TransientPolicy>
+    requires detail::ValidRegisterBuffer<ReceivedBufferT> && detail::ValidMemPolicyFor<MemPolicyT, ReceivedBufferT> && is_message_lifecycle_policy_v<LcT> &&
+             (!std::is_convertible_v<Fn, std::string_view>)
+  bool RegisterFunction(rpc::function_id_t id, Fn&& fn, std::string_view name = {}, MemPolicyT mem_policy = AlwaysOnHostPolicy{}, LcT lc_policy = TransientPolicy{}) {
+    return RegisterFunction(id, std::forward<Fn>(fn), std::string(name), detail::erase_policy<ReceivedBufferT, MemPolicyT, ServerMemoryPolicy>(std::move(mem_policy)),
+                            MessageLifecyclePolicy(std::move(lc_policy)));
+  }
+  template <class ReceivedBufferT, class MemPolicyT = AlwaysOnHostPolicy, class LcT = TransientPolicy>
+    requires detail::ValidRegisterBuffer<ReceivedBufferT> && detail::ValidMemPolicyFor<MemPolicyT, ReceivedBufferT> && is_message_lifecycle_policy_v<LcT>
+  bool RegisterFunction(rpc::function_id_t id, std::string_view name, const rpc::data::vector<rpc::ParamType>& param_types,
+                        const rpc::data::vector<rpc::ParamType>& return_types, rpc::PayloadType input_payload_type, rpc::PayloadType return_payload_type,
+                        rpc::DynamicAsyncRpcFunction&& fn, MemPolicyT mem_policy = AlwaysOnHostPolicy{}, LcT lc_policy = TransientPolicy{}) {
+    return RegisterFunction(id, std::string(name), param_types, return_types, input_payload_type, return_payload_type, std::move(fn),
+                            detail::erase_policy<ReceivedBufferT, MemPolicyT, ServerMemoryPolicy>(std::move(mem_policy)), MessageLifecyclePolicy(std::move(lc_policy)));
+  }
+  template <class ReceivedBufferT, class LcT>
+    requires detail::ValidRegisterBuffer<ReceivedBufferT> && is_message_lifecycle_policy_v<LcT> && (!detail::IsMemoryPolicy<LcT>)
+  bool RegisterFunction(rpc::function_id_t id, std::string_view name, const rpc::data::vector<rpc::ParamType>& param_types,
+                        const rpc::data::vector<rpc::ParamType>& return_types, rpc::PayloadType input_payload_type, rpc::PayloadType return_payload_type,
+                        rpc::DynamicAsyncRpcFunction&& fn, LcT lc_policy) {
+    return RegisterFunction<ReceivedBufferT>(id, name, param_types, return_types, input_payload_type, return_payload_type, std::move(fn), AlwaysOnHostPolicy{},
+                                             std::move(lc_policy));
   }
   // Dynamic registration: explicit signature, type-erased callable.
   bool RegisterFunction(rpc::function_id_t id, const std::string& name, const rpc::data::vector<rpc::ParamType>& param_types,
@@ -151,8 +231,76 @@ class AxonWorker {
     }
   }
   // Dynamic: a prepared header (its request id and clock are assigned here) and an optional payload.
-  InvokeSender InvokeRpc(std::string_view worker_name, rpc::RpcRequestHeader&& header, rpc::PayloadVariant&& payload = {},
-                         ClientMemoryPolicy mem_policy = {});
+  InvokeSender InvokeRpc(std::string_view worker_name, rpc::RpcRequestHeader&& header, rpc::PayloadVariant&& payload, ClientMemoryPolicy mem_policy);
+  InvokeSender InvokeRpc(WorkerKey worker_key, rpc::RpcRequestHeader&& header, rpc::PayloadVariant&& payload, ClientMemoryPolicy mem_policy);
+
+  // ---- calls, typed (the reference's template parameter lists over the calls above) ----
+  // InvokeRpc<RespBufferT[, MemPolicyT]>(name | key, session, function, workflow[, policy], args...): arguments
+  // packed as above; completes with {unique_ptr<RpcResponseHeader>, RespBufferT}. RespBufferT is UcxBuffer,
+  // UcxBufferVec, PayloadVariant or std::monostate (payload dropped); the policy is AlwaysOnHostPolicy, a
+  // CustomMemoryPolicy<RespBufferT> or the variant of both. A response whose payload has another form than
+  // the one named ends the call with INVALID_ARGUMENT. Errors arrive as in the untyped calls, as an exception
+  // that carries the status (reference: axon_worker.hpp:300-378).
+  template <class RespBufferT, class MemPolicyT, class... Args>
+    requires detail::ValidInvokeResponse<RespBufferT> && detail::ValidMemPolicyFor<MemPolicyT, RespBufferT>
+  auto InvokeRpc(std::string_view worker_name, rpc::session_id_t session, rpc::function_id_t function, rpc::utils::workflow_id_t workflow,
+                 MemPolicyT mem_policy, Args&&... args) {
+    return Typed<RespBufferT>(InvokeRpc(worker_name, session, function, workflow,
+                                        detail::erase_policy<RespBufferT, MemPolicyT, ClientMemoryPolicy>(std::move(mem_policy)), std::forward<Args>(args)...));
+  }
+  template <class RespBufferT, class... Args>
+    requires detail::ValidInvokeResponse<RespBufferT> && (!detail::first_arg_is_memory_policy<std::decay_t<Args>...>::value)
+  auto InvokeRpc(std::string_view worker_name, rpc::session_id_t session, rpc::function_id_t function, rpc::utils::workflow_id_t workflow,
+                 Args&&... args) {
+    return InvokeRpc<RespBufferT>(worker_name, session, function, workflow, AlwaysOnHostPolicy{}, std::forward<Args>(args)...);
+  }
+  template <class RespBufferT, class MemPolicyT, class... Args>
+    requires detail::ValidInvokeResponse<RespBufferT> && detail::ValidMemPolicyFor<MemPolicyT, RespBufferT>
+  auto InvokeRpc(WorkerKey worker_key, rpc::session_id_t session, rpc::function_id_t function, rpc::utils::workflow_id_t workflow,
+                 MemPolicyT mem_policy, Args&&... args) {
+    rpc::RpcRequestBuilderOptions opt{session, rpc::request_id_t{0}, function, {}, workflow};
+    auto policy = detail::erase_policy<RespBufferT, MemPolicyT, ClientMemoryPolicy>(std::move(mem_policy));
+    if constexpr (rpc::payload_finder<Args...>::count == 1) {
+      auto [header, payload] = rpc::RpcRequestBuilder{}.PrepareRequest(opt, std::forward<Args>(args)...);
+      return Typed<RespBufferT>(InvokeRpc(worker_key, std::move(header), rpc::PayloadVariant(std::move(payload)), std::move(policy)));
+    } else {
+      auto header = rpc::RpcRequestBuilder{}.PrepareRequest(opt, std::forward<Args>(args)...);
+      return Typed<RespBufferT>(InvokeRpc(worker_key, std::move(header), rpc::PayloadVariant{}, std::move(policy)));
+    }
+  }
+  template <class RespBufferT, class... Args>
+    requires detail::ValidInvokeResponse<RespBufferT> && (!detail::first_arg_is_memory_policy<std::decay_t<Args>...>::value)
+  auto InvokeRpc(WorkerKey worker_key, rpc::session_id_t session, rpc::function_id_t function, rpc::utils::workflow_id_t workflow, Args&&... args) {
+    return InvokeRpc<RespBufferT>(worker_key, session, function, workflow, AlwaysOnHostPolicy{}, std::forward<Args>(args)...);
+  }
+  // InvokeRpc<PayloadT, RespBufferT, MemPolicyT>(name | key, header, payload | optional<payload>, policy): a
+  // prepared header (reference: axon_worker.hpp:381-429).
+  template <class PayloadT = std::monostate, class RespBufferT = std::monostate, class MemPolicyT = AlwaysOnHostPolicy>
+    requires detail::ValidInvokePayload<PayloadT> && detail::ValidInvokeResponse<RespBufferT> && detail::ValidMemPolicyFor<MemPolicyT, RespBufferT>
+  auto InvokeRpc(std::string_view worker_name, rpc::RpcRequestHeader&& header, std::optional<PayloadT>&& payload = std::nullopt,
+                 MemPolicyT mem_policy = AlwaysOnHostPolicy{}) {
+    return Typed<RespBufferT>(InvokeRpc(worker_name, std::move(header), ErasePayload(std::move(payload)),
+                                        detail::erase_policy<RespBufferT, MemPolicyT, ClientMemoryPolicy>(std::move(mem_policy))));
+  }
+  template <class PayloadT, class RespBufferT = std::monostate, class MemPolicyT = AlwaysOnHostPolicy>
+    requires detail::ValidInvokePayload<PayloadT> && (!detail::IsMonostate<PayloadT>) && detail::ValidInvokeResponse<RespBufferT> &&
+             detail::ValidMemPolicyFor<MemPolicyT, RespBufferT>
+  auto InvokeRpc(std::string_view worker_name, rpc::RpcRequestHeader&& header, PayloadT&& payload, MemPolicyT mem_policy = AlwaysOnHostPolicy{}) {
+    return InvokeRpc<PayloadT, RespBufferT, MemPolicyT>(worker_name, std::move(header), std::optional<PayloadT>(std::move(payload)), std::move(mem_policy));
+  }
+  template <class PayloadT = std::monostate, class RespBufferT = std::monostate, class MemPolicyT = AlwaysOnHostPolicy>
+    requires detail::ValidInvokePayload<PayloadT> && detail::ValidInvokeResponse<RespBufferT> && detail::ValidMemPolicyFor<MemPolicyT, RespBufferT>
+  auto InvokeRpc(WorkerKey worker_key, rpc::RpcRequestHeader&& header, std::optional<PayloadT>&& payload = std::nullopt,
+                 MemPolicyT mem_policy = AlwaysOnHostPolicy{}) {
+    return Typed<RespBufferT>(InvokeRpc(worker_key, std::move(header), ErasePayload(std::move(payload)),
+                                        detail::erase_policy<RespBufferT, MemPolicyT, ClientMemoryPolicy>(std::move(mem_policy))));
+  }
+  template <class PayloadT, class RespBufferT = std::monostate, class MemPolicyT = AlwaysOnHostPolicy>
+    requires detail::ValidInvokePayload<PayloadT> && (!detail::IsMonostate<PayloadT>) && detail::ValidInvokeResponse<RespBufferT> &&
+             detail::ValidMemPolicyFor<MemPolicyT, RespBufferT>
+  auto InvokeRpc(WorkerKey worker_key, rpc::RpcRequestHeader&& header, PayloadT&& payload, MemPolicyT mem_policy = AlwaysOnHostPolicy{}) {
+    return InvokeRpc<PayloadT, RespBufferT, MemPolicyT>(worker_key, std::move(header), std::optional<PayloadT>(std::move(payload)), std::move(mem_policy));
+  }
 
   // ---- knobs ----
   void SetTimeout(std::chrono::milliseconds t) { timeout_ms_.store(t.count()); }
@@ -209,6 +357,44 @@ class AxonWorker {
   struct invoke_sender;
   friend class InvokeOpState;
 
+  InvokeSender InvokeOnConnection(std::optional<uint64_t> conn, std::string whom, rpc::RpcRequestHeader&& header, rpc::PayloadVariant&& payload,
+                                  ClientMemoryPolicy mem_policy);
+  template <class PayloadT>
+  static rpc::PayloadVariant ErasePayload(std::optional<PayloadT>&& p) {
+    if constexpr (detail::IsMonostate<PayloadT>) return {};
+    else if (p) return rpc::PayloadVariant(std::move(*p));
+    else return {};
+  }
+  // The untyped result in the form the caller named.
+  template <class RespBufferT>
+  TypedInvokeResult<RespBufferT> ToTyped(InvokeResult&& r) {
+    auto header = std::make_unique<rpc::RpcResponseHeader>(std::move(r.header));
+    if constexpr (detail::IsMonostate<RespBufferT>) {
+      return {std::move(header), std::monostate{}};
+    } else if constexpr (std::is_same_v<RespBufferT, rpc::PayloadVariant>) {
+      return {std::move(header), std::move(r.payload)};
+    } else {
+      if (auto* b = std::get_if<RespBufferT>(&r.payload)) return {std::move(header), std::move(*b)};
+      if constexpr (std::is_same_v<RespBufferT, ucxx::UcxBufferVec>) {
+        // a small response arrives in one piece: cut it where the header's tensor metadata says
+        if (auto* one = std::get_if<ucxx::UcxBuffer>(&r.payload)) {
+          std::vector<size_t> sizes;
+          size_t sum = 0;
+          for (auto& m : utils::GetTensorMetas(header->results)) sum += sizes.emplace_back(rpc::utils::CalculateTensorSize(m));
+          if (sizes.empty() || sum != one->size()) sizes.assign(1, one->size());
+          return {std::move(header), std::move(*one).to_buffer_vec(sizes)};
+        }
+      }
+      if (!std::holds_alternative<std::monostate>(r.payload))
+        throw std::system_error(rpc::make_error_code(rpc::RpcErrc::INVALID_ARGUMENT), "the response payload has another form than the one asked for");
+      if constexpr (std::is_same_v<RespBufferT, ucxx::UcxBuffer>) return {std::move(header), ucxx::UcxBuffer(*mr_, ucx_memory_type::HOST, 0)};
+      else return {std::move(header), ucxx::UcxBufferVec(*mr_, ucx_memory_type::HOST, std::vector<size_t>{})};
+    }
+  }
+  template <class RespBufferT>
+  auto Typed(InvokeSender&& s) {
+    return exec::then(std::move(s), [this](InvokeResult&& r) { return ToTyped<RespBufferT>(std::move(r)); });
+  }
   bool AddFunctionPolicies(rpc::function_id_t id, ServerMemoryPolicy mem, MessageLifecyclePolicy lc);
   std::optional<FunctionPolicies> FindPolicies(rpc::function_id_t id) const;
   rpc::utils::HybridLogicalClock TickHlc();

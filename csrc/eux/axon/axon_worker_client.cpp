@@ -66,6 +66,23 @@ std::optional<uint64_t> AxonWorker::GetConnectionId(std::string_view worker_name
   return *r;
 }
 
+std::optional<AxonWorker::WorkerKey> AxonWorker::GetWorkerKey(std::string_view worker_name) const {
+  std::lock_guard lk(endpoints_mu_);
+  auto it = endpoint_by_name_.find(std::string(worker_name));
+  if (it == endpoint_by_name_.end()) return std::nullopt;
+  return it->second;
+}
+
+std::optional<uint64_t> AxonWorker::GetConnectionId(WorkerKey key) const {
+  auto r = endpoints_.access(key, [](const RemoteEndpoint& e) { return e.conn_id; });
+  if (!r || *r == 0) return std::nullopt;
+  return *r;
+}
+
+std::optional<std::string> AxonWorker::GetWorkerName(WorkerKey key) const {
+  return endpoints_.access(key, [](const RemoteEndpoint& e) { return e.name; });
+}
+
 bool AxonWorker::DisconnectEndpoint(std::string_view worker_name) {
   std::optional<uint64_t> conn = GetConnectionId(worker_name);
   {
@@ -232,12 +249,20 @@ struct AxonWorker::invoke_sender {
 };
 
 InvokeSender AxonWorker::InvokeRpc(std::string_view worker_name, RpcRequestHeader&& header, PayloadVariant&& payload, ClientMemoryPolicy mem_policy) {
+  return InvokeOnConnection(GetConnectionId(worker_name), std::string(worker_name), std::move(header), std::move(payload), std::move(mem_policy));
+}
+
+InvokeSender AxonWorker::InvokeRpc(WorkerKey worker_key, RpcRequestHeader&& header, PayloadVariant&& payload, ClientMemoryPolicy mem_policy) {
+  return InvokeOnConnection(GetConnectionId(worker_key), "key " + std::to_string(worker_key.index) + "/" + std::to_string(worker_key.generation),
+                            std::move(header), std::move(payload), std::move(mem_policy));
+}
+
+InvokeSender AxonWorker::InvokeOnConnection(std::optional<uint64_t> conn, std::string whom, RpcRequestHeader&& header, PayloadVariant&& payload,
+                                            ClientMemoryPolicy mem_policy) {
   ucxx::NvtxRange range("axon.client.invoke");
   if (!client_running_.load() || !client_ctx_)
     return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::WorkerStartFailed), "the client is not running"));
-  auto conn = GetConnectionId(worker_name);
-  if (!conn)
-    return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::WorkerNotFound), "no endpoint named " + std::string(worker_name)));
+  if (!conn) return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::WorkerNotFound), "no endpoint named " + whom));
   auto call = std::make_shared<ClientCall>();
   call->conn_id = *conn;
   header.request_id = rpc::request_id_t{next_request_id_.fetch_add(1)};

@@ -72,15 +72,19 @@ decltype(auto) extract_arg(const RpcRequestHeader& req, RpcContextPtr ctx, const
     if (!p) throw RpcException(RpcErrc::INVALID_ARGUMENT, "the call needs a payload of another kind than the one supplied");
     if constexpr (std::is_lvalue_reference_v<T>) {
       return (*p);
-    } else {  // by value: take it over
+    } else {  // by value or by rvalue reference: the function takes it over
       if (!ctx.movable) throw RpcException(RpcErrc::INVALID_ARGUMENT, "the function takes its payload by value; dispatch it with DispatchMove");
-      return D(std::move(*p));
+      // `T&&` must refer to the caller's object, which outlives the call: a temporary made here would be
+      // gone before the function runs
+      if constexpr (std::is_rvalue_reference_v<T>) return std::move(*p);
+      else return D(std::move(*p));
     }
   } else if constexpr (is_payload_variant_v<D>) {
     if (!ctx.ptr) throw RpcException(RpcErrc::INVALID_ARGUMENT, "the call needs a payload");
     if (ctx.is_variant) {
       auto* v = static_cast<PayloadVariant*>(ctx.ptr);
       if constexpr (std::is_lvalue_reference_v<T>) return (*v);
+      else if constexpr (std::is_rvalue_reference_v<T>) return std::move(*v);
       else return PayloadVariant(std::move(*v));
     } else {
       throw RpcException(RpcErrc::INVALID_ARGUMENT, "the function takes a PayloadVariant; pass one");

@@ -3,6 +3,8 @@
 // wire contract (reference: rpc_core/rpc_types.hpp:45-454).
 #pragma once
 
+#include <memory>
+
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -255,5 +257,9 @@ struct RpcResponseHeader : RpcMessageAccessor<RpcResponseHeader> {
   const workflow_id_t& GetWorkflowId() const { return workflow_id; }
   workflow_id_t& GetWorkflowId() { return workflow_id; }
 };
+
+// Owning pointers to parsed headers, as handed to callers of the typed invocation API.
+using RequestHeaderUniquePtr = std::unique_ptr<RpcRequestHeader>;
+using ResponseHeaderUniquePtr = std::unique_ptr<RpcResponseHeader>;
 
 }  // namespace eux::rpc

@@ -489,6 +489,11 @@ EUX_TEST(injected_faults_end_as_errors) {
 }
 
 EUX_TEST(forked_processes_echo) {
+#if defined(__SANITIZE_THREAD__)
+  // ThreadSanitizer's runtime does not let a forked child of a process that has had threads start threads
+  // of its own, which a worker needs; the case runs in every other build.
+  return;
+#endif
   int addr_pipe[2], ctl_pipe[2];
   CHECK(pipe(addr_pipe) == 0 && pipe(ctl_pipe) == 0);
   pid_t pid = fork();

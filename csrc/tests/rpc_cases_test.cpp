@@ -142,6 +142,33 @@ EUX_TEST(payload_by_reference_is_seen_in_place) {
   CHECK(d.GetSignature(function_id_t{9})->input_payload_type == PayloadType::UCX_BUFFER);
 }
 
+EUX_TEST(payload_by_rvalue_reference_and_by_value_is_handed_over_whole) {
+  // both forms take the payload over; the function must see the caller's bytes, not a moved-from temporary
+  DefaultUcxMemoryResourceManager mr;
+  RpcDispatcher d("svc");
+  d.RegisterFunction(function_id_t{1}, [](UcxBuffer&& b) { return std::tuple<uint64_t, UcxBuffer>(b.size(), std::move(b)); }, data::string("take_rref"));
+  d.RegisterFunction(function_id_t{2}, [](UcxBuffer b) { return std::tuple<uint64_t, UcxBuffer>(b.size(), std::move(b)); }, data::string("take_value"));
+  d.RegisterFunction(function_id_t{3}, [](const RpcRequestHeader&, PayloadVariant&& v) { return uint64_t(std::get<UcxBuffer>(v).size()); }, data::string("take_variant"));
+  for (uint32_t id : {1u, 2u}) {
+    UcxBuffer buf(mr, ucx_memory_type::HOST, 24);
+    std::memset(buf.data(), int(id), 24);
+    auto r = d.DispatchMove(RpcRequestBuilder{}.PrepareRequest(opt(id)), std::move(buf));
+    CHECK(r.header.status.ok());
+    CHECK_EQ(r.header.GetPrimitive<uint64_t>(0), uint64_t(24));
+    CHECK_EQ(std::get<UcxBuffer>(r.payload).size(), size_t(24));
+    CHECK_EQ(static_cast<unsigned char*>(std::get<UcxBuffer>(r.payload).data())[23], id);
+  }
+  PayloadVariant pv(UcxBuffer(mr, ucx_memory_type::HOST, 5));
+  auto r3 = d.DispatchMove(RpcRequestBuilder{}.PrepareRequest(opt(3)), std::move(pv));
+  CHECK(r3.header.status.ok());
+  CHECK_EQ(r3.header.GetPrimitive<uint64_t>(0), uint64_t(5));
+  // without permission to move, a taking function is refused instead of being handed a copy
+  UcxBuffer keep(mr, ucx_memory_type::HOST, 8);
+  auto refused = d.Dispatch(RpcRequestBuilder{}.PrepareRequest(opt(1)), keep);
+  CHECK_EQ(refused.header.status.value, int(RpcErrc::INVALID_ARGUMENT));
+  CHECK_EQ(keep.size(), size_t(8));
+}
+
 EUX_TEST(buffer_vector_payload_and_returned_buffer_vector) {
   DefaultUcxMemoryResourceManager mr;
   RpcDispatcher d("svc");

@@ -5,7 +5,7 @@ from pathlib import Path
 import pytest
 
 LIB = Path(__file__).resolve().parent.parent / "execution_ucx_b200" / "_lib"
-BINARIES = ["eux_exec_test", "eux_transport_test", "eux_rpc_cases_test", "eux_cancel_test", "eux_am_context_test", "eux_data_test", "eux_rpc_test", "eux_axon_test", "eux_storage_test"]
+BINARIES = ["eux_exec_test", "eux_transport_test", "eux_rpc_cases_test", "eux_cancel_test", "eux_am_context_test", "eux_data_test", "eux_rpc_test", "eux_axon_test", "eux_axon_typed_test", "eux_storage_test"]
 
 
 @pytest.mark.parametrize("name", BINARIES)
