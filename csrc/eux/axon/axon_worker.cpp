@@ -114,6 +114,8 @@ ucxx::transport::Worker::Stats AxonWorker::GetTransportStats() const {
     t.device_pushes += s.device_pushes;
     t.device_push_recv += s.device_push_recv;
     t.kernel_launches += s.kernel_launches;
+    t.vmm_fds_sent += s.vmm_fds_sent;
+    t.vmm_fds_recv += s.vmm_fds_recv;
   }
   return t;
 }

@@ -226,6 +226,8 @@ class PyAxonRuntime {
     d["device_pushes"] = s.device_pushes;
     d["device_push_recv"] = s.device_push_recv;
     d["kernel_launches"] = s.kernel_launches;
+    d["vmm_fds_sent"] = s.vmm_fds_sent;
+    d["vmm_fds_recv"] = s.vmm_fds_recv;
     return d;
   }
   size_t stored_request_count() { return rt_->worker().GetStorage().size(); }

@@ -1,7 +1,11 @@
 #include "eux/ucxx/cuda/ucx_cuda_memory_manager.hpp"
 
+#include <cuda.h>  // types of the virtual memory management calls; the functions come through the runtime's entry-point lookup
 #include <cuda_runtime_api.h>
 #include <unistd.h>
+
+#include <algorithm>
+#include <atomic>
 
 #include <cstring>
 #include <new>
@@ -54,6 +58,49 @@ bool buffer_id_of(const void* ptr, uint64_t* id) {
   *id = v;
   return true;
 }
+
+// A driver function by name, through the runtime (no link-time libcuda dependency); null where there is no driver.
+template <class Fn>
+Fn driver_fn(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+    cudaGetLastError();
+    p = nullptr;
+  }
+  return reinterpret_cast<Fn>(p);
+}
+// The virtual memory management calls used to pass cuMemCreate allocations between processes.
+struct VmmApi {
+  CUresult (*retain)(CUmemGenericAllocationHandle*, void*) = nullptr;
+  CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*export_handle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+  CUresult (*import_handle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*address_free)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  bool ok = false;
+};
+const VmmApi& vmm_api() {
+  static const VmmApi api = [] {
+    VmmApi a;
+    a.retain = driver_fn<decltype(a.retain)>("cuMemRetainAllocationHandle");
+    a.release = driver_fn<decltype(a.release)>("cuMemRelease");
+    a.export_handle = driver_fn<decltype(a.export_handle)>("cuMemExportToShareableHandle");
+    a.import_handle = driver_fn<decltype(a.import_handle)>("cuMemImportFromShareableHandle");
+    a.reserve = driver_fn<decltype(a.reserve)>("cuMemAddressReserve");
+    a.address_free = driver_fn<decltype(a.address_free)>("cuMemAddressFree");
+    a.map = driver_fn<decltype(a.map)>("cuMemMap");
+    a.unmap = driver_fn<decltype(a.unmap)>("cuMemUnmap");
+    a.set_access = driver_fn<decltype(a.set_access)>("cuMemSetAccess");
+    a.ok = a.retain && a.release && a.export_handle && a.import_handle && a.reserve && a.address_free && a.map && a.unmap && a.set_access;
+    return a;
+  }();
+  return api;
+}
+std::atomic<uint64_t> g_next_vmm_id{1};
 
 // Allocation and release run on whatever thread asks (a pool thread, the caller's thread): the
 // manager's device becomes current for the duration, whatever that thread had before.
@@ -278,7 +325,9 @@ const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::
     if (r->buffer_id && buffer_id_of(ptr, &id) && id == r->buffer_id) return r;  // the very allocation that was registered
     void* base = nullptr;
     size_t size = 0;
-    if (address_range(ptr, &base, &size) && base == r->base && size == r->size) {
+    if (r->kind == kRegionVmm) {
+      // no handle to compare: without the driver's id to go by, register it again under a new number
+    } else if (address_range(ptr, &base, &size) && base == r->base && size == r->size) {
       cudaIpcMemHandle_t h;
       if (cudaIpcGetMemHandle(&h, base) == cudaSuccess) {
         if (std::memcmp(&h, r->handle, 64) == 0 && r->exportable) return r;
@@ -305,6 +354,20 @@ const UcxCudaMemoryResourceManager::Registration* UcxCudaMemoryResourceManager::
     reg.exportable = true;
   } else {
     cudaGetLastError();  // clear; the region can still be used inside this process
+    // Not a cudaMalloc allocation. If it is a cuMemCreate allocation that was made shareable as a file
+    // descriptor, that is how it travels (a trial export tells; the descriptor itself is made per peer).
+    const VmmApi& api = vmm_api();
+    CUmemGenericAllocationHandle h = 0;
+    if (api.ok && api.retain(&h, base) == CUDA_SUCCESS) {
+      int fd = -1;
+      if (api.export_handle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) == CUDA_SUCCESS && fd >= 0) {
+        ::close(fd);
+        reg.kind = kRegionVmm;
+        reg.vmm_id = g_next_vmm_id.fetch_add(1);
+        reg.exportable = true;
+      }
+      api.release(h);
+    }
   }
   std::lock_guard lk(mu_);
   auto [it, ok] = regs_.emplace(reinterpret_cast<uintptr_t>(base), reg);
@@ -333,8 +396,120 @@ bool UcxCudaMemoryResourceManager::export_region(const void* ptr, size_t len, Pe
   out->offset = p - b;
   out->length = len;
   out->exportable = r->exportable;
-  std::memcpy(out->handle, r->handle, 64);
+  out->kind = r->kind;
+  if (r->kind == kRegionVmm) {
+    PeerVmmRef ref{r->vmm_id, r->size};
+    std::memset(out->handle, 0, 64);
+    std::memcpy(out->handle, &ref, sizeof(ref));
+  } else {
+    std::memcpy(out->handle, r->handle, 64);
+  }
   return true;
+}
+
+bool UcxCudaMemoryResourceManager::export_regions(const void* ptr, size_t len, std::vector<PeerRegionDesc>* out) {
+  const size_t before = out->size();
+  const char* p = static_cast<const char*>(ptr);
+  size_t left = len;
+  do {
+    const Registration* r = register_memory(p, left);
+    if (!r) {
+      out->resize(before);
+      return false;
+    }
+    const auto a = reinterpret_cast<uintptr_t>(p), b = reinterpret_cast<uintptr_t>(r->base);
+    const size_t here = std::min<size_t>(left, b + r->size - a);
+    PeerRegionDesc d;
+    if (!export_region(p, here, &d)) {
+      out->resize(before);
+      return false;
+    }
+    out->push_back(d);
+    p += here;
+    left -= here;
+  } while (left > 0);
+  return true;
+}
+
+int UcxCudaMemoryResourceManager::export_vmm_fd(const PeerRegionDesc& d) {
+  const VmmApi& api = vmm_api();
+  if (!api.ok || d.kind != kRegionVmm || d.pid != static_cast<uint32_t>(getpid())) return -1;
+  PeerVmmRef ref;
+  std::memcpy(&ref, d.handle, sizeof(ref));
+  const Registration* r = find_registration(reinterpret_cast<const void*>(d.base));
+  if (!r || r->kind != kRegionVmm || r->vmm_id != ref.id) return -1;
+  CUmemGenericAllocationHandle h = 0;
+  if (api.retain(&h, r->base) != CUDA_SUCCESS) return -1;
+  int fd = -1;
+  if (api.export_handle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS) fd = -1;
+  api.release(h);
+  return fd;
+}
+
+bool UcxCudaMemoryResourceManager::import_vmm(uint64_t owner, const PeerVmmRef& ref, int fd) {
+  const VmmApi& api = vmm_api();
+  if (!api.ok || fd < 0 || ref.size == 0 || ref.size > (uint64_t(1) << 40)) return false;
+  std::lock_guard lk(mu_);
+  auto key = std::make_pair(owner, ref.id);
+  if (vmm_imports_.count(key)) return true;
+  DeviceGuard on_device(opt_.device);
+  cudaFree(nullptr);  // the calls below want a current context on this thread
+  VmmImported m;
+  m.size = ref.size;
+  CUmemGenericAllocationHandle h = 0;
+  if (api.import_handle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) != CUDA_SUCCESS) return false;
+  m.handle = h;
+  CUdeviceptr va = 0;
+  if (api.reserve(&va, ref.size, 0, 0, 0) != CUDA_SUCCESS) {
+    api.release(h);
+    return false;
+  }
+  // a size that is not the allocation's own (a peer that lies about it) fails here, not in a kernel
+  if (api.map(va, ref.size, 0, h, 0) != CUDA_SUCCESS) {
+    api.address_free(va, ref.size);
+    api.release(h);
+    return false;
+  }
+  CUmemAccessDesc acc{};
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = opt_.device;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  if (api.set_access(va, ref.size, &acc, 1) != CUDA_SUCCESS) {
+    api.unmap(va, ref.size);
+    api.address_free(va, ref.size);
+    api.release(h);
+    return false;
+  }
+  m.va = va;
+  vmm_imports_.emplace(key, m);
+  return true;
+}
+
+void UcxCudaMemoryResourceManager::unmap_vmm(VmmImported& m) {
+  const VmmApi& api = vmm_api();
+  if (!api.ok || !m.va) return;
+  api.unmap(m.va, m.size);
+  api.address_free(m.va, m.size);
+  api.release(m.handle);
+  m.va = 0;
+}
+
+void UcxCudaMemoryResourceManager::release_vmm(uint64_t owner, uint64_t id) {
+  std::lock_guard lk(mu_);
+  auto it = vmm_imports_.find({owner, id});
+  if (it == vmm_imports_.end()) return;
+  DeviceGuard on_device(opt_.device);
+  unmap_vmm(it->second);
+  vmm_imports_.erase(it);
+}
+
+void UcxCudaMemoryResourceManager::release_vmm_of(uint64_t owner) {
+  std::lock_guard lk(mu_);
+  DeviceGuard on_device(opt_.device);
+  for (auto it = vmm_imports_.lower_bound({owner, 0}); it != vmm_imports_.end() && it->first.first == owner;) {
+    unmap_vmm(it->second);
+    it = vmm_imports_.erase(it);
+  }
 }
 
 namespace {
@@ -348,7 +523,7 @@ bool range_is_mapped(const void* p, uint64_t len) {
 }
 }  // namespace
 
-void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d, bool same_process) {
+void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d, bool same_process, uint64_t owner) {
   if (d.offset + d.length < d.offset) return nullptr;  // wraps
   if (same_process) {
     if (d.device != opt_.device) {
@@ -369,6 +544,16 @@ void* UcxCudaMemoryResourceManager::import_region(const PeerRegionDesc& d, bool 
   // A descriptor that names this process's pid without the caller vouching for it comes from another
   // pid namespace or host (or is forged): its addresses mean nothing here. The IPC handle decides.
   if (!d.exportable) return nullptr;
+  if (d.kind == kRegionVmm) {
+    PeerVmmRef ref;
+    std::memcpy(&ref, d.handle, sizeof(ref));
+    std::lock_guard lk(mu_);
+    auto it = vmm_imports_.find({owner, ref.id});
+    if (it == vmm_imports_.end()) return nullptr;  // its file descriptor never arrived
+    if (d.length > it->second.size || d.offset > it->second.size - d.length) return nullptr;
+    return reinterpret_cast<void*>(it->second.va + d.offset);
+  }
+  if (d.kind != kRegionIpc) return nullptr;
   std::lock_guard lk(mu_);
   DeviceGuard on_device(opt_.device);
   ImportKey key{d.pid, d.base};
@@ -403,6 +588,8 @@ void UcxCudaMemoryResourceManager::release_imports() {
   DeviceGuard on_device(opt_.device);
   for (auto& [k, p] : imports_) cudaIpcCloseMemHandle(p.mapped);
   imports_.clear();
+  for (auto& [k, m] : vmm_imports_) unmap_vmm(m);
+  vmm_imports_.clear();
 }
 
 size_t UcxCudaMemoryResourceManager::pooled_bytes() const {

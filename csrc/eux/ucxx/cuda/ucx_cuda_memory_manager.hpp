@@ -10,6 +10,10 @@
 //   * register_memory() records an allocation (found from any interior pointer)
 //     and export_region() produces a PeerRegionDesc carrying its CUDA IPC
 //     handle, which a peer process opens once with import_region() and caches;
+//   * memory that somebody else made with cuMemCreate and mapped into a reserved address range (a tensor
+//     library's "expandable segments") has no CUDA IPC handle; each physical allocation under it is
+//     exported as a POSIX file descriptor instead (export_vmm_fd), which the transport passes to the peer
+//     over a Unix socket, and the peer maps it into a range of its own (import_vmm);
 //   * the same descriptor works inside one process (the address is used as is).
 #pragma once
 
@@ -32,8 +36,17 @@ struct PeerRegionDesc {
   uint64_t offset = 0;  // start of the range inside the allocation
   uint64_t length = 0;
   uint8_t exportable = 0;
-  uint8_t reserved[7] = {0};
-  unsigned char handle[64] = {0};  // cudaIpcMemHandle_t of the allocation
+  uint8_t kind = 0;  // kRegionIpc: `handle` is a cudaIpcMemHandle_t; kRegionVmm: it starts with a PeerVmmRef
+  uint8_t reserved[6] = {0};
+  unsigned char handle[64] = {0};
+};
+constexpr uint8_t kRegionIpc = 0, kRegionVmm = 1;
+// What stands for the handle of a cuMemCreate allocation: the owner's number for it (never reused within
+// the owner's process) and its size. The file descriptor itself cannot travel in a message; the owner
+// passes it once per peer over a Unix socket, labelled with the same number.
+struct PeerVmmRef {
+  uint64_t id = 0;
+  uint64_t size = 0;
 };
 static_assert(sizeof(PeerRegionDesc) == 104, "PeerRegionDesc travels on the wire");
 
@@ -55,6 +68,8 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
     bool exportable = false;
     unsigned char handle[64] = {0};
     uint64_t buffer_id = 0;  // the driver's id of the allocation (0: unknown), to recognise it again cheaply
+    uint8_t kind = kRegionIpc;
+    uint64_t vmm_id = 0;     // kRegionVmm: this process's number for the physical allocation
   };
 
   UcxCudaMemoryResourceManager();
@@ -72,12 +87,28 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
   const Registration* find_registration(const void* ptr) const;
   // Describe [ptr, ptr+len) for a peer; registers the allocation on first use.
   bool export_region(const void* ptr, size_t len, PeerRegionDesc* out);
+  // The same for a range that may run across several allocations that lie back to back in the address
+  // space (a large tensor in expandable segments is backed by one cuMemCreate allocation per 20 MiB):
+  // one descriptor per allocation touched, appended to `out`. False (and `out` as it was) when any part
+  // of the range is unknown to the driver.
+  bool export_regions(const void* ptr, size_t len, std::vector<PeerRegionDesc>* out);
+  // A new file descriptor for the cuMemCreate allocation described by a kRegionVmm descriptor of this
+  // process (the caller passes it on and closes it), or -1.
+  int export_vmm_fd(const PeerRegionDesc& d);
+  // Map a peer's cuMemCreate allocation, received as a file descriptor (not closed here), and remember it
+  // under (owner, id). `owner` is the caller's name for the peer (the transport uses the peer worker's
+  // random id). True when it is mapped (now or before).
+  bool import_vmm(uint64_t owner, const PeerVmmRef& ref, int fd);
+  // Forget one mapping of that owner (it said that the allocation is gone), or all of them.
+  void release_vmm(uint64_t owner, uint64_t id);
+  void release_vmm_of(uint64_t owner);
   // Map a peer's region into this process (cached per owner pid + allocation); nullptr on failure.
   // `same_process` is the caller's own knowledge that the region's owner lives in this process (the
   // transport derives it from its registry of live workers, never from the descriptor): only then
   // is the descriptor's address used as it is, and only after the driver confirmed that the whole
   // range lies inside one allocation of this process. A mapped region is checked the same way.
-  void* import_region(const PeerRegionDesc& d, bool same_process = false);
+  // kRegionVmm descriptors of another process are looked up among the mappings made by import_vmm under `owner`.
+  void* import_region(const PeerRegionDesc& d, bool same_process = false, uint64_t owner = 0);
   void release_imports();
 
   int device() const { return opt_.device; }
@@ -110,6 +141,13 @@ class UcxCudaMemoryResourceManager : public UcxMemoryResourceManager {
     unsigned char handle[64] = {0};  // the handle this mapping was opened with
   };
   std::map<ImportKey, Imported> imports_;
+  struct VmmImported {
+    uint64_t va = 0;
+    uint64_t size = 0;
+    uint64_t handle = 0;  // CUmemGenericAllocationHandle
+  };
+  std::map<std::pair<uint64_t, uint64_t>, VmmImported> vmm_imports_;  // by (owner, id)
+  void unmap_vmm(VmmImported& m);                                       // mu_ held
   bool is_pool_base(const void* base) const;  // mu_ held
 };
 

@@ -77,6 +77,7 @@ class ShmChannel {
   ShmChannel(const ShmChannel&) = delete;
   ShmChannel& operator=(const ShmChannel&) = delete;
   const std::string& name() const { return name_; }
+  bool creator() const { return creator_; }  // this side made the segment (it is the side that connected)
 
   // Stream semantics, like a non-blocking socket: bytes moved, or -1 with errno = EAGAIN.
   ssize_t write(const void* data, size_t len) {

@@ -5,8 +5,11 @@
 #include <errno.h>
 #include <fcntl.h>
 #include <netinet/tcp.h>
+#include <poll.h>
 #include <sys/epoll.h>
+#include <sys/socket.h>
 #include <sys/uio.h>
+#include <sys/un.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -105,6 +108,13 @@ bool live_has(uint64_t uid) {
 // the receiver buffer or allocate without bound.
 constexpr size_t kMaxHeaderLen = size_t(16) << 20;   // AM header bytes (a serialized RPC header with its parameters)
 constexpr size_t kMaxSegCount = 4096;                // scatter-gather segments per message
+constexpr uint64_t kFdListenerTag = 0xfffffffeu;     // epoll tag of the Unix socket on which descriptor channels are accepted
+// Device regions announced in an RTS: one per allocation that the payload touches. A sender that does
+// not say how many (status 0) describes one per segment.
+inline size_t rts_region_count(const FrameHeader& fh) {
+  if (!(fh.flags & kFlagDeviceRegions)) return 0;
+  return fh.status > 0 ? static_cast<size_t>(fh.status) : static_cast<size_t>(fh.seg_count);
+}
 constexpr size_t kMinInlineCap = size_t(16) << 20;   // inline payloads: the larger of this and the eager limit
 
 // Device channel geometry. The shared flag page of a direction (512 words) is split: the first 256 words
@@ -177,6 +187,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
   addr_.uid = random_uid();
   live_add(addr_.uid);
   std::strncpy(addr_.name, opt_.name.c_str(), sizeof(addr_.name) - 1);
+  if (cuda_mr_ && opt_.use_shm) open_fd_listener();
   // implicit listener: makes the worker reachable through its address blob
   sockaddr_in in{};
   in.sin_family = AF_INET;
@@ -199,6 +210,11 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
 Worker::~Worker() {
   live_remove(addr_.uid);
   for (auto& [p, ep] : eps_) teardown_device_channel(p);
+  for (auto& [p, ep] : eps_) close_fd_channel(p);
+  if (fd_listen_ >= 0) {
+    ::close(fd_listen_);
+    ::unlink(fd_path_.c_str());
+  }
   for (auto& [p, ep] : eps_)
     if (ep->fd_ >= 0) ::close(ep->fd_);
   for (auto& l : listeners_)
@@ -323,6 +339,7 @@ void Worker::activate_shm(Endpoint* ep) {
   if (!ep->shm_ || ep->shm_active_) return;
   ep->shm_active_ = true;
   shm_eps_.push_back(ep);
+  if (ep->shm_->creator()) connect_fd_channel(ep);  // before anything below is announced to the peer
   setup_device_channel(ep);
 }
 
@@ -494,6 +511,10 @@ int Worker::progress() {
     ++handled;
     if (evs[i].data.u64 >> 63) {
       size_t idx = static_cast<size_t>(evs[i].data.u64 & 0xffffffffu);
+      if (idx == kFdListenerTag) {
+        accept_fd_channels();
+        continue;
+      }
       if (idx < listeners_.size() && listeners_[idx].fd >= 0) accept_pending(listeners_[idx]);
       continue;
     }
@@ -574,6 +595,7 @@ void Worker::fail(Endpoint* ep, int status) {
     ep->fd_ = -1;
   }
   teardown_device_channel(ep);
+  close_fd_channel(ep);
   ep->shm_active_ = false;
   ep->shm_.reset();
   // every operation in flight ends with the endpoint's status
@@ -613,6 +635,7 @@ void Worker::close(Endpoint* ep, bool notify_peer) {
     ep->fd_ = -1;
   }
   teardown_device_channel(ep);
+  close_fd_channel(ep);
   ep->shm_active_ = false;
   ep->shm_.reset();
   if (ep->state_ != Endpoint::State::kFailed) {
@@ -891,7 +914,16 @@ bool Worker::parse_frames(Endpoint* ep) {
       return false;
     }
     size_t meta = fh.header_len;
-    if (fh.type == kAmRts) meta += size_t(fh.seg_count) * 8 + ((fh.flags & kFlagDeviceRegions) ? size_t(fh.seg_count) * sizeof(PeerRegionDesc) : 0);
+    if (fh.type == kAmRts) {
+      const size_t nreg = rts_region_count(fh);
+      if (nreg > kMaxSegCount) {
+        UCX_CONN_ERROR << "frame from " << ep->peer_name_ << " refused: " << nreg << " device regions";
+        ++stats_.frames_refused;
+        fail(ep, UCS_ERR_IO_ERROR);
+        return false;
+      }
+      meta += size_t(fh.seg_count) * 8 + nreg * sizeof(PeerRegionDesc);
+    }
     if (fh.type == kAmDevEager) meta += 8;  // the flag value that the payload's arrival will carry
     size_t body = meta + (fh.type == kAmEager ? fh.payload_len : 0);
     if (avail < sizeof(fh) + body) break;  // wait for the rest (eager bodies are small)
@@ -974,8 +1006,8 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
         // Device regions are addresses and handles of the sender's process: they mean something only
         // when the handshake showed that the sender runs on this host. From anyone else they are
         // ignored and the payload takes the staged host protocol.
-        info.regions.resize(fh.seg_count);
-        std::memcpy(info.regions.data(), p, size_t(fh.seg_count) * sizeof(PeerRegionDesc));
+        info.regions.resize(rts_region_count(fh));
+        std::memcpy(info.regions.data(), p, info.regions.size() * sizeof(PeerRegionDesc));
         uint64_t reg_sum = 0;
         for (auto& r : info.regions) reg_sum += r.length;
         if (reg_sum != fh.payload_len) info.regions.clear();
@@ -1147,11 +1179,11 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   fh.seg_count = static_cast<uint32_t>(seg_count);
   std::vector<PeerRegionDesc> regions;
   if (device && cuda_mr_ && peer_is_local(ep)) {
-    regions.resize(seg_count);
-    bool ok = true;
-    for (size_t i = 0; i < seg_count && ok; ++i) ok = cuda_mr_->export_region(segs[i].data, segs[i].size, &regions[i]);
-    if (ok) fh.flags |= kFlagDeviceRegions;
-    else regions.clear();
+    const bool ok = export_for_peer(ep, segs, seg_count, total, &regions);
+    if (ok) {
+      fh.flags |= kFlagDeviceRegions;
+      fh.status = static_cast<int32_t>(regions.size());  // one per allocation touched, which may be more than the segments
+    }
     if (ok && ep->out_flags_dev_ && opt_.push_threshold && total >= opt_.push_threshold) fh.flags |= kFlagPushOk;
   }
   it.owned.resize(sizeof(fh) + header_len + seg_count * 8 + regions.size() * sizeof(PeerRegionDesc));
@@ -1375,7 +1407,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
   NvtxRange range("eux.transport.device_pull");
   std::vector<void*> srcs(info.regions.size());
   for (size_t i = 0; i < info.regions.size(); ++i) {
-    srcs[i] = cuda_mr_->import_region(info.regions[i], peer_is_this_process(ep));
+    srcs[i] = import_from_peer(ep, info.regions[i]);
     if (!srcs[i]) return UCS_ERR_UNSUPPORTED;
   }
   // walk source regions and destination segments together
@@ -1533,6 +1565,209 @@ Endpoint::DevRing::~DevRing() {
   }
 }
 
+// ---- file-descriptor channel ---------------------------------------------------------------------
+// A cuMemCreate allocation is shared between processes as a POSIX file descriptor, and a descriptor
+// travels only as ancillary data of a Unix socket. Every worker that manages device memory listens on a
+// socket in /dev/shm named after its random id; the side that connected an endpoint (and so knows the
+// peer's id from the handshake) connects to it once the shared-memory channel has shown that both are on
+// one host, and says which endpoint it belongs to. From then on either side sends
+// {allocation number, size} + descriptor the first time it announces memory of that allocation, always
+// before the frame that refers to it, so the receiver finds the descriptor waiting when it reads the frame.
+namespace {
+constexpr uint32_t kFdMagic = 0x44465845u;  // "EXFD"
+struct FdMsg {
+  uint32_t magic = kFdMagic;
+  uint32_t kind = 0;  // 0: hello (a = the connecting worker's id), 1: descriptor (a = allocation number, b = size)
+  uint64_t a = 0, b = 0;
+};
+std::string fd_path_of(uint64_t uid) {
+  char buf[64];
+  std::snprintf(buf, sizeof(buf), "/dev/shm/eux-fd-%016llx", static_cast<unsigned long long>(uid));
+  return buf;
+}
+bool fill_unix_addr(const std::string& path, sockaddr_un* un) {
+  if (path.size() >= sizeof(un->sun_path)) return false;
+  un->sun_family = AF_UNIX;
+  std::memcpy(un->sun_path, path.c_str(), path.size() + 1);
+  return true;
+}
+}  // namespace
+
+void Worker::open_fd_listener() {
+  sockaddr_un un{};
+  fd_path_ = fd_path_of(addr_.uid);
+  if (!fill_unix_addr(fd_path_, &un)) return;
+  int fd = ::socket(AF_UNIX, SOCK_SEQPACKET | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
+  if (fd < 0) return;
+  ::unlink(fd_path_.c_str());
+  epoll_event ev{};
+  ev.events = EPOLLIN;
+  ev.data.u64 = (uint64_t(1) << 63) | kFdListenerTag;
+  if (::bind(fd, reinterpret_cast<sockaddr*>(&un), sizeof(un)) != 0 || ::listen(fd, 64) != 0 || epoll_ctl(epfd_, EPOLL_CTL_ADD, fd, &ev) != 0) {
+    ::close(fd);
+    ::unlink(fd_path_.c_str());
+    return;
+  }
+  fd_listen_ = fd;
+}
+
+void Worker::accept_fd_channels() {
+  if (fd_listen_ < 0) return;
+  for (;;) {
+    int fd = ::accept4(fd_listen_, nullptr, nullptr, SOCK_CLOEXEC | SOCK_NONBLOCK);
+    if (fd < 0) return;
+    // the peer wrote its hello right after connect(): it is there, or about to be
+    FdMsg m{};
+    ssize_t n = -1;
+    for (int tries = 0; tries < 50; ++tries) {
+      n = ::recv(fd, &m, sizeof(m), 0);
+      if (n >= 0 || (errno != EAGAIN && errno != EWOULDBLOCK)) break;
+      pollfd pf{fd, POLLIN, 0};
+      ::poll(&pf, 1, 1);
+    }
+    Endpoint* owner = nullptr;
+    if (n == ssize_t(sizeof(m)) && m.magic == kFdMagic && m.kind == 0)
+      for (auto& [p, ep] : eps_)
+        if (p->shm_active_ && p->fd_chan_ < 0 && p->remote_.addr.uid == m.a && !p->shm_->creator()) owner = p;
+    if (!owner) {
+      ::close(fd);
+      continue;
+    }
+    owner->fd_chan_ = fd;
+  }
+}
+
+void Worker::connect_fd_channel(Endpoint* ep) {
+  if (!cuda_mr_ || ep->fd_chan_ >= 0 || peer_is_this_process(ep)) return;
+  sockaddr_un un{};
+  if (!fill_unix_addr(fd_path_of(ep->remote_.addr.uid), &un)) return;
+  int fd = ::socket(AF_UNIX, SOCK_SEQPACKET | SOCK_CLOEXEC, 0);
+  if (fd < 0) return;
+  // a local connect: done at once, or refused (the peer manages no device memory, or shares no /dev/shm)
+  FdMsg hello;
+  hello.a = addr_.uid;
+  if (::connect(fd, reinterpret_cast<sockaddr*>(&un), sizeof(un)) != 0 || ::send(fd, &hello, sizeof(hello), MSG_NOSIGNAL) != ssize_t(sizeof(hello)) ||
+      set_nonblocking(fd) != 0) {
+    ::close(fd);
+    return;
+  }
+  ep->fd_chan_ = fd;
+}
+
+void Worker::close_fd_channel(Endpoint* ep) {
+  if (ep->fd_chan_ >= 0) {
+    ::close(ep->fd_chan_);
+    ep->fd_chan_ = -1;
+  }
+  ep->vmm_sent_.clear();
+  // mappings of the peer's allocations go with the endpoint, unless another endpoint of this worker talks
+  // to the same peer worker (its transfers may be using them)
+  if (cuda_mr_ && ep->remote_.addr.uid) {
+    bool shared = false;
+    for (auto& [p, other] : eps_) shared = shared || (p != ep && p->remote_.addr.uid == ep->remote_.addr.uid && p->state_ == Endpoint::State::kConnected);
+    if (!shared) cuda_mr_->release_vmm_of(ep->remote_.addr.uid);
+  }
+}
+
+bool Worker::send_vmm_fd(Endpoint* ep, const PeerRegionDesc& d) {
+  PeerVmmRef ref;
+  std::memcpy(&ref, d.handle, sizeof(ref));
+  if (ep->vmm_sent_.count(ref.id)) return true;
+  if (ep->fd_chan_ < 0) accept_fd_channels();
+  if (ep->fd_chan_ < 0) return false;
+  const int fd = cuda_mr_->export_vmm_fd(d);
+  if (fd < 0) return false;
+  FdMsg m;
+  m.kind = 1;
+  m.a = ref.id;
+  m.b = ref.size;
+  iovec iov{&m, sizeof(m)};
+  alignas(cmsghdr) char ctl[CMSG_SPACE(sizeof(int))] = {};
+  msghdr mh{};
+  mh.msg_iov = &iov;
+  mh.msg_iovlen = 1;
+  mh.msg_control = ctl;
+  mh.msg_controllen = sizeof(ctl);
+  cmsghdr* c = CMSG_FIRSTHDR(&mh);
+  c->cmsg_level = SOL_SOCKET;
+  c->cmsg_type = SCM_RIGHTS;
+  c->cmsg_len = CMSG_LEN(sizeof(int));
+  std::memcpy(CMSG_DATA(c), &fd, sizeof(int));
+  const ssize_t n = ::sendmsg(ep->fd_chan_, &mh, MSG_NOSIGNAL | MSG_DONTWAIT);
+  ::close(fd);
+  if (n != ssize_t(sizeof(m))) return false;  // the socket's buffer is full: this message is staged, the next one tries again
+  ep->vmm_sent_.insert(ref.id);
+  ++stats_.vmm_fds_sent;
+  return true;
+}
+
+void Worker::drain_fd_channel(Endpoint* ep) {
+  if (ep->fd_chan_ < 0) accept_fd_channels();
+  if (ep->fd_chan_ < 0 || !cuda_mr_) return;
+  for (;;) {
+    FdMsg m{};
+    iovec iov{&m, sizeof(m)};
+    alignas(cmsghdr) char ctl[CMSG_SPACE(4 * sizeof(int))] = {};
+    msghdr mh{};
+    mh.msg_iov = &iov;
+    mh.msg_iovlen = 1;
+    mh.msg_control = ctl;
+    mh.msg_controllen = sizeof(ctl);
+    const ssize_t n = ::recvmsg(ep->fd_chan_, &mh, MSG_DONTWAIT | MSG_CMSG_CLOEXEC);
+    if (n <= 0) return;
+    std::vector<int> fds;
+    for (cmsghdr* c = CMSG_FIRSTHDR(&mh); c; c = CMSG_NXTHDR(&mh, c)) {
+      if (c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS) continue;
+      const size_t cnt = (c->cmsg_len - CMSG_LEN(0)) / sizeof(int);
+      for (size_t i = 0; i < cnt; ++i) {
+        int fd;
+        std::memcpy(&fd, CMSG_DATA(c) + i * sizeof(int), sizeof(int));
+        fds.push_back(fd);
+      }
+    }
+    if (n == ssize_t(sizeof(m)) && m.magic == kFdMagic && m.kind == 1 && fds.size() == 1 && ensure_device()) {
+      if (cuda_mr_->import_vmm(ep->remote_.addr.uid, PeerVmmRef{m.a, m.b}, fds[0])) ++stats_.vmm_fds_recv;
+      else UCX_CONN_WARN << opt_.name << ": an allocation of " << m.b << " bytes offered by " << ep->peer_name_ << " could not be mapped";
+    }
+    for (int fd : fds) ::close(fd);
+  }
+}
+
+bool Worker::export_for_peer(Endpoint* ep, const ucx_buffer_t* segs, size_t seg_count, uint64_t limit, std::vector<PeerRegionDesc>* out) {
+  out->clear();
+  uint64_t left = limit;
+  for (size_t i = 0; i < seg_count && left > 0; ++i) {
+    const uint64_t n = std::min<uint64_t>(segs[i].size, left);
+    if (n == 0) continue;
+    if (!cuda_mr_->export_regions(segs[i].data, n, out) || out->size() > kMaxSegCount) {
+      out->clear();
+      return false;
+    }
+    left -= n;
+  }
+  if (left != 0 || out->empty()) {
+    out->clear();
+    return false;
+  }
+  if (!peer_is_this_process(ep))
+    for (auto& d : *out)
+      if (d.kind == kRegionVmm && !send_vmm_fd(ep, d)) {
+        out->clear();
+        return false;
+      }
+  return true;
+}
+
+void* Worker::import_from_peer(Endpoint* ep, const PeerRegionDesc& d) {
+  const bool same = peer_is_this_process(ep);
+  void* p = cuda_mr_->import_region(d, same, ep->remote_.addr.uid);
+  if (!p && !same && d.kind == kRegionVmm) {
+    drain_fd_channel(ep);  // its descriptor was sent ahead of the frame that named it
+    p = cuda_mr_->import_region(d, same, ep->remote_.addr.uid);
+  }
+  return p;
+}
+
 // Runs once per endpoint, when its shared-memory channel becomes active (so the peer is on this host)
 // and this worker drives a GPU: registers the channel's flag pages with CUDA, allocates the receive ring
 // for small device payloads and tells the peer where it is.
@@ -1598,6 +1833,7 @@ void Worker::on_dev_ring(Endpoint* ep, const FrameHeader& fh, const char* body) 
     Endpoint* ep;
     ~Release() { w->finish_connect(ep); }
   } release{this, ep};
+  if (ep->fd_chan_ < 0) accept_fd_channels();  // the peer connected it before it sent this frame
   if (fh.header_len < sizeof(PeerRegionDesc) + 8 || !cuda_mr_ || !peer_is_local(ep) || !ep->out_flags_dev_) return;
   PeerRegionDesc d;
   uint32_t geo[2];
@@ -1739,15 +1975,13 @@ int Worker::request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info,
                          Completion& done) {
   if (!cuda_mr_ || ep->push_inflight_ + 1 >= kPushWords || seg_count > kMaxSegCount) return UCS_ERR_UNSUPPORTED;
   std::vector<PeerRegionDesc> regions;
-  uint64_t left = info.payload_len;
-  for (size_t i = 0; i < seg_count && left > 0; ++i) {
-    const uint64_t n = std::min<uint64_t>(segs[i].size, left);
-    PeerRegionDesc d;
-    if (!cuda_mr_->export_region(segs[i].data, n, &d) || !d.exportable) return UCS_ERR_UNSUPPORTED;
-    regions.push_back(d);
-    left -= n;
+  if (!export_for_peer(ep, segs, seg_count, info.payload_len, &regions)) return UCS_ERR_UNSUPPORTED;
+  uint64_t room = 0;
+  for (auto& d : regions) {
+    if (!d.exportable) return UCS_ERR_UNSUPPORTED;
+    room += d.length;
   }
-  if (left != 0 || regions.empty()) return UCS_ERR_UNSUPPORTED;
+  if (room != info.payload_len || regions.empty()) return UCS_ERR_UNSUPPORTED;
   const uint64_t value = ++ep->push_seq_;
   const uint32_t word = static_cast<uint32_t>(value % kPushWords);
   ++ep->push_inflight_;
@@ -1797,7 +2031,7 @@ void Worker::on_push_cts(Endpoint* ep, const FrameHeader& fh, const char* body) 
   std::vector<char*> dsts(regions.size());
   uint64_t room = 0;
   for (size_t i = 0; i < regions.size(); ++i) {
-    dsts[i] = static_cast<char*>(cuda_mr_->import_region(regions[i], peer_is_this_process(ep)));
+    dsts[i] = static_cast<char*>(import_from_peer(ep, regions[i]));
     if (!dsts[i]) {
       refuse();
       return;

@@ -35,6 +35,7 @@
 #include <atomic>
 #include <memory>
 #include <mutex>
+#include <set>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -212,6 +213,10 @@ class Endpoint {
 
   Worker* worker_ = nullptr;
   int fd_ = -1;
+  // Same-host peers whose workers manage device memory: a Unix socket beside the control channel, over
+  // which file descriptors of cuMemCreate allocations are passed (a descriptor cannot travel in a frame).
+  int fd_chan_ = -1;
+  std::set<uint64_t> vmm_sent_;  // allocations (by this process's number) whose descriptor the peer already has
   State state_ = State::kConnecting;
   std::string peer_name_;
   RemoteInfo remote_;
@@ -324,6 +329,8 @@ class Worker {
     uint64_t device_pushes = 0;      // large device payloads pushed by this worker's kernel on a CTS(push)
     uint64_t device_push_recv = 0;   // ... and received that way
     uint64_t kernel_launches = 0;    // launches of the transfer kernels by this worker
+    uint64_t vmm_fds_sent = 0;       // cuMemCreate allocations handed to a peer as file descriptors
+    uint64_t vmm_fds_recv = 0;       // ... and mapped from descriptors that a peer handed over
   };
   const Stats& stats() const { return stats_; }
 
@@ -386,6 +393,19 @@ class Worker {
   bool ensure_device();
   void poll_device();
   void setup_device_channel(Endpoint* ep);
+  // file-descriptor channel (see Endpoint::fd_chan_)
+  void open_fd_listener();
+  void accept_fd_channels();
+  void connect_fd_channel(Endpoint* ep);
+  void close_fd_channel(Endpoint* ep);
+  bool send_vmm_fd(Endpoint* ep, const PeerRegionDesc& d);
+  void drain_fd_channel(Endpoint* ep);
+  // Describe up to `limit` bytes of the segments for this peer, one descriptor per allocation touched, and
+  // make sure the peer holds what it needs to map them. False (and `out` empty): take the staged protocol.
+  bool export_for_peer(Endpoint* ep, const ucx_buffer_t* segs, size_t seg_count, uint64_t limit, std::vector<PeerRegionDesc>* out);
+  void* import_from_peer(Endpoint* ep, const PeerRegionDesc& d);
+  int fd_listen_ = -1;
+  std::string fd_path_;
   void finish_connect(Endpoint* ep);
   void teardown_device_channel(Endpoint* ep);
   void on_dev_ring(Endpoint* ep, const FrameHeader& fh, const char* body);

@@ -1,5 +1,6 @@
 """A stand-alone Axon echo server: prints ``ADDRESS <hex>`` on stdout, serves ``echo`` and
-``add_one`` for device tensors until ``quit`` arrives on stdin.
+``add_one`` for device tensors until ``quit`` arrives on stdin; ``stats`` on stdin is answered with
+``STATS <json of the transport counters>``.
 
     python -m execution_ucx_b200.models.echo_server --device 1 --name peer
 """
@@ -38,6 +39,9 @@ async def _serve(args) -> None:
         line = await loop.run_in_executor(None, sys.stdin.readline)
         if not line or line.strip() == "quit":
             break
+        if line.strip() == "stats":
+            import json
+            print("STATS " + json.dumps(rt.transport_stats()), flush=True)
     rt.stop()
 
 

@@ -134,3 +134,12 @@ def test_two_processes_two_gpus():
             child.wait(timeout=30)
         except Exception:
             child.kill()
+
+
+def test_expandable_segment_tensors_cross_processes_on_the_device_paths():
+    """Tensors from the tensor library's expandable segments (cuMemCreate allocations, which have no CUDA
+    IPC handle) between two processes: eager, pulled and pushed, nothing staged through the host. Runs in
+    processes of its own because the allocator reads its configuration once."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), PYTORCH_CUDA_ALLOC_CONF="expandable_segments:True", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, str(ROOT / "tests" / "mp_vmm_gpu.py")], env=env, cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-2000:] + out.stderr[-4000:]
