@@ -114,6 +114,9 @@ ucxx::transport::Worker::Stats AxonWorker::GetTransportStats() const {
     t.device_pushes += s.device_pushes;
     t.device_push_recv += s.device_push_recv;
     t.kernel_launches += s.kernel_launches;
+    t.device_gathers += s.device_gathers;
+    t.device_packs += s.device_packs;
+    t.sends_held += s.sends_held;
     t.vmm_fds_sent += s.vmm_fds_sent;
     t.vmm_fds_recv += s.vmm_fds_recv;
   }

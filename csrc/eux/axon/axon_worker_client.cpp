@@ -274,6 +274,7 @@ InvokeSender AxonWorker::InvokeOnConnection(std::optional<uint64_t> conn, std::s
   call->mem = std::move(mem_policy);
   try {
     call->out.emplace(make_message(*mr_, serialize_header(*mr_, header), call->payload));
+    attach_send_attr(*client_ctx_, *call->out, call->payload);
   } catch (const std::exception& e) {
     return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::SerializeError), e.what()));
   }

@@ -76,6 +76,16 @@ inline OutMessage make_message(ucxx::UcxMemoryResourceManager& mr, UcxHeader&& h
   return m;
 }
 
+// The remarks a payload carries for the transport, filed with the context under the message's header.
+inline void attach_send_attr(ucxx::ucx_am_context& ctx, const OutMessage& m, const PayloadVariant& payload) {
+  std::shared_ptr<const ucxx::UcxSendAttr> attr;
+  if (auto* b = std::get_if<UcxBuffer>(&payload)) attr = b->send_attr();
+  else if (auto* v = std::get_if<UcxBufferVec>(&payload)) attr = v->send_attr();
+  if (!attr) return;
+  const void* header = m.iovec ? m.iovec->get()->header.data : (m.data ? m.data->get()->header.data : nullptr);
+  ctx.attach_send_attr(header, std::move(attr));
+}
+
 inline std::exception_ptr rpc_error(std::error_code ec, std::string what = {}) {
   return std::make_exception_ptr(rpc::RpcException(ec, std::move(what)));
 }

@@ -290,6 +290,7 @@ void AxonWorker::ServerSendResponse(std::shared_ptr<ServerCall> call, RpcRespons
   out->payload = std::move(payload);
   try {
     out->msg = make_message(*mr_, serialize_header(*mr_, header), out->payload);
+    attach_send_attr(*server_ctx_, out->msg, out->payload);
   } catch (const std::exception& e) {
     server_pipe_failed_.fetch_add(1);
     UCX_CTX_ERROR << name_ << ": response could not be serialised: " << e.what();

@@ -47,6 +47,20 @@ std::chrono::milliseconds parse_timeout(py::handle t) {
 // payload argument of invoke_raw / result of a Python handler -> PayloadVariant. With `metas`, the
 // metadata of every tensor that is imported is appended there (one __dlpack__ call per tensor serves
 // both the bytes and the description).
+// The stream on which the producer of a device tensor would launch its next kernel, as far as this layer can
+// know it: a torch tensor's is torch's current stream on that device; anything else is taken to work on the
+// legacy default stream (0), with which every blocking stream synchronises.
+uintptr_t producer_stream(py::handle obj, int device) {
+  try {
+    const std::string mod = py::type::handle_of(obj).attr("__module__").cast<std::string>();
+    if (mod.rfind("torch", 0) == 0)
+      return py::module_::import("torch").attr("cuda").attr("current_stream")(device).attr("cuda_stream").cast<uintptr_t>();
+  } catch (const std::exception&) {
+    PyErr_Clear();
+  }
+  return 0;
+}
+
 PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj, rpc::TensorMetaVec* metas = nullptr) {
   if (obj.is_none()) return {};
   if (py::isinstance<PyBuffer>(obj)) {
@@ -63,15 +77,28 @@ PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handl
   }
   if (py::isinstance<py::list>(obj) || py::isinstance<py::tuple>(obj)) {
     std::vector<ImportedTensor> ts;
+    py::handle first_cuda;
+    int cuda_device = -1;
     for (auto item : obj) {
       ts.push_back(import_tensor(item));
       if (metas) metas->push_back(ts.back().meta);
+      if (cuda_device < 0 && ts.back().meta.device.device_type == kDLCUDA) {
+        cuda_device = ts.back().meta.device.device_id;
+        first_cuda = item;
+      }
     }
-    return to_ucx_buffer_vec(mr, std::move(ts));
+    auto vec = to_ucx_buffer_vec(mr, std::move(ts));
+    if (cuda_device >= 0) vec.set_send_attr(make_send_attr(nullptr, cuda_device, producer_stream(first_cuda, cuda_device)));
+    return vec;
   }
-  ImportedTensor t = import_tensor(obj);
+  ImportedTensor t = import_tensor(obj, /*allow_strided=*/true);
   if (metas) metas->push_back(t.meta);
-  return to_ucx_buffer(mr, std::move(t));
+  std::shared_ptr<const ucxx::UcxSendAttr> attr;
+  if (t.meta.device.device_type == kDLCUDA && t.nbytes > 0)
+    attr = make_send_attr(&t, t.meta.device.device_id, producer_stream(obj, t.meta.device.device_id));
+  auto buf = to_ucx_buffer(mr, std::move(t));
+  buf.set_send_attr(std::move(attr));
+  return buf;
 }
 
 // The tensor description(s) go last in the parameter list, where the receiver looks first:
@@ -226,6 +253,9 @@ class PyAxonRuntime {
     d["device_pushes"] = s.device_pushes;
     d["device_push_recv"] = s.device_push_recv;
     d["kernel_launches"] = s.kernel_launches;
+    d["device_gathers"] = s.device_gathers;
+    d["device_packs"] = s.device_packs;
+    d["sends_held"] = s.sends_held;
     d["vmm_fds_sent"] = s.vmm_fds_sent;
     d["vmm_fds_recv"] = s.vmm_fds_recv;
     return d;

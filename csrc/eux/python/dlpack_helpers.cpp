@@ -1,5 +1,7 @@
 #include "dlpack_helpers.hpp"
 
+#include <cuda_runtime_api.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -27,7 +29,7 @@ DLDevice device_of(ucx_memory_type_t type, int device_id) {
   }
 }
 
-ImportedTensor import_tensor(py::handle obj) {
+ImportedTensor import_tensor(py::handle obj, bool allow_strided) {
   if (!py::hasattr(obj, "__dlpack__")) throw py::type_error("object does not implement __dlpack__");
   py::object cap_obj = obj.attr("__dlpack__")();
   if (!PyCapsule_IsValid(cap_obj.ptr(), "dltensor")) throw py::value_error("__dlpack__ did not return an unused 'dltensor' capsule");
@@ -40,7 +42,21 @@ ImportedTensor import_tensor(py::handle obj) {
   t.managed = managed;
   try {
     t.meta = rpc::utils::TensorMeta(managed->dl_tensor);
-    if (!t.meta.is_compact()) throw py::value_error("only dense row-major tensors can be sent; call .contiguous() first");
+    if (!t.meta.is_compact()) {
+      const auto& dl = managed->dl_tensor;
+      const unsigned elem_bits = unsigned(dl.dtype.bits) * (dl.dtype.lanes ? dl.dtype.lanes : 1);
+      bool ok = allow_strided && dl.device.device_type == kDLCUDA && dl.ndim >= 1 && dl.ndim <= ucxx::kSendAttrMaxDims &&
+                (elem_bits == 8 || elem_bits == 16 || elem_bits == 32 || elem_bits == 64 || elem_bits == 128);
+      for (int i = 0; ok && i < dl.ndim; ++i) ok = t.meta.strides[i] >= 0 && t.meta.shape[i] > 0;
+      if (!ok) throw py::value_error("only dense row-major tensors can be sent; call .contiguous() first");
+      t.strided = true;
+      t.src_strides.assign(t.meta.strides.begin(), t.meta.strides.end());
+      int64_t st = 1;  // what arrives is dense
+      for (int i = dl.ndim - 1; i >= 0; --i) {
+        t.meta.strides[i] = st;
+        st *= t.meta.shape[i];
+      }
+    }
   } catch (...) {
     if (managed->deleter) managed->deleter(managed);
     throw;
@@ -50,6 +66,51 @@ ImportedTensor import_tensor(py::handle obj) {
   if (t.meta.ndim == 0) t.nbytes = (t.meta.dtype.bits * (t.meta.dtype.lanes ? t.meta.dtype.lanes : 1) + 7) / 8;
   t.meta.byte_offset = 0;  // the payload starts at the first element
   return t;
+}
+
+std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* one, int device, uintptr_t stream) {
+  auto attr = std::make_shared<ucxx::UcxSendAttr>();
+  if (one && one->strided) {
+    const auto& m = one->meta;
+    attr->ndim = m.ndim;
+    attr->elem_size = (unsigned(m.dtype.bits) * (m.dtype.lanes ? m.dtype.lanes : 1) + 7) / 8;
+    uint64_t last = 0;
+    for (int i = 0; i < m.ndim; ++i) {
+      attr->shape[i] = m.shape[i];
+      attr->stride[i] = one->src_strides[i];
+      last += uint64_t(m.shape[i] - 1) * uint64_t(one->src_strides[i]);
+    }
+    attr->span_bytes = (last + 1) * attr->elem_size;
+    attr->dense_bytes = one->nbytes;
+  }
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != device) cudaSetDevice(device);
+  cudaEvent_t ev = nullptr;
+  if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) {
+    if (cudaEventRecord(ev, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess) {
+      attr->ready_event = ev;
+      attr->device = device;
+      attr->keep = std::shared_ptr<void>(ev, [device](void* e) {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (cur != device) cudaSetDevice(device);
+        cudaEventDestroy(static_cast<cudaEvent_t>(e));
+        if (cur != device && cur >= 0) cudaSetDevice(cur);
+      });
+    } else {
+      cudaEventDestroy(ev);
+    }
+  }
+  cudaGetLastError();
+  if (prev != device && prev >= 0) cudaSetDevice(prev);
+  if (!attr->ready_event) {
+    // no event to go by: wait here, once, so that what is sent is at least complete
+    cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream));
+    cudaGetLastError();
+    if (attr->ndim == 0) return nullptr;
+  }
+  return attr;
 }
 
 namespace {

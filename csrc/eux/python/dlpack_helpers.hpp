@@ -4,6 +4,8 @@
 // (reference: axon/python/src/dlpack_helpers.{hpp,cpp}).
 #pragma once
 
+#include "eux/ucxx/ucx_send_attr.hpp"
+
 #include <pybind11/pybind11.h>
 
 #include <memory>
@@ -25,11 +27,20 @@ struct ImportedTensor {
   DLManagedTensor* managed = nullptr;
   rpc::utils::TensorMeta meta;
   void* data = nullptr;   // data pointer with byte_offset applied
-  size_t nbytes = 0;
+  size_t nbytes = 0;      // size as a message: the elements, densely
+  // a device tensor that is not dense row-major and was taken as it lies (`meta` then describes the dense
+  // tensor that arrives at the other end; these are the strides it has here)
+  bool strided = false;
+  std::vector<int64_t> src_strides;
 };
 // Calls obj.__dlpack__() (any object that implements the protocol), takes the capsule's tensor.
-// Throws when the tensor is not compact (dense row-major).
-ImportedTensor import_tensor(py::handle obj);
+// Throws when the tensor is not compact (dense row-major), unless `allow_strided` and it lives on a CUDA
+// device with no negative stride and at most 8 dimensions: the transport gathers such a view itself.
+ImportedTensor import_tensor(py::handle obj, bool allow_strided = false);
+// The remarks for the transport about a device tensor that is about to be sent: its layout when it was
+// imported strided, and an event recorded now on the producer's stream (`stream`: a cudaStream_t as an
+// integer; 0: the legacy default stream), so that nobody has to wait for the producer here. Null for host tensors.
+std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* one, int device, uintptr_t stream);
 // A non-copying buffer over the tensor; releasing it calls the DLPack deleter (under the GIL).
 ucxx::UcxBuffer to_ucx_buffer(ucxx::UcxMemoryResourceManager& mr, ImportedTensor&& t);
 // One buffer vector over several tensors (all on one device kind).

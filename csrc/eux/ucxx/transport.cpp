@@ -576,6 +576,7 @@ int Worker::progress() {
     }
   }
   if (!pull_batch_.empty()) flush_pull_batch();
+  if (!held_sends_.empty()) poll_held_sends();
   if (!device_ops_.empty() || !eager_waits_.empty() || !push_waits_.empty()) poll_device();
   if (!graveyard_.empty()) {
     for (Endpoint* ep : graveyard_) eps_.erase(ep);
@@ -596,6 +597,7 @@ void Worker::fail(Endpoint* ep, int status) {
   }
   teardown_device_channel(ep);
   close_fd_channel(ep);
+  std::erase_if(held_sends_, [ep](const HeldSend& h) { return h.ep == ep; });
   ep->shm_active_ = false;
   ep->shm_.reset();
   // every operation in flight ends with the endpoint's status
@@ -636,6 +638,7 @@ void Worker::close(Endpoint* ep, bool notify_peer) {
   }
   teardown_device_channel(ep);
   close_fd_channel(ep);
+  std::erase_if(held_sends_, [ep](const HeldSend& h) { return h.ep == ep; });
   ep->shm_active_ = false;
   ep->shm_.reset();
   if (ep->state_ != Endpoint::State::kFailed) {
@@ -922,7 +925,7 @@ bool Worker::parse_frames(Endpoint* ep) {
         fail(ep, UCS_ERR_IO_ERROR);
         return false;
       }
-      meta += size_t(fh.seg_count) * 8 + nreg * sizeof(PeerRegionDesc);
+      meta += size_t(fh.seg_count) * 8 + nreg * sizeof(PeerRegionDesc) + ((fh.flags & kFlagLayout) ? sizeof(WireLayout) : 0);
     }
     if (fh.type == kAmDevEager) meta += 8;  // the flag value that the payload's arrival will carry
     size_t body = meta + (fh.type == kAmEager ? fh.payload_len : 0);
@@ -1010,7 +1013,21 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
         std::memcpy(info.regions.data(), p, info.regions.size() * sizeof(PeerRegionDesc));
         uint64_t reg_sum = 0;
         for (auto& r : info.regions) reg_sum += r.length;
-        if (reg_sum != fh.payload_len) info.regions.clear();
+        if (fh.flags & kFlagLayout) {
+          // a strided view inside the one region: what the layout says must lie inside it and add up to the payload
+          std::memcpy(&info.layout, p + info.regions.size() * sizeof(PeerRegionDesc), sizeof(WireLayout));
+          SendHint chk;
+          chk.ndim = info.layout.ndim;
+          chk.elem_size = info.layout.elem_size;
+          std::memcpy(chk.shape, info.layout.shape, sizeof(chk.shape));
+          std::memcpy(chk.stride, info.layout.stride, sizeof(chk.stride));
+          chk.span_bytes = info.layout.span_bytes;
+          chk.dense_bytes = fh.payload_len;
+          info.has_layout = info.regions.size() == 1 && info.layout.ndim > 0 && chk.layout_valid() && reg_sum == info.layout.span_bytes;
+          if (!info.has_layout) info.regions.clear();  // the sender packs it and it takes the staged way
+        } else if (reg_sum != fh.payload_len) {
+          info.regions.clear();
+        }
       }
       ep->rts_[fh.msg_id] = std::move(info);
       AmArrival a;
@@ -1135,18 +1152,45 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
 // active message send / rendezvous
 // ---------------------------------------------------------------------------
 int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t* segs, size_t seg_count,
-                    ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out) {
+                    ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out,
+                    std::shared_ptr<const SendHint> hint) {
   if (!eps_.count(ep) || ep->state_ != Endpoint::State::kConnected) return UCS_ERR_NOT_CONNECTED;
   size_t total = 0;
   for (size_t i = 0; i < seg_count; ++i) total += segs[i].size;
   const bool device = is_device_type(mem_type);
   if (device) nvtx_mark("eux.transport.am_send_device");
+  if (!device || total == 0) hint.reset();  // remarks are about device payloads
+  bool strided = hint && hint->ndim > 0;
+  if (strided && (seg_count != 1 || hint->dense_bytes != total || !hint->layout_valid())) return UCS_ERR_INVALID_PARAM;
   const bool rndv = total > 0 && (force_rndv || device || seg_count > 1 || total >= opt_.eager_limit);
   const uint64_t id = ep->next_msg_id_++;
   if (msg_id_out) *msg_id_out = id;
   if (device && !force_rndv && seg_count == 1 && total > 0 && total <= opt_.dev_eager_limit && ep->tx_ring_ && ep->out_flags_dev_) {
-    int st = dev_eager_send(ep, header, header_len, segs[0], mem_type, id, done);
+    int st = dev_eager_send(ep, header, header_len, segs[0], mem_type, id, done, hint);
     if (st != UCS_ERR_NO_RESOURCE) return st;  // no free slot right now: the rendezvous takes it
+  }
+  // A strided view travels as it lies when the peer can gather it out of this process's memory: one
+  // exportable allocation under its span, peer on this host. Otherwise it is packed here first, by the
+  // same kernel, and the dense copy travels.
+  ucx_buffer_t packed_seg{};
+  std::shared_ptr<void> packed;
+  std::vector<PeerRegionDesc> regions;
+  if (strided) {
+    bool fused = false;
+    if (cuda_mr_ && peer_is_local(ep)) {
+      ucx_buffer_t span{segs[0].data, hint->span_bytes};
+      fused = export_for_peer(ep, &span, 1, hint->span_bytes, &regions) && regions.size() == 1 && (regions[0].exportable || peer_is_this_process(ep));
+      if (!fused) regions.clear();
+    }
+    if (!fused) {
+      if (hint->ready_event && ensure_device()) cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_), static_cast<cudaEvent_t>(hint->ready_event), 0);
+      packed = pack_local(*hint, segs[0].data);
+      if (!packed) return UCS_ERR_NO_MEMORY;
+      packed_seg = {packed.get(), total};
+      segs = &packed_seg;
+      hint.reset();  // dense and complete from here on
+      strided = false;
+    }
   }
   FrameHeader fh;
   fh.header_len = static_cast<uint32_t>(header_len);
@@ -1177,8 +1221,10 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   // rendezvous: announce, keep the user's ranges until CTS or FIN
   fh.type = kAmRts;
   fh.seg_count = static_cast<uint32_t>(seg_count);
-  std::vector<PeerRegionDesc> regions;
-  if (device && cuda_mr_ && peer_is_local(ep)) {
+  if (strided) {
+    fh.flags |= kFlagDeviceRegions | kFlagLayout;
+    fh.status = 1;
+  } else if (device && cuda_mr_ && peer_is_local(ep)) {
     const bool ok = export_for_peer(ep, segs, seg_count, total, &regions);
     if (ok) {
       fh.flags |= kFlagDeviceRegions;
@@ -1186,7 +1232,7 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
     }
     if (ok && ep->out_flags_dev_ && opt_.push_threshold && total >= opt_.push_threshold) fh.flags |= kFlagPushOk;
   }
-  it.owned.resize(sizeof(fh) + header_len + seg_count * 8 + regions.size() * sizeof(PeerRegionDesc));
+  it.owned.resize(sizeof(fh) + header_len + seg_count * 8 + regions.size() * sizeof(PeerRegionDesc) + (strided ? sizeof(WireLayout) : 0));
   char* p = it.owned.data();
   std::memcpy(p, &fh, sizeof(fh));
   p += sizeof(fh);
@@ -1198,13 +1244,105 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
     p += 8;
   }
   if (!regions.empty()) std::memcpy(p, regions.data(), regions.size() * sizeof(PeerRegionDesc));
+  p += regions.size() * sizeof(PeerRegionDesc);
+  if (strided) {
+    WireLayout l;
+    l.ndim = hint->ndim;
+    l.elem_size = hint->elem_size;
+    std::memcpy(l.shape, hint->shape, sizeof(l.shape));
+    std::memcpy(l.stride, hint->stride, sizeof(l.stride));
+    l.span_bytes = hint->span_bytes;
+    std::memcpy(p, &l, sizeof(l));
+  }
   Endpoint::PendingSend ps;
   ps.segs.assign(segs, segs + seg_count);
   ps.mem_type = mem_type;
   ps.done = std::move(done);
+  if (strided) ps.layout = hint;
+  ps.keep = packed;
   ep->pending_sends_.emplace(id, std::move(ps));
+  // The peer (or this worker's staging copy) reads the memory as soon as it hears of it: the announcement
+  // waits until the producer is done. The sending thread does not.
+  if (hint && hint->ready_event && cudaEventQuery(static_cast<cudaEvent_t>(hint->ready_event)) == cudaErrorNotReady) {
+    held_sends_.push_back({ep, std::move(hint), std::move(it)});
+    ++stats_.sends_held;
+    return UCS_INPROGRESS;
+  }
+  cudaGetLastError();
   enqueue(ep, std::move(it));
   return UCS_INPROGRESS;
+}
+
+void Worker::poll_held_sends() {
+  for (auto it = held_sends_.begin(); it != held_sends_.end();) {
+    if (cudaEventQuery(static_cast<cudaEvent_t>(it->hint->ready_event)) == cudaErrorNotReady) {
+      ++it;
+      continue;
+    }
+    cudaGetLastError();  // done, or failed: either way nothing more to wait for (a failed producer shows in the data's consumer)
+    HeldSend h = std::move(*it);
+    it = held_sends_.erase(it);
+    if (eps_.count(h.ep) && h.ep->state_ == Endpoint::State::kConnected) enqueue(h.ep, std::move(h.item));
+  }
+}
+
+// The kernel's description of a gather from a WireLayout. Elements travel as opaque units: 1, 2 and 4 bytes
+// as such, 8 and 16 as two or four 4-byte units under one more innermost dimension.
+void Worker::fill_gather(eux_xfer_desc* d, const WireLayout& l) {
+  const int64_t words = l.elem_size > 4 ? l.elem_size / 4 : 1;
+  const int unit_dtype = l.elem_size == 1 ? EUX_DT_BYTES : (l.elem_size == 2 ? EUX_DT_F16 : EUX_DT_F32);
+  d->src_dtype = d->dst_dtype = unit_dtype;
+  d->op = EUX_OP_NONE;
+  uint64_t n = 1;
+  int nd = 0;
+  for (int i = 0; i < l.ndim; ++i) {
+    d->shape[nd] = l.shape[i];
+    d->stride[nd] = l.stride[i] * words;
+    n *= static_cast<uint64_t>(l.shape[i]);
+    ++nd;
+  }
+  if (words > 1) {
+    d->shape[nd] = words;
+    d->stride[nd] = 1;
+    n *= static_cast<uint64_t>(words);
+    ++nd;
+  }
+  d->ndim = nd;
+  d->n_elems = n;
+}
+
+std::shared_ptr<void> Worker::pack_local(const SendHint& h, const void* src) {
+  if (!ensure_device()) return nullptr;
+  if (h.elem_size > 4 && h.ndim >= kSendAttrMaxDims) return nullptr;
+  void* tmp = nullptr;
+  try {
+    tmp = mr_.allocate(ucx_memory_type::CUDA, h.dense_bytes);
+  } catch (...) {
+    return nullptr;
+  }
+  UcxMemoryResourceManager* mr = &mr_;
+  const size_t bytes = h.dense_bytes;
+  std::shared_ptr<void> out(tmp, [mr, bytes](void* p) {
+    try {
+      mr->deallocate(ucx_memory_type::CUDA, p, bytes);
+    } catch (...) {
+    }
+  });
+  WireLayout l;
+  l.ndim = h.ndim;
+  l.elem_size = h.elem_size;
+  std::memcpy(l.shape, h.shape, sizeof(l.shape));
+  std::memcpy(l.stride, h.stride, sizeof(l.stride));
+  eux_xfer_desc d{};
+  d.src = src;
+  d.dst = tmp;
+  fill_gather(&d, l);
+  flush_pull_batch();
+  if (eux_xfer_launch(&d, counter_dev_, 0, stream_) != 0) return nullptr;
+  ++stats_.kernel_launches;
+  ++stats_.device_packs;
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)) != cudaSuccess) return nullptr;
+  return out;
 }
 
 // CTS arrived: stream the payload as one DATA frame.
@@ -1225,6 +1363,16 @@ void Worker::start_data_send(Endpoint* ep, uint64_t msg_id, bool staged) {
   if (is_device_type(ps.mem_type)) {
     // device payload that the receiver cannot map: stage it through host memory
     (void)staged;
+    if (ps.layout) {
+      // ... and a strided one is made dense on the device first
+      ps.keep = pack_local(*ps.layout, ps.segs[0].data);
+      if (!ps.keep) {
+        if (ps.done) ps.done(UCS_ERR_NO_MEMORY);
+        return;
+      }
+      ps.segs[0].data = ps.keep.get();
+      ps.layout.reset();
+    }
     std::shared_ptr<void> bounce(std::malloc(total ? total : 1), std::free);
     try {
       char* dst = static_cast<char*>(bounce.get());
@@ -1266,7 +1414,7 @@ int Worker::rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, s
     return UCS_ERR_MESSAGE_TRUNCATED;
   }
   const bool dst_device = is_device_type(mem_type);
-  if (info.push_ok && dst_device && !info.regions.empty() && ep->shm_active_ && opt_.push_threshold) {
+  if (info.push_ok && !info.has_layout && dst_device && !info.regions.empty() && ep->shm_active_ && opt_.push_threshold) {
     int st = request_push(ep, msg_id, info, segs, seg_count, done);
     if (st == UCS_INPROGRESS) return st;  // otherwise: pull it
   }
@@ -1410,8 +1558,30 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
     srcs[i] = import_from_peer(ep, info.regions[i]);
     if (!srcs[i]) return UCS_ERR_UNSUPPORTED;
   }
-  // walk source regions and destination segments together
   if (device_ops_.size() + 2 >= kFlagSlots) return UCS_ERR_UNSUPPORTED;  // every transfer in flight owns a flag slot
+  if (info.has_layout) {
+    // a strided view: gather it straight out of the sender's memory into the (one, dense) destination
+    if (seg_count == 0 || segs[0].size < info.payload_len || (info.layout.elem_size > 4 && info.layout.ndim >= kSendAttrMaxDims)) return UCS_ERR_UNSUPPORTED;
+    const uint64_t seq = ++device_seq_;
+    eux_xfer_desc d{};
+    d.src = srcs[0];
+    d.dst = segs[0].data;
+    fill_gather(&d, info.layout);
+    d.flag = flag_dev_ + seq % kFlagSlots;
+    d.flag_value = seq;
+    flush_pull_batch();
+    const int rc = eux_xfer_launch(&d, counter_dev_, 0, stream_);
+    if (rc != 0) {
+      --device_seq_;
+      UCX_CONN_ERROR << "gather kernel launch failed: " << eux_error_string(rc);
+      return UCS_ERR_UNSUPPORTED;
+    }
+    ++stats_.kernel_launches;
+    ++stats_.device_gathers;
+    device_ops_.push_back({seq, ep, msg_id, std::move(done)});
+    return UCS_INPROGRESS;
+  }
+  // walk source regions and destination segments together
   size_t si = 0, so = 0, di = 0, dof = 0;
   struct Piece {
     const char* s;
@@ -1887,9 +2057,11 @@ void Worker::teardown_device_channel(Endpoint* ep) {
 // then raises the slot's flag in the shared page (the peer's host polls it) and this worker's own
 // completion word. The active-message header travels at once through the control ring.
 int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t& seg, ucx_memory_type_t mem_type,
-                           uint64_t msg_id, Completion& done) {
+                           uint64_t msg_id, Completion& done, const std::shared_ptr<const SendHint>& hint) {
   if (!ensure_device() || device_ops_.size() + 2 >= kFlagSlots) return UCS_ERR_NO_RESOURCE;
   if (seg.size > ep->tx_slot_bytes_) return UCS_ERR_NO_RESOURCE;
+  const bool strided = hint && hint->ndim > 0;
+  if (strided && hint->elem_size > 4 && hint->ndim >= kSendAttrMaxDims) return UCS_ERR_NO_RESOURCE;
   ep->tx_free_ |= ep->shm_->in_words()[0].exchange(0, std::memory_order_acquire);  // slots the peer has handed back
   if (!ep->tx_free_) return UCS_ERR_NO_RESOURCE;
   const uint32_t slot = static_cast<uint32_t>(__builtin_ctzll(ep->tx_free_));
@@ -1904,9 +2076,36 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
   item.flag_value = value;
   item.flag2 = flag_dev_ + seq % kFlagSlots;
   item.flag2_value = seq;
-  if (seg.size) {
+  // this worker's kernel reads the payload: it is ordered after the producer on the device
+  if (seg.size && hint && hint->ready_event) cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_), static_cast<cudaEvent_t>(hint->ready_event), 0);
+  if (seg.size && strided) {
+    // gathered on its way into the slot, by a launch of its own
+    eux_xfer_desc d{};
+    d.src = seg.data;
+    d.dst = item.dst;
+    WireLayout l;
+    l.ndim = hint->ndim;
+    l.elem_size = hint->elem_size;
+    std::memcpy(l.shape, hint->shape, sizeof(l.shape));
+    std::memcpy(l.stride, hint->stride, sizeof(l.stride));
+    fill_gather(&d, l);
+    d.flag = item.flag;
+    d.flag_value = item.flag_value;
+    d.flag2 = item.flag2;
+    d.flag2_value = item.flag2_value;
+    flush_pull_batch();
+    if (eux_xfer_launch(&d, counter_dev_, 0, stream_) != 0) {
+      --device_seq_;
+      --ep->tx_seq_;
+      ep->tx_free_ |= uint64_t(1) << slot;
+      return UCS_ERR_NO_RESOURCE;
+    }
+    ++stats_.kernel_launches;
+    ++stats_.device_gathers;
+    device_ops_.push_back({seq, ep, msg_id, std::move(done), false, hint});
+  } else if (seg.size) {
     pull_batch_.push_back(item);
-    device_ops_.push_back({seq, ep, msg_id, std::move(done), false});
+    device_ops_.push_back({seq, ep, msg_id, std::move(done), false, hint});
     if (pull_batch_.size() == EUX_PULL_BATCH_MAX) flush_pull_batch();
   } else {
     --device_seq_;

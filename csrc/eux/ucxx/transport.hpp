@@ -45,6 +45,7 @@
 #include "eux/ucxx/ucx_context_def.h"
 #include "eux/ucxx/shm_channel.hpp"
 #include "eux/ucxx/ucx_memory_resource.hpp"
+#include "eux/ucxx/ucx_send_attr.hpp"
 #include "eux/ucxx/ucx_status.hpp"
 
 namespace eux::ucxx::transport {
@@ -85,6 +86,7 @@ enum FrameFlags : uint8_t {
   kFlagShmAccept = 8,      // HELLO_ACK: the channel is mapped; frames travel through it from now on
   kFlagPushOk = 16,        // RTS: the sender can push the payload itself and signal through the shared flag page
   kFlagFromSender = 64,    // FIN: sent by the sender of the message (send withdrawn / cannot push), not by its receiver
+  kFlagLayout = 128,       // RTS: the payload is a strided view; one region (its span) and a WireLayout follow
   kFlagPush = 32,          // CTS: "push it here": the receiver's regions follow, status = flag word, payload_len = flag value
 };
 
@@ -103,6 +105,18 @@ struct FrameHeader {
 };
 #pragma pack(pop)
 static_assert(sizeof(FrameHeader) == 40);
+
+// How the elements of a strided payload lie in the sender's region (see ucx_send_attr.hpp); follows the
+// region descriptor of an RTS with kFlagLayout.
+struct WireLayout {
+  int32_t ndim = 0;
+  uint32_t elem_size = 0;
+  int64_t shape[kSendAttrMaxDims] = {0};
+  int64_t stride[kSendAttrMaxDims] = {0};
+  uint64_t span_bytes = 0;
+};
+static_assert(sizeof(WireLayout) == 144);
+using SendHint = UcxSendAttr;
 
 // Address of a worker, exchanged out of band (what get_ucp_address() returns).
 struct WorkerAddress {
@@ -190,6 +204,8 @@ class Endpoint {
     std::vector<ucx_buffer_t> segs;
     ucx_memory_type_t mem_type;
     Completion done;
+    std::shared_ptr<const SendHint> layout;  // set when segs[0] is a strided view (its size is the dense size)
+    std::shared_ptr<void> keep;              // a packed copy that stands in for the user's memory
   };
   struct PendingRecv {             // posted rendezvous receive waiting for DATA
     std::vector<ucx_buffer_t> segs;
@@ -205,6 +221,8 @@ class Endpoint {
     std::vector<uint64_t> seg_sizes;
     std::vector<PeerRegionDesc> regions;
     bool push_ok = false;          // the sender offered to push the payload itself
+    bool has_layout = false;       // the one region holds a strided view: gather it as `layout` says
+    WireLayout layout;
   };
   struct RemoteInfo {
     WorkerAddress addr{};
@@ -301,8 +319,11 @@ class Worker {
   // Active message send. `segs` must stay valid until `done` fires. Returns UCS_OK when
   // the send completed inline (done is NOT called), UCS_INPROGRESS when it will complete
   // later, or an error (done is NOT called).
+  // `hint` (device payloads only; see ucx_send_attr.hpp) may describe segs[0] as a strided view and name an
+  // event after which the payload is complete.
   int am_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t* segs, size_t seg_count,
-              ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out = nullptr);
+              ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out = nullptr,
+              std::shared_ptr<const SendHint> hint = nullptr);
   // Complete a rendezvous receive into `segs` (of `mem_type`). Same return convention.
   int rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, size_t seg_count, ucx_memory_type_t mem_type,
                 Completion done);
@@ -329,6 +350,9 @@ class Worker {
     uint64_t device_pushes = 0;      // large device payloads pushed by this worker's kernel on a CTS(push)
     uint64_t device_push_recv = 0;   // ... and received that way
     uint64_t kernel_launches = 0;    // launches of the transfer kernels by this worker
+    uint64_t device_gathers = 0;     // strided payloads gathered by the transfer itself (into a ring slot, or by a pull)
+    uint64_t device_packs = 0;       // ... and those packed into a dense copy first because they could not be
+    uint64_t sends_held = 0;         // announcements held back until the payload's producer had finished
     uint64_t vmm_fds_sent = 0;       // cuMemCreate allocations handed to a peer as file descriptors
     uint64_t vmm_fds_recv = 0;       // ... and mapped from descriptors that a peer handed over
   };
@@ -352,6 +376,12 @@ class Worker {
     uint64_t msg_id;
     Completion done;
     bool send_fin = true;  // a pull answers the sender with FIN; a push or an eager send tells nobody
+    std::shared_ptr<const void> keep = nullptr;  // what the kernel reads from or waits on, if it is the transport's to keep
+  };
+  struct HeldSend {   // a frame that announces device memory whose producer has not finished yet
+    Endpoint* ep;
+    std::shared_ptr<const SendHint> hint;
+    Endpoint::SendItem item;
   };
   struct EagerWait {  // kAmDevEager frame received, its payload still on the way into the ring slot
     Endpoint* ep;
@@ -392,6 +422,12 @@ class Worker {
   bool peer_is_local(const Endpoint* ep) const;
   bool ensure_device();
   void poll_device();
+  void poll_held_sends();
+  std::deque<HeldSend> held_sends_;
+  // strided source -> dense device buffer of this worker's pool (the fallback when the gather cannot be fused
+  // into the transfer); null on failure. Returns after the copy has finished.
+  std::shared_ptr<void> pack_local(const SendHint& h, const void* src);
+  static void fill_gather(eux_xfer_desc* d, const WireLayout& l);
   void setup_device_channel(Endpoint* ep);
   // file-descriptor channel (see Endpoint::fd_chan_)
   void open_fd_listener();
@@ -412,7 +448,7 @@ class Worker {
   void on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body);
   void on_push_cts(Endpoint* ep, const FrameHeader& fh, const char* body);
   int dev_eager_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t& seg, ucx_memory_type_t mem_type,
-                     uint64_t msg_id, Completion& done);
+                     uint64_t msg_id, Completion& done, const std::shared_ptr<const SendHint>& hint);
   int request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count, Completion& done);
   int launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs, const std::vector<size_t>& lens, uint64_t* flag, uint64_t flag_value,
                     uint64_t* flag2, uint64_t flag2_value);

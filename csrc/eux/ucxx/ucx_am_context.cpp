@@ -72,6 +72,23 @@ ucs_status_t ucx_am_context::get_ucp_address(std::vector<std::byte>& address) co
   return UCS_OK;
 }
 
+void ucx_am_context::attach_send_attr(const void* header_data, std::shared_ptr<const UcxSendAttr> attr) {
+  if (!header_data || !attr) return;
+  std::lock_guard lk(send_attr_mu_);
+  send_attrs_[header_data] = std::move(attr);
+  send_attr_count_.store(send_attrs_.size(), std::memory_order_release);
+}
+std::shared_ptr<const UcxSendAttr> ucx_am_context::take_send_attr(const void* header_data) {
+  if (send_attr_count_.load(std::memory_order_acquire) == 0) return nullptr;
+  std::lock_guard lk(send_attr_mu_);
+  auto it = send_attrs_.find(header_data);
+  if (it == send_attrs_.end()) return nullptr;
+  auto out = std::move(it->second);
+  send_attrs_.erase(it);
+  send_attr_count_.store(send_attrs_.size(), std::memory_order_release);
+  return out;
+}
+
 ucs_status_t ucx_am_context::register_ucx_memory(void* ptr, size_t size, void*& memh) {
   memh = nullptr;
   auto* cuda = dynamic_cast<UcxCudaMemoryResourceManager*>(&mr_);

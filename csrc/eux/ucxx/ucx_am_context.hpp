@@ -9,6 +9,7 @@
 // (scheduler) and :128-318 (result bundles); timers use the loop's clock instead
 // of POSIX timers + SIGUSR2.
 #pragma once
+#include <mutex>
 
 #include <atomic>
 #include <chrono>
@@ -184,6 +185,12 @@ class ucx_am_context {
   std::optional<UcxAmDesc> pop_pending_am_desc(size_t key);
   void release_rndv_am_desc(size_t key);
 
+  // Remarks about the device payload of a message that is about to be sent (ucx_send_attr.hpp), filed under
+  // the address of the message's header bytes, which no other message in flight shares; the send operation
+  // collects them. Any thread. (The C message structs have no room for them.)
+  void attach_send_attr(const void* header_data, std::shared_ptr<const UcxSendAttr> attr);
+  std::shared_ptr<const UcxSendAttr> take_send_attr(const void* header_data);
+
   UcxMemoryResourceManager& memory_resource() { return mr_; }
   const std::string& name() const { return name_; }
   bool is_running_on_io_thread() const noexcept { return io_thread_.load(std::memory_order_relaxed) == std::this_thread::get_id(); }
@@ -245,6 +252,9 @@ class ucx_am_context {
   uint64_t client_id_;
   std::unique_ptr<UcxAutoDeviceContext> device_ctx_;
   std::unique_ptr<transport::Worker> worker_;
+  std::mutex send_attr_mu_;
+  std::unordered_map<const void*, std::shared_ptr<const UcxSendAttr>> send_attrs_;
+  std::atomic<size_t> send_attr_count_{0};
   ConnectionManager conn_mgr_;
   std::vector<std::unique_ptr<UcxConnection>> connecting_;  // not yet registered
 

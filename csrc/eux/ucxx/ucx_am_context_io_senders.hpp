@@ -224,20 +224,23 @@ struct send_sender : send_args {
         else this->finish_error(this->result_status);
         return;
       }
+      const ucx_am_data* d = s.data_ref ? s.data_ref : (s.data_owned ? s.data_owned->get() : nullptr);
+      const ucx_am_iovec* v = s.iovec_ref ? s.iovec_ref : (s.iovec_owned ? s.iovec_owned->get() : nullptr);
+      // remarks filed for this message are collected whatever becomes of the send: none may stay behind
+      // for a later message whose header happens to lie at the same address
+      auto attr = this->ctx.take_send_attr(d ? d->header.data : (v ? v->header.data : nullptr));
       conn = s.conn_ptr ? s.conn_ptr : detail::resolve_conn(this->ctx, s.conn_id);
       if (!conn || !conn->is_established()) {
         this->finish_error(UCS_ERR_NOT_CONNECTED);
         return;
       }
       int st;
-      const ucx_am_data* d = s.data_ref ? s.data_ref : (s.data_owned ? s.data_owned->get() : nullptr);
-      const ucx_am_iovec* v = s.iovec_ref ? s.iovec_ref : (s.iovec_owned ? s.iovec_owned->get() : nullptr);
       if (d) {
         if (!d->header.data || d->header.size == 0) st = UCS_ERR_INVALID_PARAM;  // a message needs a header
-        else st = conn->send_am_data(d->header.data, d->header.size, d->buffer.data, d->buffer.size, d->buffer_type, &cb, &request_id);
+        else st = conn->send_am_data(d->header.data, d->header.size, d->buffer.data, d->buffer.size, d->buffer_type, &cb, &request_id, std::move(attr));
       } else if (v) {
         if (!v->header.data || v->header.size == 0) st = UCS_ERR_INVALID_PARAM;
-        else st = conn->send_am_iov_data(v->header.data, v->header.size, v->buffer_vec, v->buffer_count, v->buffer_type, &cb, &request_id);
+        else st = conn->send_am_iov_data(v->header.data, v->header.size, v->buffer_vec, v->buffer_count, v->buffer_type, &cb, &request_id, std::move(attr));
       } else {
         st = UCS_ERR_INVALID_PARAM;
       }

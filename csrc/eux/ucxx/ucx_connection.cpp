@@ -76,18 +76,18 @@ void UcxConnection::adopt(transport::Endpoint* ep) {
 }
 
 int UcxConnection::send_am_data(const void* header, size_t header_len, const void* buffer, size_t length,
-                                ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id) {
+                                ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id, std::shared_ptr<const UcxSendAttr> attr) {
   if (!ep_ || status_ != Status::kConnected) return UCS_ERR_NOT_CONNECTED;
   ucx_buffer_t seg{const_cast<void*>(buffer), length};
   return worker_.am_send(ep_, header, header_len, &seg, length ? 1 : 0, type, false,
-                         [cb](int s) { if (cb) (*cb)(s); }, request_id);
+                         [cb](int s) { if (cb) (*cb)(s); }, request_id, std::move(attr));
 }
 
 int UcxConnection::send_am_iov_data(const void* header, size_t header_len, const ucx_buffer_t* iov, size_t count,
-                                    ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id) {
+                                    ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id, std::shared_ptr<const UcxSendAttr> attr) {
   if (!ep_ || status_ != Status::kConnected) return UCS_ERR_NOT_CONNECTED;
   // scatter-gather sends always go by rendezvous, like the reference (ucx_connection.cpp:419)
-  return worker_.am_send(ep_, header, header_len, iov, count, type, true, [cb](int s) { if (cb) (*cb)(s); }, request_id);
+  return worker_.am_send(ep_, header, header_len, iov, count, type, true, [cb](int s) { if (cb) (*cb)(s); }, request_id, std::move(attr));
 }
 
 int UcxConnection::recv_am_data(const UcxAmDesc& desc, void* buffer, size_t length, ucx_memory_type_t type, UcxCallback* cb) {

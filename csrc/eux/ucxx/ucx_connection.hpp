@@ -101,10 +101,12 @@ class UcxConnection {
   void adopt(transport::Endpoint* ep);  // endpoint that the worker accepted by itself
 
   // -- active messages (return UCS_OK = finished inline, UCS_INPROGRESS, or an error) --
+  // `attr`: optional remarks about a device payload (strided layout, readiness event; ucx_send_attr.hpp)
   int send_am_data(const void* header, size_t header_len, const void* buffer, size_t length, ucx_memory_type_t type,
-                   UcxCallback* cb, uint64_t* request_id = nullptr);
+                   UcxCallback* cb, uint64_t* request_id = nullptr, std::shared_ptr<const UcxSendAttr> attr = nullptr);
   int send_am_iov_data(const void* header, size_t header_len, const ucx_buffer_t* iov, size_t count,
-                       ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id = nullptr);
+                       ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id = nullptr,
+                       std::shared_ptr<const UcxSendAttr> attr = nullptr);
   int recv_am_data(const UcxAmDesc& desc, void* buffer, size_t length, ucx_memory_type_t type, UcxCallback* cb);
   int recv_am_iov_data(const UcxAmDesc& desc, const ucx_buffer_t* iov, size_t count, ucx_memory_type_t type, UcxCallback* cb);
   bool cancel_send(uint64_t request_id);

@@ -16,6 +16,7 @@
 
 #include "eux/ucxx/ucx_context_def.h"
 #include "eux/ucxx/ucx_memory_resource.hpp"
+#include "eux/ucxx/ucx_send_attr.hpp"
 
 namespace eux::ucxx {
 
@@ -62,7 +63,7 @@ class UcxBuffer {
   UcxBuffer& operator=(const UcxBuffer&) = delete;
   UcxBuffer(UcxBuffer&& o) noexcept
       : mr_(o.mr_), type_(o.type_), buffer_(std::exchange(o.buffer_, {nullptr, 0})), mem_h_(std::exchange(o.mem_h_, nullptr)),
-        own_buffer_(std::exchange(o.own_buffer_, false)), ucp_release_fn_(std::move(o.ucp_release_fn_)) {
+        own_buffer_(std::exchange(o.own_buffer_, false)), ucp_release_fn_(std::move(o.ucp_release_fn_)), send_attr_(std::move(o.send_attr_)) {
     o.ucp_release_fn_ = nullptr;
   }
   UcxBuffer& operator=(UcxBuffer&& o) noexcept {
@@ -75,10 +76,16 @@ class UcxBuffer {
       own_buffer_ = std::exchange(o.own_buffer_, false);
       ucp_release_fn_ = std::move(o.ucp_release_fn_);
       o.ucp_release_fn_ = nullptr;
+      send_attr_ = std::move(o.send_attr_);
     }
     return *this;
   }
   ~UcxBuffer() { reset(); }
+
+  // Optional remarks for the transport when this buffer is sent (a strided layout, an event that says when
+  // the bytes are complete); see ucx_send_attr.hpp. size() stays the size of the message.
+  void set_send_attr(std::shared_ptr<const UcxSendAttr> a) { send_attr_ = std::move(a); }
+  const std::shared_ptr<const UcxSendAttr>& send_attr() const { return send_attr_; }
 
   ucx_buffer_t* get() { return &buffer_; }
   const ucx_buffer_t* get() const { return &buffer_; }
@@ -113,6 +120,7 @@ class UcxBuffer {
   void* mem_h_;
   bool own_buffer_;
   ucp_release_fn_t ucp_release_fn_;
+  std::shared_ptr<const UcxSendAttr> send_attr_;
 };
 
 // Active-message header bytes: always host memory.
@@ -218,7 +226,7 @@ class UcxBufferVec {
   UcxBufferVec(UcxBufferVec&& o) noexcept
       : mr_(o.mr_), type_(o.type_), buffers_(std::move(o.buffers_)), mem_h_(std::exchange(o.mem_h_, nullptr)),
         own_buffer_(std::exchange(o.own_buffer_, false)), ucp_release_fn_(std::move(o.ucp_release_fn_)),
-        backing_buffer_(std::move(o.backing_buffer_)) {
+        backing_buffer_(std::move(o.backing_buffer_)), send_attr_(std::move(o.send_attr_)) {
     o.buffers_.clear();
     o.ucp_release_fn_ = nullptr;
   }
@@ -234,10 +242,15 @@ class UcxBufferVec {
       ucp_release_fn_ = std::move(o.ucp_release_fn_);
       o.ucp_release_fn_ = nullptr;
       backing_buffer_ = std::move(o.backing_buffer_);
+      send_attr_ = std::move(o.send_attr_);
     }
     return *this;
   }
   ~UcxBufferVec() { reset(); }
+
+  // As for UcxBuffer; of a vector only the event is looked at (every range is dense).
+  void set_send_attr(std::shared_ptr<const UcxSendAttr> a) { send_attr_ = std::move(a); }
+  const std::shared_ptr<const UcxSendAttr>& send_attr() const { return send_attr_; }
 
   std::vector<void*> data_ptrs() {
     std::vector<void*> out;
@@ -314,6 +327,7 @@ class UcxBufferVec {
   bool own_buffer_;
   ucp_release_fn_t ucp_release_fn_;
   std::unique_ptr<UcxBuffer> backing_buffer_;
+  std::shared_ptr<const UcxSendAttr> send_attr_;
 };
 
 inline UcxBufferVec UcxBuffer::to_buffer_vec(const std::vector<size_t>& sizes) && {

@@ -251,6 +251,103 @@ EUX_TEST(forged_device_regions_are_ignored_and_the_payload_is_staged) {
   h.free_arrivals();
 }
 
+EUX_TEST(layout_of_a_strided_payload_is_checked_before_a_kernel_sees_it) {
+  UcxSendAttr a;
+  CHECK(a.layout_valid());  // dense
+  a.ndim = 2;
+  a.elem_size = 4;
+  a.shape[0] = 70, a.shape[1] = 300;
+  a.stride[0] = 1, a.stride[1] = 70;   // a transposed 300 x 70 matrix
+  a.span_bytes = 300 * 70 * 4;
+  a.dense_bytes = 300 * 70 * 4;
+  CHECK(a.layout_valid());
+  CHECK_EQ(a.elements(), uint64_t(21000));
+  auto bad = [&](auto&& change) {
+    UcxSendAttr b = a;
+    change(b);
+    return !b.layout_valid();
+  };
+  CHECK(bad([](UcxSendAttr& b) { b.span_bytes -= 4; }));          // the last element lies outside the span
+  CHECK(bad([](UcxSendAttr& b) { b.stride[1] = 71; }));           // so does it here
+  CHECK(bad([](UcxSendAttr& b) { b.stride[0] = -1; }));           // the address of the buffer would not be that of element 0
+  CHECK(bad([](UcxSendAttr& b) { b.shape[0] = 0; }));
+  CHECK(bad([](UcxSendAttr& b) { b.elem_size = 3; }));
+  CHECK(bad([](UcxSendAttr& b) { b.ndim = 9; }));
+  CHECK(bad([](UcxSendAttr& b) { b.dense_bytes += 4; }));         // the message would be longer than the elements
+  CHECK(bad([](UcxSendAttr& b) { b.shape[1] = int64_t(1) << 50; b.stride[1] = 0; }));  // more elements than any message has
+  // a stride of zero (an expanded tensor) is fine: the span is smaller than the message
+  UcxSendAttr e;
+  e.ndim = 2;
+  e.elem_size = 8;
+  e.shape[0] = 50, e.shape[1] = 100;
+  e.stride[0] = 0, e.stride[1] = 1;
+  e.span_bytes = 800;
+  e.dense_bytes = 50 * 100 * 8;
+  CHECK(e.layout_valid());
+}
+
+EUX_TEST(rts_with_a_layout_from_a_peer_not_shown_to_be_local_is_staged) {
+  // The frame is taken apart correctly (its length includes the layout), the region and the layout are
+  // ignored because the peer never proved that it runs on this host, and the payload takes the host protocol.
+  Harness h;
+  RawPeer peer(h.w.address().port);
+  peer.hello(uint32_t(getpid()), 0x1234567890abcdefull);
+  CHECK(spin(h.w, [&] { return h.ep != nullptr; }));
+  tr::FrameHeader fh;
+  fh.type = tr::kAmRts;
+  fh.flags = tr::kFlagDeviceRegions | tr::kFlagLayout;
+  fh.header_len = 8;
+  fh.seg_count = 1;
+  fh.status = 1;
+  fh.payload_len = 4096;
+  fh.msg_id = 9;
+  fh.mem_type = uint32_t(ucx_memory_type::CUDA);
+  uint64_t hdr = 1, size = 4096;
+  PeerRegionDesc d;
+  d.length = 8192;
+  tr::WireLayout l;
+  l.ndim = 1;
+  l.elem_size = 4;
+  l.shape[0] = 1024;
+  l.stride[0] = 2;
+  l.span_bytes = 8192;
+  peer.send_all(&fh, sizeof(fh));
+  peer.send_all(&hdr, 8);
+  peer.send_all(&size, 8);
+  peer.send_all(&d, sizeof(d));
+  peer.send_all(&l, sizeof(l));
+  // a second, ordinary frame right behind it shows that the first one's length was counted right
+  tr::FrameHeader eager;
+  eager.type = tr::kAmEager;
+  eager.header_len = 8;
+  eager.payload_len = 0;
+  eager.msg_id = 10;
+  peer.send_all(&eager, sizeof(eager));
+  peer.send_all(&hdr, 8);
+  CHECK(spin(h.w, [&] { return h.arrivals.size() == 2; }));
+  CHECK(h.arrivals[0].rndv && !h.arrivals[1].rndv);
+  CHECK_EQ(h.w.stats().regions_ignored, uint64_t(1));
+  CHECK_EQ(h.w.stats().frames_refused, uint64_t(0));
+  h.free_arrivals();
+}
+
+EUX_TEST(rts_that_claims_too_many_regions_is_refused) {
+  Harness h;
+  RawPeer peer(h.w.address().port);
+  peer.hello(uint32_t(getpid()), 0x1234567890abcdefull);
+  CHECK(spin(h.w, [&] { return h.ep != nullptr; }));
+  tr::FrameHeader fh;
+  fh.type = tr::kAmRts;
+  fh.flags = tr::kFlagDeviceRegions;
+  fh.header_len = 8;
+  fh.seg_count = 1;
+  fh.status = 1 << 20;   // a million descriptors: 100 MB that this worker would have to buffer
+  fh.payload_len = 4096;
+  fh.msg_id = 1;
+  peer.send_all(&fh, sizeof(fh));
+  CHECK(spin(h.w, [&] { return h.w.stats().frames_refused == 1; }));
+}
+
 EUX_TEST(short_data_frame_ends_the_receive_as_truncated) {
   Harness h;
   RawPeer peer(h.w.address().port);

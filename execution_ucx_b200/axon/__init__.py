@@ -183,16 +183,18 @@ def _add_declared(add_typed: Callable, add_plain: Callable, ptype, v: Any) -> No
         add_typed(ptype, v, "")
 
 
-def _contiguous(t):
-    """Dense row-major form of the tensor, ready to be read by another stream or process."""
+def _contiguous(t, strided_ok: bool = False):
+    """The tensor in a form the native layer can send. Host tensors: dense row-major. Device tensors are
+    handed on without waiting for their producer (the native layer records an event on the producer's stream
+    and the transport orders itself after it), and a single strided one (``strided_ok``) as it lies when its
+    strides are not negative: the transfer kernel gathers it on the way."""
+    if getattr(t, "is_cuda", False):
+        if not t.is_contiguous() and not (strided_ok and 1 <= t.dim() <= 8 and all(s >= 0 for s in t.stride()) and t.numel() > 0
+                                          and t.element_size() in (1, 2, 4, 8, 16)):
+            t = t.contiguous()
+        return t
     if hasattr(t, "is_contiguous") and not t.is_contiguous():
         t = t.contiguous()
-    if getattr(t, "is_cuda", False):
-        # the transfer kernel runs on the runtime's own stream (possibly in another process):
-        # everything queued on the producer's stream must have finished writing the tensor
-        import torch
-        torch.cuda.current_stream(t.device).synchronize()
-        return t
     if hasattr(t, "is_contiguous"):
         return t
     flags = getattr(t, "flags", None)
@@ -510,10 +512,9 @@ def _tensor_payload(tensors: list, as_vec: bool):
     DLPack export it takes the bytes from."""
     if not tensors:
         return None, 0
-    tensors = [_contiguous(t) for t in tensors]
     if len(tensors) == 1 and not as_vec:
-        return tensors[0], 1
-    return tensors, 2
+        return _contiguous(tensors[0], strided_ok=True), 1
+    return [_contiguous(t) for t in tensors], 2
 
 
 def _pack_results(sig: _Sig, result):
@@ -775,7 +776,7 @@ class AxonRuntime(_axon.AxonRuntime):
             raise RuntimeError("request_header cannot be None")
         fid, sid = request_header.function_id, request_header.session_id
         if payload is not None and not isinstance(payload, (UcxBuffer, UcxBufferVec)):
-            payload = [_contiguous(t) for t in payload] if _is_seq(payload) else _contiguous(payload)
+            payload = [_contiguous(t) for t in payload] if _is_seq(payload) else _contiguous(payload, strided_ok=True)
         return self._invoke_native(worker_name, request_header, payload, memory_policy, False,
                                    lambda resp, pay: _results_to_python(resp, pay, None, fid, sid))
 

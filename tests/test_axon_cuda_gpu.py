@@ -124,6 +124,16 @@ def test_two_processes_two_gpus():
             assert st["device_eager_sent"] == 1 and st["device_eager_recv"] == 1, st
             assert st["device_pulls"] == 1 and st["device_pushes"] == 1 and st["device_push_recv"] == 1, st
             assert st["device_staged"] == 0, st
+            # strided views cross NVLink as they lie: a small one gathered into the peer's ring by this
+            # process's kernel, a large one gathered out of this process's memory by the peer's pull
+            base = torch.randn(2048, 1024, device="cuda:0").to(torch.bfloat16)
+            for view in (base[:64, :96].t(), base.t(), base[::2, 1::3]):
+                assert not view.is_contiguous()
+                y = await client.invoke(view, worker_name="peer", session_id=1, function="echo", memory_policy=policy)
+                assert y.shape == view.shape and torch.equal(y.view(torch.int16), view.contiguous().view(torch.int16))
+                del y
+            st2 = client.transport_stats()
+            assert st2["device_gathers"] == 1 and st2["device_packs"] == 0 and st2["device_staged"] == 0, st2   # the two large ones are gathered by the peer
             client.stop()
 
         run(main())
@@ -143,3 +153,66 @@ def test_expandable_segment_tensors_cross_processes_on_the_device_paths():
     env = dict(os.environ, PYTHONPATH=str(ROOT), PYTORCH_CUDA_ALLOC_CONF="expandable_segments:True", NCCL_NVLS_ENABLE="0")
     out = subprocess.run([sys.executable, str(ROOT / "tests" / "mp_vmm_gpu.py")], env=env, cwd=str(ROOT), capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-2000:] + out.stderr[-4000:]
+
+
+def test_strided_and_unfinished_tensors(cuda_device):
+    """A strided view is sent as it lies (gathered by the transfer kernel: no dense copy is made first), and a
+    tensor whose producer is still running is sent without waiting for it on the host: the result is that of
+    the finished producer all the same."""
+    from execution_ucx_b200 import axon
+
+    async def main():
+        server = axon.AxonRuntime("sg_server", timeout=20000, device=axon.cuda(0))
+        client = axon.AxonRuntime("sg_client", timeout=20000, device=axon.cuda(0))
+        table = {(2, 32): torch.float32, (2, 64): torch.float64, (4, 16): torch.bfloat16, (1, 8): torch.uint8, (0, 64): torch.int64}
+
+        def on_device(metas):
+            m = metas[0]
+            return torch.empty(m.shape, dtype=table[(m.dtype.code, m.dtype.bits)], device="cuda:0")
+
+        async def echo(x: torch.Tensor) -> torch.Tensor:
+            return x
+
+        server.register_function(echo, memory_policy=on_device)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "sg_server")
+        big = torch.rand(1 << 24, device="cuda:0")
+        views = [
+            torch.rand(64, 50, device="cuda:0").t(),                         # 12.5 KiB: gathered into the ring slot
+            torch.rand(300, 70, device="cuda:0").t(),                        # 82 KiB: gathered by the pull
+            big[::2],                                                        # 32 MiB, every other element
+            big.view(256, 256, 256).permute(2, 0, 1),                        # 64 MiB, three dimensions
+            torch.rand(40, 30, device="cuda:0", dtype=torch.float64).t(),    # 8-byte elements
+            torch.arange(100, device="cuda:0").expand(50, 100),              # a stride of zero, int64
+            torch.randint(0, 255, (70, 33), device="cuda:0", dtype=torch.uint8)[:, 1:],   # single bytes, odd offset
+            torch.randn(128, 96, device="cuda:0").to(torch.bfloat16)[:, ::3],
+        ]
+        for v in views:
+            assert not v.is_contiguous()
+            y = await client.invoke(v, worker_name="sg_server", session_id=1, function="echo", memory_policy=on_device)
+            assert y.shape == v.shape and y.dtype == v.dtype and y.is_contiguous()
+            assert torch.equal(y, v.contiguous()), (v.shape, v.stride(), v.dtype)
+            del y
+        cs = client.transport_stats()
+        # every view was gathered by a transfer (the echo's answers are dense): none was packed first
+        assert cs["device_gathers"] + server.transport_stats()["device_gathers"] == len(views), (cs, server.transport_stats())
+        assert cs["device_packs"] == 0 and cs["device_staged"] == 0, cs
+        # a producer that is still running when the tensor is sent: ~50 ms of spinning, then the values
+        side = torch.cuda.Stream(device="cuda:0")
+        for n in (1 << 10, 1 << 22):                 # eager (ordered on the device), rendezvous (announcement held back)
+            x = torch.zeros(n, device="cuda:0")
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                torch.cuda._sleep(100_000_000)
+                x.add_(7.0)
+                fut = client.invoke(x, worker_name="sg_server", session_id=2, function="echo", memory_policy=on_device)
+                assert not side.query(), "the send was issued while the producer was still running"
+            y = await fut
+            assert float(y.min()) == 7.0 and float(y.max()) == 7.0
+            del y
+        assert client.transport_stats()["sends_held"] >= 1
+        client.stop()
+        server.stop()
+
+    run(main())
