@@ -31,7 +31,8 @@ def test_jax_example_is_gated():
 def test_pytorch_cuda_example(cuda_device):
     out = _run("execution_ucx_b200.axon.examples.pytorch_cuda_example")
     assert out.returncode == 0, out.stderr[-2000:]
-    assert out.stdout.count("same object as the policy's tensor: True") == 2
+    # the 4 KiB result arrives eagerly in the receive ring, the 64 MiB one in the tensor that the policy handed out
+    assert out.stdout.count("received into the receive ring") == 1 and out.stdout.count("received into the policy's tensor") == 1, out.stdout
 
 
 def test_text_trace_of_the_rpc_phases():
