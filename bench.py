@@ -255,7 +255,8 @@ async def service_measurements(api, group, peaks):
         return group.max_over_ranks(timing.percentile(ts, 50))
 
     wid = 20
-    for fmt, key in (("bf16", "remote_gemm_axon_bf16"), ("fp8_block", "remote_gemm_axon_fp8_block_scaled"), ("mxfp8", "remote_gemm_axon_mxfp8")):
+    for fmt, key in (("bf16", "remote_gemm_axon_bf16"), ("fp8_block", "remote_gemm_axon_fp8_block_scaled"),
+                     ("fp8_block_pow2", "remote_gemm_axon_fp8_block_scaled_pow2"), ("mxfp8", "remote_gemm_axon_mxfp8")):
         wid += 1
         w = RemoteGemmAxon(api, m, n, k, fmt=fmt, weight_id=wid)
         await api.barrier()
@@ -270,6 +271,9 @@ async def service_measurements(api, group, peaks):
                     "max_abs_err_vs_fp32_first_256_rows": err,
                     "timing": "host clock around `await remote_gemm(...)` (request, kernel, reply), max over ranks",
                     "path": "Axon call with the caller's region descriptors -> callee's handler launches the GEMM on the caller's memory -> reply"}
+        if fmt == "fp8_block_pow2":
+            out[key]["format"] = ("e4m3 + fp32 scale per 1x128 (X) and 128x128 (W), every scale a power of two: routed to the MX kernel, "
+                                  "where the tensor core applies the scales; same product as fp8_block_scaled")
         del w
     if world > 2:
         w = RemoteGemmAxon(api, m, n, k, fmt="bf16", peers="all", weight_id=30)

@@ -733,40 +733,63 @@ class AxonRuntime(_axon.AxonRuntime):
     # ---- remote GEMM: a weight resident on this runtime's GPU, callable by peers -----------------
     GEMM_FORMATS = {"bf16": 0, "fp8_block": 1, "mxfp8": 2}
 
-    def serve_gemm(self, weight_id: int, w, fmt: str = "bf16", max_m: int = 8192) -> None:
+    MX_SIBLING = 0x40000000   # weight_id | MX_SIBLING: the same fp8_block weight with its scales in the MX form
+
+    def serve_gemm(self, weight_id: int, w, fmt: str = "bf16", max_m: int = 8192, pow2_scales: bool = True) -> None:
         """Make ``W[K, N]`` (a bf16 or fp32 tensor on this runtime's GPU) callable by peers as ``weight_id``.
 
         ``fmt``: ``"bf16"``; ``"fp8_block"`` (e4m3 with one fp32 scale per 128x128 block of W, callers send e4m3
         rows with one fp32 scale per 128 elements); ``"mxfp8"`` (e4m3 with one power-of-two scale per 32 elements
         of K on both operands, scaled inside the tensor core). The weight is converted once, here. A call is served by
-        one kernel that reads the caller's X across NVLink while it computes and writes Y into the caller's memory."""
+        one kernel that reads the caller's X across NVLink while it computes and writes Y into the caller's memory.
+
+        ``pow2_scales`` (``"fp8_block"``): the weight's block scales are chosen as powers of two. They are still
+        fp32 scales per 128x128 block, and any caller is served as before; a caller whose own scales are powers
+        of two as well (``remote_gemm(..., x_scale_pow2=True)``) is served by the MX kernel, which lets the tensor
+        core apply the scales and is the faster of the two."""
         import torch
 
         from ..ops import remote_gemm as g
         code = self.GEMM_FORMATS[fmt]
         k, n = w.shape
+        keep = []
         if fmt == "bf16":
             w_t, scale = w.to(torch.bfloat16).t().contiguous(), None
         elif fmt == "fp8_block":
-            w_t, scale = g.quantize_blocks_128x128(w.to(torch.bfloat16).t().contiguous())
+            w_t, scale = g.quantize_blocks_128x128(w.to(torch.bfloat16).t().contiguous(), pow2=pow2_scales)
+            if pow2_scales and n % 256 == 0 and max_m % 256 == 0 and weight_id < self.MX_SIBLING:
+                chunks = g.mx_scale_chunks(g.block_scales_to_mx(scale, 128), True)
+                self._gemm_add_weight(weight_id | self.MX_SIBLING, w_t.data_ptr(), n, k, self.GEMM_FORMATS["mxfp8"], max_m, chunks.data_ptr())
+                keep.append(chunks)
         else:
             w_t, sf = g.quantize_mx(w.float().t().contiguous())
             scale = g.mx_scale_chunks(sf, True)
         self._gemm_add_weight(weight_id, w_t.data_ptr(), n, k, code, max_m, scale.data_ptr() if scale is not None else 0)
         if not hasattr(self, "_gemm_weights"):
             self._gemm_weights = {}
-        self._gemm_weights[weight_id] = (w_t, scale)      # the kernel reads them for as long as the weight is served
+        self._gemm_weights[weight_id] = (w_t, scale, keep)      # the kernel reads them for as long as the weight is served
 
-    def remote_gemm(self, x, y, *, worker_name: str, weight_id: int, x_scale=None):
+    def remote_gemm(self, x, y, *, worker_name: str, weight_id: int, x_scale=None, x_scale_pow2: bool = False):
         """``y[M, N] = x[M, K] @ W`` on ``worker_name``, where W is what that worker serves as ``weight_id``.
         ``x`` and ``y`` (and ``x_scale`` for the fp8 formats) are device tensors of this process that the callee's
         kernel reads and writes directly; they must stay untouched until the returned future resolves (to the
-        kernel's status word, 0 when all went well). Whatever produced ``x`` on the current stream is waited for first."""
+        kernel's status word, 0 when all went well). Whatever produced ``x`` on the current stream is waited for first.
+
+        ``x_scale_pow2`` (an ``"fp8_block"`` weight served with ``pow2_scales``): ``x_scale`` [M, K/128] holds
+        powers of two (``quantize_rows_1x128(x, pow2=True)``); the call is routed to the MX kernel. The result
+        is the same block-scaled product."""
         import torch
+        if x_scale_pow2:
+            from ..ops import remote_gemm as g
+            x_scale = g.mx_scale_chunks(g.block_scales_to_mx(x_scale, 1), False)
+            weight_id |= self.MX_SIBLING
         torch.cuda.current_stream(x.device).synchronize()
         nb = lambda t: t.numel() * t.element_size()  # noqa: E731
-        return self._remote_gemm(worker_name, weight_id, x.shape[0], x.data_ptr(), nb(x), y.data_ptr(), nb(y),
-                                 x_scale.data_ptr() if x_scale is not None else 0, nb(x_scale) if x_scale is not None else 0)
+        fut = self._remote_gemm(worker_name, weight_id, x.shape[0], x.data_ptr(), nb(x), y.data_ptr(), nb(y),
+                                x_scale.data_ptr() if x_scale is not None else 0, nb(x_scale) if x_scale is not None else 0)
+        if x_scale_pow2:
+            fut.add_done_callback(lambda _f, keep=x_scale: None)   # the converted scales live until the kernel has read them
+        return fut
 
     # ---- client side --------------------------------------------------------------------------
     def invoke_raw(self, worker_name: str, request_header: RpcRequestHeader, payload=None, memory_policy: Optional[Callable] = None):

@@ -243,14 +243,20 @@ class RemoteGemmAxon:
         self.x_scale = None
         if fmt == "bf16":
             self.x = x
-        elif fmt == "fp8_block":
-            self.x, self.x_scale = gemm_ops.quantize_rows_1x128(x)
+        elif fmt in ("fp8_block", "fp8_block_pow2"):
+            # "fp8_block": arbitrary fp32 scales on both sides (served by the kernel that applies them in its
+            # epilogue); "fp8_block_pow2": the same format with power-of-two scales (served by the MX kernel)
+            self.x, self.x_scale = gemm_ops.quantize_rows_1x128(x, pow2=fmt == "fp8_block_pow2")
         else:
             self.x, sf = gemm_ops.quantize_mx(x)
             self.x_sf = sf
             self.x_scale = gemm_ops.mx_scale_chunks(sf, False)
-        self.weight_id = weight_id if weight_id is not None else {"bf16": 1, "fp8_block": 2, "mxfp8": 3}[fmt]
-        api.server.serve_gemm(self.weight_id, self.w, fmt, max_m=m)
+        self.weight_id = weight_id if weight_id is not None else {"bf16": 1, "fp8_block": 2, "mxfp8": 3, "fp8_block_pow2": 4}[fmt]
+        self.pow2 = fmt == "fp8_block_pow2"
+        if self.pow2:
+            api.server.serve_gemm(self.weight_id, self.w, "fp8_block", max_m=m, pow2_scales=True)
+        else:
+            api.server.serve_gemm(self.weight_id, self.w, fmt, max_m=m, pow2_scales=False)
         if g.world == 1:
             self.targets = [api.partner_name]
         elif peers == "all":
@@ -262,7 +268,7 @@ class RemoteGemmAxon:
 
     async def step(self):
         import asyncio
-        futs = [self.api.client.remote_gemm(self.x, y, worker_name=t, weight_id=self.weight_id, x_scale=self.x_scale)
+        futs = [self.api.client.remote_gemm(self.x, y, worker_name=t, weight_id=self.weight_id, x_scale=self.x_scale, x_scale_pow2=self.pow2)
                 for t, y in zip(self.targets, self.ys)]
         status = await asyncio.gather(*futs)
         if any(status):
@@ -282,8 +288,8 @@ class RemoteGemmAxon:
         w = (torch.randn(self.k, self.n, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
         if self.fmt == "bf16":
             return self.x_ref[:rows].float() @ w.float()
-        if self.fmt == "fp8_block":
-            wq, ws = gemm_ops.quantize_blocks_128x128(w.t().contiguous())
+        if self.fmt in ("fp8_block", "fp8_block_pow2"):
+            wq, ws = gemm_ops.quantize_blocks_128x128(w.t().contiguous(), pow2=self.pow2)
             return gemm_ops.dequantized_reference(self.x[:rows], self.x_scale[:rows], wq, ws)
         wq, wsf = gemm_ops.quantize_mx(w.float().t().contiguous())
         return gemm_ops.mx_dequantized_reference(self.x[:rows], self.x_sf[:rows], wq, wsf)

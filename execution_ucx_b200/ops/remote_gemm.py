@@ -70,22 +70,49 @@ class RemoteGemm:
             raise RuntimeError(f"remote gemm status code={s & 0xff} where={s >> 8}")
 
 
-def quantize_rows_1x128(x: torch.Tensor):
-    """X[M,K] -> (e4m3 values [M,K], fp32 scales [M,K/128]): one scale per row per 128 columns."""
+def _block_scale(amax: torch.Tensor, pow2: bool) -> torch.Tensor:
+    scale = amax.clamp_min(2.0 ** -100) * (1.0 / 448.0)
+    # a power of two at or above what the block needs: at most one bit of e4m3's range is given up, and the
+    # scale can then be applied by the tensor core (see block_scales_to_mx)
+    return torch.exp2(torch.ceil(torch.log2(scale))) if pow2 else scale
+
+
+def quantize_rows_1x128(x: torch.Tensor, pow2: bool = False):
+    """X[M,K] -> (e4m3 values [M,K], fp32 scales [M,K/128]): one scale per row per 128 columns.
+    ``pow2``: every scale is a power of two."""
     m, k = x.shape
     g = x.float().view(m, k // 128, 128)
-    scale = g.abs().amax(-1).clamp_min(1e-10) * (1.0 / 448.0)
+    scale = _block_scale(g.abs().amax(-1), pow2)
     q = (g * (1.0 / scale).unsqueeze(-1)).to(torch.float8_e4m3fn).view(m, k)
     return q.contiguous(), scale.contiguous()
 
 
-def quantize_blocks_128x128(w_t: torch.Tensor):
-    """Wt[N,K] -> (e4m3 values [N,K], fp32 scales [N/128,K/128]): one scale per 128x128 block."""
+def quantize_blocks_128x128(w_t: torch.Tensor, pow2: bool = False):
+    """Wt[N,K] -> (e4m3 values [N,K], fp32 scales [N/128,K/128]): one scale per 128x128 block.
+    ``pow2``: every scale is a power of two."""
     n, k = w_t.shape
     g = w_t.float().view(n // 128, 128, k // 128, 128)
-    scale = g.abs().amax(dim=(1, 3)).clamp_min(1e-10) * (1.0 / 448.0)
+    scale = _block_scale(g.abs().amax(dim=(1, 3)), pow2)
     q = (g * (1.0 / scale)[:, None, :, None]).to(torch.float8_e4m3fn).view(n, k)
     return q.contiguous(), scale.contiguous()
+
+
+def scales_are_pow2(scale: torch.Tensor) -> bool:
+    """True when every fp32 scale is a normal power of two (reads the tensor back: for set-up, not per call)."""
+    bits = scale.contiguous().view(torch.int32)
+    exp = (bits >> 23) & 0xFF
+    return bool((((bits & 0x7FFFFF) == 0) & (bits > 0) & (exp > 0) & (exp < 255)).all())
+
+
+def block_scales_to_mx(scale: torch.Tensor, rows_per_scale: int) -> torch.Tensor:
+    """Power-of-two fp32 block scales -> UE8M0 exponents [R, K/32]: the scale of a 128-wide block of K stands
+    for each of its four 32-wide blocks, and (for 128x128 weight blocks, ``rows_per_scale`` = 128) for each of
+    its rows. With such scales the block-scaled product and the MX product are the same numbers, so the
+    tensor core can apply them (the MX kernel) instead of the epilogue."""
+    e8 = ((scale.contiguous().view(torch.int32) >> 23) & 0xFF).to(torch.uint8)   # the biased exponent is the UE8M0 code
+    if rows_per_scale > 1:
+        e8 = e8.repeat_interleave(rows_per_scale, dim=0)
+    return e8.repeat_interleave(4, dim=1).contiguous()
 
 
 def dequantized_reference(xq, xs, wq_t, ws) -> torch.Tensor:
