@@ -5,6 +5,9 @@
     python -m execution_ucx_b200.models.profile_case --kernel xfer
     python -m execution_ucx_b200.models.profile_case --kernel moe
     python -m execution_ucx_b200.models.profile_case --kernel pull_batch  (the transport's batched small pulls)
+    python -m execution_ucx_b200.models.profile_case --kernel gemm_pull   (two GPUs, one process: the GEMM on GPU 0 reads X out of GPU 1's memory)
+    python -m execution_ucx_b200.models.profile_case --kernel xfer_peer   (two GPUs, one process: the transfer kernel on GPU 0 writes into GPU 1's memory)
+    python -m execution_ucx_b200.models.profile_case --kernel xfer_gather (a transposed matrix gathered into a dense buffer)
 
 Each case keeps well under a few GB on the device, uses inputs larger than L2
 where DRAM figures matter, and launches the kernel of interest a handful of times.
@@ -18,7 +21,7 @@ import torch
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "pull_batch", "moe", "moe_fp8"], required=True)
+    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "pull_batch", "moe", "moe_fp8", "gemm_pull", "xfer_peer", "xfer_gather"], required=True)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -33,6 +36,46 @@ def main() -> None:
             g(x.data_ptr(), m, y.data_ptr(), x_is_local=True, cta_pairs=args.kernel == "gemm")
         torch.cuda.synchronize()
         g.check_status()
+    elif args.kernel in ("gemm_pull", "xfer_peer"):
+        # One process, two GPUs: the peer's memory is an ordinary allocation on GPU 1 that GPU 0 may access.
+        # Nothing in the profiled kernels waits for the other GPU, so a replayed launch cannot stall.
+        from ..ops import _native
+        if torch.cuda.device_count() < 2:
+            raise SystemExit("this case needs two GPUs")
+        _native.check(_native.load().eux_enable_peer_access(0, 1), "peer access 0 -> 1")
+        torch.cuda.set_device(0)
+        if args.kernel == "gemm_pull":
+            from ..ops.remote_gemm import RemoteGemm
+            m, n, k = 4096, 4096, 4096
+            x_remote = torch.randn(m, k, device="cuda:1").to(torch.bfloat16)   # complete before any launch below
+            torch.cuda.synchronize(1)
+            w = (torch.randn(k, n, device=dev) * 0.02).to(torch.bfloat16)
+            g = RemoteGemm(w, m)
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            for _ in range(args.iters):
+                g(x_remote.data_ptr(), m, y.data_ptr(), x_is_local=False)
+            torch.cuda.synchronize(0)
+            g.check_status()
+            ref = x_remote[:128].to(dev).float() @ w.float()
+            assert float((y[:128].float() - ref).abs().max()) < 0.25
+        else:
+            from ..ops import tensor_xfer as tx
+            n = 256 << 20
+            src = torch.randn(n // 2, device=dev).to(torch.bfloat16)
+            dst = torch.empty(n // 2, dtype=torch.bfloat16, device="cuda:1")
+            flag = torch.zeros(1, dtype=torch.int64, device=dev)
+            for i in range(args.iters):
+                tx.push(src, dst, flag_ptr=flag.data_ptr(), flag_value=i + 1)
+            torch.cuda.synchronize(0)
+            assert torch.equal(dst[:4096].to(dev), src[:4096])
+    elif args.kernel == "xfer_gather":
+        from ..ops import tensor_xfer as tx
+        a = torch.randn(8192, 8192, device=dev)            # 256 MiB; its transpose is read with a stride of 8192 elements
+        dst = torch.empty(8192 * 8192, device=dev)
+        for _ in range(args.iters):
+            tx.push(a.t(), dst)
+        torch.cuda.synchronize()
+        assert torch.equal(dst.view(8192, 8192)[:64], a.t()[:64].contiguous())
     elif args.kernel == "gemm_fp8":
         from ..ops.remote_gemm import RemoteGemmFp8, quantize_rows_1x128
         m, n, k = 4096, 4096, 4096
