@@ -395,6 +395,7 @@ class PyAxonRuntime {
     c.on_host = false;
     c.buffer_provider = std::move(s.buffer_provider);
     c.buffer_vec_provider = std::move(s.buffer_vec_provider);
+    c.provider_inline = s.provider_inline;  // as on the server: called on the context's thread, no hand-over to the pool and back
     return c;
   }
 

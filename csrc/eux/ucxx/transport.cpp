@@ -121,7 +121,13 @@ constexpr size_t kMinInlineCap = size_t(16) << 20;   // inline payloads: the lar
 // signal pushed rendezvous payloads (the receiver picks the word), the next kEagerSlots the eager ring's slots.
 constexpr uint32_t kPushWords = 256;
 constexpr uint32_t kEagerSlots = 32;                 // one bit each in a 64-bit free mask
-constexpr uint32_t kEagerSlotBytes = 64 << 10;
+constexpr uint32_t kEagerSlotBytesMax = 4 << 20;     // a slot holds the largest eager payload (the worker's dev_eager_limit, rounded up)
+constexpr uint32_t kEagerBatchBytes = 64 << 10;      // eager payloads up to here share one launch per pass; larger ones get a launch of several CTAs
+inline uint32_t eager_slot_bytes(size_t limit) {
+  uint32_t b = 4096;
+  while (b < limit && b < kEagerSlotBytesMax) b <<= 1;
+  return b;
+}
 constexpr uint32_t kEagerWordBase = kPushWords;
 static_assert(kEagerWordBase + kEagerSlots <= ShmChannel::kFlagWords);
 constexpr auto kEagerArrivalTimeout = std::chrono::seconds(10);
@@ -179,7 +185,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
   if (const char* e = std::getenv("EUX_SHM")) opt_.use_shm = e[0] != '0';
   if (const char* e = std::getenv("EUX_DEV_EAGER_LIMIT")) opt_.dev_eager_limit = std::strtoull(e, nullptr, 10);
   if (const char* e = std::getenv("EUX_PUSH_THRESH")) opt_.push_threshold = std::strtoull(e, nullptr, 10);
-  if (opt_.dev_eager_limit > kEagerSlotBytes) opt_.dev_eager_limit = kEagerSlotBytes;
+  if (opt_.dev_eager_limit > kEagerSlotBytesMax) opt_.dev_eager_limit = kEagerSlotBytesMax;
   epfd_ = epoll_create1(EPOLL_CLOEXEC);
   if (epfd_ < 0) throw std::system_error(errno, std::generic_category(), "epoll_create1");
   addr_.pid = static_cast<uint32_t>(getpid());
@@ -1981,13 +1987,14 @@ void Worker::setup_device_channel(Endpoint* ep) {
     // the ring: kEagerSlots slots, allocated from the pooled (already exportable) device memory
     auto ring = std::make_shared<Endpoint::DevRing>();
     try {
-      ring->bytes = size_t(kEagerSlots) * kEagerSlotBytes;
+      ring->slot_bytes = eager_slot_bytes(opt_.dev_eager_limit);
+      ring->bytes = size_t(kEagerSlots) * ring->slot_bytes;
       ring->base = mr_.allocate(ucx_memory_type::CUDA, ring->bytes);
       ring->mr = &mr_;
       if (cuda_mr_->export_region(ring->base, ring->bytes, &d)) {
         ep->rx_ring_ = std::move(ring);
         geo[0] = kEagerSlots;
-        geo[1] = kEagerSlotBytes;
+        geo[1] = ep->rx_ring_->slot_bytes;
       }
     } catch (...) {
     }
@@ -2009,7 +2016,7 @@ void Worker::on_dev_ring(Endpoint* ep, const FrameHeader& fh, const char* body) 
   uint32_t geo[2];
   std::memcpy(&d, body, sizeof(d));
   std::memcpy(geo, body + sizeof(d), 8);
-  if (geo[0] == 0 || geo[0] > 64 || geo[1] == 0 || uint64_t(geo[0]) * geo[1] != d.length) return;
+  if (geo[0] == 0 || geo[0] > 64 || geo[1] == 0 || geo[1] > kEagerSlotBytesMax || uint64_t(geo[0]) * geo[1] != d.length) return;
   void* p = cuda_mr_->import_region(d, peer_is_this_process(ep));
   if (!p) return;
   ep->tx_ring_ = static_cast<char*>(p);
@@ -2078,17 +2085,23 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
   item.flag2_value = seq;
   // this worker's kernel reads the payload: it is ordered after the producer on the device
   if (seg.size && hint && hint->ready_event) cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_), static_cast<cudaEvent_t>(hint->ready_event), 0);
-  if (seg.size && strided) {
-    // gathered on its way into the slot, by a launch of its own
+  if (seg.size && (strided || seg.size > kEagerBatchBytes)) {
+    // gathered on its way into the slot, or too much for one CTA: a launch of its own
     eux_xfer_desc d{};
     d.src = seg.data;
     d.dst = item.dst;
-    WireLayout l;
-    l.ndim = hint->ndim;
-    l.elem_size = hint->elem_size;
-    std::memcpy(l.shape, hint->shape, sizeof(l.shape));
-    std::memcpy(l.stride, hint->stride, sizeof(l.stride));
-    fill_gather(&d, l);
+    if (strided) {
+      WireLayout l;
+      l.ndim = hint->ndim;
+      l.elem_size = hint->elem_size;
+      std::memcpy(l.shape, hint->shape, sizeof(l.shape));
+      std::memcpy(l.stride, hint->stride, sizeof(l.stride));
+      fill_gather(&d, l);
+    } else {
+      d.n_elems = seg.size;
+      d.src_dtype = d.dst_dtype = EUX_DT_BYTES;
+      d.op = EUX_OP_NONE;
+    }
     d.flag = item.flag;
     d.flag_value = item.flag_value;
     d.flag2 = item.flag2;
@@ -2101,7 +2114,7 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
       return UCS_ERR_NO_RESOURCE;
     }
     ++stats_.kernel_launches;
-    ++stats_.device_gathers;
+    if (strided) ++stats_.device_gathers;
     device_ops_.push_back({seq, ep, msg_id, std::move(done), false, hint});
   } else if (seg.size) {
     pull_batch_.push_back(item);
@@ -2130,7 +2143,7 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
 
 void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body) {
   const uint32_t slot = static_cast<uint32_t>(fh.status);
-  if (!ep->rx_ring_ || !ep->shm_ || slot >= kEagerSlots || fh.payload_len > kEagerSlotBytes) {
+  if (!ep->rx_ring_ || !ep->shm_ || slot >= kEagerSlots || fh.payload_len > ep->rx_ring_->slot_bytes) {
     UCX_CONN_ERROR << opt_.name << ": eager device frame from " << ep->peer_name_ << " names a slot this worker never offered";
     ++stats_.frames_refused;
     fail(ep, UCS_ERR_IO_ERROR);
@@ -2148,7 +2161,7 @@ void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body)
   a.header_len = fh.header_len;
   a.header = fh.header_len ? mr_.allocate(ucx_memory_type::HOST, fh.header_len) : nullptr;
   if (fh.header_len) std::memcpy(a.header, body, fh.header_len);
-  a.data = static_cast<char*>(w.ring->base) + size_t(slot) * kEagerSlotBytes;
+  a.data = static_cast<char*>(w.ring->base) + size_t(slot) * w.ring->slot_bytes;
   a.data_len = fh.payload_len;
   a.msg_id = fh.msg_id;
   a.sender_mem_type = static_cast<ucx_memory_type_t>(fh.mem_type);

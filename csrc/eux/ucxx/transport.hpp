@@ -171,7 +171,7 @@ struct WorkerOptions {
   // Device payloads up to this size go out eagerly: one CTA of a batched launch stores them into a slot of
   // the peer's device receive ring and raises a flag the peer's host thread polls. No RTS, no FIN.
   // 0 turns the path off (EUX_DEV_EAGER_LIMIT). At most the ring's slot size.
-  size_t dev_eager_limit = size_t(64) << 10;
+  size_t dev_eager_limit = size_t(1) << 20;
   // Device payloads from this size on are pushed by the sender's kernel (the receiver answers the RTS with
   // its own regions) instead of pulled by the receiver's: with traffic in both directions stores keep
   // the links fuller than loads. 0 turns pushing off (EUX_PUSH_THRESH).
@@ -260,6 +260,7 @@ class Endpoint {
     UcxMemoryResourceManager* mr = nullptr;
     void* base = nullptr;
     size_t bytes = 0;
+    uint32_t slot_bytes = 0;
     ~DevRing();
   };
   bool dev_tried_ = false;           // set-up was attempted (whatever came of it)

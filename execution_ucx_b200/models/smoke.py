@@ -107,9 +107,9 @@ def _axon_round_trip(device: torch.device) -> None:
         server.start_server()
         client.start_client()
         await client.connect_endpoint_async(server.get_local_address(), "smoke_server")
-        # 256 KiB travels by rendezvous (pulled by the batched kernel), 1 KiB eagerly into the receive ring,
-        # 8 MiB is pushed by the sender's kernel
-        for n in (1 << 16, 256, 1 << 21):
+        # 2 MiB travels by rendezvous (pulled by the receiver's kernel), 1 KiB and 256 KiB eagerly into the
+        # receive ring (one CTA of a batched launch; a launch of several CTAs), 8 MiB is pushed by the sender's kernel
+        for n in (1 << 19, 256, 1 << 16, 1 << 21):
             x = torch.rand(n, device=device)
             y = await client.invoke(x, worker_name="smoke_server", session_id=1, function="add_one", memory_policy=policy)
             assert y.is_cuda and torch.equal(y, x + 1.0)

@@ -24,7 +24,7 @@ async def main():
     api = AxonTensorRpc(group, timeout_ms=30000)
     await api.start(connect_all=True)
     # echo at an eager, a pulled and a pushed size
-    for n in (2048, 1 << 20, 1 << 24):
+    for n in (2048, 1 << 21, 1 << 24):
         x = torch.randn(n // 2, device=dev).to(torch.bfloat16)
         y = await api.step(x)
         assert torch.equal(y.view(torch.int16), x.view(torch.int16)), f"echo of {n} bytes differs"

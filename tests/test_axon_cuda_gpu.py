@@ -56,7 +56,7 @@ def test_cuda_tensor_echo_same_process(cuda_device):
             x = torch.rand(n, device="cuda:0")
             y = await client.invoke(x, worker_name="gpu_server", session_id=1, function="plus_one", memory_policy=client_policy)
             assert y.is_cuda and y.shape == x.shape
-            if n * 4 > 64 << 10:
+            if n * 4 > 1 << 20:
                 assert y is made[-1], "large device results land in the tensor the policy returned"
             else:
                 assert not made, "small device results arrive eagerly in the receive ring; the policy is not asked"
@@ -124,8 +124,8 @@ def test_two_processes_two_gpus():
             assert st["device_eager_sent"] == 1 and st["device_eager_recv"] == 1, st
             assert st["device_pulls"] == 1 and st["device_pushes"] == 1 and st["device_push_recv"] == 1, st
             assert st["device_staged"] == 0, st
-            # strided views cross NVLink as they lie: a small one gathered into the peer's ring by this
-            # process's kernel, a large one gathered out of this process's memory by the peer's pull
+            # strided views cross NVLink as they lie: up to the eager limit gathered into the peer's ring by this
+            # process's kernel (12 KiB, 698 KiB), a large one (4 MiB) gathered out of this process's memory by the peer's pull
             base = torch.randn(2048, 1024, device="cuda:0").to(torch.bfloat16)
             for view in (base[:64, :96].t(), base.t(), base[::2, 1::3]):
                 assert not view.is_contiguous()
@@ -133,7 +133,7 @@ def test_two_processes_two_gpus():
                 assert y.shape == view.shape and torch.equal(y.view(torch.int16), view.contiguous().view(torch.int16))
                 del y
             st2 = client.transport_stats()
-            assert st2["device_gathers"] == 1 and st2["device_packs"] == 0 and st2["device_staged"] == 0, st2   # the two large ones are gathered by the peer
+            assert st2["device_gathers"] == 2 and st2["device_packs"] == 0 and st2["device_staged"] == 0, st2
             client.stop()
 
         run(main())
@@ -180,7 +180,8 @@ def test_strided_and_unfinished_tensors(cuda_device):
         big = torch.rand(1 << 24, device="cuda:0")
         views = [
             torch.rand(64, 50, device="cuda:0").t(),                         # 12.5 KiB: gathered into the ring slot
-            torch.rand(300, 70, device="cuda:0").t(),                        # 82 KiB: gathered by the pull
+            torch.rand(300, 70, device="cuda:0").t(),                        # 82 KiB: the same, by a launch of several CTAs
+            torch.rand(1200, 700, device="cuda:0").t(),                      # 3.2 MiB: gathered by the pull
             big[::2],                                                        # 32 MiB, every other element
             big.view(256, 256, 256).permute(2, 0, 1),                        # 64 MiB, three dimensions
             torch.rand(40, 30, device="cuda:0", dtype=torch.float64).t(),    # 8-byte elements
