@@ -15,4 +15,4 @@ The host runtime (sender/receiver executor, active-message context, rpc core,
 axon worker, storage) is C++ under ``csrc/eux`` and is reached through
 ``execution_ucx_b200.axon``.
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
