@@ -121,11 +121,14 @@ constexpr size_t kMinInlineCap = size_t(16) << 20;   // inline payloads: the lar
 // signal pushed rendezvous payloads (the receiver picks the word), the next kEagerSlots the eager ring's slots.
 constexpr uint32_t kPushWords = 256;
 constexpr uint32_t kEagerSlots = 32;                 // one bit each in a 64-bit free mask
-constexpr uint32_t kEagerSlotBytesMax = 4 << 20;     // a slot holds the largest eager payload (the worker's dev_eager_limit, rounded up)
+constexpr uint32_t kEagerSlotBytesMax = 1 << 20;     // largest slot
+constexpr uint32_t kEagerRunMax = 4;                 // an eager payload may take up to this many consecutive slots
 constexpr uint32_t kEagerBatchBytes = 64 << 10;      // eager payloads up to here share one launch per pass; larger ones get a launch of several CTAs
+// Slot size for a worker whose eager limit is `limit`: a quarter of it (a payload at the limit takes a run of
+// kEagerRunMax slots), at least 4 KiB, a power of two.
 inline uint32_t eager_slot_bytes(size_t limit) {
   uint32_t b = 4096;
-  while (b < limit && b < kEagerSlotBytesMax) b <<= 1;
+  while (size_t(b) * kEagerRunMax < limit && b < kEagerSlotBytesMax) b <<= 1;
   return b;
 }
 constexpr uint32_t kEagerWordBase = kPushWords;
@@ -185,7 +188,7 @@ Worker::Worker(UcxMemoryResourceManager& mr, const WorkerOptions& opt) : mr_(mr)
   if (const char* e = std::getenv("EUX_SHM")) opt_.use_shm = e[0] != '0';
   if (const char* e = std::getenv("EUX_DEV_EAGER_LIMIT")) opt_.dev_eager_limit = std::strtoull(e, nullptr, 10);
   if (const char* e = std::getenv("EUX_PUSH_THRESH")) opt_.push_threshold = std::strtoull(e, nullptr, 10);
-  if (opt_.dev_eager_limit > kEagerSlotBytesMax) opt_.dev_eager_limit = kEagerSlotBytesMax;
+  if (opt_.dev_eager_limit > size_t(kEagerSlotBytesMax) * kEagerRunMax) opt_.dev_eager_limit = size_t(kEagerSlotBytesMax) * kEagerRunMax;
   epfd_ = epoll_create1(EPOLL_CLOEXEC);
   if (epfd_ < 0) throw std::system_error(errno, std::generic_category(), "epoll_create1");
   addr_.pid = static_cast<uint32_t>(getpid());
@@ -2066,13 +2069,20 @@ void Worker::teardown_device_channel(Endpoint* ep) {
 int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t& seg, ucx_memory_type_t mem_type,
                            uint64_t msg_id, Completion& done, const std::shared_ptr<const SendHint>& hint) {
   if (!ensure_device() || device_ops_.size() + 2 >= kFlagSlots) return UCS_ERR_NO_RESOURCE;
-  if (seg.size > ep->tx_slot_bytes_) return UCS_ERR_NO_RESOURCE;
+  const uint32_t run = seg.size ? static_cast<uint32_t>((seg.size + ep->tx_slot_bytes_ - 1) / ep->tx_slot_bytes_) : 1;
+  if (run > kEagerRunMax || run > ep->tx_slots_) return UCS_ERR_NO_RESOURCE;
   const bool strided = hint && hint->ndim > 0;
   if (strided && hint->elem_size > 4 && hint->ndim >= kSendAttrMaxDims) return UCS_ERR_NO_RESOURCE;
   ep->tx_free_ |= ep->shm_->in_words()[0].exchange(0, std::memory_order_acquire);  // slots the peer has handed back
   if (!ep->tx_free_) return UCS_ERR_NO_RESOURCE;
-  const uint32_t slot = static_cast<uint32_t>(__builtin_ctzll(ep->tx_free_));
-  ep->tx_free_ &= ep->tx_free_ - 1;
+  // the lowest run of `run` consecutive free slots
+  uint64_t starts = ep->tx_free_;
+  for (uint32_t i = 1; i < run; ++i) starts &= ep->tx_free_ >> i;
+  if (ep->tx_slots_ < 64) starts &= (uint64_t(1) << (ep->tx_slots_ - run + 1)) - 1;
+  if (!starts) return UCS_ERR_NO_RESOURCE;
+  const uint32_t slot = static_cast<uint32_t>(__builtin_ctzll(starts));
+  const uint64_t run_mask = ((run == 64 ? ~uint64_t(0) : (uint64_t(1) << run) - 1)) << slot;
+  ep->tx_free_ &= ~run_mask;
   const uint64_t value = ++ep->tx_seq_;
   const uint64_t seq = ++device_seq_;
   eux_pull_item item{};
@@ -2110,7 +2120,7 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
     if (eux_xfer_launch(&d, counter_dev_, 0, stream_) != 0) {
       --device_seq_;
       --ep->tx_seq_;
-      ep->tx_free_ |= uint64_t(1) << slot;
+      ep->tx_free_ |= run_mask;
       return UCS_ERR_NO_RESOURCE;
     }
     ++stats_.kernel_launches;
@@ -2129,7 +2139,7 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
   fh.payload_len = seg.size;
   fh.msg_id = msg_id;
   fh.mem_type = static_cast<uint32_t>(mem_type);
-  fh.status = static_cast<int32_t>(slot);
+  fh.status = static_cast<int32_t>(slot | (run << 8));  // first slot, and how many the payload takes
   Endpoint::SendItem it;
   it.owned.resize(sizeof(fh) + header_len + 8);
   std::memcpy(it.owned.data(), &fh, sizeof(fh));
@@ -2142,8 +2152,9 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
 }
 
 void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body) {
-  const uint32_t slot = static_cast<uint32_t>(fh.status);
-  if (!ep->rx_ring_ || !ep->shm_ || slot >= kEagerSlots || fh.payload_len > ep->rx_ring_->slot_bytes) {
+  const uint32_t slot = static_cast<uint32_t>(fh.status) & 0xffu, run = (static_cast<uint32_t>(fh.status) >> 8) & 0xffu;
+  if (!ep->rx_ring_ || !ep->shm_ || run == 0 || run > kEagerRunMax || slot + run > kEagerSlots ||
+      fh.payload_len > uint64_t(run) * ep->rx_ring_->slot_bytes) {
     UCX_CONN_ERROR << opt_.name << ": eager device frame from " << ep->peer_name_ << " names a slot this worker never offered";
     ++stats_.frames_refused;
     fail(ep, UCS_ERR_IO_ERROR);
@@ -2171,13 +2182,13 @@ void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body)
   struct SlotToken {
     std::shared_ptr<ShmChannel> shm;
     std::shared_ptr<Endpoint::DevRing> ring;
-    uint32_t slot;
-    SlotToken(std::shared_ptr<ShmChannel> s, std::shared_ptr<Endpoint::DevRing> r, uint32_t i) : shm(std::move(s)), ring(std::move(r)), slot(i) {}
-    SlotToken(const SlotToken&) = delete;  // exactly one object stands for the slot: its end hands the slot back
+    uint64_t mask;  // the slots of the payload's run
+    SlotToken(std::shared_ptr<ShmChannel> s, std::shared_ptr<Endpoint::DevRing> r, uint64_t m) : shm(std::move(s)), ring(std::move(r)), mask(m) {}
+    SlotToken(const SlotToken&) = delete;  // exactly one object stands for the slots: its end hands them back
     SlotToken& operator=(const SlotToken&) = delete;
-    ~SlotToken() { shm->out_words()[0].fetch_or(uint64_t(1) << slot, std::memory_order_release); }
+    ~SlotToken() { shm->out_words()[0].fetch_or(mask, std::memory_order_release); }
   };
-  a.data_keep = std::make_shared<SlotToken>(w.shm, w.ring, slot);
+  a.data_keep = std::make_shared<SlotToken>(w.shm, w.ring, ((uint64_t(1) << run) - 1) << slot);
   eager_waits_.push_back(std::move(w));
 }
 

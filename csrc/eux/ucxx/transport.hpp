@@ -168,10 +168,12 @@ struct WorkerOptions {
   size_t eager_limit = 8192;     // payloads below this travel inline (host memory)
   size_t send_copy_limit = 8192; // inline payloads up to this size are copied, so the send completes at once
   bool use_shm = true;           // peers on this host talk through shared-memory rings (EUX_SHM=0 turns it off)
-  // Device payloads up to this size go out eagerly: one CTA of a batched launch stores them into a slot of
-  // the peer's device receive ring and raises a flag the peer's host thread polls. No RTS, no FIN.
-  // 0 turns the path off (EUX_DEV_EAGER_LIMIT). At most the ring's slot size.
-  size_t dev_eager_limit = size_t(1) << 20;
+  // Device payloads up to this size go out eagerly: the sender's kernel (one CTA of a batched launch up to
+  // 64 KiB, a launch of its own above) stores them into the peer's device receive ring (32 slots of a quarter
+  // of this limit; a payload takes up to four consecutive slots) and raises a flag the peer's host thread
+  // polls. No RTS, no FIN, and the receiver asks no memory policy: the payload is handed on where it lies.
+  // 0 turns the path off (EUX_DEV_EAGER_LIMIT); at most 4 MiB.
+  size_t dev_eager_limit = size_t(4) << 20;
   // Device payloads from this size on are pushed by the sender's kernel (the receiver answers the RTS with
   // its own regions) instead of pulled by the receiver's: with traffic in both directions stores keep
   // the links fuller than loads. 0 turns pushing off (EUX_PUSH_THRESH).

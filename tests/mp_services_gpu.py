@@ -23,14 +23,14 @@ async def main():
     group = PeerGroup(rank, world, dev)
     api = AxonTensorRpc(group, timeout_ms=30000)
     await api.start(connect_all=True)
-    # echo at an eager, a pulled and a pushed size
+    # echo at eager sizes (one slot of the peer's ring, a run of slots) and at a pushed size
     for n in (2048, 1 << 21, 1 << 24):
         x = torch.randn(n // 2, device=dev).to(torch.bfloat16)
         y = await api.step(x)
         assert torch.equal(y.view(torch.int16), x.view(torch.int16)), f"echo of {n} bytes differs"
         del y
     st = api.transport_stats()
-    assert st["device_staged"] == 0 and st["device_eager_sent"] >= 1 and st["device_pushes"] >= 1 and st["device_pulls"] >= 1, st
+    assert st["device_staged"] == 0 and st["device_eager_sent"] >= 2 and st["device_pushes"] >= 1, st
     await api.barrier()
     # remote GEMM served by the partner, each operand format
     for fmt, tol in (("bf16", 3e-2), ("fp8_block", 3e-2), ("mxfp8", 3e-2)):

@@ -30,7 +30,7 @@ def main() -> int:
             client.start_client()
             await client.connect_endpoint_async(address, "vmm_peer")
             policy = lambda metas: torch.empty(metas[0].shape, dtype=torch.bfloat16, device="cuda:0")  # noqa: E731
-            # 2 KiB: eager into the peer's ring; 2 MiB: pulled out of this process's segments by the peer's
+            # (the eager limit is 64 KiB in this test) 2 KiB: eager into the peer's ring; 2 MiB: pulled out of this process's segments by the peer's
             # kernel; 96 MiB: pushed into the peer's segments (five 20 MiB allocations under one tensor), and
             # back the same ways
             for n in (1024, 1 << 20, 48 << 20):

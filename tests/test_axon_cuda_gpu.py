@@ -56,27 +56,29 @@ def test_cuda_tensor_echo_same_process(cuda_device):
             x = torch.rand(n, device="cuda:0")
             y = await client.invoke(x, worker_name="gpu_server", session_id=1, function="plus_one", memory_policy=client_policy)
             assert y.is_cuda and y.shape == x.shape
-            if n * 4 > 1 << 20:
+            if n * 4 > 4 << 20:
                 assert y is made[-1], "large device results land in the tensor the policy returned"
             else:
-                assert not made, "small device results arrive eagerly in the receive ring; the policy is not asked"
+                assert not made, "device results up to 4 MiB arrive eagerly in the receive ring; the policy is not asked"
             torch.testing.assert_close(y, x + 1.0, rtol=0, atol=0)
             del y
         cs, ss = client.transport_stats(), server.transport_stats()
-        # 256 B and 16 KiB went out as eager device messages in both directions (no rendezvous), 2 MiB was
-        # pulled by the receiver's kernel, 64 MiB pushed by the sender's; nothing went through host memory
-        assert cs["device_eager_sent"] == 2 and ss["device_eager_recv"] == 2, (cs, ss)
-        assert ss["device_eager_sent"] == 2 and cs["device_eager_recv"] == 2, (cs, ss)
+        # 256 B, 16 KiB and 2 MiB went out as eager device messages in both directions (no rendezvous), 64 MiB
+        # was pushed by the sender's kernel; nothing went through host memory
+        assert cs["device_eager_sent"] == 3 and ss["device_eager_recv"] == 3, (cs, ss)
+        assert ss["device_eager_sent"] == 3 and cs["device_eager_recv"] == 3, (cs, ss)
         assert cs["device_pushes"] == 1 and ss["device_push_recv"] == 1 and ss["device_pushes"] == 1 and cs["device_push_recv"] == 1, (cs, ss)
-        assert ss["device_pulls"] == 1 and cs["device_pulls"] == 1, (cs, ss)
+        assert ss["device_pulls"] == 0 and cs["device_pulls"] == 0, (cs, ss)
         assert cs["device_staged"] == 0 and ss["device_staged"] == 0, (cs, ss)
         # more eager messages than the ring has slots, all in flight at once: the surplus takes the rendezvous
+        # and is pulled by the receiver's kernel
         xs = [torch.full((256,), float(i), device="cuda:0") for i in range(80)]
         ys = await asyncio.gather(*[client.invoke(x, worker_name="gpu_server", session_id=2, function="plus_one", memory_policy=client_policy)
                                     for x in xs])
         for i, y in enumerate(ys):
             assert float(y[0]) == i + 1.0 and float(y[-1]) == i + 1.0
         del ys
+        assert client.transport_stats()["device_pulls"] + server.transport_stats()["device_pulls"] >= 1
         # 2-D, non-contiguous input is packed before it is sent
         x2 = torch.rand(300, 70, device="cuda:0").t()
         y2 = await client.invoke(x2, worker_name="gpu_server", session_id=1, function="plus_one", memory_policy=client_policy)
@@ -115,25 +117,26 @@ def test_two_processes_two_gpus():
             client.start_client()
             await client.connect_endpoint_async(address, "peer")
             policy = lambda metas: torch.empty(metas[0].shape, dtype=torch.bfloat16, device="cuda:0")  # noqa: E731
-            for n in (1024, 1 << 20, 1 << 24):      # 2 KiB: eager into the peer's ring; 2 MiB: pulled; 32 MiB: pushed
+            for n in (1024, 1 << 20, 1 << 24):      # 2 KiB, 2 MiB: eager into the peer's ring (one slot, two slots); 32 MiB: pushed
                 x = torch.randn(n, device="cuda:0").to(torch.bfloat16)
                 y = await client.invoke(x, worker_name="peer", session_id=1, function="echo", memory_policy=policy)
                 assert y.device.index == 0 and torch.equal(y.view(torch.int16), x.view(torch.int16))
                 del y
             st = client.transport_stats()
-            assert st["device_eager_sent"] == 1 and st["device_eager_recv"] == 1, st
-            assert st["device_pulls"] == 1 and st["device_pushes"] == 1 and st["device_push_recv"] == 1, st
+            assert st["device_eager_sent"] == 2 and st["device_eager_recv"] == 2, st
+            assert st["device_pulls"] == 0 and st["device_pushes"] == 1 and st["device_push_recv"] == 1, st
             assert st["device_staged"] == 0, st
             # strided views cross NVLink as they lie: up to the eager limit gathered into the peer's ring by this
-            # process's kernel (12 KiB, 698 KiB), a large one (4 MiB) gathered out of this process's memory by the peer's pull
-            base = torch.randn(2048, 1024, device="cuda:0").to(torch.bfloat16)
-            for view in (base[:64, :96].t(), base.t(), base[::2, 1::3]):
+            # process's kernel (12 KiB, 698 KiB), a large one (8 MiB) gathered out of this process's memory by the peer's pull
+            base = torch.randn(4096, 1024, device="cuda:0").to(torch.bfloat16)
+            for view in (base[:64, :96].t(), base.t(), base[:2048:2, 1::3]):
                 assert not view.is_contiguous()
                 y = await client.invoke(view, worker_name="peer", session_id=1, function="echo", memory_policy=policy)
                 assert y.shape == view.shape and torch.equal(y.view(torch.int16), view.contiguous().view(torch.int16))
                 del y
             st2 = client.transport_stats()
             assert st2["device_gathers"] == 2 and st2["device_packs"] == 0 and st2["device_staged"] == 0, st2
+            assert st2["device_push_recv"] == 2, st2     # the answer to the 8 MiB view is dense: the peer pushed it
             client.stop()
 
         run(main())
@@ -150,7 +153,10 @@ def test_expandable_segment_tensors_cross_processes_on_the_device_paths():
     """Tensors from the tensor library's expandable segments (cuMemCreate allocations, which have no CUDA
     IPC handle) between two processes: eager, pulled and pushed, nothing staged through the host. Runs in
     processes of its own because the allocator reads its configuration once."""
-    env = dict(os.environ, PYTHONPATH=str(ROOT), PYTORCH_CUDA_ALLOC_CONF="expandable_segments:True", NCCL_NVLS_ENABLE="0")
+    # the eager limit is set to 64 KiB so that the 2 MiB and 3 MiB payloads are pulled out of the sender's
+    # segments by the receiver's kernel (by default they would be stored into the receiver's ring by the sender's)
+    env = dict(os.environ, PYTHONPATH=str(ROOT), PYTORCH_CUDA_ALLOC_CONF="expandable_segments:True", NCCL_NVLS_ENABLE="0",
+               EUX_DEV_EAGER_LIMIT="65536")
     out = subprocess.run([sys.executable, str(ROOT / "tests" / "mp_vmm_gpu.py")], env=env, cwd=str(ROOT), capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-2000:] + out.stderr[-4000:]
 
