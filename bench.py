@@ -380,7 +380,7 @@ def side_measurements(group, dev, rank, world, peaks, rpc, src):
             w.close()
             out8 = {}
             if fp8:
-                # no fp8 GEMM peak was measured on this pool: the nominal dense figure, labelled as such
+                # there is no measured fp8 GEMM peak to go by: the nominal dense figure, labelled as such
                 t8 = max(2.0 * m * n * k / 4.5e15 * 1e3, t_link)
                 out8 = {"roofline_ms_vs_nominal_fp8_peak_4500": round(t8, 4), "fraction_of_nominal_fp8_roofline": round(t8 / ms, 3),
                         "format": "MXFP8: e4m3 + UE8M0 scale per 32 elements, scaled in the tensor core" if fp8 == "mx"
