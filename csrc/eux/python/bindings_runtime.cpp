@@ -61,7 +61,7 @@ uintptr_t producer_stream(py::handle obj, int device) {
   return 0;
 }
 
-PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj, rpc::TensorMetaVec* metas = nullptr) {
+PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj, rpc::TensorMetaVec* metas = nullptr, int wire_dtype = 0) {
   if (obj.is_none()) return {};
   if (py::isinstance<PyBuffer>(obj)) {
     auto& b = obj.cast<PyBuffer&>();
@@ -91,7 +91,7 @@ PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handl
     if (cuda_device >= 0) vec.set_send_attr(make_send_attr(nullptr, cuda_device, producer_stream(first_cuda, cuda_device)));
     return vec;
   }
-  ImportedTensor t = import_tensor(obj, /*allow_strided=*/true);
+  ImportedTensor t = import_tensor(obj, /*allow_strided=*/true, wire_dtype);
   if (metas) metas->push_back(t.meta);
   std::shared_ptr<const ucxx::UcxSendAttr> attr;
   if (t.meta.device.device_type == kDLCUDA && t.nbytes > 0)
@@ -404,9 +404,9 @@ class PyAxonRuntime {
   // the exception it raises) settles the future: one loop iteration instead of a chained future.
   // `add_meta` (1: TENSOR_META, 2: TENSOR_META_VEC): describe the payload tensors in the header here.
   py::object invoke_raw(const std::string& worker_name, rpc::RpcRequestHeader header, py::object payload, py::object memory_policy,
-                        bool response_as_list, py::object transform, int add_meta) {
+                        bool response_as_list, py::object transform, int add_meta, int wire_dtype) {
     rpc::TensorMetaVec metas;
-    PayloadVariant p = payload_from_python(*mr_, payload, add_meta ? &metas : nullptr);
+    PayloadVariant p = payload_from_python(*mr_, payload, add_meta ? &metas : nullptr, wire_dtype);
     if (add_meta) append_tensor_metas(header.params, std::move(metas), add_meta);
     ClientMemoryPolicy pol = client_policy(memory_policy, response_as_list);
     if (response_as_list && !memory_policy.is_none()) pol.buffer_provider = nullptr;
@@ -529,12 +529,14 @@ class PyAxonRuntime {
                 }
                 py::object res = t.attr("result")();
                 py::object head = res, pay = py::none();
-                int add_meta = 0;  // third element: describe the payload tensors in the header here (see invoke_raw)
+                int add_meta = 0;    // third element: describe the payload tensors in the header here (see invoke_raw)
+                int wire_dtype = 0;  // fourth: the type in which a device tensor's elements travel
                 if (py::isinstance<py::tuple>(res) && py::len(res) >= 2) {
                   auto tup = res.cast<py::tuple>();
                   head = tup[0];
                   pay = tup[1];
                   if (py::len(res) >= 3) add_meta = tup[2].cast<int>();
+                  if (py::len(res) >= 4) wire_dtype = tup[3].cast<int>();
                 }
                 rpc::RpcResponseHeader h;
                 if (py::isinstance<rpc::RpcResponseHeader>(head)) {
@@ -547,7 +549,7 @@ class PyAxonRuntime {
                 h.session_id = st->req.session_id;
                 h.request_id = st->req.request_id;
                 rpc::TensorMetaVec metas;
-                PayloadVariant out = payload_from_python(*self->mr_, pay, add_meta ? &metas : nullptr);
+                PayloadVariant out = payload_from_python(*self->mr_, pay, add_meta ? &metas : nullptr, wire_dtype);
                 if (add_meta) append_tensor_metas(h.results, std::move(metas), add_meta);
                 if (settled->exchange(true)) return;
                 py::gil_scoped_release nogil;
@@ -661,7 +663,7 @@ void bind_runtime(py::module_& m) {
            py::arg("memory_policy") = py::none(), py::arg("lifecycle_policy") = py::none())
       .def("_invoke_native", &PyAxonRuntime::invoke_raw, py::arg("worker_name"), py::arg("request_header"), py::arg("payload") = py::none(),
            py::arg("memory_policy") = py::none(), py::arg("response_as_list") = false, py::arg("transform") = py::none(),
-           py::arg("add_meta") = 0)
+           py::arg("add_meta") = 0, py::arg("wire_dtype") = 0)
       .def("_gemm_add_weight", &PyAxonRuntime::gemm_add_weight, py::arg("weight_id"), py::arg("w_t"), py::arg("n"), py::arg("k"), py::arg("format"),
            py::arg("max_m"), py::arg("w_scale") = 0)
       .def("_remote_gemm", &PyAxonRuntime::remote_gemm, py::arg("worker_name"), py::arg("weight_id"), py::arg("m"), py::arg("x"), py::arg("x_bytes"),

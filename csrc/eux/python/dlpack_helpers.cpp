@@ -29,7 +29,7 @@ DLDevice device_of(ucx_memory_type_t type, int device_id) {
   }
 }
 
-ImportedTensor import_tensor(py::handle obj, bool allow_strided) {
+ImportedTensor import_tensor(py::handle obj, bool allow_strided, int wire_dtype) {
   if (!py::hasattr(obj, "__dlpack__")) throw py::type_error("object does not implement __dlpack__");
   py::object cap_obj = obj.attr("__dlpack__")();
   if (!PyCapsule_IsValid(cap_obj.ptr(), "dltensor")) throw py::value_error("__dlpack__ did not return an unused 'dltensor' capsule");
@@ -62,6 +62,37 @@ ImportedTensor import_tensor(py::handle obj, bool allow_strided) {
     throw;
   }
   t.data = static_cast<char*>(managed->dl_tensor.data) + managed->dl_tensor.byte_offset;
+  if (wire_dtype >= 1 && wire_dtype <= 3 && managed->dl_tensor.device.device_type == kDLCUDA && t.meta.ndim >= 1 &&
+      t.meta.ndim <= ucxx::kSendAttrMaxDims && t.meta.dtype.lanes <= 1) {
+    auto code_of = [](const DLDataType& d) -> int {
+      if (d.code == kDLFloat && d.bits == 32) return 1;
+      if (d.code == kDLFloat && d.bits == 16) return 2;
+      if (d.code == kDLBfloat && d.bits == 16) return 3;
+      return 0;
+    };
+    const int src = code_of(managed->dl_tensor.dtype);
+    bool sane = src != 0 && src != wire_dtype;
+    for (int i = 0; sane && i < t.meta.ndim; ++i) sane = t.meta.shape[i] > 0;
+    if (sane) {
+      if (!t.strided) t.src_strides.assign(managed->dl_tensor.strides ? managed->dl_tensor.strides : nullptr,
+                                           managed->dl_tensor.strides ? managed->dl_tensor.strides + t.meta.ndim : nullptr);
+      if (t.src_strides.empty()) t.src_strides.assign(t.meta.strides.begin(), t.meta.strides.end());  // compact: the row-major strides
+      bool nonneg = true;
+      for (auto v : t.src_strides) nonneg = nonneg && v >= 0;
+      if (nonneg) {
+        t.src_dtype = static_cast<uint8_t>(src);
+        t.dst_dtype = static_cast<uint8_t>(wire_dtype);
+        t.src_elem_size = src == 1 ? 4 : 2;
+        t.strided = true;  // described to the transport by a layout, dense or not
+        t.meta.dtype = wire_dtype == 1 ? DLDataType{kDLFloat, 32, 1} : (wire_dtype == 2 ? DLDataType{kDLFloat, 16, 1} : DLDataType{kDLBfloat, 16, 1});
+        int64_t st = 1;
+        for (int i = t.meta.ndim - 1; i >= 0; --i) {
+          t.meta.strides[i] = st;
+          st *= t.meta.shape[i];
+        }
+      }
+    }
+  }
   t.nbytes = rpc::utils::CalculateTensorSize(t.meta);
   if (t.meta.ndim == 0) t.nbytes = (t.meta.dtype.bits * (t.meta.dtype.lanes ? t.meta.dtype.lanes : 1) + 7) / 8;
   t.meta.byte_offset = 0;  // the payload starts at the first element
@@ -73,7 +104,9 @@ std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* on
   if (one && one->strided) {
     const auto& m = one->meta;
     attr->ndim = m.ndim;
-    attr->elem_size = (unsigned(m.dtype.bits) * (m.dtype.lanes ? m.dtype.lanes : 1) + 7) / 8;
+    attr->elem_size = one->src_elem_size ? one->src_elem_size : (unsigned(m.dtype.bits) * (m.dtype.lanes ? m.dtype.lanes : 1) + 7) / 8;
+    attr->src_dtype = one->src_dtype;
+    attr->dst_dtype = one->dst_dtype;
     uint64_t last = 0;
     for (int i = 0; i < m.ndim; ++i) {
       attr->shape[i] = m.shape[i];

@@ -32,11 +32,17 @@ struct ImportedTensor {
   // tensor that arrives at the other end; these are the strides it has here)
   bool strided = false;
   std::vector<int64_t> src_strides;
+  // the elements travel in another floating-point type (kernel codes: 1 fp32, 2 fp16, 3 bf16; 0: as they are);
+  // `meta` and `nbytes` then describe the converted tensor
+  uint8_t src_dtype = 0, dst_dtype = 0;
+  uint32_t src_elem_size = 0;
 };
 // Calls obj.__dlpack__() (any object that implements the protocol), takes the capsule's tensor.
 // Throws when the tensor is not compact (dense row-major), unless `allow_strided` and it lives on a CUDA
 // device with no negative stride and at most 8 dimensions: the transport gathers such a view itself.
-ImportedTensor import_tensor(py::handle obj, bool allow_strided = false);
+// `wire_dtype` (1 fp32, 2 fp16, 3 bf16; 0: none): a CUDA tensor of another one of these types is announced in
+// that type and converted by the transfer kernel on the way.
+ImportedTensor import_tensor(py::handle obj, bool allow_strided = false, int wire_dtype = 0);
 // The remarks for the transport about a device tensor that is about to be sent: its layout when it was
 // imported strided, and an event recorded now on the producer's stream (`stream`: a cudaStream_t as an
 // integer; 0: the legacy default stream), so that nobody has to wait for the producer here. Null for host tensors.

@@ -1028,6 +1028,8 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
           SendHint chk;
           chk.ndim = info.layout.ndim;
           chk.elem_size = info.layout.elem_size;
+          chk.src_dtype = info.layout.src_dtype;
+          chk.dst_dtype = info.layout.dst_dtype;
           std::memcpy(chk.shape, info.layout.shape, sizeof(chk.shape));
           std::memcpy(chk.stride, info.layout.stride, sizeof(chk.stride));
           chk.span_bytes = info.layout.span_bytes;
@@ -1257,7 +1259,9 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   if (strided) {
     WireLayout l;
     l.ndim = hint->ndim;
-    l.elem_size = hint->elem_size;
+    l.elem_size = static_cast<uint16_t>(hint->elem_size);
+    l.src_dtype = hint->src_dtype;
+    l.dst_dtype = hint->dst_dtype;
     std::memcpy(l.shape, hint->shape, sizeof(l.shape));
     std::memcpy(l.stride, hint->stride, sizeof(l.stride));
     l.span_bytes = hint->span_bytes;
@@ -1302,6 +1306,24 @@ void Worker::fill_gather(eux_xfer_desc* d, const WireLayout& l) {
   const int unit_dtype = l.elem_size == 1 ? EUX_DT_BYTES : (l.elem_size == 2 ? EUX_DT_F16 : EUX_DT_F32);
   d->src_dtype = d->dst_dtype = unit_dtype;
   d->op = EUX_OP_NONE;
+  if (l.src_dtype != l.dst_dtype) {  // converted on the way (the layout was checked: both are floating-point types of the kernel)
+    d->src_dtype = l.src_dtype;
+    d->dst_dtype = l.dst_dtype;
+    // a dense row-major source takes the vectorised kernel; anything else the element-wise one
+    bool dense = true;
+    int64_t expect = 1;
+    for (int i = l.ndim - 1; i >= 0 && dense; --i) {
+      dense = l.shape[i] == 1 || l.stride[i] == expect;
+      expect *= l.shape[i];
+    }
+    if (dense) {
+      uint64_t n = 1;
+      for (int i = 0; i < l.ndim; ++i) n *= static_cast<uint64_t>(l.shape[i]);
+      d->ndim = 0;
+      d->n_elems = n;
+      return;
+    }
+  }
   uint64_t n = 1;
   int nd = 0;
   for (int i = 0; i < l.ndim; ++i) {
@@ -1339,7 +1361,9 @@ std::shared_ptr<void> Worker::pack_local(const SendHint& h, const void* src) {
   });
   WireLayout l;
   l.ndim = h.ndim;
-  l.elem_size = h.elem_size;
+  l.elem_size = static_cast<uint16_t>(h.elem_size);
+  l.src_dtype = h.src_dtype;
+  l.dst_dtype = h.dst_dtype;
   std::memcpy(l.shape, h.shape, sizeof(l.shape));
   std::memcpy(l.stride, h.stride, sizeof(l.stride));
   eux_xfer_desc d{};
@@ -2103,7 +2127,9 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
     if (strided) {
       WireLayout l;
       l.ndim = hint->ndim;
-      l.elem_size = hint->elem_size;
+      l.elem_size = static_cast<uint16_t>(hint->elem_size);
+      l.src_dtype = hint->src_dtype;
+      l.dst_dtype = hint->dst_dtype;
       std::memcpy(l.shape, hint->shape, sizeof(l.shape));
       std::memcpy(l.stride, hint->stride, sizeof(l.stride));
       fill_gather(&d, l);

@@ -110,7 +110,8 @@ static_assert(sizeof(FrameHeader) == 40);
 // region descriptor of an RTS with kFlagLayout.
 struct WireLayout {
   int32_t ndim = 0;
-  uint32_t elem_size = 0;
+  uint16_t elem_size = 0;                  // of an element in the sender's memory
+  uint8_t src_dtype = 0, dst_dtype = 0;    // see UcxSendAttr
   int64_t shape[kSendAttrMaxDims] = {0};
   int64_t stride[kSendAttrMaxDims] = {0};
   uint64_t span_bytes = 0;

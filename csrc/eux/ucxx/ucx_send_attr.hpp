@@ -2,6 +2,8 @@
 //   * a layout: the payload is a strided view (a transposed or sliced tensor); the bytes that travel are its
 //     elements in row-major order, gathered by the transfer kernel on the way (into the peer's receive ring
 //     for a small message, by the receiver's pull for a large one), so the sender makes no dense copy first;
+//   * a cast: the elements travel in another floating-point type than they have in memory (fp32 activations
+//     as bf16, say), converted by the same kernel on the way; the message's size is that of the converted elements;
 //   * an event: the payload is complete once this CUDA event has completed (the producer's kernels may still
 //     be running when the send is issued). The transport orders its own kernels after the event on the
 //     device and holds back the announcement of a payload that a peer will read until the event is done;
@@ -24,7 +26,9 @@ struct UcxSendAttr {
   int64_t shape[kSendAttrMaxDims] = {0};
   int64_t stride[kSendAttrMaxDims] = {0};  // in elements, none negative: the buffer's address is that of element 0
   uint64_t span_bytes = 0;                // from element 0 to one past the last element touched
-  uint64_t dense_bytes = 0;               // number of elements * elem_size: the size of the buffer as a message
+  uint64_t dense_bytes = 0;               // the size of the buffer as a message: number of elements * element size on the wire
+  // ---- cast (both 0: the elements travel as they are) ----
+  uint8_t src_dtype = 0, dst_dtype = 0;   // kernel element types (eux_dtype: 1 fp32, 2 fp16, 3 bf16); elem_size is the source's
   // ---- readiness ----
   void* ready_event = nullptr;            // cudaEvent_t, or null: the payload is complete now
   int device = -1;                        // the device of the event
@@ -47,8 +51,15 @@ struct UcxSendAttr {
       n *= static_cast<unsigned __int128>(shape[i]);
       if (n > (static_cast<unsigned __int128>(1) << 48) || last > (static_cast<unsigned __int128>(1) << 48)) return false;
     }
-    return (last + 1) * elem_size <= span_bytes && n * elem_size == dense_bytes;
+    unsigned wire_size = elem_size;
+    if (src_dtype || dst_dtype) {
+      auto size_of = [](uint8_t dt) -> unsigned { return dt == 1 ? 4u : (dt == 2 || dt == 3 ? 2u : 0u); };
+      if (size_of(src_dtype) != elem_size || size_of(dst_dtype) == 0) return false;
+      wire_size = size_of(dst_dtype);
+    }
+    return (last + 1) * elem_size <= span_bytes && n * wire_size == dense_bytes;
   }
+  bool casts() const { return src_dtype != dst_dtype; }
 };
 
 }  // namespace eux::ucxx

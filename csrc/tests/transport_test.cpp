@@ -275,6 +275,18 @@ EUX_TEST(layout_of_a_strided_payload_is_checked_before_a_kernel_sees_it) {
   CHECK(bad([](UcxSendAttr& b) { b.ndim = 9; }));
   CHECK(bad([](UcxSendAttr& b) { b.dense_bytes += 4; }));         // the message would be longer than the elements
   CHECK(bad([](UcxSendAttr& b) { b.shape[1] = int64_t(1) << 50; b.stride[1] = 0; }));  // more elements than any message has
+  // converted on the way: fp32 in memory, bf16 on the wire; the message is half the size of the elements
+  UcxSendAttr c = a;
+  c.src_dtype = 1;
+  c.dst_dtype = 3;
+  CHECK(!c.layout_valid());           // ... so the dense size of the fp32 elements is wrong for it
+  c.dense_bytes = 300 * 70 * 2;
+  CHECK(c.layout_valid() && c.casts());
+  c.elem_size = 2;                    // the source's element size must be that of its type
+  CHECK(!c.layout_valid());
+  c.elem_size = 4;
+  c.dst_dtype = 9;                    // a type the kernel does not know
+  CHECK(!c.layout_valid());
   // a stride of zero (an expanded tensor) is fine: the span is smaller than the message
   UcxSendAttr e;
   e.ndim = 2;

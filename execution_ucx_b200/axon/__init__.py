@@ -209,6 +209,28 @@ def _contiguous(t, strided_ok: bool = False):
     return t
 
 
+def _wire_code(wire_dtype) -> int:
+    """Kernel code of the type in which a device tensor's elements shall travel (0: as they are)."""
+    if wire_dtype is None:
+        return 0
+    name = str(wire_dtype).rsplit(".", 1)[-1]
+    code = {"float32": 1, "float16": 2, "half": 2, "bfloat16": 3}.get(name)
+    if code is None:
+        raise ValueError(f"wire_dtype must be float32, float16 or bfloat16, not {wire_dtype}")
+    return code
+
+
+def _apply_wire_dtype(payload, wire_dtype):
+    """What the transfer kernel cannot convert on the way (host tensors, lists of tensors) is converted here."""
+    if wire_dtype is None or payload is None:
+        return payload
+    if isinstance(payload, list):
+        return [t.to(wire_dtype).contiguous() if hasattr(t, "is_floating_point") and t.is_floating_point() else t for t in payload]
+    if hasattr(payload, "is_floating_point") and payload.is_floating_point() and not getattr(payload, "is_cuda", False):
+        return payload.to(wire_dtype)
+    return payload
+
+
 def _reinterpret(piece, meta: TensorMeta, fn):
     """uint8 1-D view -> tensor of meta's dtype and shape (numpy or torch)."""
     code, bits = meta.dtype.code, meta.dtype.bits
@@ -645,9 +667,15 @@ class AxonRuntime(_axon.AxonRuntime):
         self._functions = {}
 
     # ---- server side ------------------------------------------------------------------------
-    def _register(self, fid: int, name: str, sig: _Sig, fn: Callable, memory_policy, lifecycle_policy) -> int:
-        async def handler(header, payload):
-            return _pack_results(sig, await fn(*_params_to_args(sig, header, payload)))
+    def _register(self, fid: int, name: str, sig: _Sig, fn: Callable, memory_policy, lifecycle_policy, wire_dtype=None) -> int:
+        code = _wire_code(wire_dtype)
+        if code:
+            async def handler(header, payload):
+                head, pay, add_meta = _pack_results(sig, await fn(*_params_to_args(sig, header, payload)))
+                return head, _apply_wire_dtype(pay, wire_dtype), add_meta, code
+        else:
+            async def handler(header, payload):
+                return _pack_results(sig, await fn(*_params_to_args(sig, header, payload)))
 
         ok = self._register_native(fid, name, sig.param_types, sig.return_types, sig.in_payload, sig.out_payload, handler,
                                    memory_policy, lifecycle_policy)
@@ -662,9 +690,11 @@ class AxonRuntime(_axon.AxonRuntime):
 
     def register_function(self, callable: Callable, function_id: Optional[int] = None, function_name: Optional[str] = None,
                           memory_policy: Optional[Callable] = None, lifecycle_policy: Optional[Callable] = None,
-                          from_dlpack_fn: Optional[Callable] = None) -> int:
+                          from_dlpack_fn: Optional[Callable] = None, wire_dtype=None) -> int:
         """Register ``async def callable(...)`` under ``function_id`` (default: the hash of its name and
-        this worker's name). Every parameter and the return need an annotation this layer can carry:
+        this worker's name). ``wire_dtype`` (float32, float16 or bfloat16; not in the reference): the floating-point
+        tensors the function returns travel in that type; a single CUDA tensor is converted by the transfer
+        kernel on its way, anything else before it is sent. Every parameter and the return need an annotation this layer can carry:
         ``int`` (INT64), ``float`` (FLOAT64), ``bool``, ``str``, a DLPack tensor type, ``List[...]`` of
         those, ``List[List[int|float|bool|Tensor]]``; ``Tuple[...]`` only as the return annotation."""
         if not _is_async_callable(callable):
@@ -687,7 +717,7 @@ class AxonRuntime(_axon.AxonRuntime):
                 "asked. Please provide from_dlpack_fn (e.g., numpy.from_dlpack, torch.from_dlpack, jax.dlpack.from_dlpack).")
         if from_dlpack_fn is not None:
             sig.param_from_dlpack = {i: from_dlpack_fn for i in sig.param_from_dlpack}
-        return self._register(fid, name, sig, callable, memory_policy, lifecycle_policy)
+        return self._register(fid, name, sig, callable, memory_policy, lifecycle_policy, wire_dtype)
 
     def register_function_raw(self, function_id: int, *args, **kwargs) -> int:
         """Two forms, as in the reference:
@@ -804,9 +834,11 @@ class AxonRuntime(_axon.AxonRuntime):
                                    lambda resp, pay: _results_to_python(resp, pay, None, fid, sid))
 
     def invoke(self, *args, worker_name: str, session_id: int, function, workflow_id: int = 0,
-               memory_policy: Optional[Callable] = None, from_dlpack_fn: Optional[Callable] = None):
+               memory_policy: Optional[Callable] = None, from_dlpack_fn: Optional[Callable] = None, wire_dtype=None):
         """Call ``function`` (an id, or a name hashed with the worker name) on ``worker_name`` with natural
-        arguments: values, tensors, lists of tensors, lists of lists of tensors. Returns a future of the
+        arguments: values, tensors, lists of tensors, lists of lists of tensors. ``wire_dtype`` (float32, float16
+        or bfloat16; not in the reference): floating-point tensor arguments travel in that type, a single CUDA
+        tensor converted by the transfer kernel on its way (no converted copy is made first). Returns a future of the
         result: a single value, or a tuple of values, tensors included."""
         if isinstance(function, bool) or not isinstance(function, (int, str)):
             raise ValueError("function must be int (ID) or str (name)")
@@ -837,8 +869,8 @@ class AxonRuntime(_axon.AxonRuntime):
         payload, add_meta = _tensor_payload(tensors, len(tensors) > 1)
         fn = from_dlpack_fn or (_default_from_dlpack(sample) if sample is not None else None)
         # the response is unpacked on the loop thread by the binding itself and settles the future
-        return self._invoke_native(worker_name, header, payload, memory_policy, False,
-                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id), add_meta)
+        return self._invoke_native(worker_name, header, _apply_wire_dtype(payload, wire_dtype), memory_policy, False,
+                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id), add_meta, _wire_code(wire_dtype))
 
 
 

@@ -223,3 +223,65 @@ def test_strided_and_unfinished_tensors(cuda_device):
         server.stop()
 
     run(main())
+
+
+def test_tensors_converted_on_the_way(cuda_device):
+    """``wire_dtype``: fp32 tensors travel as bf16 (or fp16), converted by the transfer kernel while it moves
+    them: into the ring slot for a small one, by the receiver's pull for a large or a strided one. What arrives
+    is the tensor rounded once to the wire type, and the function's fp32 result can come back the same way."""
+    from execution_ucx_b200 import axon
+
+    async def main():
+        server = axon.AxonRuntime("cv_server", timeout=20000, device=axon.cuda(0))
+        client = axon.AxonRuntime("cv_client", timeout=20000, device=axon.cuda(0))
+        table = {(2, 32): torch.float32, (2, 16): torch.float16, (4, 16): torch.bfloat16}
+        seen = []
+
+        def on_device(metas):
+            m = metas[0]
+            return torch.empty(m.shape, dtype=table[(m.dtype.code, m.dtype.bits)], device="cuda:0")
+
+        async def what_arrived(x: torch.Tensor) -> torch.Tensor:
+            seen.append((x.dtype, tuple(x.shape)))
+            return x
+
+        async def as_fp32(x: torch.Tensor) -> torch.Tensor:
+            return x.float() * 2.0
+
+        server.register_function(what_arrived, memory_policy=on_device)
+        server.register_function(as_fp32, memory_policy=on_device, wire_dtype=torch.bfloat16)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "cv_server")
+        cases = [
+            (torch.randn(1000, device="cuda:0"), torch.bfloat16),                       # 2 KiB on the wire: eager, converted on its way into the ring slot
+            (torch.randn(1 << 20, device="cuda:0"), torch.bfloat16),                    # 2 MiB on the wire: eager, several CTAs
+            (torch.randn(1 << 23, device="cuda:0"), torch.bfloat16),                    # 16 MiB on the wire: converted by the receiver's pull
+            (torch.randn(1 << 23, device="cuda:0")[3:], torch.float16),                 # an unaligned start: the element-wise kernel
+            (torch.randn(2048, 1500, device="cuda:0").t(), torch.bfloat16),             # strided and converted at once
+            (torch.randn(4096, device="cuda:0").to(torch.bfloat16), torch.float32),     # widening
+        ]
+        for x, wire in cases:
+            y = await client.invoke(x, worker_name="cv_server", session_id=1, function="what_arrived", memory_policy=on_device, wire_dtype=wire)
+            assert seen[-1] == (wire, tuple(x.shape)), (seen[-1], wire, x.shape)
+            assert y.dtype == wire and y.shape == x.shape
+            assert torch.equal(y, x.contiguous().to(wire)), (x.shape, x.dtype, wire)
+            del y
+        st = client.transport_stats()
+        assert st["device_packs"] == 0 and st["device_staged"] == 0, st
+        # the same value without wire_dtype travels as it is
+        x = torch.randn(1000, device="cuda:0")
+        y = await client.invoke(x, worker_name="cv_server", session_id=1, function="what_arrived", memory_policy=on_device)
+        assert y.dtype == torch.float32 and torch.equal(y, x)
+        # a function whose fp32 results travel as bf16
+        x = torch.randn(1 << 22, device="cuda:0").to(torch.bfloat16)
+        y = await client.invoke(x, worker_name="cv_server", session_id=1, function="as_fp32", memory_policy=on_device)
+        assert y.dtype == torch.bfloat16 and torch.equal(y, (x.float() * 2.0).to(torch.bfloat16))
+        # host tensors are converted before they are sent
+        h = torch.randn(64)
+        y = await client.invoke(h, worker_name="cv_server", session_id=1, function="what_arrived", wire_dtype=torch.bfloat16)
+        assert y.dtype == torch.bfloat16 and torch.equal(y.cpu(), h.to(torch.bfloat16))
+        client.stop()
+        server.stop()
+
+    run(main())
