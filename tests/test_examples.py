@@ -22,9 +22,11 @@ def test_pytorch_cpu_example():
     assert "add_all: [[1.0, 1.0, 1.0], [2.0, 2.0, 2.0, 2.0, 2.0]]" in out.stdout
 
 
-def test_jax_example_is_gated():
+def test_foreign_array_example():
+    """With JAX where it is installed, else with an array type that offers the DLPack protocol and nothing more."""
     out = _run("execution_ucx_b200.axon.examples.jax_example")
     assert out.returncode == 0, out.stderr[-2000:]
+    assert "[0.0, 2.0, 4.0, 6.0, 8.0, 10.0, 12.0, 14.0]" in out.stdout, out.stdout
 
 
 @pytest.mark.gpu
