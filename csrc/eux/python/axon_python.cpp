@@ -4,7 +4,10 @@
 
 #include <cstdlib>
 
+#include <cuda_runtime_api.h>
+
 #include "bindings_common.hpp"
+#include "eux/ucxx/transport.hpp"
 
 namespace {
 // With EUX_BACKTRACE=1 in the environment a fatal signal prints the native call
@@ -21,8 +24,41 @@ void fatal_signal_backtrace(int sig) {
 }
 }  // namespace
 
+namespace {
+namespace py = pybind11;
+// Where the consumers of a received device tensor queue their work, as far as this layer can know: the tensor
+// library's current stream on the thread that drops the tensor (it is dropped right after the code that used
+// it). An event recorded there tells the transport when the ring slot under the tensor may be written again.
+void* consumer_event_on_torch_stream(int device) {
+  if (!Py_IsInitialized() || !PyGILState_Check()) return nullptr;  // not a Python thread: the transport's default applies
+  try {
+    py::object modules = py::module_::import("sys").attr("modules");
+    if (!modules.contains("torch")) return nullptr;
+    py::object cuda = modules["torch"].attr("cuda");
+    if (!cuda.attr("is_initialized")().cast<bool>()) return nullptr;
+    const auto stream = cuda.attr("current_stream")(device).attr("cuda_stream").cast<uintptr_t>();
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) return nullptr;
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess &&
+        cudaEventRecord(ev, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
+      cudaEventDestroy(ev);
+      ev = nullptr;
+    }
+    cudaGetLastError();
+    if (prev != device && prev >= 0) cudaSetDevice(prev);
+    return ev;
+  } catch (...) {
+    PyErr_Clear();
+    return nullptr;
+  }
+}
+}  // namespace
+
 PYBIND11_MODULE(_axon, m) {
   m.doc() = "Axon tensor RPC runtime (native part)";
+  eux::ucxx::transport::set_consumer_event_hook(&consumer_event_on_torch_stream);
   if (const char* e = std::getenv("EUX_BACKTRACE"); e && e[0] == '1') {
     // its own stack, so that a stack overflow can still be reported
     static char alt_stack[1 << 16];

@@ -586,6 +586,7 @@ int Worker::progress() {
   }
   if (!pull_batch_.empty()) flush_pull_batch();
   if (!held_sends_.empty()) poll_held_sends();
+  drain_slot_releases();
   if (!device_ops_.empty() || !eager_waits_.empty() || !push_waits_.empty()) poll_device();
   if (!graveyard_.empty()) {
     for (Endpoint* ep : graveyard_) eps_.erase(ep);
@@ -683,6 +684,60 @@ std::atomic<bool> g_fault_on{false};
 }  // namespace
 
 bool is_live_local_uid(uint64_t uid) { return live_has(uid); }
+
+namespace {
+std::atomic<ConsumerEventHook> g_consumer_event_hook{nullptr};
+struct SlotRelease {  // slots waiting for the consumer's queued GPU work before they go back to the sender
+  void* event;
+  int device;
+  std::shared_ptr<ShmChannel> shm;
+  uint64_t mask;
+};
+std::mutex g_slot_release_mu;
+std::vector<SlotRelease> g_slot_releases;
+std::atomic<size_t> g_slot_release_count{0};
+
+void* record_consumer_event(int device) {
+  if (auto hook = g_consumer_event_hook.load(std::memory_order_acquire))
+    if (void* ev = hook(device)) return ev;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != device && cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  cudaEvent_t ev = nullptr;
+  if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess && cudaEventRecord(ev, cudaStreamLegacy) != cudaSuccess) {
+    cudaEventDestroy(ev);
+    ev = nullptr;
+  }
+  cudaGetLastError();
+  if (prev != device && prev >= 0) cudaSetDevice(prev);
+  return ev;
+}
+}  // namespace
+
+void set_consumer_event_hook(ConsumerEventHook hook) { g_consumer_event_hook.store(hook, std::memory_order_release); }
+
+// Any worker of the process hands back the slots whose consumers have finished (the entry owns what it touches).
+void Worker::drain_slot_releases() {
+  if (g_slot_release_count.load(std::memory_order_acquire) == 0) return;
+  std::unique_lock lk(g_slot_release_mu, std::try_to_lock);
+  if (!lk.owns_lock()) return;
+  for (size_t i = 0; i < g_slot_releases.size();) {
+    auto& r = g_slot_releases[i];
+    if (cudaEventQuery(static_cast<cudaEvent_t>(r.event)) == cudaErrorNotReady) {
+      ++i;
+      continue;
+    }
+    cudaGetLastError();
+    cudaEventDestroy(static_cast<cudaEvent_t>(r.event));
+    r.shm->out_words()[0].fetch_or(r.mask, std::memory_order_release);
+    if (i + 1 != g_slot_releases.size()) g_slot_releases[i] = std::move(g_slot_releases.back());
+    g_slot_releases.pop_back();
+  }
+  g_slot_release_count.store(g_slot_releases.size(), std::memory_order_release);
+}
 
 void set_fault_hook(FaultHook hook) {
   std::lock_guard lk(g_fault_mu);
@@ -2209,12 +2264,23 @@ void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body)
     std::shared_ptr<ShmChannel> shm;
     std::shared_ptr<Endpoint::DevRing> ring;
     uint64_t mask;  // the slots of the payload's run
-    SlotToken(std::shared_ptr<ShmChannel> s, std::shared_ptr<Endpoint::DevRing> r, uint64_t m) : shm(std::move(s)), ring(std::move(r)), mask(m) {}
+    int device;
+    SlotToken(std::shared_ptr<ShmChannel> s, std::shared_ptr<Endpoint::DevRing> r, uint64_t m, int dev)
+        : shm(std::move(s)), ring(std::move(r)), mask(m), device(dev) {}
     SlotToken(const SlotToken&) = delete;  // exactly one object stands for the slots: its end hands them back
     SlotToken& operator=(const SlotToken&) = delete;
-    ~SlotToken() { shm->out_words()[0].fetch_or(mask, std::memory_order_release); }
+    ~SlotToken() {
+      // ... once the GPU work that the application queued to read them has run (see set_consumer_event_hook)
+      if (void* ev = record_consumer_event(device)) {
+        std::lock_guard lk(g_slot_release_mu);
+        g_slot_releases.push_back({ev, device, shm, mask});
+        g_slot_release_count.store(g_slot_releases.size(), std::memory_order_release);
+      } else {
+        shm->out_words()[0].fetch_or(mask, std::memory_order_release);
+      }
+    }
   };
-  a.data_keep = std::make_shared<SlotToken>(w.shm, w.ring, ((uint64_t(1) << run) - 1) << slot);
+  a.data_keep = std::make_shared<SlotToken>(w.shm, w.ring, ((uint64_t(1) << run) - 1) << slot, opt_.device);
   eager_waits_.push_back(std::move(w));
 }
 

@@ -62,6 +62,16 @@ using Completion = std::function<void(int status)>;
 using FaultHook = std::function<bool(const std::string& worker_name, uint8_t frame_type, uint64_t msg_id)>;
 void set_fault_hook(FaultHook hook);
 
+// A device payload that arrived eagerly lies in a slot of the receive ring and is handed to the application as
+// it lies. When the application drops it, work that it queued on the GPU to read the slot may not have run yet,
+// so the slot is handed back to the sender only after an event recorded at that moment has completed. By
+// default the event is recorded on the device's legacy default stream (which every blocking stream
+// synchronises with). A layer that knows better which stream its consumers use (the Python binding: the
+// tensor library's current stream) installs a function that records the event there and returns it (a
+// cudaEvent_t that the transport destroys), or null to fall back to the default.
+using ConsumerEventHook = void* (*)(int device);
+void set_consumer_event_hook(ConsumerEventHook hook);
+
 // True when a worker with this uid (the random number in its address) is alive in this process. A peer
 // is taken to be "this process" only on that evidence, never on a pid that came over the wire.
 bool is_live_local_uid(uint64_t uid);
@@ -427,6 +437,7 @@ class Worker {
   bool ensure_device();
   void poll_device();
   void poll_held_sends();
+  static void drain_slot_releases();
   std::deque<HeldSend> held_sends_;
   // strided source -> dense device buffer of this worker's pool (the fallback when the gather cannot be fused
   // into the transfer); null on failure. Returns after the copy has finished.

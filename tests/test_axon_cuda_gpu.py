@@ -285,3 +285,137 @@ def test_tensors_converted_on_the_way(cuda_device):
         server.stop()
 
     run(main())
+
+
+def test_many_mixed_calls_in_flight(cuda_device):
+    """Several hundred calls of random size (256 B to 24 MiB), dense, strided or converted, up to 24 in flight at
+    once, between a client and a server runtime: eager runs of ring slots, pulls, pushes and held announcements
+    all mix, slots run out and come back, and every reply is checked."""
+    import random
+
+    from execution_ucx_b200 import axon
+
+    async def main():
+        server = axon.AxonRuntime("mix_server", timeout=60000, device=axon.cuda(0))
+        client = axon.AxonRuntime("mix_client", timeout=60000, device=axon.cuda(0))
+        table = {(2, 32): torch.float32, (2, 16): torch.float16, (4, 16): torch.bfloat16}
+
+        def on_device(metas):
+            m = metas[0]
+            return torch.empty(m.shape, dtype=table[(m.dtype.code, m.dtype.bits)], device="cuda:0")
+
+        async def scale(x: torch.Tensor, k: float) -> torch.Tensor:
+            return x * k
+
+        server.register_function(scale, memory_policy=on_device)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "mix_server")
+        rng = random.Random(1234)
+        sem = asyncio.Semaphore(24)
+        failures = []
+
+        async def one(i: int):
+            async with sem:
+                kind = rng.choice(("dense", "dense", "strided", "cast", "fresh"))
+                n = int(2 ** rng.uniform(6, 22.5))                       # elements
+                if kind == "strided":
+                    rows = max(2, int(n ** 0.5))
+                    x = torch.randn(rows, rows + 3, device="cuda:0")[:, 1:-2].t()
+                    want_dtype, wire = torch.float32, None
+                elif kind == "cast":
+                    x = torch.randn(n, device="cuda:0")
+                    want_dtype, wire = torch.bfloat16, torch.bfloat16
+                elif kind == "fresh":
+                    # produced on a side stream right before the call: the send must wait for it on the device
+                    s = torch.cuda.Stream(device="cuda:0")
+                    s.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(s):
+                        x = torch.zeros(n, device="cuda:0")
+                        torch.cuda._sleep(2_000_000)
+                        x.add_(float(i % 97))
+                        fut = client.invoke(x, 2.0, worker_name="mix_server", session_id=i, function="scale", memory_policy=on_device)
+                    y = await fut
+                    torch.cuda.current_stream().wait_stream(s)
+                    if not (float(y.min()) == float(y.max()) == 2.0 * (i % 97)):
+                        failures.append((i, kind, n, float(y.min()), float(y.max())))
+                    return
+                else:
+                    x = torch.randn(n, device="cuda:0")
+                    want_dtype, wire = torch.float32, None
+                y = await client.invoke(x, 2.0, worker_name="mix_server", session_id=i, function="scale", memory_policy=on_device, wire_dtype=wire)
+                ref = (x.contiguous().to(want_dtype) * 2.0)
+                if y.dtype != want_dtype or y.shape != x.shape or not torch.equal(y, ref):
+                    failures.append((i, kind, tuple(x.shape), y.dtype))
+
+        await asyncio.gather(*[one(i) for i in range(400)])
+        assert not failures, failures[:5]
+        cs, ss = client.transport_stats(), server.transport_stats()
+        assert cs["device_staged"] == 0 and ss["device_staged"] == 0, (cs, ss)
+        assert cs["device_eager_sent"] > 0 and cs["device_pushes"] + ss["device_pulls"] > 0, (cs, ss)
+        client.stop()
+        server.stop()
+
+    run(main())
+
+
+def test_many_mixed_calls_between_processes():
+    """The same mix against a server in another process (on GPU 1 where there is one): the payloads cross
+    through mapped peer memory, the flags through the shared page, and slots come back through the segment."""
+    import random
+
+    server_dev = 1 if torch.cuda.device_count() > 1 else 0
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    child = subprocess.Popen([sys.executable, "-m", "execution_ucx_b200.models.echo_server", "--device", str(server_dev), "--name", "mix_peer",
+                              "--timeout-ms", "60000"], stdout=subprocess.PIPE, stdin=subprocess.PIPE, env=env, cwd=str(ROOT))
+    try:
+        line = child.stdout.readline().decode().strip()
+        assert line.startswith("ADDRESS "), line
+        address = bytes.fromhex(line.split()[1])
+        from execution_ucx_b200 import axon
+
+        async def main():
+            client = axon.AxonRuntime("mix_client2", timeout=60000, device=axon.cuda(0))
+            client.start_client()
+            await client.connect_endpoint_async(address, "mix_peer")
+            table = {(2, 32): torch.float32, (2, 16): torch.float16, (4, 16): torch.bfloat16}
+
+            def on_device(metas):
+                m = metas[0]
+                return torch.empty(m.shape, dtype=table[(m.dtype.code, m.dtype.bits)], device="cuda:0")
+
+            rng = random.Random(99)
+            sem = asyncio.Semaphore(24)
+            failures = []
+
+            async def one(i: int):
+                async with sem:
+                    kind = rng.choice(("dense", "dense", "strided", "cast"))
+                    n = int(2 ** rng.uniform(6, 22.5))
+                    wire = None
+                    if kind == "strided":
+                        rows = max(2, int(n ** 0.5))
+                        x = torch.randn(rows, rows + 3, device="cuda:0")[:, 1:-2].t()
+                    else:
+                        x = torch.randn(n, device="cuda:0")
+                        if kind == "cast":
+                            wire = torch.bfloat16
+                    y = await client.invoke(x, worker_name="mix_peer", session_id=i, function="add_one", memory_policy=on_device, wire_dtype=wire)
+                    ref = x.contiguous().to(wire or torch.float32) + 1.0
+                    if y.dtype != ref.dtype or y.shape != x.shape or not torch.equal(y, ref):
+                        failures.append((i, kind, tuple(x.shape), y.dtype))
+
+            await asyncio.gather(*[one(i) for i in range(300)])
+            assert not failures, failures[:5]
+            st = client.transport_stats()
+            assert st["device_staged"] == 0 and st["device_eager_sent"] > 0 and st["device_packs"] == 0, st
+            client.stop()
+
+        run(main())
+    finally:
+        try:
+            child.stdin.write(b"quit\n")
+            child.stdin.flush()
+            child.wait(timeout=30)
+        except Exception:
+            child.kill()
