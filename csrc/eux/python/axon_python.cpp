@@ -7,6 +7,7 @@
 #include <cuda_runtime_api.h>
 
 #include "bindings_common.hpp"
+#include "dlpack_helpers.hpp"
 #include "eux/ucxx/transport.hpp"
 
 namespace {
@@ -29,36 +30,48 @@ namespace py = pybind11;
 // Where the consumers of a received device tensor queue their work, as far as this layer can know: the tensor
 // library's current stream on the thread that drops the tensor (it is dropped right after the code that used
 // it). An event recorded there tells the transport when the ring slot under the tensor may be written again.
-void* consumer_event_on_torch_stream(int device) {
-  if (!Py_IsInitialized() || !PyGILState_Check()) return nullptr;  // not a Python thread: the transport's default applies
-  try {
-    py::object modules = py::module_::import("sys").attr("modules");
-    if (!modules.contains("torch")) return nullptr;
-    py::object cuda = modules["torch"].attr("cuda");
-    if (!cuda.attr("is_initialized")().cast<bool>()) return nullptr;
-    const auto stream = cuda.attr("current_stream")(device).attr("cuda_stream").cast<uintptr_t>();
-    int prev = -1;
-    cudaGetDevice(&prev);
-    if (prev != device && cudaSetDevice(device) != cudaSuccess) return nullptr;
-    cudaEvent_t ev = nullptr;
-    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess &&
-        cudaEventRecord(ev, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
-      cudaEventDestroy(ev);
-      ev = nullptr;
+int consumer_event_on_torch_stream(int device, void** event) {
+  namespace tr = eux::ucxx::transport;
+  uintptr_t stream = 0;  // not a Python thread, or no torch: the legacy default stream, with which blocking streams synchronise
+  if (Py_IsInitialized() && PyGILState_Check()) {
+    try {
+      py::object modules = py::module_::import("sys").attr("modules");
+      if (modules.contains("torch")) {
+        py::object cuda = modules["torch"].attr("cuda");
+        if (cuda.attr("is_initialized")().cast<bool>()) stream = cuda.attr("current_stream")(device).attr("cuda_stream").cast<uintptr_t>();
+      }
+    } catch (...) {
+      PyErr_Clear();
     }
-    cudaGetLastError();
-    if (prev != device && prev >= 0) cudaSetDevice(prev);
-    return ev;
-  } catch (...) {
-    PyErr_Clear();
-    return nullptr;
   }
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != device && cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return tr::kConsumerDone;
+  }
+  cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : cudaStreamLegacy;
+  int state = tr::kConsumerDone;
+  if (cudaStreamQuery(st) == cudaErrorNotReady) {  // something is queued there: the slot waits for it
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) {
+      if (cudaEventRecord(ev, st) == cudaSuccess) {
+        *event = ev;
+        state = tr::kConsumerEvent;
+      } else {
+        cudaEventDestroy(ev);
+      }
+    }
+  }
+  cudaGetLastError();
+  if (prev != device && prev >= 0) cudaSetDevice(prev);
+  return state;
 }
 }  // namespace
 
 PYBIND11_MODULE(_axon, m) {
   m.doc() = "Axon tensor RPC runtime (native part)";
-  eux::ucxx::transport::set_consumer_event_hook(&consumer_event_on_torch_stream);
+  if (eux::python::stream_ordering_enabled()) eux::ucxx::transport::set_consumer_event_hook(&consumer_event_on_torch_stream);
   if (const char* e = std::getenv("EUX_BACKTRACE"); e && e[0] == '1') {
     // its own stack, so that a stack overflow can still be reported
     static char alt_stack[1 << 16];

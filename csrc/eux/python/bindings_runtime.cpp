@@ -380,8 +380,20 @@ class PyAxonRuntime {
       const bool on_gpu = py::hasattr(out, "is_cuda") && out.attr("is_cuda").cast<bool>();
       remember_owner(data, out);
       auto keep = gil_shared(out);
-      return UcxBuffer(mr, on_gpu ? ucx_memory_type::CUDA : ucx_memory_type::HOST, data, bytes, nullptr, true,
-                       [keep](void*) mutable { keep.reset(); });
+      UcxBuffer buf(mr, on_gpu ? ucx_memory_type::CUDA : ucx_memory_type::HOST, data, bytes, nullptr, true,
+                    [keep](void*) mutable { keep.reset(); });
+      if (on_gpu && bytes) {
+        // memory fresh from the tensor library's allocator may still be in use by work queued on its stream
+        // before it was handed out: the transport writes it after that work (an event on that stream)
+        int device = 0;
+        try {
+          device = out.attr("device").attr("index").cast<int>();
+        } catch (const std::exception&) {
+          PyErr_Clear();
+        }
+        buf.set_send_attr(make_send_attr(nullptr, device, producer_stream(out, device)));
+      }
+      return buf;
     } catch (py::error_already_set&) {
       return std::nullopt;  // not that kind of object after all: the DLPack road
     }

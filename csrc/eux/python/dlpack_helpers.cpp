@@ -2,6 +2,7 @@
 
 #include <cuda_runtime_api.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -99,6 +100,14 @@ ImportedTensor import_tensor(py::handle obj, bool allow_strided, int wire_dtype)
   return t;
 }
 
+bool stream_ordering_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("EUX_STREAM_ORDERING");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* one, int device, uintptr_t stream) {
   auto attr = std::make_shared<ucxx::UcxSendAttr>();
   if (one && one->strided) {
@@ -119,9 +128,17 @@ std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* on
   int prev = -1;
   cudaGetDevice(&prev);
   if (prev != device) cudaSetDevice(device);
+  cudaStream_t producer = stream ? reinterpret_cast<cudaStream_t>(stream) : cudaStreamLegacy;
+  if (!stream_ordering_enabled() || cudaStreamQuery(producer) == cudaSuccess) {
+    // nothing is queued on the producer's stream: the tensor is complete (and free to be written) as it is
+    if (prev != device && prev >= 0) cudaSetDevice(prev);
+    if (attr->ndim == 0) return nullptr;
+    return attr;
+  }
+  cudaGetLastError();
   cudaEvent_t ev = nullptr;
   if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) {
-    if (cudaEventRecord(ev, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess) {
+    if (cudaEventRecord(ev, producer) == cudaSuccess) {
       attr->ready_event = ev;
       attr->device = device;
       attr->keep = std::shared_ptr<void>(ev, [device](void* e) {
@@ -139,7 +156,7 @@ std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* on
   if (prev != device && prev >= 0) cudaSetDevice(prev);
   if (!attr->ready_event) {
     // no event to go by: wait here, once, so that what is sent is at least complete
-    cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream));
+    cudaStreamSynchronize(producer);
     cudaGetLastError();
     if (attr->ndim == 0) return nullptr;
   }

@@ -46,6 +46,10 @@ ImportedTensor import_tensor(py::handle obj, bool allow_strided = false, int wir
 // The remarks for the transport about a device tensor that is about to be sent: its layout when it was
 // imported strided, and an event recorded now on the producer's stream (`stream`: a cudaStream_t as an
 // integer; 0: the legacy default stream), so that nobody has to wait for the producer here. Null for host tensors.
+// EUX_STREAM_ORDERING=0 turns off everything this layer does to order the transport after the tensor library's
+// streams (events behind producers, behind the previous users of receive buffers, behind the consumers of ring
+// slots), for applications that synchronise their streams themselves before they send and after they receive.
+bool stream_ordering_enabled();
 std::shared_ptr<const ucxx::UcxSendAttr> make_send_attr(const ImportedTensor* one, int device, uintptr_t stream);
 // A non-copying buffer over the tensor; releasing it calls the DLPack deleter (under the GIL).
 ucxx::UcxBuffer to_ucx_buffer(ucxx::UcxMemoryResourceManager& mr, ImportedTensor&& t);

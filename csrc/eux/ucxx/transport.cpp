@@ -698,22 +698,10 @@ std::vector<SlotRelease> g_slot_releases;
 std::atomic<size_t> g_slot_release_count{0};
 
 void* record_consumer_event(int device) {
+  void* ev = nullptr;
   if (auto hook = g_consumer_event_hook.load(std::memory_order_acquire))
-    if (void* ev = hook(device)) return ev;
-  int prev = -1;
-  cudaGetDevice(&prev);
-  if (prev != device && cudaSetDevice(device) != cudaSuccess) {
-    cudaGetLastError();
-    return nullptr;
-  }
-  cudaEvent_t ev = nullptr;
-  if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess && cudaEventRecord(ev, cudaStreamLegacy) != cudaSuccess) {
-    cudaEventDestroy(ev);
-    ev = nullptr;
-  }
-  cudaGetLastError();
-  if (prev != device && prev >= 0) cudaSetDevice(prev);
-  return ev;
+    if (hook(device, &ev) == kConsumerEvent) return ev;
+  return nullptr;
 }
 }  // namespace
 
@@ -1194,7 +1182,7 @@ void Worker::dispatch_frame(Endpoint* ep, const FrameHeader& fh, const char* bod
         if (fh.status == UCS_ERR_UNSUPPORTED) {
           w.info.push_ok = false;
           ep->rts_[w.msg_id] = std::move(w.info);
-          int st = rndv_recv(ep, w.msg_id, w.segs.data(), w.segs.size(), ucx_memory_type::CUDA, w.done);
+          int st = rndv_recv(ep, w.msg_id, w.segs.data(), w.segs.size(), ucx_memory_type::CUDA, w.done, w.ready);
           if (st != UCS_INPROGRESS && w.done) w.done(st);
         } else if (w.done) {
           w.done(fh.status);
@@ -1489,7 +1477,8 @@ std::vector<uint64_t> Worker::rndv_segment_sizes(Endpoint* ep, uint64_t msg_id) 
 }
 
 int Worker::rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, size_t seg_count, ucx_memory_type_t mem_type,
-                      Completion done) {
+                      Completion done, std::shared_ptr<const SendHint> ready) {
+  if (ready && !ready->ready_event) ready.reset();
   if (!eps_.count(ep) || ep->state_ != Endpoint::State::kConnected) return UCS_ERR_NOT_CONNECTED;
   auto rit = ep->rts_.find(msg_id);
   if (rit == ep->rts_.end()) return UCS_ERR_NO_MESSAGE;
@@ -1503,11 +1492,11 @@ int Worker::rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, s
   }
   const bool dst_device = is_device_type(mem_type);
   if (info.push_ok && !info.has_layout && dst_device && !info.regions.empty() && ep->shm_active_ && opt_.push_threshold) {
-    int st = request_push(ep, msg_id, info, segs, seg_count, done);
+    int st = request_push(ep, msg_id, info, segs, seg_count, done, ready);
     if (st == UCS_INPROGRESS) return st;  // otherwise: pull it
   }
   if (!info.regions.empty() && dst_device) {
-    int st = device_pull(ep, msg_id, info, segs, seg_count, done);
+    int st = device_pull(ep, msg_id, info, segs, seg_count, done, ready);
     if (st == UCS_INPROGRESS || st == UCS_OK) {
       ++stats_.device_pulls;
       return st;
@@ -1638,8 +1627,10 @@ bool Worker::ensure_device() {
 // device segments with the transfer kernel; the last launch publishes a sequence
 // number in pinned host memory that poll_device() watches.
 int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
-                        Completion& done) {
+                        Completion& done, const std::shared_ptr<const SendHint>& ready) {
   if (!cuda_mr_ || !ensure_device()) return UCS_ERR_UNSUPPORTED;
+  // the destination may still be in use by work queued before it was handed out: this worker's kernels come after it
+  if (ready) cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_), static_cast<cudaEvent_t>(ready->ready_event), 0);
   NvtxRange range("eux.transport.device_pull");
   std::vector<void*> srcs(info.regions.size());
   for (size_t i = 0; i < info.regions.size(); ++i) {
@@ -1666,7 +1657,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
     }
     ++stats_.kernel_launches;
     ++stats_.device_gathers;
-    device_ops_.push_back({seq, ep, msg_id, std::move(done)});
+    device_ops_.push_back({seq, ep, msg_id, std::move(done), true, ready});
     return UCS_INPROGRESS;
   }
   // walk source regions and destination segments together
@@ -1695,7 +1686,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
   if (pieces.size() == 1 && pieces[0].n <= kBatchMaxBytes) {
     // a small message: it leaves with the others of this pass in one launch
     pull_batch_.push_back({pieces[0].s, pieces[0].d, pieces[0].n, flag, seq});
-    device_ops_.push_back({seq, ep, msg_id, std::move(done)});
+    device_ops_.push_back({seq, ep, msg_id, std::move(done), true, ready});
     if (pull_batch_.size() == EUX_PULL_BATCH_MAX) flush_pull_batch();
     return UCS_INPROGRESS;
   }
@@ -1718,7 +1709,7 @@ int Worker::device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, 
     }
     ++stats_.kernel_launches;
   }
-  device_ops_.push_back({seq, ep, msg_id, std::move(done)});
+  device_ops_.push_back({seq, ep, msg_id, std::move(done), true, ready});
   return UCS_INPROGRESS;
 }
 
@@ -2287,7 +2278,7 @@ void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body)
 // Receiver side of a pushed rendezvous: answer the RTS with the posted buffers' regions and the flag word
 // the sender's kernel shall raise when the bytes are in place.
 int Worker::request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
-                         Completion& done) {
+                         Completion& done, const std::shared_ptr<const SendHint>& ready) {
   if (!cuda_mr_ || ep->push_inflight_ + 1 >= kPushWords || seg_count > kMaxSegCount) return UCS_ERR_UNSUPPORTED;
   std::vector<PeerRegionDesc> regions;
   if (!export_for_peer(ep, segs, seg_count, info.payload_len, &regions)) return UCS_ERR_UNSUPPORTED;
@@ -2323,7 +2314,15 @@ int Worker::request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info,
   // a bound that no healthy transfer comes near: 30 s plus a second per GiB
   w.deadline = std::chrono::steady_clock::now() + std::chrono::seconds(30 + (info.payload_len >> 30));
   w.info = std::move(info);
+  w.ready = ready;
   push_waits_.push_back(std::move(w));
+  // the peer writes as soon as it is asked to: it is asked once the buffers may be written
+  if (ready && cudaEventQuery(static_cast<cudaEvent_t>(ready->ready_event)) == cudaErrorNotReady) {
+    held_sends_.push_back({ep, ready, std::move(it)});
+    ++stats_.sends_held;
+    return UCS_INPROGRESS;
+  }
+  cudaGetLastError();
   enqueue(ep, std::move(it));
   nvtx_mark("eux.transport.cts_push_sent");
   return UCS_INPROGRESS;

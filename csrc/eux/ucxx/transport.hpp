@@ -63,13 +63,16 @@ using FaultHook = std::function<bool(const std::string& worker_name, uint8_t fra
 void set_fault_hook(FaultHook hook);
 
 // A device payload that arrived eagerly lies in a slot of the receive ring and is handed to the application as
-// it lies. When the application drops it, work that it queued on the GPU to read the slot may not have run yet,
-// so the slot is handed back to the sender only after an event recorded at that moment has completed. By
-// default the event is recorded on the device's legacy default stream (which every blocking stream
-// synchronises with). A layer that knows better which stream its consumers use (the Python binding: the
-// tensor library's current stream) installs a function that records the event there and returns it (a
-// cudaEvent_t that the transport destroys), or null to fall back to the default.
-using ConsumerEventHook = void* (*)(int device);
+// it lies; the slot goes back to the sender when the application drops the buffer. The contract of the C++
+// interface is that dropping it means being done with it, work queued on the GPU included (a handler that
+// launches a kernel on the payload keeps the payload until the kernel has finished, as the handlers that return
+// schedule_when_flag senders do). A layer whose users cannot keep that contract (the Python binding: a tensor
+// is dropped when its last reference goes, whatever is still queued on the tensor library's stream) installs a
+// hook that is asked at every drop: it returns kConsumerDone (hand the slot back now: nothing is queued), or
+// records an event behind the queued work, stores it in *event (a cudaEvent_t that the transport destroys) and
+// returns kConsumerEvent: the slot goes back when the event has completed.
+enum ConsumerState : int { kConsumerDone = 0, kConsumerEvent = 1 };
+using ConsumerEventHook = int (*)(int device, void** event);
 void set_consumer_event_hook(ConsumerEventHook hook);
 
 // True when a worker with this uid (the random number in its address) is alive in this process. A peer
@@ -339,8 +342,11 @@ class Worker {
               ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out = nullptr,
               std::shared_ptr<const SendHint> hint = nullptr);
   // Complete a rendezvous receive into `segs` (of `mem_type`). Same return convention.
+  // `ready` (device destinations): an event after which the posted buffers may be written. Memory fresh from a
+  // stream-ordered allocator may still be in use by work queued before it was handed out; the transport's own
+  // kernel waits for the event on the device, and a peer is asked to push only once it has completed.
   int rndv_recv(Endpoint* ep, uint64_t msg_id, const ucx_buffer_t* segs, size_t seg_count, ucx_memory_type_t mem_type,
-                Completion done);
+                Completion done, std::shared_ptr<const SendHint> ready = nullptr);
   // Drop a rendezvous message that will never be received (tells the sender).
   void rndv_discard(Endpoint* ep, uint64_t msg_id);
   // Segment sizes announced by the sender of a rendezvous message (empty if unknown).
@@ -416,6 +422,7 @@ class Worker {
     Endpoint::RtsInfo info;               // kept for the fall-back when the peer cannot push after all
     std::vector<ucx_buffer_t> segs;
     std::chrono::steady_clock::time_point deadline;
+    std::shared_ptr<const SendHint> ready;  // kept for the fall-back (and owns the event until then)
   };
   Endpoint* new_endpoint(int fd);
   void fail(Endpoint* ep, int status);
@@ -431,7 +438,7 @@ class Worker {
   void poll_hellos();
   void start_data_send(Endpoint* ep, uint64_t msg_id, bool staged);
   int device_pull(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count,
-                  Completion& done);
+                  Completion& done, const std::shared_ptr<const SendHint>& ready);
   bool peer_is_this_process(const Endpoint* ep) const;
   bool peer_is_local(const Endpoint* ep) const;
   bool ensure_device();
@@ -464,7 +471,8 @@ class Worker {
   void on_push_cts(Endpoint* ep, const FrameHeader& fh, const char* body);
   int dev_eager_send(Endpoint* ep, const void* header, size_t header_len, const ucx_buffer_t& seg, ucx_memory_type_t mem_type,
                      uint64_t msg_id, Completion& done, const std::shared_ptr<const SendHint>& hint);
-  int request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count, Completion& done);
+  int request_push(Endpoint* ep, uint64_t msg_id, Endpoint::RtsInfo& info, const ucx_buffer_t* segs, size_t seg_count, Completion& done,
+                   const std::shared_ptr<const SendHint>& ready);
   int launch_pieces(const std::vector<std::pair<const void*, void*>>& ptrs, const std::vector<size_t>& lens, uint64_t* flag, uint64_t flag_value,
                     uint64_t* flag2, uint64_t flag2_value);
   void flush_pull_batch();

@@ -106,7 +106,7 @@ struct recv_buffer_sender : recv_buffer_args<Target> {
       try {
         if constexpr (std::is_same_v<Target, UcxBuffer>) {
           if (!s.target) s.target = std::make_shared<UcxBuffer>(mr, s.alloc_type, desc.data_length);
-          st = conn->recv_am_data(desc, s.target->data(), s.target->size(), s.target->type(), &cb);
+          st = conn->recv_am_data(desc, s.target->data(), s.target->size(), s.target->type(), &cb, s.target->send_attr());
         } else {
           if (!s.target) {
             auto sizes64 = conn->rndv_segment_sizes(desc);
@@ -114,7 +114,7 @@ struct recv_buffer_sender : recv_buffer_args<Target> {
             if (sizes.empty()) sizes.push_back(desc.data_length);
             s.target = std::make_shared<UcxBufferVec>(mr, s.alloc_type, sizes);
           }
-          st = conn->recv_am_iov_data(desc, s.target->buffers().data(), s.target->size(), s.target->type(), &cb);
+          st = conn->recv_am_iov_data(desc, s.target->buffers().data(), s.target->size(), s.target->type(), &cb, s.target->send_attr());
         }
       } catch (...) {
         conn->release_rndv(desc);

@@ -90,16 +90,17 @@ int UcxConnection::send_am_iov_data(const void* header, size_t header_len, const
   return worker_.am_send(ep_, header, header_len, iov, count, type, true, [cb](int s) { if (cb) (*cb)(s); }, request_id, std::move(attr));
 }
 
-int UcxConnection::recv_am_data(const UcxAmDesc& desc, void* buffer, size_t length, ucx_memory_type_t type, UcxCallback* cb) {
+int UcxConnection::recv_am_data(const UcxAmDesc& desc, void* buffer, size_t length, ucx_memory_type_t type, UcxCallback* cb,
+                                std::shared_ptr<const UcxSendAttr> attr) {
   if (!ep_ || status_ != Status::kConnected) return UCS_ERR_NOT_CONNECTED;
   ucx_buffer_t seg{buffer, length};
-  return worker_.rndv_recv(ep_, desc.msg_id, &seg, 1, type, [cb](int s) { if (cb) (*cb)(s); });
+  return worker_.rndv_recv(ep_, desc.msg_id, &seg, 1, type, [cb](int s) { if (cb) (*cb)(s); }, std::move(attr));
 }
 
 int UcxConnection::recv_am_iov_data(const UcxAmDesc& desc, const ucx_buffer_t* iov, size_t count, ucx_memory_type_t type,
-                                    UcxCallback* cb) {
+                                    UcxCallback* cb, std::shared_ptr<const UcxSendAttr> attr) {
   if (!ep_ || status_ != Status::kConnected) return UCS_ERR_NOT_CONNECTED;
-  return worker_.rndv_recv(ep_, desc.msg_id, iov, count, type, [cb](int s) { if (cb) (*cb)(s); });
+  return worker_.rndv_recv(ep_, desc.msg_id, iov, count, type, [cb](int s) { if (cb) (*cb)(s); }, std::move(attr));
 }
 
 bool UcxConnection::cancel_send(uint64_t request_id) { return ep_ ? worker_.cancel_send(ep_, request_id) : true; }

@@ -107,8 +107,11 @@ class UcxConnection {
   int send_am_iov_data(const void* header, size_t header_len, const ucx_buffer_t* iov, size_t count,
                        ucx_memory_type_t type, UcxCallback* cb, uint64_t* request_id = nullptr,
                        std::shared_ptr<const UcxSendAttr> attr = nullptr);
-  int recv_am_data(const UcxAmDesc& desc, void* buffer, size_t length, ucx_memory_type_t type, UcxCallback* cb);
-  int recv_am_iov_data(const UcxAmDesc& desc, const ucx_buffer_t* iov, size_t count, ucx_memory_type_t type, UcxCallback* cb);
+  // `attr` of a receive buffer: only its event is looked at (the buffer may be written once it has completed)
+  int recv_am_data(const UcxAmDesc& desc, void* buffer, size_t length, ucx_memory_type_t type, UcxCallback* cb,
+                   std::shared_ptr<const UcxSendAttr> attr = nullptr);
+  int recv_am_iov_data(const UcxAmDesc& desc, const ucx_buffer_t* iov, size_t count, ucx_memory_type_t type, UcxCallback* cb,
+                       std::shared_ptr<const UcxSendAttr> attr = nullptr);
   bool cancel_send(uint64_t request_id);
   bool cancel_recv(uint64_t msg_id);
   void release_rndv(const UcxAmDesc& desc);
