@@ -270,7 +270,8 @@ class RemoteGemmAxon:
         import asyncio
         futs = [self.api.client.remote_gemm(self.x, y, worker_name=t, weight_id=self.weight_id, x_scale=self.x_scale, x_scale_pow2=self.pow2)
                 for t, y in zip(self.targets, self.ys)]
-        status = await asyncio.gather(*futs)
+        # one call: awaited as it is (gathering it would cost one more turn of the event loop)
+        status = [await futs[0]] if len(futs) == 1 else await asyncio.gather(*futs)
         if any(status):
             raise RuntimeError(f"remote gemm kernel status {status}")
         return self.ys[0]
