@@ -402,6 +402,8 @@ class Worker {
     Endpoint* ep;
     std::shared_ptr<const SendHint> hint;
     Endpoint::SendItem item;
+    uint64_t msg_id = 0;  // of an RTS (0: a CTS, whose wait has a deadline of its own)
+    std::chrono::steady_clock::time_point deadline{};
   };
   struct EagerWait {  // kAmDevEager frame received, its payload still on the way into the ring slot
     Endpoint* ep;
