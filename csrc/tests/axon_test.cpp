@@ -317,8 +317,8 @@ EUX_TEST(inline_handlers_start_on_the_server_context_thread) {
   // handler_inline: a handler that only starts asynchronous work is called on the server's context thread
   // (the thread that also runs an inline buffer provider); without the flag it is called on a pool thread.
   // Either way its sender may finish elsewhere, here on the pool, and the reply is the same.
+  ex::static_thread_pool elsewhere(1);  // made first, gone last: the workers' threads submit to it until they stop
   Pair p;
-  ex::static_thread_pool elsewhere(1);
   std::mutex mu;
   std::thread::id inline_started, pooled_started, provider_thread;
   auto make_handler = [&](std::thread::id& started) {
