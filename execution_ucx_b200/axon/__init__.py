@@ -813,7 +813,9 @@ class AxonRuntime(_axon.AxonRuntime):
             from ..ops import remote_gemm as g
             x_scale = g.mx_scale_chunks(g.block_scales_to_mx(x_scale, 1), False)
             weight_id |= self.MX_SIBLING
-        torch.cuda.current_stream(x.device).synchronize()
+        producer = torch.cuda.current_stream(x.device)
+        if not producer.query():          # the callee's kernel reads x as soon as the request arrives
+            producer.synchronize()
         nb = lambda t: t.numel() * t.element_size()  # noqa: E731
         fut = self._remote_gemm(worker_name, weight_id, x.shape[0], x.data_ptr(), nb(x), y.data_ptr(), nb(y),
                                 x_scale.data_ptr() if x_scale is not None else 0, nb(x_scale) if x_scale is not None else 0)
