@@ -58,9 +58,55 @@ async def main():
         torch.testing.assert_close(out.float(), m.reference(), rtol=2e-2, atol=2e-2)
         await m.close()
     await api.barrier()
+    await mixed_traffic(api, dev, rank, world)
+    await api.barrier()
     api.stop()
     if rank == 0:
         print("SERVICES_OK", flush=True)
+
+
+async def mixed_traffic(api, dev, rank, world):
+    """Every rank serves and calls at once: 150 calls of random size (dense, strided, converted) to random peers,
+    16 in flight, every reply checked. Ring slots, pushes in both directions and the descriptor of every peer
+    are all in use together."""
+    import random
+    table = {(2, 32): torch.float32, (2, 16): torch.float16, (4, 16): torch.bfloat16}
+
+    def fresh(metas):
+        m = metas[0]
+        return torch.empty(m.shape, dtype=table[(m.dtype.code, m.dtype.bits)], device=dev)
+
+    async def twice(x: torch.Tensor) -> torch.Tensor:
+        return x * 2.0
+
+    api.server.register_function(twice, memory_policy=fresh)
+    await api.barrier()
+    rng = random.Random(1000 + rank)
+    sem = asyncio.Semaphore(16)
+    failures = []
+    peers = [n for i, n in enumerate(api.names) if i != rank]
+
+    async def one(i):
+        async with sem:
+            kind = rng.choice(("dense", "dense", "strided", "cast"))
+            n = int(2 ** rng.uniform(6, 22))
+            wire = None
+            if kind == "strided":
+                rows = max(2, int(n ** 0.5))
+                x = torch.randn(rows, rows + 3, device=dev)[:, 1:-2].t()
+            else:
+                x = torch.randn(n, device=dev)
+                if kind == "cast":
+                    wire = torch.bfloat16
+            y = await api.client.invoke(x, worker_name=rng.choice(peers), session_id=i, function="twice", memory_policy=fresh, wire_dtype=wire)
+            ref = x.contiguous().to(wire or torch.float32) * 2.0
+            if y.dtype != ref.dtype or y.shape != x.shape or not torch.equal(y, ref):
+                failures.append((i, kind, tuple(x.shape), str(y.dtype)))
+
+    await asyncio.gather(*[one(i) for i in range(150)])
+    assert not failures, f"rank {rank}: {failures[:5]}"
+    st = api.transport_stats()
+    assert st["device_staged"] == 0 and st["device_packs"] == 0, st
 
 
 if __name__ == "__main__":
