@@ -364,7 +364,9 @@ static int run_mesh(const Options& o) {
                    [fin](InvokeResult r) mutable { fin(r.header.status.ok()); }),
           [fin](std::exception_ptr) mutable { fin(false); }));
     }
-    if (!any) std::this_thread::yield();
+    // every window is full: sleep for a moment instead of spinning (with one process per GPU the issuing
+    // threads would otherwise take a core each away from the context threads that do the work)
+    if (!any) std::this_thread::sleep_for(std::chrono::microseconds(20));
   }
   ex::sync_wait(scope.join());
   const double secs = std::chrono::duration<double>(clk::now() - t0).count();
