@@ -807,11 +807,13 @@ class AxonRuntime(_axon.AxonRuntime):
 
         ``x_scale_pow2`` (an ``"fp8_block"`` weight served with ``pow2_scales``): ``x_scale`` [M, K/128] holds
         powers of two (``quantize_rows_1x128(x, pow2=True)``); the call is routed to the MX kernel. The result
-        is the same block-scaled product."""
+        is the same block-scaled product. ``x_scale`` may also be given already in the MX form (uint8:
+        ``mx_scale_chunks(block_scales_to_mx(scale, 1), False)``), which saves the conversion per call."""
         import torch
         if x_scale_pow2:
-            from ..ops import remote_gemm as g
-            x_scale = g.mx_scale_chunks(g.block_scales_to_mx(x_scale, 1), False)
+            if x_scale.dtype != torch.uint8:      # fp32 scales: brought into the MX form here; a caller that quantises
+                from ..ops import remote_gemm as g    # X once and calls often converts once itself and passes the bytes
+                x_scale = g.mx_scale_chunks(g.block_scales_to_mx(x_scale, 1), False)
             weight_id |= self.MX_SIBLING
         producer = torch.cuda.current_stream(x.device)
         if not producer.query():          # the callee's kernel reads x as soon as the request arrives

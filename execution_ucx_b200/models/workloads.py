@@ -253,6 +253,8 @@ class RemoteGemmAxon:
             self.x_scale = gemm_ops.mx_scale_chunks(sf, False)
         self.weight_id = weight_id if weight_id is not None else {"bf16": 1, "fp8_block": 2, "mxfp8": 3, "fp8_block_pow2": 4}[fmt]
         self.pow2 = fmt == "fp8_block_pow2"
+        # the scales as they are sent: fp32 per 1x128 block, or (power-of-two route) their MX form, made once with X
+        self.x_scale_sent = gemm_ops.mx_scale_chunks(gemm_ops.block_scales_to_mx(self.x_scale, 1), False) if self.pow2 else self.x_scale
         if self.pow2:
             api.server.serve_gemm(self.weight_id, self.w, "fp8_block", max_m=m, pow2_scales=True)
         else:
@@ -268,7 +270,7 @@ class RemoteGemmAxon:
 
     async def step(self):
         import asyncio
-        futs = [self.api.client.remote_gemm(self.x, y, worker_name=t, weight_id=self.weight_id, x_scale=self.x_scale, x_scale_pow2=self.pow2)
+        futs = [self.api.client.remote_gemm(self.x, y, worker_name=t, weight_id=self.weight_id, x_scale=self.x_scale_sent, x_scale_pow2=self.pow2)
                 for t, y in zip(self.targets, self.ys)]
         # one call: awaited as it is (gathering it would cost one more turn of the event loop)
         status = [await futs[0]] if len(futs) == 1 else await asyncio.gather(*futs)
