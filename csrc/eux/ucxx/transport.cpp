@@ -1223,7 +1223,12 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
   const bool rndv = total > 0 && (force_rndv || device || seg_count > 1 || total >= opt_.eager_limit);
   const uint64_t id = ep->next_msg_id_++;
   if (msg_id_out) *msg_id_out = id;
-  if (device && !force_rndv && seg_count == 1 && total > 0 && total <= opt_.dev_eager_limit && ep->tx_ring_ && ep->out_flags_dev_) {
+  // A payload whose producer is still running does not go out eagerly: the eager kernel would have to wait for
+  // the producer on this worker's stream, and every other transfer of the worker behind it. It is announced
+  // instead, once the producer is done (below), and nothing else waits.
+  const bool producer_running = hint && hint->ready_event && cudaEventQuery(static_cast<cudaEvent_t>(hint->ready_event)) == cudaErrorNotReady;
+  if (!producer_running) cudaGetLastError();
+  if (device && !force_rndv && !producer_running && seg_count == 1 && total > 0 && total <= opt_.dev_eager_limit && ep->tx_ring_ && ep->out_flags_dev_) {
     int st = dev_eager_send(ep, header, header_len, segs[0], mem_type, id, done, hint);
     if (st != UCS_ERR_NO_RESOURCE) return st;  // no free slot right now: the rendezvous takes it
   }

@@ -242,7 +242,7 @@ EUX_TEST(a_payload_whose_producer_is_still_running_is_sent_when_it_is_done) {
   Pair p;
   cudaStream_t st;
   CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess);
-  for (size_t n : {size_t(8) << 10, size_t(8) << 20}) {  // eager: ordered on the device; pushed: the announcement is held back
+  for (size_t n : {size_t(8) << 10, size_t(8) << 20}) {  // a small and a large one: either is announced once its producer is done
     UcxBuffer dev(p.cli.mr, ucx_memory_type::CUDA, n);
     cudaMemset(dev.data(), 0, n);
     cudaDeviceSynchronize();

@@ -207,7 +207,7 @@ def test_strided_and_unfinished_tensors(cuda_device):
         assert cs["device_packs"] == 0 and cs["device_staged"] == 0, cs
         # a producer that is still running when the tensor is sent: ~50 ms of spinning, then the values
         side = torch.cuda.Stream(device="cuda:0")
-        for n in (1 << 10, 1 << 22):                 # eager (ordered on the device), rendezvous (announcement held back)
+        for n in (1 << 10, 1 << 22):                 # a small and a large one: either is announced once its producer is done
             x = torch.zeros(n, device="cuda:0")
             torch.cuda.synchronize()
             with torch.cuda.stream(side):
