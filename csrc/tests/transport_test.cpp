@@ -12,6 +12,8 @@
 #include <unistd.h>
 
 #include <chrono>
+#include <sys/stat.h>
+#include <sys/un.h>
 #include <cstring>
 #include <thread>
 
@@ -358,6 +360,51 @@ EUX_TEST(rts_that_claims_too_many_regions_is_refused) {
   fh.msg_id = 1;
   peer.send_all(&fh, sizeof(fh));
   CHECK(spin(h.w, [&] { return h.w.stats().frames_refused == 1; }));
+}
+
+EUX_TEST(descriptor_channel_socket_is_private_and_ignores_strangers) {
+  // A worker that manages device memory listens on a Unix socket over which file descriptors of device
+  // allocations travel. The socket is this user's only; a connection that names no endpoint of the worker is
+  // closed, and the worker goes on. (No GPU is needed: nothing is allocated.)
+  UcxCudaMemoryResourceManager::Options mo;
+  mo.device = 0;
+  UcxCudaMemoryResourceManager mr(mo);
+  tr::WorkerOptions o;
+  o.name = "fd_owner";
+  tr::Worker w(mr, o);
+  char path[64];
+  std::snprintf(path, sizeof(path), "/dev/shm/eux-fd-%016llx", static_cast<unsigned long long>(w.address().uid));
+  struct stat st{};
+  CHECK(::stat(path, &st) == 0);
+  CHECK(S_ISSOCK(st.st_mode));
+  CHECK_EQ(int(st.st_mode & 0777), 0600);
+  int fd = ::socket(AF_UNIX, SOCK_SEQPACKET, 0);
+  sockaddr_un un{};
+  un.sun_family = AF_UNIX;
+  std::strncpy(un.sun_path, path, sizeof(un.sun_path) - 1);
+  CHECK(::connect(fd, reinterpret_cast<sockaddr*>(&un), sizeof(un)) == 0);
+  struct {
+    uint32_t magic = 0x44465845u, kind = 0;
+    uint64_t a = 0x1122334455667788ull, b = 0;  // a worker id that this worker has no endpoint for
+  } hello;
+  CHECK(::send(fd, &hello, sizeof(hello), MSG_NOSIGNAL) == ssize_t(sizeof(hello)));
+  char buf[8];
+  ssize_t n = -1;
+  for (int i = 0; i < 2000; ++i) {
+    w.progress();
+    n = ::recv(fd, buf, sizeof(buf), MSG_DONTWAIT);
+    if (n == 0) break;  // closed by the worker
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
+  CHECK_EQ(n, ssize_t(0));
+  ::close(fd);
+  CHECK_EQ(w.stats().vmm_fds_recv, uint64_t(0));
+  {
+    tr::Worker gone(mr, o);
+    std::snprintf(path, sizeof(path), "/dev/shm/eux-fd-%016llx", static_cast<unsigned long long>(gone.address().uid));
+    CHECK(::stat(path, &st) == 0);
+  }
+  CHECK(::stat(path, &st) != 0);  // the socket's name goes with its worker
 }
 
 EUX_TEST(short_data_frame_ends_the_receive_as_truncated) {
