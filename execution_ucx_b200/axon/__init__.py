@@ -209,11 +209,17 @@ def _contiguous(t, strided_ok: bool = False):
     return t
 
 
+def _dtype_name(dtype) -> str:
+    """'float16' for torch.float16, numpy.float16, numpy.dtype('float16') and 'float16'."""
+    name = getattr(dtype, "__name__", None) or getattr(dtype, "name", None) or str(dtype)
+    return str(name).rsplit(".", 1)[-1]
+
+
 def _wire_code(wire_dtype) -> int:
     """Kernel code of the type in which a device tensor's elements shall travel (0: as they are)."""
     if wire_dtype is None:
         return 0
-    name = str(wire_dtype).rsplit(".", 1)[-1]
+    name = _dtype_name(wire_dtype)
     code = {"float32": 1, "float16": 2, "half": 2, "bfloat16": 3}.get(name)
     if code is None:
         raise ValueError(f"wire_dtype must be float32, float16 or bfloat16, not {wire_dtype}")
@@ -224,11 +230,25 @@ def _apply_wire_dtype(payload, wire_dtype):
     """What the transfer kernel cannot convert on the way (host tensors, lists of tensors) is converted here."""
     if wire_dtype is None or payload is None:
         return payload
+
+    def convert(t, even_on_device):
+        if hasattr(t, "is_floating_point"):                      # torch
+            if t.is_floating_point() and (even_on_device or not getattr(t, "is_cuda", False)):
+                import torch
+                target = getattr(torch, _dtype_name(wire_dtype))
+                return t.to(target).contiguous() if even_on_device else t.to(target)
+            return t
+        kind = getattr(getattr(t, "dtype", None), "kind", None)   # numpy
+        if kind == "f":
+            name = _dtype_name(wire_dtype)
+            if name == "bfloat16":
+                raise ValueError("numpy has no bfloat16: send the array as float16 or float32, or as a torch tensor")
+            return t.astype(name)
+        return t
+
     if isinstance(payload, list):
-        return [t.to(wire_dtype).contiguous() if hasattr(t, "is_floating_point") and t.is_floating_point() else t for t in payload]
-    if hasattr(payload, "is_floating_point") and payload.is_floating_point() and not getattr(payload, "is_cuda", False):
-        return payload.to(wire_dtype)
-    return payload
+        return [convert(t, True) for t in payload]
+    return convert(payload, False)
 
 
 def _reinterpret(piece, meta: TensorMeta, fn):

@@ -149,3 +149,52 @@ def test_raw_api_retention_and_checkpoint(axon, tmp_path):
         server.stop()
 
     run(main())
+
+
+def test_wire_dtype_converts_host_tensors_before_they_are_sent(axon):
+    """``wire_dtype``: floating-point tensors travel in another type than they have in memory. On the host the
+    conversion happens before the send (on a GPU the transfer kernel does it on the way); what the function sees,
+    and what comes back, has the wire type."""
+    torch = pytest.importorskip("torch")
+
+    async def main():
+        server = axon.AxonRuntime("wd_server", timeout=5000)
+        client = axon.AxonRuntime("wd_client", timeout=5000)
+        seen = []
+
+        async def what_arrived(x: torch.Tensor) -> torch.Tensor:
+            seen.append(x.dtype)
+            return x
+
+        async def halves(xs: List[np.ndarray]) -> List[np.ndarray]:
+            seen.append([a.dtype for a in xs])
+            return xs
+
+        async def as_float(x: torch.Tensor) -> torch.Tensor:
+            return x.float() * 3.0
+
+        server.register_function(what_arrived)
+        server.register_function(halves)
+        server.register_function(as_float, wire_dtype=torch.float16)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "wd_server")
+        for n in (100, 100000):       # eager and rendezvous
+            x = torch.randn(n)
+            y = await client.invoke(x, worker_name="wd_server", session_id=1, function="what_arrived", wire_dtype=torch.bfloat16)
+            assert seen[-1] == torch.bfloat16 and y.dtype == torch.bfloat16
+            assert torch.equal(y, x.to(torch.bfloat16))
+        ys = await client.invoke([np.ones(8, dtype=np.float32), np.arange(4, dtype=np.float64)], worker_name="wd_server", session_id=1,
+                                 function="halves", wire_dtype=np.float16, from_dlpack_fn=np.from_dlpack)
+        assert seen[-1] == [np.dtype("float16"), np.dtype("float16")]
+        assert [a.dtype for a in ys] == [np.dtype("float16")] * 2 and float(ys[1][3]) == 3.0
+        z = await client.invoke(torch.ones(16, dtype=torch.float64), worker_name="wd_server", session_id=1, function="as_float")
+        assert z.dtype == torch.float16 and float(z[0]) == 3.0      # the function's fp32 result came back as fp16
+        with pytest.raises(ValueError):
+            client.invoke(np.ones(4, dtype=np.float32), worker_name="wd_server", session_id=1, function="what_arrived", wire_dtype=torch.bfloat16)
+        with pytest.raises(ValueError):
+            client.invoke(torch.ones(4), worker_name="wd_server", session_id=1, function="what_arrived", wire_dtype=torch.int32)
+        client.stop()
+        server.stop()
+
+    run(main())
