@@ -1575,7 +1575,9 @@ bool Worker::cancel_send(Endpoint* ep, uint64_t msg_id) {
   auto it = ep->pending_sends_.find(msg_id);
   if (it != ep->pending_sends_.end()) {
     ep->pending_sends_.erase(it);
-    if (ep->state_ == Endpoint::State::kConnected) send_control(ep, kRndvFin, kFlagFromSender, msg_id, UCS_ERR_CANCELED);
+    // an announcement that still waits for its payload's producer never leaves: the peer never hears of the message
+    const size_t held = std::erase_if(held_sends_, [ep, msg_id](const HeldSend& h) { return h.ep == ep && h.msg_id == msg_id; });
+    if (!held && ep->state_ == Endpoint::State::kConnected) send_control(ep, kRndvFin, kFlagFromSender, msg_id, UCS_ERR_CANCELED);
     return true;
   }
   for (auto s = ep->sendq_.begin(); s != ep->sendq_.end(); ++s) {
