@@ -823,7 +823,8 @@ class AxonRuntime(_axon.AxonRuntime):
         """``y[M, N] = x[M, K] @ W`` on ``worker_name``, where W is what that worker serves as ``weight_id``.
         ``x`` and ``y`` (and ``x_scale`` for the fp8 formats) are device tensors of this process that the callee's
         kernel reads and writes directly; they must stay untouched until the returned future resolves (to the
-        kernel's status word, 0 when all went well). Whatever produced ``x`` on the current stream is waited for first.
+        kernel's status word, 0 when all went well). The request leaves once whatever produces ``x`` on the current
+        stream has finished; that is waited for on a helper thread, not on the event loop.
 
         ``x_scale_pow2`` (an ``"fp8_block"`` weight served with ``pow2_scales``): ``x_scale`` [M, K/128] holds
         powers of two (``quantize_rows_1x128(x, pow2=True)``); the call is routed to the MX kernel. The result
@@ -835,15 +836,26 @@ class AxonRuntime(_axon.AxonRuntime):
                 from ..ops import remote_gemm as g    # X once and calls often converts once itself and passes the bytes
                 x_scale = g.mx_scale_chunks(g.block_scales_to_mx(x_scale, 1), False)
             weight_id |= self.MX_SIBLING
-        producer = torch.cuda.current_stream(x.device)
-        if not producer.query():          # the callee's kernel reads x as soon as the request arrives
-            producer.synchronize()
         nb = lambda t: t.numel() * t.element_size()  # noqa: E731
-        fut = self._remote_gemm(worker_name, weight_id, x.shape[0], x.data_ptr(), nb(x), y.data_ptr(), nb(y),
-                                x_scale.data_ptr() if x_scale is not None else 0, nb(x_scale) if x_scale is not None else 0)
-        if x_scale_pow2:
-            fut.add_done_callback(lambda _f, keep=x_scale: None)   # the converted scales live until the kernel has read them
-        return fut
+
+        def call():
+            fut = self._remote_gemm(worker_name, weight_id, x.shape[0], x.data_ptr(), nb(x), y.data_ptr(), nb(y),
+                                    x_scale.data_ptr() if x_scale is not None else 0, nb(x_scale) if x_scale is not None else 0)
+            if x_scale_pow2:
+                fut.add_done_callback(lambda _f, keep=x_scale: None)   # the converted scales live until the kernel has read them
+            return fut
+
+        # the callee's kernel reads x as soon as the request arrives: the request leaves when x is complete
+        producer = torch.cuda.current_stream(x.device)
+        if producer.query():
+            return call()
+
+        async def when_produced():
+            # the producer is waited for on a helper thread, so that this runtime's handlers keep running meanwhile
+            await asyncio.get_running_loop().run_in_executor(None, producer.synchronize)
+            return await call()
+
+        return asyncio.ensure_future(when_produced())
 
     # ---- client side --------------------------------------------------------------------------
     def invoke_raw(self, worker_name: str, request_header: RpcRequestHeader, payload=None, memory_policy: Optional[Callable] = None):
