@@ -9,7 +9,7 @@ LIB = Path(__file__).resolve().parent.parent / "execution_ucx_b200" / "_lib"
 
 
 @pytest.mark.parametrize("binary", ["eux_am_context_cuda_test"])
-def test_native_gpu_binary(binary, cuda_device):
+def test_native_gpu_binary(binary, native_build, cuda_device):
     exe = LIB / binary
     assert exe.exists(), f"{exe} is not built: run python -m execution_ucx_b200._build"
     out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
