@@ -5,7 +5,8 @@
     python -m execution_ucx_b200.models.profile_case --kernel xfer
     python -m execution_ucx_b200.models.profile_case --kernel moe
     python -m execution_ucx_b200.models.profile_case --kernel pull_batch  (the transport's batched small pulls)
-    python -m execution_ucx_b200.models.profile_case --kernel gemm_pull   (two GPUs, one process: the GEMM on GPU 0 reads X out of GPU 1's memory)
+    python -m execution_ucx_b200.models.profile_case --kernel gemm_pull   (two GPUs, one process: the GEMM on GPU 0 reads X out of GPU 1's memory;
+                                                                           gemm_mx_pull, gemm_fp8_pull: the same for the fp8 kernels)
     python -m execution_ucx_b200.models.profile_case --kernel xfer_peer   (two GPUs, one process: the transfer kernel on GPU 0 writes into GPU 1's memory)
     python -m execution_ucx_b200.models.profile_case --kernel xfer_gather (a transposed matrix gathered into a dense buffer)
 
@@ -21,7 +22,7 @@ import torch
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "pull_batch", "moe", "moe_fp8", "gemm_pull", "xfer_peer", "xfer_gather"], required=True)
+    ap.add_argument("--kernel", choices=["gemm", "gemm_1cta", "gemm_fp8", "gemm_mx", "xfer", "pull_batch", "moe", "moe_fp8", "gemm_pull", "gemm_mx_pull", "gemm_fp8_pull", "xfer_peer", "xfer_gather"], required=True)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -36,7 +37,7 @@ def main() -> None:
             g(x.data_ptr(), m, y.data_ptr(), x_is_local=True, cta_pairs=args.kernel == "gemm")
         torch.cuda.synchronize()
         g.check_status()
-    elif args.kernel in ("gemm_pull", "xfer_peer"):
+    elif args.kernel in ("gemm_pull", "gemm_mx_pull", "gemm_fp8_pull", "xfer_peer"):
         # One process, two GPUs: the peer's memory is an ordinary allocation on GPU 1 that GPU 0 may access.
         # Nothing in the profiled kernels waits for the other GPU, so a replayed launch cannot stall.
         from ..ops import _native
@@ -57,6 +58,28 @@ def main() -> None:
             torch.cuda.synchronize(0)
             g.check_status()
             ref = x_remote[:128].to(dev).float() @ w.float()
+            assert float((y[:128].float() - ref).abs().max()) < 0.25
+        elif args.kernel in ("gemm_mx_pull", "gemm_fp8_pull"):
+            from ..ops import remote_gemm as g
+            m, n, k = 4096, 4096, 4096
+            x = torch.randn(m, k, device=dev)
+            w = torch.randn(k, n, device=dev) * 0.02
+            if args.kernel == "gemm_mx_pull":
+                gemm = g.RemoteGemmMx(w, m)
+                xq, xsf = g.quantize_mx(x)
+                xs = g.mx_scale_chunks(xsf, False)
+                ref = g.mx_dequantized_reference(xq[:128], xsf[:128], gemm.w_q_t, gemm.w_sf)
+            else:
+                gemm = g.RemoteGemmFp8(w.to(torch.bfloat16), m)
+                xq, xs = g.quantize_rows_1x128(x.to(torch.bfloat16))
+                ref = g.dequantized_reference(xq[:128], xs[:128], gemm.w_q_t, gemm.w_scale)
+            xq_remote, xs_remote = xq.to("cuda:1"), xs.to("cuda:1")    # values and scales lie on GPU 1, complete before any launch
+            torch.cuda.synchronize(1)
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            for _ in range(args.iters):
+                gemm(xq_remote.data_ptr(), xs_remote.data_ptr(), m, y.data_ptr(), x_is_local=False)
+            torch.cuda.synchronize(0)
+            gemm.check_status()
             assert float((y[:128].float() - ref).abs().max()) < 0.25
         else:
             from ..ops import tensor_xfer as tx
