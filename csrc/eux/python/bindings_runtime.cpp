@@ -652,6 +652,10 @@ void bind_runtime(py::module_& m) {
       .def("pooled_bytes", &ucxx::UcxCudaMemoryResourceManager::pooled_bytes)
       .def("pooled_bytes_in_use", &ucxx::UcxCudaMemoryResourceManager::pooled_bytes_in_use);
   m.def("get_default_resource_manager", [] { return default_manager(); });
+  m.def("_spin_for_wake", [](double seconds) {
+    py::gil_scoped_release nogil;
+    return spin_for_wake(std::chrono::nanoseconds(static_cast<int64_t>(seconds * 1e9)));
+  }, "Spin without the GIL until a native thread has queued work for an event loop of this process, or the time is up.");
   m.def("get_device_context_handle", [](const std::string& kind) -> py::object {
     if (kind != "cuda") return py::none();
     int dev = -1;

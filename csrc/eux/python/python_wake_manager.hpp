@@ -9,6 +9,8 @@
 #include <sys/eventfd.h>
 #include <unistd.h>
 
+#include <atomic>
+#include <chrono>
 #include <deque>
 #include <functional>
 #include <mutex>
@@ -17,6 +19,28 @@ namespace eux::python {
 
 namespace py = pybind11;
 
+// Closures queued by any manager of this process and not yet taken by its loop. A loop that prefers to
+// spin for a while before it sleeps in the selector watches this one word.
+inline std::atomic<int64_t>& pending_wakes() {
+  static std::atomic<int64_t> n{0};
+  return n;
+}
+
+// Spins (GIL released by the caller) until a closure is queued or `budget` has passed.
+inline bool spin_for_wake(std::chrono::nanoseconds budget) {
+  auto& n = pending_wakes();
+  const auto end = std::chrono::steady_clock::now() + budget;
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      if (n.load(std::memory_order_acquire) > 0) return true;
+#if defined(__x86_64__)
+      __builtin_ia32_pause();
+#endif
+    }
+    if (std::chrono::steady_clock::now() >= end) return n.load(std::memory_order_acquire) > 0;
+  }
+}
+
 class PythonWakeManager {
  public:
   PythonWakeManager() {
@@ -24,6 +48,7 @@ class PythonWakeManager {
     if (fd_ < 0) throw std::runtime_error("eventfd failed");
   }
   ~PythonWakeManager() {
+    pending_wakes().fetch_sub(static_cast<int64_t>(queue_.size()), std::memory_order_release);
     if (fd_ >= 0) ::close(fd_);
   }
   PythonWakeManager(const PythonWakeManager&) = delete;
@@ -53,6 +78,7 @@ class PythonWakeManager {
       std::lock_guard lk(mu_);
       queue_.push_back(std::move(fn));
     }
+    pending_wakes().fetch_add(1, std::memory_order_release);
     uint64_t one = 1;
     (void)!::write(fd_, &one, sizeof(one));
   }
@@ -71,6 +97,7 @@ class PythonWakeManager {
         batch.swap(queue_);
       }
       if (batch.empty()) return;
+      pending_wakes().fetch_sub(static_cast<int64_t>(batch.size()), std::memory_order_release);
       for (auto& fn : batch) {
         try {
           fn();

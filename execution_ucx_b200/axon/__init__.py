@@ -46,6 +46,7 @@ from ._axon import (CudaMemoryResourceManager, DefaultUcxMemoryResourceManager, 
                     get_default_resource_manager, get_device_context_handle)
 from .device import (CpuDevice, CudaDevice, Device, DeviceType, RocmDevice, SyclDevice, auto_detect, cpu, cuda,  # noqa: E402
                      rocm, sycl)
+from .loop import SpinningSelector, new_event_loop, run  # noqa: E402
 
 _GROUP_SIZES = "__ntl_group_sizes"   # name of the VECTOR_UINT32 param that carries nested-tensor-list group sizes
 _NESTED_TAGS = {"nli64": "q", "nlf64": "d", "nlb": "B"}
@@ -915,5 +916,6 @@ __all__ = [
     "DLPackCapsuleWrapper", "RpcRequestHeader", "RpcResponseHeader", "RpcFunctionSignature", "deserialize_signatures",
     "UcxMemoryResourceManager", "DefaultUcxMemoryResourceManager", "CudaMemoryResourceManager", "get_default_resource_manager",
     "get_device_context_handle", "function_id_from_name", "MemoryType",
+    "SpinningSelector", "new_event_loop", "run",
     "Device", "DeviceType", "CpuDevice", "CudaDevice", "RocmDevice", "SyclDevice", "cpu", "cuda", "rocm", "sycl", "auto_detect",
 ]
