@@ -32,17 +32,10 @@ namespace py = pybind11;
 // it). An event recorded there tells the transport when the ring slot under the tensor may be written again.
 int consumer_event_on_torch_stream(int device, void** event) {
   namespace tr = eux::ucxx::transport;
-  uintptr_t stream = 0;  // not a Python thread, or no torch: the legacy default stream, with which blocking streams synchronise
+  // not a Python thread, or no torch: the legacy default stream, with which blocking streams synchronise
+  uintptr_t stream = 0;
   if (Py_IsInitialized() && PyGILState_Check()) {
-    try {
-      py::object modules = py::module_::import("sys").attr("modules");
-      if (modules.contains("torch")) {
-        py::object cuda = modules["torch"].attr("cuda");
-        if (cuda.attr("is_initialized")().cast<bool>()) stream = cuda.attr("current_stream")(device).attr("cuda_stream").cast<uintptr_t>();
-      }
-    } catch (...) {
-      PyErr_Clear();
-    }
+    stream = eux::python::torch_current_stream(py::handle(), device);
   }
   int prev = -1;
   cudaGetDevice(&prev);

@@ -50,16 +50,7 @@ std::chrono::milliseconds parse_timeout(py::handle t) {
 // The stream on which the producer of a device tensor would launch its next kernel, as far as this layer can
 // know it: a torch tensor's is torch's current stream on that device; anything else is taken to work on the
 // legacy default stream (0), with which every blocking stream synchronises.
-uintptr_t producer_stream(py::handle obj, int device) {
-  try {
-    const std::string mod = py::type::handle_of(obj).attr("__module__").cast<std::string>();
-    if (mod.rfind("torch", 0) == 0)
-      return py::module_::import("torch").attr("cuda").attr("current_stream")(device).attr("cuda_stream").cast<uintptr_t>();
-  } catch (const std::exception&) {
-    PyErr_Clear();
-  }
-  return 0;
-}
+uintptr_t producer_stream(py::handle obj, int device) { return torch_current_stream(obj, device); }
 
 PayloadVariant payload_from_python(ucxx::UcxMemoryResourceManager& mr, py::handle obj, rpc::TensorMetaVec* metas = nullptr, int wire_dtype = 0) {
   if (obj.is_none()) return {};

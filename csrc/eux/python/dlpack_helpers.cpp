@@ -3,6 +3,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -30,9 +31,88 @@ DLDevice device_of(ucx_memory_type_t type, int device_id) {
   }
 }
 
-ImportedTensor import_tensor(py::handle obj, bool allow_strided, int wire_dtype) {
+namespace {
+// What this layer asks torch for on every call, looked up once (under the GIL; the references are never given
+// back, so that nothing is destroyed after the interpreter has gone).
+struct TorchHooks {
+  PyObject* tensor_type = nullptr;   // torch.Tensor
+  PyObject* to_dlpack = nullptr;     // torch.utils.dlpack.to_dlpack: the capsule without the checks of Tensor.__dlpack__
+  PyObject* raw_stream = nullptr;    // torch._C._cuda_getCurrentRawStream, where this torch has it
+  PyObject* current_stream = nullptr;  // torch.cuda.current_stream
+};
+const TorchHooks* torch_hooks() {
+  static TorchHooks hooks;
+  static bool ready = false;
+  if (ready) return &hooks;
+  py::object modules = py::module_::import("sys").attr("modules");
+  if (!modules.contains("torch")) return nullptr;  // not loaded (yet): asked again next time
+  try {
+    py::object torch = modules["torch"];
+    hooks.tensor_type = py::object(torch.attr("Tensor")).release().ptr();
+    hooks.current_stream = py::object(torch.attr("cuda").attr("current_stream")).release().ptr();
+    py::object c = py::getattr(torch, "_C", py::none());
+    if (!c.is_none() && py::hasattr(c, "_cuda_getCurrentRawStream")) hooks.raw_stream = py::object(c.attr("_cuda_getCurrentRawStream")).release().ptr();
+    py::object dl = py::module_::import("torch.utils.dlpack");
+    hooks.to_dlpack = py::object(dl.attr("to_dlpack")).release().ptr();
+  } catch (py::error_already_set&) {
+    PyErr_Clear();
+  }
+  ready = true;
+  return &hooks;
+}
+
+// A plain torch.Tensor (no subclass) that Tensor.__dlpack__ would export without complaint: its capsule comes
+// from torch.utils.dlpack.to_dlpack, which skips the Python-level checks of __dlpack__ (about ten times the cost
+// of the export itself). Everything else goes through __dlpack__ and gets its errors from there.
+py::object export_capsule(py::handle obj) {
+  if (std::strcmp(Py_TYPE(obj.ptr())->tp_name, "Tensor") == 0) {
+    const TorchHooks* h = torch_hooks();
+    if (h && h->to_dlpack && reinterpret_cast<PyObject*>(Py_TYPE(obj.ptr())) == h->tensor_type) {
+      try {
+        if (!obj.attr("requires_grad").cast<bool>() && !obj.attr("is_conj")().cast<bool>())
+          return py::reinterpret_steal<py::object>(PyObject_CallOneArg(h->to_dlpack, obj.ptr()));
+      } catch (py::error_already_set&) {
+        PyErr_Clear();
+      }
+    }
+  }
   if (!py::hasattr(obj, "__dlpack__")) throw py::type_error("object does not implement __dlpack__");
-  py::object cap_obj = obj.attr("__dlpack__")();
+  return obj.attr("__dlpack__")();
+}
+}  // namespace
+
+uintptr_t torch_current_stream(py::handle obj, int device) {
+  try {
+    const TorchHooks* h = torch_hooks();
+    if (!h) return 0;
+    if (obj) {
+      // a tensor of another library works on the legacy default stream as far as this layer knows
+      if (reinterpret_cast<PyObject*>(Py_TYPE(obj.ptr())) != h->tensor_type &&
+          py::type::handle_of(obj).attr("__module__").cast<std::string>().rfind("torch", 0) != 0)
+        return 0;
+    } else {
+      // nobody showed a torch tensor: torch's stream counts only once torch has a CUDA context of its own
+      static bool initialized = false;
+      if (!initialized) {
+        initialized = py::module_::import("torch").attr("cuda").attr("is_initialized")().cast<bool>();
+        if (!initialized) return 0;
+      }
+    }
+    if (h->raw_stream) {
+      py::object s = py::reinterpret_steal<py::object>(PyObject_CallOneArg(h->raw_stream, py::int_(device).ptr()));
+      if (s) return s.cast<uintptr_t>();
+      PyErr_Clear();
+    }
+    if (h->current_stream) return py::handle(h->current_stream)(device).attr("cuda_stream").cast<uintptr_t>();
+  } catch (const std::exception&) {
+    PyErr_Clear();
+  }
+  return 0;
+}
+
+ImportedTensor import_tensor(py::handle obj, bool allow_strided, int wire_dtype) {
+  py::object cap_obj = export_capsule(obj);
+  if (!cap_obj) throw py::error_already_set();
   if (!PyCapsule_IsValid(cap_obj.ptr(), "dltensor")) throw py::value_error("__dlpack__ did not return an unused 'dltensor' capsule");
   auto* managed = static_cast<DLManagedTensor*>(PyCapsule_GetPointer(cap_obj.ptr(), "dltensor"));
   if (!managed) throw py::error_already_set();

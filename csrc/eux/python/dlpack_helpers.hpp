@@ -43,6 +43,10 @@ struct ImportedTensor {
 // `wire_dtype` (1 fp32, 2 fp16, 3 bf16; 0: none): a CUDA tensor of another one of these types is announced in
 // that type and converted by the transfer kernel on the way.
 ImportedTensor import_tensor(py::handle obj, bool allow_strided = false, int wire_dtype = 0);
+// torch's current stream on `device` as a cudaStream_t in an integer, when the tensor library in use is torch
+// (`obj`: a tensor that tells, or null to go by whether torch is loaded at all); 0 otherwise: the legacy default
+// stream, with which every blocking stream synchronises.
+uintptr_t torch_current_stream(py::handle obj, int device);
 // The remarks for the transport about a device tensor that is about to be sent: its layout when it was
 // imported strided, and an event recorded now on the producer's stream (`stream`: a cudaStream_t as an
 // integer; 0: the legacy default stream), so that nobody has to wait for the producer here. Null for host tensors.

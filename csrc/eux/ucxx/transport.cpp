@@ -123,15 +123,19 @@ constexpr size_t kMinInlineCap = size_t(16) << 20;   // inline payloads: the lar
 constexpr uint32_t kPushWords = 256;
 constexpr uint32_t kEagerSlots = 32;                 // one bit each in a 64-bit free mask
 constexpr uint32_t kEagerSlotBytesMax = 1 << 20;     // largest slot
-constexpr uint32_t kEagerRunMax = 4;                 // an eager payload may take up to this many consecutive slots
+constexpr uint32_t kEagerRunMax = 16;                // an eager payload may take up to this many consecutive slots (half the ring)
+constexpr uint32_t kEagerRunSizing = 4;              // a payload at the limit takes this many slots, as far as the largest slot allows
 constexpr uint32_t kEagerBatchBytes = 64 << 10;      // eager payloads up to here share one launch per pass; larger ones get a launch of several CTAs
 // Slot size for a worker whose eager limit is `limit`: a quarter of it (a payload at the limit takes a run of
-// kEagerRunMax slots), at least 4 KiB, a power of two.
+// kEagerRunSizing slots), at least 4 KiB and at most kEagerSlotBytesMax, a power of two. A limit above four of
+// the largest slots keeps that slot size and lets a payload take a longer run, up to kEagerRunMax.
 inline uint32_t eager_slot_bytes(size_t limit) {
   uint32_t b = 4096;
-  while (size_t(b) * kEagerRunMax < limit && b < kEagerSlotBytesMax) b <<= 1;
+  while (size_t(b) * kEagerRunSizing < limit && b < kEagerSlotBytesMax) b <<= 1;
   return b;
 }
+// The longest run a ring of these slots takes: rings of smaller slots were sized for a smaller limit and keep it.
+inline uint32_t eager_run_max(uint32_t slot_bytes) { return slot_bytes < kEagerSlotBytesMax ? kEagerRunSizing : kEagerRunMax; }
 constexpr uint32_t kEagerWordBase = kPushWords;
 static_assert(kEagerWordBase + kEagerSlots <= ShmChannel::kFlagWords);
 constexpr auto kEagerArrivalTimeout = std::chrono::seconds(10);
@@ -2178,7 +2182,7 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
                            uint64_t msg_id, Completion& done, const std::shared_ptr<const SendHint>& hint) {
   if (!ensure_device() || device_ops_.size() + 2 >= kFlagSlots) return UCS_ERR_NO_RESOURCE;
   const uint32_t run = seg.size ? static_cast<uint32_t>((seg.size + ep->tx_slot_bytes_ - 1) / ep->tx_slot_bytes_) : 1;
-  if (run > kEagerRunMax || run > ep->tx_slots_) return UCS_ERR_NO_RESOURCE;
+  if (run > eager_run_max(ep->tx_slot_bytes_) || run > ep->tx_slots_) return UCS_ERR_NO_RESOURCE;
   const bool strided = hint && hint->ndim > 0;
   if (strided && hint->elem_size > 4 && hint->ndim >= kSendAttrMaxDims) return UCS_ERR_NO_RESOURCE;
   ep->tx_free_ |= ep->shm_->in_words()[0].exchange(0, std::memory_order_acquire);  // slots the peer has handed back
@@ -2263,7 +2267,7 @@ int Worker::dev_eager_send(Endpoint* ep, const void* header, size_t header_len, 
 
 void Worker::on_dev_eager(Endpoint* ep, const FrameHeader& fh, const char* body) {
   const uint32_t slot = static_cast<uint32_t>(fh.status) & 0xffu, run = (static_cast<uint32_t>(fh.status) >> 8) & 0xffu;
-  if (!ep->rx_ring_ || !ep->shm_ || run == 0 || run > kEagerRunMax || slot + run > kEagerSlots ||
+  if (!ep->rx_ring_ || !ep->shm_ || run == 0 || run > eager_run_max(ep->rx_ring_->slot_bytes) || slot + run > kEagerSlots ||
       fh.payload_len > uint64_t(run) * ep->rx_ring_->slot_bytes) {
     UCX_CONN_ERROR << opt_.name << ": eager device frame from " << ep->peer_name_ << " names a slot this worker never offered";
     ++stats_.frames_refused;

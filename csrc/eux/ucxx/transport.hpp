@@ -184,10 +184,10 @@ struct WorkerOptions {
   bool use_shm = true;           // peers on this host talk through shared-memory rings (EUX_SHM=0 turns it off)
   // Device payloads up to this size go out eagerly: the sender's kernel (one CTA of a batched launch up to
   // 64 KiB, a launch of its own above) stores them into the peer's device receive ring (32 slots of a quarter
-  // of this limit; a payload takes up to four consecutive slots) and raises a flag the peer's host thread
-  // polls. No RTS, no FIN, and the receiver asks no memory policy: the payload is handed on where it lies.
-  // 0 turns the path off (EUX_DEV_EAGER_LIMIT); at most 4 MiB.
-  size_t dev_eager_limit = size_t(4) << 20;
+  // of this limit, at most 1 MiB each; a payload takes a run of consecutive slots, up to 16) and raises a flag
+  // the peer's host thread polls. No RTS, no FIN, and the receiver asks no memory policy: the payload is handed
+  // on where it lies. 0 turns the path off (EUX_DEV_EAGER_LIMIT); at most 16 MiB.
+  size_t dev_eager_limit = size_t(16) << 20;
   // Device payloads from this size on are pushed by the sender's kernel (the receiver answers the RTS with
   // its own regions) instead of pulled by the receiver's: with traffic in both directions stores keep
   // the links fuller than loads. 0 turns pushing off (EUX_PUSH_THRESH).

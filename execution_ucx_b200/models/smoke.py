@@ -108,14 +108,14 @@ def _axon_round_trip(device: torch.device) -> None:
         client.start_client()
         await client.connect_endpoint_async(server.get_local_address(), "smoke_server")
         # 1 KiB and 256 KiB travel eagerly into the receive ring (one CTA of a batched launch; a launch of
-        # several CTAs), 8 MiB is pushed by the sender's kernel
-        for n in (256, 1 << 16, 1 << 21):
+        # several CTAs), 32 MiB is pushed by the sender's kernel
+        for n in (256, 1 << 16, 1 << 23):
             x = torch.rand(n, device=device)
             y = await client.invoke(x, worker_name="smoke_server", session_id=1, function="add_one", memory_policy=policy)
             assert y.is_cuda and torch.equal(y, x + 1.0)
             del y
-        # a transposed 8 MiB matrix is gathered out of the sender's memory by the receiver's pull
-        xt = torch.rand(2048, 1024, device=device).t()
+        # a transposed 32 MiB matrix is gathered out of the sender's memory by the receiver's pull
+        xt = torch.rand(4096, 2048, device=device).t()
         y = await client.invoke(xt, worker_name="smoke_server", session_id=1, function="add_one", memory_policy=policy)
         assert torch.equal(y, xt.contiguous() + 1.0)
         del y

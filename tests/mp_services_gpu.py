@@ -24,7 +24,7 @@ async def main():
     api = AxonTensorRpc(group, timeout_ms=30000)
     await api.start(connect_all=True)
     # echo at eager sizes (one slot of the peer's ring, a run of slots) and at a pushed size
-    for n in (2048, 1 << 21, 1 << 24):
+    for n in (2048, 1 << 21, 1 << 25):
         x = torch.randn(n // 2, device=dev).to(torch.bfloat16)
         y = await api.step(x)
         assert torch.equal(y.view(torch.int16), x.view(torch.int16)), f"echo of {n} bytes differs"

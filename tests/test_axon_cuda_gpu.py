@@ -56,10 +56,10 @@ def test_cuda_tensor_echo_same_process(cuda_device):
             x = torch.rand(n, device="cuda:0")
             y = await client.invoke(x, worker_name="gpu_server", session_id=1, function="plus_one", memory_policy=client_policy)
             assert y.is_cuda and y.shape == x.shape
-            if n * 4 > 4 << 20:
+            if n * 4 > 16 << 20:
                 assert y is made[-1], "large device results land in the tensor the policy returned"
             else:
-                assert not made, "device results up to 4 MiB arrive eagerly in the receive ring; the policy is not asked"
+                assert not made, "device results up to 16 MiB arrive eagerly in the receive ring; the policy is not asked"
             torch.testing.assert_close(y, x + 1.0, rtol=0, atol=0)
             del y
         cs, ss = client.transport_stats(), server.transport_stats()
@@ -127,8 +127,8 @@ def test_two_processes_two_gpus():
             assert st["device_pulls"] == 0 and st["device_pushes"] == 1 and st["device_push_recv"] == 1, st
             assert st["device_staged"] == 0, st
             # strided views cross NVLink as they lie: up to the eager limit gathered into the peer's ring by this
-            # process's kernel (12 KiB, 698 KiB), a large one (8 MiB) gathered out of this process's memory by the peer's pull
-            base = torch.randn(4096, 1024, device="cuda:0").to(torch.bfloat16)
+            # process's kernel (12 KiB, 2.7 MiB), a large one (32 MiB) gathered out of this process's memory by the peer's pull
+            base = torch.randn(4096, 4096, device="cuda:0").to(torch.bfloat16)
             for view in (base[:64, :96].t(), base.t(), base[:2048:2, 1::3]):
                 assert not view.is_contiguous()
                 y = await client.invoke(view, worker_name="peer", session_id=1, function="echo", memory_policy=policy)
@@ -136,7 +136,7 @@ def test_two_processes_two_gpus():
                 del y
             st2 = client.transport_stats()
             assert st2["device_gathers"] == 2 and st2["device_packs"] == 0 and st2["device_staged"] == 0, st2
-            assert st2["device_push_recv"] == 2, st2     # the answer to the 8 MiB view is dense: the peer pushed it
+            assert st2["device_push_recv"] == 2, st2     # the answer to the 32 MiB view is dense: the peer pushed it
             client.stop()
 
         run(main())
@@ -187,7 +187,7 @@ def test_strided_and_unfinished_tensors(cuda_device):
         views = [
             torch.rand(64, 50, device="cuda:0").t(),                         # 12.5 KiB: gathered into the ring slot
             torch.rand(300, 70, device="cuda:0").t(),                        # 82 KiB: the same, by a launch of several CTAs
-            torch.rand(1200, 700, device="cuda:0").t(),                      # 3.2 MiB: gathered by the pull
+            torch.rand(1200, 700, device="cuda:0").t(),                      # 3.2 MiB: gathered into a run of four slots
             big[::2],                                                        # 32 MiB, every other element
             big.view(256, 256, 256).permute(2, 0, 1),                        # 64 MiB, three dimensions
             torch.rand(40, 30, device="cuda:0", dtype=torch.float64).t(),    # 8-byte elements
@@ -256,8 +256,9 @@ def test_tensors_converted_on_the_way(cuda_device):
         cases = [
             (torch.randn(1000, device="cuda:0"), torch.bfloat16),                       # 2 KiB on the wire: eager, converted on its way into the ring slot
             (torch.randn(1 << 20, device="cuda:0"), torch.bfloat16),                    # 2 MiB on the wire: eager, several CTAs
-            (torch.randn(1 << 23, device="cuda:0"), torch.bfloat16),                    # 16 MiB on the wire: converted by the receiver's pull
-            (torch.randn(1 << 23, device="cuda:0")[3:], torch.float16),                 # an unaligned start: the element-wise kernel
+            (torch.randn(3 << 20, device="cuda:0"), torch.bfloat16),                    # 6 MiB on the wire: eager, a run of six slots
+            (torch.randn(1 << 24, device="cuda:0"), torch.bfloat16),                    # 32 MiB on the wire: converted by the receiver's pull
+            (torch.randn(1 << 24, device="cuda:0")[3:], torch.float16),                 # an unaligned start: the element-wise kernel
             (torch.randn(2048, 1500, device="cuda:0").t(), torch.bfloat16),             # strided and converted at once
             (torch.randn(4096, device="cuda:0").to(torch.bfloat16), torch.float32),     # widening
         ]
