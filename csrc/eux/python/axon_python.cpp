@@ -81,4 +81,5 @@ PYBIND11_MODULE(_axon, m) {
   }
   eux::python::bind_types(m);
   eux::python::bind_runtime(m);
+  eux::python::bind_call_conversion(m);
 }

@@ -48,5 +48,6 @@ rpc::ParamMeta python_to_param_typed(py::handle v, rpc::ParamType t);
 
 void bind_types(py::module_& m);
 void bind_runtime(py::module_& m);
+void bind_call_conversion(py::module_& m);
 
 }  // namespace eux::python

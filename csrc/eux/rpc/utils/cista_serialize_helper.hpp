@@ -99,7 +99,10 @@ void put_scalar(W& w, size_t pos, T v) {
 // ---- encoders: each writes the fixed part at `pos` (already reserved) and appends children ----
 template <class W>
 void enc_string(W& w, size_t pos, std::string_view s) {
-  if (s.size() <= 15) {
+  // The short form has no length field: a reader takes the bytes up to the first NUL. A short string that
+  // holds a NUL (a binary blob carried as a string parameter) is therefore written in the long form, which
+  // every reader accepts at any length.
+  if (s.size() <= 15 && std::memchr(s.data(), 0, s.size()) == nullptr) {
     uint8_t img[16] = {0};
     img[0] = 1;
     std::memcpy(img + 1, s.data(), s.size());

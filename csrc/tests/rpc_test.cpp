@@ -78,6 +78,21 @@ EUX_TEST(golden_strings_and_empty_vector) {
   CHECK_EQ(target, 72u + 104u);
   CHECK(std::memcmp(b.data() + target, "a string that", 13) == 0);
   CHECK_EQ(b.size(), 72u + 104u + 47u);
+  // a short string with a NUL inside (a binary blob carried as a string parameter) keeps every byte: it goes
+  // to the long form, because the short form ends at the first NUL for its reader
+  RpcResponseHeader blobs;
+  const std::string blob("\x02\x00\x00\x00\x01\x00\x00\x00" "a", 9);
+  blobs.AddResult(data::string(blob));
+  blobs.AddResult(data::string(std::string("tail\0", 5)));
+  blobs.AddResult(data::string("plain"));
+  b = Serialize(blobs);
+  CHECK_EQ(b[72 + 16], 0);              // long form
+  CHECK_EQ(b[72 + 2 * 104 + 16], 1);    // "plain": short form, as before
+  RpcResponseHeader back = Deserialize<RpcResponseHeader>(b.data(), b.size());
+  CHECK_EQ(back.results.size(), 3u);
+  CHECK(std::get<data::string>(back.results[0].value) == data::string(blob));
+  CHECK_EQ(std::get<data::string>(back.results[1].value).size(), 5u);
+  CHECK(std::get<data::string>(back.results[2].value) == data::string("plain"));
 }
 
 EUX_TEST(round_trip_all_kinds) {

@@ -327,7 +327,7 @@ class _Sig:
     axon/python/src/python_helpers.cpp:405-560)."""
 
     __slots__ = ("param_types", "return_types", "in_payload", "out_payload", "encoded", "param_from_dlpack",
-                 "n_tensor_params", "tensor_return_indices", "non_tensor_indices", "non_tensor_types", "mode")
+                 "n_tensor_params", "tensor_return_indices", "non_tensor_indices", "non_tensor_types", "mode", "plan")
 
     def __init__(self):
         self.param_types: List[Any] = []
@@ -341,6 +341,7 @@ class _Sig:
         self.non_tensor_indices: List[int] = []
         self.non_tensor_types: List[Any] = []
         self.mode = "void"                   # void | single | tensor | tensor_list | tuple
+        self.plan = None                     # native counterpart of _params_to_args for this signature (see _register)
 
 
 def _is_list_alias(t: Any) -> bool:
@@ -519,7 +520,12 @@ def _sig_from_types(param_types, return_types, in_payload, out_payload, from_dlp
 def _params_to_args(sig: _Sig, header, payload) -> list:
     """Positional arguments of the handler, in declaration order (reference:
     bindings_runtime_wrapper.cpp:97-329): every tensor-typed parameter draws from one stream of
-    tensors, every other parameter from the non-tensor params in their order on the wire."""
+    tensors, every other parameter from the non-tensor params in their order on the wire. The native plan does
+    the same without the interpreter and leaves the rare forms (NotImplemented) to the code below."""
+    if sig.plan is not None:
+        args = sig.plan.args(header, payload)
+        if args is not NotImplemented:
+            return args
     plain, metas = _split_params(header.params_meta)
     stream = _TensorStream(payload, metas)
     args, pi = [], 0
@@ -626,7 +632,11 @@ def _error_text(resp, fid: int, session_id: int) -> str:
 def _results_to_python(resp, payload, from_dlpack_fn, fid: int, session_id: int):
     """Response -> what the awaiting caller gets (reference: param_conversion.hpp:83-176): nothing ->
     None, one result -> the value (a tensor, or the list of tensors), several -> a tuple with the tensors
-    spliced in after the plain values."""
+    spliced in after the plain values. The native function does the same without the interpreter and leaves
+    failed responses and the rare forms (NotImplemented) to the code below."""
+    out = _axon._results_to_python(resp, payload, from_dlpack_fn)
+    if out is not NotImplemented:
+        return out
     if not resp.ok:
         raise RuntimeError(_error_text(resp, fid, session_id))
     results = resp.results_meta
@@ -690,6 +700,8 @@ class AxonRuntime(_axon.AxonRuntime):
     # ---- server side ------------------------------------------------------------------------
     def _register(self, fid: int, name: str, sig: _Sig, fn: Callable, memory_policy, lifecycle_policy, wire_dtype=None) -> int:
         code = _wire_code(wire_dtype)
+        sig.plan = _axon._ArgPlan(list(sig.param_types), [i for i, tag in sig.encoded.items() if tag == "ntl"],
+                                  [sig.param_from_dlpack.get(i) for i in range(len(sig.param_types))])
         if code:
             async def handler(header, payload):
                 head, pay, add_meta = _pack_results(sig, await fn(*_params_to_args(sig, header, payload)))

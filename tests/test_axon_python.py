@@ -198,3 +198,100 @@ def test_wire_dtype_converts_host_tensors_before_they_are_sent(axon):
         server.stop()
 
     run(main())
+
+
+def test_native_call_conversion_agrees_with_the_python_layer(axon, monkeypatch):
+    """Arguments and results are drawn from a message by native code where it covers the case and by the
+    Python layer otherwise: both must give the same values for every shape of call."""
+    from typing import List, Tuple
+
+    import torch
+
+    async def battery(tag: str):
+        server = axon.AxonRuntime("conv_srv_" + tag, timeout=5000)
+        client = axon.AxonRuntime("conv_cli_" + tag, timeout=5000)
+
+        async def mixed(a: int, x: np.ndarray, s: str, f: float, flags: List[bool]) -> Tuple[int, np.ndarray, str]:
+            return a + len(flags), x * f, s.upper()
+
+        async def many(xs: List[np.ndarray], k: int) -> List[np.ndarray]:
+            return [x + k for x in xs]
+
+        async def nested(groups: List[List[np.ndarray]], names: List[str], table: List[List[int]]) -> Tuple[List[int], float]:
+            return [len(g) for g in groups] + [len(names), sum(map(sum, table))], float(sum(float(t.sum()) for g in groups for t in g))
+
+        async def flat_from_nested(xs: List[np.ndarray]) -> int:
+            return len(xs)
+
+        async def nothing() -> None:
+            return None
+
+        async def plain(a: int, b: float) -> float:
+            return a * b
+
+        async def torch_echo(x: torch.Tensor) -> torch.Tensor:
+            return x
+
+        async def pair(a: int, b: str) -> Tuple[int, str]:
+            return a, b
+
+        for fn in (mixed, many, nested, flat_from_nested, nothing, plain, pair):
+            server.register_function(fn, from_dlpack_fn=np.from_dlpack)
+        server.register_function(torch_echo)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "conv_srv_" + tag)
+        call = lambda name, *a, **k: client.invoke(*a, worker_name="conv_srv_" + tag, session_id=1, function=name,  # noqa: E731
+                                                   from_dlpack_fn=k.get("fd", np.from_dlpack))
+        x = np.arange(12, dtype=np.float32).reshape(3, 4)
+        big = np.arange(1 << 16, dtype=np.float32)             # rendezvous: the response lands through the memory policy path
+        out = {}
+        out["mixed"] = await call("mixed", 5, x, "abc", 0.5, [True, False, True])
+        out["mixed_big"] = await call("mixed", 1, big, "q", 2.0, [False])
+        out["many"] = await call("many", [x, x[:1].copy(), big], 3)
+        out["nested"] = await call("nested", [[x, x], [], [x]], ["a", "b"], [[1, 2], [3]])
+        out["flat_from_nested"] = await call("flat_from_nested", [[x], [x, x]])
+        out["nothing"] = await call("nothing")
+        out["plain"] = await call("plain", 6, 1.5)
+        out["pair"] = await call("pair", 7, "seven")
+        out["torch"] = await call("torch_echo", torch.arange(10, dtype=torch.int32), fd=None)
+        with pytest.raises(RuntimeError) as too_few:
+            await call("mixed", 5, "abc")
+        out["error"] = str(too_few.value).split(" (function_id")[0]   # the id hashes the worker's name, which differs between the two runs
+        client.stop()
+        server.stop()
+        return out
+
+    def normal(v):
+        if isinstance(v, (tuple, list)):
+            return type(v).__name__, [normal(x) for x in v]
+        if isinstance(v, np.ndarray):
+            return "ndarray", str(v.dtype), v.shape, v.tobytes()
+        if hasattr(v, "numpy"):
+            return "torch", str(v.dtype), tuple(v.shape), v.numpy().tobytes()
+        return v
+
+    native = run(battery("n"))
+    calls = {"plan": 0, "results": 0}
+
+    class PythonOnlyPlan:
+        def __init__(self, *a, **k):
+            pass
+
+        def args(self, header, payload):
+            calls["plan"] += 1
+            return NotImplemented
+
+    def python_only_results(*a):
+        calls["results"] += 1
+        return NotImplemented
+
+    monkeypatch.setattr(axon._axon, "_ArgPlan", PythonOnlyPlan)
+    monkeypatch.setattr(axon._axon, "_results_to_python", python_only_results)
+    python = run(battery("p"))
+    assert calls["plan"] >= 9 and calls["results"] >= 9
+    assert native.keys() == python.keys()
+    for key in native:
+        assert normal(native[key]) == normal(python[key]), key
+    assert native["mixed"][0] == 8 and native["mixed"][1] == "ABC" and native["mixed"][2].shape == (3, 4) and native["nothing"] is None and native["plain"] == 9.0
+    assert native["nested"][0] == [2, 0, 1, 2, 6] and native["flat_from_nested"] == 3 and native["pair"] == (7, "seven")
