@@ -327,7 +327,8 @@ class _Sig:
     axon/python/src/python_helpers.cpp:405-560)."""
 
     __slots__ = ("param_types", "return_types", "in_payload", "out_payload", "encoded", "param_from_dlpack",
-                 "n_tensor_params", "tensor_return_indices", "non_tensor_indices", "non_tensor_types", "mode", "plan")
+                 "n_tensor_params", "tensor_return_indices", "non_tensor_indices", "non_tensor_types", "mode", "plan",
+                 "pack_kind")
 
     def __init__(self):
         self.param_types: List[Any] = []
@@ -342,6 +343,7 @@ class _Sig:
         self.non_tensor_types: List[Any] = []
         self.mode = "void"                   # void | single | tensor | tensor_list | tuple
         self.plan = None                     # native counterpart of _params_to_args for this signature (see _register)
+        self.pack_kind = None                # which branch of _pack_results this signature takes (see _register)
 
 
 def _is_list_alias(t: Any) -> bool:
@@ -566,26 +568,32 @@ def _tensor_payload(tensors: list, as_vec: bool):
     return [_contiguous(t) for t in tensors], 2
 
 
+def _pack_kind(sig: _Sig) -> str:
+    """The branch of ``_pack_results`` a signature takes: its return mode, or "inferred" when an annotation is
+    missing or unknown and the wire form follows the value."""
+    if sig.mode == "void" and not (sig.return_types and sig.return_types[0] == ParamType.UNKNOWN):
+        return "void"
+    if any(t == ParamType.UNKNOWN for t in sig.return_types) or not sig.return_types:
+        return "inferred"
+    return sig.mode
+
+
 def _pack_results(sig: _Sig, result):
     """Handler return value -> (RpcResponseHeader with the plain result params, payload, add_meta)."""
     header = RpcResponseHeader()
-
-    def add_typed(ptype, v, name):
-        header.add_result_typed(ptype, v, name)
-
-    def add_plain(v):
-        header.AddResult(v)
-
-    if sig.mode == "void" and not (sig.return_types and sig.return_types[0] == ParamType.UNKNOWN):
+    kind = sig.pack_kind or _pack_kind(sig)
+    if kind == "tensor":
+        return header, _contiguous(result, strided_ok=True), 1
+    if kind == "void":
         return header, None, 0
-    if any(t == ParamType.UNKNOWN for t in sig.return_types) or not sig.return_types:
+
+    add_typed, add_plain = header.add_result_typed, header.AddResult
+    if kind == "inferred":
         return _pack_inferred(result, header, add_typed, add_plain)
-    if sig.mode == "single":
+    if kind == "single":
         _add_declared(add_typed, add_plain, sig.return_types[0], result)
         return header, None, 0
-    if sig.mode == "tensor":
-        return (header, *_tensor_payload([result], False))
-    if sig.mode == "tensor_list":
+    if kind == "tensor_list":
         return (header, *_tensor_payload(list(result), True))
     items = tuple(result) if isinstance(result, (tuple, list)) else (result,)
     for ptype, i in zip(sig.non_tensor_types, sig.non_tensor_indices):
@@ -700,6 +708,7 @@ class AxonRuntime(_axon.AxonRuntime):
     # ---- server side ------------------------------------------------------------------------
     def _register(self, fid: int, name: str, sig: _Sig, fn: Callable, memory_policy, lifecycle_policy, wire_dtype=None) -> int:
         code = _wire_code(wire_dtype)
+        sig.pack_kind = _pack_kind(sig)
         sig.plan = _axon._ArgPlan(list(sig.param_types), [i for i, tag in sig.encoded.items() if tag == "ntl"],
                                   [sig.param_from_dlpack.get(i) for i in range(len(sig.param_types))])
         if code:
@@ -894,13 +903,6 @@ class AxonRuntime(_axon.AxonRuntime):
         fid = function if isinstance(function, int) else function_id_from_name(function, worker_name)
         header = RpcRequestHeader()
         header.session_id, header.function_id, header.workflow_id = session_id, fid, workflow_id
-
-        def add_typed(ptype, v, name):
-            header.add_param_typed(ptype, v, name)
-
-        def add_plain(v):
-            header.AddParam(v)
-
         tensors: list = []
         for a in args:
             kind = _classify(a)
@@ -909,17 +911,20 @@ class AxonRuntime(_axon.AxonRuntime):
             elif kind == "flat":
                 tensors.extend(a)
             elif kind == "nested":
-                add_typed(ParamType.VECTOR_UINT32, [len(g) for g in a], _GROUP_SIZES)
+                header.add_param_typed(ParamType.VECTOR_UINT32, [len(g) for g in a], _GROUP_SIZES)
                 for g in a:
                     tensors.extend(g)
             else:
-                _add_inferred(add_typed, add_plain, a)
+                _add_inferred(header.add_param_typed, header.AddParam, a)
         sample = tensors[0] if tensors else None
         payload, add_meta = _tensor_payload(tensors, len(tensors) > 1)
         fn = from_dlpack_fn or (_default_from_dlpack(sample) if sample is not None else None)
+        code = 0
+        if wire_dtype is not None:
+            payload, code = _apply_wire_dtype(payload, wire_dtype), _wire_code(wire_dtype)
         # the response is unpacked on the loop thread by the binding itself and settles the future
-        return self._invoke_native(worker_name, header, _apply_wire_dtype(payload, wire_dtype), memory_policy, False,
-                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id), add_meta, _wire_code(wire_dtype))
+        return self._invoke_native(worker_name, header, payload, memory_policy, False,
+                                   lambda resp, pay: _results_to_python(resp, pay, fn, fid, session_id), add_meta, code)
 
 
 
