@@ -437,8 +437,9 @@ class AxonTensorRpc:
     With one rank the server and the client runtime live in this process on the same GPU; with more,
     every rank runs one runtime that serves ``echo`` and calls it on its partner (rank r with r^1).
     Request and response land in buffers that the memory policies hand out, allocated once per shape,
-    so the steady state allocates nothing. The control messages travel over the runtime's TCP
-    connections; the tensor bytes are pulled by the transfer kernel from the sender's memory.
+    so the steady state allocates nothing. The control messages travel through the runtime's shared-memory
+    rings; the tensor bytes are moved by its transfer kernels over the peer mapping: stored into the
+    receiver's ring up to the eager limit (no policy is asked then), pushed into the policy's buffer above it.
     """
 
     def __init__(self, group: PeerGroup, dtype=torch.bfloat16, timeout_ms: int = 60000):
