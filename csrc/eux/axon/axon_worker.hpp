@@ -380,7 +380,7 @@ class AxonWorker {
         if (auto* one = std::get_if<ucxx::UcxBuffer>(&r.payload)) {
           std::vector<size_t> sizes;
           size_t sum = 0;
-          for (auto& m : utils::GetTensorMetas(header->results)) sum += sizes.emplace_back(rpc::utils::CalculateTensorSize(m));
+          for (auto& m : utils::GetTensorMetas(header->results)) sum += sizes.emplace_back(rpc::utils::TensorPayloadBytes(m));
           if (sizes.empty() || sum != one->size()) sizes.assign(1, one->size());
           return {std::move(header), std::move(*one).to_buffer_vec(sizes)};
         }

@@ -33,7 +33,7 @@ inline PayloadVariant view_of(PayloadVariant& p) {
 inline std::vector<size_t> sizes_of(utils::TensorMetaSpan metas) {
   std::vector<size_t> out;
   out.reserve(metas.size());
-  for (auto& m : metas) out.push_back(rpc::utils::CalculateTensorSize(m));
+  for (auto& m : metas) out.push_back(rpc::utils::TensorPayloadBytes(m));
   return out;
 }
 

@@ -75,8 +75,8 @@ struct AxonMessage {
     }
     if (auto* buf = std::get_if<ucxx::UcxBuffer>(&payload)) {
       size_t off = 0;
-      for (size_t k = 0; k < i; ++k) off += rpc::utils::CalculateTensorSize(metas[k]);
-      if (off + rpc::utils::CalculateTensorSize(metas[i]) > buf->size()) throw std::out_of_range("the payload is smaller than its tensors");
+      for (size_t k = 0; k < i; ++k) off += rpc::utils::TensorPayloadBytes(metas[k]);
+      if (off + rpc::utils::TensorPayloadBytes(metas[i]) > buf->size()) throw std::out_of_range("the payload is smaller than its tensors");
       return Tensor<>(static_cast<char*>(buf->data()) + off, metas[i]);
     }
     throw std::runtime_error("the message has no payload");

@@ -4,8 +4,9 @@
 //
 // The package's Python layer holds the same logic in `_params_to_args` and `_results_to_python` and stays the
 // definition of the behaviour; these functions do the common cases without the interpreter and answer
-// NotImplemented for what they leave to it (several tensors packed into one host buffer, a failed response, a
-// payload object of a foreign type), always before anything has been taken out of the message.
+// NotImplemented for what they leave to it (several tensors packed into one host buffer, tensors without
+// elements that came without a payload, a failed response, a payload object of a foreign type), always before
+// anything has been taken out of the message.
 #include "bindings_common.hpp"
 
 namespace eux::python {
@@ -75,8 +76,15 @@ class TensorStream {
     else if (py::isinstance<PyBuffer>(payload)) buf_ = &payload.cast<PyBuffer&>();
     else foreign_ = true;
   }
-  // what this class leaves to the Python layer
-  bool unsupported() const { return foreign_ || (buf_ && metas_.size() > 1); }
+  // What this class leaves to the Python layer: a payload object of another type, several tensors packed into
+  // one buffer, and tensors without elements that came without any payload (they are made there).
+  bool unsupported() const {
+    if (foreign_ || (buf_ && metas_.size() > 1)) return true;
+    if (buf_ || vec_ || metas_.empty()) return false;
+    for (auto* m : metas_)
+      if (rpc::utils::TensorPayloadBytes(*m) != 0) return false;
+    return true;
+  }
   size_t size() const { return (buf_ || vec_) ? metas_.size() : 0; }
   size_t remaining() const { return size() > pos_ ? size() - pos_ : 0; }
 

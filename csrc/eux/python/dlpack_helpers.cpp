@@ -174,8 +174,7 @@ ImportedTensor import_tensor(py::handle obj, bool allow_strided, int wire_dtype)
       }
     }
   }
-  t.nbytes = rpc::utils::CalculateTensorSize(t.meta);
-  if (t.meta.ndim == 0) t.nbytes = (t.meta.dtype.bits * (t.meta.dtype.lanes ? t.meta.dtype.lanes : 1) + 7) / 8;
+  t.nbytes = rpc::utils::TensorPayloadBytes(t.meta);  // a rank-0 tensor travels as its one element
   t.meta.byte_offset = 0;  // the payload starts at the first element
   return t;
 }

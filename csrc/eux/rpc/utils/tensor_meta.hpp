@@ -34,6 +34,8 @@ struct TensorMeta {
     }
   }
   bool is_compact() const {
+    for (int i = 0; i < ndim; ++i)
+      if (shape[i] == 0) return true;  // no elements: any strides describe the same (empty) bytes
     int64_t s = 1;
     for (int i = ndim - 1; i >= 0; --i) {
       if (shape[i] != 1 && strides[i] != s) return false;
@@ -66,6 +68,14 @@ inline size_t CalculateTensorSize(const TensorMeta& meta) {
   int64_t n = 1;
   for (int32_t i = 0; i < meta.ndim; ++i) n *= meta.shape[i];
   return static_cast<size_t>(n) * ((meta.dtype.bits * (meta.dtype.lanes ? meta.dtype.lanes : 1) + 7) / 8);
+}
+
+// Bytes a tensor of this description takes in a payload. The same as CalculateTensorSize, except that a
+// rank-0 tensor is one element there (the senders put the element on the wire, so the receivers must make
+// room for it).
+inline size_t TensorPayloadBytes(const TensorMeta& meta) {
+  if (meta.ndim == 0) return (size_t(meta.dtype.bits) * (meta.dtype.lanes ? meta.dtype.lanes : 1) + 7) / 8;
+  return CalculateTensorSize(meta);
 }
 
 }  // namespace eux::rpc::utils

@@ -252,18 +252,40 @@ def _apply_wire_dtype(payload, wire_dtype):
     return convert(payload, False)
 
 
+_TORCH_DTYPES = {(2, 32): "float32", (2, 64): "float64", (2, 16): "float16", (4, 16): "bfloat16", (0, 64): "int64", (0, 32): "int32",
+                 (0, 16): "int16", (0, 8): "int8", (1, 8): "uint8", (6, 8): "bool"}
+_NUMPY_KINDS = {0: "i", 1: "u", 2: "f", 6: "b"}
+
+
 def _reinterpret(piece, meta: TensorMeta, fn):
     """uint8 1-D view -> tensor of meta's dtype and shape (numpy or torch)."""
     code, bits = meta.dtype.code, meta.dtype.bits
     mod = type(piece).__module__
     if mod.startswith("torch"):
         import torch
-        table = {(2, 32): torch.float32, (2, 64): torch.float64, (2, 16): torch.float16, (4, 16): torch.bfloat16,
-                 (0, 64): torch.int64, (0, 32): torch.int32, (0, 16): torch.int16, (0, 8): torch.int8, (1, 8): torch.uint8, (6, 8): torch.bool}
-        return piece.view(table[(code, bits)]).reshape(list(meta.shape))
+        return piece.view(getattr(torch, _TORCH_DTYPES[(code, bits)])).reshape(list(meta.shape))
     import numpy
-    kinds = {0: "i", 1: "u", 2: "f", 6: "b"}
-    return numpy.asarray(piece).view(numpy.dtype("%s%d" % (kinds.get(code, "u"), bits // 8))).reshape(list(meta.shape))
+    return numpy.asarray(piece).view(numpy.dtype("%s%d" % (_NUMPY_KINDS.get(code, "u"), bits // 8))).reshape(list(meta.shape))
+
+
+def _payload_nbytes(meta: TensorMeta) -> int:
+    """Bytes the tensor takes in a payload: ``meta.nbytes()``, except that a rank-0 tensor is one element there."""
+    if meta.ndim == 0:
+        return (meta.dtype.bits * (meta.dtype.lanes or 1) + 7) // 8
+    return meta.nbytes()
+
+
+def _empty_tensor(meta: TensorMeta, fn: Optional[Callable]):
+    """A tensor without elements never travels (a message of no bytes has no payload): it is made here, in host
+    memory, with the shape and type that its description gives."""
+    code, bits = meta.dtype.code, meta.dtype.bits
+    f = fn or _default_from_dlpack()
+    if _takes_capsule(f) or (code, bits) == (4, 16):
+        import torch
+        return torch.empty(list(meta.shape), dtype=getattr(torch, _TORCH_DTYPES[(code, bits)]))
+    import numpy
+    made = numpy.empty(list(meta.shape), dtype=numpy.dtype("%s%d" % (_NUMPY_KINDS.get(code, "u"), bits // 8)))
+    return made if f is numpy.from_dlpack else f(made)
 
 
 class _TensorStream:
@@ -278,7 +300,10 @@ class _TensorStream:
         self._whole = None
 
     def __len__(self) -> int:
-        return len(self.metas) if self.payload is not None else 0
+        if self.payload is not None:
+            return len(self.metas)
+        # no payload at all: tensors without elements are still there
+        return len(self.metas) if self.metas and all(_payload_nbytes(m) == 0 for m in self.metas) else 0
 
     def remaining(self) -> int:
         return len(self) - self.pos
@@ -288,6 +313,8 @@ class _TensorStream:
         if i >= len(self):
             raise RuntimeError("the message carries fewer tensors than the function takes")
         p, m = self.payload, self.metas[i]
+        if p is None:
+            return _empty_tensor(m, fn)
         if isinstance(p, UcxBufferVec):
             owner = p.owner(i)
             if owner is not None:
@@ -304,8 +331,8 @@ class _TensorStream:
         f = fn or _default_from_dlpack()
         if self._whole is None:
             self._whole = f(p)  # uint8 view
-        off = sum(x.nbytes() for x in self.metas[:i])
-        return _reinterpret(self._whole[off: off + m.nbytes()], m, f)
+        off = sum(_payload_nbytes(x) for x in self.metas[:i])
+        return _reinterpret(self._whole[off: off + _payload_nbytes(m)], m, f)
 
 
 def _split_params(meta_list):
