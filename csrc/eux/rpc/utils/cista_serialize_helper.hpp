@@ -288,8 +288,10 @@ void dec_scalar_vector(const Reader& r, size_t pos, std::vector<E>& out) {
   size_t t;
   out.clear();
   if (n == 0 || !r.target(pos, &t)) return;
+  // the count comes from the wire: the elements must be inside the message before room is made for them
+  const uint8_t* src = r.at(t, sizeof(E) * size_t(n));
   out.resize(n);
-  std::memcpy(static_cast<void*>(out.data()), r.at(t, sizeof(E) * size_t(n)), sizeof(E) * size_t(n));
+  std::memcpy(static_cast<void*>(out.data()), src, sizeof(E) * size_t(n));
 }
 
 inline void dec_tensor_meta(const Reader& r, size_t pos, TensorMeta& m) {
@@ -337,6 +339,7 @@ inline void dec_param_value(const Reader& r, size_t pos, ParamValue& v) {
       uint32_t n = r.get<uint32_t>(s + 8);
       size_t t;
       if (n && r.target(s, &t)) {
+        (void)r.at(t, size_t(n) * kTensorMetaSize);  // all inside the message, or an exception before any allocation
         vec.resize(n);
         for (uint32_t i = 0; i < n; ++i) dec_tensor_meta(r, t + size_t(i) * kTensorMetaSize, vec[i]);
       }
@@ -351,6 +354,7 @@ inline void dec_param_vector(const Reader& r, size_t pos, data::vector<ParamMeta
   uint32_t n = r.get<uint32_t>(pos + 8);
   size_t t;
   if (n == 0 || !r.target(pos, &t)) return;
+  (void)r.at(t, size_t(n) * kParamMetaSize);
   out.resize(n);
   for (uint32_t i = 0; i < n; ++i) {
     size_t p = t + size_t(i) * kParamMetaSize;
@@ -382,6 +386,7 @@ inline void decode(const Reader& r, data::vector<RpcFunctionSignature>& out) {
   uint32_t n = r.get<uint32_t>(8);
   size_t t;
   if (n == 0 || !r.target(0, &t)) return;
+  (void)r.at(t, size_t(n) * kSignatureSize);
   out.resize(n);
   for (uint32_t i = 0; i < n; ++i) {
     size_t p = t + size_t(i) * kSignatureSize;

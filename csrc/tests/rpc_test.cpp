@@ -2,6 +2,7 @@
 // dispatcher, hybrid logical clock (CPU only).
 #include <atomic>
 #include <cstring>
+#include <chrono>
 #include <random>
 
 #include "check.hpp"
@@ -155,6 +156,35 @@ EUX_TEST(round_trip_all_kinds) {
   for (size_t n = 0; n < b.size(); n += 7) {
     try { (void)Deserialize<RpcRequestHeader>(b.data(), n); } catch (const std::exception&) {}
   }
+}
+
+// A count read from the wire is checked against the message before memory is reserved for it: an image that
+// claims four billion elements is refused at once instead of after tens of gigabytes of allocation.
+EUX_TEST(counts_from_the_wire_are_checked_before_memory_is_reserved) {
+  RpcRequestHeader h;
+  h.session_id = session_id_t{1};
+  h.AddParam(data::vector<int64_t>{1, 2, 3});
+  TensorMetaVec metas(2);
+  h.params.push_back(ParamMeta(ParamType::TENSOR_META_VEC, ParamValue(std::in_place_type<TensorMetaVec>, metas)));
+  const byte_buf good = Serialize(h);
+  CHECK_EQ(Deserialize<RpcRequestHeader>(good.data(), good.size()).params.size(), 2u);
+  const uint32_t huge = 0xffffffffu;
+  auto refused_quickly = [&](size_t count_at) {
+    byte_buf bad = good;
+    std::memcpy(bad.data() + count_at, &huge, 4);
+    auto t0 = std::chrono::steady_clock::now();
+    bool threw = false;
+    try {
+      (void)Deserialize<RpcRequestHeader>(bad.data(), bad.size());
+    } catch (const std::exception&) {
+      threw = true;
+    }
+    return threw && std::chrono::steady_clock::now() - t0 < std::chrono::milliseconds(200);
+  };
+  const size_t params_at = 56;                      // the header's fixed part; the ParamMeta records follow
+  CHECK(refused_quickly(32 + 8));                   // how many parameters
+  CHECK(refused_quickly(params_at + 8 + 8 + 8 + 8));              // elements of the int64 vector: ParamMeta +8 value, +8 storage, +8 vector, +8 count
+  CHECK(refused_quickly(params_at + 104 + 8 + 8 + 8));            // tensor descriptions in the second parameter
 }
 
 static int32_t add(int32_t a, int32_t b) { return a + b; }
