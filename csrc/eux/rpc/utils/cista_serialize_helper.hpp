@@ -304,6 +304,19 @@ inline void dec_tensor_meta(const Reader& r, size_t pos, TensorMeta& m) {
   m.byte_offset = r.get<uint64_t>(pos + 16);
   dec_scalar_vector(r, pos + 24, m.shape);
   dec_scalar_vector(r, pos + 48, m.strides);
+  // rank, shape and strides travel as three separate fields; the code that reads a description indexes the two
+  // vectors by the rank, so a description in which they disagree (or with a negative extent) is refused here
+  bool ok = m.ndim >= 0 && m.ndim <= 64 && m.shape.size() == size_t(m.ndim) && (m.strides.empty() || m.strides.size() == size_t(m.ndim));
+  for (size_t i = 0; ok && i < m.shape.size(); ++i) ok = m.shape[i] >= 0;
+  if (!ok) throw std::runtime_error("deserialize: tensor metadata whose rank, shape and strides disagree");
+  if (m.strides.empty() && m.ndim > 0) {  // a sender that left the strides out meant the dense ones
+    m.strides.resize(m.ndim);
+    int64_t st = 1;
+    for (int i = m.ndim - 1; i >= 0; --i) {
+      m.strides[i] = st;
+      if (m.shape[i] > 0 && __builtin_mul_overflow(st, m.shape[i], &st)) throw std::runtime_error("deserialize: tensor metadata too large");
+    }
+  }
 }
 
 template <size_t I = 0>
@@ -349,6 +362,29 @@ inline void dec_param_value(const Reader& r, size_t pos, ParamValue& v) {
   }
 }
 
+// A parameter's declared type and the alternative its value holds come from two separate bytes of the message.
+// Every typed accessor looks at the first and then takes the second for granted, so a message in which they
+// disagree is refused here, once, instead of surfacing as a bad variant access wherever the value is read.
+// UNKNOWN (and numbers no version of the enum has) promise nothing and are left alone.
+inline bool type_matches_value(ParamType t, const ParamValue& v) {
+  const unsigned k = static_cast<unsigned>(t);
+  if (k <= static_cast<unsigned>(ParamType::PRIMITIVE_FLOAT64)) {
+    auto* p = std::get_if<PrimitiveValue>(&v);
+    return p && p->index() == k;
+  }
+  if (k <= static_cast<unsigned>(ParamType::VECTOR_FLOAT64)) {
+    auto* p = std::get_if<VectorValue>(&v);
+    return p && p->index() == k - static_cast<unsigned>(ParamType::VECTOR_BOOL);
+  }
+  switch (t) {
+    case ParamType::STRING: return std::holds_alternative<data::string>(v);
+    case ParamType::VOID: return std::holds_alternative<std::nullptr_t>(v);
+    case ParamType::TENSOR_META: return std::holds_alternative<TensorMeta>(v);
+    case ParamType::TENSOR_META_VEC: return std::holds_alternative<TensorMetaVec>(v);
+    default: return true;
+  }
+}
+
 inline void dec_param_vector(const Reader& r, size_t pos, data::vector<ParamMeta>& out) {
   out.clear();
   uint32_t n = r.get<uint32_t>(pos + 8);
@@ -360,6 +396,7 @@ inline void dec_param_vector(const Reader& r, size_t pos, data::vector<ParamMeta
     size_t p = t + size_t(i) * kParamMetaSize;
     out[i].type = static_cast<ParamType>(r.get<uint8_t>(p));
     dec_param_value(r, p + 8, out[i].value);
+    if (!type_matches_value(out[i].type, out[i].value)) throw std::runtime_error("deserialize: a parameter's type does not match its value");
     out[i].name = dec_string(r, p + 88);
   }
 }

@@ -34,6 +34,7 @@ struct TensorMeta {
     }
   }
   bool is_compact() const {
+    if (ndim < 0 || size_t(ndim) > shape.size() || size_t(ndim) > strides.size()) return false;
     for (int i = 0; i < ndim; ++i)
       if (shape[i] == 0) return true;  // no elements: any strides describe the same (empty) bytes
     int64_t s = 1;
@@ -63,11 +64,20 @@ using TensorMetaSpan = std::span<const TensorMeta>;
 
 // Bytes of the dense tensor the metadata describes: prod(shape) * ceil(bits/8).
 // Rank-0 metadata counts as empty, like the reference (tensor_meta.hpp:91-104).
+// A description that is no tensor (rank and shape disagree, a negative extent, a byte count beyond size_t)
+// counts as the largest size there is, so that every "does it fit" check of a caller fails for it.
 inline size_t CalculateTensorSize(const TensorMeta& meta) {
   if (meta.ndim == 0) return 0;
-  int64_t n = 1;
-  for (int32_t i = 0; i < meta.ndim; ++i) n *= meta.shape[i];
-  return static_cast<size_t>(n) * ((meta.dtype.bits * (meta.dtype.lanes ? meta.dtype.lanes : 1) + 7) / 8);
+  constexpr size_t kInvalid = static_cast<size_t>(-1);
+  if (meta.ndim < 0 || static_cast<size_t>(meta.ndim) > meta.shape.size()) return kInvalid;
+  size_t n = 1;
+  for (int32_t i = 0; i < meta.ndim; ++i) {
+    if (meta.shape[i] < 0 || __builtin_mul_overflow(n, static_cast<size_t>(meta.shape[i]), &n)) return kInvalid;
+  }
+  const size_t elem = (size_t(meta.dtype.bits) * (meta.dtype.lanes ? meta.dtype.lanes : 1) + 7) / 8;
+  size_t bytes = 0;
+  if (__builtin_mul_overflow(n, elem, &bytes)) return kInvalid;
+  return bytes;
 }
 
 // Bytes a tensor of this description takes in a payload. The same as CalculateTensorSize, except that a

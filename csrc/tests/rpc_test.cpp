@@ -187,6 +187,53 @@ EUX_TEST(counts_from_the_wire_are_checked_before_memory_is_reserved) {
   CHECK(refused_quickly(params_at + 104 + 8 + 8 + 8));            // tensor descriptions in the second parameter
 }
 
+// The declared type of a parameter and the alternative its value holds are separate bytes of the image; so are a
+// tensor description's rank and the lengths of its shape and strides. An image in which they disagree is refused
+// when it is read, not wherever the value is used later.
+EUX_TEST(images_that_contradict_themselves_are_refused) {
+  RpcRequestHeader h;
+  h.AddParam(int64_t{5});
+  TensorMeta m;
+  m.ndim = 2;
+  m.dtype = {kDLFloat, 32, 1};
+  m.shape = {3, 4};
+  m.strides = {4, 1};
+  h.params.push_back(ParamMeta(ParamType::TENSOR_META, ParamValue(std::in_place_type<TensorMeta>, m)));
+  const byte_buf good = Serialize(h);
+  RpcRequestHeader back = Deserialize<RpcRequestHeader>(good.data(), good.size());
+  CHECK_EQ(back.GetPrimitive<int64_t>(0), int64_t{5});
+  CHECK_EQ(utils::CalculateTensorSize(back.GetTensor(1)), size_t(48));
+  const size_t p0 = 56, p1 = 56 + 104;  // the two ParamMeta records
+  auto refused = [&](size_t at, auto value) {
+    byte_buf bad = good;
+    std::memcpy(bad.data() + at, &value, sizeof(value));
+    try {
+      (void)Deserialize<RpcRequestHeader>(bad.data(), bad.size());
+    } catch (const std::exception&) {
+      return true;
+    }
+    return false;
+  };
+  CHECK(refused(p0, uint8_t(ParamType::STRING)));              // says string, holds an int64
+  CHECK(refused(p0, uint8_t(ParamType::PRIMITIVE_FLOAT64)));   // says double, holds an int64
+  CHECK(refused(p0, uint8_t(ParamType::TENSOR_META)));         // says tensor, holds an int64
+  CHECK(refused(p1, uint8_t(ParamType::VECTOR_INT64)));        // says vector, holds a tensor description
+  CHECK(!refused(p0, uint8_t(ParamType::UNKNOWN)));            // promises nothing: nobody reads it by type
+  const size_t meta_at = p1 + 8 + 8;                           // ParamMeta +8 value, +8 storage
+  CHECK(refused(meta_at + 8, int32_t(3)));                     // rank 3, two extents
+  CHECK(refused(meta_at + 8, int32_t(-1)));
+  CHECK(refused(meta_at + 8, int32_t(1 << 20)));
+  // descriptions that are no tensor count as larger than any buffer
+  TensorMeta huge = m;
+  huge.shape = {int64_t(1) << 62, 8};
+  CHECK_EQ(utils::CalculateTensorSize(huge), static_cast<size_t>(-1));
+  huge.shape = {-3, 4};
+  CHECK_EQ(utils::CalculateTensorSize(huge), static_cast<size_t>(-1));
+  huge.ndim = 5;
+  CHECK_EQ(utils::CalculateTensorSize(huge), static_cast<size_t>(-1));
+  CHECK(!huge.is_compact());
+}
+
 static int32_t add(int32_t a, int32_t b) { return a + b; }
 
 EUX_TEST(thousand_add_calls) {

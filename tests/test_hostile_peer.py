@@ -1,0 +1,19 @@
+"""Whatever a TCP peer sends, a runtime refuses it or serves it: no crash, no stall, no unbounded allocation.
+(The cases this kind of run has found are pinned one by one in csrc/tests/rpc_test.cpp: counts checked before
+memory is reserved, parameter types that contradict their values, tensor descriptions that are no tensor.)"""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("seed", [3, 4])
+def test_mutated_client_streams_do_not_bring_the_server_down(native_build, seed):
+    env = dict(os.environ, PYTHONPATH=str(ROOT), EUX_LOG_LEVEL="OFF")
+    out = subprocess.run([sys.executable, str(ROOT / "tests" / "mp_hostile_peer.py"), str(seed), "600"], env=env, cwd=str(ROOT),
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-1500:] + out.stderr[-3000:]
