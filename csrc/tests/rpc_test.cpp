@@ -266,6 +266,65 @@ EUX_TEST(thousand_add_calls) {
   CHECK_EQ(ok.function_id.v_, 1u);
 }
 
+// Forty thousand mutated copies of a valid request image go through the dispatcher, payload attached: each ends
+// as a response with a status (or as an exception from the reader), none as a fault, and the handler only ever
+// sees arguments that agree with the image it was given.
+EUX_TEST(mutated_request_images_end_as_statuses) {
+  DefaultUcxMemoryResourceManager mr;
+  RpcDispatcher disp("svc");
+  size_t handled = 0;
+  disp.RegisterFunction(
+      function_id_t{3},
+      [&handled](const RpcRequestHeader& req, int32_t a, const data::string& s, const data::vector<int64_t>& v, const TensorMeta& m, UcxBuffer& buf,
+                 const RpcResponseBuilder& b) {
+        ++handled;
+        int64_t sum = a;
+        for (auto x : v) sum += x;
+        // the dispatcher has checked the description against the payload: every element may be touched
+        const size_t bytes = utils::CalculateTensorSize(m);
+        CHECK(bytes <= buf.size());
+        unsigned char acc = 0;
+        for (size_t i = 0; i < bytes; ++i) acc ^= static_cast<unsigned char*>(buf.data())[i];
+        return b.PrepareResponse(req.session_id, req.request_id, data::string(s.str() + "!"), sum + acc);
+      },
+      data::string("mixed"));
+  TensorMeta m;
+  m.ndim = 2;
+  m.dtype = {kDLFloat, 32, 1};
+  m.shape = {4, 8};
+  m.strides = {8, 1};
+  UcxBuffer buf(mr, ucx_memory_type::HOST, 128);
+  std::memset(buf.data(), 1, 128);
+  auto [req, payload] = RpcRequestBuilder{}.PrepareRequest({session_id_t{8}, request_id_t{9}, function_id_t{3}}, int32_t(5),
+                                                          data::string("a string of more than fifteen bytes"),
+                                                          data::vector<int64_t>{1, 2, 3}, m, std::move(buf));
+  const byte_buf good = Serialize(req);
+  CHECK(disp.Dispatch(Deserialize<RpcRequestHeader>(good.data(), good.size()), payload).header.status.ok());
+  std::mt19937 rng(7);
+  size_t refused_by_reader = 0, statuses = 0, served = 0;
+  for (int i = 0; i < 40000; ++i) {
+    byte_buf bad = good;
+    const int flips = 1 + int(rng() % 6);
+    for (int k = 0; k < flips; ++k) {
+      const size_t at = rng() % bad.size();
+      if (rng() % 10 < 6) bad[at] = static_cast<unsigned char>(rng() & 0xff);
+      else bad[at] ^= static_cast<unsigned char>(1u << (rng() % 8));
+    }
+    size_t len = bad.size();
+    if (rng() % 4 == 0) len = rng() % (bad.size() + 1);
+    try {
+      RpcRequestHeader h = Deserialize<RpcRequestHeader>(bad.data(), len);
+      auto res = disp.Dispatch(h, payload);
+      res.header.status.ok() ? ++served : ++statuses;
+    } catch (const std::exception&) {
+      ++refused_by_reader;
+    }
+  }
+  CHECK_EQ(refused_by_reader + statuses + served, size_t(40000));
+  CHECK(served > 0 && statuses > 0 && refused_by_reader > 0);
+  CHECK(handled >= served);
+}
+
 EUX_TEST(dispatch_errors_and_argument_kinds) {
   DefaultUcxMemoryResourceManager mr;
   RpcDispatcher disp("svc");
