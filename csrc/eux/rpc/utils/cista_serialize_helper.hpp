@@ -245,9 +245,13 @@ class Reader {
   template <class T>
   T get(size_t pos) const {
     check(pos, sizeof(T));
-    T v;
-    std::memcpy(&v, p_ + pos, sizeof(T));
-    return v;
+    if constexpr (std::is_same_v<T, bool>) {
+      return p_[pos] != 0;  // any byte may stand there; only 0 and 1 are values of a bool
+    } else {
+      T v;
+      std::memcpy(&v, p_ + pos, sizeof(T));
+      return v;
+    }
   }
   const uint8_t* at(size_t pos, size_t len) const {
     check(pos, len);

@@ -278,14 +278,14 @@ EUX_TEST(mutated_request_images_end_as_statuses) {
       [&handled](const RpcRequestHeader& req, int32_t a, const data::string& s, const data::vector<int64_t>& v, const TensorMeta& m, UcxBuffer& buf,
                  const RpcResponseBuilder& b) {
         ++handled;
-        int64_t sum = a;
-        for (auto x : v) sum += x;
+        uint64_t sum = static_cast<uint64_t>(a);   // unsigned: the mutated values may be anything
+        for (auto x : v) sum += static_cast<uint64_t>(x);
         // the dispatcher has checked the description against the payload: every element may be touched
         const size_t bytes = utils::CalculateTensorSize(m);
         CHECK(bytes <= buf.size());
         unsigned char acc = 0;
         for (size_t i = 0; i < bytes; ++i) acc ^= static_cast<unsigned char*>(buf.data())[i];
-        return b.PrepareResponse(req.session_id, req.request_id, data::string(s.str() + "!"), sum + acc);
+        return b.PrepareResponse(req.session_id, req.request_id, data::string(s.str() + "!"), static_cast<int64_t>(sum + acc));
       },
       data::string("mixed"));
   TensorMeta m;
