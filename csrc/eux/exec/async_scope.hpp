@@ -195,26 +195,77 @@ class async_scope {
     });
   }
 
+  // Completes with a value when nothing spawned is still running, and with done when the receiver asks it to
+  // stop first (`stop_when(scope.join(), deadline)` gives the stragglers a deadline): the scope then simply has
+  // no waiter any more, and may be joined again later.
   struct join_sender {
     using value_type = void;
     async_scope* scope;
     template <class R>
     struct op {
+      // Who completes the operation: the scope's last work item or the stop request, whichever turns `finished`
+      // first. The state is shared because the loser may run after the winner's completion has destroyed the
+      // operation, and must find that out without touching it. A stop request that arrives while start() is
+      // still setting up is only noted; start() acts on it when it is done.
+      struct state {
+        std::atomic<bool> finished{false};
+        std::atomic<bool> starting{true};
+        std::atomic<bool> stop_seen{false};
+      };
+      struct stop_fn {
+        op* o;
+        void operator()() const noexcept {
+          auto s = o->st;  // the callback's registration keeps the operation alive while this runs
+          if (s->starting.load(std::memory_order_acquire)) {
+            s->stop_seen.store(true, std::memory_order_release);
+            if (s->starting.load(std::memory_order_acquire)) return;  // start() will see the note
+          }
+          cancel(o, s);
+        }
+      };
+      using stop_cb_t = typename stop_token_of_t<R>::template callback_type<stop_fn>;
       async_scope* scope;
       R r;
+      std::shared_ptr<state> st;
+      std::optional<stop_cb_t> cb;
+
+      op(async_scope* s, R&& r_) : scope(s), r(std::move(r_)) {}
+      op(op&&) = delete;
+
       void start() noexcept {
-        std::unique_lock lk(scope->mu_);
-        if (scope->outstanding_.load(std::memory_order_acquire) == 0) {
-          lk.unlock();
-          r.set_value();
-        } else {
-          scope->waiter_ = [this] { r.set_value(); };
+        auto s = st = std::make_shared<state>();
+        cb.emplace(::eux::exec::get_stop_token(r), stop_fn{this});
+        {
+          std::unique_lock lk(scope->mu_);
+          if (scope->outstanding_.load(std::memory_order_acquire) == 0) {
+            lk.unlock();
+            s->finished.store(true, std::memory_order_release);
+            cb.reset();
+            r.set_value();
+            return;
+          }
+          scope->waiter_ = [this, s] {
+            if (s->finished.exchange(true)) return;  // the stop request completed it: `this` may be gone
+            cb.reset();                               // waits for a stop callback that is running right now
+            r.set_value();
+          };
         }
+        // from here on the waiter may complete (and destroy) the operation at any moment: only `s` is touched
+        s->starting.store(false, std::memory_order_release);
+        if (s->stop_seen.load(std::memory_order_acquire)) cancel(this, s);
+      }
+      static void cancel(op* o, const std::shared_ptr<state>& s) noexcept {
+        if (s->finished.exchange(true)) return;
+        {
+          std::lock_guard lk(o->scope->mu_);
+          o->scope->waiter_ = nullptr;
+        }
+        o->r.set_done();
       }
     };
     template <class R>
     auto connect(R&& r) const {
-      return op<std::decay_t<R>>{scope, std::forward<R>(r)};
+      return op<std::decay_t<R>>(scope, std::decay_t<R>(std::forward<R>(r)));
     }
   };
   // completes when nothing spawned is still running

@@ -177,18 +177,34 @@ class PyAxonRuntime {
   }
   void start() {
     attach_loop();
+    open_gate();
     throw_if(rt_->Start());
   }
   void start_server() {
     attach_loop();
+    open_gate();
     throw_if(rt_->StartServer());
   }
   void start_client() {
     attach_loop();
     throw_if(rt_->StartClient());
   }
+  // No call reaches the event loop from here on; those already queued for it are answered now (on this thread,
+  // which is the loop's), because the code that follows blocks this thread until every call has an answer.
+  void close_gate() {
+    {
+      std::lock_guard lk(gate_mu_);
+      stopping_ = true;
+    }
+    wake_.process_queue();
+  }
+  void open_gate() {
+    std::lock_guard lk(gate_mu_);
+    stopping_ = false;
+  }
   void stop() {
     if (!rt_) return;
+    close_gate();
     // handlers that are still awaiting are answered with CANCELLED and their tasks cancelled
     auto running = std::move(running_tasks_);
     running_tasks_.clear();
@@ -209,6 +225,17 @@ class PyAxonRuntime {
     wake_.detach();
   }
   void stop_server() {
+    close_gate();
+    auto running = std::move(running_tasks_);
+    running_tasks_.clear();
+    for (auto& [id, t] : running) {
+      t.answer_cancelled();
+      try {
+        t.task.attr("cancel")();
+      } catch (py::error_already_set&) {
+      }
+    }
+    running.clear();
     py::gil_scoped_release nogil;
     rt_->StopServer();
   }
@@ -492,6 +519,17 @@ class PyAxonRuntime {
       return rpc::AsyncInvokeSender(ex::create<rpc::RpcInvokeResult<rpc::ReturnedPayload>>([self, fn, st](auto handle) {
         // hop to the asyncio thread: start the coroutine as a task, finish the C++ call from its done-callback
         ucxx::nvtx_mark("axon.python.handler_queued");
+        // A runtime that is stopping takes no more work onto the event loop: its stop() runs on the loop's thread
+        // and waits there for every call to be answered, so a call that waited for the loop would wait for ever.
+        // The gate is closed and the queue drained under one mutex, so that no call slips in between.
+        std::unique_lock gate(self->gate_mu_);
+        if (self->stopping_) {
+          gate.unlock();
+          handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{
+              st->builder.PrepareError(st->req.session_id, st->req.request_id, rpc::make_error_code(rpc::RpcErrc::UNAVAILABLE), "the server is stopping"),
+              rpc::ReturnedPayload{}});
+          return;
+        }
         self->wake_.enqueue([self, fn, st, handle]() mutable {
           ucxx::NvtxRange range("axon.python.handler_on_loop");
           // the call is answered exactly once: by the task's completion, or by stop() while it still runs
@@ -502,6 +540,10 @@ class PyAxonRuntime {
             handle.set_value(rpc::RpcInvokeResult<rpc::ReturnedPayload>{
                 st->builder.PrepareError(st->req.session_id, st->req.request_id, ec, what), rpc::ReturnedPayload{}});
           };
+          if (self->stopping_) {  // queued before the gate closed, run by stop()'s drain
+            fail(rpc::make_error_code(rpc::RpcErrc::UNAVAILABLE), "the server is stopping");
+            return;
+          }
           try {
             py::object payload_obj = payload_to_python(std::move(st->payload), self->device_id_, self->mr_);
             py::object coro = (*fn)(py::cast(st->req), payload_obj);
@@ -607,6 +649,8 @@ class PyAxonRuntime {
   bool is_cuda_ = false;
   std::shared_ptr<ucxx::UcxMemoryResourceManager> mr_;
   PythonWakeManager wake_;
+  std::mutex gate_mu_;      // see close_gate()
+  bool stopping_ = false;
   struct RunningTask {
     py::object task;
     std::function<void()> answer_cancelled;

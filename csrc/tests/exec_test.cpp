@@ -127,6 +127,42 @@ EUX_TEST(async_scope_spawn_and_join) {
   CHECK(std::chrono::steady_clock::now() - t0 < 2s);
 }
 
+// join() under a deadline: work that ignores its stop request does not hold the joiner for ever; once the work
+// has finished, the same scope joins as usual. Many rounds, so that the work's end and the deadline also meet.
+EUX_TEST(async_scope_join_gives_up_at_a_deadline) {
+  timed_single_thread_context timer;
+  auto sch = timer.get_scheduler();
+  {
+    async_scope scope;
+    std::thread worker;
+    std::atomic<bool> release{false};
+    scope.spawn_detached(create<int>([&](auto h) {
+                           worker = std::thread([h, &release]() mutable {
+                             while (!release.load()) std::this_thread::sleep_for(1ms);
+                             h.set_value(1);
+                           });
+                         }) |
+                         then([](int) {}));
+    auto t0 = std::chrono::steady_clock::now();
+    auto r = sync_wait(stop_when(scope.join(), schedule_after(sch, 30ms)));
+    CHECK(!r.has_value());  // done: the deadline came first
+    CHECK(std::chrono::steady_clock::now() - t0 < 2s);
+    release.store(true);
+    CHECK(sync_wait(scope.join()).has_value());
+    worker.join();
+  }
+  static_thread_pool pool(2);
+  int joined = 0, gave_up = 0;
+  for (int round = 0; round < 300; ++round) {
+    async_scope scope;
+    scope.spawn_detached(on(pool.get_scheduler(), just_from([round] { std::this_thread::sleep_for(std::chrono::microseconds(50 + (round * 37) % 400)); })));
+    auto r = sync_wait(stop_when(scope.join(), schedule_after(sch, std::chrono::microseconds(50 + (round * 53) % 400))));
+    r.has_value() ? ++joined : ++gave_up;
+    CHECK(sync_wait(scope.join()).has_value());
+  }
+  CHECK_EQ(joined + gave_up, 300);
+}
+
 EUX_TEST(any_sender_type_erasure) {
   any_sender_of<int> a = just(5) | then([](int x) { return x * 3; });
   auto r = sync_wait(std::move(a));

@@ -172,3 +172,19 @@ def test_devices_and_context_handle(axon):
     assert h is None or isinstance(h, int)
     with pytest.raises(ValueError):
         axon.AxonRuntime("bad_device", device=axon.rocm(0))
+
+
+def test_stop_drop_and_cancel_with_calls_in_flight(native_build):
+    """stop() runs on the event loop's thread and waits for every call to be answered: requests that were queued
+    for the loop at that moment used to wait for the loop in turn. Forty rounds of stopping, dropping and
+    cancelling with calls in flight, in a process of its own so that a deadlock shows as a timeout."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root), EUX_LOG_LEVEL="OFF")
+    out = subprocess.run([sys.executable, str(root / "tests" / "mp_stop_in_flight.py"), "40"], env=env, cwd=str(root),
+                         capture_output=True, text=True, timeout=240)
+    assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-1000:] + out.stderr[-3000:]
