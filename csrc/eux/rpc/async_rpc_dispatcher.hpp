@@ -93,6 +93,12 @@ class AsyncRpcDispatcher {
           ReturnedPayload{}};
       return AsyncInvokeSender(exec::just(std::move(r)));
     }
+    if (!RpcDispatcher::TensorsFitPayload(req.params, std::get_if<ucxx::UcxBuffer>(&payload), std::get_if<ucxx::UcxBufferVec>(&payload))) {
+      RpcInvokeResult<ReturnedPayload> r{
+          detail::error_header(req, b, make_error_code(RpcErrc::INVALID_ARGUMENT), "the tensor metadata describes more bytes than the payload holds"),
+          ReturnedPayload{}};
+      return AsyncInvokeSender(exec::just(std::move(r)));
+    }
     return e->fn(req, std::move(payload), b);
   }
 

@@ -397,7 +397,45 @@ class RpcDispatcher {
     if (!e)
       return {detail::error_header(req, b, make_error_code(RpcErrc::NOT_FOUND), "function " + std::to_string(req.function_id.v_) + " is not registered"),
               ReturnedPayload{}};
+    if (!TensorsFitPayload(req.params, ctx.get<ucxx::UcxBuffer>(), ctx.get<ucxx::UcxBufferVec>()))
+      return {detail::error_header(req, b, make_error_code(RpcErrc::INVALID_ARGUMENT), "the tensor metadata describes more bytes than the payload holds"),
+              ReturnedPayload{}};
     return e->fn(req, ctx, b);
+  }
+
+  // What a handler may take for granted about a call that carries both tensor descriptions and a payload: every
+  // described tensor lies inside the payload (one description: inside the buffer, or the vector's first segment;
+  // several: one segment each, or back to back in one buffer). The descriptions come from the caller, so this is
+  // checked before any handler runs. A call without a payload, or without descriptions, passes: nothing to compare.
+  static bool TensorsFitPayload(const data::vector<ParamMeta>& params, const ucxx::UcxBuffer* buf, const ucxx::UcxBufferVec* vec) {
+    if (!buf && !vec) return true;
+    const TensorMeta* one = nullptr;
+    const TensorMetaVec* many = nullptr;
+    for (auto& p : params) {
+      if (p.type == ParamType::TENSOR_META) one = std::get_if<TensorMeta>(&p.value), many = nullptr;
+      else if (p.type == ParamType::TENSOR_META_VEC) many = std::get_if<TensorMetaVec>(&p.value), one = nullptr;
+    }
+    if (one) {
+      const size_t need = utils::TensorPayloadBytes(*one);
+      if (buf) return need <= buf->size();
+      return vec->size() >= 1 && need <= (*vec)[0].size;
+    }
+    if (many) {
+      if (vec) {
+        if (vec->size() < many->size()) return false;
+        for (size_t i = 0; i < many->size(); ++i)
+          if (utils::TensorPayloadBytes((*many)[i]) > (*vec)[i].size) return false;
+        return true;
+      }
+      size_t total = 0;
+      for (auto& m : *many) {
+        const size_t n = utils::TensorPayloadBytes(m);
+        if (n > buf->size() - std::min(total, buf->size())) return false;  // also what overflows the sum
+        total += n;
+      }
+      return true;
+    }
+    return true;
   }
 
   // ---- response (de)serialisation helpers ----

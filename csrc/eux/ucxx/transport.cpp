@@ -380,7 +380,14 @@ ssize_t Worker::io_readv(Endpoint* ep, const iovec* iov, int cnt) {
   return total;
 }
 ssize_t Worker::io_writev(Endpoint* ep, const iovec* iov, int cnt) {
-  if (!ep->shm_active_) return ::writev(ep->fd_, iov, cnt);
+  if (!ep->shm_active_) {
+    // sendmsg, not writev: a peer that has gone away must end as EPIPE here, not as a SIGPIPE for the whole
+    // process (a library cannot count on the application ignoring that signal)
+    msghdr mh{};
+    mh.msg_iov = const_cast<iovec*>(iov);
+    mh.msg_iovlen = static_cast<size_t>(cnt);
+    return ::sendmsg(ep->fd_, &mh, MSG_NOSIGNAL);
+  }
   ssize_t total = 0;
   for (int i = 0; i < cnt; ++i) {
     ssize_t n = ep->shm_->write(iov[i].iov_base, iov[i].iov_len);
@@ -646,7 +653,7 @@ void Worker::close(Endpoint* ep, bool notify_peer) {
     fh.type = kClose;
     // best effort, blocking for at most the socket buffer: the frame is 40 bytes
     if (ep->shm_active_) (void)ep->shm_->write(&fh, sizeof(fh));
-    else (void)!::write(ep->fd_, &fh, sizeof(fh));
+    else (void)!::send(ep->fd_, &fh, sizeof(fh), MSG_NOSIGNAL);
   }
   if (ep->fd_ >= 0) {
     epoll_ctl(epfd_, EPOLL_CTL_DEL, ep->fd_, nullptr);

@@ -119,7 +119,9 @@ static void register_plus_one(AxonRuntime& rt, const Options& o) {
       UcxBuffer out(*mr, buf.type(), buf.size());
       const float* f = static_cast<const float*>(buf.data());
       float* g = static_cast<float*>(out.data());
-      for (int64_t i = 0; i < m.shape[0]; ++i) g[i] = f[i] + 1.0f;
+      // the element count comes from the bytes that arrived, not from the caller's description of them
+      const size_t count = buf.size() / sizeof(float);
+      for (size_t i = 0; i < count; ++i) g[i] = f[i] + 1.0f;
       return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out));
     };
     rt.RegisterFunction(function_id_t{1}, handler, "plus_one");
