@@ -60,7 +60,9 @@ class ShmChannel {
     int fd = ::shm_open(name.c_str(), O_RDWR | O_CLOEXEC, 0600);
     if (fd < 0) return nullptr;
     struct stat st{};
-    if (::fstat(fd, &st) != 0 || static_cast<size_t>(st.st_size) != total_bytes()) {
+    // only a segment of this user's own making is mapped: its indices and flag words are taken as they are
+    // afterwards, which is more than a stranger on the same host is trusted with (he keeps the socket)
+    if (::fstat(fd, &st) != 0 || static_cast<size_t>(st.st_size) != total_bytes() || st.st_uid != ::geteuid()) {
       ::close(fd);
       return nullptr;
     }
@@ -84,7 +86,12 @@ class ShmChannel {
     ShmRing* r = out_ring();
     const uint64_t tail = r->tail.load(std::memory_order_relaxed);
     const uint64_t head = r->head.load(std::memory_order_acquire);
-    const size_t room = kRingBytes - static_cast<size_t>(tail - head);
+    const uint64_t used = tail - head;
+    if (used > kRingBytes) {  // indices that no honest peer produces: the ring is not written through them
+      errno = EIO;
+      return -1;
+    }
+    const size_t room = kRingBytes - static_cast<size_t>(used);
     size_t n = len < room ? len : room;
     if (n == 0) {
       errno = EAGAIN;
@@ -102,6 +109,10 @@ class ShmChannel {
     ShmRing* r = in_ring();
     const uint64_t head = r->head.load(std::memory_order_relaxed);
     const uint64_t tail = r->tail.load(std::memory_order_acquire);
+    if (tail - head > kRingBytes) {  // see write()
+      errno = EIO;
+      return -1;
+    }
     const size_t avail = static_cast<size_t>(tail - head);
     size_t n = len < avail ? len : avail;
     if (n == 0) {

@@ -369,6 +369,7 @@ ssize_t Worker::io_readv(Endpoint* ep, const iovec* iov, int cnt) {
   ssize_t total = 0;
   for (int i = 0; i < cnt; ++i) {
     ssize_t n = ep->shm_->read(iov[i].iov_base, iov[i].iov_len);
+    if (n < 0 && errno == EIO && total == 0) return -1;  // a ring with impossible indices: the connection ends
     if (n < 0) break;
     total += n;
     if (static_cast<size_t>(n) < iov[i].iov_len) break;
@@ -391,6 +392,7 @@ ssize_t Worker::io_writev(Endpoint* ep, const iovec* iov, int cnt) {
   ssize_t total = 0;
   for (int i = 0; i < cnt; ++i) {
     ssize_t n = ep->shm_->write(iov[i].iov_base, iov[i].iov_len);
+    if (n < 0 && errno == EIO && total == 0) return -1;
     if (n < 0) break;
     total += n;
     if (static_cast<size_t>(n) < iov[i].iov_len) break;

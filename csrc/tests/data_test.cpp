@@ -1,3 +1,6 @@
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <sys/mman.h>
 // RAII buffers, memory resource, lock-free queue, connection manager (CPU only).
 #include <cstring>
 #include <thread>
@@ -148,6 +151,45 @@ EUX_TEST(lock_free_queue_mpmc) {
 // The shared-memory byte rings: a producer thread streams 16 MiB of a known sequence through a 2 MiB
 // ring in odd-sized pieces while the consumer reads odd-sized pieces; every byte arrives in order,
 // in both directions, and a full ring reports EAGAIN instead of overwriting.
+// Ring indices that no honest peer produces (more bytes in flight than the ring holds, a head ahead of its tail)
+// end as an error of the channel; nothing is copied through them.
+EUX_TEST(shm_channel_refuses_impossible_indices) {
+  using eux::ucxx::transport::ShmChannel;
+  using eux::ucxx::transport::ShmRing;
+  const std::string name = "/eux-test-idx-" + std::to_string(getpid());
+  auto a = ShmChannel::create(name);
+  CHECK(a != nullptr);
+  int fd = ::shm_open(name.c_str(), O_RDWR, 0600);  // a second mapping of the same segment, to play the hostile peer with
+  CHECK(fd >= 0);
+  struct stat st{};
+  CHECK(::fstat(fd, &st) == 0);
+  char* raw = static_cast<char*>(::mmap(nullptr, size_t(st.st_size), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0));
+  ::close(fd);
+  CHECK(raw != MAP_FAILED);
+  auto b = ShmChannel::open(name);
+  CHECK(b != nullptr);
+  auto* ring0 = reinterpret_cast<ShmRing*>(raw + 64);  // creator -> opener, right behind the 64-byte header
+  char buf[16] = {0};
+  CHECK_EQ(a->write("abc", 3), ssize_t(3));
+  CHECK_EQ(b->read(buf, sizeof(buf)), ssize_t(3));
+  const uint64_t at = ring0->tail.load();
+  ring0->tail.store(at + ShmChannel::kRingBytes + 1);
+  errno = 0;
+  CHECK(b->read(buf, sizeof(buf)) == -1 && errno == EIO);
+  errno = 0;
+  CHECK(a->write(buf, sizeof(buf)) == -1 && errno == EIO);
+  ring0->tail.store(at);
+  ring0->head.store(at + 5);
+  errno = 0;
+  CHECK(b->read(buf, sizeof(buf)) == -1 && errno == EIO);
+  errno = 0;
+  CHECK(a->write(buf, sizeof(buf)) == -1 && errno == EIO);
+  ring0->head.store(at);
+  CHECK_EQ(a->write("z", 1), ssize_t(1));
+  CHECK(b->read(buf, sizeof(buf)) == 1 && buf[0] == 'z');
+  ::munmap(raw, size_t(st.st_size));
+}
+
 EUX_TEST(shm_channel_streams_bytes_both_ways) {
   using eux::ucxx::transport::ShmChannel;
   const std::string name = "/eux-test-" + std::to_string(getpid());
