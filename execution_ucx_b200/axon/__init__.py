@@ -610,6 +610,8 @@ def _pack_results(sig: _Sig, result):
     header = RpcResponseHeader()
     kind = sig.pack_kind or _pack_kind(sig)
     if kind == "tensor":
+        if result is None:
+            raise TypeError("the function returned None where its annotation promises a tensor")
         return header, _contiguous(result, strided_ok=True), 1
     if kind == "void":
         return header, None, 0

@@ -295,3 +295,33 @@ def test_native_call_conversion_agrees_with_the_python_layer(axon, monkeypatch):
         assert normal(native[key]) == normal(python[key]), key
     assert native["mixed"][0] == 8 and native["mixed"][1] == "ABC" and native["mixed"][2].shape == (3, 4) and native["nothing"] is None and native["plain"] == 9.0
     assert native["nested"][0] == [2, 0, 1, 2, 6] and native["flat_from_nested"] == 3 and native["pair"] == (7, "seven")
+
+
+def test_a_handler_that_breaks_its_annotation_fails_the_call(axon):
+    async def main():
+        server = axon.AxonRuntime("brk_srv", timeout=3000)
+        client = axon.AxonRuntime("brk_cli", timeout=3000)
+
+        async def nothing_for_a_tensor(x: np.ndarray) -> np.ndarray:
+            return None
+
+        async def number_for_a_tensor(x: np.ndarray) -> np.ndarray:
+            return 5
+
+        async def fine(x: np.ndarray) -> np.ndarray:
+            return x
+
+        for f in (nothing_for_a_tensor, number_for_a_tensor, fine):
+            server.register_function(f, from_dlpack_fn=np.from_dlpack)
+        server.start_server()
+        client.start_client()
+        await client.connect_endpoint_async(server.get_local_address(), "brk_srv")
+        x = np.arange(4, dtype=np.float32)
+        for name, text in (("nothing_for_a_tensor", "returned None"), ("number_for_a_tensor", "__dlpack__")):
+            with pytest.raises(RuntimeError, match=text):
+                await client.invoke(x, worker_name="brk_srv", session_id=1, function=name, from_dlpack_fn=np.from_dlpack)
+        assert np.array_equal(await client.invoke(x, worker_name="brk_srv", session_id=1, function="fine", from_dlpack_fn=np.from_dlpack), x)
+        client.stop()
+        server.stop()
+
+    run(main())
