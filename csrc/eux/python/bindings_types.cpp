@@ -423,6 +423,10 @@ void bind_types(py::module_& m) {
       .def("serialize", [](const rpc::RpcResponseHeader& h) {
         auto b = rpc::Serialize(h);
         return py::bytes(reinterpret_cast<const char*>(b.data()), b.size());
+      })
+      .def_static("deserialize", [](py::bytes data) {
+        std::string s = data;
+        return rpc::Deserialize<rpc::RpcResponseHeader>(s.data(), s.size());
       });
   py::class_<rpc::RpcFunctionSignature>(m, "RpcFunctionSignature")
       .def_property_readonly("instance_name", [](const rpc::RpcFunctionSignature& s) { return std::string(s.instance_name); })

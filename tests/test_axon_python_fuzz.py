@@ -87,6 +87,18 @@ def test_header_params_survive_the_wire_image(axon):
                 assert (g.encode() if isinstance(g, str) else bytes(g)) == v
             else:
                 assert g == v
+        # the same values as the results of a response
+        r = axon.RpcResponseHeader()
+        r.session_id = sid
+        for v in vals:
+            r.AddResult(v)
+        rback = axon.RpcResponseHeader.deserialize(r.serialize())
+        assert rback.session_id == sid and rback.ok and len(rback.results) == len(vals)
+        for v, g in zip(vals, rback.results):
+            if isinstance(v, bytes):
+                assert (g.encode() if isinstance(g, str) else bytes(g)) == v
+            else:
+                assert g == v
 
     check()
 
