@@ -273,7 +273,12 @@ InvokeSender AxonWorker::InvokeOnConnection(std::optional<uint64_t> conn, std::s
   call->payload = std::move(payload);
   call->mem = std::move(mem_policy);
   try {
-    call->out.emplace(make_message(*mr_, serialize_header(*mr_, header), call->payload));
+    auto image = serialize_header(*mr_, header);
+    if (image.size() > ucxx::transport::kMaxHeaderLen)
+      return ex::just_error<InvokeResult>(rpc_error(rpc::make_error_code(RpcErrc::RESOURCE_EXHAUSTED),
+                                                    "the request header is " + std::to_string(image.size()) + " bytes; a message carries at most " +
+                                                        std::to_string(ucxx::transport::kMaxHeaderLen) + " (large arguments belong in a tensor payload)"));
+    call->out.emplace(make_message(*mr_, std::move(image), call->payload));
     attach_send_attr(*client_ctx_, *call->out, call->payload);
   } catch (const std::exception& e) {
     return ex::just_error<InvokeResult>(rpc_error(errors::make_error_code(errors::AxonErrc::SerializeError), e.what()));

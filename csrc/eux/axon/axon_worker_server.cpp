@@ -289,7 +289,21 @@ void AxonWorker::ServerSendResponse(std::shared_ptr<ServerCall> call, RpcRespons
   auto out = std::make_shared<Out>();
   out->payload = std::move(payload);
   try {
-    out->msg = make_message(*mr_, serialize_header(*mr_, header), out->payload);
+    auto image = serialize_header(*mr_, header);
+    if (image.size() > ucxx::transport::kMaxHeaderLen) {
+      // results too large for a message header (they belong in a payload): the caller hears that, at once,
+      // instead of waiting for its deadline
+      server_pipe_failed_.fetch_add(1);
+      RpcResponseHeader err = rpc::RpcResponseBuilder{}.PrepareError(
+          call->req.session_id, call->req.request_id, rpc::make_error_code(RpcErrc::RESOURCE_EXHAUSTED),
+          "the response header is " + std::to_string(image.size()) + " bytes; a message carries at most " +
+              std::to_string(ucxx::transport::kMaxHeaderLen) + " (large results belong in a tensor payload)");
+      err.hlc = header.hlc;
+      err.workflow_id = header.workflow_id;
+      out->payload = PayloadVariant{};
+      image = serialize_header(*mr_, err);
+    }
+    out->msg = make_message(*mr_, std::move(image), out->payload);
     attach_send_attr(*server_ctx_, out->msg, out->payload);
   } catch (const std::exception& e) {
     server_pipe_failed_.fetch_add(1);

@@ -18,6 +18,12 @@ class AsyncRpcDispatcher {
   explicit AsyncRpcDispatcher(std::string instance_name = "default") : instance_name_(std::move(instance_name)) {}
   const std::string& instance_name() const { return instance_name_; }
 
+  // A handler's return type is taken for a sender when it has the mark of one (a nested value_type) and is not
+  // one of the wire's own containers, which carry the same mark (data::string, data::vector<T>).
+  template <class T>
+  static constexpr bool returns_sender_v = exec::sender<T> && !is_wire_param_v<T> && !is_data_vector<std::remove_cvref_t<T>>::value &&
+                                           !std::is_same_v<std::remove_cvref_t<T>, data::string> && !is_payload_v<std::remove_cvref_t<T>>;
+
   // f(args...) -> value | sender of value. Arguments are filled as in RpcDispatcher.
   template <class F>
   bool RegisterFunction(function_id_t id, F&& f, const data::string& name = {}) {
@@ -28,7 +34,7 @@ class AsyncRpcDispatcher {
     sig.id = id;
     sig.function_name = name;
     detail::signature_of_args<typename Traits::args_tuple>::fill(sig);
-    if constexpr (exec::sender<Ret>) detail::fill_return_signature<exec::value_t<Ret>>(sig);
+    if constexpr (returns_sender_v<Ret>) detail::fill_return_signature<exec::value_t<Ret>>(sig);
     else detail::fill_return_signature<Ret>(sig);
     return insert(id, std::move(sig), MakeAsyncWrapper(std::forward<F>(f)));
   }
@@ -120,7 +126,7 @@ class AsyncRpcDispatcher {
       };
       try {
         RpcContextPtr ctx = RpcContextPtr::of(st->payload, true);
-        if constexpr (exec::sender<Ret>) {
+        if constexpr (returns_sender_v<Ret>) {
           size_t idx = 0;
           auto snd = call(fn, st->req, ctx, st->b, idx, static_cast<Args*>(nullptr), std::make_index_sequence<std::tuple_size_v<Args>>{});
           using V = exec::value_t<Ret>;

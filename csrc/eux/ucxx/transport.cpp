@@ -107,7 +107,6 @@ bool live_has(uint64_t uid) {
 
 // Limits on what a frame may claim. One frame from an unauthenticated socket must not be able to make
 // the receiver buffer or allocate without bound.
-constexpr size_t kMaxHeaderLen = size_t(16) << 20;   // AM header bytes (a serialized RPC header with its parameters)
 constexpr size_t kMaxSegCount = 4096;                // scatter-gather segments per message
 constexpr uint64_t kFdListenerTag = 0xfffffffeu;     // epoll tag of the Unix socket on which descriptor channels are accepted
 // Device regions announced in an RTS: one per allocation that the payload touches. A sender that does
@@ -1226,6 +1225,9 @@ int Worker::am_send(Endpoint* ep, const void* header, size_t header_len, const u
                     ucx_memory_type_t mem_type, bool force_rndv, Completion done, uint64_t* msg_id_out,
                     std::shared_ptr<const SendHint> hint) {
   if (!eps_.count(ep) || ep->state_ != Endpoint::State::kConnected) return UCS_ERR_NOT_CONNECTED;
+  // What the receiving side would refuse (and close the connection over) is not sent in the first place: the
+  // caller gets the error at once and the connection stays.
+  if (header_len > kMaxHeaderLen || seg_count > kMaxSegCount) return UCS_ERR_EXCEEDS_LIMIT;
   size_t total = 0;
   for (size_t i = 0; i < seg_count; ++i) total += segs[i].size;
   const bool device = is_device_type(mem_type);

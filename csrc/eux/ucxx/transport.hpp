@@ -80,6 +80,9 @@ void set_consumer_event_hook(ConsumerEventHook hook);
 bool is_live_local_uid(uint64_t uid);
 
 constexpr uint32_t kFrameMagic = 0x46585545u;  // "EUXF"
+// Most bytes an active-message header may have (a serialized RPC header with its parameters). A longer one is
+// refused by the sender before it leaves and by the receiver when it is announced.
+inline constexpr size_t kMaxHeaderLen = size_t(16) << 20;
 enum FrameType : uint8_t {
   kHello = 1,
   kHelloAck = 2,

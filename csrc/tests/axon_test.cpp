@@ -142,6 +142,44 @@ EUX_TEST(errors_deadline_and_unknown_worker) {
   std::this_thread::sleep_for(350ms);  // let the overrunning handler end before the workers go away
 }
 
+// A header image larger than a message may carry is refused where it is made: the caller of an oversize request
+// gets the error at once, the caller of a function with oversize results gets it as the response, and the
+// connection serves the next call (the receiving side would have closed it over such a frame).
+EUX_TEST(oversize_headers_end_as_errors_and_the_connection_stays) {
+  Pair p;
+  p.server.RegisterFunction(function_id_t{1}, [](int32_t n) -> data::string {
+    const std::string text(static_cast<size_t>(n), 'x');
+    return data::string(text);
+  }, "text");
+  p.server.RegisterFunction(function_id_t{2}, [](const data::string& s) { return int64_t(s.size()); }, "length");
+  p.server.RegisterFunction(function_id_t{3}, [](int32_t n) {
+    data::vector<int64_t> squares;
+    for (int32_t i = 0; i < n; ++i) squares.push_back(int64_t(i) * i);
+    return squares;
+  }, "squares");
+  p.connect();
+  const int32_t too_much = int32_t(eux::ucxx::transport::kMaxHeaderLen + 100);
+  auto ok = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(1 << 20)));
+  CHECK(ok && ok->header.status.ok() && ok->header.GetString(0).size() == size_t(1 << 20));
+  auto t0 = std::chrono::steady_clock::now();
+  auto big = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{1}, workflow_id_t{}, ClientMemoryPolicy{}, too_much));
+  CHECK(big && big->header.status.value == int(RpcErrc::RESOURCE_EXHAUSTED));
+  CHECK(std::chrono::steady_clock::now() - t0 < 1500ms);  // an answer, not the caller's deadline
+  bool refused = false;
+  const std::string oversize(static_cast<size_t>(too_much), 'y');
+  try {
+    ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}, data::string(oversize)));
+  } catch (const RpcException& e) {
+    refused = e.code() == make_error_code(RpcErrc::RESOURCE_EXHAUSTED);
+  }
+  CHECK(refused);
+  auto after = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{2}, workflow_id_t{}, ClientMemoryPolicy{}, data::string("four")));
+  CHECK(after && after->header.status.ok() && after->header.GetPrimitive<int64_t>(0) == 4);
+  // (a function may return one of the wire's containers by itself: they are values, not senders)
+  auto sq = ex::sync_wait(p.client.InvokeRpc("server", session_id_t{1}, function_id_t{3}, workflow_id_t{}, ClientMemoryPolicy{}, int32_t(4)));
+  CHECK(sq && sq->header.status.ok() && (sq->header.GetVector<int64_t>(0) == data::vector<int64_t>{0, 1, 4, 9}));
+}
+
 EUX_TEST(concurrent_calls_and_buffer_vec) {
   Pair p;
   p.server.RegisterFunction(function_id_t{1}, [](int32_t a) { return a * 2; }, "dbl");
