@@ -424,6 +424,71 @@ EUX_TEST(async_handler_value_error_and_void) {
   CHECK(r4 && r4->header.status.value == int(RpcErrc::NOT_FOUND));
 }
 
+// Every kind of return value the synchronous dispatcher takes, through the asynchronous one, plain and as the
+// value of a sender. The wire's own containers (string, vector) have a nested value_type like a sender has: they
+// are values all the same.
+EUX_TEST(async_handlers_return_every_kind_of_value) {
+  DefaultUcxMemoryResourceManager mr;
+  AsyncRpcDispatcher d("async");
+  TensorMeta m;
+  m.ndim = 2;
+  m.dtype = {kDLFloat, 32, 1};
+  m.shape = {2, 3};
+  m.strides = {3, 1};
+  d.RegisterFunction(function_id_t{1}, [](const data::string& s) { return data::string(s.str() + "!"); }, data::string("string"));
+  d.RegisterFunction(function_id_t{2}, [](int32_t n) {
+    data::vector<double> v;
+    for (int32_t i = 0; i < n; ++i) v.push_back(i * 0.5);
+    return v;
+  }, data::string("doubles"));
+  d.RegisterFunction(function_id_t{3}, [](const data::vector<bool>& v) {
+    data::vector<bool> out;
+    for (auto b : v) out.push_back(!bool(b));
+    return out;
+  }, data::string("flip"));
+  d.RegisterFunction(function_id_t{4}, [m](int32_t) { return m; }, data::string("meta"));
+  d.RegisterFunction(function_id_t{5}, [m](int32_t n) { return TensorMetaVec(size_t(n), m); }, data::string("metas"));
+  d.RegisterFunction(function_id_t{6}, [](int32_t x) { return std::tuple<data::string, int64_t, bool>(data::string("t"), int64_t(x) * 2, x > 0); }, data::string("tuple"));
+  d.RegisterFunction(function_id_t{7}, [](int32_t x) { return x > 3; }, data::string("bool"));
+  d.RegisterFunction(function_id_t{8}, [](const data::string& s) { return ex::just(data::string(s.str() + "?")); }, data::string("later_string"));
+  d.RegisterFunction(function_id_t{9}, [](int32_t n) { return ex::just(data::vector<int64_t>(size_t(n), int64_t(7))); }, data::string("later_vector"));
+  d.RegisterFunction(function_id_t{10}, [&mr, m](int32_t) {
+    UcxBuffer out(mr, ucx_memory_type::HOST, 24);
+    std::memset(out.data(), 5, 24);
+    return std::tuple<TensorMeta, UcxBuffer>(m, std::move(out));
+  }, data::string("tensor"));
+  d.RegisterFunction(function_id_t{11}, [](const RpcRequestHeader& rq, const RpcResponseBuilder& b) { return b.PrepareResponse(rq.session_id, rq.request_id, int32_t(1), data::string("two")); },
+                     data::string("header"));
+  RpcRequestBuilder rb;
+  auto call = [&](uint32_t fn, auto&&... args) { return ex::sync_wait(d.Dispatch(rb.PrepareRequest(opt(fn), std::forward<decltype(args)>(args)...))); };
+  auto r1 = call(1, data::string("hi"));
+  CHECK(r1 && r1->header.status.ok() && r1->header.GetString(0) == "hi!");
+  auto r2 = call(2, int32_t(3));
+  CHECK(r2 && (r2->header.GetVector<double>(0) == data::vector<double>{0.0, 0.5, 1.0}));
+  auto r3 = call(3, data::vector<bool>{true, false, true});
+  CHECK(r3 && (r3->header.GetVector<bool>(0) == data::vector<bool>{false, true, false}));
+  auto r4 = call(4, int32_t(0));
+  CHECK(r4 && r4->header.GetTensor(0) == m);
+  auto r5 = call(5, int32_t(3));
+  CHECK(r5 && r5->header.GetTensorVec(0).size() == 3u);
+  auto r6 = call(6, int32_t(21));
+  CHECK(r6 && r6->header.results.size() == 3u && r6->header.GetString(0) == "t" && r6->header.GetPrimitive<int64_t>(1) == 42 && r6->header.GetPrimitive<bool>(2));
+  auto r7 = call(7, int32_t(4));
+  CHECK(r7 && r7->header.GetPrimitive<bool>(0));
+  auto r8 = call(8, data::string("well"));
+  CHECK(r8 && r8->header.GetString(0) == "well?");
+  auto r9 = call(9, int32_t(2));
+  CHECK(r9 && (r9->header.GetVector<int64_t>(0) == data::vector<int64_t>{7, 7}));
+  auto r10 = call(10, int32_t(0));
+  CHECK(r10 && r10->header.GetTensor(0) == m && std::get<UcxBuffer>(r10->payload).size() == 24u);
+  auto r11 = call(11);
+  CHECK(r11 && r11->header.GetPrimitive<int32_t>(0) == 1 && r11->header.GetString(1) == "two");
+  auto sig = d.GetSignature(function_id_t{1});
+  CHECK(sig && (sig->return_types == data::vector<ParamType>{ParamType::STRING}));
+  sig = d.GetSignature(function_id_t{9});
+  CHECK(sig && (sig->return_types == data::vector<ParamType>{ParamType::VECTOR_INT64}));
+}
+
 EUX_TEST(async_handler_with_payload_in_and_out) {
   DefaultUcxMemoryResourceManager mr;
   ex::static_thread_pool pool(1);
