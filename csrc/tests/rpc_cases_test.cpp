@@ -489,6 +489,56 @@ EUX_TEST(async_handlers_return_every_kind_of_value) {
   CHECK(sig && (sig->return_types == data::vector<ParamType>{ParamType::VECTOR_INT64}));
 }
 
+// ... and every kind of argument: by value, by reference, the request itself, the builder, payloads taken over.
+EUX_TEST(async_handlers_take_every_kind_of_argument) {
+  DefaultUcxMemoryResourceManager mr;
+  AsyncRpcDispatcher d("async");
+  d.RegisterFunction(function_id_t{1}, [](bool b, int8_t a, uint16_t c, int64_t e, float f, double g) { return int64_t(b) + a + c + e + int64_t(f) + int64_t(g); },
+                     data::string("numbers"));
+  d.RegisterFunction(function_id_t{2}, [](const data::string& s, const data::vector<int32_t>& v) { return int64_t(s.size() + v.size()); }, data::string("by_reference"));
+  d.RegisterFunction(function_id_t{3}, [](data::string s, data::vector<uint8_t> v) { return int64_t(s.size() * 10 + v.size()); }, data::string("by_value"));
+  d.RegisterFunction(function_id_t{4}, [](const RpcRequestHeader& rq, const TensorMetaVec& metas, UcxBufferVec& bufs, const RpcResponseBuilder& b) {
+    return b.PrepareResponse(rq.session_id, rq.request_id, int64_t(metas.size()), int64_t(bufs.size()), int64_t(bufs[1].size));
+  }, data::string("vec"));
+  d.RegisterFunction(function_id_t{5}, [](const TensorMeta& m, UcxBuffer buf) { return int64_t(utils::CalculateTensorSize(m) + buf.size()); }, data::string("taken"));
+  d.RegisterFunction(function_id_t{6}, [](int32_t k, PayloadVariant&& any) { return int64_t(k) + int64_t(any.index()); }, data::string("variant"));
+  RpcRequestBuilder rb;
+  auto r1 = ex::sync_wait(d.Dispatch(rb.PrepareRequest(opt(1), true, int8_t(-2), uint16_t(300), int64_t(1) << 40, 2.5f, 7.9)));
+  CHECK(r1 && r1->header.status.ok() && r1->header.GetPrimitive<int64_t>(0) == 1 - 2 + 300 + (int64_t(1) << 40) + 2 + 7);
+  auto r2 = ex::sync_wait(d.Dispatch(rb.PrepareRequest(opt(2), data::string("abc"), data::vector<int32_t>{1, 2})));
+  CHECK(r2 && r2->header.GetPrimitive<int64_t>(0) == 5);
+  auto r3 = ex::sync_wait(d.Dispatch(rb.PrepareRequest(opt(3), data::string("ab"), data::vector<uint8_t>{1, 2, 3})));
+  CHECK(r3 && r3->header.GetPrimitive<int64_t>(0) == 23);
+  TensorMeta m;
+  m.ndim = 1;
+  m.dtype = {kDLUInt, 8, 1};
+  m.shape = {4};
+  m.strides = {1};
+  {
+    auto [req, payload] = rb.PrepareRequest(opt(4), TensorMetaVec{m, m}, UcxBufferVec(mr, ucx_memory_type::HOST, std::vector<size_t>{4, 6}));
+    auto r = ex::sync_wait(d.Dispatch(req, std::move(payload)));
+    CHECK(r && r->header.status.ok() && r->header.GetPrimitive<int64_t>(0) == 2 && r->header.GetPrimitive<int64_t>(1) == 2 && r->header.GetPrimitive<int64_t>(2) == 6);
+  }
+  {
+    auto [req, payload] = rb.PrepareRequest(opt(5), m, UcxBuffer(mr, ucx_memory_type::HOST, 4));
+    auto r = ex::sync_wait(d.Dispatch(req, std::move(payload)));
+    CHECK(r && r->header.status.ok() && r->header.GetPrimitive<int64_t>(0) == 8);
+  }
+  {
+    auto [req, payload] = rb.PrepareRequest(opt(6), int32_t(10), UcxBuffer(mr, ucx_memory_type::HOST, 4));
+    auto r = ex::sync_wait(d.Dispatch(req, std::move(payload)));
+    CHECK(r && r->header.status.ok() && r->header.GetPrimitive<int64_t>(0) == 11);
+  }
+  // a description that does not fit its payload never reaches the function
+  {
+    TensorMeta big = m;
+    big.shape = {400};
+    auto [req, payload] = rb.PrepareRequest(opt(5), big, UcxBuffer(mr, ucx_memory_type::HOST, 4));
+    auto r = ex::sync_wait(d.Dispatch(req, std::move(payload)));
+    CHECK(r && r->header.status.value == int(RpcErrc::INVALID_ARGUMENT));
+  }
+}
+
 EUX_TEST(async_handler_with_payload_in_and_out) {
   DefaultUcxMemoryResourceManager mr;
   ex::static_thread_pool pool(1);
