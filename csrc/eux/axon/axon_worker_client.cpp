@@ -187,6 +187,11 @@ struct AxonWorker::invoke_sender {
       // what completes the operation, from whichever thread owns the table entry
       call->finish_value = [this](InvokeResult&& v) {
         stop_cb.reset();
+        // the caller reads the response's tensors by their descriptions: they must lie inside the payload that came
+        if (!rpc::RpcDispatcher::TensorsFitPayload(v.header.results, std::get_if<ucxx::UcxBuffer>(&v.payload), std::get_if<ucxx::UcxBufferVec>(&v.payload))) {
+          r.set_error(rpc_error(rpc::make_error_code(RpcErrc::INVALID_ARGUMENT), "the response's tensor metadata describes more bytes than its payload holds"));
+          return;
+        }
         r.set_value(std::move(v));
       };
       call->finish_error = [this](std::exception_ptr e) {
