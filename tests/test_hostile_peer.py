@@ -1,4 +1,5 @@
-"""Whatever a TCP peer sends, a runtime refuses it or serves it: no crash, no stall, no unbounded allocation.
+"""Whatever a TCP peer sends, a runtime refuses it or serves it: no crash, no stall, no unbounded allocation,
+as a server under hostile clients and as a client of a hostile server.
 (The cases this kind of run has found are pinned one by one in csrc/tests/rpc_test.cpp: counts checked before
 memory is reserved, parameter types that contradict their values, tensor descriptions that are no tensor.)"""
 import os
@@ -15,5 +16,12 @@ ROOT = Path(__file__).resolve().parent.parent
 def test_mutated_client_streams_do_not_bring_the_server_down(native_build, seed):
     env = dict(os.environ, PYTHONPATH=str(ROOT), EUX_LOG_LEVEL="OFF")
     out = subprocess.run([sys.executable, str(ROOT / "tests" / "mp_hostile_peer.py"), str(seed), "600"], env=env, cwd=str(ROOT),
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-1500:] + out.stderr[-3000:]
+
+
+def test_mutated_server_streams_do_not_bring_a_client_down(native_build):
+    env = dict(os.environ, PYTHONPATH=str(ROOT), EUX_LOG_LEVEL="OFF")
+    out = subprocess.run([sys.executable, str(ROOT / "tests" / "mp_hostile_server.py"), "2", "100"], env=env, cwd=str(ROOT),
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout[-1500:] + out.stderr[-3000:]
