@@ -14,6 +14,7 @@
 #include <chrono>
 #include <sys/stat.h>
 #include <sys/un.h>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 
@@ -366,6 +367,7 @@ EUX_TEST(descriptor_channel_socket_is_private_and_ignores_strangers) {
   // A worker that manages device memory listens on a Unix socket over which file descriptors of device
   // allocations travel. The socket is this user's only; a connection that names no endpoint of the worker is
   // closed, and the worker goes on. (No GPU is needed: nothing is allocated.)
+  ::setenv("EUX_SHM", "1", 1);  // the socket belongs to the shared-memory control plane; a run of the tests with it off gets it here
   UcxCudaMemoryResourceManager::Options mo;
   mo.device = 0;
   UcxCudaMemoryResourceManager mr(mo);
